@@ -1,0 +1,198 @@
+// Token sampling for the generation engine: temperature, top-k, top-p, multinomial draw and the
+// log-probability of the drawn token under the *processed* distribution, one CTA per sequence.
+//
+// The draw uses the Gumbel-max construction: argmax_i (z_i / T + g_i) with g_i ~ Gumbel(0,1) is a
+// sample of softmax(z / T). That needs no normalisation and no prefix sums, so the unfiltered case
+// is a single pass over the logits. top-k / top-p turn into a threshold on the logit value, found by
+// bisection over the ordered bit pattern of fp32 (exact, 32 passes over an L2-resident row).
+// Random numbers come from Philox4x32-10 keyed by (seed, step), counter (row, column / 4).
+//
+// Stands in for the vLLM sampler and FlashInfer sampling kernels the reference calls
+// (nemo_rl/models/generation/vllm/vllm_worker.py:641-668) and mirrors the train-side filter
+// semantics of nemo_rl/algorithms/logits_sampling_utils.py:112-210.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+using namespace rlb;
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+  const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+  const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+  c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+}
+__device__ __forceinline__ void philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                           uint32_t k1, uint32_t (&out)[4]) {
+  uint32_t c[4] = {c0, c1, c2, c3};
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    philox_round(c, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c[0]; out[1] = c[1]; out[2] = c[2]; out[3] = c[3];
+}
+__device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
+  // u in (0,1): 24 random bits, centred
+  const float u = (static_cast<float>(bits >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -__logf(-__logf(u));
+}
+// order-preserving map float -> uint
+__device__ __forceinline__ uint32_t f2ord(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ord2f(uint32_t o) {
+  const uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+  return __uint_as_float(u);
+}
+
+template <typename T>
+__device__ __forceinline__ float ldz(const T* p, int i) {
+  return static_cast<float>(p[i]);
+}
+
+struct ArgBest {
+  float key;
+  int idx;
+};
+__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
+  if (b.key > a.key || (b.key == a.key && b.idx < a.idx)) return b;
+  return a;
+}
+__device__ __forceinline__ ArgBest block_argmax(ArgBest v, ArgBest* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest t;
+    t.key = __shfl_xor_sync(0xffffffffu, v.key, o);
+    t.idx = __shfl_xor_sync(0xffffffffu, v.idx, o);
+    v = better(v, t);
+  }
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  ArgBest r = (lane < nw) ? red[lane] : ArgBest{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest t;
+    t.key = __shfl_xor_sync(0xffffffffu, r.key, o);
+    t.idx = __shfl_xor_sync(0xffffffffu, r.idx, o);
+    r = better(r, t);
+  }
+  return r;
+}
+
+// Per-row parameters may be null (then the scalar defaults apply).
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temps,
+              const int* __restrict__ top_ks, const float* __restrict__ top_ps, float def_temp, int def_top_k,
+              float def_top_p, int greedy, unsigned long long seed, unsigned long long step,
+              int* __restrict__ out_tok, float* __restrict__ out_logprob) {
+  __shared__ float red[32];
+  __shared__ ArgBest redb[32];
+  const int row = blockIdx.x;
+  const T* z = logits + static_cast<long long>(row) * row_stride;
+  float temp = temps ? temps[row] : def_temp;
+  const int top_k = top_ks ? top_ks[row] : def_top_k;
+  const float top_p = top_ps ? top_ps[row] : def_top_p;
+  const bool is_greedy = greedy || temp <= 0.f;
+  if (temp <= 0.f) temp = 1.f;
+  const float inv_t = 1.f / temp;
+
+  // pass 1: maximum
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, ldz(z, i));
+  mx = block_max(mx, red);
+
+  // threshold from top-k / top-p (on raw logits; scaling by 1/T > 0 keeps the order)
+  float thr = -INFINITY;
+  const bool need_k = top_k > 0 && top_k < V;
+  const bool need_p = top_p < 1.f;
+  if (need_k || need_p) {
+    float total = 0.f;
+    if (need_p) {
+      for (int i = threadIdx.x; i < V; i += blockDim.x) total += __expf((ldz(z, i) - mx) * inv_t);
+      total = block_sum(total, red);
+    }
+    // Largest threshold x with count(z >= x) >= k and mass(z >= x) >= top_p * total, i.e. the smallest
+    // kept logit. Bisection on the ordered-uint image; invariant: `lo` satisfies the predicate.
+    uint32_t lo = 0u, hi = f2ord(mx);
+    // predicate(hi = max) may already hold (e.g. top_k = 1)
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo + 1u) >> 1);
+      const float x = ord2f(mid);
+      float cnt = 0.f, mass = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = ldz(z, i);
+        if (v >= x) {
+          cnt += 1.f;
+          if (need_p) mass += __expf((v - mx) * inv_t);
+        }
+      }
+      cnt = block_sum(cnt, red);
+      if (need_p) mass = block_sum(mass, red);
+      const bool ok = (!need_k || cnt >= static_cast<float>(top_k)) && (!need_p || mass >= top_p * total);
+      if (ok) lo = mid;
+      else hi = mid - 1u;
+    }
+    thr = ord2f(lo);
+  }
+
+  // pass 2: normaliser over the kept set, and the draw
+  float sum = 0.f;
+  ArgBest best{-INFINITY, 0x7fffffff};
+  const uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  for (int i4 = threadIdx.x * 4; i4 < V; i4 += blockDim.x * 4) {
+    uint32_t rnd[4] = {0, 0, 0, 0};
+    if (!is_greedy)
+      philox4x32(static_cast<uint32_t>(i4 >> 2), static_cast<uint32_t>(row), static_cast<uint32_t>(step),
+                 static_cast<uint32_t>(step >> 32), k0, k1, rnd);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i4 + j;
+      if (i < V) {
+        const float v = ldz(z, i);
+        if (v >= thr) {
+          const float s = (v - mx) * inv_t;
+          sum += __expf(s);
+          const float key = is_greedy ? v : s + gumbel_from_bits(rnd[j]);
+          best = better(best, ArgBest{key, i});
+        }
+      }
+    }
+  }
+  sum = block_sum(sum, red);
+  best = block_argmax(best, redb);
+  if (threadIdx.x == 0) {
+    out_tok[row] = best.idx;
+    if (out_logprob) {
+      const float zt = ldz(z, best.idx);
+      out_logprob[row] = (zt - mx) * inv_t - __logf(sum);
+    }
+  }
+}
+
+}  // namespace
+
+// logits: [B, V] with row stride; dtype 0 = fp32, 1 = bf16. temps / top_ks / top_ps: per-row device arrays
+// or null. Writes the sampled token and (optionally) its log-probability after temperature and filtering.
+RLB_API int rlb_sample(const void* logits, int dtype, long long row_stride, int B, int V, const float* temps,
+                       const int* top_ks, const float* top_ps, float def_temp, int def_top_k, float def_top_p,
+                       int greedy, unsigned long long seed, unsigned long long step, int* out_tok,
+                       float* out_logprob, void* stream) {
+  if (B <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    sample_kernel<float><<<B, 1024, 0, s>>>(reinterpret_cast<const float*>(logits), row_stride, V, temps, top_ks,
+                                           top_ps, def_temp, def_top_k, def_top_p, greedy, seed, step, out_tok,
+                                           out_logprob);
+  else
+    sample_kernel<__nv_bfloat16><<<B, 1024, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V,
+                                                    temps, top_ks, top_ps, def_temp, def_top_k, def_top_p, greedy,
+                                                    seed, step, out_tok, out_logprob);
+  return static_cast<int>(cudaGetLastError());
+}

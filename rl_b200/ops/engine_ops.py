@@ -1,0 +1,119 @@
+"""Operators used by the generation engine: paged KV cache write, paged decode attention, sampling."""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import lib as _L
+from .lib import call, ptr, stream_ptr, use_native
+
+
+def kv_cache_write(qkv: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   Hq: int, Hkv: int, D: int) -> None:
+    """Scatters the k and v heads of a fused [T, (Hq+2Hkv)*D] projection into the paged cache.
+
+    ``slots`` [T] int64: block * block_size + offset of each token (negative: skip).
+    Cache tensors are [num_blocks, Hkv, block_size, D].
+    """
+    block_size = k_cache.shape[2]
+    if not use_native(qkv):
+        T = qkv.shape[0]
+        k = qkv[:, Hq * D : (Hq + Hkv) * D].reshape(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D :].reshape(T, Hkv, D)
+        ok = slots >= 0
+        blk = (slots[ok] // block_size).long()
+        off = (slots[ok] % block_size).long()
+        k_cache[blk, :, off] = k[ok]
+        v_cache[blk, :, off] = v[ok]
+        return
+    call("rlb_kv_cache_write", ptr(qkv), ptr(slots), ptr(k_cache), ptr(v_cache), qkv.shape[0], Hq, Hkv, D,
+         block_size, qkv.stride(0), stream_ptr())
+
+
+def decode_scratch_sizes(B: int, Hq: int, num_splits: int, D: int = 128) -> tuple[int, int]:
+    return B * Hq * num_splits * D, B * Hq * num_splits * 2
+
+
+def choose_splits(B: int, Hkv: int, max_len: int, block_size: int, sm_count: int = 148) -> int:
+    """Enough KV splits to put ~2 CTAs on every SM, never finer than one cache block per split."""
+    ctas = max(1, B * Hkv)
+    want = max(1, (2 * sm_count + ctas - 1) // ctas)
+    return int(max(1, min(want, max(1, max_len // max(block_size, 128)), 32)))
+
+
+def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                 seq_lens: torch.Tensor, Hq: int, Hkv: int, D: int, *, scale: Optional[float] = None,
+                 num_splits: int = 1, scratch: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one query token per sequence against its paged KV. ``q`` [B, Hq*D] (rows may be strided)."""
+    B = q.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    block_size = k_cache.shape[2]
+    if out is None:
+        out = torch.empty((B, Hq * D), dtype=q.dtype, device=q.device)
+    if not use_native(q):
+        g = Hq // Hkv
+        for b in range(B):
+            n = int(seq_lens[b])
+            if n == 0:
+                out[b] = 0
+                continue
+            nb = (n + block_size - 1) // block_size
+            blocks = block_table[b, :nb].long()
+            k = k_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, :n].float()
+            v = v_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, :n].float()
+            qb = q[b, : Hq * D].reshape(Hkv, g, D).float() * scale
+            p = torch.softmax(qb @ k.transpose(1, 2), dim=-1)
+            out[b] = (p @ v).reshape(Hq * D).to(out.dtype)
+        return out
+    po = pml = None
+    if num_splits > 1:
+        if scratch is None:
+            no, nml = decode_scratch_sizes(B, Hq, num_splits, D)
+            scratch = (torch.empty(no, dtype=torch.float32, device=q.device),
+                       torch.empty(nml, dtype=torch.float32, device=q.device))
+        po, pml = scratch
+    call("rlb_paged_decode", ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
+         ptr(seq_lens), B, Hq, Hkv, D, block_size, scale, num_splits, ptr(po), ptr(pml), ptr(out), out.stride(0),
+         stream_ptr())
+    return out
+
+
+def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, greedy: bool = False,
+           seed: int = 0, step: int = 0, temps: Optional[torch.Tensor] = None, top_ks: Optional[torch.Tensor] = None,
+           top_ps: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None):
+    """Draws one token per row of ``logits`` [B, V] and returns (tokens int32 [B], logprobs fp32 [B]); the
+    log-probabilities are those of the distribution after temperature / top-k / top-p."""
+    B, V = logits.shape
+    if not use_native(logits):
+        z = logits.float()
+        t = temperature if temperature > 0 else 1.0
+        z = z / t
+        if top_k and 0 < top_k < V:
+            kth = torch.topk(z, top_k, dim=-1).values[:, -1:]
+            z = z.masked_fill(z < kth, float("-inf"))
+        if top_p < 1.0:
+            sz, si = torch.sort(z, dim=-1, descending=True)
+            probs = torch.softmax(sz, dim=-1)
+            cum = probs.cumsum(-1)
+            drop = (cum - probs) >= top_p  # keep the smallest prefix whose mass reaches top_p
+            sz = sz.masked_fill(drop, float("-inf"))
+            z = torch.full_like(z, float("-inf")).scatter(-1, si, sz)
+        logp = torch.log_softmax(z, dim=-1)
+        if greedy or temperature <= 0:
+            tok = logp.argmax(-1)
+        else:
+            tok = torch.multinomial(logp.exp(), 1, generator=generator).squeeze(-1)
+        return tok.to(torch.int32), logp.gather(-1, tok.long().unsqueeze(-1)).squeeze(-1)
+    assert logits.stride(1) == 1
+    tok = torch.empty(B, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    dtype = 0 if logits.dtype == torch.float32 else 1
+    assert logits.dtype in (torch.float32, torch.bfloat16)
+    call("rlb_sample", ptr(logits), dtype, logits.stride(0), B, V, ptr(temps), ptr(top_ks), ptr(top_ps),
+         float(temperature), int(top_k), float(top_p), int(greedy), seed & (2**64 - 1), step & (2**64 - 1),
+         ptr(tok), ptr(lp), stream_ptr())
+    return tok, lp

@@ -1,0 +1,33 @@
+"""Shared pytest configuration: registers the ``gpu`` marker and skips GPU tests on machines without CUDA."""
+
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """Builds (if needed) and loads the native library; GPU tests must run on it, never on a fallback."""
+    from rl_b200.csrc.build import build_all
+    from rl_b200.ops import lib as L
+
+    if not L.available():
+        build_all()
+    return L.lib()

@@ -1,0 +1,251 @@
+"""Memory-bound kernels (RMSNorm, RoPE, SwiGLU, embedding, AdamW, ClippedPG, sampling, paged decode) against the
+fp32 PyTorch restatement of each operator."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol):
+    err = (a.float() - b.float()).abs().max().item()
+    ref = b.float().abs().max().item() + 1e-6
+    assert err / ref < tol, f"rel err {err / ref:.3e}"
+
+
+def _ref_mode(fn, *args, **kw):
+    """Runs an operator's PyTorch restatement on CPU copies of the arguments."""
+    cpu = [a.detach().cpu() if isinstance(a, torch.Tensor) else a for a in args]
+    return fn(*cpu, **kw)
+
+
+@pytest.mark.parametrize("rows,d", [(7, 64), (513, 4096), (33, 5120), (100, 128)])
+def test_rmsnorm_fwd_bwd(native_lib, rows, d):
+    from rl_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = F.rmsnorm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    yr.backward(g.float())
+    _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 2e-2)
+    _close(w.grad, wr.grad, 2e-2)
+
+
+def test_rmsnorm_residual(native_lib):
+    from rl_b200.ops import functional as F
+
+    x = torch.randn(65, 1024, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(65, 1024, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(1024, device="cuda", dtype=torch.bfloat16)
+    r_ref = (r.float() + x.float()).to(torch.bfloat16)
+    y_ref = F._rmsnorm_ref(r_ref, w, 1e-6)
+    y = F.rmsnorm_residual_(x, r, w, 1e-6)
+    _close(r, r_ref, 1e-6)
+    _close(y, y_ref, 1e-2)
+
+
+def test_rope_and_inverse(native_lib):
+    from rl_b200.ops import functional as F
+
+    T, Hq, Hkv, D = 50, 8, 2, 128
+    x = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 4000, (T,), device="cuda", dtype=torch.int32)
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ref = F._rope_ref(x.clone(), pos, inv_freq, Hq + Hkv, D)
+    x0 = x.clone()
+    y = F.rope(x, pos, inv_freq, Hq + Hkv, D)
+    _close(y, ref, 1e-2)
+    assert torch.equal(y[:, (Hq + Hkv) * D :], x0[:, (Hq + Hkv) * D :])
+    # autograd: gradient of sum(rope(x) * g) is the inverse rotation of g
+    xg = x0.clone().requires_grad_()
+    g = torch.randn_like(x0)
+    (F.rope(xg * 1.0, pos, inv_freq, Hq + Hkv, D) * g).sum().backward()
+    ref_g = F._rope_ref(g, pos, inv_freq, Hq + Hkv, D, sign=-1.0)
+    _close(xg.grad, ref_g, 1e-2)
+
+
+def test_head_rmsnorm(native_lib):
+    from rl_b200.ops import functional as F
+
+    T, Hq, Hkv, D = 40, 4, 2, 128
+    buf = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16).requires_grad_()
+    out = F.head_rmsnorm(buf, w, 0, Hq, D, 1e-6)
+    g = torch.randn_like(out)
+    out.backward(g)
+    bc = buf.detach().cpu().float().requires_grad_()
+    wc = w.detach().cpu().float().requires_grad_()
+    oc = F.head_rmsnorm(bc, wc, 0, Hq, D, 1e-6)
+    oc.backward(g.cpu().float())
+    _close(out.cpu(), oc, 1e-2)
+    _close(buf.grad.cpu(), bc.grad, 2e-2)
+    _close(w.grad.cpu(), wc.grad, 2e-2)
+
+
+def test_swiglu(native_lib):
+    from rl_b200.ops import functional as F
+
+    gu = torch.randn(130, 2 * 688, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = F.swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    a, b = gr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    _close(y, yr, 1e-2)
+    _close(gu.grad, gr.grad, 2e-2)
+
+
+def test_embedding(native_lib):
+    from rl_b200.ops import functional as F
+
+    table = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (4, 33), device="cuda")
+    y = F.embedding(ids, table)
+    assert torch.equal(y, table.detach()[ids])
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref = torch.zeros(1000, 256, device="cuda")
+    ref.index_add_(0, ids.reshape(-1), g.reshape(-1, 256).float())
+    _close(table.grad, ref, 1e-2)
+
+
+@pytest.mark.parametrize("split", [False, True])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_adamw(native_lib, split, gdtype):
+    from rl_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    n = 100_003
+    w0 = torch.randn(n, device="cuda")
+    g = (torch.randn(n, device="cuda") * 0.1).to(gdtype)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    ref = torch.nn.Parameter(w0.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    if split:
+        hi, lo = F.split_master(w0)
+        assert torch.equal(F.join_master(hi, lo), w0)
+        p32 = None
+    else:
+        hi, lo, p32 = torch.empty(n, device="cuda", dtype=torch.bfloat16), None, w0.clone()
+    for step in range(1, 4):
+        ref.grad = g.float().clone()
+        opt.step()
+        F.adamw_step(hi, lo, p32, g, m, v, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    got = F.join_master(hi, lo) if split else p32
+    assert (got - ref.detach()).abs().max().item() < 1e-5
+    assert torch.equal(hi, got.to(torch.bfloat16))
+
+
+def test_sumsq_clip(native_lib):
+    from rl_b200.ops import functional as F
+
+    x = torch.randn(1_000_001, device="cuda")
+    acc = torch.zeros(1, device="cuda")
+    F.sumsq_(x, acc)
+    F.sumsq_(x.to(torch.bfloat16), acc)
+    ref = x.pow(2).sum() + x.to(torch.bfloat16).float().pow(2).sum()
+    assert abs(acc.item() - ref.item()) / ref.item() < 1e-4
+    scale = torch.zeros(1, device="cuda")
+    norm = torch.zeros(1, device="cuda")
+    F.clip_scale(acc, 1.0, 0.5, scale, norm)
+    assert abs(norm.item() - math.sqrt(ref.item())) / norm.item() < 1e-4
+    assert abs(scale.item() - 0.5 / math.sqrt(ref.item())) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sampling_greedy_and_logprob(native_lib, dtype):
+    from rl_b200.ops.engine_ops import sample
+
+    torch.manual_seed(0)
+    B, V = 9, 128256
+    logits = (torch.randn(B, V, device="cuda") * 3).to(dtype)
+    tok, lp = sample(logits, greedy=True)
+    ref = torch.log_softmax(logits.float(), -1)
+    assert torch.equal(tok.long(), logits.float().argmax(-1))
+    assert (lp - ref.gather(-1, tok.long()[:, None])[:, 0]).abs().max().item() < 1e-3
+    # stochastic: logprob consistent with temperature-scaled distribution, tokens differ across steps
+    t1, l1 = sample(logits, temperature=0.7, seed=5, step=1)
+    t2, _ = sample(logits, temperature=0.7, seed=5, step=2)
+    t1b, _ = sample(logits, temperature=0.7, seed=5, step=1)
+    assert torch.equal(t1, t1b) and not torch.equal(t1, t2)
+    ref7 = torch.log_softmax(logits.float() / 0.7, -1)
+    assert (l1 - ref7.gather(-1, t1.long()[:, None])[:, 0]).abs().max().item() < 1e-3
+
+
+def test_sampling_distribution_and_filters(native_lib):
+    from rl_b200.ops.engine_ops import sample
+
+    torch.manual_seed(1)
+    V = 50
+    base = torch.randn(V, device="cuda") * 2
+    n = 20000
+    logits = base[None].repeat(n, 1).contiguous()
+    tok, lp = sample(logits, temperature=1.0, seed=11, step=0)
+    freq = torch.bincount(tok.long(), minlength=V).float() / n
+    p = torch.softmax(base, -1)
+    assert (freq - p).abs().max().item() < 0.015
+    # top-k = 5: only the 5 largest appear and logprobs renormalise over them
+    tok, lp = sample(logits, top_k=5, seed=3, step=0)
+    top5 = torch.topk(base, 5).indices
+    assert set(tok.unique().tolist()) <= set(top5.tolist())
+    ref = torch.log_softmax(base[top5], -1)
+    idx = {int(t): i for i, t in enumerate(top5.tolist())}
+    want = torch.tensor([ref[idx[int(t)]].item() for t in tok[:100].tolist()], device="cuda")
+    assert (lp[:100] - want).abs().max().item() < 1e-3
+    # top-p = 0.6: the kept set is the smallest prefix of the sorted probabilities reaching 0.6
+    tok, lp = sample(logits, top_p=0.6, seed=4, step=0)
+    sp, si = torch.sort(p, descending=True)
+    keep = int(((sp.cumsum(0) - sp) < 0.6).sum().item())
+    assert set(tok.unique().tolist()) <= set(si[:keep].tolist())
+    assert len(tok.unique()) == keep
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 2)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_paged_decode(native_lib, Hq, Hkv, splits):
+    from rl_b200.ops import engine_ops as E
+
+    torch.manual_seed(0)
+    D, bs, nblocks, B = 128, 16, 64, 5
+    kc = torch.randn(nblocks, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(nblocks, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    lens = torch.tensor([1, 17, 100, 160, 33], device="cuda", dtype=torch.int32)
+    perm = torch.randperm(nblocks, device="cuda").to(torch.int32)
+    bt = torch.zeros(B, 12, device="cuda", dtype=torch.int32)
+    c = 0
+    for b in range(B):
+        nb = (int(lens[b]) + bs - 1) // bs
+        bt[b, :nb] = perm[c : c + nb]
+        c += nb
+    q = torch.randn(B, Hq * D, device="cuda", dtype=torch.bfloat16)
+    out = E.paged_decode(q, kc, vc, bt, lens, Hq, Hkv, D, num_splits=splits)
+    ref = E.paged_decode(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), lens.cpu(), Hq, Hkv, D)
+    _close(out.cpu(), ref, 2e-2)
+
+
+def test_kv_cache_write(native_lib):
+    from rl_b200.ops import engine_ops as E
+
+    Hq, Hkv, D, bs = 8, 2, 128, 16
+    T = 37
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(10, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(10 * bs, device="cuda")[:T].to(torch.int64)
+    slots[3] = -1
+    E.kv_cache_write(qkv, slots, kc, vc, Hq, Hkv, D)
+    kr, vr = torch.zeros_like(kc).cpu(), torch.zeros_like(vc).cpu()
+    E.kv_cache_write(qkv.cpu(), slots.cpu(), kr, vr, Hq, Hkv, D)
+    assert torch.equal(kc.cpu(), kr) and torch.equal(vc.cpu(), vr)

@@ -1,0 +1,131 @@
+"""Model / optimizer state on disk: HF safetensors, ``torch.save`` and torch-DCP (distributed checkpoint).
+
+* ``safetensors`` (default): rank 0 writes the HF layout (every rank holds the full bf16 parameters), so the result
+  loads in ``transformers`` and in this package alike. With expert parallelism each rank writes its own experts.
+* ``torch_save``: one ``model.pt`` state dict in HF names.
+* ``dcp``: ``torch.distributed.checkpoint`` of the flat parameter shard per rank (``ModelState`` / ``OptimizerState``
+  style keys), the format of nemo_rl/utils/native_checkpoint.py:68-238; ``convert_dcp_to_hf`` rebuilds HF tensors.
+
+Optimizer state is always sharded: every rank writes ``optimizer/rank_<r>.pt`` (moments + master remainder).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def _rank_world(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
+    from rl_b200.models.hf_io import iter_hf_tensors, save_pretrained
+
+    rank, world = _rank_world(worker.dp_group)
+    fmt = (fmt or "safetensors").lower()
+    if fmt == "dcp":
+        import torch.distributed.checkpoint as dcp
+
+        os.makedirs(path, exist_ok=True)
+        opt = worker.optimizer
+        lo, hi = (opt.lo, opt.hi) if opt is not None else (0, worker.flat.padded)
+        state = {"model": {f"flat.rank{rank}": worker.flat.flat[lo:hi].detach().clone()}}
+        if world > 1:
+            dcp.save(state, checkpoint_id=path)
+        else:
+            dcp.save(state, checkpoint_id=path, no_dist=True)
+        if rank == 0:
+            meta = {"names": worker.flat.names, "offsets": worker.flat.offsets, "numels": worker.flat.numels,
+                    "shapes": [list(s) for s in worker.flat.shapes], "padded": worker.flat.padded, "world": world,
+                    "dtype": str(worker.flat.flat.dtype)}
+            json.dump(meta, open(os.path.join(path, "flat_layout.json"), "w"))
+            worker.model_cfg.save_pretrained(path)
+        return
+    if rank != 0:
+        return
+    if fmt == "torch_save":
+        os.makedirs(path, exist_ok=True)
+        sd = {n: t.detach().cpu().clone() for n, t in iter_hf_tensors(worker.model)}
+        torch.save(sd, os.path.join(path, "model.pt"))
+        worker.model_cfg.save_pretrained(path)
+    else:
+        save_pretrained(worker.model, path)
+
+
+@torch.no_grad()
+def load_weights(worker, path: str) -> None:
+    from rl_b200.models.hf_io import _SafetensorsDir, load_hf_tensors
+
+    rank, world = _rank_world(worker.dp_group)
+    if os.path.exists(os.path.join(path, "flat_layout.json")):
+        import torch.distributed.checkpoint as dcp
+
+        meta = json.load(open(os.path.join(path, "flat_layout.json")))
+        assert meta["world"] == world, "DCP flat shards are tied to the data-parallel size they were written with"
+        opt = worker.optimizer
+        lo, hi = (opt.lo, opt.hi) if opt is not None else (0, worker.flat.padded)
+        state = {"model": {f"flat.rank{rank}": torch.empty_like(worker.flat.flat[lo:hi])}}
+        dcp.load(state, checkpoint_id=path, **({} if world > 1 else {"no_dist": True}))
+        worker.flat.flat[lo:hi].copy_(state["model"][f"flat.rank{rank}"])
+        if world > 1:
+            dist.all_gather_into_tensor(worker.flat.flat, worker.flat.flat[lo:hi].clone(), group=worker.dp_group)
+        return
+    if os.path.exists(os.path.join(path, "model.pt")):
+        sd = torch.load(os.path.join(path, "model.pt"), map_location="cpu")
+        load_hf_tensors(worker.model, sd.get)
+        return
+    reader = _SafetensorsDir(path)
+    load_hf_tensors(worker.model, reader.get)
+
+
+def save_optimizer_shard(worker, path: str) -> None:
+    rank, _ = _rank_world(worker.dp_group)
+    os.makedirs(path, exist_ok=True)
+    sd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in worker.optimizer.state_dict().items()}
+    sd["scheduler"] = worker.scheduler.state_dict() if worker.scheduler is not None else None
+    torch.save(sd, os.path.join(path, f"rank_{rank}.pt"))
+
+
+def load_optimizer_shard(worker, path: str) -> None:
+    rank, _ = _rank_world(worker.dp_group)
+    f = os.path.join(path, f"rank_{rank}.pt")
+    sd = torch.load(f, map_location=worker.device, weights_only=False)
+    worker.optimizer.load_state_dict(sd)
+    if worker.scheduler is not None and sd.get("scheduler") is not None:
+        worker.scheduler.load_state_dict(sd["scheduler"])
+
+
+def convert_dcp_to_hf(dcp_path: str, hf_path: str) -> str:
+    """Offline: DCP flat shards -> HF safetensors directory (examples/converters/convert_dcp_to_hf.py in the reference)."""
+    import torch.distributed.checkpoint as dcp
+
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import save_pretrained
+    from rl_b200.models.transformer import CausalLM
+
+    meta = json.load(open(os.path.join(dcp_path, "flat_layout.json")))
+    cfg = ModelConfig.from_pretrained(dcp_path)
+    dtype = getattr(torch, meta["dtype"].replace("torch.", ""))
+    model = CausalLM(cfg, dtype=dtype, device="cpu", init=False)
+    flat = model.flatten_parameters(align=1)
+    world = meta["world"]
+    shard = meta["padded"] // world
+    full = torch.zeros(meta["padded"], dtype=dtype)
+    state = {"model": {f"flat.rank{r}": torch.empty(shard, dtype=dtype) for r in range(world)}}
+    dcp.load(state, checkpoint_id=dcp_path, no_dist=True)
+    for r in range(world):
+        full[r * shard : (r + 1) * shard] = state["model"][f"flat.rank{r}"]
+    name_to = {n: (o, k) for n, o, k in zip(meta["names"], meta["offsets"], meta["numels"])}
+    with torch.no_grad():
+        for n, o, k, s in flat.named_slices():
+            so, sk = name_to[n]
+            flat.flat[o : o + k].copy_(full[so : so + sk])
+    save_pretrained(model, hf_path)
+    return hf_path

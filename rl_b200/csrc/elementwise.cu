@@ -317,17 +317,19 @@ __global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfl
 }
 
 // ------------------------------------------------------------------ AdamW
-// The fp32 master weight is stored as the bf16 parameter (its round-to-nearest value, the tensor the
-// GEMMs read) plus a signed 16-bit remainder: master_bits = (bf16_bits << 16) + lo. The pair restores
-// the fp32 value exactly, at 4 bytes per parameter instead of 6.
+// The fp32 master weight is stored as the bf16 parameter (the tensor the GEMMs read) plus a signed 16-bit
+// remainder: master_bits = (bf16_bits << 16) + lo. The bf16 half is the master rounded to nearest with ties
+// away from zero, which keeps the remainder inside [-32768, 32767] for every input, so the pair restores
+// the fp32 value exactly at 4 bytes per parameter instead of 6.
 __device__ __forceinline__ float master_join(__nv_bfloat16 hi, int16_t lo) {
   const uint32_t bits = (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16) + static_cast<uint32_t>(static_cast<int32_t>(lo));
   return __uint_as_float(bits);
 }
 __device__ __forceinline__ void master_split(float v, __nv_bfloat16& hi, int16_t& lo) {
-  hi = __float2bfloat16_rn(v);
-  const uint32_t hb = static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16;
-  lo = static_cast<int16_t>(static_cast<int32_t>(__float_as_uint(v) - hb));
+  const uint32_t bits = __float_as_uint(v);
+  const uint32_t hb = (bits + 0x8000u) & 0xFFFF0000u;
+  hi = __ushort_as_bfloat16(static_cast<unsigned short>(hb >> 16));
+  lo = static_cast<int16_t>(static_cast<int32_t>(bits - hb));
 }
 
 struct AdamArgs {
@@ -392,7 +394,7 @@ __global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_nor
 //  2 sum ratio*mask   3 sum clamped ratio*mask   4 sum exp(|gen-prev|)*mask (token_mult_prob_error)
 //  5 sum mask   6 gen_kl_error numerator   7 policy_kl_error numerator   8 sum w_is*mask
 //  9 approx entropy numerator (-sum curr*mask... with IS weight)   10 ratio min  11 ratio max
-//  12 clamped ratio min   13 clamped ratio max   14 js_divergence numerator  15 count of clipped tokens
+//  12 clamped ratio min   13 clamped ratio max   14 js_divergence numerator  15 tokens whose IS weight left the truncation bounds
 struct PGArgs {
   float eps_lo, eps_hi, dual_c;  // dual_c <= 0: no dual clip
   float kl_beta;
@@ -415,7 +417,7 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
   float acc[10];
 #pragma unroll
   for (int i = 0; i < 10; ++i) acc[i] = 0.f;
-  float js = 0.f, nclip = 0.f;
+  float js = 0.f, nclip = 0.f, oob = 0.f;
   float rmin = INFINITY, rmax = -INFINITY, cmin = INFINITY, cmax = -INFINITY;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < T;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -486,7 +488,8 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
     float wis_used = 1.f;
     if (a.use_is) {
       wis_used = wis;
-      if (a.tis_type == 1) wis_used = fminf(wis, a.tis_max);
+      if (a.tis_type != 0 && (wis > a.tis_max || wis < a.tis_min)) oob += mk;
+      if (a.tis_type == 1) wis_used = fminf(fmaxf(wis, a.tis_min), a.tis_max);
       else if (a.tis_type == 2) wis_used = (wis >= a.tis_min && wis <= a.tis_max) ? wis : 0.f;
     }
     grad += wis_used * dloss;
@@ -498,17 +501,29 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
     acc[3] += rc * mk;
     acc[4] += __expf(fabsf(gn - pv)) * mk;
     acc[5] += mk;
-    // gen_kl_error: KL(gen || policy) estimated on generator samples with k3 of (prev - gen)
     {
+      // gen_kl_error: KL(gen || train) estimated with logr = prev - gen; policy_kl_error: the reverse.
       const float d = pv - gn;
-      acc[6] += (__expf(d) - 1.f - d) * mk;
-      // policy_kl_error: KL(policy || gen) with samples re-weighted by wis
-      acc[7] += (wis * d) * mk;
-      // JS estimate: 0.5*(k3(d) + wis*k3(-d)) is a common symmetric proxy
-      js += 0.5f * ((__expf(d) - 1.f - d) + wis * (__expf(-d) - 1.f + d)) * mk;
+      float gk, pk;
+      if (a.kl_type == 1) {
+        gk = -d;
+        pk = d;
+      } else if (a.kl_type == 2) {
+        gk = 0.5f * d * d;
+        pk = gk;
+      } else {
+        gk = __expf(d) - 1.f - d;
+        pk = __expf(-d) - 1.f + d;
+      }
+      acc[6] += gk * mk;
+      acc[7] += pk * mk;
+      // Jensen-Shannon: M = (P_train + P_gen) / 2, JSD = (KL(P_train||M) + KL(P_gen||M)) / 2, k3 estimates
+      const float lm = __logf(0.5f * __expf(pv) + 0.5f * __expf(gn));
+      const float a1 = pv - lm, a2 = gn - lm;
+      js += 0.5f * ((__expf(a1) - 1.f - a1) + (__expf(a2) - 1.f - a2)) * mk;
     }
     acc[8] += wis * mk;
-    acc[9] += -(wis * c) * mk;
+    acc[9] += -(__expf(c - gn) * c) * mk;
     if (mk > 0.f) {
       rmin = fminf(rmin, ratio);
       rmax = fmaxf(rmax, ratio);
@@ -524,7 +539,8 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
   {
     const float s = block_sum(js, red);
     if (threadIdx.x == 0) atomicAdd(sums + 14, s);
-    const float s2 = block_sum(nclip, red);
+    (void)nclip;
+    const float s2 = block_sum(oob, red);
     if (threadIdx.x == 0) atomicAdd(sums + 15, s2);
   }
   // min/max via integer atomics on non-negative floats (ratios are > 0)

@@ -1,0 +1,330 @@
+// Host runtime of the generation engine: paged-KV block manager with reference counts (prefix
+// sharing between the samples of one prompt, copy-on-write of the partial tail block), and a
+// continuous-batching scheduler (admission by free blocks / running limit / prefill token budget,
+// preemption by recompute when blocks run out).
+//
+// The model forward, attention and sampling run as CUDA kernels driven from Python; this file owns
+// the bookkeeping that decides, every step, which sequences prefill, which decode, and where each
+// new token's K/V goes. It is the in-house counterpart of the scheduler and block manager that the
+// reference gets from vLLM (nemo_rl/models/generation/vllm/vllm_worker.py:570-597).
+//
+// Plain C ABI; all handles are opaque pointers. Not thread-safe: one engine, one driver thread.
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <deque>
+#include <unordered_map>
+#include <vector>
+
+#define RLB_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+enum SeqState : int { WAITING = 0, RUNNING = 1, FINISHED = 2 };
+
+struct Seq {
+  long long id = 0;
+  int prompt_len = 0;
+  int max_new = 0;
+  int num_tokens = 0;      // tokens whose K/V is (or is about to be) in the cache
+  int num_generated = 0;
+  int state = WAITING;
+  long long share_with = -1;  // id of a sequence with an identical prompt whose blocks can be shared
+  bool prefilled = false;
+  long long arrival = 0;
+  std::vector<int> blocks;
+};
+
+struct Engine {
+  int num_blocks, block_size, max_running, max_prefill_tokens;
+  std::vector<int> free_list;
+  std::vector<int> refcount;
+  std::unordered_map<long long, Seq> seqs;
+  std::deque<long long> waiting;
+  std::vector<long long> running;
+  long long clock = 0;
+  long long n_preempt = 0;
+  // scratch of the last schedule() call
+  std::vector<long long> prefill_ids, decode_ids, shared_ids;
+  std::vector<int> copy_src, copy_dst;
+
+  int blocks_for(int tokens) const { return (tokens + block_size - 1) / block_size; }
+  int alloc_block() {
+    if (free_list.empty()) return -1;
+    int b = free_list.back();
+    free_list.pop_back();
+    refcount[b] = 1;
+    return b;
+  }
+  void release_block(int b) {
+    if (--refcount[b] == 0) free_list.push_back(b);
+  }
+  void release_seq(Seq& s) {
+    for (int b : s.blocks) release_block(b);
+    s.blocks.clear();
+  }
+  // Grows `s` to hold `tokens` tokens. Returns false (and changes nothing) when blocks run out.
+  bool ensure_capacity(Seq& s, int tokens) {
+    const int need = blocks_for(tokens) - static_cast<int>(s.blocks.size());
+    if (need <= 0) return true;
+    if (static_cast<int>(free_list.size()) < need) return false;
+    for (int i = 0; i < need; ++i) s.blocks.push_back(alloc_block());
+    return true;
+  }
+};
+
+}  // namespace
+
+RLB_API void* rlb_engine_create(int num_blocks, int block_size, int max_running, int max_prefill_tokens) {
+  if (num_blocks <= 0 || block_size <= 0 || max_running <= 0) return nullptr;
+  Engine* e = new Engine();
+  e->num_blocks = num_blocks;
+  e->block_size = block_size;
+  e->max_running = max_running;
+  e->max_prefill_tokens = max_prefill_tokens > 0 ? max_prefill_tokens : (1 << 30);
+  e->refcount.assign(num_blocks, 0);
+  e->free_list.reserve(num_blocks);
+  for (int b = num_blocks - 1; b >= 0; --b) e->free_list.push_back(b);
+  return e;
+}
+
+RLB_API void rlb_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
+
+RLB_API int rlb_engine_num_free_blocks(void* h) { return static_cast<int>(static_cast<Engine*>(h)->free_list.size()); }
+RLB_API int rlb_engine_num_running(void* h) { return static_cast<int>(static_cast<Engine*>(h)->running.size()); }
+RLB_API int rlb_engine_num_waiting(void* h) { return static_cast<int>(static_cast<Engine*>(h)->waiting.size()); }
+RLB_API long long rlb_engine_num_preemptions(void* h) { return static_cast<Engine*>(h)->n_preempt; }
+
+// Adds a request. share_with: id of an earlier request with the same prompt tokens (or -1). Returns 0,
+// or -1 when the id exists / the request can never fit.
+RLB_API int rlb_engine_add(void* h, long long id, int prompt_len, int max_new_tokens, long long share_with) {
+  Engine* e = static_cast<Engine*>(h);
+  if (e->seqs.count(id) || prompt_len <= 0) return -1;
+  if (e->blocks_for(prompt_len + max_new_tokens) > e->num_blocks) return -1;
+  Seq s;
+  s.id = id;
+  s.prompt_len = prompt_len;
+  s.max_new = max_new_tokens;
+  s.share_with = share_with;
+  s.arrival = e->clock++;
+  e->seqs.emplace(id, std::move(s));
+  e->waiting.push_back(id);
+  return 0;
+}
+
+// Plans one engine step.
+//  * running sequences get room for one more token; when blocks run out the most recently arrived
+//    running sequence is preempted (blocks freed, back to the head of the waiting queue, recompute);
+//  * waiting sequences are admitted in order while blocks, the running limit and the prefill token
+//    budget allow. A sequence whose `share_with` partner has been prefilled in an earlier step (or is
+//    being prefilled in this one) reuses the partner's full prompt blocks by reference and receives a
+//    private copy of the partial tail block, so it needs no prefill compute of its own.
+// Counts are returned through n_*; the id lists are read with rlb_engine_get_*.
+RLB_API int rlb_engine_schedule(void* h, int* n_prefill, int* n_shared, int* n_decode, int* n_copies) {
+  Engine* e = static_cast<Engine*>(h);
+  e->prefill_ids.clear();
+  e->decode_ids.clear();
+  e->shared_ids.clear();
+  e->copy_src.clear();
+  e->copy_dst.clear();
+
+  // 1. decode slots for the running set (oldest first so that preemption hits the youngest)
+  std::sort(e->running.begin(), e->running.end(),
+            [&](long long a, long long b) { return e->seqs[a].arrival < e->seqs[b].arrival; });
+  size_t i = 0;
+  while (i < e->running.size()) {
+    Seq& s = e->seqs[e->running[i]];
+    if (e->ensure_capacity(s, s.num_tokens + 1)) {
+      ++i;
+      continue;
+    }
+    // out of blocks: preempt the youngest running sequence (possibly this one)
+    long long victim_id = e->running.back();
+    Seq& v = e->seqs[victim_id];
+    e->release_seq(v);
+    v.state = WAITING;
+    v.prefilled = false;
+    // recompute from scratch: generated tokens become part of the prompt on re-admission
+    v.num_tokens = 0;
+    e->running.pop_back();
+    e->waiting.push_front(victim_id);
+    ++e->n_preempt;
+    if (victim_id == s.id) break;  // everything at and after i is gone
+  }
+  for (long long id : e->running) e->decode_ids.push_back(id);
+
+  // 2. admission
+  int prefill_tokens = 0;
+  while (!e->waiting.empty() && static_cast<int>(e->running.size()) < e->max_running) {
+    const long long id = e->waiting.front();
+    Seq& s = e->seqs[id];
+    const int context = s.prompt_len + s.num_generated;  // recompute includes what was generated
+    Seq* partner = nullptr;
+    if (s.share_with >= 0 && s.num_generated == 0) {
+      auto it = e->seqs.find(s.share_with);
+      if (it != e->seqs.end() && it->second.state == RUNNING && it->second.prefilled &&
+          it->second.prompt_len == s.prompt_len &&
+          static_cast<int>(it->second.blocks.size()) >= e->blocks_for(s.prompt_len))
+        partner = &it->second;
+    }
+    if (partner) {
+      const int full = s.prompt_len / e->block_size;
+      const int total = e->blocks_for(s.prompt_len + 1);
+      const int fresh = total - full;
+      if (static_cast<int>(e->free_list.size()) < fresh) break;
+      for (int b = 0; b < full; ++b) {
+        s.blocks.push_back(partner->blocks[b]);
+        ++e->refcount[partner->blocks[b]];
+      }
+      for (int b = full; b < total; ++b) s.blocks.push_back(e->alloc_block());
+      if (s.prompt_len % e->block_size) {
+        e->copy_src.push_back(partner->blocks[full]);
+        e->copy_dst.push_back(s.blocks[full]);
+      }
+      s.num_tokens = s.prompt_len;
+      s.prefilled = true;
+      s.state = RUNNING;
+      e->shared_ids.push_back(id);
+    } else {
+      if (prefill_tokens > 0 && prefill_tokens + context > e->max_prefill_tokens) break;
+      if (!e->ensure_capacity(s, context + 1)) break;
+      prefill_tokens += context;
+      s.num_tokens = context;
+      s.prefilled = true;  // true once this step's prefill kernels have run; partners see it from the next admission on
+      s.state = RUNNING;
+      e->prefill_ids.push_back(id);
+    }
+    e->running.push_back(id);
+    e->waiting.pop_front();
+  }
+  *n_prefill = static_cast<int>(e->prefill_ids.size());
+  *n_shared = static_cast<int>(e->shared_ids.size());
+  *n_decode = static_cast<int>(e->decode_ids.size());
+  *n_copies = static_cast<int>(e->copy_src.size());
+  return 0;
+}
+
+RLB_API void rlb_engine_get_lists(void* h, long long* prefill_ids, long long* shared_ids, long long* decode_ids,
+                                  int* copy_src, int* copy_dst) {
+  Engine* e = static_cast<Engine*>(h);
+  if (prefill_ids) std::copy(e->prefill_ids.begin(), e->prefill_ids.end(), prefill_ids);
+  if (shared_ids) std::copy(e->shared_ids.begin(), e->shared_ids.end(), shared_ids);
+  if (decode_ids) std::copy(e->decode_ids.begin(), e->decode_ids.end(), decode_ids);
+  if (copy_src) std::copy(e->copy_src.begin(), e->copy_src.end(), copy_src);
+  if (copy_dst) std::copy(e->copy_dst.begin(), e->copy_dst.end(), copy_dst);
+}
+
+// Fills, for `n` sequence ids: the block table rows (padded with 0 to `max_blocks`), the current
+// token counts (context lengths before the step's new token), and the cache slot of the next token.
+RLB_API int rlb_engine_fill_tables(void* h, const long long* ids, int n, int max_blocks, int* block_table,
+                                   int* context_lens, long long* next_slots) {
+  Engine* e = static_cast<Engine*>(h);
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) return -1;
+    const Seq& s = it->second;
+    const int nb = static_cast<int>(s.blocks.size());
+    if (nb > max_blocks) return -2;
+    int* row = block_table + static_cast<long long>(i) * max_blocks;
+    std::memcpy(row, s.blocks.data(), sizeof(int) * nb);
+    std::memset(row + nb, 0, sizeof(int) * (max_blocks - nb));
+    if (context_lens) context_lens[i] = s.num_tokens;
+    if (next_slots) {
+      const int blk = s.num_tokens / e->block_size;
+      next_slots[i] = blk < nb ? static_cast<long long>(s.blocks[blk]) * e->block_size + s.num_tokens % e->block_size
+                               : -1;
+    }
+  }
+  return 0;
+}
+
+// Cache slots of tokens [first, first+count) of one sequence (used by prefill to scatter K/V).
+RLB_API int rlb_engine_fill_slots(void* h, long long id, int first, int count, long long* slots) {
+  Engine* e = static_cast<Engine*>(h);
+  auto it = e->seqs.find(id);
+  if (it == e->seqs.end()) return -1;
+  const Seq& s = it->second;
+  for (int t = 0; t < count; ++t) {
+    const int pos = first + t;
+    const int blk = pos / e->block_size;
+    if (blk >= static_cast<int>(s.blocks.size())) return -2;
+    slots[t] = static_cast<long long>(s.blocks[blk]) * e->block_size + pos % e->block_size;
+  }
+  return 0;
+}
+
+// Records one generated token for every id; `finished[i]` != 0 retires the sequence (its blocks are
+// released). A sequence that reached max_new tokens is retired as well; the return value is the
+// number of sequences retired by this call, and finished[i] is set to 2 for length-retired ones.
+RLB_API int rlb_engine_commit(void* h, const long long* ids, int n, int* finished) {
+  Engine* e = static_cast<Engine*>(h);
+  int retired = 0;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) continue;
+    Seq& s = it->second;
+    ++s.num_tokens;
+    ++s.num_generated;
+    bool done = finished[i] != 0;
+    if (!done && s.num_generated >= s.max_new) {
+      done = true;
+      finished[i] = 2;
+    }
+    if (done) {
+      e->release_seq(s);
+      s.state = FINISHED;
+      e->running.erase(std::remove(e->running.begin(), e->running.end(), s.id), e->running.end());
+      e->seqs.erase(it);
+      ++retired;
+    }
+  }
+  return retired;
+}
+
+// The first sampled token of a freshly prefilled sequence does not occupy a cache slot yet (its K/V
+// is written by the next decode step); this variant counts the token as generated without growing
+// the cached length.
+RLB_API int rlb_engine_commit_first(void* h, const long long* ids, int n, int* finished) {
+  Engine* e = static_cast<Engine*>(h);
+  int retired = 0;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) continue;
+    Seq& s = it->second;
+    ++s.num_generated;
+    bool done = finished[i] != 0;
+    if (!done && s.num_generated >= s.max_new) {
+      done = true;
+      finished[i] = 2;
+    }
+    if (done) {
+      e->release_seq(s);
+      s.state = FINISHED;
+      e->running.erase(std::remove(e->running.begin(), e->running.end(), s.id), e->running.end());
+      e->seqs.erase(it);
+      ++retired;
+    }
+  }
+  return retired;
+}
+
+RLB_API int rlb_engine_seq_info(void* h, long long id, int* num_tokens, int* num_generated, int* state) {
+  Engine* e = static_cast<Engine*>(h);
+  auto it = e->seqs.find(id);
+  if (it == e->seqs.end()) return -1;
+  if (num_tokens) *num_tokens = it->second.num_tokens;
+  if (num_generated) *num_generated = it->second.num_generated;
+  if (state) *state = it->second.state;
+  return 0;
+}
+
+// Drops every request and returns all blocks (end of a generation phase / KV cache invalidation).
+RLB_API void rlb_engine_reset(void* h) {
+  Engine* e = static_cast<Engine*>(h);
+  e->seqs.clear();
+  e->waiting.clear();
+  e->running.clear();
+  e->free_list.clear();
+  std::fill(e->refcount.begin(), e->refcount.end(), 0);
+  for (int b = e->num_blocks - 1; b >= 0; --b) e->free_list.push_back(b);
+}

@@ -52,6 +52,8 @@ struct EpiParams {
   void* C;              // output (EPI_STORE, EPI_DLOGITS)
   long long ldc;        // leading dimension of C in elements
   const float* bias;    // [N] or null
+  const void* residual; // bf16 [M, ldr] added to the result (the residual stream), or null
+  long long ldr;
   int out_fp32;         // EPI_STORE: 1 -> fp32 output
   int accumulate;       // EPI_STORE: 1 -> C += acc
   // vocab-projection epilogues
@@ -243,6 +245,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col + i < N) v[i] += ep.bias[col + i];
+          }
+          if (ep.residual) {
+            const __nv_bfloat16* rsd =
+                reinterpret_cast<const __nv_bfloat16*>(ep.residual) + static_cast<long long>(row) * ep.ldr + col;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col + q * 8 < N) {
+                const uint4 old = *reinterpret_cast<const uint4*>(rsd + q * 8);
+                const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z),
+                             o3 = unpack_bf16x2(old.w);
+                v[q * 8 + 0] += o0.x; v[q * 8 + 1] += o0.y; v[q * 8 + 2] += o1.x; v[q * 8 + 3] += o1.y;
+                v[q * 8 + 4] += o2.x; v[q * 8 + 5] += o2.y; v[q * 8 + 6] += o3.x; v[q * 8 + 7] += o3.y;
+              }
+            }
           }
           if (ep.out_fp32) {
             float* dst = reinterpret_cast<float*>(ep.C) + static_cast<long long>(row) * ep.ldc + col;
@@ -467,6 +483,13 @@ int rlb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
   RlbEncodeTiledFn enc = rlb_get_encode_tiled();
   if (!enc) return -1;
   (void)elem_bytes;
+  // The driver call needs the primary context current on the calling thread. Threads that have made
+  // no runtime call yet (autograd's backward threads) get it bound by a no-op runtime call.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {pitch_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -482,9 +505,11 @@ int rlb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dty
 // code for bad arguments.
 RLB_API int rlb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
-                          int accumulate, const float* bias, int* status, int max_ctas, void* stream) {
+                          int accumulate, const float* bias, const void* residual, long long ldr, int* status,
+                          int max_ctas, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (N % 8)) return -2;
+  if (residual && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -2;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return -3;
   CUtensorMap ta, tb;
@@ -494,6 +519,8 @@ RLB_API int rlb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   ep.C = C;
   ep.ldc = ldc;
   ep.bias = bias;
+  ep.residual = residual;
+  ep.ldr = ldr;
   ep.out_fp32 = out_fp32;
   ep.accumulate = accumulate;
   return dispatch_layout<EPI_STORE>(a_mn_major != 0, b_mn_major != 0, ta, tb, M, N, K, ep, status, max_ctas,

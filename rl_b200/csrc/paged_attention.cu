@@ -245,7 +245,55 @@ int launch_decode(const void* q, long long q_stride, const void* k_cache, const 
   return static_cast<int>(cudaGetLastError());
 }
 
+// Copies whole cache blocks src[i] -> dst[i] in both caches.
+__global__ void block_copy_kernel(__nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                  const int* __restrict__ src, const int* __restrict__ dst, long long elems) {
+  const int pair = blockIdx.y;
+  const long long s = static_cast<long long>(src[pair]) * elems, d = static_cast<long long>(dst[pair]) * elems;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < elems;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    *reinterpret_cast<uint4*>(k_cache + d + i) = *reinterpret_cast<const uint4*>(k_cache + s + i);
+    *reinterpret_cast<uint4*>(v_cache + d + i) = *reinterpret_cast<const uint4*>(v_cache + s + i);
+  }
+}
+
+// out[i, :] = x[idx[i], :], bf16 rows of width d (multiple of 8).
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ out, long long n, int d, long long x_stride,
+                                   long long out_stride) {
+  const int vecs = d / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n * vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vecs;
+    const int c = static_cast<int>(i - r * vecs) * 8;
+    *reinterpret_cast<uint4*>(out + r * out_stride + c) =
+        *reinterpret_cast<const uint4*>(x + static_cast<long long>(idx[r]) * x_stride + c);
+  }
+}
+
 }  // namespace
+
+RLB_API int rlb_block_copy(void* k_cache, void* v_cache, const int* src, const int* dst, int n, long long elems,
+                           void* stream) {
+  if (n <= 0) return 0;
+  if (elems % 8) return -2;
+  dim3 grid(static_cast<unsigned>((elems / 8 + 255) / 256), n);
+  block_copy_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), src, dst, elems);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RLB_API int rlb_gather_rows(const void* x, const int* idx, void* out, long long n, int d, long long x_stride,
+                            long long out_stride, void* stream) {
+  if (n <= 0) return 0;
+  if (d % 8 || x_stride % 8 || out_stride % 8) return -2;
+  long long grid = (n * (d / 8) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  gather_rows_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), idx, reinterpret_cast<__nv_bfloat16*>(out), n, d, x_stride,
+      out_stride);
+  return static_cast<int>(cudaGetLastError());
+}
 
 RLB_API int rlb_kv_cache_write(const void* qkv, const long long* slots, void* k_cache, void* v_cache, long long T,
                                int Hq, int Hkv, int D, int block_size, long long row_stride, void* stream) {

@@ -91,7 +91,9 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temps,
               const int* __restrict__ top_ks, const float* __restrict__ top_ps, float def_temp, int def_top_k,
               float def_top_p, int greedy, unsigned long long seed, unsigned long long step,
-              int* __restrict__ out_tok, float* __restrict__ out_logprob) {
+              const unsigned long long* __restrict__ step_ptr, int* __restrict__ out_tok,
+              float* __restrict__ out_logprob) {
+  if (step_ptr) step = *step_ptr;  // a counter in device memory lets a captured graph draw fresh numbers
   __shared__ float red[32];
   __shared__ ArgBest redb[32];
   const int row = blockIdx.x;
@@ -182,17 +184,17 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
 // or null. Writes the sampled token and (optionally) its log-probability after temperature and filtering.
 RLB_API int rlb_sample(const void* logits, int dtype, long long row_stride, int B, int V, const float* temps,
                        const int* top_ks, const float* top_ps, float def_temp, int def_top_k, float def_top_p,
-                       int greedy, unsigned long long seed, unsigned long long step, int* out_tok,
-                       float* out_logprob, void* stream) {
+                       int greedy, unsigned long long seed, unsigned long long step,
+                       const unsigned long long* step_ptr, int* out_tok, float* out_logprob, void* stream) {
   if (B <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
     sample_kernel<float><<<B, 1024, 0, s>>>(reinterpret_cast<const float*>(logits), row_stride, V, temps, top_ks,
-                                           top_ps, def_temp, def_top_k, def_top_p, greedy, seed, step, out_tok,
-                                           out_logprob);
+                                           top_ps, def_temp, def_top_k, def_top_p, greedy, seed, step, step_ptr,
+                                           out_tok, out_logprob);
   else
     sample_kernel<__nv_bfloat16><<<B, 1024, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V,
                                                     temps, top_ks, top_ps, def_temp, def_top_k, def_top_p, greedy,
-                                                    seed, step, out_tok, out_logprob);
+                                                    seed, step, step_ptr, out_tok, out_logprob);
   return static_cast<int>(cudaGetLastError());
 }

@@ -1,0 +1,618 @@
+"""In-house generation engine: paged KV cache, continuous batching, prompt-prefix sharing between the samples of one
+prompt, CUDA-graph decode, temperature / top-k / top-p sampling with per-token log-probabilities.
+
+The host-side scheduler and block manager are C++ (``rl_b200/csrc/engine.cpp``); the forward pass reuses the policy
+model's own parameters (the engine holds *views* of the trainer's flat bf16 buffer when colocated at TP1, so a weight
+refit is a pointer hand-off) and runs on this repository's kernels. It fills the role that vLLM / SGLang / the mcore
+DynamicInferenceEngine play in the reference (nemo_rl/models/generation/vllm/vllm_worker.py:850-1074).
+
+Token accounting: after a prompt of P tokens is prefilled the cache holds P tokens; the first sampled token enters
+the cache when the next decode step processes it. A decode step feeds each running sequence's last token at
+position ``n = cached tokens``, writes its K/V into slot n and attends over n + 1 tokens.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from rl_b200.models.transformer import CausalLM, PackedBatch
+from rl_b200.ops import engine_ops as E
+from rl_b200.ops import functional as F
+from rl_b200.ops import lib as _L
+
+_P, _I, _LL = C.c_void_p, C.c_int, C.c_longlong
+_ENGINE_SIGS = {
+    "rlb_engine_create": ([_I, _I, _I, _I], C.c_void_p),
+    "rlb_engine_destroy": ([_P], None),
+    "rlb_engine_num_free_blocks": ([_P], _I),
+    "rlb_engine_num_running": ([_P], _I),
+    "rlb_engine_num_waiting": ([_P], _I),
+    "rlb_engine_num_preemptions": ([_P], _LL),
+    "rlb_engine_add": ([_P, _LL, _I, _I, _LL], _I),
+    "rlb_engine_schedule": ([_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I)], _I),
+    "rlb_engine_get_lists": ([_P, _P, _P, _P, _P, _P], None),
+    "rlb_engine_fill_tables": ([_P, _P, _I, _I, _P, _P, _P], _I),
+    "rlb_engine_fill_slots": ([_P, _LL, _I, _I, _P], _I),
+    "rlb_engine_commit": ([_P, _P, _I, _P], _I),
+    "rlb_engine_commit_first": ([_P, _P, _I, _P], _I),
+    "rlb_engine_reset": ([_P], None),
+}
+_bound = False
+
+
+def _bind():
+    global _bound
+    lib = _L.lib()
+    if not _bound:
+        for name, (args, res) in _ENGINE_SIGS.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = res
+        _bound = True
+    return lib
+
+
+class _PyScheduler:
+    """Pure-Python twin of the C++ scheduler (same rules), used when the native library is not built (CPU tests)."""
+
+    def __init__(self, num_blocks, block_size, max_running, max_prefill_tokens):
+        self.nb, self.bs, self.max_running = num_blocks, block_size, max_running
+        self.max_prefill = max_prefill_tokens if max_prefill_tokens > 0 else 1 << 30
+        self.reset()
+
+    def reset(self):
+        self.free = list(range(self.nb - 1, -1, -1))
+        self.ref = [0] * self.nb
+        self.seqs: dict[int, dict] = {}
+        self.waiting: list[int] = []
+        self.running: list[int] = []
+        self.clock = 0
+        self.n_preempt = 0
+
+    def _blocks_for(self, t):
+        return (t + self.bs - 1) // self.bs
+
+    def _alloc(self):
+        b = self.free.pop()
+        self.ref[b] = 1
+        return b
+
+    def _release(self, s):
+        for b in s["blocks"]:
+            self.ref[b] -= 1
+            if self.ref[b] == 0:
+                self.free.append(b)
+        s["blocks"] = []
+
+    def _ensure(self, s, tokens):
+        need = self._blocks_for(tokens) - len(s["blocks"])
+        if need <= 0:
+            return True
+        if len(self.free) < need:
+            return False
+        for _ in range(need):
+            s["blocks"].append(self._alloc())
+        return True
+
+    def add(self, sid, prompt_len, max_new, share_with):
+        if sid in self.seqs or prompt_len <= 0 or self._blocks_for(prompt_len + max_new) > self.nb:
+            return -1
+        self.seqs[sid] = dict(id=sid, prompt_len=prompt_len, max_new=max_new, num_tokens=0, num_generated=0, running=False,
+                              share_with=share_with, prefilled=False, arrival=self.clock, blocks=[])
+        self.clock += 1
+        self.waiting.append(sid)
+        return 0
+
+    def schedule(self):
+        prefill, shared, copies = [], [], []
+        self.running.sort(key=lambda i: self.seqs[i]["arrival"])
+        i = 0
+        while i < len(self.running):
+            s = self.seqs[self.running[i]]
+            if self._ensure(s, s["num_tokens"] + 1):
+                i += 1
+                continue
+            vid = self.running.pop()
+            v = self.seqs[vid]
+            self._release(v)
+            v.update(running=False, prefilled=False, num_tokens=0)
+            self.waiting.insert(0, vid)
+            self.n_preempt += 1
+            if vid == s["id"]:
+                break
+        decode = list(self.running)
+        ptoks = 0
+        while self.waiting and len(self.running) < self.max_running:
+            sid = self.waiting[0]
+            s = self.seqs[sid]
+            context = s["prompt_len"] + s["num_generated"]
+            partner = None
+            if s["share_with"] >= 0 and s["num_generated"] == 0:
+                p = self.seqs.get(s["share_with"])
+                if p and p["running"] and p["prefilled"] and p["prompt_len"] == s["prompt_len"] and len(p["blocks"]) >= self._blocks_for(s["prompt_len"]):
+                    partner = p
+            if partner:
+                full = s["prompt_len"] // self.bs
+                total = self._blocks_for(s["prompt_len"] + 1)
+                if len(self.free) < total - full:
+                    break
+                for b in range(full):
+                    s["blocks"].append(partner["blocks"][b])
+                    self.ref[partner["blocks"][b]] += 1
+                for b in range(full, total):
+                    s["blocks"].append(self._alloc())
+                if s["prompt_len"] % self.bs:
+                    copies.append((partner["blocks"][full], s["blocks"][full]))
+                s.update(num_tokens=s["prompt_len"], prefilled=True, running=True)
+                shared.append(sid)
+            else:
+                if ptoks > 0 and ptoks + context > self.max_prefill:
+                    break
+                if not self._ensure(s, context + 1):
+                    break
+                ptoks += context
+                s.update(num_tokens=context, prefilled=True, running=True)
+                prefill.append(sid)
+            self.running.append(sid)
+            self.waiting.pop(0)
+        return prefill, shared, decode, copies
+
+    def tables(self, ids, max_blocks):
+        bt = torch.zeros((len(ids), max_blocks), dtype=torch.int32)
+        ctx = torch.zeros(len(ids), dtype=torch.int32)
+        slots = torch.full((len(ids),), -1, dtype=torch.int64)
+        for i, sid in enumerate(ids):
+            s = self.seqs[sid]
+            nb = len(s["blocks"])
+            bt[i, :nb] = torch.tensor(s["blocks"], dtype=torch.int32)
+            ctx[i] = s["num_tokens"]
+            blk = s["num_tokens"] // self.bs
+            if blk < nb:
+                slots[i] = s["blocks"][blk] * self.bs + s["num_tokens"] % self.bs
+        return bt, ctx, slots
+
+    def slots(self, sid, first, count):
+        s = self.seqs[sid]
+        return torch.tensor([s["blocks"][(first + t) // self.bs] * self.bs + (first + t) % self.bs for t in range(count)], dtype=torch.int64)
+
+    def commit(self, ids, finished, first=False):
+        out = list(finished)
+        for i, sid in enumerate(ids):
+            s = self.seqs.get(sid)
+            if s is None:
+                continue
+            if not first:
+                s["num_tokens"] += 1
+            s["num_generated"] += 1
+            done = out[i] != 0
+            if not done and s["num_generated"] >= s["max_new"]:
+                done = True
+                out[i] = 2
+            if done:
+                self._release(s)
+                self.running.remove(sid)
+                del self.seqs[sid]
+        return out
+
+    @property
+    def num_free_blocks(self):
+        return len(self.free)
+
+    @property
+    def num_preemptions(self):
+        return self.n_preempt
+
+    def idle(self):
+        return not self.waiting and not self.running
+
+
+class _NativeScheduler:
+    """ctypes front of the C++ scheduler."""
+
+    def __init__(self, num_blocks, block_size, max_running, max_prefill_tokens):
+        self.lib = _bind()
+        self.h = self.lib.rlb_engine_create(num_blocks, block_size, max_running, max_prefill_tokens)
+        if not self.h:
+            raise RuntimeError("engine creation failed")
+        self.bs = block_size
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.lib.rlb_engine_destroy(self.h)
+        except Exception:
+            pass
+
+    def reset(self):
+        self.lib.rlb_engine_reset(self.h)
+
+    def add(self, sid, prompt_len, max_new, share_with):
+        return self.lib.rlb_engine_add(self.h, sid, prompt_len, max_new, share_with)
+
+    def schedule(self):
+        n = [_I(0) for _ in range(4)]
+        self.lib.rlb_engine_schedule(self.h, *[C.byref(x) for x in n])
+        npf, nsh, ndc, ncp = (x.value for x in n)
+        pf = (_LL * max(npf, 1))()
+        sh = (_LL * max(nsh, 1))()
+        dc = (_LL * max(ndc, 1))()
+        cs = (_I * max(ncp, 1))()
+        cd = (_I * max(ncp, 1))()
+        self.lib.rlb_engine_get_lists(self.h, pf, sh, dc, cs, cd)
+        return list(pf[:npf]), list(sh[:nsh]), list(dc[:ndc]), list(zip(cs[:ncp], cd[:ncp]))
+
+    def tables(self, ids, max_blocks, out=None):
+        n = len(ids)
+        if out is None:
+            bt = torch.empty((n, max_blocks), dtype=torch.int32)
+            ctx = torch.empty(n, dtype=torch.int32)
+            slots = torch.empty(n, dtype=torch.int64)
+        else:
+            bt, ctx, slots = out
+        arr = (_LL * n)(*ids)
+        rc = self.lib.rlb_engine_fill_tables(self.h, arr, n, max_blocks, bt.data_ptr(), ctx.data_ptr(), slots.data_ptr())
+        if rc:
+            raise RuntimeError(f"fill_tables failed ({rc}): a sequence outgrew max_blocks={max_blocks}")
+        return bt, ctx, slots
+
+    def slots(self, sid, first, count):
+        out = torch.empty(count, dtype=torch.int64)
+        rc = self.lib.rlb_engine_fill_slots(self.h, sid, first, count, out.data_ptr())
+        if rc:
+            raise RuntimeError(f"fill_slots failed ({rc})")
+        return out
+
+    def commit(self, ids, finished, first=False):
+        n = len(ids)
+        arr = (_LL * n)(*ids)
+        fin = (_I * n)(*[int(x) for x in finished])
+        (self.lib.rlb_engine_commit_first if first else self.lib.rlb_engine_commit)(self.h, arr, n, fin)
+        return list(fin)
+
+    @property
+    def num_free_blocks(self):
+        return self.lib.rlb_engine_num_free_blocks(self.h)
+
+    @property
+    def num_preemptions(self):
+        return self.lib.rlb_engine_num_preemptions(self.h)
+
+    def idle(self):
+        return self.lib.rlb_engine_num_running(self.h) == 0 and self.lib.rlb_engine_num_waiting(self.h) == 0
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0  # 0 or None: off
+    max_new_tokens: int = 128
+    stop_token_ids: Optional[Sequence[int]] = None
+    greedy: bool = False
+    seed: int = 0
+
+
+@dataclass
+class _Request:
+    rid: int
+    prompt: list[int]
+    max_new: int
+    out_tokens: list[int] = field(default_factory=list)
+    out_logprobs: list[float] = field(default_factory=list)
+    finished: bool = False
+    truncated: bool = False
+    share_with: int = -1
+
+
+class GenerationEngine:
+    """Generates continuations for batches of token prompts with the model's current weights."""
+
+    BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+    def __init__(self, model: CausalLM, *, block_size: int = 64, num_blocks: Optional[int] = None,
+                 kv_cache_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.5, max_running: int = 512,
+                 max_prefill_tokens: int = 16384, max_model_len: int = 8192, use_cuda_graphs: bool = True,
+                 logits_fp32: bool = True, tokenizer=None):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.embed_tokens.device
+        self.block_size = block_size
+        self.max_model_len = max_model_len
+        self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size + 1
+        self.max_running = max_running
+        self.max_prefill_tokens = max_prefill_tokens
+        self.tokenizer = tokenizer
+        self.native = self.device.type == "cuda" and _L.available()
+        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe
+        self.logits_dtype = torch.float32 if logits_fp32 else model.dtype
+        c = self.cfg
+        if num_blocks is None:
+            if kv_cache_tokens is not None:
+                num_blocks = (kv_cache_tokens + block_size - 1) // block_size + max_running
+            elif self.device.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(self.device)
+                per_block = 2 * c.num_hidden_layers * c.num_key_value_heads * block_size * c.head_dim * 2
+                num_blocks = max(16, int(free * gpu_memory_utilization) // per_block)
+            else:
+                num_blocks = 256
+        self.num_blocks = int(num_blocks)
+        self.k_cache: Optional[list[torch.Tensor]] = None
+        self.v_cache: Optional[list[torch.Tensor]] = None
+        sched_cls = _NativeScheduler if _L.available() else _PyScheduler
+        self.sched = sched_cls(self.num_blocks, block_size, max_running, max_prefill_tokens)
+        self._graphs: dict[int, tuple] = {}
+        self._static: Optional[dict] = None
+        self._step_counter = 0
+        self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
+
+    # ------------------------------------------------------------------ memory
+    def wake(self) -> None:
+        """Allocates the KV cache (no-op when it is resident)."""
+        if self.k_cache is not None:
+            return
+        c = self.cfg
+        shape = (self.num_blocks, c.num_key_value_heads, self.block_size, c.head_dim)
+        dt = self.model.dtype
+        self.k_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(c.num_hidden_layers)]
+        self.v_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(c.num_hidden_layers)]
+
+    def sleep(self, free_kv_cache: bool = True) -> None:
+        """Ends a generation phase: drops all requests; optionally returns the KV cache memory (captured graphs are
+        tied to the cache addresses and are dropped with it)."""
+        self.sched.reset()
+        if free_kv_cache:
+            self._graphs.clear()
+            self._static = None
+            self.k_cache = self.v_cache = None
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+
+    def kv_cache_bytes(self) -> int:
+        c = self.cfg
+        return 2 * c.num_hidden_layers * self.num_blocks * c.num_key_value_heads * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
+
+    # ------------------------------------------------------------------ model forward (inference)
+    def _layer_tail(self, layer, h, a):
+        eps = self.cfg.rms_norm_eps
+        h = F.linear(a, layer.self_attn.o_proj, None, h)
+        return layer.mlp(F.rmsnorm(h, layer.post_attention_layernorm, eps), h)
+
+    @torch.no_grad()
+    def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor) -> torch.Tensor:
+        m, c = self.model, self.cfg
+        h = F.embedding(batch.input_ids, m.embed_tokens)
+        for li, layer in enumerate(m.layers):
+            x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
+            qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq)
+            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+            a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+            h = self._layer_tail(layer, h, a)
+        hl = E.gather_rows(h, last_idx.to(torch.int32))
+        hl = F.rmsnorm(hl, m.norm, c.rms_norm_eps)
+        return F.gemm(hl, m.output_weight, out_dtype=self.logits_dtype)
+
+    @torch.no_grad()
+    def _decode_forward(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
+        m, c = self.model, self.cfg
+        h = F.embedding(ids, m.embed_tokens)
+        for li, layer in enumerate(m.layers):
+            x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
+            qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq)
+            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+            a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, c.num_attention_heads,
+                               c.num_key_value_heads, c.head_dim, num_splits=num_splits, scratch=scratch)
+            h = self._layer_tail(layer, h, a)
+        h = F.rmsnorm(h, m.norm, c.rms_norm_eps)
+        return F.gemm(h, m.output_weight, out=logits_out, out_dtype=self.logits_dtype)
+
+    # ------------------------------------------------------------------ decode step (eager or CUDA graph)
+    def _static_buffers(self):
+        if self._static is None:
+            B = self.max_running
+            dev = self.device
+            self._static = dict(
+                ids=torch.zeros(B, dtype=torch.int32, device=dev),
+                positions=torch.zeros(B, dtype=torch.int32, device=dev),
+                slots=torch.full((B,), -1, dtype=torch.int64, device=dev),
+                block_table=torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32, device=dev),
+                seq_lens=torch.zeros(B, dtype=torch.int32, device=dev),
+                temps=torch.ones(B, dtype=torch.float32, device=dev),
+                top_ks=torch.zeros(B, dtype=torch.int32, device=dev),
+                top_ps=torch.ones(B, dtype=torch.float32, device=dev),
+                step=torch.zeros(1, dtype=torch.int64, device=dev),
+                tok=torch.zeros(B, dtype=torch.int32, device=dev),
+                lp=torch.zeros(B, dtype=torch.float32, device=dev),
+                host=dict(
+                    ids=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
+                    positions=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
+                    slots=torch.zeros(B, dtype=torch.int64).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int64),
+                    block_table=torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32),
+                    seq_lens=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
+                ),
+            )
+        return self._static
+
+    def _bucket(self, n: int) -> int:
+        for b in self.BUCKETS:
+            if b >= n:
+                return min(b, self.max_running) if b <= self.max_running else n
+        return n
+
+    def _decode_body(self, st, B, sp: SamplingParams, num_splits, scratch):
+        logits = self._decode_forward(st["ids"][:B], st["positions"][:B], st["slots"][:B], st["block_table"][:B],
+                                      st["seq_lens"][:B], num_splits, scratch)
+        E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=sp.seed,
+                 step_tensor=st["step"] if self.native else None, step=self._step_counter, temps=None,
+                 out=(st["tok"][:B], st["lp"][:B]) if self.native else None)
+        return logits
+
+    def _run_decode(self, n: int, sp: SamplingParams, max_ctx: int):
+        st = self._static_buffers()
+        B = self._bucket(n)
+        c = self.cfg
+        num_splits = E.choose_splits(B, c.num_key_value_heads, max(self.max_model_len // 2, 1), self.block_size, self._sm_count) if self.native else 1
+        if not self.native:
+            logits = self._decode_forward(st["ids"][:n].long(), st["positions"][:n], st["slots"][:n], st["block_table"][:n],
+                                          st["seq_lens"][:n], 1, None)
+            gen = torch.Generator().manual_seed(sp.seed * 1000003 + self._step_counter)
+            tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, generator=gen)
+            return tok[:n], lp[:n]
+        key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed)
+        if self.use_graphs:
+            g = self._graphs.get(key)
+            if g is None:
+                no, nml = E.decode_scratch_sizes(B, c.num_attention_heads, num_splits, c.head_dim)
+                scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
+                # warm-up outside capture (sets kernel attributes, sizes the allocator), then capture
+                side = torch.cuda.Stream(device=self.device)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._decode_body(st, B, sp, num_splits, scratch)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._decode_body(st, B, sp, num_splits, scratch)
+                g = (graph, scratch)
+                self._graphs[key] = g
+            g[0].replay()
+        else:
+            no, nml = E.decode_scratch_sizes(B, c.num_attention_heads, num_splits, c.head_dim)
+            scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
+            self._decode_body(st, B, sp, num_splits, scratch)
+        return st["tok"][:n], st["lp"][:n]
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, max_new_tokens: Optional[Sequence[int]] = None,
+                 share_prefixes: bool = True) -> list[_Request]:
+        """Runs all prompts to completion with continuous batching. Returns one record per prompt (in input order)
+        with the generated tokens, their log-probabilities and whether generation was cut by the length limit."""
+        self.wake()
+        self.model.eval()
+        stop = set(int(t) for t in (sp.stop_token_ids or []))
+        reqs: dict[int, _Request] = {}
+        first_of: dict[tuple, int] = {}
+        for i, p in enumerate(prompts):
+            p = [int(t) for t in p]
+            mx = int(max_new_tokens[i]) if max_new_tokens is not None else sp.max_new_tokens
+            mx = max(1, min(mx, self.max_model_len - len(p)))
+            share = -1
+            if share_prefixes:
+                key = tuple(p)
+                if key in first_of:
+                    share = first_of[key]
+                else:
+                    first_of[key] = i
+            reqs[i] = _Request(i, p, mx, share_with=share)
+            if self.sched.add(i, len(p), mx, share) != 0:
+                raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
+        dev = self.device
+        st = self._static_buffers()
+        last_logits: dict[int, torch.Tensor] = {}
+        while not self.sched.idle():
+            prefill, shared, decode, copies = self.sched.schedule()
+            if not prefill and not shared and not decode:
+                raise RuntimeError("scheduler made no progress (KV cache too small for a single request)")
+            # ---- decode the sequences that were already running
+            if decode:
+                t0 = time.perf_counter()
+                n = len(decode)
+                hb = st["host"]
+                if isinstance(self.sched, _NativeScheduler):
+                    self.sched.tables(decode, self.max_blocks_per_seq, out=(hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n]))
+                    ctx = hb["seq_lens"][:n]
+                else:
+                    bt, ctx_t, sl = self.sched.tables(decode, self.max_blocks_per_seq)
+                    hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n] = bt, ctx_t, sl
+                    ctx = hb["seq_lens"][:n]
+                hb["positions"][:n] = ctx
+                max_ctx = int(ctx.max()) + 1
+                hb["seq_lens"][:n] += 1
+                for j, sid in enumerate(decode):
+                    hb["ids"][j] = reqs[sid].out_tokens[-1]
+                B = self._bucket(n)
+                if B > n:  # padding rows: no cache write, empty context
+                    hb["slots"][n:B] = -1
+                    hb["seq_lens"][n:B] = 0
+                    hb["ids"][n:B] = 0
+                    hb["positions"][n:B] = 0
+                    hb["block_table"][n:B] = 0
+                for k in ("ids", "positions", "slots", "block_table", "seq_lens"):
+                    st[k][:B].copy_(hb[k][:B], non_blocking=True)
+                self._step_counter += 1
+                st["step"].fill_(self._step_counter)
+                tok, lp = self._run_decode(n, sp, max_ctx)
+                tok_h, lp_h = tok.cpu().tolist(), lp.cpu().tolist()
+                fin = [1 if t in stop else 0 for t in tok_h]
+                fin = self.sched.commit(decode, fin)
+                for j, sid in enumerate(decode):
+                    r = reqs[sid]
+                    r.out_tokens.append(tok_h[j])
+                    r.out_logprobs.append(lp_h[j])
+                    if fin[j]:
+                        r.finished = True
+                        r.truncated = fin[j] == 2 and tok_h[j] not in stop
+                self.stats["decode_steps"] += 1
+                self.stats["generated_tokens"] += n
+                self.stats["decode_s"] += time.perf_counter() - t0
+            # ---- prefill newly admitted sequences (and recomputed ones)
+            if prefill or shared:
+                t0 = time.perf_counter()
+                if prefill:
+                    toks, lens, slots = [], [], []
+                    for sid in prefill:
+                        r = reqs[sid]
+                        seq = r.prompt + r.out_tokens
+                        toks.extend(seq)
+                        lens.append(len(seq))
+                        slots.append(self.sched.slots(sid, 0, len(seq)))
+                    ids = torch.tensor(toks, dtype=torch.int32 if self.native else torch.int64, device=dev)
+                    lens_t = torch.tensor(lens, dtype=torch.int64)
+                    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+                    cu[1:] = lens_t.cumsum(0)
+                    pos = torch.cat([torch.arange(L, dtype=torch.int32) for L in lens]).to(dev)
+                    batch = PackedBatch(ids, pos, cu.to(dev), max(lens))
+                    last_idx = (cu[1:] - 1).to(dev)
+                    logits = self._prefill_forward(batch, torch.cat(slots).to(dev), last_idx)
+                    for j, sid in enumerate(prefill):
+                        last_logits[sid] = logits[j]
+                    self.stats["prefill_tokens"] += len(toks)
+                if copies:
+                    src = torch.tensor([a for a, _ in copies], dtype=torch.int32, device=dev)
+                    dst = torch.tensor([b for _, b in copies], dtype=torch.int32, device=dev)
+                    for li in range(self.cfg.num_hidden_layers):
+                        E.block_copy(self.k_cache[li], self.v_cache[li], src, dst)
+                new = list(prefill) + list(shared)
+                rows = torch.stack([last_logits[sid] if sid in last_logits else last_logits[reqs[sid].share_with] for sid in new])
+                self._step_counter += 1
+                if self.native:
+                    tok, lp = E.sample(rows.contiguous(), temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p,
+                                       greedy=sp.greedy, seed=sp.seed, step=self._step_counter)
+                else:
+                    gen = torch.Generator().manual_seed(sp.seed * 1000003 + self._step_counter)
+                    tok, lp = E.sample(rows, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, generator=gen)
+                tok_h, lp_h = tok.cpu().tolist(), lp.cpu().tolist()
+                fin = [1 if t in stop else 0 for t in tok_h]
+                fin = self.sched.commit(new, fin, first=True)
+                for j, sid in enumerate(new):
+                    r = reqs[sid]
+                    r.out_tokens.append(tok_h[j])
+                    r.out_logprobs.append(lp_h[j])
+                    if fin[j]:
+                        r.finished = True
+                        r.truncated = fin[j] == 2 and tok_h[j] not in stop
+                # logits of a prompt are kept while siblings that share it may still be admitted
+                pending_partners = {reqs[s].share_with for s in reqs if not reqs[s].out_tokens and reqs[s].share_with >= 0}
+                for sid in list(last_logits):
+                    if sid not in pending_partners:
+                        del last_logits[sid]
+                self.stats["generated_tokens"] += len(new)
+                self.stats["prefill_s"] += time.perf_counter() - t0
+        return [reqs[i] for i in range(len(prompts))]

@@ -1,0 +1,150 @@
+"""Generation facade: the token-in / token-out contract of the algorithms over the in-house engine.
+
+``generate(data, greedy)`` takes right-padded ``input_ids`` [B, S] with ``input_lengths`` [B] and returns
+``output_ids`` [B, S'] (prompt + response, right-padded), ``generation_lengths``, ``unpadded_sequence_lengths``,
+``logprobs`` [B, S'] (zero on prompt and padding positions) and ``truncated`` — the shapes and meanings of
+nemo_rl/models/generation/interfaces.py:291-380 and :392-527. Backends such as vLLM or SGLang are not wrapped: this
+engine is the generation backend.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+
+from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+from .engine import GenerationEngine, SamplingParams
+
+GENERATION_DEFAULTS = dict(
+    backend="native",
+    max_new_tokens=512,
+    temperature=1.0,
+    top_p=1.0,
+    top_k=None,
+    stop_token_ids=None,
+    stop_strings=None,
+    block_size=64,
+    gpu_memory_utilization=0.5,
+    kv_cache_tokens=None,
+    max_model_len=None,
+    max_running=512,
+    max_prefill_tokens=16384,
+    use_cuda_graphs=True,
+    free_kv_cache_on_sleep=False,
+    seed=0,
+)
+
+
+def configure_generation_config(cfg: Optional[dict], tokenizer=None, is_eval: bool = False) -> dict:
+    """Fills defaults: pad id and stop ids from the tokenizer's eos (the job of
+    nemo_rl/models/generation/__init__.py:27-107)."""
+    out = dict(GENERATION_DEFAULTS)
+    out.update(cfg or {})
+    if tokenizer is not None:
+        out.setdefault("_pad_token_id", tokenizer.pad_token_id)
+        if out.get("stop_token_ids") is None and getattr(tokenizer, "eos_token_id", None) is not None:
+            out["stop_token_ids"] = [tokenizer.eos_token_id]
+    out.setdefault("_pad_token_id", 0)
+    return out
+
+
+def verify_right_padding(data: BatchedDataDict, pad_value: int = 0) -> tuple[bool, str]:
+    """Checks that every row of ``input_ids`` holds its tokens first and padding last."""
+    ids = data["input_ids"]
+    key = "input_lengths" if "input_lengths" in data else "unpadded_sequence_lengths"
+    lens = data[key]
+    B, S = ids.shape
+    if (lens > S).any() or (lens < 0).any():
+        return False, "lengths outside [0, S]"
+    ar = torch.arange(S, device=ids.device)[None, :]
+    pad_region = ar >= lens.to(ids.device)[:, None]
+    if pad_region.any() and (ids[pad_region] != pad_value).any():
+        return False, "non-pad token after the sequence end (left-padded input?)"
+    return True, ""
+
+
+class NativeGeneration:
+    """Driver-facing generation object (one per GPU rank in the SPMD runtime)."""
+
+    def __init__(self, model, cfg: Optional[dict] = None, tokenizer=None):
+        self.cfg = configure_generation_config(cfg, tokenizer)
+        c = self.cfg
+        self.tokenizer = tokenizer
+        self.pad_id = int(c["_pad_token_id"] or 0)
+        self.engine = GenerationEngine(
+            model, block_size=c["block_size"], kv_cache_tokens=c["kv_cache_tokens"],
+            gpu_memory_utilization=c["gpu_memory_utilization"], max_running=c["max_running"],
+            max_prefill_tokens=c["max_prefill_tokens"], max_model_len=c["max_model_len"] or 8192,
+            use_cuda_graphs=c["use_cuda_graphs"], tokenizer=tokenizer)
+        self._calls = 0
+
+    # lifecycle hooks of the generation contract
+    def prepare_for_generation(self, *args, **kw) -> bool:
+        self.engine.wake()
+        return True
+
+    def finish_generation(self, *args, **kw) -> bool:
+        self.engine.sleep(free_kv_cache=bool(self.cfg["free_kv_cache_on_sleep"]))
+        return True
+
+    def invalidate_kv_cache(self) -> bool:
+        self.engine.sched.reset()
+        return True
+
+    def shutdown(self) -> bool:
+        self.engine.sleep(True)
+        return True
+
+    def _sampling(self, greedy: bool) -> SamplingParams:
+        c = self.cfg
+        self._calls += 1
+        return SamplingParams(temperature=float(c["temperature"]), top_p=float(c["top_p"]), top_k=int(c["top_k"] or 0),
+                              max_new_tokens=int(c["max_new_tokens"]), stop_token_ids=c["stop_token_ids"], greedy=greedy,
+                              seed=int(c["seed"]) * 7919 + self._calls)
+
+    def generate(self, data: BatchedDataDict, greedy: bool = False) -> BatchedDataDict:
+        ids, lens = data["input_ids"], data["input_lengths"]
+        B = ids.shape[0]
+        lens_l = lens.tolist()
+        ids_cpu = ids.cpu()
+        prompts = [ids_cpu[i, : lens_l[i]].tolist() for i in range(B)]
+        sp = self._sampling(greedy)
+        recs = self.engine.generate(prompts, sp)
+        stop_strings = data.get("stop_strings") or self.cfg.get("stop_strings")
+        if stop_strings and self.tokenizer is not None:
+            self._apply_stop_strings(recs, stop_strings)
+        out_len = max(len(r.prompt) + len(r.out_tokens) for r in recs) if recs else 0
+        out_ids = torch.full((B, out_len), self.pad_id, dtype=torch.long)
+        logprobs = torch.zeros((B, out_len), dtype=torch.float32)
+        gen_lens = torch.zeros(B, dtype=torch.long)
+        tot_lens = torch.zeros(B, dtype=torch.long)
+        trunc = torch.zeros(B, dtype=torch.bool)
+        for i, r in enumerate(recs):
+            P, G = len(r.prompt), len(r.out_tokens)
+            out_ids[i, :P] = torch.tensor(r.prompt, dtype=torch.long)
+            out_ids[i, P : P + G] = torch.tensor(r.out_tokens, dtype=torch.long)
+            logprobs[i, P : P + G] = torch.tensor(r.out_logprobs, dtype=torch.float32)
+            gen_lens[i], tot_lens[i], trunc[i] = G, P + G, r.truncated
+        return BatchedDataDict({"output_ids": out_ids, "generation_lengths": gen_lens,
+                                "unpadded_sequence_lengths": tot_lens, "logprobs": logprobs, "truncated": trunc})
+
+    def _apply_stop_strings(self, recs, stop_strings) -> None:
+        """Cuts each response at the first token whose decoded prefix contains a stop string."""
+        per_sample = isinstance(stop_strings, list) and stop_strings and isinstance(stop_strings[0], (list, type(None)))
+        for i, r in enumerate(recs):
+            ss = stop_strings[i] if per_sample else stop_strings
+            if not ss:
+                continue
+            text = ""
+            for t in range(len(r.out_tokens)):
+                text = self.tokenizer.decode(r.out_tokens[: t + 1])
+                if any(s in text for s in ss):
+                    r.out_tokens = r.out_tokens[: t + 1]
+                    r.out_logprobs = r.out_logprobs[: t + 1]
+                    r.truncated = False
+                    break
+
+    def stats(self) -> dict[str, Any]:
+        return dict(self.engine.stats)

@@ -1,0 +1,198 @@
+"""Architecture description for the decoder-only model families the framework trains and serves.
+
+One dataclass covers Llama (2/3/3.1/3.2), Mistral, Qwen2/2.5, Qwen3 and Qwen3-MoE; the differences are switches
+(QKV bias, per-head q/k RMSNorm, tied embeddings, RoPE scaling, mixture-of-experts FFN). ``from_hf_dict`` reads a
+HuggingFace ``config.json`` dictionary; ``PRESETS`` names the architectures used by the benchmark configs.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any, Optional
+
+import torch
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None
+    max_position_embeddings: int = 131072
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False       # Qwen2: bias on q/k/v projections
+    qk_norm: bool = False              # Qwen3: RMSNorm over head_dim on q and k before RoPE
+    # mixture of experts (Qwen3-MoE): num_experts > 0 replaces the dense FFN
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    bos_token_id: Optional[int] = None
+    eos_token_id: Optional[Any] = None
+    pad_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+    value_head: bool = False           # critic / reward model: scalar head instead of the vocabulary projection
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def qkv_size(self) -> int:
+        return self.q_size + 2 * self.kv_size
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def num_parameters(self) -> int:
+        d, L = self.hidden_size, self.num_hidden_layers
+        attn = d * self.qkv_size + self.q_size * d + (self.qkv_size if self.attention_bias else 0)
+        if self.is_moe:
+            ffn = self.num_experts * 3 * d * self.moe_intermediate_size + self.num_experts * d
+        else:
+            ffn = 3 * d * self.intermediate_size
+        norms = 2 * d + (2 * self.head_dim if self.qk_norm else 0)
+        emb = self.vocab_size * d * (1 if self.tie_word_embeddings else 2)
+        return L * (attn + ffn + norms) + emb + d
+
+    def to_hf_dict(self) -> dict:
+        arch = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
+                "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+        d = asdict(self)
+        d.pop("value_head")
+        d.pop("qk_norm")
+        d["architectures"] = [arch]
+        if not self.is_moe:
+            for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob", "router_aux_loss_coef"):
+                d.pop(k)
+        return d
+
+    @classmethod
+    def from_hf_dict(cls, hf: dict, **overrides) -> "ModelConfig":
+        mt = hf.get("model_type", "llama")
+        n_heads = hf["num_attention_heads"]
+        cfg = cls(
+            model_type=mt,
+            vocab_size=hf["vocab_size"],
+            hidden_size=hf["hidden_size"],
+            intermediate_size=hf.get("intermediate_size", 0),
+            num_hidden_layers=hf["num_hidden_layers"],
+            num_attention_heads=n_heads,
+            num_key_value_heads=hf.get("num_key_value_heads", n_heads),
+            head_dim=hf.get("head_dim") or hf["hidden_size"] // n_heads,
+            rms_norm_eps=hf.get("rms_norm_eps", 1e-5),
+            rope_theta=float(hf.get("rope_theta", 10000.0)),
+            rope_scaling=hf.get("rope_scaling"),
+            max_position_embeddings=hf.get("max_position_embeddings", 131072),
+            tie_word_embeddings=bool(hf.get("tie_word_embeddings", False)),
+            attention_bias=bool(hf.get("attention_bias", mt == "qwen2")),
+            qk_norm=mt in ("qwen3", "qwen3_moe"),
+            num_experts=hf.get("num_experts", 0) if mt.endswith("_moe") else 0,
+            num_experts_per_tok=hf.get("num_experts_per_tok", 0),
+            moe_intermediate_size=hf.get("moe_intermediate_size", 0),
+            norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
+            router_aux_loss_coef=float(hf.get("router_aux_loss_coef", 0.0)),
+            bos_token_id=hf.get("bos_token_id"),
+            eos_token_id=hf.get("eos_token_id"),
+            pad_token_id=hf.get("pad_token_id"),
+            torch_dtype=str(hf.get("torch_dtype", hf.get("dtype", "bfloat16"))),
+        )
+        for k, v in overrides.items():
+            setattr(cfg, k, v)
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str, **overrides) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_hf_dict(json.load(f), **overrides)
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.to_hf_dict(), f, indent=2)
+
+
+def rope_inv_freq(cfg: ModelConfig, device=None) -> torch.Tensor:
+    """Inverse frequencies [head_dim/2] including the ``llama3`` / ``linear`` / ``yarn`` scaling rules."""
+    D = cfg.head_dim
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    rs = cfg.rope_scaling or {}
+    kind = rs.get("rope_type", rs.get("type", "default"))
+    if kind == "linear":
+        inv = inv / float(rs["factor"])
+    elif kind == "llama3":
+        factor, lo_f, hi_f = rs["factor"], rs.get("low_freq_factor", 1.0), rs.get("high_freq_factor", 4.0)
+        old = rs.get("original_max_position_embeddings", 8192)
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen) - lo_f) / (hi_f - lo_f)
+        scaled = torch.where(wavelen > old / lo_f, inv / factor, inv)
+        mid = (1 - smooth) * inv / factor + smooth * inv
+        is_mid = (wavelen <= old / lo_f) & (wavelen >= old / hi_f)
+        inv = torch.where(is_mid, mid, scaled)
+    elif kind == "yarn":
+        factor = float(rs["factor"])
+        old = rs.get("original_max_position_embeddings", cfg.max_position_embeddings)
+        beta_fast, beta_slow = rs.get("beta_fast", 32.0), rs.get("beta_slow", 1.0)
+
+        def corr_dim(rot):
+            return (D * math.log(old / (rot * 2 * math.pi))) / (2 * math.log(cfg.rope_theta))
+
+        lo = max(math.floor(corr_dim(beta_fast)), 0)
+        hi = min(math.ceil(corr_dim(beta_slow)), D // 2 - 1)
+        ramp = ((torch.arange(D // 2, dtype=torch.float32) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+        inv = inv / factor * ramp + inv * (1 - ramp)
+    return inv.to(device) if device is not None else inv
+
+
+PRESETS: dict[str, dict] = {
+    # Llama-3.1-8B: 32 layers, d 4096, GQA 32q/8kv, SwiGLU 14336, vocab 128256, RoPE theta 5e5 (llama3 scaling)
+    "llama3.1-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                        num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                        rms_norm_eps=1e-5, rope_theta=500000.0,
+                        rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                          original_max_position_embeddings=8192),
+                        bos_token_id=128000, eos_token_id=128001),
+    "llama3.2-1b": dict(model_type="llama", vocab_size=128256, hidden_size=2048, intermediate_size=8192,
+                        num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                        rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True,
+                        rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                          original_max_position_embeddings=8192)),
+    "qwen3-32b": dict(model_type="qwen3", vocab_size=151936, hidden_size=5120, intermediate_size=25600,
+                      num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                      rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True),
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                          num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                          rms_norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True, num_experts=128,
+                          num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True),
+    "qwen2.5-0.5b": dict(model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
+                         num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
+                         rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=True, tie_word_embeddings=True),
+    # the CPU/gloo oracle model: 4 layers, d 256, 4 heads, SwiGLU 688, vocab 2048
+    "tiny-llama-oracle": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
+                              num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
+                              rms_norm_eps=1e-5, rope_theta=10000.0),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    cfg = ModelConfig(**PRESETS[name])
+    for k, v in overrides.items():
+        setattr(cfg, k, v)
+    return cfg

@@ -1,0 +1,183 @@
+"""HuggingFace checkpoint interchange: safetensors in HF tensor names <-> this package's fused parameters.
+
+The on-disk contract is the HF layout (``config.json`` + ``model-0000x-of-0000y.safetensors`` +
+``model.safetensors.index.json``) with per-projection names (``q_proj``, ``k_proj``, ``v_proj``, ``gate_proj``,
+``up_proj``...). In memory q/k/v and gate/up are fused, and MoE experts are stacked; this module is the single place
+that knows both namings. The same mapping names the logical tensors of a weight refit
+(nemo_rl/models/policy/workers/dtensor_policy_worker_v2.py:1074 ships HF names as the wire format).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Callable, Iterator, Optional
+
+import torch
+
+from .config import ModelConfig
+from .transformer import CausalLM
+
+
+def hf_name_map(cfg: ModelConfig) -> list[tuple[str, str, Optional[tuple[int, int]], Optional[int]]]:
+    """Rows of (hf_name, local_name, row_range or None, expert index or None): the HF tensor is rows
+    ``row_range`` of the local tensor (of local expert ``e`` when the local tensor is expert-stacked)."""
+    rows = [("model.embed_tokens.weight", "embed_tokens", None, None), ("model.norm.weight", "norm", None, None)]
+    if cfg.value_head:
+        rows.append(("score.weight", "score", (0, 1), None))
+    elif not cfg.tie_word_embeddings:
+        rows.append(("lm_head.weight", "lm_head", None, None))
+    q, kv = cfg.q_size, cfg.kv_size
+    for i in range(cfg.num_hidden_layers):
+        hp, lp = f"model.layers.{i}", f"layers.{i}"
+        rows += [
+            (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None),
+            (f"{hp}.post_attention_layernorm.weight", f"{lp}.post_attention_layernorm", None, None),
+            (f"{hp}.self_attn.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, q), None),
+            (f"{hp}.self_attn.k_proj.weight", f"{lp}.self_attn.qkv_proj", (q, q + kv), None),
+            (f"{hp}.self_attn.v_proj.weight", f"{lp}.self_attn.qkv_proj", (q + kv, q + 2 * kv), None),
+            (f"{hp}.self_attn.o_proj.weight", f"{lp}.self_attn.o_proj", None, None),
+        ]
+        if cfg.attention_bias:
+            rows += [
+                (f"{hp}.self_attn.q_proj.bias", f"{lp}.self_attn.qkv_bias", (0, q), None),
+                (f"{hp}.self_attn.k_proj.bias", f"{lp}.self_attn.qkv_bias", (q, q + kv), None),
+                (f"{hp}.self_attn.v_proj.bias", f"{lp}.self_attn.qkv_bias", (q + kv, q + 2 * kv), None),
+            ]
+        if cfg.qk_norm:
+            rows += [(f"{hp}.self_attn.q_norm.weight", f"{lp}.self_attn.q_norm", None, None),
+                     (f"{hp}.self_attn.k_norm.weight", f"{lp}.self_attn.k_norm", None, None)]
+        if cfg.is_moe:
+            f = cfg.moe_intermediate_size
+            rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None))
+            for e in range(cfg.num_experts):
+                rows += [
+                    (f"{hp}.mlp.experts.{e}.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), e),
+                    (f"{hp}.mlp.experts.{e}.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), e),
+                    (f"{hp}.mlp.experts.{e}.down_proj.weight", f"{lp}.mlp.down_proj", None, e),
+                ]
+        else:
+            f = cfg.intermediate_size
+            rows += [
+                (f"{hp}.mlp.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), None),
+                (f"{hp}.mlp.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), None),
+                (f"{hp}.mlp.down_proj.weight", f"{lp}.mlp.down_proj", None, None),
+            ]
+    return rows
+
+
+def _local(model: CausalLM) -> dict[str, torch.Tensor]:
+    return dict(model.named_parameters())
+
+
+def iter_hf_tensors(model: CausalLM, ep_rank: int = 0, ep_size: int = 1) -> Iterator[tuple[str, torch.Tensor]]:
+    """Yields (hf_name, tensor view) for every logical HF tensor held by this model instance."""
+    cfg = model.cfg
+    params = _local(model)
+    per = cfg.num_experts // ep_size if cfg.is_moe else 0
+    for hf, loc, rows, e in hf_name_map(cfg):
+        p = params[loc]
+        if e is not None:
+            if not (ep_rank * per <= e < (ep_rank + 1) * per):
+                continue
+            p = p[e - ep_rank * per]
+        yield hf, (p if rows is None else p[rows[0] : rows[1]])
+
+
+@torch.no_grad()
+def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]], strict: bool = True,
+                    ep_rank: int = 0, ep_size: int = 1) -> list[str]:
+    """Copies HF-named tensors (as returned by ``get(name)``) into the fused parameters. Returns missing names."""
+    missing = []
+    for hf, dst in iter_hf_tensors(model, ep_rank, ep_size):
+        src = get(hf)
+        if src is None:
+            missing.append(hf)
+            continue
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"{hf}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
+        dst.copy_(src.to(dst.dtype))
+    if strict and missing:
+        raise KeyError(f"{len(missing)} tensors missing from checkpoint, first: {missing[:5]}")
+    return missing
+
+
+def save_pretrained(model: CausalLM, path: str, max_shard_bytes: int = 5 * 1024**3, dtype: Optional[torch.dtype] = None) -> None:
+    """Writes an HF-layout checkpoint (config + sharded safetensors + index)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    model.cfg.save_pretrained(path)
+    shards: list[dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for name, t in iter_hf_tensors(model):
+        t = t.detach().to("cpu", dtype or t.dtype).contiguous()
+        nbytes = t.numel() * t.element_size()
+        if size + nbytes > max_shard_bytes and shards[-1]:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t
+        size += nbytes
+    n = len(shards)
+    weight_map, total = {}, 0
+    for i, sh in enumerate(shards):
+        fname = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        save_file(sh, os.path.join(path, fname), metadata={"format": "pt"})
+        for k, t in sh.items():
+            weight_map[k] = fname
+            total += t.numel() * t.element_size()
+    if n > 1:
+        with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
+
+
+class _SafetensorsDir:
+    """Lazy reader over an HF checkpoint directory (single file or sharded with an index)."""
+
+    def __init__(self, path: str):
+        from safetensors import safe_open
+
+        self.path = path
+        self.safe_open = safe_open
+        idx = os.path.join(path, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            self.weight_map = json.load(open(idx))["weight_map"]
+        else:
+            self.weight_map = {}
+            for fn in sorted(os.listdir(path)):
+                if fn.endswith(".safetensors"):
+                    with safe_open(os.path.join(path, fn), framework="pt") as f:
+                        for k in f.keys():
+                            self.weight_map[k] = fn
+        self._open: dict[str, object] = {}
+
+    def get(self, name: str) -> Optional[torch.Tensor]:
+        fn = self.weight_map.get(name)
+        if fn is None:
+            return None
+        h = self._open.get(fn)
+        if h is None:
+            h = self.safe_open(os.path.join(self.path, fn), framework="pt")
+            self._open[fn] = h
+        return h.get_tensor(name)
+
+
+def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None, strict: bool = True,
+                    **cfg_overrides) -> CausalLM:
+    """Builds a model from an HF checkpoint directory."""
+    cfg = ModelConfig.from_pretrained(path, **cfg_overrides)
+    model = CausalLM(cfg, dtype=dtype, device=device, init=False)
+    reader = _SafetensorsDir(path)
+    get = reader.get
+    if cfg.tie_word_embeddings or cfg.value_head:
+        pass
+    missing = load_hf_tensors(model, get, strict=False)
+    # a value model initialised from a causal LM has no score.weight yet: start it at zero
+    really_missing = [m for m in missing if not m.startswith("score.")]
+    if strict and really_missing:
+        raise KeyError(f"tensors missing from {path}: {really_missing[:5]}")
+    if cfg.value_head and "score.weight" in missing:
+        with torch.no_grad():
+            model.score.zero_()
+    return model

@@ -1,0 +1,279 @@
+"""Decoder-only transformer (Llama / Mistral / Qwen2 / Qwen3 / Qwen3-MoE) over *packed* token streams.
+
+The model consumes a flat token vector ``[T]`` with ``cu_seqlens`` marking sequence boundaries (no padding tokens
+ever reach a GEMM), keeps the q/k/v and gate/up projections fused, and calls the operators of
+:mod:`rl_b200.ops.functional`, so that on a GPU every hot op is one of this repository's kernels. Parameters live
+as views into one flat bf16 buffer (:class:`FlatParams`), which is what the sharded optimizer, the weight refit and
+the generation engine address directly.
+
+It replaces the HF modeling code + nemo-automodel wrapping that the reference's DTensor worker builds on
+(nemo_rl/models/automodel/setup.py:576-878) and the mcore GPT model of its Megatron worker.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint as ckpt
+
+from rl_b200.ops import functional as F
+
+from .config import ModelConfig, rope_inv_freq
+
+
+def _dtype_of(name: str) -> torch.dtype:
+    return {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16,
+            "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32}.get(str(name), torch.bfloat16)
+
+
+class FlatParams:
+    """All parameters of a module tree as views of one flat buffer (plus a same-shaped gradient buffer).
+
+    ``flat``  the parameter values (bf16 for training on GPU, fp32 for the CPU oracle); length padded to a multiple
+              of ``align`` so that it splits evenly over optimizer shards.
+    ``grad``  optional gradient accumulation buffer (fp32 or bf16); every parameter gets a ``main_grad`` view into
+              it, and the linear / norm backward kernels accumulate into those views directly.
+    """
+
+    def __init__(self, module: nn.Module, align: int = 2048):
+        params = [(n, p) for n, p in module.named_parameters()]
+        self.names = [n for n, _ in params]
+        self.shapes = [tuple(p.shape) for _, p in params]
+        self.numels = [p.numel() for _, p in params]
+        # every tensor starts on a 16-byte boundary (TMA / vector loads)
+        self.offsets = []
+        off = 0
+        for n in self.numels:
+            self.offsets.append(off)
+            off += -(-n // 8) * 8
+        self.numel = off
+        self.padded = -(-off // align) * align
+        p0 = params[0][1]
+        self.flat = torch.zeros(self.padded, dtype=p0.dtype, device=p0.device)
+        for (name, p), o, n in zip(params, self.offsets, self.numels):
+            self.flat[o : o + n].copy_(p.data.reshape(-1))
+            p.data = self.flat[o : o + n].view(p.shape)
+        self.params = [p for _, p in params]
+        self.grad: Optional[torch.Tensor] = None
+
+    def attach_grad_buffer(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        self.grad = torch.zeros(self.padded, dtype=dtype, device=self.flat.device)
+        for p, o, n in zip(self.params, self.offsets, self.numels):
+            p.main_grad = self.grad[o : o + n].view(p.shape)
+        return self.grad
+
+    def drop_grad_buffer(self) -> None:
+        self.grad = None
+        for p in self.params:
+            if hasattr(p, "main_grad"):
+                del p.main_grad
+
+    def fold_autograd_grads(self) -> None:
+        """Adds any ``.grad`` that autograd produced (ops without a fused accumulate path) into ``main_grad``."""
+        for p in self.params:
+            if p.grad is not None:
+                if getattr(p, "main_grad", None) is not None:
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                    p.grad = None
+
+    def named_slices(self):
+        for n, o, k, s in zip(self.names, self.offsets, self.numels, self.shapes):
+            yield n, o, k, s
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.hidden_size
+        self.qkv_proj = nn.Parameter(torch.empty(cfg.qkv_size, d, dtype=dtype, device=device))
+        self.qkv_bias = nn.Parameter(torch.zeros(cfg.qkv_size, dtype=dtype, device=device)) if cfg.attention_bias else None
+        self.o_proj = nn.Parameter(torch.empty(d, cfg.q_size, dtype=dtype, device=device))
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
+            self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
+
+    def project_qkv(self, x, positions, inv_freq):
+        """x [T, d] -> fused [T, (Hq+2Hkv)*D] with q/k normalised (Qwen3) and rotated."""
+        c = self.cfg
+        qkv = F.linear(x, self.qkv_proj, self.qkv_bias)
+        if c.qk_norm:
+            qkv = F.head_rmsnorm(qkv, self.q_norm, 0, c.num_attention_heads, c.head_dim, c.rms_norm_eps)
+            qkv = F.head_rmsnorm(qkv, self.k_norm, c.q_size, c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
+        return F.rope(qkv, positions, inv_freq, c.num_attention_heads + c.num_key_value_heads, c.head_dim)
+
+    def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen):
+        c = self.cfg
+        qkv = self.project_qkv(x, positions, inv_freq)
+        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+        return F.linear(a, self.o_proj, None, residual)
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        d, f = cfg.hidden_size, cfg.intermediate_size
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
+
+    def forward(self, x, residual):
+        return F.linear(F.swiglu(F.linear(x, self.gate_up_proj)), self.down_proj, None, residual)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.hidden_size
+        self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        self.self_attn = Attention(cfg, dtype, device)
+        self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        if cfg.is_moe:
+            from .moe import MoEMLP
+
+            self.mlp = MoEMLP(cfg, dtype, device)
+        else:
+            self.mlp = DenseMLP(cfg, dtype, device)
+
+    def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
+        eps = self.cfg.rms_norm_eps
+        h = self.self_attn(F.rmsnorm(h, self.input_layernorm, eps), h, positions, inv_freq, cu_seqlens, max_seqlen)
+        h = self.mlp(F.rmsnorm(h, self.post_attention_layernorm, eps), h)
+        return h
+
+
+@dataclass
+class PackedBatch:
+    """A packed micro-batch: ``input_ids`` [T], ``positions`` [T], ``cu_seqlens`` [B+1] (int32), ``max_seqlen``."""
+
+    input_ids: torch.Tensor
+    positions: torch.Tensor
+    cu_seqlens: torch.Tensor
+    max_seqlen: int
+
+    @staticmethod
+    def from_padded(input_ids: torch.Tensor, lengths: torch.Tensor) -> "PackedBatch":
+        """[B, S] right-padded ids + lengths [B] -> packed stream (pads dropped)."""
+        B, S = input_ids.shape
+        lengths = lengths.to(input_ids.device).long().clamp(max=S)
+        ar = torch.arange(S, device=input_ids.device)
+        keep = ar[None, :] < lengths[:, None]
+        ids = input_ids[keep]
+        pos = ar[None, :].expand(B, S)[keep]
+        cu = torch.zeros(B + 1, dtype=torch.int32, device=input_ids.device)
+        cu[1:] = lengths.cumsum(0).to(torch.int32)
+        return PackedBatch(ids.contiguous(), pos.to(torch.int32).contiguous(), cu, int(lengths.max().item()) if B else 0)
+
+    def unpack(self, flat: torch.Tensor, S: int, fill=0.0) -> torch.Tensor:
+        """[T, ...] packed values -> [B, S, ...] right-padded."""
+        B = self.cu_seqlens.numel() - 1
+        lengths = (self.cu_seqlens[1:] - self.cu_seqlens[:-1]).long()
+        out = flat.new_full((B, S) + tuple(flat.shape[1:]), fill)
+        ar = torch.arange(S, device=flat.device)
+        keep = ar[None, :] < lengths[:, None]
+        out[keep] = flat
+        return out
+
+
+class CausalLM(nn.Module):
+    """Packed-sequence causal language model with HF-compatible weights (see :mod:`rl_b200.models.hf_io`)."""
+
+    def __init__(self, cfg: ModelConfig, dtype: Optional[torch.dtype] = None, device="cpu", init: bool = True,
+                 seed: int = 0, activation_checkpointing: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        dtype = dtype or _dtype_of(cfg.torch_dtype)
+        self.dtype = dtype
+        d = cfg.hidden_size
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        if cfg.value_head:
+            self.score = nn.Parameter(torch.empty(8, d, dtype=dtype, device=device))  # row 0 is the head; 8 rows keep TMA alignment
+            self.lm_head = None
+        elif cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
+        self.register_buffer("inv_freq", rope_inv_freq(cfg, device), persistent=False)
+        self.activation_checkpointing = activation_checkpointing
+        if init:
+            self.reset_parameters(seed)
+        self.flat: Optional[FlatParams] = None
+
+    # ------------------------------------------------------------------ parameters
+    @torch.no_grad()
+    def reset_parameters(self, seed: int = 0, std: float = 0.02) -> None:
+        """Normal(0, 0.02) weights (HF's default initializer range), ones for norms, zeros for biases.
+        Generated on the parameter's device with a seeded generator so every rank builds identical weights."""
+        for i, (name, p) in enumerate(self.named_parameters()):
+            if name.endswith("norm") or name.endswith("layernorm"):
+                p.fill_(1.0)
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                g = torch.Generator(device=p.device)
+                g.manual_seed(seed * 1000003 + i)
+                # normal_ in fp32 chunks keeps the memory bounded for 1 GB embedding tables
+                flat = p.view(-1)
+                step = 1 << 26
+                for s in range(0, flat.numel(), step):
+                    e = min(flat.numel(), s + step)
+                    flat[s:e] = (torch.randn(e - s, generator=g, device=p.device, dtype=torch.float32) * std).to(p.dtype)
+
+    def flatten_parameters(self, align: int = 2048) -> FlatParams:
+        self.flat = FlatParams(self, align)
+        return self.flat
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    # ------------------------------------------------------------------ forward
+    def hidden_states(self, batch: PackedBatch) -> torch.Tensor:
+        h = F.embedding(batch.input_ids, self.embed_tokens)
+        inv_freq = self.inv_freq
+        for layer in self.layers:
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                h = ckpt.checkpoint(layer, h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen, use_reentrant=False)
+            else:
+                h = layer(h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen)
+        return F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+
+    def logits(self, batch: PackedBatch) -> torch.Tensor:
+        """[T, V] logits in fp32 (small models, tests and the distillation / top-k paths)."""
+        return F.linear(self.hidden_states(batch), self.output_weight).float()
+
+    def next_token_logprobs(self, batch: PackedBatch, temperature: float = 1.0, want_entropy: bool = False):
+        """Log-probability of each token given its prefix: out[t] = log p(ids[t] | ids[<t]) for t > 0 within a sequence,
+        0 at sequence starts. Returns ([T] fp32, entropy [T] or None). Uses the fused projection + log-softmax."""
+        h = self.hidden_states(batch)
+        T = h.shape[0]
+        ids = batch.input_ids.long()
+        starts = batch.cu_seqlens[:-1].long()
+        is_start = torch.zeros(T, dtype=torch.bool, device=h.device)
+        is_start[starts[starts < T]] = True
+        # hidden state t-1 predicts token t: rows [0, T-1) against targets ids[1:]
+        logp_n, ent_n = F.lm_head_logprobs(h[:-1], self.output_weight, ids[1:], temperature, want_entropy)
+        logp = torch.zeros(T, dtype=torch.float32, device=h.device)
+        valid = ~is_start[1:]
+        logp[1:] = torch.where(valid, logp_n, torch.zeros_like(logp_n))
+        ent = None
+        if want_entropy:
+            ent = torch.zeros(T, dtype=torch.float32, device=h.device)
+            ent[1:] = torch.where(valid, ent_n, torch.zeros_like(ent_n))
+        return logp, ent
+
+    def values(self, batch: PackedBatch) -> torch.Tensor:
+        """Scalar head output per token [T] (critic / reward model)."""
+        h = self.hidden_states(batch)
+        return F.linear(h, self.score).float()[:, 0]
+
+
+def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
+                activation_checkpointing: bool = False, init: bool = True) -> CausalLM:
+    return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing)

@@ -84,7 +84,8 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 
 def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, greedy: bool = False,
            seed: int = 0, step: int = 0, temps: Optional[torch.Tensor] = None, top_ks: Optional[torch.Tensor] = None,
-           top_ps: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None):
+           top_ps: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None,
+           step_tensor: Optional[torch.Tensor] = None, out: Optional[tuple[torch.Tensor, torch.Tensor]] = None):
     """Draws one token per row of ``logits`` [B, V] and returns (tokens int32 [B], logprobs fp32 [B]); the
     log-probabilities are those of the distribution after temperature / top-k / top-p."""
     B, V = logits.shape
@@ -109,11 +110,39 @@ def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, to
             tok = torch.multinomial(logp.exp(), 1, generator=generator).squeeze(-1)
         return tok.to(torch.int32), logp.gather(-1, tok.long().unsqueeze(-1)).squeeze(-1)
     assert logits.stride(1) == 1
-    tok = torch.empty(B, dtype=torch.int32, device=logits.device)
-    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    if out is None:
+        tok = torch.empty(B, dtype=torch.int32, device=logits.device)
+        lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    else:
+        tok, lp = out
     dtype = 0 if logits.dtype == torch.float32 else 1
     assert logits.dtype in (torch.float32, torch.bfloat16)
+    # step_tensor: a 1-element int64 CUDA tensor holding the draw counter, for launches replayed from a CUDA graph
     call("rlb_sample", ptr(logits), dtype, logits.stride(0), B, V, ptr(temps), ptr(top_ks), ptr(top_ps),
          float(temperature), int(top_k), float(top_p), int(greedy), seed & (2**64 - 1), step & (2**64 - 1),
-         ptr(tok), ptr(lp), stream_ptr())
+         ptr(step_tensor), ptr(tok), ptr(lp), stream_ptr())
     return tok, lp
+
+
+def block_copy(k_cache: torch.Tensor, v_cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
+    """Copies whole cache blocks ``src[i] -> dst[i]`` in both caches (copy-on-write of a shared prompt's tail block)."""
+    n = src.numel()
+    if n == 0:
+        return
+    if not use_native(k_cache):
+        k_cache[dst.long()] = k_cache[src.long()]
+        v_cache[dst.long()] = v_cache[src.long()]
+        return
+    elems = k_cache[0].numel()
+    call("rlb_block_copy", ptr(k_cache), ptr(v_cache), ptr(src), ptr(dst), n, elems, stream_ptr())
+
+
+def gather_rows(x: torch.Tensor, idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = x[idx[i]] for a bf16 [T, d] matrix (last-token hidden states of a packed batch)."""
+    if not use_native(x):
+        return x[idx.long()]
+    n, d = idx.numel(), x.shape[1]
+    if out is None:
+        out = torch.empty((n, d), dtype=x.dtype, device=x.device)
+    call("rlb_gather_rows", ptr(x), ptr(idx), ptr(out), n, d, x.stride(0), out.stride(0), stream_ptr())
+    return out

@@ -30,6 +30,7 @@ def gemm(
     out_dtype: torch.dtype = BF16,
     accumulate: bool = False,
     bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
     max_ctas: int = 0,
 ) -> torch.Tensor:
     """C[M,N] = op(A) @ op(B)^T. ``a`` is [M,K] (or [K,M] when ``a_mn``), ``b`` is [N,K] (or [K,N] when ``b_mn``).
@@ -49,6 +50,8 @@ def gemm(
         res = A.float() @ B.float()
         if bias is not None:
             res = res + bias.float()
+        if residual is not None:
+            res = res + residual.float()
         if accumulate:
             res = res + out.float()
         out.copy_(res.to(out.dtype))
@@ -64,6 +67,7 @@ def gemm(
     call(
         "rlb_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ptr(bias),
+        ptr(residual), residual.stride(0) if residual is not None else 0,
         ptr(_L.status_word(a.device)), max_ctas, stream_ptr(),
     )
     return out
@@ -71,11 +75,15 @@ def gemm(
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, residual):
         ctx.save_for_backward(x, w)
         ctx.has_bias = bias is not None
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w, bias=bias, out_dtype=x.dtype)
+        r2 = None
+        if residual is not None:
+            r2 = residual.reshape(-1, residual.shape[-1])
+            assert r2.dtype == BF16 and r2.stride(-1) == 1
+        y = gemm(x2, w, bias=bias, residual=r2, out_dtype=x.dtype)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -98,14 +106,21 @@ class _Linear(torch.autograd.Function):
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0)
-        return dx, dw, db
+            bias_grad = getattr(ctx, "bias_main_grad", None)
+        dres = dy if ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x @ w^T (+ bias); w is [out_features, in_features] as in ``nn.Linear``."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w^T (+ bias) (+ residual); w is [out_features, in_features] as in ``nn.Linear``.
+
+    ``residual`` (same shape as y) is added inside the GEMM epilogue, which saves one read-modify-write pass over
+    the residual stream per projection."""
     if not use_native(x):
-        return tF.linear(x, w, bias)
-    return _Linear.apply(x, w, bias)
+        y = tF.linear(x, w, bias)
+        return y if residual is None else y + residual
+    return _Linear.apply(x, w, bias, residual)
 
 
 # --------------------------------------------------------------------------------------- RMSNorm
@@ -475,10 +490,13 @@ def adamw_step(p_bf16, p_lo, p32, grad, m, v, *, lr, beta1, beta2, eps, weight_d
 
 
 def split_master(w32: torch.Tensor):
-    """fp32 -> (bf16 round-to-nearest, int16 remainder) with ``bits(w32) == (bits(hi) << 16) + lo`` exactly."""
-    hi = w32.to(BF16)
-    hb = hi.view(torch.int16).to(torch.int32) << 16
-    lo = (w32.view(torch.int32) - hb).to(torch.int16)
+    """fp32 -> (bf16, int16 remainder) with ``bits(w32) == (bits(hi) << 16) + lo`` exactly.
+
+    The bf16 half rounds to nearest with ties away from zero, so the remainder always fits 16 signed bits."""
+    bits = w32.contiguous().view(torch.int32)
+    hb = (bits + 0x8000) & -65536
+    hi = (hb >> 16).to(torch.int16).view(BF16)
+    lo = (bits - hb).to(torch.int16)
     return hi, lo
 
 

@@ -26,7 +26,7 @@ U64 = C.c_ulonglong
 
 # name -> argument types (all functions return int: 0 ok, >0 CUDA error, <0 bad argument)
 _SIGS: dict[str, list[Any]] = {
-    "rlb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, P, P, I, P],
+    "rlb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, P, P, L, P, I, P],
     "rlb_gemm_num_n_tiles": [I],
     "rlb_lm_head_logprob": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P, P, P, P],
     "rlb_logprob_combine": [P, P, P, P, I, I, P, P, P, P],
@@ -50,7 +50,9 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_add_bf16": [P, P, P, L, P],
     "rlb_kv_cache_write": [P, P, P, P, L, I, I, I, I, L, P],
     "rlb_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
-    "rlb_sample": [P, I, L, I, I, P, P, P, F, I, F, I, U64, U64, P, P, P],
+    "rlb_sample": [P, I, L, I, I, P, P, P, F, I, F, I, U64, U64, P, P, P, P],
+    "rlb_block_copy": [P, P, P, P, I, L, P],
+    "rlb_gather_rows": [P, P, P, L, I, L, L, P],
 }
 
 

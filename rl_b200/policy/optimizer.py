@@ -1,0 +1,215 @@
+"""Sharded AdamW over the model's flat parameter buffer (ZeRO-1/2 style, laid out for 180 GB GPUs).
+
+Every data-parallel rank keeps the full bf16 parameters and a full gradient-accumulation buffer resident (no
+parameter all-gather inside forward / backward), and owns 1/N of the optimizer state: the low 16 bits of the fp32
+master weights, and the two Adam moments. One optimizer step is
+
+    reduce-scatter(grad) -> global grad-norm / clip scale -> AdamW on the shard -> all-gather(bf16 params)
+
+On NVLink-connected GPUs the three stages run as one fused peer-memory kernel (:mod:`rl_b200.parallel.fused_optim`);
+the NCCL/gloo form below is its twin and the CPU path. The reference reaches the same end state with FSDP2
+reduce-scatter + ``torch.optim.AdamW`` on DTensor shards (nemo_rl/models/automodel/setup.py:481-493, :806-820) and
+``clip_grad_by_total_norm_`` (nemo_rl/models/dtensor/parallelize.py:780-882).
+"""
+
+from __future__ import annotations
+
+import importlib
+import math
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from rl_b200.models.transformer import FlatParams
+from rl_b200.ops import functional as F
+
+
+def _world(group) -> tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+class ShardedAdamW:
+    def __init__(self, flat: FlatParams, *, lr: float = 1e-5, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, group=None,
+                 master_format: str = "split16", fused_comm: Optional[Any] = None):
+        """``master_format``: ``split16`` keeps bf16 + 16 low bits (exact fp32 master at 4 B/param), ``fp32`` keeps a
+        separate fp32 master shard (CPU / fp32 models use this)."""
+        self.flat = flat
+        self.group = group
+        self.rank, self.world = _world(group)
+        assert flat.padded % self.world == 0, "flat parameter buffer must split evenly over optimizer shards"
+        self.shard_numel = flat.padded // self.world
+        self.lo, self.hi = self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
+        self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.step_count = 0
+        dev = flat.flat.device
+        p_shard = flat.flat[self.lo : self.hi]
+        if flat.flat.dtype != torch.bfloat16:
+            master_format = "fp32"
+        self.master_format = master_format
+        if master_format == "split16":
+            self.p_lo = torch.zeros(self.shard_numel, dtype=torch.int16, device=dev)  # bf16 value is the exact master at start
+            self.p32 = None
+        else:
+            self.p_lo = None
+            self.p32 = p_shard.float().clone()
+        self.m = torch.zeros(self.shard_numel, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.shard_numel, dtype=torch.float32, device=dev)
+        self.grad_shard: Optional[torch.Tensor] = None
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.fused_comm = fused_comm
+        self.last_grad_norm: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ step
+    def zero_grad(self) -> None:
+        if self.flat.grad is not None:
+            self.flat.grad.zero_()
+        for p in self.flat.params:
+            p.grad = None
+
+    def _reduce_scatter(self) -> torch.Tensor:
+        g = self.flat.grad
+        if self.world == 1:
+            return g
+        mine = g[self.lo : self.hi]
+        if g.is_cuda:
+            out = torch.empty_like(mine)
+            dist.reduce_scatter_tensor(out, g, op=dist.ReduceOp.SUM, group=self.group)
+            return out
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce-scatter
+        return mine
+
+    def _all_gather(self) -> None:
+        if self.world == 1:
+            return
+        flat = self.flat.flat
+        mine = flat[self.lo : self.hi]
+        if flat.is_cuda:
+            dist.all_gather_into_tensor(flat, mine.clone(), group=self.group)
+        else:
+            parts = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(parts, mine.contiguous(), group=self.group)
+            for r, p in enumerate(parts):
+                flat[r * self.shard_numel : (r + 1) * self.shard_numel].copy_(p)
+
+    @torch.no_grad()
+    def step(self, grad_div: float = 1.0) -> torch.Tensor:
+        """Applies one update. ``grad_div`` divides the summed gradient (1 when the loss is already normalised by
+        the global token count). Returns the global gradient norm (a 1-element tensor, no host sync)."""
+        self.flat.fold_autograd_grads()
+        self.step_count += 1
+        if self.fused_comm is not None and self.world > 1:
+            return self.fused_comm.step(self, grad_div)
+        gs = self._reduce_scatter()
+        self._sumsq.zero_()
+        F.sumsq_(gs, self._sumsq)
+        if self.world > 1:
+            dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=self.group)
+        if grad_div != 1.0:
+            self._sumsq.mul_(1.0 / (grad_div * grad_div))
+        F.clip_scale(self._sumsq, float(self.max_grad_norm or 0.0), 1.0 / grad_div, self._scale, self._norm)
+        p_shard = self.flat.flat[self.lo : self.hi]
+        F.adamw_step(p_shard if p_shard.dtype == torch.bfloat16 else None, self.p_lo, self.p32, gs, self.m, self.v,
+                     lr=self.lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=self.weight_decay,
+                     step=self.step_count, grad_scale=self._scale)
+        if self.p32 is not None and p_shard.dtype != torch.bfloat16:
+            p_shard.copy_(self.p32.to(p_shard.dtype))
+        self._all_gather()
+        self.last_grad_norm = self._norm.clone()
+        return self.last_grad_norm
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "m": self.m, "v": self.v, "p_lo": self.p_lo, "p32": self.p32,
+                "rank": self.rank, "world": self.world, "lr": self.lr, "master_format": self.master_format}
+
+    def load_state_dict(self, sd: dict) -> None:
+        assert sd["world"] == self.world and sd["rank"] == self.rank, "optimizer shards are tied to the data-parallel layout"
+        self.step_count = int(sd["step"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        if self.p_lo is not None and sd.get("p_lo") is not None:
+            self.p_lo.copy_(sd["p_lo"])
+        if self.p32 is not None and sd.get("p32") is not None:
+            self.p32.copy_(sd["p32"])
+
+    def offload_state(self) -> None:
+        """Moves the moments (and master remainder) to pinned host memory (``offload_optimizer_for_logprob``)."""
+        for k in ("m", "v", "p_lo", "p32"):
+            t = getattr(self, k)
+            if t is not None and t.is_cuda:
+                setattr(self, k, t.to("cpu", non_blocking=False).pin_memory())
+        torch.cuda.empty_cache()
+
+    def reload_state(self, device) -> None:
+        for k in ("m", "v", "p_lo", "p32"):
+            t = getattr(self, k)
+            if t is not None and not t.is_cuda and torch.device(device).type == "cuda":
+                setattr(self, k, t.to(device, non_blocking=True))
+
+
+# ---------------------------------------------------------------------- config glue
+def build_optimizer(flat: FlatParams, policy_cfg: dict, group=None, fused_comm=None) -> ShardedAdamW:
+    """Reads ``policy.optimizer = {name: <dotted class path>, kwargs: {...}}``. Adam / AdamW (any module path) map to
+    the sharded fused implementation."""
+    ocfg = policy_cfg.get("optimizer") or {}
+    name = str(ocfg.get("name", "torch.optim.AdamW"))
+    kw = dict(ocfg.get("kwargs") or {})
+    short = name.rsplit(".", 1)[-1].lower()
+    if short not in ("adamw", "adam", "fusedadam"):
+        raise ValueError(f"optimizer '{name}' is not supported (AdamW / Adam)")
+    wd = kw.get("weight_decay", 0.01 if short == "adamw" else 0.0)
+    return ShardedAdamW(flat, lr=float(kw.get("lr", 1e-5)), betas=tuple(kw.get("betas", (0.9, 0.999))),
+                        eps=float(kw.get("eps", 1e-8)), weight_decay=float(wd),
+                        max_grad_norm=policy_cfg.get("max_grad_norm"), group=group, fused_comm=fused_comm,
+                        master_format=policy_cfg.get("master_weight_format", "split16"))
+
+
+class LRSchedule:
+    """``policy.scheduler`` is a list of ``{name, kwargs}`` torch scheduler specs, optionally ending with
+    ``{milestones: [...]}`` that chains them as a SequentialLR (nemo_rl/models/automodel/setup.py:844). The schedule is
+    evaluated on a one-parameter stand-in optimizer and its learning rate copied to the sharded optimizer; it advances
+    once per ``train()`` call."""
+
+    def __init__(self, opt: ShardedAdamW, spec):
+        self.opt = opt
+        self._dummy = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=opt.lr)
+        self.sched = None
+        if spec:
+            if isinstance(spec, dict):
+                spec = [spec]
+            scheds, milestones = [], None
+            for s in spec:
+                if "milestones" in s and "name" not in s:
+                    milestones = s["milestones"]
+                    continue
+                mod, cls = s["name"].rsplit(".", 1) if "." in s["name"] else ("torch.optim.lr_scheduler", s["name"])
+                klass = getattr(importlib.import_module(mod), cls)
+                scheds.append(klass(self._dummy, **(s.get("kwargs") or {})))
+            if len(scheds) == 1:
+                self.sched = scheds[0]
+            elif scheds:
+                self.sched = torch.optim.lr_scheduler.SequentialLR(self._dummy, scheds, milestones or [])
+        self.opt.lr = self._dummy.param_groups[0]["lr"]
+
+    def step(self) -> float:
+        if self.sched is not None:
+            self._dummy.step()
+            self.sched.step()
+            self.opt.lr = self._dummy.param_groups[0]["lr"]
+        return self.opt.lr
+
+    def state_dict(self):
+        return {"sched": self.sched.state_dict() if self.sched is not None else None, "lr": self.opt.lr}
+
+    def load_state_dict(self, sd):
+        if self.sched is not None and sd.get("sched") is not None:
+            self.sched.load_state_dict(sd["sched"])
+        self.opt.lr = sd.get("lr", self.opt.lr)
+        self._dummy.param_groups[0]["lr"] = self.opt.lr

@@ -1,0 +1,376 @@
+"""Policy worker: one process per GPU holding the policy model, its sharded optimizer, an optional reference copy and
+(when colocated) the generation engine that shares the same weight buffers.
+
+One class with a parallelism spec replaces the reference's three worker backends (DTensor V1/V2 and Megatron:
+nemo_rl/models/policy/workers/dtensor_policy_worker_v2.py:401-683, megatron_policy_worker.py:749-1125). The public
+methods keep the reference's worker API: ``train``, ``get_logprobs``, ``get_reference_policy_logprobs``,
+``get_topk_logits``, ``score``, ``prepare_for_training`` / ``prepare_for_lp_inference``, ``save_checkpoint`` /
+``load_checkpoint`` and the refit hooks. All batches are packed (padding never reaches a GEMM), so "sequence packing"
+and "dynamic batching" only choose how samples are grouped into micro-batches.
+
+Normalisation contract: losses are divided by the *global* number of valid tokens / sequences of the optimizer step
+(all ranks, all micro-batches), gradients are summed over ranks, so no rank-count factor appears anywhere.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import os
+import time
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from rl_b200.algorithms.loss.interfaces import LossInputType, LossType
+from rl_b200.distributed.batched_data_dict import BatchedDataDict
+from rl_b200.models.config import ModelConfig, preset
+from rl_b200.models.transformer import CausalLM, PackedBatch, build_model
+from rl_b200.policy.optimizer import LRSchedule, ShardedAdamW, build_optimizer
+from rl_b200.utils.flops import transformer_flops
+
+POLICY_DEFAULTS = dict(
+    model_name=None,
+    train_global_batch_size=32,
+    train_micro_batch_size=4,
+    logprob_batch_size=8,
+    generation_batch_size=32,
+    max_total_sequence_length=4096,
+    precision="bfloat16",
+    activation_checkpointing=False,
+    max_grad_norm=1.0,
+    grad_dtype="float32",
+    logprob_chunk_size=None,
+    make_sequence_length_divisible_by=1,
+    offload_optimizer_for_logprob=False,
+)
+
+
+def _dp_info(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def _precision(name) -> torch.dtype:
+    return {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+            "float16": torch.float16}.get(str(name), torch.bfloat16)
+
+
+class PolicyWorker:
+    def __init__(self, policy_cfg: dict, model_cfg: Optional[ModelConfig] = None, device=None, dp_group=None,
+                 init_optimizer: bool = True, init_reference_model: bool = True, tokenizer=None, seed: int = 0,
+                 weights_path: Optional[str] = None, fused_comm=None):
+        cfg = dict(POLICY_DEFAULTS)
+        cfg.update(policy_cfg or {})
+        self.cfg = cfg
+        self.dp_group = dp_group
+        self.rank, self.world = _dp_info(dp_group)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.tokenizer = tokenizer
+        dtype = _precision(cfg["precision"])
+        name = cfg.get("model_name")
+        overrides = cfg.get("hf_config_overrides") or {}
+        if model_cfg is None:
+            if name in (None, ""):
+                raise ValueError("policy.model_name or an explicit ModelConfig is required")
+            from rl_b200.models.config import PRESETS
+
+            if name in PRESETS:
+                model_cfg = preset(name, **overrides)
+            elif os.path.isdir(name):
+                model_cfg = ModelConfig.from_pretrained(name, **overrides)
+                weights_path = weights_path or name
+            else:
+                raise ValueError(f"unknown model '{name}': give a preset name or a local HF checkpoint directory")
+        self.model_cfg = model_cfg
+        dtc = cfg.get("dtensor_cfg") or {}
+        act_ckpt = bool(cfg.get("activation_checkpointing") or dtc.get("activation_checkpointing", False))
+        if weights_path:
+            from rl_b200.models.hf_io import load_pretrained
+
+            self.model = load_pretrained(weights_path, device=self.device, dtype=dtype)
+            self.model.activation_checkpointing = act_ckpt
+        else:
+            self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt)
+        self.flat = self.model.flatten_parameters(align=256 * self.world)
+        self.ref_flat: Optional[torch.Tensor] = None
+        if init_reference_model:
+            # the reference policy stays resident in HBM as a second flat buffer (no CPU swap)
+            self.ref_flat = self.flat.flat.clone()
+        self.optimizer: Optional[ShardedAdamW] = None
+        self.scheduler: Optional[LRSchedule] = None
+        if init_optimizer:
+            self.flat.attach_grad_buffer(_precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32)
+            self.optimizer = build_optimizer(self.flat, cfg, group=dp_group, fused_comm=fused_comm)
+            self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
+        self.generation = None
+        self.temperature = 1.0
+        gen_cfg = cfg.get("generation") or {}
+        if gen_cfg:
+            self.temperature = float(gen_cfg.get("temperature", 1.0) or 1.0)
+        self.timers: dict[str, float] = {}
+
+    # ------------------------------------------------------------------ generation (colocated, shared weights)
+    def build_generation(self, gen_cfg: Optional[dict] = None):
+        """Creates the colocated generation engine over this worker's own weight buffers."""
+        from rl_b200.engine.generation import NativeGeneration
+
+        g = dict(self.cfg.get("generation") or {})
+        g.update(gen_cfg or {})
+        native_cfg = dict(g.get("native_cfg") or g.get("vllm_cfg") or {})
+        merged = {k: v for k, v in g.items() if k not in ("native_cfg", "vllm_cfg", "colocated", "sglang_cfg")}
+        for k in ("gpu_memory_utilization", "max_model_len", "block_size", "kv_cache_tokens", "max_running", "use_cuda_graphs"):
+            if k in native_cfg:
+                merged[k] = native_cfg[k]
+        if native_cfg.get("enforce_eager"):
+            merged["use_cuda_graphs"] = False
+        merged.setdefault("max_model_len", self.cfg["max_total_sequence_length"])
+        self.generation = NativeGeneration(self.model, merged, self.tokenizer)
+        self.temperature = float(self.generation.cfg["temperature"] or 1.0)
+        return self.generation
+
+    # ------------------------------------------------------------------ modes
+    def prepare_for_training(self, *a, **k):
+        self.model.train()
+        if self.optimizer is not None:
+            self.optimizer.reload_state(self.device)
+
+    def prepare_for_lp_inference(self, *a, **k):
+        self.model.eval()
+        if self.cfg.get("offload_optimizer_for_logprob") and self.optimizer is not None:
+            self.optimizer.offload_state()
+
+    def finish_training(self, *a, **k):
+        pass
+
+    @contextlib.contextmanager
+    def use_reference_weights(self):
+        """Runs the model on the reference policy's weights by re-pointing every parameter at the second buffer."""
+        assert self.ref_flat is not None, "the worker was built without a reference model"
+        fl = self.flat
+        try:
+            for p, o, n in zip(fl.params, fl.offsets, fl.numels):
+                p.data = self.ref_flat[o : o + n].view(p.shape)
+            yield
+        finally:
+            for p, o, n in zip(fl.params, fl.offsets, fl.numels):
+                p.data = fl.flat[o : o + n].view(p.shape)
+
+    # ------------------------------------------------------------------ micro-batching
+    def _microbatches(self, data: BatchedDataDict, mbs: int, token_budget: Optional[int]):
+        """Yields (micro-batch, original indices). With a token budget samples are bin-packed by length."""
+        n = data.size
+        if token_budget:
+            from rl_b200.data.packing import get_packer
+
+            algo = (self.cfg.get("sequence_packing") or {}).get("algorithm", "modified_first_fit_decreasing")
+            lens = data["input_lengths"].tolist()
+            cap = max(int(token_budget), max(lens) if lens else 1)
+            for b in get_packer(algo, cap).pack(lens):
+                yield data.select_indices(b), b
+        else:
+            for s in range(0, n, mbs):
+                idx = list(range(s, min(n, s + mbs)))
+                yield data.slice(s, min(n, s + mbs)), idx
+
+    def _token_budget(self, kind: str) -> Optional[int]:
+        sp = self.cfg.get("sequence_packing") or {}
+        db = self.cfg.get("dynamic_batching") or {}
+        key = "train_mb_tokens" if kind == "train" else "logprob_mb_tokens"
+        if sp.get("enabled"):
+            return int(sp.get(key) or self.cfg["max_total_sequence_length"])
+        if db.get("enabled"):
+            return int(db.get(key) or self.cfg["max_total_sequence_length"])
+        return None
+
+    def _pack(self, mb: BatchedDataDict) -> tuple[PackedBatch, int]:
+        ids = mb["input_ids"].to(self.device, non_blocking=True)
+        lens = mb["input_lengths"].to(self.device, non_blocking=True)
+        batch = PackedBatch.from_padded(ids, lens)
+        if self.device.type == "cuda":
+            batch.input_ids = batch.input_ids.to(torch.int32)
+        return batch, ids.shape[1]
+
+    # ------------------------------------------------------------------ inference passes
+    @torch.no_grad()
+    def _logprob_pass(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> torch.Tensor:
+        self.model.eval()
+        n, S = data["input_ids"].shape
+        out = torch.zeros((n, S), dtype=torch.float32)
+        mbs = micro_batch_size or self.cfg["logprob_batch_size"]
+        for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob")):
+            batch, Smb = self._pack(mb)
+            lp, _ = self.model.next_token_logprobs(batch, self.temperature)
+            out[torch.as_tensor(idx), :Smb] = batch.unpack(lp, Smb).cpu()
+        return out
+
+    def get_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        """{logprobs [B, S]}: log p(token t | tokens < t) under the current weights; position 0 is 0."""
+        return BatchedDataDict({"logprobs": self._logprob_pass(data, micro_batch_size)})
+
+    def get_reference_policy_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        with self.use_reference_weights():
+            lp = self._logprob_pass(data, micro_batch_size)
+        return BatchedDataDict({"reference_logprobs": lp})
+
+    @torch.no_grad()
+    def get_topk_logits(self, data: BatchedDataDict, k: int, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        """Top-k next-token logits and their vocabulary ids for S-1 positions (teacher side of distillation)."""
+        self.model.eval()
+        n, S = data["input_ids"].shape
+        vals = torch.zeros((n, S - 1, k), dtype=torch.float32)
+        idxs = torch.zeros((n, S - 1, k), dtype=torch.long)
+        mbs = micro_batch_size or self.cfg["logprob_batch_size"]
+        for mb, idx in self._microbatches(data, mbs, None):
+            batch, Smb = self._pack(mb)
+            z = self.model.logits(batch) / self.temperature
+            v, i = torch.topk(z, k, dim=-1)
+            vals[torch.as_tensor(idx), : Smb - 1] = batch.unpack(v, Smb)[:, :-1].cpu()
+            idxs[torch.as_tensor(idx), : Smb - 1] = batch.unpack(i, Smb)[:, :-1].cpu()
+        return BatchedDataDict({"topk_logits": vals, "topk_indices": idxs})
+
+    @torch.no_grad()
+    def score(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        """Reward-model / critic head: per-token values [B, S] and the value at each sequence's last token."""
+        self.model.eval()
+        n, S = data["input_ids"].shape
+        vals = torch.zeros((n, S), dtype=torch.float32)
+        mbs = micro_batch_size or self.cfg["logprob_batch_size"]
+        for mb, idx in self._microbatches(data, mbs, None):
+            batch, Smb = self._pack(mb)
+            vals[torch.as_tensor(idx), :Smb] = batch.unpack(self.model.values(batch), Smb).cpu()
+        last = (data["input_lengths"].long() - 1).clamp(min=0)
+        return BatchedDataDict({"values": vals, "scores": vals.gather(1, last[:, None])[:, 0]})
+
+    # ------------------------------------------------------------------ training
+    def _loss_inputs(self, loss_fn, batch: PackedBatch, S: int, mb: BatchedDataDict) -> dict:
+        it = getattr(loss_fn, "input_type", LossInputType.LOGPROB)
+        if it == LossInputType.LOGPROB:
+            lp, _ = self.model.next_token_logprobs(batch, self.temperature)
+            return {"next_token_logprobs": batch.unpack(lp, S)[:, 1:]}
+        if it == LossInputType.VALUE:
+            return {"values": batch.unpack(self.model.values(batch), S)}
+        if it == LossInputType.LOGIT:
+            if self.model_cfg.value_head:  # reward model: score at the last token of each sequence
+                v = self.model.values(batch)
+                last = (batch.cu_seqlens[1:].long() - 1).clamp(min=0)
+                return {"logits": v[last]}
+            return {"logits": batch.unpack(self.model.logits(batch), S)}
+        if it == LossInputType.DISTILLATION:
+            z = self.model.logits(batch) / self.temperature
+            logp = torch.log_softmax(batch.unpack(z, S)[:, :-1], dim=-1)
+            ti = mb["teacher_topk_indices"].to(self.device)
+            s_topk = logp[:, : ti.shape[1]].gather(-1, ti)
+            t_topk = torch.log_softmax(mb["teacher_topk_logits"].to(self.device).float(), dim=-1)
+            return {"student_topk_logprobs": s_topk, "teacher_topk_logprobs": t_topk}
+        raise ValueError(f"unsupported loss input type {it}")
+
+    def train(self, data: BatchedDataDict, loss_fn, eval_mode: bool = False, *, gbs: Optional[int] = None,
+              mbs: Optional[int] = None) -> dict[str, Any]:
+        """Runs optimizer steps over this rank's shard of ``data`` (``gbs`` counts samples over all ranks; each rank
+        holds ``gbs / dp`` samples of every global batch). Returns loss / grad-norm / per-micro-batch metrics."""
+        assert self.optimizer is not None or eval_mode
+        gbs = gbs or self.cfg["train_global_batch_size"]
+        mbs = mbs or self.cfg["train_micro_batch_size"]
+        local_gbs = max(1, gbs // self.world)
+        n_local = data.size
+        num_gb = max(1, n_local // local_gbs)
+        self.model.train(not eval_mode)
+        losses, grad_norms, all_mb_metrics = [], [], []
+        total_tokens = 0
+        t_start = time.perf_counter()
+        for g in range(num_gb):
+            gb = data.slice(g * local_gbs, min(n_local, (g + 1) * local_gbs))
+            tm = gb["token_mask"][:, 1:].float() if "token_mask" in gb else None
+            sm = gb["sample_mask"].float() if "sample_mask" in gb else torch.ones(gb.size)
+            counts = torch.stack([sm.sum(), (tm * sm[:, None]).sum() if tm is not None else sm.sum()]).to(self.device)
+            if self.world > 1:
+                dist.all_reduce(counts, group=self.dp_group)
+            global_valid_seqs, global_valid_toks = counts[0], counts[1]
+            if not eval_mode:
+                self.optimizer.zero_grad()
+            gb_loss = torch.zeros((), device=self.device)
+            for mb, _ in self._microbatches(gb, mbs, self._token_budget("train")):
+                batch, S = self._pack(mb)
+                mb_dev = BatchedDataDict({k: (v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v)
+                                          for k, v in mb.items()})
+                mb_dev.truncate_tensors(1, S)
+                total_tokens += int(batch.input_ids.numel())
+                with torch.set_grad_enabled(not eval_mode):
+                    inputs = self._loss_inputs(loss_fn, batch, S, mb_dev)
+                    loss, metrics = loss_fn(data=mb_dev, global_valid_seqs=global_valid_seqs,
+                                            global_valid_toks=global_valid_toks, **inputs)
+                    if not eval_mode:
+                        loss.backward()
+                gb_loss += loss.detach()
+                metrics = dict(metrics)
+                metrics["lr"] = self.optimizer.lr if self.optimizer else 0.0
+                metrics["global_valid_seqs"] = float(global_valid_seqs)
+                metrics["global_valid_toks"] = float(global_valid_toks)
+                all_mb_metrics.append(metrics)
+            if not eval_mode:
+                gn = self.optimizer.step()
+                grad_norms.append(gn)
+            if self.world > 1:
+                dist.all_reduce(gb_loss, group=self.dp_group)
+            losses.append(gb_loss)
+        if not eval_mode and self.scheduler is not None:
+            self.scheduler.step()  # once per train() call
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        elapsed = time.perf_counter() - t_start
+        mb_metrics: dict[str, list] = {}
+        for m in all_mb_metrics:
+            for k, v in m.items():
+                mb_metrics.setdefault(k, []).append(v)
+        flops = transformer_flops(self.model_cfg, total_tokens, self.cfg["max_total_sequence_length"], backward=not eval_mode)
+        return {
+            "loss": torch.stack(losses).cpu() if losses else torch.zeros(0),
+            "grad_norm": torch.stack([g.reshape(()) for g in grad_norms]).cpu() if grad_norms else torch.zeros(0),
+            "all_mb_metrics": mb_metrics,
+            "total_flops": flops,
+            "num_ranks": self.world,
+            "train_time_s": elapsed,
+            "train_tokens": total_tokens,
+        }
+
+    # ------------------------------------------------------------------ refit hooks
+    def prepare_refit_info(self) -> dict:
+        """name -> (shape, dtype) of every logical HF tensor (the refit wire format)."""
+        from rl_b200.models.hf_io import iter_hf_tensors
+
+        return {n: (tuple(t.shape), t.dtype) for n, t in iter_hf_tensors(self.model)}
+
+    def offload_before_refit(self):
+        pass
+
+    def offload_after_refit(self):
+        pass
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, weights_path: str, optimizer_path: Optional[str] = None, tokenizer_path: Optional[str] = None,
+                        model_save_format: str = "safetensors", **kw) -> None:
+        from rl_b200.checkpoint.io import save_optimizer_shard, save_weights
+
+        save_weights(self, weights_path, model_save_format)
+        if optimizer_path and self.optimizer is not None:
+            save_optimizer_shard(self, optimizer_path)
+        if tokenizer_path and self.tokenizer is not None and self.rank == 0:
+            self.tokenizer.save_pretrained(tokenizer_path)
+        if self.world > 1:
+            dist.barrier(group=self.dp_group)
+
+    def load_checkpoint(self, weights_path: str, optimizer_path: Optional[str] = None) -> None:
+        from rl_b200.checkpoint.io import load_optimizer_shard, load_weights
+
+        load_weights(self, weights_path)
+        if optimizer_path and self.optimizer is not None and os.path.exists(optimizer_path):
+            load_optimizer_shard(self, optimizer_path)
+
+    def shutdown(self) -> bool:
+        if self.generation is not None:
+            self.generation.shutdown()
+        return True

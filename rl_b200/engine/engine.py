@@ -477,11 +477,13 @@ class GenerationEngine:
                 torch.cuda.current_stream().wait_stream(side)
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
+                before = _L.Counters.launches
                 with torch.cuda.graph(graph):
                     self._decode_body(st, B, sp, num_splits, scratch)
-                g = (graph, scratch)
+                g = (graph, scratch, _L.Counters.launches - before)
                 self._graphs[key] = g
             g[0].replay()
+            _L.Counters.graph_replayed(g[2])
         else:
             no, nml = E.decode_scratch_sizes(B, c.num_attention_heads, num_splits, c.head_dim)
             scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
@@ -546,10 +548,11 @@ class GenerationEngine:
                     hb["block_table"][n:B] = 0
                 for k in ("ids", "positions", "slots", "block_table", "seq_lens"):
                     st[k][:B].copy_(hb[k][:B], non_blocking=True)
+                    _L.Counters.h2d_bytes += hb[k][:B].numel() * hb[k].element_size()
                 self._step_counter += 1
                 st["step"].fill_(self._step_counter)
                 tok, lp = self._run_decode(n, sp, max_ctx)
-                tok_h, lp_h = tok.cpu().tolist(), lp.cpu().tolist()
+                tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(decode, fin)
                 for j, sid in enumerate(decode):
@@ -573,7 +576,7 @@ class GenerationEngine:
                         toks.extend(seq)
                         lens.append(len(seq))
                         slots.append(self.sched.slots(sid, 0, len(seq)))
-                    ids = torch.tensor(toks, dtype=torch.int32 if self.native else torch.int64, device=dev)
+                    ids = _L.to_device(torch.tensor(toks, dtype=torch.int32 if self.native else torch.int64), dev)
                     lens_t = torch.tensor(lens, dtype=torch.int64)
                     cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
                     cu[1:] = lens_t.cumsum(0)
@@ -598,7 +601,7 @@ class GenerationEngine:
                 else:
                     gen = torch.Generator().manual_seed(sp.seed * 1000003 + self._step_counter)
                     tok, lp = E.sample(rows, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, generator=gen)
-                tok_h, lp_h = tok.cpu().tolist(), lp.cpu().tolist()
+                tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(new, fin, first=True)
                 for j, sid in enumerate(new):

@@ -83,8 +83,11 @@ class _Linear(torch.autograd.Function):
         if residual is not None:
             r2 = residual.reshape(-1, residual.shape[-1])
             assert r2.dtype == BF16 and r2.stride(-1) == 1
-        y = gemm(x2, w, bias=bias, residual=r2, out_dtype=x.dtype)
-        return y.view(*x.shape[:-1], w.shape[0])
+        # the result is allocated in its final shape so that the returned tensor is not a view (in-place consumers
+        # such as RoPE may then modify it under autograd)
+        y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
+        gemm(x2, w, bias=bias, residual=r2, out=y.view(-1, w.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -354,9 +357,9 @@ def _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale):
         if e <= s:
             continue
         qs = q[s:e].transpose(0, 1).unsqueeze(0)
-        ks = k[s:e].transpose(0, 1).repeat_interleave(g, 0).unsqueeze(0)
-        vs = v[s:e].transpose(0, 1).repeat_interleave(g, 0).unsqueeze(0)
-        o = tF.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale)
+        ks = k[s:e].transpose(0, 1).unsqueeze(0)
+        vs = v[s:e].transpose(0, 1).unsqueeze(0)
+        o = tF.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale, enable_gqa=g > 1)
         out[s:e] = o[0].transpose(0, 1)
     return out.reshape(T, Hq * D)
 

@@ -123,11 +123,49 @@ def check_status(device=None) -> int:
     return v
 
 
+class Counters:
+    """Process-wide counts of native kernel launches and host<->device bytes, for benchmark reporting.
+
+    ``launches`` counts every entry-point call that enqueues kernels; a CUDA-graph replay adds the number of calls
+    that were recorded while the graph was captured (``graph_replayed``)."""
+
+    launches = 0
+    h2d_bytes = 0
+    d2h_bytes = 0
+
+    @classmethod
+    def reset(cls) -> None:
+        cls.launches = cls.h2d_bytes = cls.d2h_bytes = 0
+
+    @classmethod
+    def graph_replayed(cls, calls_in_graph: int) -> None:
+        cls.launches += calls_in_graph
+
+
 def call(name: str, *args) -> None:
     fn = getattr(lib(), name)
     rc = fn(*args)
+    Counters.launches += 1
     if rc != 0:
         raise NativeLibraryError(f"{name} failed with code {rc}")
+
+
+def to_device(t: torch.Tensor, device, non_blocking: bool = True) -> torch.Tensor:
+    """Host -> device copy through pinned memory, counted in ``Counters.h2d_bytes``."""
+    if t.device.type != "cpu" or torch.device(device).type == "cpu":
+        return t.to(device)
+    if not t.is_pinned():
+        t = t.pin_memory()
+    Counters.h2d_bytes += t.numel() * t.element_size()
+    return t.to(device, non_blocking=non_blocking)
+
+
+def to_host(t: torch.Tensor) -> torch.Tensor:
+    """Device -> host copy, counted in ``Counters.d2h_bytes``."""
+    if t.device.type == "cpu":
+        return t
+    Counters.d2h_bytes += t.numel() * t.element_size()
+    return t.cpu()
 
 
 def use_native(t: torch.Tensor) -> bool:

@@ -27,6 +27,7 @@ from rl_b200.distributed.batched_data_dict import BatchedDataDict
 from rl_b200.models.config import ModelConfig, preset
 from rl_b200.models.transformer import CausalLM, PackedBatch, build_model
 from rl_b200.policy.optimizer import LRSchedule, ShardedAdamW, build_optimizer
+from rl_b200.ops.lib import to_device, to_host
 from rl_b200.utils.flops import transformer_flops
 
 POLICY_DEFAULTS = dict(
@@ -187,8 +188,8 @@ class PolicyWorker:
         return None
 
     def _pack(self, mb: BatchedDataDict) -> tuple[PackedBatch, int]:
-        ids = mb["input_ids"].to(self.device, non_blocking=True)
-        lens = mb["input_lengths"].to(self.device, non_blocking=True)
+        ids = to_device(mb["input_ids"], self.device)
+        lens = to_device(mb["input_lengths"], self.device)
         batch = PackedBatch.from_padded(ids, lens)
         if self.device.type == "cuda":
             batch.input_ids = batch.input_ids.to(torch.int32)
@@ -204,7 +205,7 @@ class PolicyWorker:
         for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob")):
             batch, Smb = self._pack(mb)
             lp, _ = self.model.next_token_logprobs(batch, self.temperature)
-            out[torch.as_tensor(idx), :Smb] = batch.unpack(lp, Smb).cpu()
+            out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
         return out
 
     def get_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
@@ -295,8 +296,8 @@ class PolicyWorker:
             gb_loss = torch.zeros((), device=self.device)
             for mb, _ in self._microbatches(gb, mbs, self._token_budget("train")):
                 batch, S = self._pack(mb)
-                mb_dev = BatchedDataDict({k: (v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v)
-                                          for k, v in mb.items()})
+                mb_dev = BatchedDataDict({k: (to_device(v, self.device) if isinstance(v, torch.Tensor) else v)
+                                          for k, v in mb.items() if k != "input_ids"})
                 mb_dev.truncate_tensors(1, S)
                 total_tokens += int(batch.input_ids.numel())
                 with torch.set_grad_enabled(not eval_mode):

@@ -753,3 +753,60 @@ RLB_API int rlb_add_bf16(const void* a, const void* b, void* y, long long n, voi
   add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, S(stream)>>>(CBF(a), CBF(b), BF(y), n / 8);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ RMSNorm backward without device allocation
+// See no_alloc.h for who this is for and what it costs. The scratch that rlb_rmsnorm_bwd takes from its caller is a
+// fixed array in the library image here. In host code the array's name is only a host-side handle, not a device
+// address, so the address the kernels receive is looked up once per device with cudaGetSymbolAddress.
+#include "no_alloc.h"
+
+namespace {
+static __device__ __align__(256) float g_rmsnorm_static_scratch[RLB_RMSNORM_STATIC_MAX_PARTS * RLB_RMSNORM_STATIC_MAX_D];
+constexpr int kMaxDevices = 64;
+float* g_rmsnorm_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device, resolved on first use there.
+int rmsnorm_static_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return RLB_STATIC_ERR_NO_SYMBOL;
+  if (!g_rmsnorm_static_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_static_scratch);
+    if (e != cudaSuccess || !p) return e != cudaSuccess ? static_cast<int>(e) : RLB_STATIC_ERR_NO_SYMBOL;
+    g_rmsnorm_static_ptr[dev] = p;
+  }
+  *out = g_rmsnorm_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+RLB_API int rlb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                   float* dw_f32, int dw_accumulate, long long rows, int d, long long x_stride,
+                                   long long dy_stride, void* stream) {
+  if (rows <= 0) return 0;
+  if (d <= 0 || d % 8 || x_stride % 8 || dy_stride % 8) return RLB_STATIC_ERR_BAD_SHAPE;
+  if (d > RLB_RMSNORM_STATIC_MAX_D) return RLB_STATIC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = rmsnorm_static_scratch(&scratch);
+  if (rc) return rc;
+  const int threads = rms_threads(d);
+  const int parts = static_cast<int>(rows < RLB_RMSNORM_STATIC_MAX_PARTS ? rows : RLB_RMSNORM_STATIC_MAX_PARTS);
+  // Every CTA writes its whole row of the partial matrix before the column-sum kernel reads it, so what an earlier
+  // call left in the array is never read.
+  rmsnorm_bwd_kernel<<<parts, threads, 0, S(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch,
+                                                       static_cast<int>(rows), d, x_stride, dy_stride, 0);
+  colsum_kernel<<<(d + 255) / 256, 256, 0, S(stream)>>>(scratch, parts, d, dw_f32, nullptr, dw_accumulate);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RLB_API const char* rlb_rmsnorm_bwd_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case RLB_STATIC_ERR_BAD_SHAPE: return "d and the strides must be positive multiples of 8 elements";
+    case RLB_STATIC_ERR_TOO_LARGE: return "d exceeds RLB_RMSNORM_STATIC_MAX_D (8192): use rlb_rmsnorm_bwd with caller scratch";
+    case RLB_STATIC_ERR_NO_SYMBOL: return "the static scratch array's device address could not be resolved";
+    default: return code > 0 ? "CUDA error (see cudaGetErrorString)" : "unknown code";
+  }
+}

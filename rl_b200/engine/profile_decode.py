@@ -1,0 +1,63 @@
+"""Decode-phase profiler for the generation engine.
+
+    python -m rl_b200.engine.profile_decode --model llama3.1-8b --batch 64 --context 768 --steps 64 [--layers N] [--eager]
+
+Builds a random-init model, prefills ``batch`` prompts of ``context`` tokens, decodes ``steps`` tokens and prints the
+wall time per decode step (host + device) and, from CUDA events around graph replays, the device time per step. Run it
+under ``ncu --metrics gpu__time_duration.sum`` with ``--eager --layers 4`` to list every kernel of a decode step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import time
+
+import torch
+
+from rl_b200.engine.engine import GenerationEngine, SamplingParams
+from rl_b200.models.config import preset
+from rl_b200.models.transformer import CausalLM
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3.1-8b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=768)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--distinct-prompts", action="store_true", help="no prefix sharing between the prompts")
+    a = ap.parse_args(argv)
+    mc = preset(a.model)
+    if a.layers:
+        mc.num_hidden_layers = a.layers
+    dev = torch.device("cuda", 0)
+    model = CausalLM(mc, dtype=torch.bfloat16, device=dev, seed=0)
+    eng = GenerationEngine(model, block_size=64, kv_cache_tokens=a.batch * (a.context + a.steps + 64), max_running=max(64, a.batch),
+                           max_model_len=a.context + a.steps + 64, use_cuda_graphs=not a.eager)
+    g = torch.Generator().manual_seed(0)
+    n_unique = a.batch if a.distinct_prompts else max(1, a.batch // 8)
+    uniq = [torch.randint(0, mc.vocab_size, (a.context,), generator=g).tolist() for _ in range(n_unique)]
+    prompts = [uniq[i % n_unique] for i in range(a.batch)]
+    sp = SamplingParams(max_new_tokens=a.steps, stop_token_ids=[], seed=1)
+    eng.generate(prompts, SamplingParams(max_new_tokens=4, stop_token_ids=[], seed=1))  # warm-up, graph capture
+    eng.sleep(free_kv_cache=False)
+    for k in eng.stats:
+        eng.stats[k] = 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eng.generate(prompts, sp)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    st = eng.stats
+    out = dict(model=a.model, layers=mc.num_hidden_layers, batch=a.batch, context=a.context, steps=st["decode_steps"],
+               graphs=not a.eager, wall_s=round(wall, 4), prefill_s=round(st["prefill_s"], 4),
+               decode_ms_per_step=round(1e3 * st["decode_s"] / max(1, st["decode_steps"]), 4),
+               weight_stream_floor_ms=round(mc.num_parameters() * 2 / 6.5e12 * 1e3, 3))
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -17,6 +17,7 @@ from . import lib as _L
 from .lib import call, ptr, stream_ptr, use_native
 
 BF16 = torch.bfloat16
+SKINNY_MAX_M = 256  # batches up to this many rows take the weight-streaming GEMM
 
 
 # --------------------------------------------------------------------------------------- GEMM
@@ -64,6 +65,12 @@ def gemm(
     assert out.stride(1) == 1 and out.dtype in (BF16, torch.float32)
     if bias is not None:
         bias = bias.float().contiguous()
+    if M <= SKINNY_MAX_M and not a_mn and not b_mn and not accumulate and max_ctas == 0 and K >= 256:
+        # decode-sized batches: weight-streaming kernel with cluster split-K
+        call("rlb_gemm_skinny", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+             int(out.dtype == torch.float32), ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
+             0, ptr(_L.status_word(a.device)), stream_ptr())
+        return out
     call(
         "rlb_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ptr(bias),

@@ -28,6 +28,8 @@ U64 = C.c_ulonglong
 _SIGS: dict[str, list[Any]] = {
     "rlb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, P, P, L, P, I, P],
     "rlb_gemm_num_n_tiles": [I],
+    "rlb_gemm_skinny": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, P, P],
+    "rlb_gemm_skinny_split": [I, I],
     "rlb_lm_head_logprob": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P, P, P, P],
     "rlb_logprob_combine": [P, P, P, P, I, I, P, P, P, P],
     "rlb_lm_head_partials": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P],
@@ -50,6 +52,7 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_add_bf16": [P, P, P, L, P],
     "rlb_kv_cache_write": [P, P, P, P, L, I, I, I, I, L, P],
     "rlb_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
+    "rlb_paged_decode_tma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
     "rlb_sample": [P, I, L, I, I, P, P, P, F, I, F, I, U64, U64, P, P, P, P],
     "rlb_block_copy": [P, P, P, P, I, L, P],
     "rlb_gather_rows": [P, P, P, L, I, L, L, P],

@@ -217,16 +217,18 @@ def test_sampling_distribution_and_filters(native_lib):
 
 @pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 2)])
 @pytest.mark.parametrize("splits", [1, 3])
-def test_paged_decode(native_lib, Hq, Hkv, splits):
+@pytest.mark.parametrize("bs", [16, 64, 128, 48])
+def test_paged_decode(native_lib, Hq, Hkv, splits, bs):
     from rl_b200.ops import engine_ops as E
+    from rl_b200.ops.lib import check_status
 
     torch.manual_seed(0)
-    D, bs, nblocks, B = 128, 16, 64, 5
+    D, nblocks, B = 128, 64, 5
     kc = torch.randn(nblocks, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
     vc = torch.randn(nblocks, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
-    lens = torch.tensor([1, 17, 100, 160, 33], device="cuda", dtype=torch.int32)
+    lens = torch.tensor([1, 17, 100, 160, 333], device="cuda", dtype=torch.int32)
     perm = torch.randperm(nblocks, device="cuda").to(torch.int32)
-    bt = torch.zeros(B, 12, device="cuda", dtype=torch.int32)
+    bt = torch.zeros(B, 24, device="cuda", dtype=torch.int32)
     c = 0
     for b in range(B):
         nb = (int(lens[b]) + bs - 1) // bs
@@ -234,6 +236,8 @@ def test_paged_decode(native_lib, Hq, Hkv, splits):
         c += nb
     q = torch.randn(B, Hq * D, device="cuda", dtype=torch.bfloat16)
     out = E.paged_decode(q, kc, vc, bt, lens, Hq, Hkv, D, num_splits=splits)
+    torch.cuda.synchronize()
+    assert check_status() == 0
     ref = E.paged_decode(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), lens.cpu(), Hq, Hkv, D)
     _close(out.cpu(), ref, 2e-2)
 

@@ -103,3 +103,40 @@ def test_lm_head_logprob(native_lib, M, V, K):
     (lr * cl + er * ce).sum().backward()
     assert _rel_err(h.grad, hr.grad) < 3e-2
     assert _rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("M", [1, 7, 32, 64, 100, 128, 200, 256])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (6144, 4096), (4096, 14336), (1000, 512), (128256, 1024)])
+def test_skinny_gemm(native_lib, M, N, K):
+    """Decode-sized GEMM (operands swapped, cluster split-K) against fp32 matmul, with bias / residual / fp32 output."""
+    from rl_b200.ops import functional as F
+    from rl_b200.ops.lib import check_status
+
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    y = F.gemm(x, w)
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    assert _rel_err(y, ref) < 1e-2
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    y2 = F.gemm(x, w, bias=bias, residual=res, out_dtype=torch.float32)
+    assert _rel_err(y2, ref + bias + res.float()) < 2e-3
+
+
+def test_skinny_split_values(native_lib):
+    from rl_b200.ops.lib import call, lib, ptr, status_word, stream_ptr
+
+    x = torch.randn(64, 4096, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(4096, 4096, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    outs = []
+    for split in (1, 2, 3, 4, 8):
+        y = torch.empty(64, 4096, device="cuda", dtype=torch.bfloat16)
+        call("rlb_gemm_skinny", ptr(x), ptr(w), ptr(y), 64, 4096, 4096, 4096, 4096, 4096, 0, None, None, 0, split,
+             ptr(status_word()), stream_ptr())
+        assert _rel_err(y, ref) < 1e-2, split
+        outs.append(y)
+    assert lib().rlb_gemm_skinny_split(4096, 4096) in (1, 2, 4, 8)

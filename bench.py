@@ -29,6 +29,8 @@ import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
+# one growing segment per stream instead of fixed-size blocks: the training phase re-uses what generation freed
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 
 def parse():
@@ -267,8 +269,9 @@ def main() -> int:
         e2e = dict(seconds=e2e_s, h2d=L.Counters.h2d_bytes // args.steps, d2h=L.Counters.d2h_bytes // args.steps)
 
     # ---------------------------------------------------------------- reduce over ranks
-    stats = torch.tensor([dev_ms, e2e["seconds"] if e2e else 0.0, float(sum(tokens_per_step)), float(launches)] +
+    stats = torch.tensor([dev_ms, e2e["seconds"] if e2e else 0.0, float(sum(tokens_per_step)), float(launches), mult_prob_err] +
                          [phase_ms[k] for k in ("generation", "refit", "logprobs", "training")], dtype=torch.float64, device=dev)
+    PH = 5  # index of the first phase entry
     mx = stats.clone()
     sm = stats.clone()
     if world > 1:
@@ -301,8 +304,8 @@ def main() -> int:
                 "l2": "inputs larger than L2 (16 GB of weights streamed every pass)",
             },
             "tokens_per_sec_per_gpu": round(value / world, 1),
-            "step_split_ms": {k: round(float(mx[4 + i]) / args.steps, 2) for i, k in enumerate(("generation", "refit", "logprobs", "training"))},
-            "token_mult_prob_error": round(mult_prob_err, 5),
+            "step_split_ms": {k: round(float(mx[PH + i]) / args.steps, 2) for i, k in enumerate(("generation", "refit", "logprobs", "training"))},
+            "token_mult_prob_error": round(float(sm[4]), 5),  # per-rank partial means sum to the global mean
             "clocks": clocks,
             "gpu_launches": int(float(mx[3])),
             "impl": "ours",

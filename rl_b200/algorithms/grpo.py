@@ -328,6 +328,8 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                 with timer.time("data_processing"):
                     repeated = batch.repeat_interleave(n_gen)
                     repeated["message_log"] = [[dict(m) for m in log] for log in repeated["message_log"]]
+                    # random streams keyed by (global sample index, turn): rollouts do not depend on the rank layout
+                    repeated["rng_ids"] = repeated["idx"] * n_gen + torch.arange(n_gen).repeat(batch.size)
                     prompt_flat, prompt_lens = batched_message_log_to_flat_message(repeated["message_log"], {"token_ids": pad})
                     prompt_ids = prompt_flat["token_ids"]
                 # ---- refit + generation

@@ -91,9 +91,12 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temps,
               const int* __restrict__ top_ks, const float* __restrict__ top_ps, float def_temp, int def_top_k,
               float def_top_p, int greedy, unsigned long long seed, unsigned long long step,
-              const unsigned long long* __restrict__ step_ptr, int* __restrict__ out_tok,
-              float* __restrict__ out_logprob) {
+              const unsigned long long* __restrict__ step_ptr, const long long* __restrict__ row_keys,
+              int* __restrict__ out_tok, float* __restrict__ out_logprob) {
   if (step_ptr) step = *step_ptr;  // a counter in device memory lets a captured graph draw fresh numbers
+  // With row_keys the random stream of a row depends only on (seed, key), e.g. key = request id and token position:
+  // the draw is then independent of which other rows share the batch or which rank serves the request.
+  const unsigned long long rk = row_keys ? static_cast<unsigned long long>(row_keys[blockIdx.x]) : 0ull;
   __shared__ float red[32];
   __shared__ ArgBest redb[32];
   const int row = blockIdx.x;
@@ -151,8 +154,9 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
   for (int i4 = threadIdx.x * 4; i4 < V; i4 += blockDim.x * 4) {
     uint32_t rnd[4] = {0, 0, 0, 0};
     if (!is_greedy)
-      philox4x32(static_cast<uint32_t>(i4 >> 2), static_cast<uint32_t>(row), static_cast<uint32_t>(step),
-                 static_cast<uint32_t>(step >> 32), k0, k1, rnd);
+      philox4x32(static_cast<uint32_t>(i4 >> 2), row_keys ? static_cast<uint32_t>(rk) : static_cast<uint32_t>(row),
+                 row_keys ? static_cast<uint32_t>(rk >> 32) : static_cast<uint32_t>(step),
+                 row_keys ? 0x5eedu : static_cast<uint32_t>(step >> 32), k0, k1, rnd);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int i = i4 + j;
@@ -185,16 +189,17 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
 RLB_API int rlb_sample(const void* logits, int dtype, long long row_stride, int B, int V, const float* temps,
                        const int* top_ks, const float* top_ps, float def_temp, int def_top_k, float def_top_p,
                        int greedy, unsigned long long seed, unsigned long long step,
-                       const unsigned long long* step_ptr, int* out_tok, float* out_logprob, void* stream) {
+                       const unsigned long long* step_ptr, const long long* row_keys, int* out_tok,
+                       float* out_logprob, void* stream) {
   if (B <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
     sample_kernel<float><<<B, 1024, 0, s>>>(reinterpret_cast<const float*>(logits), row_stride, V, temps, top_ks,
                                            top_ps, def_temp, def_top_k, def_top_p, greedy, seed, step, step_ptr,
-                                           out_tok, out_logprob);
+                                           row_keys, out_tok, out_logprob);
   else
     sample_kernel<__nv_bfloat16><<<B, 1024, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V,
                                                     temps, top_ks, top_ps, def_temp, def_top_k, def_top_p, greedy,
-                                                    seed, step, step_ptr, out_tok, out_logprob);
+                                                    seed, step, step_ptr, row_keys, out_tok, out_logprob);
   return static_cast<int>(cudaGetLastError());
 }

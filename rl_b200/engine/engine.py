@@ -307,6 +307,7 @@ class _Request:
     finished: bool = False
     truncated: bool = False
     share_with: int = -1
+    uid: int = 0  # keys the request's random stream: same uid and seed -> same draws on any rank / batch
 
 
 class GenerationEngine:
@@ -426,6 +427,7 @@ class GenerationEngine:
                 top_ks=torch.zeros(B, dtype=torch.int32, device=dev),
                 top_ps=torch.ones(B, dtype=torch.float32, device=dev),
                 step=torch.zeros(1, dtype=torch.int64, device=dev),
+                keys=torch.zeros(B, dtype=torch.int64, device=dev),
                 tok=torch.zeros(B, dtype=torch.int32, device=dev),
                 lp=torch.zeros(B, dtype=torch.float32, device=dev),
                 host=dict(
@@ -448,8 +450,7 @@ class GenerationEngine:
         logits = self._decode_forward(st["ids"][:B], st["positions"][:B], st["slots"][:B], st["block_table"][:B],
                                       st["seq_lens"][:B], num_splits, scratch)
         E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=sp.seed,
-                 step_tensor=st["step"] if self.native else None, step=self._step_counter, temps=None,
-                 out=(st["tok"][:B], st["lp"][:B]) if self.native else None)
+                 row_keys=st["keys"][:B], out=(st["tok"][:B], st["lp"][:B]))
         return logits
 
     def _run_decode(self, n: int, sp: SamplingParams, max_ctx: int):
@@ -460,8 +461,8 @@ class GenerationEngine:
         if not self.native:
             logits = self._decode_forward(st["ids"][:n].long(), st["positions"][:n], st["slots"][:n], st["block_table"][:n],
                                           st["seq_lens"][:n], 1, None)
-            gen = torch.Generator().manual_seed(sp.seed * 1000003 + self._step_counter)
-            tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, generator=gen)
+            tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy,
+                               seed=sp.seed, row_keys=st["keys"][:n])
             return tok[:n], lp[:n]
         key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed)
         if self.use_graphs:
@@ -493,7 +494,7 @@ class GenerationEngine:
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, max_new_tokens: Optional[Sequence[int]] = None,
-                 share_prefixes: bool = True) -> list[_Request]:
+                 share_prefixes: bool = True, request_uids: Optional[Sequence[int]] = None) -> list[_Request]:
         """Runs all prompts to completion with continuous batching. Returns one record per prompt (in input order)
         with the generated tokens, their log-probabilities and whether generation was cut by the length limit."""
         self.wake()
@@ -512,7 +513,7 @@ class GenerationEngine:
                     share = first_of[key]
                 else:
                     first_of[key] = i
-            reqs[i] = _Request(i, p, mx, share_with=share)
+            reqs[i] = _Request(i, p, mx, share_with=share, uid=int(request_uids[i]) if request_uids is not None else i)
             if self.sched.add(i, len(p), mx, share) != 0:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
         dev = self.device
@@ -537,6 +538,8 @@ class GenerationEngine:
                 hb["positions"][:n] = ctx
                 max_ctx = int(ctx.max()) + 1
                 hb["seq_lens"][:n] += 1
+                keys_h = torch.tensor([(reqs[sid].uid << 20) | len(reqs[sid].out_tokens) for sid in decode], dtype=torch.int64)
+                st["keys"][:n].copy_(keys_h)
                 for j, sid in enumerate(decode):
                     hb["ids"][j] = reqs[sid].out_tokens[-1]
                 B = self._bucket(n)
@@ -595,12 +598,9 @@ class GenerationEngine:
                 new = list(prefill) + list(shared)
                 rows = torch.stack([last_logits[sid] if sid in last_logits else last_logits[reqs[sid].share_with] for sid in new])
                 self._step_counter += 1
-                if self.native:
-                    tok, lp = E.sample(rows.contiguous(), temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p,
-                                       greedy=sp.greedy, seed=sp.seed, step=self._step_counter)
-                else:
-                    gen = torch.Generator().manual_seed(sp.seed * 1000003 + self._step_counter)
-                    tok, lp = E.sample(rows, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, generator=gen)
+                keys_new = torch.tensor([(reqs[sid].uid << 20) | len(reqs[sid].out_tokens) for sid in new], dtype=torch.int64, device=dev)
+                tok, lp = E.sample(rows.contiguous(), temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p,
+                                   greedy=sp.greedy, seed=sp.seed, row_keys=keys_new)
                 tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(new, fin, first=True)

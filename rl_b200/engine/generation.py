@@ -111,7 +111,8 @@ class NativeGeneration:
         ids_cpu = ids.cpu()
         prompts = [ids_cpu[i, : lens_l[i]].tolist() for i in range(B)]
         sp = self._sampling(greedy)
-        recs = self.engine.generate(prompts, sp)
+        uids = data["rng_ids"].tolist() if "rng_ids" in data else None
+        recs = self.engine.generate(prompts, sp, request_uids=uids)
         stop_strings = data.get("stop_strings") or self.cfg.get("stop_strings")
         if stop_strings and self.tokenizer is not None:
             self._apply_stop_strings(recs, stop_strings)

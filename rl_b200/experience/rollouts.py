@@ -27,6 +27,8 @@ def generate_responses(generation, flat_ids: torch.Tensor, input_lengths: torch.
     gen_in = BatchedDataDict(input_ids=flat_ids, input_lengths=input_lengths)
     if stop_strings is not None:
         gen_in["stop_strings"] = stop_strings
+    if "rng_ids" in batch:
+        gen_in["rng_ids"] = batch["rng_ids"]
     out = generation.generate(gen_in, greedy=greedy)
     out_ids, logprobs = out["output_ids"], out["logprobs"]
     gen_lens, tot_lens = out["generation_lengths"], out["unpadded_sequence_lengths"]

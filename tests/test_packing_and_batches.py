@@ -1,0 +1,90 @@
+"""Sequence packers and BatchedDataDict sharding / micro-batching."""
+
+import random
+
+import pytest
+import torch
+
+from rl_b200.data.packing import get_packer
+from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+ALGOS = ["concatenative", "first_fit", "first_fit_decreasing", "first_fit_shuffle", "modified_first_fit_decreasing"]
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+def test_packers_are_valid_partitions(algo):
+    rng = random.Random(0)
+    lens = [rng.randint(1, 1000) for _ in range(500)]
+    p = get_packer(algo, 1024, collect_metrics=True)
+    bins = p.pack(lens)
+    flat = sorted(i for b in bins for i in b)
+    assert flat == list(range(len(lens)))
+    assert all(sum(lens[i] for i in b) <= 1024 for b in bins)
+    assert p.metrics.aggregated()["total_sequences"] == 500
+
+
+def test_mffd_no_worse_than_ffd_on_classic_case():
+    lens = [51] * 6 + [27] * 6 + [26] * 6 + [23] * 12
+    ffd = len(get_packer("first_fit_decreasing", 100).pack(lens))
+    mffd = len(get_packer("modified_first_fit_decreasing", 100).pack(lens))
+    lower = -(-sum(lens) // 100)
+    assert lower <= mffd <= ffd
+
+
+def test_packer_rejects_oversize_and_pads_bin_count():
+    with pytest.raises(ValueError):
+        get_packer("first_fit", 10).pack([11])
+    bins = get_packer("first_fit_decreasing", 100, min_bin_count=4, bin_count_multiple=4).pack([60, 30, 20])
+    assert len(bins) % 4 == 0 and sorted(i for b in bins for i in b) == [0, 1, 2]
+
+
+def _data(n=16, S=12):
+    lens = torch.randint(2, S + 1, (n,), generator=torch.Generator().manual_seed(0))
+    return BatchedDataDict(input_ids=torch.arange(n * S).reshape(n, S), input_lengths=lens, tag=[f"s{i}" for i in range(n)])
+
+
+def test_shard_plain_and_uneven():
+    d = _data()
+    shards = d.shard_by_batch_size(4, batch_size=8)
+    assert [s.size for s in shards] == [4, 4, 4, 4]
+    # every global batch of 8 is split evenly: shard r holds samples r*2..r*2+1 of batch 0 and of batch 1
+    assert shards[1]["tag"] == ["s2", "s3", "s10", "s11"]
+    un = d.slice(0, 10).shard_by_batch_size(4, allow_uneven_shards=True)
+    assert [s.size for s in un] == [3, 3, 2, 2]
+
+
+def test_dynamic_batching_respects_budget_and_roundtrips():
+    d = _data(32, 64)
+    shards, order = d.shard_by_batch_size(2, batch_size=16, dynamic_batching_args=dict(
+        input_key="input_ids", input_lengths_key="input_lengths", sequence_length_round=8, max_tokens_per_microbatch=128))
+    assert sorted(order) == list(range(32))
+    for sh in shards:
+        n = 0
+        for mb in sh.make_microbatch_iterator_with_dynamic_shapes():
+            assert mb["input_ids"].shape[0] * mb["input_ids"].shape[1] <= 128 or mb["input_ids"].shape[0] == 1
+            assert int(mb["input_lengths"].max()) <= mb["input_ids"].shape[1]
+            n += mb.size
+        assert n == sh.size
+    merged = BatchedDataDict.from_batches(shards).reorder_data(order)
+    assert merged["tag"] == d["tag"] and torch.equal(merged["input_ids"], d["input_ids"])
+
+
+def test_sequence_packing_bins():
+    d = _data(32, 64)
+    shards, order = d.shard_by_batch_size(4, batch_size=32, sequence_packing_args=dict(
+        input_key="input_ids", input_lengths_key="input_lengths", max_tokens_per_microbatch=160, algorithm="modified_first_fit_decreasing"))
+    counts = {sh.get_microbatch_iterator_len() for sh in shards}
+    assert len(counts) == 1  # every rank steps the same number of micro-batches
+    assert sorted(order) == list(range(32))
+    for sh in shards:
+        for mb in sh.make_microbatch_iterator_for_packable_sequences():
+            assert int(mb["input_lengths"].sum()) <= 160
+
+
+def test_from_batches_pads_and_repeat_interleave():
+    a = BatchedDataDict(x=torch.ones(2, 3), l=[1, 2])
+    b = BatchedDataDict(x=torch.ones(1, 5), l=[3])
+    m = BatchedDataDict.from_batches([a, b], pad_value_dict={"x": -1})
+    assert m["x"].shape == (3, 5) and m["x"][0, 4] == -1 and m["l"] == [1, 2, 3]
+    r = m.repeat_interleave(2)
+    assert r.size == 6 and r["l"] == [1, 1, 2, 2, 3, 3]

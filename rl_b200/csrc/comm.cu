@@ -1,0 +1,311 @@
+// Peer-memory communication over NVLink / NVSwitch: symmetric buffers shared between the ranks of one node through
+// CUDA IPC, flag barriers with bounded waits, and the fused optimizer step
+//
+//     reduce-scatter(fp32 grads) -> global grad-norm + clip -> AdamW on the local shard -> all-gather(bf16 params)
+//
+// as ONE cooperative kernel. Every rank pulls its shard of the gradient from all peers with plain P2P loads (fixed
+// rank order, so the sum is bit-reproducible), keeps the reduced shard in its own gradient buffer, exchanges one
+// float per rank for the global norm, applies AdamW to the split fp32 master (bf16 + 16 low bits), and pushes the new
+// bf16 parameters straight into every peer's parameter buffer with P2P stores. No NCCL call, no staging copy, no
+// separate cast / scale / norm kernels; the NCCL form in rl_b200/policy/optimizer.py is its twin.
+//
+// Cross-GPU waits spin on flag words that peers write with st.release.sys; every wait is bounded by %globaltimer and
+// records a status code instead of hanging. No multimem / multicast object is used, so a rank that dies cannot fault
+// its peers' GPUs through a shared multicast binding.
+//
+// Counterpart in the reference: FSDP2 reduce-scatter + torch.optim.AdamW + parameter all-gather
+// (nemo_rl/models/automodel/setup.py:481-493, nemo_rl/models/dtensor/parallelize.py:780-882).
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+#include <string.h>
+
+namespace {
+using namespace rlb;
+namespace cg = cooperative_groups;
+
+constexpr int MAX_RANKS = 8;
+constexpr int FLAG_STAGES = 4;
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct PeerTable {
+  float* grad[MAX_RANKS];            // full fp32 gradient buffers
+  __nv_bfloat16* param[MAX_RANKS];   // full bf16 parameter buffers
+  unsigned int* flags[MAX_RANKS];    // [FLAG_STAGES][MAX_RANKS] epoch words
+  float* slots[MAX_RANKS];           // [MAX_RANKS] per-rank partial sums of squares
+};
+
+// Flag barrier run by the first `world` threads of one CTA. Returns false when a peer did not arrive in time.
+__device__ bool peer_barrier(const PeerTable& t, int rank, int world, int stage, unsigned int epoch,
+                             unsigned long long limit_ns, int* status) {
+  bool ok = true;
+  if (threadIdx.x < world) {
+    st_release_sys(t.flags[threadIdx.x] + stage * MAX_RANKS + rank, epoch);
+    const unsigned int* mine = t.flags[rank] + stage * MAX_RANKS + threadIdx.x;
+    const unsigned long long t0 = globaltimer_ns();
+    // epochs only grow; the signed difference tolerates wrap-around
+    while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (globaltimer_ns() - t0 > limit_ns) {
+        if (status) atomicCAS(status, 0, RLB_ERR_WAIT_PEER);
+        ok = false;
+        break;
+      }
+    }
+  }
+  return __syncthreads_and(ok);
+}
+
+struct FusedOptimArgs {
+  PeerTable peers;
+  int rank, world;
+  long long shard_n;      // elements per rank (multiple of 8)
+  int16_t* p_lo;          // [shard_n] low 16 bits of the fp32 master
+  float* m;
+  float* v;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  float max_grad_norm;    // <= 0: no clipping
+  float grad_div;         // the summed gradient is divided by this
+  unsigned int epoch;     // grows by one per call
+  unsigned long long limit_ns;
+  float* sumsq_local;     // [1] scratch, zeroed by the kernel
+  float* norm_out;        // [1] global gradient norm
+  int* status;
+};
+
+__device__ __forceinline__ void split16(float w, __nv_bfloat16& hi, int16_t& lo) {
+  const uint32_t bits = __float_as_uint(w);
+  const uint32_t hb = (bits + 0x8000u) & 0xFFFF0000u;
+  hi = __ushort_as_bfloat16(static_cast<unsigned short>(hb >> 16));
+  lo = static_cast<int16_t>(static_cast<int32_t>(bits - hb));
+}
+__device__ __forceinline__ float join16(__nv_bfloat16 hi, int16_t lo) {
+  return __uint_as_float((static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16) + static_cast<uint32_t>(static_cast<int32_t>(lo)));
+}
+
+__global__ void __launch_bounds__(512, 1) fused_optim_kernel(FusedOptimArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  __shared__ float red[32];
+  __shared__ float s_scale;
+  const long long lo = static_cast<long long>(a.rank) * a.shard_n;
+  const long long n4 = a.shard_n / 4;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+
+  // stage 0: every rank's gradients are complete
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) *a.sumsq_local = 0.f;
+    peer_barrier(a.peers, a.rank, a.world, 0, a.epoch, a.limit_ns, a.status);
+  }
+  grid.sync();
+
+  // pass 1: pull-reduce my shard from all peers (fixed order), keep it locally, accumulate the sum of squares
+  float ss = 0.f;
+  float* mine = a.peers.grad[a.rank] + lo;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < a.world) {
+        const float4 g = reinterpret_cast<const float4*>(a.peers.grad[r] + lo)[i];
+        acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+      }
+    }
+    reinterpret_cast<float4*>(mine)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) atomicAdd(a.sumsq_local, ss);
+  grid.sync();
+
+  // stage 1: exchange the partial sums, derive the clip coefficient
+  if (blockIdx.x == 0) {
+    if (threadIdx.x < a.world) a.peers.slots[threadIdx.x][a.rank] = *a.sumsq_local;
+    __threadfence_system();
+    __syncthreads();
+    peer_barrier(a.peers, a.rank, a.world, 1, a.epoch, a.limit_ns, a.status);
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int r = 0; r < a.world; ++r) total += reinterpret_cast<volatile float*>(a.peers.slots[a.rank])[r];
+      const float norm = sqrtf(total) / a.grad_div;
+      float scale = 1.f / a.grad_div;
+      if (a.max_grad_norm > 0.f) scale *= fminf(1.f, a.max_grad_norm / (norm + 1e-6f));
+      *a.norm_out = norm;
+      *a.sumsq_local = scale;  // broadcast to the grid through global memory
+    }
+  }
+  grid.sync();
+  if (threadIdx.x == 0) s_scale = *reinterpret_cast<volatile float*>(a.sumsq_local);
+  __syncthreads();
+  const float gs = s_scale;
+
+  // pass 2: AdamW on the shard, new bf16 parameters written into every rank's parameter buffer
+  const __nv_bfloat16* p_mine = a.peers.param[a.rank] + lo;
+  for (long long i = tid; i < n4; i += nthreads) {
+    const float4 g4 = reinterpret_cast<const float4*>(mine)[i];
+    float4 m4 = reinterpret_cast<float4*>(a.m)[i];
+    float4 v4 = reinterpret_cast<float4*>(a.v)[i];
+    const uint2 pw = reinterpret_cast<const uint2*>(p_mine)[i];
+    const uint2 lw = reinterpret_cast<const uint2*>(a.p_lo)[i];
+    const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&pw);
+    const int16_t* pl = reinterpret_cast<const int16_t*>(&lw);
+    float g[4] = {g4.x * gs, g4.y * gs, g4.z * gs, g4.w * gs};
+    float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+    float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+    __nv_bfloat16 nh[4];
+    int16_t nl[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float w = join16(ph[j], pl[j]);
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * g[j];
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * g[j] * g[j];
+      w *= (1.f - a.lr * a.weight_decay);
+      w -= a.lr * (mm[j] / a.bc1) / (sqrtf(vv[j] / a.bc2) + a.eps);
+      split16(w, nh[j], nl[j]);
+    }
+    reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<uint2*>(a.p_lo)[i] = *reinterpret_cast<const uint2*>(nl);
+    const uint2 out = *reinterpret_cast<const uint2*>(nh);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < a.world) reinterpret_cast<uint2*>(a.peers.param[r] + lo)[i] = out;
+  }
+  __threadfence_system();
+  grid.sync();
+  // stage 2: every rank has written its shard into my parameter buffer
+  if (blockIdx.x == 0) peer_barrier(a.peers, a.rank, a.world, 2, a.epoch, a.limit_ns, a.status);
+}
+
+// out[r * n .. (r+1) * n) = peer r's `src` for every r (pull all-gather); flags as in the optimizer.
+struct GatherArgs {
+  const uint4* src[MAX_RANKS];
+  uint4* dst;
+  unsigned int* flags[MAX_RANKS];
+  int rank, world;
+  long long n16;  // 16-byte words per rank
+  unsigned int epoch;
+  unsigned long long limit_ns;
+  int* status;
+};
+__global__ void __launch_bounds__(512, 1) p2p_allgather_kernel(GatherArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  if (blockIdx.x == 0) {
+    PeerTable t;
+    for (int r = 0; r < MAX_RANKS; ++r) t.flags[r] = a.flags[r];
+    peer_barrier(t, a.rank, a.world, 3, a.epoch, a.limit_ns, a.status);
+  }
+  grid.sync();
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int r = 0; r < a.world; ++r) {
+    const int src_rank = (a.rank + r) % a.world;  // start with the local copy, stagger the peers
+    for (long long i = tid; i < a.n16; i += nthreads) a.dst[src_rank * a.n16 + i] = a.src[src_rank][i];
+  }
+}
+
+int coop_grid(const void* kernel, int threads) {
+  int dev = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+  if (per_sm < 1) per_sm = 1;
+  return sms;  // one CTA per SM leaves the copy engines and other streams room
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- symmetric buffers (CUDA IPC)
+// Allocates `bytes` of device memory and returns its 64-byte IPC handle. Peers of the same node map it with
+// rlb_symm_open. The memory comes from cudaMalloc (not the framework's caching allocator) so that it can be exported.
+RLB_API int rlb_symm_alloc(unsigned long long bytes, void** ptr, char* handle64) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+RLB_API int rlb_symm_open(const char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+RLB_API int rlb_symm_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+RLB_API int rlb_symm_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+
+// One fused optimizer step. Pointer tables have `world` entries, entry `rank` being this rank's own buffer.
+// flags: uint32 [4][8] per rank (zero-initialised symmetric memory); slots: float [8] per rank.
+RLB_API int rlb_fused_optim_step(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs,
+                                 void* const* slot_ptrs, int rank, int world, long long shard_n, void* p_lo, float* m,
+                                 float* v, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                                 float max_grad_norm, float grad_div, unsigned int epoch, double wait_limit_s,
+                                 float* sumsq_scratch, float* norm_out, int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || shard_n % 8) return -2;
+  FusedOptimArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int r = 0; r < world; ++r) {
+    a.peers.grad[r] = static_cast<float*>(grad_ptrs[r]);
+    a.peers.param[r] = static_cast<__nv_bfloat16*>(param_ptrs[r]);
+    a.peers.flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
+    a.peers.slots[r] = static_cast<float*>(slot_ptrs[r]);
+  }
+  a.rank = rank;
+  a.world = world;
+  a.shard_n = shard_n;
+  a.p_lo = static_cast<int16_t*>(p_lo);
+  a.m = m;
+  a.v = v;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.weight_decay = weight_decay;
+  a.bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  a.bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  a.max_grad_norm = max_grad_norm;
+  a.grad_div = grad_div;
+  a.epoch = epoch;
+  a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
+  a.sumsq_local = sumsq_scratch;
+  a.norm_out = norm_out;
+  a.status = status;
+  const int grid = coop_grid(reinterpret_cast<const void*>(fused_optim_kernel), 512);
+  void* args[] = {&a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fused_optim_kernel), dim3(grid), dim3(512),
+                                                      args, 0, static_cast<cudaStream_t>(stream)));
+}
+
+// dst[r * bytes_per_rank ...] = peer r's src (pull all-gather over peer memory). bytes_per_rank multiple of 16.
+RLB_API int rlb_p2p_allgather(void* const* src_ptrs, void* dst, void* const* flag_ptrs, int rank, int world,
+                              long long bytes_per_rank, unsigned int epoch, double wait_limit_s, int* status,
+                              void* stream) {
+  if (world < 1 || world > MAX_RANKS || bytes_per_rank % 16) return -2;
+  GatherArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int r = 0; r < world; ++r) {
+    a.src[r] = static_cast<const uint4*>(src_ptrs[r]);
+    a.flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
+  }
+  a.dst = static_cast<uint4*>(dst);
+  a.rank = rank;
+  a.world = world;
+  a.n16 = bytes_per_rank / 16;
+  a.epoch = epoch;
+  a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
+  a.status = status;
+  const int grid = coop_grid(reinterpret_cast<const void*>(p2p_allgather_kernel), 512);
+  void* args[] = {&a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_allgather_kernel), dim3(grid),
+                                                      dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
+}

@@ -436,6 +436,7 @@ class GenerationEngine:
                     slots=torch.zeros(B, dtype=torch.int64).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int64),
                     block_table=torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32),
                     seq_lens=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
+                    keys=torch.zeros(B, dtype=torch.int64).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int64),
                 ),
             )
         return self._static
@@ -538,10 +539,11 @@ class GenerationEngine:
                 hb["positions"][:n] = ctx
                 max_ctx = int(ctx.max()) + 1
                 hb["seq_lens"][:n] += 1
-                keys_h = torch.tensor([(reqs[sid].uid << 20) | len(reqs[sid].out_tokens) for sid in decode], dtype=torch.int64)
-                st["keys"][:n].copy_(keys_h)
+                ids_np, keys_np = hb["ids"].numpy(), hb["keys"].numpy()
                 for j, sid in enumerate(decode):
-                    hb["ids"][j] = reqs[sid].out_tokens[-1]
+                    r = reqs[sid]
+                    ids_np[j] = r.out_tokens[-1]
+                    keys_np[j] = (r.uid << 20) | len(r.out_tokens)
                 B = self._bucket(n)
                 if B > n:  # padding rows: no cache write, empty context
                     hb["slots"][n:B] = -1
@@ -549,7 +551,8 @@ class GenerationEngine:
                     hb["ids"][n:B] = 0
                     hb["positions"][n:B] = 0
                     hb["block_table"][n:B] = 0
-                for k in ("ids", "positions", "slots", "block_table", "seq_lens"):
+                    hb["keys"][n:B] = 0
+                for k in ("ids", "positions", "slots", "block_table", "seq_lens", "keys"):
                     st[k][:B].copy_(hb[k][:B], non_blocking=True)
                     _L.Counters.h2d_bytes += hb[k][:B].numel() * hb[k].element_size()
                 self._step_counter += 1

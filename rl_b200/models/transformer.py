@@ -39,7 +39,10 @@ class FlatParams:
               it, and the linear / norm backward kernels accumulate into those views directly.
     """
 
-    def __init__(self, module: nn.Module, align: int = 2048):
+    def __init__(self, module: nn.Module, align: int = 2048, allocator=None):
+        """``allocator(numel, dtype, device) -> 1-D tensor`` lets the caller place the flat buffers (e.g. in peer-mapped
+        memory); the default is an ordinary zero-filled tensor."""
+        self._allocator = allocator
         params = [(n, p) for n, p in module.named_parameters()]
         self.names = [n for n, _ in params]
         self.shapes = [tuple(p.shape) for _, p in params]
@@ -53,15 +56,23 @@ class FlatParams:
         self.numel = off
         self.padded = -(-off // align) * align
         p0 = params[0][1]
-        self.flat = torch.zeros(self.padded, dtype=p0.dtype, device=p0.device)
+        if allocator is not None:
+            self.flat = allocator(self.padded, p0.dtype, p0.device)
+            self.flat.zero_()
+        else:
+            self.flat = torch.zeros(self.padded, dtype=p0.dtype, device=p0.device)
         for (name, p), o, n in zip(params, self.offsets, self.numels):
             self.flat[o : o + n].copy_(p.data.reshape(-1))
             p.data = self.flat[o : o + n].view(p.shape)
         self.params = [p for _, p in params]
         self.grad: Optional[torch.Tensor] = None
 
-    def attach_grad_buffer(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
-        self.grad = torch.zeros(self.padded, dtype=dtype, device=self.flat.device)
+    def attach_grad_buffer(self, dtype: torch.dtype = torch.float32, allocator=None) -> torch.Tensor:
+        if allocator is not None:
+            self.grad = allocator(self.padded, dtype, self.flat.device)
+            self.grad.zero_()
+        else:
+            self.grad = torch.zeros(self.padded, dtype=dtype, device=self.flat.device)
         for p, o, n in zip(self.params, self.offsets, self.numels):
             p.main_grad = self.grad[o : o + n].view(p.shape)
         return self.grad
@@ -225,8 +236,8 @@ class CausalLM(nn.Module):
                     e = min(flat.numel(), s + step)
                     flat[s:e] = (torch.randn(e - s, generator=g, device=p.device, dtype=torch.float32) * std).to(p.dtype)
 
-    def flatten_parameters(self, align: int = 2048) -> FlatParams:
-        self.flat = FlatParams(self, align)
+    def flatten_parameters(self, align: int = 2048, allocator=None) -> FlatParams:
+        self.flat = FlatParams(self, align, allocator)
         return self.flat
 
     @property

@@ -104,7 +104,7 @@ class ShardedAdamW:
         the global token count). Returns the global gradient norm (a 1-element tensor, no host sync)."""
         self.flat.fold_autograd_grads()
         self.step_count += 1
-        if self.fused_comm is not None and self.world > 1:
+        if self.fused_comm is not None and self.world > 1 and self.fused_comm.usable(self):
             return self.fused_comm.step(self, grad_div)
         gs = self._reduce_scatter()
         self._sumsq.zero_()

@@ -96,7 +96,21 @@ class PolicyWorker:
             self.model.activation_checkpointing = act_ckpt
         else:
             self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt)
-        self.flat = self.model.flatten_parameters(align=256 * self.world)
+        # On several GPUs of one node the flat parameter / gradient buffers live in peer-mapped memory so that the
+        # optimizer step can run as one fused kernel over NVLink (rl_b200/csrc/comm.cu); NCCL is the fallback.
+        if fused_comm is None and self.world > 1 and self.device.type == "cuda" and cfg.get("fused_optimizer", True) \
+                and dtype == torch.bfloat16 and init_optimizer:
+            try:
+                from rl_b200.parallel.symmetric import FusedOptimizerComm
+
+                fused_comm = FusedOptimizerComm(dp_group, wait_limit_s=float(cfg.get("peer_wait_limit_s", 2.0)))
+            except Exception as e:  # no peer access between these GPUs: keep NCCL
+                if self.rank == 0:
+                    print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
+                fused_comm = None
+        self.fused_comm = fused_comm
+        self.flat = self.model.flatten_parameters(align=256 * self.world,
+                                                  allocator=fused_comm.alloc_params if fused_comm is not None else None)
         self.ref_flat: Optional[torch.Tensor] = None
         if init_reference_model:
             # the reference policy stays resident in HBM as a second flat buffer (no CPU swap)
@@ -104,7 +118,8 @@ class PolicyWorker:
         self.optimizer: Optional[ShardedAdamW] = None
         self.scheduler: Optional[LRSchedule] = None
         if init_optimizer:
-            self.flat.attach_grad_buffer(_precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32)
+            gdt = _precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32
+            self.flat.attach_grad_buffer(gdt, allocator=fused_comm.alloc_grads if (fused_comm is not None and gdt == torch.float32) else None)
             self.optimizer = build_optimizer(self.flat, cfg, group=dp_group, fused_comm=fused_comm)
             self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
         self.generation = None

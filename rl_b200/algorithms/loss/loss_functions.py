@@ -333,6 +333,7 @@ class PreferenceLossFn:
 
     loss_type = LossType.SEQUENCE_LEVEL
     input_type = LossInputType.LOGIT
+    requires_pairs = True  # rows 2i / 2i+1 belong together: micro-batches must not separate or reorder them
 
     @staticmethod
     def split(t: torch.Tensor):

@@ -309,7 +309,8 @@ class PolicyWorker:
             if not eval_mode:
                 self.optimizer.zero_grad()
             gb_loss = torch.zeros((), device=self.device)
-            for mb, _ in self._microbatches(gb, mbs, self._token_budget("train")):
+            budget = None if getattr(loss_fn, "requires_pairs", False) else self._token_budget("train")
+            for mb, _ in self._microbatches(gb, mbs, budget):
                 batch, S = self._pack(mb)
                 mb_dev = BatchedDataDict({k: (to_device(v, self.device) if isinstance(v, torch.Tensor) else v)
                                           for k, v in mb.items() if k != "input_ids"})

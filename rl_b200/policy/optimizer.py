@@ -6,7 +6,7 @@ master weights, and the two Adam moments. One optimizer step is
 
     reduce-scatter(grad) -> global grad-norm / clip scale -> AdamW on the shard -> all-gather(bf16 params)
 
-On NVLink-connected GPUs the three stages run as one fused peer-memory kernel (:mod:`rl_b200.parallel.fused_optim`);
+On NVLink-connected GPUs the three stages run as one fused peer-memory kernel (:mod:`rl_b200.parallel.symmetric`);
 the NCCL/gloo form below is its twin and the CPU path. The reference reaches the same end state with FSDP2
 reduce-scatter + ``torch.optim.AdamW`` on DTensor shards (nemo_rl/models/automodel/setup.py:481-493, :806-820) and
 ``clip_grad_by_total_norm_`` (nemo_rl/models/dtensor/parallelize.py:780-882).

@@ -1,0 +1,70 @@
+"""Environments: math verification, code execution, sliding puzzle, synthetic token rewards."""
+
+import torch
+
+from rl_b200.environments.code_environment import CodeEnvironment, CodeJaccardEnvironment, extract_code
+from rl_b200.environments.games.sliding_puzzle import SlidingPuzzleEnv, apply_move, make_initial_state, solved_grid
+from rl_b200.environments.math_environment import MathEnvironment, answers_match, extract_answer
+from rl_b200.environments.registry import create_env
+from rl_b200.environments.synthetic import HashParityEnv, TokenFractionEnv
+
+
+def _log(text):
+    return [{"role": "user", "content": "q", "token_ids": torch.tensor([1])}, {"role": "assistant", "content": text, "token_ids": torch.tensor([2, 7, 7, 3])}]
+
+
+def test_math_answers():
+    assert extract_answer(r"so the answer is \boxed{\frac{3}{4}}.") == r"\frac{3}{4}"
+    assert answers_match(r"\frac{3}{4}", "0.75") and answers_match("1,000", "1000") and answers_match("x = 5", "5")
+    assert answers_match(r"\boxed{2}".replace("\\boxed{", "").rstrip("}"), "2.0") and not answers_match("3", "4") and not answers_match(None, "4")
+    env = MathEnvironment({"num_workers": 2})
+    out = env.step([_log(r"thus \boxed{42}"), _log("I think 41")], [{"ground_truth": "42"}, {"ground_truth": "42"}])
+    assert out.rewards.tolist() == [1.0, 0.0] and out.terminateds.all() and out.answers[0] == "42"
+    env.shutdown()
+
+
+def test_code_env_executes_with_limits():
+    env = CodeEnvironment({"timeout_s": 3})
+    good = "```python\ndef add(a, b):\n    return a + b\n```"
+    bad = "```python\ndef add(a, b):\n    return a - b\n```"
+    loop = "```python\nwhile True:\n    pass\n```"
+    out = env.step([_log(good), _log(bad), _log(loop), _log("no code")],
+                   [{"tests": ["assert add(1, 2) == 3"]}, {"tests": ["assert add(1, 2) == 3"]}, {"tests": ["assert True"]}, {}])
+    assert out.rewards.tolist() == [1.0, 0.0, 0.0, 0.0]
+    assert extract_code(good).startswith("def add")
+    j = CodeJaccardEnvironment().step([_log(good)], [{"ground_truth": "def add(a, b):\n    return a + b"}])
+    assert j.rewards[0] > 0.9
+    env.shutdown()
+
+
+def test_sliding_puzzle_multi_turn():
+    st = {"grid": solved_grid(3), "moves": 0, "max_moves": 5, "size": 3}
+    apply_move(st["grid"], "left")  # blank moved left: solving move is "right"
+    env = SlidingPuzzleEnv()
+    out = env.step([_log("<action>up</action>")], [st])
+    assert not out.terminateds[0] and out.rewards[0] == 0 and out.metadata[0]["moves"] == 1
+    out2 = env.step([_log("<action>right</action> then <action>down</action>")], [st])
+    assert out2.rewards[0] == 0  # the last action wins, and "down" leaves the board
+    out3 = env.step([_log("<action>right</action>")], [st])
+    assert out3.rewards[0] == 1 and out3.terminateds[0]
+    s = make_initial_state(3, 8, 20, seed=1)
+    assert s["grid"] != solved_grid(3) and sorted(v for r in s["grid"] for v in r) == list(range(9))
+
+
+def test_synthetic_envs_and_registry():
+    out = TokenFractionEnv({"target_token_id": 7}).step([_log("")], [None])
+    assert out.rewards[0] == 0.5
+    h = HashParityEnv().step([_log(""), _log("")], [None, None])
+    assert h.rewards[0] == h.rewards[1] and 0 <= h.rewards[0] <= 1
+    assert isinstance(create_env("math", {}), MathEnvironment)
+
+
+def test_named_sharding_axes():
+    from rl_b200.distributed.named_sharding import NamedSharding
+
+    ns = NamedSharding.from_sizes(8, dp=2, pp=1, cp=1, tp=4)
+    assert ns.size == 8 and ns.get_axis_size("tp") == 4
+    assert ns.get_worker_coords(5) == {"dp": 1, "pp": 0, "cp": 0, "tp": 1}
+    assert ns.get_ranks(dp=1) == [4, 5, 6, 7] and ns.get_ranks(dp=0, tp=2) == 2
+    assert ns.axis_groups("tp") == [[0, 1, 2, 3], [4, 5, 6, 7]] and ns.axis_groups("dp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert ns.group_of(6, "dp") == [2, 6]

@@ -65,6 +65,6 @@ def test_named_sharding_axes():
     ns = NamedSharding.from_sizes(8, dp=2, pp=1, cp=1, tp=4)
     assert ns.size == 8 and ns.get_axis_size("tp") == 4
     assert ns.get_worker_coords(5) == {"dp": 1, "pp": 0, "cp": 0, "tp": 1}
-    assert ns.get_ranks(dp=1) == [4, 5, 6, 7] and ns.get_ranks(dp=0, tp=2) == 2
+    assert ns.get_ranks(dp=1) == [4, 5, 6, 7] and ns.get_ranks(dp=0, tp=2) == [2] and ns.get_ranks(dp=0, pp=0, cp=0, tp=2) == 2
     assert ns.axis_groups("tp") == [[0, 1, 2, 3], [4, 5, 6, 7]] and ns.axis_groups("dp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
     assert ns.group_of(6, "dp") == [2, 6]

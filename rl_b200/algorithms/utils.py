@@ -120,6 +120,10 @@ def set_seed(seed: int) -> None:
 
 def get_tokenizer(tokenizer_config: dict):
     """Loads a HF tokenizer by name; applies chat template overrides and makes sure a pad token exists."""
+    if str(tokenizer_config.get("name", "")).lower() in ("byte", "bytes"):
+        from rl_b200.data.tokenizers import ByteTokenizer
+
+        return ByteTokenizer(int(tokenizer_config.get("vocab_size", 512)))
     from transformers import AutoTokenizer
 
     tok = AutoTokenizer.from_pretrained(tokenizer_config["name"], trust_remote_code=True)

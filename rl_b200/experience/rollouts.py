@@ -84,6 +84,7 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
     truncated = torch.zeros(n, dtype=torch.bool)
     gen_tokens = torch.zeros(n, dtype=torch.long)
     turns = torch.zeros(n, dtype=torch.long)
+    answers: list[Any] = [None] * n
     stop_strings = batch.get("stop_strings")
     gen_metrics_acc: dict[str, float] = {"total_generated_tokens": 0}
     for turn in range(max_rollout_turns):
@@ -111,6 +112,8 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
         for j, i in enumerate(active):
             total_reward[i] += r[j]
             batch["extra_env_info"][i] = env_out.metadata[j]
+            if env_out.answers is not None:
+                answers[i] = env_out.answers[j]
             if stop_strings is not None:
                 stop_strings[i] = env_out.next_stop_strings[j]
             done = bool(env_out.terminateds[j])
@@ -126,6 +129,7 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
         active = still
     batch["total_reward"] = total_reward
     batch["truncated"] = truncated
+    batch["answers"] = answers
     batch["generation_lengths"] = gen_tokens
     if reward_components is not None:
         batch["reward_components"] = reward_components

@@ -1,0 +1,42 @@
+"""Shared bootstrap of the example entrypoints: ``--config`` + Hydra-style overrides -> resolved config, process group,
+tokenizer (nemo_rl's examples do the same with OmegaConf + ``init_ray``: examples/run_grpo.py:71-254)."""
+
+from __future__ import annotations
+
+import os
+import pprint
+from typing import Optional
+
+from rl_b200.distributed.launch import init_distributed
+from rl_b200.utils.config import load_config, parse_args_and_overrides
+
+
+def bootstrap(default_config: str, argv: Optional[list[str]] = None, backend: Optional[str] = None):
+    """Returns (cfg, rank, world, device, tokenizer)."""
+    path, overrides = parse_args_and_overrides(argv)
+    cfg = load_config(path or default_config, overrides)
+    for k, v in (cfg.get("env_vars") or {}).items():  # YAML env_vars override the shell (docs/design-docs/env-vars.md:5-31)
+        os.environ[str(k)] = str(v)
+    rank, world, device = init_distributed(backend or (cfg.get("cluster") or {}).get("backend"))
+    if rank == 0:
+        print(f"Loaded configuration from {path or default_config}")
+        pprint.pprint(cfg, width=140, compact=True)
+    from rl_b200.algorithms.utils import get_tokenizer
+
+    tcfg = (cfg.get("policy") or {}).get("tokenizer") or {"name": "byte"}
+    tokenizer = get_tokenizer(tcfg)
+    return cfg, rank, world, device, tokenizer
+
+
+def model_cfg_for_tokenizer(cfg: dict, tokenizer):
+    """When the config asks for a preset architecture with a byte tokenizer, shrink the vocabulary to the tokenizer's."""
+    from rl_b200.models.config import PRESETS, preset
+
+    pcfg = cfg["policy"]
+    name = pcfg.get("model_name")
+    if name in PRESETS:
+        over = dict(pcfg.get("hf_config_overrides") or {})
+        if getattr(tokenizer, "name_or_path", None) == "byte":
+            over.setdefault("vocab_size", len(tokenizer))
+        return preset(name, **over)
+    return None

@@ -156,7 +156,16 @@ def _find_innermost(s: str):
     return None
 
 
-def _resolve_str(s: str, root: Mapping, stack: tuple) -> Any:
+def _absolute_key(expr: str, here: tuple) -> str:
+    """``.key`` names a sibling of the value being resolved, ``..key`` a key of the parent container, and so on."""
+    if not expr.startswith("."):
+        return expr
+    up = len(expr) - len(expr.lstrip("."))
+    base = here[: len(here) - (up - 1)] if up - 1 <= len(here) else ()
+    return ".".join([*map(str, base), expr[up:]])
+
+
+def _resolve_str(s: str, root: Mapping, stack: tuple, here: tuple = ()) -> Any:
     while True:
         span = _find_innermost(s)
         if span is None:
@@ -170,21 +179,25 @@ def _resolve_str(s: str, root: Mapping, stack: tuple) -> Any:
             args = [yaml.safe_load(x) if x != "" else "" for x in _split_args(argstr)]
             val = RESOLVERS[name](*args)
         else:
+            expr = _absolute_key(expr, here)
             if expr in stack:
                 raise ConfigError(f"interpolation cycle through '{expr}'")
-            val = _resolve_node(_get_path(root, expr), root, stack + (expr,))
+            val = _resolve_node(_get_path(root, expr), root, stack + (expr,), tuple(expr.split(".")[:-1]))
         if a == 0 and b == len(s):
             return val
         s = s[:a] + str(val) + s[b:]
 
 
-def _resolve_node(node: Any, root: Mapping, stack: tuple = ()) -> Any:
+def _resolve_node(node: Any, root: Mapping, stack: tuple = (), here: tuple = ()) -> Any:
+    """``here`` is the path of the container that holds ``node`` (for relative ``${.key}`` interpolation)."""
     if isinstance(node, str) and "${" in node:
-        return _resolve_str(node, root, stack)
+        return _resolve_str(node, root, stack, here)
     if isinstance(node, dict):
-        return {k: _resolve_node(v, root, stack) for k, v in node.items()}
+        return {k: (_resolve_node(v, root, stack, here + (k,)) if isinstance(v, (dict, list)) else _resolve_node(v, root, stack, here))
+                for k, v in node.items()}
     if isinstance(node, list):
-        return [_resolve_node(v, root, stack) for v in node]
+        return [(_resolve_node(v, root, stack, here + (i,)) if isinstance(v, (dict, list)) else _resolve_node(v, root, stack, here))
+                for i, v in enumerate(node)]
     return node
 
 

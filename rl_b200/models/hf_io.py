@@ -20,49 +20,64 @@ from .config import ModelConfig
 from .transformer import CausalLM
 
 
-def hf_name_map(cfg: ModelConfig) -> list[tuple[str, str, Optional[tuple[int, int]], Optional[int]]]:
-    """Rows of (hf_name, local_name, row_range or None, expert index or None): the HF tensor is rows
-    ``row_range`` of the local tensor (of local expert ``e`` when the local tensor is expert-stacked)."""
-    rows = [("model.embed_tokens.weight", "embed_tokens", None, None), ("model.norm.weight", "norm", None, None)]
-    if cfg.value_head:
-        rows.append(("score.weight", "score", (0, 1), None))
-    elif not cfg.tie_word_embeddings:
-        rows.append(("lm_head.weight", "lm_head", None, None))
-    q, kv = cfg.q_size, cfg.kv_size
-    for i in range(cfg.num_hidden_layers):
-        hp, lp = f"model.layers.{i}", f"layers.{i}"
+def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offset: int = 0, num_local_layers: Optional[int] = None,
+                first_stage: bool = True, last_stage: bool = True):
+    """Rows of (hf_name, local_name, local_rows or None, expert index or None, hf_slice or None).
+
+    The HF tensor, restricted to ``hf_slice = (dim, start, length)`` when this rank holds a tensor-parallel shard of it,
+    is rows ``local_rows`` of the local parameter (of global expert ``e`` when the local parameter is expert-stacked).
+    Local layer ``j`` is HF layer ``layer_offset + j`` (pipeline stages own contiguous layer ranges)."""
+    n_layers = cfg.num_hidden_layers - layer_offset if num_local_layers is None else num_local_layers
+    tied = cfg.tie_word_embeddings and not cfg.value_head
+    rows = []
+    if first_stage or (last_stage and tied):
+        rows.append(("model.embed_tokens.weight", "embed_tokens", None, None, None))
+    if last_stage:
+        rows.append(("model.norm.weight", "norm", None, None, None))
+        if cfg.value_head:
+            rows.append(("score.weight", "score", (0, 1), None, None))
+        elif not tied:
+            vl = cfg.vocab_size // tp_size
+            rows.append(("lm_head.weight", "lm_head", None, None, (0, tp_rank * vl, vl) if tp_size > 1 else None))
+    q, kv = cfg.q_size // tp_size, cfg.kv_size // tp_size
+
+    def sl(dim, n):  # this rank's slice of a dimension of (global) length n * tp_size
+        return (dim, tp_rank * n, n) if tp_size > 1 else None
+
+    for j in range(n_layers):
+        hp, lp = f"model.layers.{layer_offset + j}", f"layers.{j}"
         rows += [
-            (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None),
-            (f"{hp}.post_attention_layernorm.weight", f"{lp}.post_attention_layernorm", None, None),
-            (f"{hp}.self_attn.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, q), None),
-            (f"{hp}.self_attn.k_proj.weight", f"{lp}.self_attn.qkv_proj", (q, q + kv), None),
-            (f"{hp}.self_attn.v_proj.weight", f"{lp}.self_attn.qkv_proj", (q + kv, q + 2 * kv), None),
-            (f"{hp}.self_attn.o_proj.weight", f"{lp}.self_attn.o_proj", None, None),
+            (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None, None),
+            (f"{hp}.post_attention_layernorm.weight", f"{lp}.post_attention_layernorm", None, None, None),
+            (f"{hp}.self_attn.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, q), None, sl(0, q)),
+            (f"{hp}.self_attn.k_proj.weight", f"{lp}.self_attn.qkv_proj", (q, q + kv), None, sl(0, kv)),
+            (f"{hp}.self_attn.v_proj.weight", f"{lp}.self_attn.qkv_proj", (q + kv, q + 2 * kv), None, sl(0, kv)),
+            (f"{hp}.self_attn.o_proj.weight", f"{lp}.self_attn.o_proj", None, None, sl(1, q)),
         ]
         if cfg.attention_bias:
             rows += [
-                (f"{hp}.self_attn.q_proj.bias", f"{lp}.self_attn.qkv_bias", (0, q), None),
-                (f"{hp}.self_attn.k_proj.bias", f"{lp}.self_attn.qkv_bias", (q, q + kv), None),
-                (f"{hp}.self_attn.v_proj.bias", f"{lp}.self_attn.qkv_bias", (q + kv, q + 2 * kv), None),
+                (f"{hp}.self_attn.q_proj.bias", f"{lp}.self_attn.qkv_bias", (0, q), None, sl(0, q)),
+                (f"{hp}.self_attn.k_proj.bias", f"{lp}.self_attn.qkv_bias", (q, q + kv), None, sl(0, kv)),
+                (f"{hp}.self_attn.v_proj.bias", f"{lp}.self_attn.qkv_bias", (q + kv, q + 2 * kv), None, sl(0, kv)),
             ]
         if cfg.qk_norm:
-            rows += [(f"{hp}.self_attn.q_norm.weight", f"{lp}.self_attn.q_norm", None, None),
-                     (f"{hp}.self_attn.k_norm.weight", f"{lp}.self_attn.k_norm", None, None)]
+            rows += [(f"{hp}.self_attn.q_norm.weight", f"{lp}.self_attn.q_norm", None, None, None),
+                     (f"{hp}.self_attn.k_norm.weight", f"{lp}.self_attn.k_norm", None, None, None)]
         if cfg.is_moe:
             f = cfg.moe_intermediate_size
-            rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None))
+            rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None, None))
             for e in range(cfg.num_experts):
                 rows += [
-                    (f"{hp}.mlp.experts.{e}.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), e),
-                    (f"{hp}.mlp.experts.{e}.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), e),
-                    (f"{hp}.mlp.experts.{e}.down_proj.weight", f"{lp}.mlp.down_proj", None, e),
+                    (f"{hp}.mlp.experts.{e}.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), e, None),
+                    (f"{hp}.mlp.experts.{e}.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), e, None),
+                    (f"{hp}.mlp.experts.{e}.down_proj.weight", f"{lp}.mlp.down_proj", None, e, None),
                 ]
         else:
-            f = cfg.intermediate_size
+            f = cfg.intermediate_size // tp_size
             rows += [
-                (f"{hp}.mlp.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), None),
-                (f"{hp}.mlp.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), None),
-                (f"{hp}.mlp.down_proj.weight", f"{lp}.mlp.down_proj", None, None),
+                (f"{hp}.mlp.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), None, sl(0, f)),
+                (f"{hp}.mlp.up_proj.weight", f"{lp}.mlp.gate_up_proj", (f, 2 * f), None, sl(0, f)),
+                (f"{hp}.mlp.down_proj.weight", f"{lp}.mlp.down_proj", None, None, sl(1, f)),
             ]
     return rows
 
@@ -71,30 +86,52 @@ def _local(model: CausalLM) -> dict[str, torch.Tensor]:
     return dict(model.named_parameters())
 
 
-def iter_hf_tensors(model: CausalLM, ep_rank: int = 0, ep_size: int = 1) -> Iterator[tuple[str, torch.Tensor]]:
-    """Yields (hf_name, tensor view) for every logical HF tensor held by this model instance."""
+def _model_map(model: CausalLM):
+    return hf_name_map(model.cfg, model.tp.rank, model.tp.world, model.layer_offset, len(model.layers), model.first_stage, model.last_stage)
+
+
+def iter_hf_shards(model: CausalLM) -> Iterator[tuple[str, torch.Tensor, Optional[tuple[int, int, int]]]]:
+    """Yields (hf_name, local tensor view, hf_slice) for every logical HF tensor (or shard of one) this rank holds."""
     cfg = model.cfg
     params = _local(model)
+    ep_rank, ep_size = (model.ep.rank, model.ep.world) if model.ep is not None else (0, 1)
     per = cfg.num_experts // ep_size if cfg.is_moe else 0
-    for hf, loc, rows, e in hf_name_map(cfg):
+    for hf, loc, rows, e, hs in _model_map(model):
         p = params[loc]
         if e is not None:
             if not (ep_rank * per <= e < (ep_rank + 1) * per):
                 continue
             p = p[e - ep_rank * per]
-        yield hf, (p if rows is None else p[rows[0] : rows[1]])
+        yield hf, (p if rows is None else p[rows[0] : rows[1]]), hs
+
+
+def iter_hf_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
+    """Yields (hf_name, FULL tensor). Without model parallelism these are views of the parameters; with tensor
+    parallelism every shard is all-gathered over the tp group (collective: all tp ranks must iterate together)."""
+    from rl_b200.parallel.tensor import all_gather_rows
+
+    tp = model.tp
+    for hf, t, hs in iter_hf_shards(model):
+        if hs is None or tp.world == 1:
+            yield hf, t
+        elif hs[0] == 0:
+            yield hf, all_gather_rows(t.detach(), tp.group, tp.world)
+        else:
+            yield hf, all_gather_rows(t.detach().t().contiguous(), tp.group, tp.world).t().contiguous()
 
 
 @torch.no_grad()
-def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]], strict: bool = True,
-                    ep_rank: int = 0, ep_size: int = 1) -> list[str]:
-    """Copies HF-named tensors (as returned by ``get(name)``) into the fused parameters. Returns missing names."""
+def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]], strict: bool = True) -> list[str]:
+    """Copies HF-named tensors (as returned by ``get(name)``) into the fused (and possibly sharded) parameters.
+    Returns missing names."""
     missing = []
-    for hf, dst in iter_hf_tensors(model, ep_rank, ep_size):
+    for hf, dst, hs in iter_hf_shards(model):
         src = get(hf)
         if src is None:
             missing.append(hf)
             continue
+        if hs is not None:
+            src = src.narrow(hs[0], hs[1], hs[2])
         if tuple(src.shape) != tuple(dst.shape):
             raise ValueError(f"{hf}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
         dst.copy_(src.to(dst.dtype))
@@ -111,7 +148,7 @@ def save_pretrained(model: CausalLM, path: str, max_shard_bytes: int = 5 * 1024*
     model.cfg.save_pretrained(path)
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
-    for name, t in iter_hf_tensors(model):
+    for name, t in iter_hf_tensors(model):  # collective over the tp group when the model is tensor parallel
         t = t.detach().to("cpu", dtype or t.dtype).contiguous()
         nbytes = t.numel() * t.element_size()
         if size + nbytes > max_shard_bytes and shards[-1]:
@@ -163,11 +200,11 @@ class _SafetensorsDir:
         return h.get_tensor(name)
 
 
-def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None, strict: bool = True,
-                    **cfg_overrides) -> CausalLM:
-    """Builds a model from an HF checkpoint directory."""
+def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None, strict: bool = True, tp=None, ep=None,
+                    pp_rank: int = 0, pp_size: int = 1, **cfg_overrides) -> CausalLM:
+    """Builds a model (or this rank's tensor / expert / pipeline shard of it) from an HF checkpoint directory."""
     cfg = ModelConfig.from_pretrained(path, **cfg_overrides)
-    model = CausalLM(cfg, dtype=dtype, device=device, init=False)
+    model = CausalLM(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size)
     reader = _SafetensorsDir(path)
     get = reader.get
     if cfg.tie_word_embeddings or cfg.value_head:

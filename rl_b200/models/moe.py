@@ -19,9 +19,13 @@ from .config import ModelConfig
 
 
 class MoEMLP(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, ep_rank: int = 0, ep_size: int = 1):
+    def __init__(self, cfg: ModelConfig, dtype, device, ep=None):
         super().__init__()
+        from rl_b200.parallel.expert import EP
+
         self.cfg = cfg
+        self.ep = ep or EP()
+        ep_rank, ep_size = self.ep.rank, self.ep.world
         d, f, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
         assert E % ep_size == 0
         self.ep_rank, self.ep_size = ep_rank, ep_size
@@ -29,7 +33,6 @@ class MoEMLP(nn.Module):
         self.router = nn.Parameter(torch.empty(E, d, dtype=dtype, device=device))
         self.gate_up_proj = nn.Parameter(torch.empty(self.local_experts, 2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(self.local_experts, d, f, dtype=dtype, device=device))
-        self.ep_group = None
         self.last_routing: Optional[torch.Tensor] = None  # top-k expert ids of the last forward (router replay / traces)
         self.forced_routing: Optional[torch.Tensor] = None  # when set, replaces the router's choice (router replay)
 
@@ -74,7 +77,7 @@ class MoEMLP(nn.Module):
         if self.ep_size > 1:
             from rl_b200.parallel.expert import all_to_all_tokens
 
-            ys = all_to_all_tokens(xs, counts, self.ep_group, self.ep_size, self.local_experts, self._experts)
+            ys = all_to_all_tokens(xs, counts, self.ep, self.local_experts, self._experts)
         else:
             ys = self._experts(xs, counts.tolist())
         wy = ys * w.reshape(-1)[order].unsqueeze(-1).to(ys.dtype)

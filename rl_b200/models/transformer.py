@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.utils.checkpoint as ckpt
 
 from rl_b200.ops import functional as F
+from rl_b200.parallel.tensor import TP, column_linear, gather_rows, row_linear, scatter_rows
 
 from .config import ModelConfig, rope_inv_freq
 
@@ -97,13 +98,22 @@ class FlatParams:
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    """Fused-QKV attention. With tensor parallelism this rank holds ``Hq/tp`` query and ``Hkv/tp`` key/value heads:
+    ``qkv_proj`` is column-parallel (rows = local q, k, v heads), ``o_proj`` row-parallel."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None):
         super().__init__()
         self.cfg = cfg
+        self.tp = tp or TP()
+        w = self.tp.world
+        assert cfg.num_attention_heads % w == 0 and cfg.num_key_value_heads % w == 0, "heads must divide by the tensor-parallel size"
+        self.hq, self.hkv = cfg.num_attention_heads // w, cfg.num_key_value_heads // w
+        self.q_local, self.kv_local = self.hq * cfg.head_dim, self.hkv * cfg.head_dim
         d = cfg.hidden_size
-        self.qkv_proj = nn.Parameter(torch.empty(cfg.qkv_size, d, dtype=dtype, device=device))
-        self.qkv_bias = nn.Parameter(torch.zeros(cfg.qkv_size, dtype=dtype, device=device)) if cfg.attention_bias else None
-        self.o_proj = nn.Parameter(torch.empty(d, cfg.q_size, dtype=dtype, device=device))
+        qkv = self.q_local + 2 * self.kv_local
+        self.qkv_proj = nn.Parameter(torch.empty(qkv, d, dtype=dtype, device=device))
+        self.qkv_bias = nn.Parameter(torch.zeros(qkv, dtype=dtype, device=device)) if cfg.attention_bias else None
+        self.o_proj = nn.Parameter(torch.empty(d, self.q_local, dtype=dtype, device=device))
         if cfg.qk_norm:
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
@@ -111,44 +121,49 @@ class Attention(nn.Module):
     def project_qkv(self, x, positions, inv_freq):
         """x [T, d] -> fused [T, (Hq+2Hkv)*D] with q/k normalised (Qwen3) and rotated."""
         c = self.cfg
-        qkv = F.linear(x, self.qkv_proj, self.qkv_bias)
+        qkv = column_linear(x, self.qkv_proj, self.qkv_bias, self.tp)
         if c.qk_norm:
-            qkv = F.head_rmsnorm(qkv, self.q_norm, 0, c.num_attention_heads, c.head_dim, c.rms_norm_eps)
-            qkv = F.head_rmsnorm(qkv, self.k_norm, c.q_size, c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
-        return F.rope(qkv, positions, inv_freq, c.num_attention_heads + c.num_key_value_heads, c.head_dim)
+            qkv = F.head_rmsnorm(qkv, self.q_norm, 0, self.hq, c.head_dim, c.rms_norm_eps)
+            qkv = F.head_rmsnorm(qkv, self.k_norm, self.q_local, self.hkv, c.head_dim, c.rms_norm_eps)
+        return F.rope(qkv, positions, inv_freq, self.hq + self.hkv, c.head_dim)
 
     def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen):
         c = self.cfg
         qkv = self.project_qkv(x, positions, inv_freq)
-        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
-        return F.linear(a, self.o_proj, None, residual)
+        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim)
+        return row_linear(a, self.o_proj, residual, self.tp)
 
 
 class DenseMLP(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    """SwiGLU MLP; ``gate_up_proj`` rows are [local gate | local up] (column-parallel), ``down_proj`` row-parallel."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None):
         super().__init__()
-        d, f = cfg.hidden_size, cfg.intermediate_size
+        self.tp = tp or TP()
+        assert cfg.intermediate_size % self.tp.world == 0
+        d, f = cfg.hidden_size, cfg.intermediate_size // self.tp.world
         self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
 
     def forward(self, x, residual):
-        return F.linear(F.swiglu(F.linear(x, self.gate_up_proj)), self.down_proj, None, residual)
+        return row_linear(F.swiglu(column_linear(x, self.gate_up_proj, None, self.tp)), self.down_proj, residual, self.tp)
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None):
         super().__init__()
         self.cfg = cfg
         d = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device)
+        self.self_attn = Attention(cfg, dtype, device, tp)
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if cfg.is_moe:
             from .moe import MoEMLP
 
-            self.mlp = MoEMLP(cfg, dtype, device)
+            assert tp is None or tp.world == 1, "MoE layers shard experts (ep), not tensors"
+            self.mlp = MoEMLP(cfg, dtype, device, ep=ep)
         else:
-            self.mlp = DenseMLP(cfg, dtype, device)
+            self.mlp = DenseMLP(cfg, dtype, device, tp)
 
     def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
         eps = self.cfg.rms_norm_eps
@@ -191,25 +206,48 @@ class PackedBatch:
 
 
 class CausalLM(nn.Module):
-    """Packed-sequence causal language model with HF-compatible weights (see :mod:`rl_b200.models.hf_io`)."""
+    """Packed-sequence causal language model with HF-compatible weights (see :mod:`rl_b200.models.hf_io`).
+
+    Model parallelism: ``tp`` shards attention heads, MLP columns and the output vocabulary over a tensor-parallel group
+    (activations between blocks are sequence parallel when ``tp.sequence_parallel``); ``ep`` shards MoE experts;
+    ``pp_rank`` / ``pp_size`` keep a contiguous slice of the layers on this rank (embedding on the first stage, final
+    norm and output head on the last)."""
 
     def __init__(self, cfg: ModelConfig, dtype: Optional[torch.dtype] = None, device="cpu", init: bool = True,
-                 seed: int = 0, activation_checkpointing: bool = False):
+                 seed: int = 0, activation_checkpointing: bool = False, tp: Optional[TP] = None, ep=None,
+                 pp_rank: int = 0, pp_size: int = 1):
         super().__init__()
         self.cfg = cfg
         dtype = dtype or _dtype_of(cfg.torch_dtype)
         self.dtype = dtype
+        self.tp = tp or TP()
+        self.ep = ep
+        self.pp_rank, self.pp_size = pp_rank, pp_size
+        L = cfg.num_hidden_layers
+        per = -(-L // pp_size)
+        self.layer_offset = pp_rank * per
+        n_local = max(0, min(L, (pp_rank + 1) * per) - self.layer_offset)
+        self.first_stage, self.last_stage = pp_rank == 0, pp_rank == pp_size - 1
         d = cfg.hidden_size
-        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
-        self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        if cfg.value_head:
-            self.score = nn.Parameter(torch.empty(8, d, dtype=dtype, device=device))  # row 0 is the head; 8 rows keep TMA alignment
-            self.lm_head = None
-        elif cfg.tie_word_embeddings:
-            self.lm_head = None
+        tpw = self.tp.world
+        assert cfg.vocab_size % tpw == 0, "vocabulary must divide by the tensor-parallel size"
+        self.vocab_local = cfg.vocab_size // tpw
+        self.vocab_start = self.tp.rank * self.vocab_local
+        tied = cfg.tie_word_embeddings and not cfg.value_head
+        if self.first_stage or (self.last_stage and tied):
+            self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
         else:
-            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
+            self.embed_tokens = None
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep) for _ in range(n_local)])
+        self.lm_head = None
+        if self.last_stage:
+            self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+            if cfg.value_head:
+                self.score = nn.Parameter(torch.empty(8, d, dtype=dtype, device=device))  # row 0 is the head; 8 rows keep TMA alignment
+            elif not tied:
+                self.lm_head = nn.Parameter(torch.empty(self.vocab_local, d, dtype=dtype, device=device))
+        else:
+            self.norm = None
         self.register_buffer("inv_freq", rope_inv_freq(cfg, device), persistent=False)
         self.activation_checkpointing = activation_checkpointing
         if init:
@@ -217,10 +255,20 @@ class CausalLM(nn.Module):
         self.flat: Optional[FlatParams] = None
 
     # ------------------------------------------------------------------ parameters
+    _TP_SHARDED = ("qkv_proj", "qkv_bias", "o_proj", "gate_up_proj", "down_proj", "lm_head")
+
+    def is_tp_sharded(self, name: str) -> bool:
+        """Whether parameter ``name`` holds a tensor-parallel shard (False: replicated over the tp group)."""
+        if self.tp.world == 1:
+            return False
+        leaf = name.rsplit(".", 1)[-1]
+        return leaf in self._TP_SHARDED and ".mlp.router" not in name and not (self.cfg.is_moe and ".mlp." in name)
+
     @torch.no_grad()
     def reset_parameters(self, seed: int = 0, std: float = 0.02) -> None:
         """Normal(0, 0.02) weights (HF's default initializer range), ones for norms, zeros for biases.
-        Generated on the parameter's device with a seeded generator so every rank builds identical weights."""
+        Generated on the parameter's device with a seeded generator: replicated parameters are identical on every rank,
+        tensor-parallel shards differ per tp rank."""
         for i, (name, p) in enumerate(self.named_parameters()):
             if name.endswith("norm") or name.endswith("layernorm"):
                 p.fill_(1.0)
@@ -228,7 +276,7 @@ class CausalLM(nn.Module):
                 p.zero_()
             else:
                 g = torch.Generator(device=p.device)
-                g.manual_seed(seed * 1000003 + i)
+                g.manual_seed(seed * 1000003 + i + 7919 * self.layer_offset + (104729 * self.tp.rank if self.is_tp_sharded(name) else 0))
                 # normal_ in fp32 chunks keeps the memory bounded for 1 GB embedding tables
                 flat = p.view(-1)
                 step = 1 << 26
@@ -242,49 +290,82 @@ class CausalLM(nn.Module):
 
     @property
     def output_weight(self) -> torch.Tensor:
-        return self.embed_tokens if self.lm_head is None else self.lm_head
+        """This rank's rows of the output projection ([V/tp, d])."""
+        if self.lm_head is not None:
+            return self.lm_head
+        if self.tp.world == 1:
+            return self.embed_tokens
+        return self.embed_tokens[self.vocab_start : self.vocab_start + self.vocab_local]
 
     # ------------------------------------------------------------------ forward
-    def hidden_states(self, batch: PackedBatch) -> torch.Tensor:
+    def embed(self, batch: PackedBatch) -> torch.Tensor:
         h = F.embedding(batch.input_ids, self.embed_tokens)
+        return scatter_rows(h, self.tp) if self.tp.sequence_parallel else h
+
+    def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         inv_freq = self.inv_freq
         for layer in self.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = ckpt.checkpoint(layer, h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen, use_reentrant=False)
             else:
                 h = layer(h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen)
-        return F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+        return h
 
-    def logits(self, batch: PackedBatch) -> torch.Tensor:
+    def hidden_states(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Output of this stage: the normed final hidden states on the last stage, else the residual stream handed to
+        the next stage. Rows are this rank's sequence-parallel shard when ``tp.sequence_parallel``."""
+        h = self.embed(batch) if self.first_stage else h_in
+        h = self.run_layers(h, batch)
+        return F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.last_stage else h
+
+    def logits(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """[T, V] logits in fp32 (small models, tests and the distillation / top-k paths)."""
-        return F.linear(self.hidden_states(batch), self.output_weight).float()
+        h = self.hidden_states(batch, h_in)
+        if self.tp.world == 1:
+            return F.linear(h, self.output_weight).float()
+        from rl_b200.parallel.tensor import gather_cols
 
-    def next_token_logprobs(self, batch: PackedBatch, temperature: float = 1.0, want_entropy: bool = False):
-        """Log-probability of each token given its prefix: out[t] = log p(ids[t] | ids[<t]) for t > 0 within a sequence,
-        0 at sequence starts. Returns ([T] fp32, entropy [T] or None). Uses the fused projection + log-softmax."""
-        h = self.hidden_states(batch)
-        T = h.shape[0]
+        return gather_cols(column_linear(h, self.output_weight, None, self.tp), self.tp).float()
+
+    def logprobs_from_hidden(self, h: torch.Tensor, batch: PackedBatch, temperature: float = 1.0, want_entropy: bool = False):
+        """``h``: normed final hidden states (this rank's rows). out[t] = log p(ids[t] | ids[<t]), 0 at sequence starts."""
         ids = batch.input_ids.long()
+        T = ids.shape[0]
         starts = batch.cu_seqlens[:-1].long()
         is_start = torch.zeros(T, dtype=torch.bool, device=h.device)
         is_start[starts[starts < T]] = True
-        # hidden state t-1 predicts token t: rows [0, T-1) against targets ids[1:]
-        logp_n, ent_n = F.lm_head_logprobs(h[:-1], self.output_weight, ids[1:], temperature, want_entropy)
-        logp = torch.zeros(T, dtype=torch.float32, device=h.device)
+        # hidden state t predicts token t+1: every row is scored against the next token, then shifted by one
+        targets = torch.roll(ids, -1)
+        if self.tp.world == 1:
+            lp_rows, ent_rows = F.lm_head_logprobs(h, self.output_weight, targets, temperature, want_entropy)
+        else:
+            from rl_b200.parallel.vocab import vocab_parallel_logprobs
+
+            lp_rows, ent_rows = vocab_parallel_logprobs(h, self.output_weight, targets, self.tp, self.vocab_start, temperature, want_entropy)
         valid = ~is_start[1:]
-        logp[1:] = torch.where(valid, logp_n, torch.zeros_like(logp_n))
+        logp = torch.zeros(T, dtype=torch.float32, device=h.device)
+        logp[1:] = torch.where(valid, lp_rows[:-1], torch.zeros_like(lp_rows[:-1]))
         ent = None
         if want_entropy:
             ent = torch.zeros(T, dtype=torch.float32, device=h.device)
-            ent[1:] = torch.where(valid, ent_n, torch.zeros_like(ent_n))
+            ent[1:] = torch.where(valid, ent_rows[:-1], torch.zeros_like(ent_rows[:-1]))
         return logp, ent
 
-    def values(self, batch: PackedBatch) -> torch.Tensor:
+    def next_token_logprobs(self, batch: PackedBatch, temperature: float = 1.0, want_entropy: bool = False,
+                            h_in: Optional[torch.Tensor] = None):
+        """Log-probability of each token given its prefix ([T] fp32, entropy [T] or None), through the fused projection +
+        log-softmax (vocabulary-parallel under tensor parallelism)."""
+        return self.logprobs_from_hidden(self.hidden_states(batch, h_in), batch, temperature, want_entropy)
+
+    def values(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Scalar head output per token [T] (critic / reward model)."""
-        h = self.hidden_states(batch)
-        return F.linear(h, self.score).float()[:, 0]
+        h = self.hidden_states(batch, h_in)
+        v = F.linear(h, self.score).float()[:, 0]
+        return gather_rows(v, self.tp) if self.tp.sequence_parallel else v
 
 
 def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
-                activation_checkpointing: bool = False, init: bool = True) -> CausalLM:
-    return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing)
+                activation_checkpointing: bool = False, init: bool = True, tp: Optional[TP] = None, ep=None,
+                pp_rank: int = 0, pp_size: int = 1) -> CausalLM:
+    return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
+                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size)

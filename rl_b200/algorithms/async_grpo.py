@@ -16,7 +16,7 @@ from typing import Callable, Optional
 import torch
 
 from rl_b200.algorithms.advantage_estimator import create_advantage_estimator
-from rl_b200.algorithms.grpo import (_aggregate_train_metrics, _all_reduce_scalars, _world, build_train_data, refit_policy_generation,
+from rl_b200.algorithms.grpo import (_aggregate_train_metrics, _all_reduce_scalars, _is_main, _world, build_train_data, refit_policy_generation,
                                      save_checkpoint)
 from rl_b200.algorithms.utils import calculate_baseline_and_std_per_prompt
 from rl_b200.data.llm_message_utils import batched_message_log_to_flat_message
@@ -143,7 +143,7 @@ def async_grpo_train(policy, generation, dataloader, tokenizer, loss_fn, task_to
         if logger is not None:
             logger.log_metrics(metrics, total_steps, prefix="train")
             logger.log_metrics(timing, total_steps, prefix="timing/train")
-        if rank == 0:
+        if _is_main():
             print(f"[async_grpo] step {total_steps}: loss={metrics['loss']:.5f} reward={metrics['reward']:.4f} age={item['age']} "
                   f"buffer={len(buffer)}", flush=True)
         last = {"train": metrics, "timing": timing}

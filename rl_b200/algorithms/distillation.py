@@ -11,7 +11,7 @@ from typing import Callable, Optional
 
 import torch
 
-from rl_b200.algorithms.grpo import (_aggregate_train_metrics, _all_reduce_scalars, _ShardedPromptLoader, _world, build_train_data,
+from rl_b200.algorithms.grpo import (_aggregate_train_metrics, _all_reduce_scalars, _ShardedPromptLoader, _is_main, _world, build_train_data,
                                      refit_policy_generation, save_checkpoint)
 from rl_b200.algorithms.loss.loss_functions import DistillationLossFn
 from rl_b200.algorithms.utils import set_seed
@@ -28,12 +28,15 @@ def setup(cfg: dict, tokenizer, dataset, val_dataset, task_to_env, student_cfg=N
     from rl_b200.data.collate import rl_collate_fn
     from rl_b200.policy.worker import PolicyWorker
 
+    from rl_b200.policy.worker import ensure_parallel
+
+    ensure_parallel(cfg["policy"])
     rank, world = _world()
     d = dict(DISTILLATION_DEFAULTS)
     d.update(cfg.get("distillation") or {})
     cfg["distillation"] = d
     set_seed(d["seed"] + rank)
-    logger = Logger(cfg.get("logger"), is_main=rank == 0)
+    logger = Logger(cfg.get("logger"), is_main=_is_main())
     checkpointer = CheckpointManager(cfg.get("checkpointing"))
     save_state = {"current_step": 0, "total_steps": 0, "current_epoch": 0}
     loader = _ShardedPromptLoader(dataset, d["num_prompts_per_step"], rl_collate_fn, bool((cfg.get("data") or {}).get("shuffle", True)),
@@ -89,7 +92,7 @@ def distillation_train(student, teacher, generation, loader, tokenizer, loss_fn,
             if logger is not None:
                 logger.log_metrics(metrics, total_steps, prefix="train")
                 logger.log_metrics(timing, total_steps, prefix="timing/train")
-            if rank == 0:
+            if _is_main():
                 print(f"[distillation] step {total_steps}: loss={metrics['loss']:.5f} step_time={timing.get('total_step_time', 0):.2f}s", flush=True)
             last = {"train": metrics, "timing": timing}
             if step_callback is not None:

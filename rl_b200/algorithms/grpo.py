@@ -67,19 +67,42 @@ GRPO_DEFAULTS = dict(
 
 
 def _world():
+    """(data-parallel rank, data-parallel size): the coordinates that shard data. Ranks of one model-parallel group
+    (tensor / pipeline / context) share a data-parallel rank and therefore see the same samples."""
+    from rl_b200.parallel.state import get_state
+
+    st = get_state()
+    if st.world > 1:
+        return st.dp_rank, st.dp
     if dist.is_available() and dist.is_initialized():
         return dist.get_rank(), dist.get_world_size()
     return 0, 1
 
 
+def _dp_group():
+    from rl_b200.parallel.state import get_state
+
+    st = get_state()
+    if st.world > 1 and st.tp * st.pp * st.cp > 1:
+        return st.dp_group if st.dp > 1 else "self"
+    return None
+
+
+def _is_main() -> bool:
+    return not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0
+
+
 def _all_reduce_scalars(values: dict[str, float], op: str = "sum") -> dict[str, float]:
+    """Combines per-rank scalars over the data-parallel ranks."""
     rank, world = _world()
-    if world == 1:
+    group = _dp_group()
+    if world == 1 or group == "self":
         return dict(values)
     keys = sorted(values)
-    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
-    t = torch.tensor([float(values[k]) for k in keys], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op={"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op])
+    t = torch.tensor([float(values[k]) for k in keys], dtype=torch.float64)
+    if torch.cuda.is_available() and dist.get_backend() == "nccl":
+        t = t.cuda()
+    dist.all_reduce(t, op={"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op], group=group)
     return {k: float(v) for k, v in zip(keys, t.tolist())}
 
 
@@ -135,14 +158,17 @@ def setup(master_config: dict, tokenizer, dataset, val_dataset, task_to_env: dic
     from rl_b200.data.collate import rl_collate_fn
     from rl_b200.policy.worker import PolicyWorker
 
+    from rl_b200.policy.worker import ensure_parallel
+
+    ensure_parallel(master_config["policy"])
     rank, world = _world()
     cfg = master_config
     g = dict(GRPO_DEFAULTS)
     g.update(cfg.get("grpo") or {})
     cfg["grpo"] = g
     set_seed(g["seed"] + rank)
-    logger = Logger(cfg.get("logger"), is_main=rank == 0)
-    if rank == 0:
+    logger = Logger(cfg.get("logger"), is_main=_is_main())
+    if _is_main():
         logger.log_hyperparams(cfg)
     checkpointer = CheckpointManager(cfg.get("checkpointing"))
     save_state = default_save_state()
@@ -438,7 +464,7 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                 logger.log_metrics(metrics, total_steps, prefix="train")
                 logger.log_metrics(timing, total_steps, prefix="timing/train")
                 logger.log_metrics(perf, total_steps, prefix="performance")
-            if rank == 0:
+            if _is_main():
                 print(f"[grpo] step {total_steps}: loss={metrics['loss']:.5f} reward={metrics['reward']:.4f} "
                       f"mult_prob_err={metrics.get('token_mult_prob_error', float('nan')):.4f} "
                       f"step_time={timing.get('total_step_time', 0):.2f}s gen={timing.get('generation', 0):.2f}s "
@@ -466,9 +492,9 @@ def save_checkpoint(policy, dataloader, checkpointer: CheckpointManager, save_st
     if val_metrics:
         info["val"] = val_metrics
     tmp = None
-    if rank == 0:
+    if _is_main():
         tmp = str(checkpointer.init_tmp_checkpoint(step, info, cfg))
-    if world > 1:
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         box = [tmp]
         dist.broadcast_object_list(box, src=0)
         tmp = box[0]
@@ -477,8 +503,8 @@ def save_checkpoint(policy, dataloader, checkpointer: CheckpointManager, save_st
         os.path.join(tmp, "policy", "optimizer") if ck.get("save_optimizer", True) else None,
         os.path.join(tmp, "policy", "tokenizer"),
         model_save_format=ck.get("model_save_format", "safetensors"))
-    if rank == 0:
+    if _is_main():
         torch.save(dataloader.state_dict(), os.path.join(tmp, "train_dataloader.pt"))
         checkpointer.finalize_checkpoint(tmp)
-    if world > 1:
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.barrier()

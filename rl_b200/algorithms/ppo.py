@@ -12,7 +12,7 @@ from typing import Callable, Optional
 import torch
 
 from rl_b200.algorithms.advantage_estimator import GAEAdvantageEstimator
-from rl_b200.algorithms.grpo import (GRPO_DEFAULTS, _aggregate_train_metrics, _all_reduce_scalars, _ShardedPromptLoader, _world,
+from rl_b200.algorithms.grpo import (GRPO_DEFAULTS, _aggregate_train_metrics, _all_reduce_scalars, _is_main, _ShardedPromptLoader, _world,
                                      build_train_data, refit_policy_generation, save_checkpoint)
 from rl_b200.algorithms.loss.loss_functions import ClippedPGLossFn, MseValueLossFn
 from rl_b200.algorithms.reward_functions import apply_reward_shaping, scale_rewards
@@ -38,12 +38,15 @@ def setup(cfg: dict, tokenizer, dataset, val_dataset, task_to_env, model_cfg=Non
     from rl_b200.data.collate import rl_collate_fn
     from rl_b200.policy.worker import PolicyWorker
 
+    from rl_b200.policy.worker import ensure_parallel
+
+    ensure_parallel(cfg["policy"])
     rank, world = _world()
     p = dict(PPO_DEFAULTS)
     p.update(cfg.get("ppo") or {})
     cfg["ppo"] = p
     set_seed(p["seed"] + rank)
-    logger = Logger(cfg.get("logger"), is_main=rank == 0)
+    logger = Logger(cfg.get("logger"), is_main=_is_main())
     checkpointer = CheckpointManager(cfg.get("checkpointing"))
     save_state = {"current_step": 0, "total_steps": 0, "current_epoch": 0, "consumed_samples": 0, "total_valid_tokens": 0, "val_reward": -1e9}
     loader = _ShardedPromptLoader(dataset, p["num_prompts_per_step"], rl_collate_fn, bool((cfg.get("data") or {}).get("shuffle", True)),
@@ -130,7 +133,7 @@ def ppo_train(policy, value, generation, loader, tokenizer, policy_loss, value_l
                 logger.log_metrics(metrics, total_steps, prefix="train")
                 logger.log_metrics(timing, total_steps, prefix="timing/train")
                 logger.log_metrics(perf, total_steps, prefix="performance")
-            if rank == 0:
+            if _is_main():
                 print(f"[ppo] step {total_steps}: reward={metrics['reward']:.4f} policy_loss={metrics.get('loss', float('nan')):.5f} "
                       f"value_loss={metrics.get('value_loss', float('nan')):.5f} step_time={timing.get('total_step_time', 0):.2f}s", flush=True)
             last = {"train": metrics, "timing": timing, "performance": perf}

@@ -14,7 +14,7 @@ from typing import Callable, Optional
 import torch
 import torch.distributed as dist
 
-from rl_b200.algorithms.grpo import _ShardedPromptLoader, _aggregate_train_metrics, _all_reduce_scalars, _world, save_checkpoint
+from rl_b200.algorithms.grpo import _ShardedPromptLoader, _aggregate_train_metrics, _all_reduce_scalars, _is_main, _world, save_checkpoint
 from rl_b200.algorithms.loss.loss_functions import DPOLossFn, NLLLossFn, PreferenceLossFn
 from rl_b200.algorithms.utils import set_seed
 from rl_b200.distributed.batched_data_dict import BatchedDataDict
@@ -33,12 +33,15 @@ def _setup_common(cfg: dict, key: str, defaults: dict, tokenizer, dataset, val_d
                   needs_reference: bool = False, value_head: bool = False, policy=None):
     from rl_b200.policy.worker import PolicyWorker
 
+    from rl_b200.policy.worker import ensure_parallel
+
+    ensure_parallel(cfg["policy"])
     rank, world = _world()
     a = dict(defaults)
     a.update(cfg.get(key) or {})
     cfg[key] = a
     set_seed(a["seed"] + rank)
-    logger = Logger(cfg.get("logger"), is_main=rank == 0)
+    logger = Logger(cfg.get("logger"), is_main=_is_main())
     checkpointer = CheckpointManager(cfg.get("checkpointing"))
     save_state = {"current_step": 0, "current_epoch": 0, "total_steps": 0, "consumed_samples": 0, "val_loss": None}
     resume = checkpointer.get_resume_paths() if checkpointer.enabled else None
@@ -178,7 +181,7 @@ def _supervised_train(policy, loader, val_loader, loss_fn, logger, checkpointer,
             if logger is not None:
                 logger.log_metrics(metrics, total_steps, prefix="train")
                 logger.log_metrics(timing, total_steps, prefix="timing/train")
-            if rank == 0:
+            if _is_main():
                 extra = f" acc={metrics['accuracy']:.3f}" if "accuracy" in metrics else ""
                 print(f"[{key}] step {total_steps}: loss={metrics['loss']:.5f}{extra} grad_norm={metrics['grad_norm']:.3f} "
                       f"tokens={int(tok['tokens'])} step_time={timing.get('total_step_time', 0):.2f}s", flush=True)

@@ -24,6 +24,7 @@ from rl_b200.models.transformer import CausalLM, PackedBatch
 from rl_b200.ops import engine_ops as E
 from rl_b200.ops import functional as F
 from rl_b200.ops import lib as _L
+from rl_b200.parallel.tensor import gather_cols, row_linear
 
 _P, _I, _LL = C.c_void_p, C.c_int, C.c_longlong
 _ENGINE_SIGS = {
@@ -329,7 +330,14 @@ class GenerationEngine:
         self.max_prefill_tokens = max_prefill_tokens
         self.tokenizer = tokenizer
         self.native = self.device.type == "cuda" and _L.available()
-        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe
+        # tensor parallelism: this rank serves Hq/tp query and Hkv/tp key/value heads; every tp rank runs the same
+        # scheduler on the same requests and samples the same tokens (rank 0's sample is broadcast each step)
+        self.tp = getattr(model, "tp", None)
+        self.tpw = self.tp.world if self.tp is not None else 1
+        attn0 = model.layers[0].self_attn if len(model.layers) else None
+        self.hq = attn0.hq if attn0 is not None else self.cfg.num_attention_heads
+        self.hkv = attn0.hkv if attn0 is not None else self.cfg.num_key_value_heads
+        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe and self.tpw == 1
         self.logits_dtype = torch.float32 if logits_fp32 else model.dtype
         c = self.cfg
         if num_blocks is None:
@@ -337,7 +345,7 @@ class GenerationEngine:
                 num_blocks = (kv_cache_tokens + block_size - 1) // block_size + max_running
             elif self.device.type == "cuda":
                 free, _ = torch.cuda.mem_get_info(self.device)
-                per_block = 2 * c.num_hidden_layers * c.num_key_value_heads * block_size * c.head_dim * 2
+                per_block = 2 * len(model.layers) * self.hkv * block_size * c.head_dim * 2
                 num_blocks = max(16, int(free * gpu_memory_utilization) // per_block)
             else:
                 num_blocks = 256
@@ -358,10 +366,10 @@ class GenerationEngine:
         if self.k_cache is not None:
             return
         c = self.cfg
-        shape = (self.num_blocks, c.num_key_value_heads, self.block_size, c.head_dim)
+        shape = (self.num_blocks, self.hkv, self.block_size, c.head_dim)
         dt = self.model.dtype
-        self.k_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(c.num_hidden_layers)]
-        self.v_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(c.num_hidden_layers)]
+        self.k_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(len(self.model.layers))]
+        self.v_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(len(self.model.layers))]
 
     def sleep(self, free_kv_cache: bool = True) -> None:
         """Ends a generation phase: drops all requests; optionally returns the KV cache memory (captured graphs are
@@ -376,13 +384,31 @@ class GenerationEngine:
 
     def kv_cache_bytes(self) -> int:
         c = self.cfg
-        return 2 * c.num_hidden_layers * self.num_blocks * c.num_key_value_heads * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
+        return 2 * len(self.model.layers) * self.num_blocks * self.hkv * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
 
     # ------------------------------------------------------------------ model forward (inference)
     def _layer_tail(self, layer, h, a):
         eps = self.cfg.rms_norm_eps
-        h = F.linear(a, layer.self_attn.o_proj, None, h)
+        if self.tpw == 1:
+            h = F.linear(a, layer.self_attn.o_proj, None, h)
+        else:
+            h = row_linear(a, layer.self_attn.o_proj, h, self.tp)  # GEMM + all-reduce (+ residual) in one kernel
         return layer.mlp(F.rmsnorm(h, layer.post_attention_layernorm, eps), h)
+
+    def _output_logits(self, h, out=None):
+        """[n, V] logits: the local vocabulary slice is projected here and the slices are gathered over the tp group."""
+        z = F.gemm(h, self.model.output_weight, out=out if self.tpw == 1 else None, out_dtype=self.logits_dtype)
+        return z if self.tpw == 1 else gather_cols(z, self.tp)
+
+    def _agree(self, tok, lp):
+        """All tp ranks must take the same scheduling decisions: rank 0's samples win."""
+        if self.tpw > 1:
+            import torch.distributed as dist
+
+            src = dist.get_global_rank(self.tp.group, 0) if self.tp.group is not None else 0
+            dist.broadcast(tok, src=src, group=self.tp.group)
+            dist.broadcast(lp, src=src, group=self.tp.group)
+        return tok, lp
 
     @torch.no_grad()
     def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor) -> torch.Tensor:
@@ -391,12 +417,12 @@ class GenerationEngine:
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq)
-            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
-            a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, self.hq, self.hkv, c.head_dim)
             h = self._layer_tail(layer, h, a)
         hl = E.gather_rows(h, last_idx.to(torch.int32))
         hl = F.rmsnorm(hl, m.norm, c.rms_norm_eps)
-        return F.gemm(hl, m.output_weight, out_dtype=self.logits_dtype)
+        return self._output_logits(hl)
 
     @torch.no_grad()
     def _decode_forward(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
@@ -405,12 +431,12 @@ class GenerationEngine:
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq)
-            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
-            a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, c.num_attention_heads,
-                               c.num_key_value_heads, c.head_dim, num_splits=num_splits, scratch=scratch)
+            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, self.hq,
+                               self.hkv, c.head_dim, num_splits=num_splits, scratch=scratch)
             h = self._layer_tail(layer, h, a)
         h = F.rmsnorm(h, m.norm, c.rms_norm_eps)
-        return F.gemm(h, m.output_weight, out=logits_out, out_dtype=self.logits_dtype)
+        return self._output_logits(h, logits_out)
 
     # ------------------------------------------------------------------ decode step (eager or CUDA graph)
     def _static_buffers(self):
@@ -452,24 +478,26 @@ class GenerationEngine:
                                       st["seq_lens"][:B], num_splits, scratch)
         E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=sp.seed,
                  row_keys=st["keys"][:B], out=(st["tok"][:B], st["lp"][:B]))
+        self._agree(st["tok"][:B], st["lp"][:B])
         return logits
 
     def _run_decode(self, n: int, sp: SamplingParams, max_ctx: int):
         st = self._static_buffers()
         B = self._bucket(n)
         c = self.cfg
-        num_splits = E.choose_splits(B, c.num_key_value_heads, max(self.max_model_len // 2, 1), self.block_size, self._sm_count) if self.native else 1
+        num_splits = E.choose_splits(B, self.hkv, max(self.max_model_len // 2, 1), self.block_size, self._sm_count) if self.native else 1
         if not self.native:
             logits = self._decode_forward(st["ids"][:n].long(), st["positions"][:n], st["slots"][:n], st["block_table"][:n],
                                           st["seq_lens"][:n], 1, None)
             tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy,
                                seed=sp.seed, row_keys=st["keys"][:n])
+            tok, lp = self._agree(tok, lp)
             return tok[:n], lp[:n]
         key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed)
         if self.use_graphs:
             g = self._graphs.get(key)
             if g is None:
-                no, nml = E.decode_scratch_sizes(B, c.num_attention_heads, num_splits, c.head_dim)
+                no, nml = E.decode_scratch_sizes(B, self.hq, num_splits, c.head_dim)
                 scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
                 # warm-up outside capture (sets kernel attributes, sizes the allocator), then capture
                 side = torch.cuda.Stream(device=self.device)
@@ -487,17 +515,28 @@ class GenerationEngine:
             g[0].replay()
             _L.Counters.graph_replayed(g[2])
         else:
-            no, nml = E.decode_scratch_sizes(B, c.num_attention_heads, num_splits, c.head_dim)
+            no, nml = E.decode_scratch_sizes(B, self.hq, num_splits, c.head_dim)
             scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
             self._decode_body(st, B, sp, num_splits, scratch)
         return st["tok"][:n], st["lp"][:n]
 
     # ------------------------------------------------------------------ public API
-    @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, max_new_tokens: Optional[Sequence[int]] = None,
                  share_prefixes: bool = True, request_uids: Optional[Sequence[int]] = None) -> list[_Request]:
         """Runs all prompts to completion with continuous batching. Returns one record per prompt (in input order)
         with the generated tokens, their log-probabilities and whether generation was cut by the length limit."""
+        # inference keeps all rows on every tensor-parallel rank (all-reduce form), whatever the training layout is
+        saved = self.tp.sequence_parallel if self.tp is not None else False
+        if self.tp is not None:
+            self.tp.sequence_parallel = False
+        try:
+            return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids)
+        finally:
+            if self.tp is not None:
+                self.tp.sequence_parallel = saved
+
+    @torch.no_grad()
+    def _generate(self, prompts, sp: SamplingParams, max_new_tokens=None, share_prefixes: bool = True, request_uids=None) -> list[_Request]:
         self.wake()
         self.model.eval()
         stop = set(int(t) for t in (sp.stop_token_ids or []))
@@ -596,7 +635,7 @@ class GenerationEngine:
                 if copies:
                     src = torch.tensor([a for a, _ in copies], dtype=torch.int32, device=dev)
                     dst = torch.tensor([b for _, b in copies], dtype=torch.int32, device=dev)
-                    for li in range(self.cfg.num_hidden_layers):
+                    for li in range(len(self.model.layers)):
                         E.block_copy(self.k_cache[li], self.v_cache[li], src, dst)
                 new = list(prefill) + list(shared)
                 rows = torch.stack([last_logits[sid] if sid in last_logits else last_logits[reqs[sid].share_with] for sid in new])
@@ -604,6 +643,7 @@ class GenerationEngine:
                 keys_new = torch.tensor([(reqs[sid].uid << 20) | len(reqs[sid].out_tokens) for sid in new], dtype=torch.int64, device=dev)
                 tok, lp = E.sample(rows.contiguous(), temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p,
                                    greedy=sp.greedy, seed=sp.seed, row_keys=keys_new)
+                tok, lp = self._agree(tok, lp)
                 tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(new, fin, first=True)

@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from rl_b200.algorithms.grpo import _all_reduce_scalars, _world
+from rl_b200.algorithms.grpo import _all_reduce_scalars, _is_main, _world
 from rl_b200.experience.rollouts import run_multi_turn_rollout
 
 
@@ -68,7 +68,7 @@ def run_env_eval(generation, loader, tokenizer, task_to_env, cfg: dict) -> dict:
         else:
             raise ValueError(f"unknown eval metric {e['metric']}")
         count += batch.size
-        if e.get("save_path") and rank == 0:
+        if e.get("save_path") and _is_main():
             for i, log in enumerate(rep["message_log"]):
                 records.append({"idx": int(rep["idx"][i]), "reward": float(rewards[i]),
                                 "response": "".join(str(m["content"]) for m in log if m["role"] == "assistant")})
@@ -76,7 +76,7 @@ def run_env_eval(generation, loader, tokenizer, task_to_env, cfg: dict) -> dict:
     tot = _all_reduce_scalars({"s": score, "n": float(count)})
     out = {"metric": f"{e['metric'].split('@')[0]}@{e['k_value']}", "score": tot["s"] / max(1.0, tot["n"]), "num_prompts": int(tot["n"]),
            "num_tests_per_prompt": n}
-    if e.get("save_path") and rank == 0:
+    if e.get("save_path") and _is_main():
         with open(e["save_path"], "w") as f:
             json.dump({"summary": out, "samples": records}, f, indent=1)
     return out

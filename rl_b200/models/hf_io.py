@@ -105,6 +105,15 @@ def iter_hf_shards(model: CausalLM) -> Iterator[tuple[str, torch.Tensor, Optiona
         yield hf, (p if rows is None else p[rows[0] : rows[1]]), hs
 
 
+def hf_full_shape(local_shape: tuple, hf_slice, tp_size: int) -> tuple:
+    """Shape of the whole HF tensor given the shape of this rank's slice of it."""
+    if hf_slice is None:
+        return tuple(local_shape)
+    full = list(local_shape)
+    full[hf_slice[0]] *= tp_size
+    return tuple(full)
+
+
 def iter_hf_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
     """Yields (hf_name, FULL tensor). Without model parallelism these are views of the parameters; with tensor
     parallelism every shard is all-gathered over the tp group (collective: all tp ranks must iterate together)."""

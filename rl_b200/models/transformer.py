@@ -180,6 +180,20 @@ class PackedBatch:
     positions: torch.Tensor
     cu_seqlens: torch.Tensor
     max_seqlen: int
+    num_real_tokens: Optional[int] = None  # set when a dummy tail sequence pads the stream (see pad_to_multiple)
+
+    def pad_to_multiple(self, m: int, pad_id: int = 0) -> "PackedBatch":
+        """Appends one dummy sequence of pad tokens so that the token count divides by ``m`` (sequence-parallel rows
+        must split evenly over the tensor-parallel ranks). Per-token outputs keep the real tokens first."""
+        T = int(self.input_ids.numel())
+        r = (-T) % m
+        if r == 0:
+            return self
+        dev = self.input_ids.device
+        ids = torch.cat([self.input_ids, torch.full((r,), pad_id, dtype=self.input_ids.dtype, device=dev)])
+        pos = torch.cat([self.positions, torch.arange(r, dtype=self.positions.dtype, device=dev)])
+        cu = torch.cat([self.cu_seqlens, torch.tensor([T + r], dtype=self.cu_seqlens.dtype, device=dev)])
+        return PackedBatch(ids, pos, cu, max(self.max_seqlen, r), num_real_tokens=T)
 
     @staticmethod
     def from_padded(input_ids: torch.Tensor, lengths: torch.Tensor) -> "PackedBatch":
@@ -196,8 +210,11 @@ class PackedBatch:
 
     def unpack(self, flat: torch.Tensor, S: int, fill=0.0) -> torch.Tensor:
         """[T, ...] packed values -> [B, S, ...] right-padded."""
-        B = self.cu_seqlens.numel() - 1
-        lengths = (self.cu_seqlens[1:] - self.cu_seqlens[:-1]).long()
+        cu = self.cu_seqlens
+        if self.num_real_tokens is not None:  # drop the dummy tail sequence
+            cu, flat = cu[:-1], flat[: self.num_real_tokens]
+        B = cu.numel() - 1
+        lengths = (cu[1:] - cu[:-1]).long()
         out = flat.new_full((B, S) + tuple(flat.shape[1:]), fill)
         ar = torch.arange(S, device=flat.device)
         keep = ar[None, :] < lengths[:, None]
@@ -267,22 +284,38 @@ class CausalLM(nn.Module):
     @torch.no_grad()
     def reset_parameters(self, seed: int = 0, std: float = 0.02) -> None:
         """Normal(0, 0.02) weights (HF's default initializer range), ones for norms, zeros for biases.
-        Generated on the parameter's device with a seeded generator: replicated parameters are identical on every rank,
-        tensor-parallel shards differ per tp rank."""
-        for i, (name, p) in enumerate(self.named_parameters()):
+
+        Every logical (HuggingFace-named) tensor is drawn from its own generator seeded by ``seed`` and the tensor's name,
+        and each rank keeps its slice: the model is the same whatever the tensor / pipeline / expert layout is."""
+        import zlib
+
+        from .hf_io import iter_hf_shards, hf_full_shape
+
+        for name, p in self.named_parameters():
             if name.endswith("norm") or name.endswith("layernorm"):
                 p.fill_(1.0)
             elif name.endswith("bias"):
                 p.zero_()
-            else:
-                g = torch.Generator(device=p.device)
-                g.manual_seed(seed * 1000003 + i + 7919 * self.layer_offset + (104729 * self.tp.rank if self.is_tp_sharded(name) else 0))
-                # normal_ in fp32 chunks keeps the memory bounded for 1 GB embedding tables
-                flat = p.view(-1)
-                step = 1 << 26
-                for s in range(0, flat.numel(), step):
-                    e = min(flat.numel(), s + step)
-                    flat[s:e] = (torch.randn(e - s, generator=g, device=p.device, dtype=torch.float32) * std).to(p.dtype)
+        for hf, dst, hs in iter_hf_shards(self):
+            if hf.endswith("norm.weight") or hf.endswith("layernorm.weight") or hf.endswith(".bias"):
+                continue
+            g = torch.Generator(device=dst.device)
+            g.manual_seed((seed * 1000003 + zlib.crc32(hf.encode())) & 0x7FFFFFFFFFFFFFFF)
+            full = hf_full_shape(tuple(dst.shape), hs, self.tp.world)
+            rows, cols = full[0], (full[1] if len(full) > 1 else 1)
+            r0, r1 = (hs[1], hs[1] + hs[2]) if hs is not None and hs[0] == 0 else (0, rows)
+            c0, c1 = (hs[1], hs[1] + hs[2]) if hs is not None and hs[0] == 1 else (0, cols)
+            # rows are generated in order in bounded fp32 chunks; only this rank's slice is kept
+            step = max(1, (1 << 26) // max(1, cols))
+            d2 = dst.view(dst.shape[0], -1)
+            for s0 in range(0, r1, step):
+                e0 = min(rows, s0 + step)
+                blk = torch.randn((e0 - s0, cols), generator=g, device=dst.device, dtype=torch.float32) * std
+                lo, hi = max(s0, r0), min(e0, r1)
+                if hi > lo:
+                    d2[lo - r0 : hi - r0].copy_(blk[lo - s0 : hi - s0, c0:c1].to(dst.dtype))
+        if self.cfg.value_head and self.last_stage:
+            self.score[1:].zero_()
 
     def flatten_parameters(self, align: int = 2048, allocator=None) -> FlatParams:
         self.flat = FlatParams(self, align, allocator)
@@ -299,8 +332,12 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def embed(self, batch: PackedBatch) -> torch.Tensor:
-        h = F.embedding(batch.input_ids, self.embed_tokens)
-        return scatter_rows(h, self.tp) if self.tp.sequence_parallel else h
+        if self.tp.world > 1 and self.tp.sequence_parallel:
+            # each rank embeds its own rows: like every replicated parameter under sequence parallelism, the table's
+            # gradient is a partial sum that the worker all-reduces over the tensor-parallel group
+            rows = batch.input_ids.numel() // self.tp.world
+            return F.embedding(batch.input_ids[self.tp.rank * rows : (self.tp.rank + 1) * rows], self.embed_tokens)
+        return F.embedding(batch.input_ids, self.embed_tokens)
 
     def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         inv_freq = self.inv_freq

@@ -26,6 +26,8 @@ from rl_b200.ops import functional as F
 
 
 def _world(group) -> tuple[int, int]:
+    if isinstance(group, str):  # "self": a group of one (a single data-parallel replica inside a larger job)
+        return 0, 1
     if dist.is_available() and dist.is_initialized():
         return dist.get_rank(group), dist.get_world_size(group)
     return 0, 1
@@ -65,6 +67,18 @@ class ShardedAdamW:
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.fused_comm = fused_comm
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self._replicated: list[tuple[int, int]] = []   # shard-relative ranges replicated over the tensor-parallel group
+        self._replicas = 1
+        self._norm_groups: list = []
+
+    def set_model_parallel(self, replicated_runs: list[tuple[int, int]], replicas: int, norm_groups: list) -> None:
+        """``replicated_runs``: flat ranges whose parameters every one of ``replicas`` tensor-parallel ranks holds in full
+        (their squared gradient norm must count once); ``norm_groups``: process groups over which the squared norm is
+        summed besides the optimizer's own (tensor / pipeline parallel)."""
+        self._replicas = int(replicas)
+        self._norm_groups = list(norm_groups)
+        self._replicated = [(max(a, self.lo) - self.lo, min(b, self.hi) - self.lo) for a, b in replicated_runs
+                            if min(b, self.hi) > max(a, self.lo)]
 
     # ------------------------------------------------------------------ step
     def zero_grad(self) -> None:
@@ -109,8 +123,15 @@ class ShardedAdamW:
         gs = self._reduce_scatter()
         self._sumsq.zero_()
         F.sumsq_(gs, self._sumsq)
+        if self._replicas > 1 and self._replicated:
+            rep = torch.zeros_like(self._sumsq)
+            for a, b in self._replicated:
+                F.sumsq_(gs[a:b], rep)
+            self._sumsq.sub_(rep * (1.0 - 1.0 / self._replicas))
         if self.world > 1:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=self.group)
+        for g in self._norm_groups:
+            dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=g)
         if grad_div != 1.0:
             self._sumsq.mul_(1.0 / (grad_div * grad_div))
         F.clip_scale(self._sumsq, float(self.max_grad_norm or 0.0), 1.0 / grad_div, self._scale, self._norm)

@@ -53,6 +53,39 @@ def _dp_info(group=None):
     return 0, 1
 
 
+def parallel_sizes(policy_cfg: dict) -> dict:
+    """tp / pp / cp / ep sizes and the sequence-parallel flag from ``policy.parallel`` (or, for configs written for the
+    reference, ``dtensor_cfg`` / ``megatron_cfg`` keys)."""
+    par = dict(policy_cfg.get("parallel") or {})
+    dt, mg = policy_cfg.get("dtensor_cfg") or {}, policy_cfg.get("megatron_cfg") or {}
+    src = mg if mg.get("enabled") else dt
+
+    def pick(k_new, *alts):
+        if par.get(k_new) is not None:
+            return par[k_new]
+        for a in alts:
+            if src.get(a) is not None:
+                return src[a]
+        return None
+
+    tp = int(pick("tensor_parallel_size", "tensor_parallel_size", "tensor_model_parallel_size") or 1)
+    return dict(tp=tp, pp=int(pick("pipeline_parallel_size", "pipeline_model_parallel_size") or 1),
+                cp=int(pick("context_parallel_size", "context_parallel_size") or 1),
+                ep=int(pick("expert_parallel_size", "expert_model_parallel_size") or 1),
+                sequence_parallel=bool(tp > 1 and (pick("sequence_parallel", "sequence_parallel") in (None, True))))
+
+
+def ensure_parallel(policy_cfg: dict):
+    """Initialises the process-wide parallel layout from the policy config (idempotent; collective on first use)."""
+    from rl_b200.parallel.state import get_state, init_parallel
+
+    st = get_state()
+    ps = parallel_sizes(policy_cfg)
+    if st.world == 1 and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        st = init_parallel(ps["tp"], ps["pp"], ps["cp"], ps["ep"], ps["sequence_parallel"])
+    return st
+
+
 def _precision(name) -> torch.dtype:
     return {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
             "float16": torch.float16}.get(str(name), torch.bfloat16)
@@ -65,8 +98,17 @@ class PolicyWorker:
         cfg = dict(POLICY_DEFAULTS)
         cfg.update(policy_cfg or {})
         self.cfg = cfg
-        self.dp_group = dp_group
-        self.rank, self.world = _dp_info(dp_group)
+        st = ensure_parallel(cfg)
+        self.pstate = st
+        if st.world > 1 and st.tp * st.pp * st.cp > 1 and dp_group is None:
+            # data parallel = the ranks that hold the same model shard; "self" when there is only one replica
+            dp_group = st.dp_cp_group
+            self.dp_group = None if dp_group == "self" else dp_group
+            self.rank, self.world = (0, 1) if dp_group == "self" else (st.dp_rank * st.cp + st.cp_rank, st.dp * st.cp)
+        else:
+            self.dp_group = dp_group
+            self.rank, self.world = _dp_info(dp_group)
+        dp_group = self.dp_group
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = torch.device(device)
@@ -89,17 +131,33 @@ class PolicyWorker:
         self.model_cfg = model_cfg
         dtc = cfg.get("dtensor_cfg") or {}
         act_ckpt = bool(cfg.get("activation_checkpointing") or dtc.get("activation_checkpointing", False))
+        from rl_b200.parallel.expert import EP
+        from rl_b200.parallel.tensor import TP
+
+        self.tp = TP.from_state(st)
+        self.ep = EP.from_state(st)
+        if self.tp.world > 1 and self.device.type == "cuda" and dtype == torch.bfloat16 and cfg.get("fused_tensor_parallel", True) \
+                and st.tp_comm is None:
+            try:
+                from rl_b200.parallel.tensor import TPFusedComm
+
+                st.tp_comm = TPFusedComm(st.tp_group, wait_limit_s=float(cfg.get("peer_wait_limit_s", 10.0)))
+            except Exception as e:  # no peer access between these GPUs: NCCL collectives around the plain GEMM
+                print(f"[policy] fused tensor-parallel kernels unavailable ({type(e).__name__}: {e}); using NCCL")
+        self.tp.comm = st.tp_comm
+        mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp)
         if weights_path:
             from rl_b200.models.hf_io import load_pretrained
 
-            self.model = load_pretrained(weights_path, device=self.device, dtype=dtype)
+            self.model = load_pretrained(weights_path, device=self.device, dtype=dtype, **mp)
             self.model.activation_checkpointing = act_ckpt
         else:
-            self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt)
+            self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt, **mp)
         # On several GPUs of one node the flat parameter / gradient buffers live in peer-mapped memory so that the
         # optimizer step can run as one fused kernel over NVLink (rl_b200/csrc/comm.cu); NCCL is the fallback.
+        model_parallel = st.tp * st.pp * st.cp * st.ep > 1
         if fused_comm is None and self.world > 1 and self.device.type == "cuda" and cfg.get("fused_optimizer", True) \
-                and dtype == torch.bfloat16 and init_optimizer:
+                and dtype == torch.bfloat16 and init_optimizer and not model_parallel:
             try:
                 from rl_b200.parallel.symmetric import FusedOptimizerComm
 
@@ -109,7 +167,7 @@ class PolicyWorker:
                     print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
                 fused_comm = None
         self.fused_comm = fused_comm
-        self.flat = self.model.flatten_parameters(align=256 * self.world,
+        self.flat = self.model.flatten_parameters(align=256 * max(1, self.world),
                                                   allocator=fused_comm.alloc_params if fused_comm is not None else None)
         self.ref_flat: Optional[torch.Tensor] = None
         if init_reference_model:
@@ -120,7 +178,9 @@ class PolicyWorker:
         if init_optimizer:
             gdt = _precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32
             self.flat.attach_grad_buffer(gdt, allocator=fused_comm.alloc_grads if (fused_comm is not None and gdt == torch.float32) else None)
-            self.optimizer = build_optimizer(self.flat, cfg, group=dp_group, fused_comm=fused_comm)
+            self.optimizer = build_optimizer(self.flat, cfg, group=dp_group if self.world > 1 or st.world == 1 else "self",
+                                             fused_comm=fused_comm)
+            self._configure_model_parallel_grads()
             self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
         self.generation = None
         self.temperature = 1.0
@@ -128,6 +188,37 @@ class PolicyWorker:
         if gen_cfg:
             self.temperature = float(gen_cfg.get("temperature", 1.0) or 1.0)
         self.timers: dict[str, float] = {}
+
+    # ------------------------------------------------------------------ model-parallel gradient bookkeeping
+    def _configure_model_parallel_grads(self) -> None:
+        """Tells the optimizer which flat ranges are replicated over the tensor-parallel group (their squared norm counts
+        once, and with sequence parallelism their gradients are partial sums that must be all-reduced) and over which
+        groups the gradient norm has to be combined."""
+        st = self.pstate
+        self._replicated_runs: list[tuple[int, int]] = []
+        if st.tp > 1:
+            runs: list[list[int]] = []
+            for n, o, k, _ in self.flat.named_slices():
+                if self.model.is_tp_sharded(n):
+                    continue
+                end = o + -(-k // 8) * 8
+                if runs and runs[-1][1] == o:
+                    runs[-1][1] = end
+                else:
+                    runs.append([o, end])
+            self._replicated_runs = [(a, min(b, self.flat.padded)) for a, b in runs]
+        if self.optimizer is not None:
+            groups = [g for g in (st.tp_group if st.tp > 1 else None, st.pp_group if st.pp > 1 else None) if g is not None]
+            self.optimizer.set_model_parallel(self._replicated_runs, st.tp, groups)
+
+    def _sync_replicated_grads(self) -> None:
+        """Sequence parallelism: every tp rank saw only its rows, so gradients of replicated parameters are partial."""
+        st = self.pstate
+        if st.tp == 1 or not st.sequence_parallel or self.flat.grad is None:
+            return
+        self.flat.fold_autograd_grads()
+        for a, b in self._replicated_runs:
+            dist.all_reduce(self.flat.grad[a:b], group=st.tp_group)
 
     # ------------------------------------------------------------------ generation (colocated, shared weights)
     def build_generation(self, gen_cfg: Optional[dict] = None):
@@ -208,6 +299,8 @@ class PolicyWorker:
         batch = PackedBatch.from_padded(ids, lens)
         if self.device.type == "cuda":
             batch.input_ids = batch.input_ids.to(torch.int32)
+        if self.tp.world > 1 and self.tp.sequence_parallel:
+            batch = batch.pad_to_multiple(8 * self.tp.world)
         return batch, ids.shape[1]
 
     # ------------------------------------------------------------------ inference passes
@@ -329,6 +422,7 @@ class PolicyWorker:
                 metrics["global_valid_toks"] = float(global_valid_toks)
                 all_mb_metrics.append(metrics)
             if not eval_mode:
+                self._sync_replicated_grads()
                 gn = self.optimizer.step()
                 grad_norms.append(gn)
             if self.world > 1:

@@ -1,0 +1,154 @@
+"""Model parallelism on CPU (gloo, 2 ranks): a tensor-parallel (+ sequence-parallel) model must reproduce the
+single-rank model's log-probabilities, loss and gradients; expert-parallel MoE must match the local-expert loop."""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _spawn(fn, world, *args):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    out = {}
+    while not q.empty():
+        r, v = q.get()
+        out[r] = v
+    for p in procs:
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}: {out}"
+    return out
+
+
+def _entry(fn, rank, world, port, q, args):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.manual_seed(0)
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q.put((rank, fn(rank, world, *args)))
+    finally:
+        dist.destroy_process_group()
+
+
+def _full_model(seed=3, **over):
+    from rl_b200.models.config import preset
+    from rl_b200.models.transformer import build_model
+
+    cfg = preset("tiny-llama-oracle", **over)
+    return cfg, build_model(cfg, dtype=torch.float32, seed=seed)
+
+
+def _batch(cfg, T_seqs=(9, 14, 5)):
+    from rl_b200.models.transformer import PackedBatch
+
+    g = torch.Generator().manual_seed(1)
+    S = max(T_seqs)
+    ids = torch.randint(0, cfg.vocab_size, (len(T_seqs), S), generator=g)
+    return PackedBatch.from_padded(ids, torch.tensor(T_seqs))
+
+
+def _tp_worker(rank, world, sp, tied):
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+    from rl_b200.models.transformer import build_model
+    from rl_b200.parallel.state import init_parallel
+    from rl_b200.parallel.tensor import TP
+
+    st = init_parallel(tp=world, sequence_parallel=sp)
+    cfg, full = _full_model(tie_word_embeddings=tied)
+    sd = dict(iter_hf_tensors(full))
+    tp = TP.from_state(st)
+    model = build_model(cfg, dtype=torch.float32, seed=99, tp=tp)
+    load_hf_tensors(model, sd.get)
+    batch = _batch(cfg)
+    pb = batch.pad_to_multiple(world) if sp else batch
+    T = batch.input_ids.numel()
+    ref_lp, ref_ent = full.next_token_logprobs(batch, 0.7, want_entropy=True)
+    lp, ent = model.next_token_logprobs(pb, 0.7, want_entropy=True)
+    w = torch.linspace(0.5, 1.5, T)
+    (ref_lp * w).sum().backward()
+    (lp[:T] * w).sum().backward()
+    # gather the tp model's gradients back into HF tensors and compare with the full model
+    if sp:  # partial gradients of replicated parameters
+        for n, p in model.named_parameters():
+            if not model.is_tp_sharded(n):
+                dist.all_reduce(p.grad)
+    full_g = {n: t for n, t in iter_hf_tensors(_GradView(full))}
+    tp_g = {n: t for n, t in iter_hf_tensors(_GradView(model))}
+    gerr = max(float((full_g[n] - tp_g[n]).abs().max()) for n in full_g)
+    # round trip: gathered weights equal the originals
+    werr = max(float((sd[n] - t).abs().max()) for n, t in iter_hf_tensors(model))
+    return dict(lp=float((lp[:T] - ref_lp).abs().max()), ent=float((ent[:T] - ref_ent).abs().max()), grad=gerr, w=werr,
+                logits=float((model.logits(pb)[:T] - full.logits(batch)).abs().max()) if not sp else 0.0)
+
+
+class _GradView:
+    """Presents a model's gradients under its parameter names so that the HF mapping can gather them."""
+
+    def __init__(self, model):
+        self.__dict__.update(cfg=model.cfg, tp=model.tp, ep=model.ep, layer_offset=model.layer_offset, layers=model.layers,
+                             first_stage=model.first_stage, last_stage=model.last_stage)
+        self._m = model
+
+    def named_parameters(self):
+        for n, p in self._m.named_parameters():
+            yield n, (p.grad if p.grad is not None else torch.zeros_like(p))
+
+
+@pytest.mark.parametrize("sp,tied", [(True, False), (False, False), (True, True)])
+def test_tensor_parallel_matches_single_rank(sp, tied):
+    out = _spawn(_tp_worker, 2, sp, tied)
+    for r, m in out.items():
+        assert m["lp"] < 2e-4 and m["ent"] < 2e-4 and m["grad"] < 2e-3 and m["w"] == 0.0 and m["logits"] < 2e-4, (r, m)
+
+
+def _ep_worker(rank, world):
+    from rl_b200.models.config import preset
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+    from rl_b200.models.transformer import build_model
+    from rl_b200.parallel.expert import EP
+    from rl_b200.parallel.state import init_parallel
+
+    st = init_parallel(ep=world)
+    cfg = preset("tiny-llama-oracle", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True)
+    full = build_model(cfg, dtype=torch.float32, seed=5)
+    sd = dict(iter_hf_tensors(full))
+    model = build_model(cfg, dtype=torch.float32, seed=77, ep=EP.from_state(st))
+    load_hf_tensors(model, sd.get)
+    # every rank routes different tokens (data parallel over the expert group)
+    batch = _batch(cfg, (7 + rank, 11, 4 + 2 * rank))
+    ref, _ = full.next_token_logprobs(batch)
+    got, _ = model.next_token_logprobs(batch)
+    ref.sum().backward()
+    got.sum().backward()
+    gl = dict(model.named_parameters())["layers.0.mlp.gate_up_proj"].grad
+    gf = dict(full.named_parameters())["layers.0.mlp.gate_up_proj"].grad
+    # expert gradients: the ep model accumulates contributions from both ranks' tokens; compare after summing the
+    # full model's gradients over the ranks
+    dist.all_reduce(gf)
+    per = cfg.num_experts // world
+    return dict(lp=float((got - ref).abs().max()), g=float((gl - gf[rank * per : (rank + 1) * per]).abs().max()))
+
+
+def test_expert_parallel_matches_local_experts():
+    out = _spawn(_ep_worker, 2)
+    for r, m in out.items():
+        assert m["lp"] < 2e-4 and m["g"] < 2e-3, (r, m)

@@ -56,4 +56,5 @@ def test_dpo_and_rm_improve_accuracy(tmp_path):
     policy, loader, vl, loss_fn, logger, ck, ss, cfg = setup_rm(cfg, None, ds, None, model_cfg=_mc())
     hist = []
     rm_train(policy, loader, vl, None, loss_fn, logger, ck, ss, cfg, step_callback=lambda s, m: hist.append(m["train"]))
-    assert hist[-1]["accuracy"] > hist[0]["accuracy"] and hist[-1]["loss"] < hist[0]["loss"]
+    acc = [h["accuracy"] for h in hist]
+    assert sum(acc[-5:]) > sum(acc[:5]) and hist[-1]["loss"] < hist[0]["loss"], acc

@@ -66,3 +66,128 @@ def _worker(rank, world, port, fused):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_optimizer_matches_nccl(native_lib):
     mp.spawn(_worker, args=(2, _free_port(), True), nprocs=2, join=True)
+
+
+def _tp_kernel_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.ops.lib import check_status
+    from rl_b200.parallel.tensor import TPFusedComm, all_gather_rows
+
+    dev = torch.device("cuda", rank)
+    comm = TPFusedComm(None, wait_limit_s=5.0)
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
+
+    # (rows per rank, N, K): tile-aligned, ragged rows (tiles straddle two ranks), small
+    for it, (rows, N, K) in enumerate([(256, 512, 512), (200, 768, 320), (72, 256, 1024), (1024, 1536, 512), (200, 768, 320)]):
+        x = rnd(rows, K)
+        w = rnd(N, K, scale=0.05)
+        bias = torch.randn(N, generator=g, device=dev)
+        xf = all_gather_rows(x, None, world).float()
+        # gather: Y = allgather(x) @ w^T + bias
+        y = comm.gather_gemm(x, w, bias=bias)
+        ref = xf @ w.float().t() + bias
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2, ("gather", it)
+        assert torch.equal(comm.gathered(world * rows, K).float(), xf), ("staging holds the gathered rows", it)
+        # gather with a [K, N] weight (the backward form)
+        wt = w.t().contiguous()
+        y2 = comm.gather_gemm(x, wt, b_mn=True)
+        assert (y2.float() - (ref - bias)).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2, ("gather b_mn", it)
+        # scatter: out = reduce_scatter(a @ w2^T) + residual
+        M = world * rows
+        a = rnd(M, K)
+        w2 = rnd(N, K, scale=0.05)
+        res = rnd(rows, N)
+        part = a.float() @ w2.float().t()
+        tot = part.clone()
+        dist.all_reduce(tot)
+        out = comm.scatter_gemm(a, w2, residual=res)
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        ref_rs = tot[rank * rows : (rank + 1) * rows] + res.float()
+        tol = 2e-2 * ref_rs.abs().max().item() + 2e-2
+        assert (out.float() - ref_rs).abs().max().item() <= tol, ("scatter", it, (out.float() - ref_rs).abs().max().item())
+        # all-reduce form on a decode-sized batch
+        m = 48
+        a3 = rnd(m, K)
+        res3 = rnd(m, N)
+        dist.broadcast(res3, src=0)
+        tot3 = a3.float() @ w2.float().t()
+        dist.all_reduce(tot3)
+        out3 = comm.scatter_gemm(a3, w2, residual=res3, all_reduce=True)
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        assert (out3.float() - (tot3 + res3.float())).abs().max().item() <= 2e-2 * tot3.abs().max().item() + 2e-2, ("allreduce", it)
+        # every rank holds bit-identical all-reduced rows (fixed summation order)
+        other = out3.clone()
+        dist.broadcast(other, src=0)
+        assert torch.equal(out3, other)
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tensor_parallel_gemms(native_lib):
+    mp.spawn(_tp_kernel_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _tp_train_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(model_type="llama", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(1, 4096, (8, 96), generator=g)
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([96, 80, 64, 96, 33, 70, 96, 51]), token_mask=torch.ones(8, 96),
+                           sample_mask=torch.ones(8))
+    res = {}
+    for mode in ("fused", "nccl"):
+        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=8, train_micro_batch_size=4, max_total_sequence_length=128,
+                              fused_tensor_parallel=(mode == "fused"), max_grad_norm=1.0, parallel=dict(tensor_parallel_size=2),
+                              optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.0)),
+                              generation=dict(max_new_tokens=16, temperature=1.0, stop_token_ids=[], kv_cache_tokens=4096, block_size=16,
+                                              max_running=16)),
+                         model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, seed=3)
+        if mode == "nccl":
+            p.tp.comm = None
+            p.pstate.tp_comm = None
+        assert (p.tp.comm is not None) == (mode == "fused")
+        lp0 = p.get_logprobs(data)["logprobs"]
+        outs = [p.train(data, NLLLossFn(), gbs=8, mbs=4) for _ in range(2)]
+        gen = p.build_generation()
+        gen.prepare_for_generation()
+        gout = gen.generate(BatchedDataDict(input_ids=ids[:, :24], input_lengths=torch.full((8,), 24)))
+        gen.finish_generation()
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        res[mode] = (lp0, [float(o["loss"][0]) for o in outs], [float(o["grad_norm"][0]) for o in outs], gout["logprobs"])
+        # trainer log-probabilities of the sampled tokens agree with the engine's
+        tl = p.get_logprobs(BatchedDataDict(input_ids=gout["output_ids"], input_lengths=gout["unpadded_sequence_lengths"]))["logprobs"]
+        pos = torch.arange(gout["output_ids"].shape[1])[None, :]
+        mask = (pos >= 24) & (pos < gout["unpadded_sequence_lengths"][:, None])
+        assert (tl - gout["logprobs"])[mask].abs().max().item() < 0.08, mode
+    f, n = res["fused"], res["nccl"]
+    assert (f[0] - n[0]).abs().max().item() < 0.05
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[1], n[1])) < 5e-3, (f[1], n[1])
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[2], n[2])) < 2e-2, (f[2], n[2])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_worker_fused_vs_nccl(native_lib):
+    mp.spawn(_tp_train_worker, args=(2, _free_port()), nprocs=2, join=True)

@@ -44,7 +44,9 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int EPI_ROW_BYTES = 144;  // 128 B of bf16 per row + 16 B pad (conflict-free 16-byte accesses)
+constexpr int EPI_STAGE_BYTES = 4 * 32 * EPI_ROW_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + EPI_STAGE_BYTES + 1024;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
@@ -53,6 +55,11 @@ constexpr int MAX_TP = 8;
 enum { MODE_GATHER = 1, MODE_SCATTER = 2 };
 // flag words of one rank (uint32, symmetric memory, zero-initialised)
 enum { FLAG_START = 0, FLAG_DATA = 8, FLAG_END = 16, FLAG_GO = 32, FLAG_COUNT = 33, FLAG_WORDS = 64 };
+
+// Phase timestamps (%globaltimer, ns) of the last scatter-mode launch, written by thread 0 of CTA 0:
+// [0] kernel start, [1] own tiles done, [2] after the first grid sync, [3] after the peer barrier + second grid sync,
+// [4] reduce phase done. Read back with rlb_gemm_tp_phase_times (a profiling aid; costs five stores).
+__device__ unsigned long long g_tp_phase_ns[8];
 
 struct TpArgs {
   int mode, rank, world;
@@ -129,9 +136,23 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int 
 }
 
 // ------------------------------------------------------------------------------------------ pusher CTAs (gather)
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+               "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
+}
+
 // Copies this rank's [rows_per_rank, K] shard into rows [rank * rows_per_rank, ...) of every rank's staging buffer
 // ([world * rows_per_rank, K] bf16, row pitch K) and then raises FLAG_DATA[rank] on every rank.
-__device__ void push_rows(const TpArgs& t, int K, int* status, int* s_flag) {
+//
+// A contiguous shard (row pitch K) moves as 48 KB bulk copies through the CTA's (otherwise unused) pipeline buffers:
+// one thread keeps three loads in flight and forwards every chunk to all ranks with bulk stores, so a handful of CTAs
+// saturates NVLink. A strided shard falls back to 16-byte loads / stores by all threads.
+__device__ void push_rows(const TpArgs& t, int K, int* status, int* s_flag, uint8_t* smem, uint64_t* full_bar,
+                          volatile int* abort_flag) {
   const int npush = gridDim.x - t.gemm_ctas;
   const int pidx = blockIdx.x - t.gemm_ctas;
   unsigned int* my_flags = t.flags[t.rank];
@@ -143,14 +164,56 @@ __device__ void push_rows(const TpArgs& t, int K, int* status, int* s_flag) {
   if (threadIdx.x == 0)
     *s_flag = wait_flag(my_flags + FLAG_GO, t.epoch, t.limit_ns, false, status, RLB_ERR_WAIT_FLAG) ? 1 : 0;
   __syncthreads();
-  if (*s_flag) {
+  const long long shard_bytes = static_cast<long long>(t.rows_per_rank) * K * 2;
+  const long long rank_off = static_cast<long long>(t.rank) * shard_bytes;
+  if (*s_flag && t.lda_local == K) {
+    if (threadIdx.x == 0) {
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(t.a_local);
+      const long long nchunks = (shard_bytes + STAGE_BYTES - 1) / STAGE_BYTES;
+      const long long mine = pidx < nchunks ? (nchunks - pidx + npush - 1) / npush : 0;  // chunks pidx, pidx+npush, ...
+      auto issue = [&](long long j) {
+        const long long c = pidx + j * npush;
+        const long long off = c * STAGE_BYTES;
+        const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(STAGE_BYTES), shard_bytes - off));
+        const uint32_t bar = smem_u32(&full_bar[j % STAGES]);
+        mbar_arrive_expect_tx(bar, bytes);
+        bulk_load(smem_u32(smem + (j % STAGES) * STAGE_BYTES), src + off, bytes, bar);
+      };
+      for (long long j = 0; j < mine && j < STAGES - 1; ++j) issue(j);
+      bool ok = true;
+      for (long long j = 0; j < mine && ok; ++j) {
+        if (!mbar_wait(smem_u32(&full_bar[j % STAGES]), static_cast<uint32_t>((j / STAGES) & 1), abort_flag, status,
+                       RLB_ERR_WAIT_FULL)) {
+          ok = false;
+          break;
+        }
+        const long long off = (pidx + j * npush) * static_cast<long long>(STAGE_BYTES);
+        const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(STAGE_BYTES), shard_bytes - off));
+        const uint32_t s_src = smem_u32(smem + (j % STAGES) * STAGE_BYTES);
+        for (int p = 0; p < t.world; ++p) {
+          int peer = t.rank + p;
+          if (peer >= t.world) peer -= t.world;
+          bulk_store(t.stage[peer] + rank_off + off, s_src, bytes);
+        }
+        tma_store_commit();
+        // the buffer of chunk j-1 is free once its stores have read it: refill it with chunk j + STAGES - 1
+        if (j + STAGES - 1 < mine) {
+          tma_store_wait_read<1>();
+          issue(j + STAGES - 1);
+        }
+      }
+      tma_store_wait<0>();   // all bulk stores of this CTA are complete
+      fence_proxy_async();
+      if (!ok) *s_flag = 0;
+    }
+  } else if (*s_flag) {
     const long long vec_per_row = K / 8;
     const long long total = static_cast<long long>(t.rows_per_rank) * vec_per_row;
     for (long long i = static_cast<long long>(pidx) * NUM_THREADS + threadIdx.x; i < total;
          i += static_cast<long long>(npush) * NUM_THREADS) {
       const long long row = i / vec_per_row, v = i - row * vec_per_row;
       const uint4 x = *reinterpret_cast<const uint4*>(t.a_local + row * t.lda_local + v * 8);
-      const long long off = ((static_cast<long long>(t.rank) * t.rows_per_rank + row) * K + v * 8) * 2;
+      const long long off = rank_off + (row * K + v * 8) * 2;
       for (int p = 0; p < t.world; ++p) {
         int peer = t.rank + p;
         if (peer >= t.world) peer -= t.world;
@@ -190,6 +253,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const bool stamp = blockIdx.x == 0 && threadIdx.x == 0 && t.mode == MODE_SCATTER;
+  if (stamp) g_tp_phase_ns[0] = globaltimer_ns();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
@@ -229,7 +294,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   unsigned int* my_flags = t.flags[t.rank];
 
   if (gather && static_cast<int>(blockIdx.x) >= t.gemm_ctas) {
-    push_rows(t, K, status, s_flag);
+    push_rows(t, K, status, s_flag, smem, full_bar, abort_flag);
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -346,55 +411,65 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool row_ok = row < M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const int col0 = n_blk * BN;
-      // scatter: where this row's partial goes
-      int dest = 0;
-      long long slot_row = 0;
-      if (!gather && row_ok) {
-        dest = t.all_reduce ? 0 : row / t.rows_per_rank;
-        slot_row = static_cast<long long>(t.rank) * rows_out + (t.all_reduce ? row : row - dest * t.rows_per_rank);
-      }
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col = col0 + c * 32;
-        if (!row_ok || col >= N) continue;
-        float v[32];
+      uint8_t* epi = smem + STAGES * STAGE_BYTES + 256 + (warp - 2) * 32 * EPI_ROW_BYTES;
+      const int row_base = m_blk * BM + quarter * 32;
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col = col0 + c * 64;
+        uint4 o[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        if (gather && t.bias) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 64 + half * 32, r);
+          tmem_ld_wait();
+          if (gather && t.bias) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col + i < N) v[i] += t.bias[col + i];
-        }
-        uint4 o[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-          o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-          o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-          o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-        }
-        if (gather) {
-          __nv_bfloat16* dst = t.C + static_cast<long long>(row) * t.ldc + col;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            if (col + q * 8 < N) *reinterpret_cast<uint4*>(dst + q * 8) = o[q];
-        } else {
-          const long long off = (slot_row * N + col) * 2;
-          if (t.all_reduce) {
-            for (int p = 0; p < t.world; ++p) {
-              int peer = t.rank + p;
-              if (peer >= t.world) peer -= t.world;
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                if (col + q * 8 < N) *reinterpret_cast<uint4*>(t.stage[peer] + off + q * 16) = o[q];
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              if (col + q * 8 < N) *reinterpret_cast<uint4*>(t.stage[dest] + off + q * 16) = o[q];
+            for (int i = 0; i < 32; ++i)
+              if (col + half * 32 + i < N) r[i] = __float_as_uint(__uint_as_float(r[i]) + t.bias[col + half * 32 + i]);
           }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            o[half * 4 + q].x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+            o[half * 4 + q].y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+            o[half * 4 + q].z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+            o[half * 4 + q].w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+          }
+        }
+        if (col >= N) continue;  // uniform over the warp
+        if (gather) {
+          if (row_ok) {
+            __nv_bfloat16* dst = t.C + static_cast<long long>(row) * t.ldc + col;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (col + q * 8 < N) *reinterpret_cast<uint4*>(dst + q * 8) = o[q];
+          }
+        } else {
+          // transpose through shared memory so that 8 lanes write one row's 128 contiguous bytes: peer stores leave
+          // the GPU as full 128-byte NVLink writes instead of scattered 16-byte ones
+#pragma unroll
+          for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(epi + lane * EPI_ROW_BYTES + q * 16) = o[q];
+          __syncwarp();
+          const int piece = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const int grow = row_base + rr;
+            if (grow < M && col + piece * 8 < N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(epi + rr * EPI_ROW_BYTES + piece * 16);
+              if (t.all_reduce) {
+                const long long off = ((static_cast<long long>(t.rank) * rows_out + grow) * N + col + piece * 8) * 2;
+                for (int p = 0; p < t.world; ++p) {
+                  int peer = t.rank + p;
+                  if (peer >= t.world) peer -= t.world;
+                  *reinterpret_cast<uint4*>(t.stage[peer] + off) = v;
+                }
+              } else {
+                const int dest = grow / t.rows_per_rank;
+                const long long srow = static_cast<long long>(t.rank) * rows_out + (grow - dest * t.rows_per_rank);
+                *reinterpret_cast<uint4*>(t.stage[dest] + (srow * N + col + piece * 8) * 2) = v;
+              }
+            }
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
@@ -412,8 +487,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (gather) return;
 
   // ------------------------------------------------------------ scatter: partials visible everywhere, then reduce
+  if (stamp) g_tp_phase_ns[1] = globaltimer_ns();
   __threadfence_system();
   grid.sync();
+  if (stamp) g_tp_phase_ns[2] = globaltimer_ns();
   if (blockIdx.x == 0) {
     if (warp == 0) {
       const bool b_ok = peer_barrier_warp(t, FLAG_END, status);
@@ -423,35 +500,67 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (threadIdx.x == 0) st_release_gpu(my_flags + FLAG_GO + 2, *s_flag ? t.epoch : t.epoch - 1);
   }
   grid.sync();
+  if (stamp) g_tp_phase_ns[3] = globaltimer_ns();
   if (ld_acquire_gpu(my_flags + FLAG_GO + 2) != t.epoch) return;  // a peer did not arrive: leave `out` untouched
   const int rows_out = t.all_reduce ? M : t.rows_per_rank;
   const long long vec_per_row = N / 8;
   const long long total = static_cast<long long>(rows_out) * vec_per_row;
   const unsigned char* mine = t.stage[t.rank];
-  for (long long i = static_cast<long long>(blockIdx.x) * NUM_THREADS + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * NUM_THREADS) {
-    const long long row = i / vec_per_row, c = (i - row * vec_per_row) * 8;
-    float acc[8];
+  // four independent vectors per thread and iteration keep enough loads in flight to run at memory bandwidth
+  constexpr int U = 4;
+  const long long stride = static_cast<long long>(gridDim.x) * NUM_THREADS;
+  for (long long i0 = static_cast<long long>(blockIdx.x) * NUM_THREADS + threadIdx.x; i0 < total; i0 += stride * U) {
+    float acc[U][8];
+    long long row[U], c[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      live[u] = i < total;
+      row[u] = live[u] ? i / vec_per_row : 0;
+      c[u] = live[u] ? (i - row[u] * vec_per_row) * 8 : 0;
+    }
     if (t.residual) {
-      const uint4 rv = *reinterpret_cast<const uint4*>(t.residual + row * t.ldr + c);
-      const float2 a0 = unpack_bf16x2(rv.x), a1 = unpack_bf16x2(rv.y), a2 = unpack_bf16x2(rv.z), a3 = unpack_bf16x2(rv.w);
-      acc[0] = a0.x; acc[1] = a0.y; acc[2] = a1.x; acc[3] = a1.y; acc[4] = a2.x; acc[5] = a2.y; acc[6] = a3.x; acc[7] = a3.y;
+      uint4 rv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) rv[u] = live[u] ? *reinterpret_cast<const uint4*>(t.residual + row[u] * t.ldr + c[u]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float2 a0 = unpack_bf16x2(rv[u].x), a1 = unpack_bf16x2(rv[u].y), a2 = unpack_bf16x2(rv[u].z), a3 = unpack_bf16x2(rv[u].w);
+        acc[u][0] = a0.x; acc[u][1] = a0.y; acc[u][2] = a1.x; acc[u][3] = a1.y;
+        acc[u][4] = a2.x; acc[u][5] = a2.y; acc[u][6] = a3.x; acc[u][7] = a3.y;
+      }
     } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
     }
     for (int s = 0; s < t.world; ++s) {
-      const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(mine + ((static_cast<long long>(s) * rows_out + row) * N + c) * 2));
-      const float2 a0 = unpack_bf16x2(pv.x), a1 = unpack_bf16x2(pv.y), a2 = unpack_bf16x2(pv.z), a3 = unpack_bf16x2(pv.w);
-      acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y; acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+      uint4 pv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        pv[u] = live[u] ? __ldcg(reinterpret_cast<const uint4*>(mine + ((static_cast<long long>(s) * rows_out + row[u]) * N + c[u]) * 2))
+                        : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float2 a0 = unpack_bf16x2(pv[u].x), a1 = unpack_bf16x2(pv[u].y), a2 = unpack_bf16x2(pv[u].z), a3 = unpack_bf16x2(pv[u].w);
+        acc[u][0] += a0.x; acc[u][1] += a0.y; acc[u][2] += a1.x; acc[u][3] += a1.y;
+        acc[u][4] += a2.x; acc[u][5] += a2.y; acc[u][6] += a3.x; acc[u][7] += a3.y;
+      }
     }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(t.out + row * t.ldo + c) = o;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      uint4 o;
+      o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+      o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+      o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+      o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+      *reinterpret_cast<uint4*>(t.out + row[u] * t.ldo + c[u]) = o;
+    }
   }
+  if (stamp) g_tp_phase_ns[4] = globaltimer_ns();
 }
 
 int g_sms = 0;
@@ -503,6 +612,13 @@ void fill_common(TpArgs& t, void* const* stage_ptrs, void* const* flag_ptrs, int
 
 }  // namespace
 
+// Copies the five phase timestamps of the last scatter-mode launch to `out_ns` (host memory). Synchronises the device.
+RLB_API int rlb_gemm_tp_phase_times(unsigned long long* out_ns) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaMemcpyFromSymbol(out_ns, g_tp_phase_ns, 5 * sizeof(unsigned long long)));
+}
+
 // Bytes of flag memory each rank must provide (zero-initialised, symmetric).
 RLB_API int rlb_gemm_tp_flag_bytes() { return FLAG_WORDS * 4; }
 
@@ -536,7 +652,7 @@ RLB_API int rlb_gemm_tp_gather(const void* a_local, long long lda_local, const v
   rc = make_b_map(&tb, B, N, K, ldb, b_mn != 0);
   if (rc) return -100 - rc;
   const int sms = sm_count();
-  if (pushers <= 0) pushers = 16;
+  if (pushers <= 0) pushers = 12;
   if (pushers > sms / 2) pushers = sms / 2;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   t.gemm_ctas = tiles < sms - pushers ? tiles : sms - pushers;

@@ -1,0 +1,105 @@
+"""FP8 weight quantisation used by refit into FP8 engines: 128x128 block scales and MXFP8 (1x32 groups, E8M0 scales).
+
+``quantize_fp8_blockwise`` follows ``cast_tensor_to_fp8_blockwise`` of the reference
+(nemo_rl/models/generation/vllm/quantization/fp8.py:533-620): per-block amax, de-scale = amax / 448 (optionally rounded
+up to a power of two), saturating cast to e4m3, ragged edges padded with the matrix's last element. ``quantize_mxfp8``
+produces e4m3 data with one E8M0 scale byte per 32 consecutive elements of a row (scale = 2^ceil(log2(amax / 448)), so
+nothing saturates). On a GPU both run as one native kernel; the torch forms below are the CPU path and the test oracle.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from rl_b200.ops import lib as _L
+from rl_b200.ops.lib import P, I, L, F as _F, call, ptr, register, stream_ptr, use_native
+
+FP8_MAX = 448.0
+E4M3 = torch.float8_e4m3fn
+
+register("rlb_quant_fp8_block128", [P, L, P, L, P, I, I, I, _F, P])
+register("rlb_quant_mxfp8", [P, L, P, L, P, L, I, I, P])
+register("rlb_dequant_fp8_block128", [P, L, P, P, L, I, I, P])
+register("rlb_dequant_mxfp8", [P, L, P, L, P, L, I, I, P])
+
+
+def _pow2_descale(descale: torch.Tensor):
+    e = torch.ceil(torch.log2(descale)).clamp(-127, 127) + 127
+    e = torch.where(descale > 0, e, torch.zeros_like(e)).to(torch.uint8)
+    ds = torch.where(e == 0, torch.ones_like(descale), torch.exp2(e.float() - 127))
+    return ds, e
+
+
+def quantize_fp8_blockwise_ref(w: torch.Tensor, block: int = 128, pow2: bool = False):
+    R, C = w.shape
+    pr, pc = (-R) % block, (-C) % block
+    x = w.float()
+    if pr or pc:
+        x = torch.nn.functional.pad(x, (0, pc, 0, pr), value=float(x[-1, -1]))
+    br, bc = x.shape[0] // block, x.shape[1] // block
+    xb = x.reshape(br, block, bc, block).permute(0, 2, 1, 3)
+    amax = xb.abs().amax(dim=(-1, -2))
+    if pow2:
+        ds, _ = _pow2_descale(amax / FP8_MAX)
+        scale = 1.0 / ds
+    else:
+        scale = torch.where((amax == 0) | torch.isinf(amax), torch.ones_like(amax), FP8_MAX / amax)
+        ds = 1.0 / scale
+    q = (xb * scale[:, :, None, None]).clamp(-FP8_MAX, FP8_MAX).to(E4M3)
+    q = q.permute(0, 2, 1, 3).reshape(x.shape)[:R, :C].contiguous()
+    return q, ds
+
+
+def quantize_fp8_blockwise(w: torch.Tensor, pow2: bool = False):
+    """bf16 [R, C] -> (e4m3 [R, C], fp32 de-scale [ceil(R/128), ceil(C/128)]); ``w ~= q.float() * descale[block]``."""
+    if not (use_native(w) and w.dtype == torch.bfloat16):
+        return quantize_fp8_blockwise_ref(w, 128, pow2)
+    R, C = w.shape
+    w = w if w.stride(1) == 1 else w.contiguous()
+    q = torch.empty((R, C), dtype=E4M3, device=w.device)
+    ds = torch.empty(((R + 127) // 128, (C + 127) // 128), dtype=torch.float32, device=w.device)
+    pad_abs = float(w[-1, -1].abs()) if (R % 128 or C % 128) else 0.0
+    call("rlb_quant_fp8_block128", ptr(w), w.stride(0), ptr(q), q.stride(0), ptr(ds), R, C, int(pow2), pad_abs, stream_ptr())
+    return q, ds
+
+
+def dequantize_fp8_blockwise(q: torch.Tensor, descale: torch.Tensor) -> torch.Tensor:
+    R, C = q.shape
+    if use_native(q):
+        out = torch.empty((R, C), dtype=torch.bfloat16, device=q.device)
+        call("rlb_dequant_fp8_block128", ptr(q), q.stride(0), ptr(descale.contiguous()), ptr(out), out.stride(0), R, C, stream_ptr())
+        return out
+    ds = descale.repeat_interleave(128, 0)[:R].repeat_interleave(128, 1)[:, :C]
+    return (q.float() * ds).to(torch.bfloat16)
+
+
+def quantize_mxfp8_ref(w: torch.Tensor):
+    R, C = w.shape
+    assert C % 32 == 0
+    x = w.float().reshape(R, C // 32, 32)
+    amax = x.abs().amax(-1)
+    ds, e = _pow2_descale(amax / FP8_MAX)
+    q = (x / ds[..., None]).clamp(-FP8_MAX, FP8_MAX).to(E4M3).reshape(R, C)
+    return q, e
+
+
+def quantize_mxfp8(w: torch.Tensor):
+    """bf16 [R, C] (C % 32 == 0) -> (e4m3 [R, C], uint8 E8M0 scales [R, C/32]); value = q * 2^(scale - 127)."""
+    if not (use_native(w) and w.dtype == torch.bfloat16):
+        return quantize_mxfp8_ref(w)
+    R, C = w.shape
+    w = w if w.stride(1) == 1 else w.contiguous()
+    q = torch.empty((R, C), dtype=E4M3, device=w.device)
+    sc = torch.empty((R, C // 32), dtype=torch.uint8, device=w.device)
+    call("rlb_quant_mxfp8", ptr(w), w.stride(0), ptr(q), q.stride(0), ptr(sc), sc.stride(0), R, C, stream_ptr())
+    return q, sc
+
+
+def dequantize_mxfp8(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    R, C = q.shape
+    if use_native(q):
+        out = torch.empty((R, C), dtype=torch.bfloat16, device=q.device)
+        call("rlb_dequant_mxfp8", ptr(q), q.stride(0), ptr(scales), scales.stride(0), ptr(out), out.stride(0), R, C, stream_ptr())
+        return out
+    ds = torch.where(scales == 0, torch.ones((), dtype=torch.float32), torch.exp2(scales.float() - 127))
+    return (q.float().reshape(R, C // 32, 32) * ds[..., None]).reshape(R, C).to(torch.bfloat16)

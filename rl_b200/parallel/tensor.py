@@ -82,7 +82,7 @@ class TPFusedComm:
     ``max_rows`` is the largest gathered row count (tokens of a micro-batch), ``max_cols`` the widest gathered /
     scattered matrix (the hidden size). Buffers grow on demand (collectively: all ranks see the same shapes)."""
 
-    def __init__(self, group, max_rows: int = 0, max_cols: int = 0, wait_limit_s: float = 10.0, pushers: int = 16):
+    def __init__(self, group, max_rows: int = 0, max_cols: int = 0, wait_limit_s: float = 10.0, pushers: int = 12):
         from rl_b200.parallel.symmetric import SymmetricBuffer
 
         self._SB = SymmetricBuffer
@@ -156,6 +156,19 @@ class TPFusedComm:
         if rc:
             raise RuntimeError(f"rlb_gemm_tp_scatter failed with code {rc}")
         return out
+
+    @staticmethod
+    def phase_times_us() -> list[float]:
+        """Durations (us) of the phases of the last ``scatter_gemm`` launch on this GPU, measured by CTA 0:
+        [own tiles, first grid sync, peer barrier + second grid sync, reduce]."""
+        lib = _bind()
+        buf = (C.c_ulonglong * 5)()
+        lib.rlb_gemm_tp_phase_times.argtypes = [C.POINTER(C.c_ulonglong)]
+        lib.rlb_gemm_tp_phase_times.restype = C.c_int
+        rc = lib.rlb_gemm_tp_phase_times(buf)
+        if rc:
+            raise RuntimeError(f"rlb_gemm_tp_phase_times failed with code {rc}")
+        return [(buf[i + 1] - buf[i]) / 1e3 for i in range(4)]
 
     def close(self):
         for b in (self.stage_a, self.stage_c, self.ctrl):

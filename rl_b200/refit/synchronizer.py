@@ -1,0 +1,143 @@
+"""Weight synchronizer: executes a :class:`RefitPlan` with one copy kernel per rank (rl_b200/csrc/refit.cu).
+
+Every rank owns a *weight arena* for its engine shard in peer-mapped memory. ``sync_weights()`` pushes the pieces of
+this rank's trainer parameters that some engine rank needs straight into that rank's arena (local stores or P2P stores
+over NVLink), then all ranks meet at a barrier; after it every arena holds the current weights in the engine's layout.
+When trainer and engine share a layout no synchronizer is needed at all: the engine reads the trainer's buffers.
+
+``WeightSynchronizer.twin_sync()`` is the collective form (all-gather of every HF tensor + slicing), the NCCL / gloo
+baseline and the CPU path.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import struct
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from rl_b200.models.config import ModelConfig
+from rl_b200.models.transformer import CausalLM
+from rl_b200.parallel.tensor import TP
+from rl_b200.refit.plan import RefitPlan, build_refit_plan, serving_param_layout
+
+WORK_VECS = 8192  # 128 KB per work item
+
+
+def build_serving_model(cfg: ModelConfig, tp_serve: int, rank: int, arena: torch.Tensor, group=None, comm=None) -> CausalLM:
+    """An engine-side model whose parameters are views into ``arena`` (laid out by :func:`serving_param_layout`)."""
+    tp = TP(group, rank % tp_serve, tp_serve, comm, sequence_parallel=False)
+    model = CausalLM(cfg, dtype=arena.dtype, device="meta", init=False, tp=tp)
+    layout, total = serving_param_layout(cfg, tp_serve)
+    assert arena.numel() >= total
+    for name, p in list(model.named_parameters()):
+        off, (r, c) = layout[name]
+        view = arena[off : off + r * c].view(p.shape)
+        mod = model
+        *path, leaf = name.split(".")
+        for part in path:
+            mod = getattr(mod, part) if not part.isdigit() else mod[int(part)]
+        setattr(mod, leaf, torch.nn.Parameter(view, requires_grad=False))
+    from rl_b200.models.config import rope_inv_freq
+
+    model.inv_freq = rope_inv_freq(cfg, arena.device)
+    return model
+
+
+class WeightSynchronizer:
+    def __init__(self, train_model: CausalLM, cfg: ModelConfig, tp_serve: int, group=None, serve_group=None, serve_comm=None):
+        self.cfg = cfg
+        self.train_model = train_model
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.group = group
+        self.tp_train, self.tp_serve = train_model.tp.world, tp_serve
+        self.plan: RefitPlan = build_refit_plan(cfg, self.world, self.tp_train, tp_serve)
+        self.layout, self.arena_numel = serving_param_layout(cfg, tp_serve)
+        p0 = next(train_model.parameters())
+        self.dtype, self.device = p0.dtype, p0.device
+        self.native = self.device.type == "cuda"
+        self._sym = None
+        if self.native and self.world > 1:
+            from rl_b200.parallel.symmetric import SymmetricBuffer
+
+            self._sym = SymmetricBuffer(self.arena_numel * p0.element_size(), group)
+            self.arena = self._sym.tensor(self.dtype, self.arena_numel)
+            self._arena_ptrs = list(self._sym.peer_ptrs)
+        else:
+            self.arena = torch.zeros(self.arena_numel, dtype=self.dtype, device=self.device)
+            self._arena_ptrs = [self.arena.data_ptr()] * max(1, self.world)
+        self.serving_model = build_serving_model(cfg, tp_serve, self.rank, self.arena, serve_group, serve_comm)
+        self._descs = self._work = None
+        self._num_work = 0
+        self.last_bytes = 0
+
+    # ------------------------------------------------------------------ native path
+    def _prepare(self) -> None:
+        from rl_b200.ops import lib as _L
+
+        lib = _L.lib()
+        params = dict(self.train_model.named_parameters())
+        es = next(iter(params.values())).element_size()
+        descs, work = [], []
+        total = 0
+        for op in self.plan.ops_from(self.rank):
+            src = params[op.src_param].data_ptr() + op.src_offset * es
+            dst = self._arena_ptrs[op.dst_rank] + (self.layout[op.dst_param][0] + op.dst_offset) * es
+            row_bytes = op.row_elems * es
+            vec_ok = row_bytes % 16 == 0 and src % 16 == 0 and dst % 16 == 0 and (op.src_pitch * es) % 16 == 0 and (op.dst_pitch * es) % 16 == 0
+            rows, sp, dp = op.rows, op.src_pitch * es, op.dst_pitch * es
+            if rows > 1 and sp == row_bytes and dp == row_bytes:  # contiguous on both sides: one long row
+                row_bytes, rows = row_bytes * rows, 1
+            if row_bytes >= 2**31:
+                split = -(-row_bytes // 2**30)
+                assert rows == 1 and row_bytes % (16 * split) == 0
+                parts = [(src + i * (row_bytes // split), dst + i * (row_bytes // split), row_bytes // split) for i in range(split)]
+            else:
+                parts = [(src, dst, row_bytes)]
+            for s_, d_, rb in parts:
+                di = len(descs)
+                descs.append(struct.pack("<QQqqii", s_, d_, sp, dp, rows, rb))
+                n = rows * (rb // 16) if vec_ok else rows * (rb // 2)
+                for f in range(0, n, WORK_VECS):
+                    work.append(struct.pack("<iiii", di, f, min(WORK_VECS, n - f), 0 if vec_ok else 1))
+                total += rows * rb
+        assert lib.rlb_refit_desc_bytes() == 40 and lib.rlb_refit_work_bytes() == 16
+        self._descs = torch.frombuffer(bytearray(b"".join(descs) or b"\0" * 40), dtype=torch.uint8).to(self.device)
+        self._work = torch.frombuffer(bytearray(b"".join(work) or b"\0" * 16), dtype=torch.uint8).to(self.device)
+        self._num_work = len(work)
+        self.last_bytes = total
+        lib.rlb_refit_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        lib.rlb_refit_copy.restype = C.c_int
+
+    def sync_weights(self, timer=None) -> None:
+        """Pushes this rank's pieces into every engine arena; returns after all ranks' pushes are complete."""
+        if not self.native:
+            return self.twin_sync()
+        from rl_b200.ops import lib as _L
+
+        if self._descs is None:
+            self._prepare()
+        if self.world > 1:
+            dist.barrier(group=self.group)  # no engine still reads its arena
+        rc = _L.lib().rlb_refit_copy(self._descs.data_ptr(), self._work.data_ptr(), self._num_work, 0, torch.cuda.current_stream().cuda_stream)
+        _L.Counters.launches += 1
+        if rc:
+            raise RuntimeError(f"rlb_refit_copy failed with code {rc}")
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # every peer's stores into this arena have landed
+
+    # ------------------------------------------------------------------ collective twin / CPU path
+    @torch.no_grad()
+    def twin_sync(self) -> None:
+        from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+
+        full = {n: t.detach() for n, t in iter_hf_tensors(self.train_model)}
+        load_hf_tensors(self.serving_model, full.get)
+
+    def close(self) -> None:
+        if self._sym is not None:
+            self._sym.close()

@@ -191,3 +191,47 @@ def _tp_train_worker(rank, world, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tensor_parallel_worker_fused_vs_nccl(native_lib):
     mp.spawn(_tp_train_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _refit_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.transformer import PackedBatch, build_model
+    from rl_b200.parallel.tensor import TP
+    from rl_b200.refit.synchronizer import WeightSynchronizer
+
+    mc = ModelConfig(model_type="qwen3", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128, qk_norm=True, tie_word_embeddings=False)
+    dev = f"cuda:{rank}"
+    for tp_train, tp_serve in ((2, 1), (1, 2)):
+        tp = TP(None, rank % tp_train, tp_train)
+        train = build_model(mc, device=dev, dtype=torch.bfloat16, seed=21, tp=tp)
+        ws = WeightSynchronizer(train, mc, tp_serve)
+        for it in range(2):
+            with torch.no_grad():
+                for p in train.parameters():
+                    p.mul_(1.0 + 0.25 * it)
+            ws.sync_weights()
+            got = ws.arena.clone()
+            ws.arena.zero_()
+            ws.twin_sync()
+            torch.cuda.synchronize()
+            assert torch.equal(got, ws.arena), (tp_train, tp_serve, it)
+        sent, recv = ws.plan.bytes_over_link(rank)
+        assert (sent == 0) == (tp_train == 1)
+        if tp_serve == 1:  # the serving model is a complete model: it runs on its own
+            ids = torch.randint(0, 4096, (2, 32), device=dev)
+            b = PackedBatch.from_padded(ids, torch.tensor([32, 20], device=dev))
+            b.input_ids = b.input_ids.to(torch.int32)
+            z = ws.serving_model.logits(b)
+            assert torch.isfinite(z).all()
+        dist.barrier()
+        ws.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_refit_reshard_kernel_matches_collective_twin(native_lib):
+    mp.spawn(_refit_worker, args=(2, _free_port()), nprocs=2, join=True)

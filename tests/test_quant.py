@@ -1,0 +1,71 @@
+"""FP8 block-wise and MXFP8 quantisation: CPU oracle properties and the native kernels against the oracle."""
+
+import pytest
+import torch
+
+from rl_b200.ops.quant import (FP8_MAX, dequantize_fp8_blockwise, dequantize_mxfp8, quantize_fp8_blockwise, quantize_fp8_blockwise_ref,
+                               quantize_mxfp8, quantize_mxfp8_ref)
+
+
+def _w(R, C, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(R, C, generator=g) * torch.rand(R, 1, generator=g) * 3
+    w[0, :5] = 0
+    return w.to(torch.bfloat16).to(device)
+
+
+@pytest.mark.parametrize("pow2", [False, True])
+def test_blockwise_oracle_properties(pow2):
+    w = _w(300, 200)  # ragged in both dimensions: 3 x 2 blocks
+    q, ds = quantize_fp8_blockwise_ref(w, 128, pow2)
+    assert q.shape == w.shape and q.dtype == torch.float8_e4m3fn and ds.shape == (3, 2)
+    back = dequantize_fp8_blockwise(q, ds).float()
+    rel = (back - w.float()).abs().max() / w.float().abs().max()
+    assert rel < 0.07  # e4m3 has 3 mantissa bits: relative step 2^-4 at the top of a block's range
+    # full blocks use the whole fp8 range: max |q| is 448 without pow2 scales, within a factor 2 with them
+    qmax = q.float()[:128, :128].abs().max()
+    assert qmax == FP8_MAX if not pow2 else FP8_MAX / 2 < qmax <= FP8_MAX
+    if pow2:
+        assert torch.all(torch.log2(ds) == torch.log2(ds).round())
+    # the ragged corner block is padded with the last element, which takes part in its amax
+    w2 = w.clone()
+    w2[-1, -1] = 1000.0
+    _, ds2 = quantize_fp8_blockwise_ref(w2, 128, pow2)
+    assert ds2[2, 0] > ds[2, 0] and ds2[0, 1] > ds[0, 1] and ds2[0, 0] == ds[0, 0]
+
+
+def test_mxfp8_oracle_properties():
+    w = _w(64, 256, seed=1)
+    q, e = quantize_mxfp8_ref(w)
+    assert e.dtype == torch.uint8 and e.shape == (64, 8)
+    assert q.float().abs().max() <= FP8_MAX
+    back = dequantize_mxfp8(q, e).float()
+    assert ((back - w.float()).abs() <= 0.0625 * w.float().abs().reshape(64, 8, 32).amax(-1).repeat_interleave(32, 1) + 1e-9).all()
+    assert e[0, 0] != 0 and quantize_mxfp8_ref(torch.zeros(1, 32, dtype=torch.bfloat16))[1].item() == 0  # all-zero group -> byte 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(256, 384), (300, 200), (4096, 1536)])
+@pytest.mark.parametrize("pow2", [False, True])
+def test_native_blockwise_matches_oracle(native_lib, shape, pow2):
+    w = _w(*shape, seed=2, device="cuda")
+    q, ds = quantize_fp8_blockwise(w, pow2)
+    qr, dsr = quantize_fp8_blockwise_ref(w, 128, pow2)
+    torch.cuda.synchronize()
+    assert torch.allclose(ds, dsr, rtol=1e-6, atol=0)
+    diff = (q.float() - qr.float()).abs()
+    # identical up to a one-code difference where x * scale lands on a rounding tie computed in a different order
+    assert (diff > 0).float().mean() < 1e-3 and (diff <= q.float().abs() * 0.13 + 2 ** -9).all()
+    assert torch.equal(dequantize_fp8_blockwise(q, ds), (q.float() * dsr.repeat_interleave(128, 0)[: shape[0]].repeat_interleave(128, 1)[:, : shape[1]]).to(torch.bfloat16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(64, 256), (2048, 768), (777, 2048)])
+def test_native_mxfp8_matches_oracle(native_lib, shape):
+    w = _w(*shape, seed=3, device="cuda")
+    q, e = quantize_mxfp8(w)
+    qr, er = quantize_mxfp8_ref(w)
+    torch.cuda.synchronize()
+    assert torch.equal(e, er)
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    assert torch.equal(dequantize_mxfp8(q, e), dequantize_mxfp8(qr.cpu(), er.cpu()).cuda())

@@ -536,17 +536,27 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
     }
-    for (int s = 0; s < t.world; ++s) {
-      uint4 pv[U];
+    // all slots of all U vectors are requested before the first one is consumed (up to 32 loads in flight per thread)
+    uint4 pv[MAX_TP][U];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        pv[u] = live[u] ? __ldcg(reinterpret_cast<const uint4*>(mine + ((static_cast<long long>(s) * rows_out + row[u]) * N + c[u]) * 2))
-                        : make_uint4(0, 0, 0, 0);
+    for (int s = 0; s < MAX_TP; ++s) {
+      if (s < t.world) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const float2 a0 = unpack_bf16x2(pv[u].x), a1 = unpack_bf16x2(pv[u].y), a2 = unpack_bf16x2(pv[u].z), a3 = unpack_bf16x2(pv[u].w);
-        acc[u][0] += a0.x; acc[u][1] += a0.y; acc[u][2] += a1.x; acc[u][3] += a1.y;
-        acc[u][4] += a2.x; acc[u][5] += a2.y; acc[u][6] += a3.x; acc[u][7] += a3.y;
+        for (int u = 0; u < U; ++u)
+          pv[s][u] = live[u] ? __ldcg(reinterpret_cast<const uint4*>(mine + ((static_cast<long long>(s) * rows_out + row[u]) * N + c[u]) * 2))
+                             : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < MAX_TP; ++s) {
+      if (s < t.world) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float2 a0 = unpack_bf16x2(pv[s][u].x), a1 = unpack_bf16x2(pv[s][u].y), a2 = unpack_bf16x2(pv[s][u].z),
+                       a3 = unpack_bf16x2(pv[s][u].w);
+          acc[u][0] += a0.x; acc[u][1] += a0.y; acc[u][2] += a1.x; acc[u][3] += a1.y;
+          acc[u][4] += a2.x; acc[u][5] += a2.y; acc[u][6] += a3.x; acc[u][7] += a3.y;
+        }
       }
     }
 #pragma unroll

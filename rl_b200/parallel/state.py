@@ -114,6 +114,17 @@ def init_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, sequence_p
                         mine = g
                         st.ep_rank = ranks.index(rank)
         st.ep_group = mine
+    if pp > 1:
+        # first + last stage of every pipeline: they share the tied embedding table and all-reduce its gradient
+        mine = None
+        for d in range(dp):
+            for c_ in range(cp):
+                for t in range(tp):
+                    ranks = sorted({ns.get_ranks(pp=0, dp=d, cp=c_, tp=t), ns.get_ranks(pp=pp - 1, dp=d, cp=c_, tp=t)})
+                    g = dist.new_group(ranks=ranks, backend=backend)
+                    if rank in ranks:
+                        mine = g
+        st.extras["embed_group"] = mine
     if tp * pp * cp > 1 and tp * pp * cp < world:
         mine = None
         for d in range(dp):

@@ -70,8 +70,10 @@ class ShardedAdamW:
         self._replicated: list[tuple[int, int]] = []   # shard-relative ranges replicated over the tensor-parallel group
         self._replicas = 1
         self._norm_groups: list = []
+        self._excluded: list[tuple[int, int]] = []
 
-    def set_model_parallel(self, replicated_runs: list[tuple[int, int]], replicas: int, norm_groups: list) -> None:
+    def set_model_parallel(self, replicated_runs: list[tuple[int, int]], replicas: int, norm_groups: list,
+                           excluded_runs: Optional[list[tuple[int, int]]] = None) -> None:
         """``replicated_runs``: flat ranges whose parameters every one of ``replicas`` tensor-parallel ranks holds in full
         (their squared gradient norm must count once); ``norm_groups``: process groups over which the squared norm is
         summed besides the optimizer's own (tensor / pipeline parallel)."""
@@ -79,6 +81,9 @@ class ShardedAdamW:
         self._norm_groups = list(norm_groups)
         self._replicated = [(max(a, self.lo) - self.lo, min(b, self.hi) - self.lo) for a, b in replicated_runs
                             if min(b, self.hi) > max(a, self.lo)]
+        # ranges whose norm another rank of a norm group already counts (second copy of a tied table)
+        self._excluded = [(max(a, self.lo) - self.lo, min(b, self.hi) - self.lo) for a, b in (excluded_runs or [])
+                          if min(b, self.hi) > max(a, self.lo)]
 
     # ------------------------------------------------------------------ step
     def zero_grad(self) -> None:
@@ -128,6 +133,11 @@ class ShardedAdamW:
             for a, b in self._replicated:
                 F.sumsq_(gs[a:b], rep)
             self._sumsq.sub_(rep * (1.0 - 1.0 / self._replicas))
+        if self._excluded:
+            exc = torch.zeros_like(self._sumsq)
+            for a, b in self._excluded:
+                F.sumsq_(gs[a:b], exc)
+            self._sumsq.sub_(exc * (1.0 / self._replicas if any(a <= x < b for x, _ in self._excluded for a, b in self._replicated) else 1.0))
         if self.world > 1:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=self.group)
         for g in self._norm_groups:

@@ -182,6 +182,13 @@ class PolicyWorker:
                                              fused_comm=fused_comm)
             self._configure_model_parallel_grads()
             self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
+        self.pipeline = None
+        if st.pp > 1:
+            from rl_b200.parallel.pipeline import PipelineRunner
+
+            div = self.tp.world if (self.tp.world > 1 and self.tp.sequence_parallel) else 1
+            self.pipeline = PipelineRunner(self.model, st.pp_group, st.pp_rank, st.pp, model_cfg.hidden_size, dtype, self.device,
+                                           rows_of=lambda item: int(item[0].input_ids.numel()) // div)
         self.generation = None
         self.temperature = 1.0
         gen_cfg = cfg.get("generation") or {}
@@ -207,18 +214,31 @@ class PolicyWorker:
                 else:
                     runs.append([o, end])
             self._replicated_runs = [(a, min(b, self.flat.padded)) for a, b in runs]
+        # tied embeddings under pipeline parallelism: the last stage holds a second copy of the table (for the output
+        # projection); its gradient is all-reduced with the first stage's and its norm counted once
+        self._tied_pp = bool(st.pp > 1 and self.model.embed_tokens is not None and self.model.lm_head is None
+                             and not self.model_cfg.value_head and self.model_cfg.tie_word_embeddings)
+        excluded = []
+        if self._tied_pp and self.model.last_stage and not self.model.first_stage:
+            for n, o, k, _ in self.flat.named_slices():
+                if n == "embed_tokens":
+                    excluded.append((o, o + k))
         if self.optimizer is not None:
             groups = [g for g in (st.tp_group if st.tp > 1 else None, st.pp_group if st.pp > 1 else None) if g is not None]
-            self.optimizer.set_model_parallel(self._replicated_runs, st.tp, groups)
+            self.optimizer.set_model_parallel(self._replicated_runs, st.tp, groups, excluded)
 
     def _sync_replicated_grads(self) -> None:
         """Sequence parallelism: every tp rank saw only its rows, so gradients of replicated parameters are partial."""
         st = self.pstate
-        if st.tp == 1 or not st.sequence_parallel or self.flat.grad is None:
+        if self.flat.grad is None:
             return
-        self.flat.fold_autograd_grads()
-        for a, b in self._replicated_runs:
-            dist.all_reduce(self.flat.grad[a:b], group=st.tp_group)
+        if st.tp > 1 and st.sequence_parallel:
+            self.flat.fold_autograd_grads()
+            for a, b in self._replicated_runs:
+                dist.all_reduce(self.flat.grad[a:b], group=st.tp_group)
+        if getattr(self, "_tied_pp", False) and (self.model.first_stage or self.model.last_stage):
+            self.flat.fold_autograd_grads()
+            dist.all_reduce(self.model.embed_tokens.main_grad, group=st.extras["embed_group"])
 
     # ------------------------------------------------------------------ generation (colocated, shared weights)
     def build_generation(self, gen_cfg: Optional[dict] = None):
@@ -310,6 +330,18 @@ class PolicyWorker:
         n, S = data["input_ids"].shape
         out = torch.zeros((n, S), dtype=torch.float32)
         mbs = micro_batch_size or self.cfg["logprob_batch_size"]
+        if self.pipeline is not None:
+            items = [(*self._pack(mb), idx) for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob"))]
+
+            def stage(item, h_in):
+                if self.model.last_stage:
+                    return self.model.next_token_logprobs(item[0], self.temperature, h_in=h_in)[0]
+                return self.model.hidden_states(item[0], h_in)
+
+            lps = self.pipeline.forward_only(items, stage, lambda item: (int(item[0].input_ids.numel()),))
+            for (batch, Smb, idx), lp in zip(items, lps):
+                out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
+            return out
         for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob")):
             batch, Smb = self._pack(mb)
             lp, _ = self.model.next_token_logprobs(batch, self.temperature)
@@ -355,21 +387,23 @@ class PolicyWorker:
         return BatchedDataDict({"values": vals, "scores": vals.gather(1, last[:, None])[:, 0]})
 
     # ------------------------------------------------------------------ training
-    def _loss_inputs(self, loss_fn, batch: PackedBatch, S: int, mb: BatchedDataDict) -> dict:
+    def _loss_inputs(self, loss_fn, batch: PackedBatch, S: int, mb: BatchedDataDict, h_in=None) -> dict:
+        """Model outputs in the form the loss wants. ``h_in``: the residual stream from the previous pipeline stage."""
         it = getattr(loss_fn, "input_type", LossInputType.LOGPROB)
         if it == LossInputType.LOGPROB:
-            lp, _ = self.model.next_token_logprobs(batch, self.temperature)
+            lp, _ = self.model.next_token_logprobs(batch, self.temperature, h_in=h_in)
             return {"next_token_logprobs": batch.unpack(lp, S)[:, 1:]}
         if it == LossInputType.VALUE:
-            return {"values": batch.unpack(self.model.values(batch), S)}
+            return {"values": batch.unpack(self.model.values(batch, h_in), S)}
         if it == LossInputType.LOGIT:
             if self.model_cfg.value_head:  # reward model: score at the last token of each sequence
-                v = self.model.values(batch)
-                last = (batch.cu_seqlens[1:].long() - 1).clamp(min=0)
+                v = self.model.values(batch, h_in)
+                ncu = batch.cu_seqlens[:-1] if batch.num_real_tokens is not None else batch.cu_seqlens
+                last = (ncu[1:].long() - 1).clamp(min=0)
                 return {"logits": v[last]}
-            return {"logits": batch.unpack(self.model.logits(batch), S)}
+            return {"logits": batch.unpack(self.model.logits(batch, h_in), S)}
         if it == LossInputType.DISTILLATION:
-            z = self.model.logits(batch) / self.temperature
+            z = self.model.logits(batch, h_in) / self.temperature
             logp = torch.log_softmax(batch.unpack(z, S)[:, :-1], dim=-1)
             ti = mb["teacher_topk_indices"].to(self.device)
             s_topk = logp[:, : ti.shape[1]].gather(-1, ti)
@@ -403,7 +437,11 @@ class PolicyWorker:
                 self.optimizer.zero_grad()
             gb_loss = torch.zeros((), device=self.device)
             budget = None if getattr(loss_fn, "requires_pairs", False) else self._token_budget("train")
-            for mb, _ in self._microbatches(gb, mbs, budget):
+            if self.pipeline is not None:
+                gb_loss, mbm, ntok = self._pipeline_global_batch(gb, mbs, budget, loss_fn, eval_mode, global_valid_seqs, global_valid_toks)
+                all_mb_metrics.extend(mbm)
+                total_tokens += ntok
+            for mb, _ in (self._microbatches(gb, mbs, budget) if self.pipeline is None else ()):
                 batch, S = self._pack(mb)
                 mb_dev = BatchedDataDict({k: (to_device(v, self.device) if isinstance(v, torch.Tensor) else v)
                                           for k, v in mb.items() if k != "input_ids"})
@@ -447,6 +485,47 @@ class PolicyWorker:
             "train_time_s": elapsed,
             "train_tokens": total_tokens,
         }
+
+    def _pipeline_global_batch(self, gb, mbs, budget, loss_fn, eval_mode, global_valid_seqs, global_valid_toks):
+        """One accumulation window through the pipeline schedule. Losses and metrics live on the last stage and are
+        shared with the other stages afterwards so that every rank reports the same numbers."""
+        items, ntok = [], 0
+        for mb, _ in self._microbatches(gb, mbs, budget):
+            batch, S = self._pack(mb)
+            mb_dev = BatchedDataDict({k: (to_device(v, self.device) if isinstance(v, torch.Tensor) else v)
+                                      for k, v in mb.items() if k != "input_ids"})
+            mb_dev.truncate_tensors(1, S)
+            items.append((batch, S, mb_dev))
+            ntok += int(batch.input_ids.numel())
+        collected: list[dict] = []
+
+        def stage(item, h_in):
+            batch, S, mb_dev = item
+            if not self.model.last_stage:
+                return self.model.hidden_states(batch, h_in)
+            inputs = self._loss_inputs(loss_fn, batch, S, mb_dev, h_in)
+            loss, metrics = loss_fn(data=mb_dev, global_valid_seqs=global_valid_seqs, global_valid_toks=global_valid_toks, **inputs)
+            collected.append(dict(metrics))
+            return loss
+
+        if eval_mode:
+            with torch.no_grad():
+                outs = self.pipeline.forward_only(items, stage, lambda item: (), torch.float32)
+            losses = outs
+        else:
+            losses = self.pipeline.train_step(items, stage)
+        st = self.pstate
+        box = [collected, [float(x) for x in losses]] if self.model.last_stage else [None, None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(st.pp_group, st.pp - 1), group=st.pp_group)
+        collected, loss_vals = box
+        mbm = []
+        for m in collected:
+            m = dict(m)
+            m["lr"] = self.optimizer.lr if self.optimizer else 0.0
+            m["global_valid_seqs"] = float(global_valid_seqs)
+            m["global_valid_toks"] = float(global_valid_toks)
+            mbm.append(m)
+        return torch.tensor(sum(loss_vals), device=self.device, dtype=torch.float32), mbm, ntok
 
     # ------------------------------------------------------------------ refit hooks
     def prepare_refit_info(self) -> dict:

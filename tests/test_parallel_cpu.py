@@ -152,3 +152,57 @@ def test_expert_parallel_matches_local_experts():
     out = _spawn(_ep_worker, 2)
     for r, m in out.items():
         assert m["lp"] < 2e-4 and m["g"] < 2e-3, (r, m)
+
+
+def _worker_cfg(**par):
+    return dict(precision="float32", train_global_batch_size=4, train_micro_batch_size=1, max_total_sequence_length=64, max_grad_norm=1.0,
+                logprob_batch_size=2, optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.0)), parallel=par)
+
+
+def _train_data():
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+    g = torch.Generator().manual_seed(0)
+    return BatchedDataDict(input_ids=torch.randint(0, 2048, (4, 24), generator=g), input_lengths=torch.tensor([24, 17, 9, 20]),
+                           token_mask=torch.ones(4, 24), sample_mask=torch.ones(4))
+
+
+def _pp_worker(rank, world, tied, tp):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.models.config import preset
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied)
+    w = PolicyWorker(_worker_cfg(pipeline_parallel_size=world // tp, tensor_parallel_size=tp), model_cfg=mc, init_reference_model=False, seed=4)
+    data = _train_data()
+    lp = w.get_logprobs(data)["logprobs"]
+    outs = [w.train(data, NLLLossFn(), gbs=4, mbs=1) for _ in range(2)]
+    lp2 = w.get_logprobs(data)["logprobs"]
+    return dict(lp=lp.sum().item(), lp2=lp2.sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
+
+
+def _single_reference(tied):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.models.config import preset
+    from rl_b200.parallel.state import reset_parallel
+    from rl_b200.policy.worker import PolicyWorker
+
+    reset_parallel()
+    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied)
+    w = PolicyWorker(_worker_cfg(), model_cfg=mc, init_reference_model=False, seed=4)
+    data = _train_data()
+    lp = w.get_logprobs(data)["logprobs"]
+    outs = [w.train(data, NLLLossFn(), gbs=4, mbs=1) for _ in range(2)]
+    lp2 = w.get_logprobs(data)["logprobs"]
+    return dict(lp=lp.sum().item(), lp2=lp2.sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
+
+
+@pytest.mark.parametrize("world,tp,tied", [(2, 1, False), (2, 1, True), (4, 2, True)])
+def test_pipeline_parallel_worker_matches_single_rank(world, tp, tied):
+    ref = _single_reference(tied)
+    out = _spawn(_pp_worker, world, tied, tp)
+    for r, m in out.items():
+        assert m["lp"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)
+        assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
+        assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
+        assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)

@@ -18,7 +18,10 @@ constexpr float FP8_MAX = 448.f;
 
 __device__ __forceinline__ float pow2_ceil_descale(float descale, unsigned char* e8m0) {
   // exponent = clamp(ceil(log2(descale)), -127, 127) + 127 as a byte; byte 0 stands for scale 1 (all-zero block)
-  float e = ceilf(log2f(descale));
+  // ceil(log2(x)) from the float's own exponent: exact, unlike log2f near powers of two
+  int ex = 0;
+  const float mant = frexpf(descale, &ex);  // descale = mant * 2^ex, mant in [0.5, 1)
+  float e = static_cast<float>(mant == 0.5f ? ex - 1 : ex);
   e = fminf(fmaxf(e, -127.f), 127.f) + 127.f;
   if (!(descale > 0.f)) e = 0.f;
   const unsigned char b = static_cast<unsigned char>(e);

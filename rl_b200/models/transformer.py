@@ -101,10 +101,12 @@ class Attention(nn.Module):
     """Fused-QKV attention. With tensor parallelism this rank holds ``Hq/tp`` query and ``Hkv/tp`` key/value heads:
     ``qkv_proj`` is column-parallel (rows = local q, k, v heads), ``o_proj`` row-parallel."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, cp=None):
         super().__init__()
         self.cfg = cfg
         self.tp = tp or TP()
+        self.cp = cp if (cp is not None and cp.world > 1) else None
+        assert self.cp is None or self.tp.world == 1, "context parallelism and tensor parallelism are not combined"
         w = self.tp.world
         assert cfg.num_attention_heads % w == 0 and cfg.num_key_value_heads % w == 0, "heads must divide by the tensor-parallel size"
         self.hq, self.hkv = cfg.num_attention_heads // w, cfg.num_key_value_heads // w
@@ -129,6 +131,13 @@ class Attention(nn.Module):
 
     def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen):
         c = self.cfg
+        if self.cp is not None:
+            from rl_b200.parallel.context import cp_attention_varlen
+
+            r0, r1 = self.cp.local_rows(positions.numel())
+            qkv = self.project_qkv(x, positions[r0:r1], inv_freq)
+            a = cp_attention_varlen(qkv, cu_seqlens, self.cp, self.hq, self.hkv, c.head_dim)
+            return F.linear(a, self.o_proj, None, residual)
         qkv = self.project_qkv(x, positions, inv_freq)
         a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim)
         return row_linear(a, self.o_proj, residual, self.tp)
@@ -150,12 +159,12 @@ class DenseMLP(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None):
         super().__init__()
         self.cfg = cfg
         d = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device, tp)
+        self.self_attn = Attention(cfg, dtype, device, tp, cp)
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if cfg.is_moe:
             from .moe import MoEMLP
@@ -232,13 +241,14 @@ class CausalLM(nn.Module):
 
     def __init__(self, cfg: ModelConfig, dtype: Optional[torch.dtype] = None, device="cpu", init: bool = True,
                  seed: int = 0, activation_checkpointing: bool = False, tp: Optional[TP] = None, ep=None,
-                 pp_rank: int = 0, pp_size: int = 1):
+                 pp_rank: int = 0, pp_size: int = 1, cp=None):
         super().__init__()
         self.cfg = cfg
         dtype = dtype or _dtype_of(cfg.torch_dtype)
         self.dtype = dtype
         self.tp = tp or TP()
         self.ep = ep
+        self.cp = cp if (cp is not None and cp.world > 1) else None
         self.pp_rank, self.pp_size = pp_rank, pp_size
         L = cfg.num_hidden_layers
         per = -(-L // pp_size)
@@ -255,7 +265,7 @@ class CausalLM(nn.Module):
             self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
         else:
             self.embed_tokens = None
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep) for _ in range(n_local)])
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp) for _ in range(n_local)])
         self.lm_head = None
         if self.last_stage:
             self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
@@ -337,6 +347,9 @@ class CausalLM(nn.Module):
             # gradient is a partial sum that the worker all-reduces over the tensor-parallel group
             rows = batch.input_ids.numel() // self.tp.world
             return F.embedding(batch.input_ids[self.tp.rank * rows : (self.tp.rank + 1) * rows], self.embed_tokens)
+        if self.cp is not None:
+            r0, r1 = self.cp.local_rows(batch.input_ids.numel())
+            return F.embedding(batch.input_ids[r0:r1], self.embed_tokens)
         return F.embedding(batch.input_ids, self.embed_tokens)
 
     def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
@@ -373,7 +386,16 @@ class CausalLM(nn.Module):
         is_start[starts[starts < T]] = True
         # hidden state t predicts token t+1: every row is scored against the next token, then shifted by one
         targets = torch.roll(ids, -1)
-        if self.tp.world == 1:
+        if self.cp is not None:
+            # local rows are scored locally; the [T]-sized results are gathered (backward: each rank keeps its rows' share)
+            from rl_b200.parallel.tensor import TP as _TP
+
+            r0, r1 = self.cp.local_rows(T)
+            lp_l, ent_l = F.lm_head_logprobs(h, self.output_weight, targets[r0:r1], temperature, want_entropy)
+            rows_tp = _TP(self.cp.group, self.cp.rank, self.cp.world)
+            lp_rows = gather_rows(lp_l, rows_tp)
+            ent_rows = gather_rows(ent_l, rows_tp) if want_entropy else None
+        elif self.tp.world == 1:
             lp_rows, ent_rows = F.lm_head_logprobs(h, self.output_weight, targets, temperature, want_entropy)
         else:
             from rl_b200.parallel.vocab import vocab_parallel_logprobs
@@ -398,11 +420,13 @@ class CausalLM(nn.Module):
         """Scalar head output per token [T] (critic / reward model)."""
         h = self.hidden_states(batch, h_in)
         v = F.linear(h, self.score).float()[:, 0]
+        if self.cp is not None:
+            return gather_rows(v, TP(self.cp.group, self.cp.rank, self.cp.world))
         return gather_rows(v, self.tp) if self.tp.sequence_parallel else v
 
 
 def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
                 activation_checkpointing: bool = False, init: bool = True, tp: Optional[TP] = None, ep=None,
-                pp_rank: int = 0, pp_size: int = 1) -> CausalLM:
+                pp_rank: int = 0, pp_size: int = 1, cp=None) -> CausalLM:
     return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
-                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size)
+                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp)

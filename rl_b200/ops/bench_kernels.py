@@ -109,11 +109,16 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--which", default="gemm,mem")
     ap.add_argument("--json", default="")
+    ap.add_argument("--gemm-shape", default="", help="M,N,K: time only this GEMM shape (small case for profiler captures)")
     a = ap.parse_args(argv)
     out = []
     which = a.which.split(",")
     if "gemm" in which:
-        out += bench_gemm()
+        shapes = None
+        if a.gemm_shape:
+            M, N, K = (int(x) for x in a.gemm_shape.split(","))
+            shapes = [(M, N, K, False, False)]
+        out += bench_gemm(shapes)
     if "mem" in which:
         out += bench_memory_bound()
     if a.json:

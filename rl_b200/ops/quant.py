@@ -24,7 +24,8 @@ register("rlb_dequant_mxfp8", [P, L, P, L, P, L, I, I, P])
 
 
 def _pow2_descale(descale: torch.Tensor):
-    e = torch.ceil(torch.log2(descale)).clamp(-127, 127) + 127
+    mant, ex = torch.frexp(descale)  # exact ceil(log2(x)): x = mant * 2^ex with mant in [0.5, 1)
+    e = torch.where(mant == 0.5, ex - 1, ex).float().clamp(-127, 127) + 127
     e = torch.where(descale > 0, e, torch.zeros_like(e)).to(torch.uint8)
     ds = torch.where(e == 0, torch.ones_like(descale), torch.exp2(e.float() - 127))
     return ds, e

@@ -145,7 +145,10 @@ class PolicyWorker:
             except Exception as e:  # no peer access between these GPUs: NCCL collectives around the plain GEMM
                 print(f"[policy] fused tensor-parallel kernels unavailable ({type(e).__name__}: {e}); using NCCL")
         self.tp.comm = st.tp_comm
-        mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp)
+        from rl_b200.parallel.context import CP
+
+        self.cp = CP.from_state(st)
+        mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp, cp=self.cp)
         if weights_path:
             from rl_b200.models.hf_io import load_pretrained
 
@@ -321,6 +324,8 @@ class PolicyWorker:
             batch.input_ids = batch.input_ids.to(torch.int32)
         if self.tp.world > 1 and self.tp.sequence_parallel:
             batch = batch.pad_to_multiple(8 * self.tp.world)
+        elif self.cp.world > 1:
+            batch = batch.pad_to_multiple(8 * self.cp.world)
         return batch, ids.shape[1]
 
     # ------------------------------------------------------------------ inference passes
@@ -418,7 +423,8 @@ class PolicyWorker:
         assert self.optimizer is not None or eval_mode
         gbs = gbs or self.cfg["train_global_batch_size"]
         mbs = mbs or self.cfg["train_micro_batch_size"]
-        local_gbs = max(1, gbs // self.world)
+        cpw = self.cp.world  # context-parallel ranks of one replica see the same samples
+        local_gbs = max(1, gbs // max(1, self.world // cpw))
         n_local = data.size
         num_gb = max(1, n_local // local_gbs)
         self.model.train(not eval_mode)
@@ -432,6 +438,7 @@ class PolicyWorker:
             counts = torch.stack([sm.sum(), (tm * sm[:, None]).sum() if tm is not None else sm.sum()]).to(self.device)
             if self.world > 1:
                 dist.all_reduce(counts, group=self.dp_group)
+                counts = counts / cpw
             global_valid_seqs, global_valid_toks = counts[0], counts[1]
             if not eval_mode:
                 self.optimizer.zero_grad()
@@ -465,6 +472,7 @@ class PolicyWorker:
                 grad_norms.append(gn)
             if self.world > 1:
                 dist.all_reduce(gb_loss, group=self.dp_group)
+                gb_loss = gb_loss / cpw
             losses.append(gb_loss)
         if not eval_mode and self.scheduler is not None:
             self.scheduler.step()  # once per train() call

@@ -206,3 +206,27 @@ def test_pipeline_parallel_worker_matches_single_rank(world, tp, tied):
         assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
         assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
         assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)
+
+
+def _cp_worker(rank, world):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.models.config import preset
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    w = PolicyWorker(_worker_cfg(context_parallel_size=world), model_cfg=mc, init_reference_model=False, seed=4)
+    data = _train_data()
+    lp = w.get_logprobs(data)["logprobs"]
+    outs = [w.train(data, NLLLossFn(), gbs=4, mbs=2) for _ in range(2)]
+    lp2 = w.get_logprobs(data)["logprobs"]
+    return dict(lp=lp.sum().item(), lp2=lp2.sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
+
+
+def test_context_parallel_worker_matches_single_rank():
+    ref = _single_reference(False)
+    out = _spawn(_cp_worker, 2)
+    for r, m in out.items():
+        assert m["lp"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)
+        assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
+        assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
+        assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)

@@ -28,8 +28,17 @@ def _rank_world(group=None):
 def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
     from rl_b200.models.hf_io import iter_hf_tensors, save_pretrained
 
-    rank, world = _rank_world(worker.dp_group)
+    from rl_b200.models.hf_io import save_roles
+    from rl_b200.parallel.state import get_state
+
+    rank, world = (worker.rank, worker.world)
     fmt = (fmt or "safetensors").lower()
+    st = get_state()
+    if st.tp * st.pp * st.ep * st.cp > 1:
+        # model-parallel layouts always write HF safetensors (one file set per pipeline stage / expert-parallel rank)
+        if save_roles(st)[0]:
+            save_pretrained(worker.model, path)
+        return
     if fmt == "dcp":
         import torch.distributed.checkpoint as dcp
 
@@ -63,7 +72,7 @@ def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
 def load_weights(worker, path: str) -> None:
     from rl_b200.models.hf_io import _SafetensorsDir, load_hf_tensors
 
-    rank, world = _rank_world(worker.dp_group)
+    rank, world = (worker.rank, worker.world)
     if os.path.exists(os.path.join(path, "flat_layout.json")):
         import torch.distributed.checkpoint as dcp
 
@@ -85,19 +94,26 @@ def load_weights(worker, path: str) -> None:
     load_hf_tensors(worker.model, reader.get)
 
 
+def _global_rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
 def save_optimizer_shard(worker, path: str) -> None:
-    rank, _ = _rank_world(worker.dp_group)
+    """One file per rank (named by the global rank: optimizer shards are tied to the whole parallel layout)."""
     os.makedirs(path, exist_ok=True)
     sd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in worker.optimizer.state_dict().items()}
     sd["scheduler"] = worker.scheduler.state_dict() if worker.scheduler is not None else None
-    torch.save(sd, os.path.join(path, f"rank_{rank}.pt"))
+    if getattr(worker, "optimizer_e", None) is not None:
+        sd["experts"] = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in worker.optimizer_e.state_dict().items()}
+    torch.save(sd, os.path.join(path, f"rank_{_global_rank()}.pt"))
 
 
 def load_optimizer_shard(worker, path: str) -> None:
-    rank, _ = _rank_world(worker.dp_group)
-    f = os.path.join(path, f"rank_{rank}.pt")
+    f = os.path.join(path, f"rank_{_global_rank()}.pt")
     sd = torch.load(f, map_location=worker.device, weights_only=False)
     worker.optimizer.load_state_dict(sd)
+    if getattr(worker, "optimizer_e", None) is not None and sd.get("experts") is not None:
+        worker.optimizer_e.load_state_dict(sd["experts"])
     if worker.scheduler is not None and sd.get("scheduler") is not None:
         worker.scheduler.load_state_dict(sd["scheduler"])
 

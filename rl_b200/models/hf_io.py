@@ -149,15 +149,42 @@ def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]
     return missing
 
 
+def save_roles(state=None) -> tuple[bool, bool, str]:
+    """(takes part in the save, writes dense tensors, file-name suffix) for this rank under the current parallel layout.
+
+    Tensor-parallel ranks of the writing replica all take part (shards are all-gathered) and rank 0 of the group writes;
+    every pipeline stage writes its own layers; every rank of the first expert-parallel group writes its own experts."""
+    from rl_b200.parallel.state import get_state
+
+    st = state or get_state()
+    if st.world == 1:
+        return True, True, ""
+    plane = st.dp_rank * st.cp + st.cp_rank
+    takes_part = plane < max(1, st.ep)
+    writes_dense = plane == 0
+    suffix = "" if st.pp * st.ep == 1 else f"-pp{st.pp_rank}-ep{st.ep_rank}"
+    return takes_part, writes_dense, suffix
+
+
 def save_pretrained(model: CausalLM, path: str, max_shard_bytes: int = 5 * 1024**3, dtype: Optional[torch.dtype] = None) -> None:
-    """Writes an HF-layout checkpoint (config + sharded safetensors + index)."""
+    """Writes an HF-layout checkpoint (config + sharded safetensors + index). Under model parallelism this is a
+    collective over the tensor-parallel group; pipeline stages and expert-parallel ranks write separate shard files."""
     from safetensors.torch import save_file
 
+    takes_part, writes_dense, suffix = save_roles()
+    if not takes_part:
+        return
     os.makedirs(path, exist_ok=True)
-    model.cfg.save_pretrained(path)
+    is_writer = model.tp.rank == 0
+    if is_writer and writes_dense and model.first_stage:
+        model.cfg.save_pretrained(path)
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
     for name, t in iter_hf_tensors(model):  # collective over the tp group when the model is tensor parallel
+        if not is_writer or not (writes_dense or ".mlp.experts." in name):
+            continue
+        if name == "model.embed_tokens.weight" and not model.first_stage:
+            continue  # the last stage's copy of a tied table
         t = t.detach().to("cpu", dtype or t.dtype).contiguous()
         nbytes = t.numel() * t.element_size()
         if size + nbytes > max_shard_bytes and shards[-1]:
@@ -165,15 +192,19 @@ def save_pretrained(model: CausalLM, path: str, max_shard_bytes: int = 5 * 1024*
             size = 0
         shards[-1][name] = t
         size += nbytes
+    if not is_writer:
+        return
     n = len(shards)
     weight_map, total = {}, 0
     for i, sh in enumerate(shards):
-        fname = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        if not sh:
+            continue
+        fname = f"model{suffix}.safetensors" if n == 1 else f"model{suffix}-{i + 1:05d}-of-{n:05d}.safetensors"
         save_file(sh, os.path.join(path, fname), metadata={"format": "pt"})
         for k, t in sh.items():
             weight_map[k] = fname
             total += t.numel() * t.element_size()
-    if n > 1:
+    if n > 1 and not suffix:
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
 

@@ -50,19 +50,14 @@ class MoEMLP(nn.Module):
         self.last_routing = idx.detach()
         return w, idx, probs
 
-    def _experts(self, xs: torch.Tensor, counts: list[int]) -> torch.Tensor:
-        """xs: tokens sorted by local expert; counts[e] tokens for local expert e. Returns the MLP outputs."""
-        outs = []
-        s = 0
-        for e, n in enumerate(counts):
-            if n == 0:
-                continue
-            xe = xs[s : s + n]
-            outs.append(F.linear(F.swiglu(F.linear(xe, self.gate_up_proj[e])), self.down_proj[e]))
-            s += n
-        if not outs:
-            return xs.new_zeros((0, xs.shape[1]))
-        return torch.cat(outs, 0)
+    def _experts(self, xs: torch.Tensor, counts) -> torch.Tensor:
+        """xs: tokens sorted by local expert; counts[e] tokens for local expert e (tensor or list). One grouped-GEMM MLP
+        over all local experts (see :mod:`rl_b200.ops.moe_ops`)."""
+        from rl_b200.ops.moe_ops import grouped_expert_mlp
+
+        if not isinstance(counts, torch.Tensor):
+            counts = torch.tensor(counts, dtype=torch.int64, device=xs.device)
+        return grouped_expert_mlp(xs, counts, self.gate_up_proj, self.down_proj)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.cfg
@@ -73,13 +68,17 @@ class MoEMLP(nn.Module):
         order = torch.argsort(flat_e, stable=True)
         tok = order // k
         xs = x[tok]
-        counts = torch.bincount(flat_e, minlength=E)
+        counts = torch.zeros(E, dtype=torch.int64, device=x.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
         if self.ep_size > 1:
-            from rl_b200.parallel.expert import all_to_all_tokens
+            from rl_b200.parallel.expert import all_to_all_tokens, fused_dispatch_experts_combine
 
-            ys = all_to_all_tokens(xs, counts, self.ep, self.local_experts, self._experts)
+            if self.ep.comm is not None and xs.is_cuda and xs.dtype == torch.bfloat16 and xs.shape[0] <= self.ep.comm.max_copies:
+                # dispatch, grouped expert MLP and combine over peer memory: no host-side split sizes, no NCCL all-to-all
+                ys = fused_dispatch_experts_combine(xs, counts, self.ep, self.local_experts, self.gate_up_proj, self.down_proj)
+            else:
+                ys = all_to_all_tokens(xs, counts, self.ep, self.local_experts, self._experts)
         else:
-            ys = self._experts(xs, counts.tolist())
+            ys = self._experts(xs, counts)
         wy = ys * w.reshape(-1)[order].unsqueeze(-1).to(ys.dtype)
         out = torch.zeros_like(x) if residual is None else residual.clone()
         out = out.index_add(0, tok, wy)

@@ -40,11 +40,12 @@ class FlatParams:
               it, and the linear / norm backward kernels accumulate into those views directly.
     """
 
-    def __init__(self, module: nn.Module, align: int = 2048, allocator=None):
+    def __init__(self, module: nn.Module, align: int = 2048, allocator=None, include=None):
         """``allocator(numel, dtype, device) -> 1-D tensor`` lets the caller place the flat buffers (e.g. in peer-mapped
-        memory); the default is an ordinary zero-filled tensor."""
+        memory); the default is an ordinary zero-filled tensor. ``include(name) -> bool`` restricts the buffer to a subset
+        of the parameters (dense and expert parameters are reduced over different groups and live in two buffers)."""
         self._allocator = allocator
-        params = [(n, p) for n, p in module.named_parameters()]
+        params = [(n, p) for n, p in module.named_parameters() if include is None or include(n)]
         self.names = [n for n, _ in params]
         self.shapes = [tuple(p.shape) for _, p in params]
         self.numels = [p.numel() for _, p in params]
@@ -327,9 +328,16 @@ class CausalLM(nn.Module):
         if self.cfg.value_head and self.last_stage:
             self.score[1:].zero_()
 
-    def flatten_parameters(self, align: int = 2048, allocator=None) -> FlatParams:
-        self.flat = FlatParams(self, align, allocator)
-        return self.flat
+    def flatten_parameters(self, align: int = 2048, allocator=None, include=None) -> FlatParams:
+        fl = FlatParams(self, align, allocator, include)
+        if include is None or self.flat is None:
+            self.flat = fl
+        return fl
+
+    @staticmethod
+    def is_expert_param(name: str) -> bool:
+        """Expert-parallel parameters (stacked expert weights); the router is replicated like any dense parameter."""
+        return name.endswith(".mlp.gate_up_proj") or name.endswith(".mlp.down_proj")
 
     @property
     def output_weight(self) -> torch.Tensor:

@@ -114,6 +114,22 @@ def init_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, sequence_p
                         mine = g
                         st.ep_rank = ranks.index(rank)
         st.ep_group = mine
+        # ranks that hold the same experts (same position inside their expert-parallel group): they all-reduce the expert
+        # gradients and shard the expert optimizer state
+        mine = None
+        for p in range(pp):
+            for t in range(tp):
+                plane = sorted(ns.get_ranks_by_coord(pp=p, tp=t))
+                for i in range(ep):
+                    ranks = plane[i::ep]
+                    if len(ranks) > 1:
+                        g = dist.new_group(ranks=ranks, backend=backend)
+                        if rank in ranks:
+                            mine = g
+                    elif rank in ranks:
+                        mine = "self"
+        st.extras["expert_dp_group"] = mine
+        st.extras["expert_dp_size"] = (dp * cp) // ep
     if pp > 1:
         # first + last stage of every pipeline: they share the tied embedding table and all-reduce its gradient
         mine = None

@@ -118,14 +118,14 @@ class ShardedAdamW:
                 flat[r * self.shard_numel : (r + 1) * self.shard_numel].copy_(p)
 
     @torch.no_grad()
-    def step(self, grad_div: float = 1.0) -> torch.Tensor:
-        """Applies one update. ``grad_div`` divides the summed gradient (1 when the loss is already normalised by
-        the global token count). Returns the global gradient norm (a 1-element tensor, no host sync)."""
+    def reduce_and_sumsq(self) -> torch.Tensor:
+        """First half of a step: reduce-scatter the gradients and return this optimizer's squared gradient norm, already
+        summed over its own group and its model-parallel groups (a 1-element tensor). Used when several optimizers
+        (dense + expert parameters) must share one clipping coefficient."""
         self.flat.fold_autograd_grads()
         self.step_count += 1
-        if self.fused_comm is not None and self.world > 1 and self.fused_comm.usable(self):
-            return self.fused_comm.step(self, grad_div)
         gs = self._reduce_scatter()
+        self._gs = gs
         self._sumsq.zero_()
         F.sumsq_(gs, self._sumsq)
         if self._replicas > 1 and self._replicated:
@@ -142,6 +142,15 @@ class ShardedAdamW:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=self.group)
         for g in self._norm_groups:
             dist.all_reduce(self._sumsq, op=dist.ReduceOp.SUM, group=g)
+        return self._sumsq
+
+    @torch.no_grad()
+    def apply(self, total_sumsq: torch.Tensor, grad_div: float = 1.0) -> torch.Tensor:
+        """Second half: clip with the (global) squared norm, AdamW on the shard, all-gather the parameters."""
+        gs = self._gs
+        self._gs = None
+        if total_sumsq is not self._sumsq:
+            self._sumsq.copy_(total_sumsq)
         if grad_div != 1.0:
             self._sumsq.mul_(1.0 / (grad_div * grad_div))
         F.clip_scale(self._sumsq, float(self.max_grad_norm or 0.0), 1.0 / grad_div, self._scale, self._norm)
@@ -154,6 +163,16 @@ class ShardedAdamW:
         self._all_gather()
         self.last_grad_norm = self._norm.clone()
         return self.last_grad_norm
+
+    @torch.no_grad()
+    def step(self, grad_div: float = 1.0) -> torch.Tensor:
+        """Applies one update. ``grad_div`` divides the summed gradient (1 when the loss is already normalised by
+        the global token count). Returns the global gradient norm (a 1-element tensor, no host sync)."""
+        if self.fused_comm is not None and self.world > 1 and self.fused_comm.usable(self):
+            self.flat.fold_autograd_grads()
+            self.step_count += 1
+            return self.fused_comm.step(self, grad_div)
+        return self.apply(self.reduce_and_sumsq(), grad_div)
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:

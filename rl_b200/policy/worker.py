@@ -170,19 +170,50 @@ class PolicyWorker:
                     print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
                 fused_comm = None
         self.fused_comm = fused_comm
+        # expert-parallel MoE: expert weights differ between the ranks of an expert-parallel group, so they live in their
+        # own flat buffer whose gradients are reduced (and optimizer state sharded) over the ranks holding the SAME experts
+        split_experts = self.ep.world > 1 and model_cfg.is_moe
+        if self.ep.world > 1 and model_cfg.is_moe and self.device.type == "cuda" and dtype == torch.bfloat16 \
+                and cfg.get("fused_expert_parallel", True) and st.ep_comm is None:
+            try:
+                from rl_b200.parallel.expert import EPFusedComm
+
+                sp_cfg = cfg.get("sequence_packing") or {}
+                max_tok = max(int(sp_cfg.get("train_mb_tokens") or 0), int(sp_cfg.get("logprob_mb_tokens") or 0),
+                              cfg["max_total_sequence_length"] * max(cfg["train_micro_batch_size"], cfg["logprob_batch_size"]), 16384)
+                st.ep_comm = EPFusedComm(st.ep_group, model_cfg.hidden_size, (max_tok + 64) * model_cfg.num_experts_per_tok,
+                                         model_cfg.num_experts // self.ep.world, wait_limit_s=float(cfg.get("peer_wait_limit_s", 10.0)))
+            except Exception as e:
+                print(f"[policy] fused expert-parallel dispatch unavailable ({type(e).__name__}: {e}); using NCCL all-to-all")
+        self.ep.comm = st.ep_comm
+        dense = (lambda n: not CausalLM.is_expert_param(n)) if split_experts else None
         self.flat = self.model.flatten_parameters(align=256 * max(1, self.world),
-                                                  allocator=fused_comm.alloc_params if fused_comm is not None else None)
+                                                  allocator=fused_comm.alloc_params if fused_comm is not None else None, include=dense)
+        self.flat_e = None
+        e_group, e_world = None, 1
+        if split_experts:
+            e_group, e_world = st.extras.get("expert_dp_group"), int(st.extras.get("expert_dp_size", 1))
+            self.flat_e = self.model.flatten_parameters(align=256 * max(1, e_world), include=CausalLM.is_expert_param)
         self.ref_flat: Optional[torch.Tensor] = None
+        self.ref_flat_e: Optional[torch.Tensor] = None
         if init_reference_model:
             # the reference policy stays resident in HBM as a second flat buffer (no CPU swap)
             self.ref_flat = self.flat.flat.clone()
+            if self.flat_e is not None:
+                self.ref_flat_e = self.flat_e.flat.clone()
         self.optimizer: Optional[ShardedAdamW] = None
+        self.optimizer_e: Optional[ShardedAdamW] = None
         self.scheduler: Optional[LRSchedule] = None
         if init_optimizer:
             gdt = _precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32
             self.flat.attach_grad_buffer(gdt, allocator=fused_comm.alloc_grads if (fused_comm is not None and gdt == torch.float32) else None)
             self.optimizer = build_optimizer(self.flat, cfg, group=dp_group if self.world > 1 or st.world == 1 else "self",
                                              fused_comm=fused_comm)
+            if self.flat_e is not None:
+                self.flat_e.attach_grad_buffer(gdt)
+                self.optimizer_e = build_optimizer(self.flat_e, cfg, group=e_group if (e_world > 1 and e_group != "self") else "self")
+                # distinct experts live on the ranks of an expert-parallel group: their squared norms add up over it
+                self.optimizer_e.set_model_parallel([], 1, [st.ep_group])
             self._configure_model_parallel_grads()
             self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
         self.pipeline = None
@@ -265,13 +296,16 @@ class PolicyWorker:
     # ------------------------------------------------------------------ modes
     def prepare_for_training(self, *a, **k):
         self.model.train()
-        if self.optimizer is not None:
-            self.optimizer.reload_state(self.device)
+        for opt in (self.optimizer, self.optimizer_e):
+            if opt is not None:
+                opt.reload_state(self.device)
 
     def prepare_for_lp_inference(self, *a, **k):
         self.model.eval()
-        if self.cfg.get("offload_optimizer_for_logprob") and self.optimizer is not None:
-            self.optimizer.offload_state()
+        if self.cfg.get("offload_optimizer_for_logprob"):
+            for opt in (self.optimizer, self.optimizer_e):
+                if opt is not None:
+                    opt.offload_state()
 
     def finish_training(self, *a, **k):
         pass
@@ -280,14 +314,16 @@ class PolicyWorker:
     def use_reference_weights(self):
         """Runs the model on the reference policy's weights by re-pointing every parameter at the second buffer."""
         assert self.ref_flat is not None, "the worker was built without a reference model"
-        fl = self.flat
+        pairs = [(self.flat, self.ref_flat)] + ([(self.flat_e, self.ref_flat_e)] if self.flat_e is not None else [])
         try:
-            for p, o, n in zip(fl.params, fl.offsets, fl.numels):
-                p.data = self.ref_flat[o : o + n].view(p.shape)
+            for fl, ref in pairs:
+                for p, o, n in zip(fl.params, fl.offsets, fl.numels):
+                    p.data = ref[o : o + n].view(p.shape)
             yield
         finally:
-            for p, o, n in zip(fl.params, fl.offsets, fl.numels):
-                p.data = fl.flat[o : o + n].view(p.shape)
+            for fl, _ in pairs:
+                for p, o, n in zip(fl.params, fl.offsets, fl.numels):
+                    p.data = fl.flat[o : o + n].view(p.shape)
 
     # ------------------------------------------------------------------ micro-batching
     def _microbatches(self, data: BatchedDataDict, mbs: int, token_budget: Optional[int]):
@@ -442,6 +478,8 @@ class PolicyWorker:
             global_valid_seqs, global_valid_toks = counts[0], counts[1]
             if not eval_mode:
                 self.optimizer.zero_grad()
+                if self.optimizer_e is not None:
+                    self.optimizer_e.zero_grad()
             gb_loss = torch.zeros((), device=self.device)
             budget = None if getattr(loss_fn, "requires_pairs", False) else self._token_budget("train")
             if self.pipeline is not None:
@@ -468,7 +506,13 @@ class PolicyWorker:
                 all_mb_metrics.append(metrics)
             if not eval_mode:
                 self._sync_replicated_grads()
-                gn = self.optimizer.step()
+                if self.optimizer_e is None:
+                    gn = self.optimizer.step()
+                else:  # dense and expert parameters share one clipping coefficient
+                    total = self.optimizer.reduce_and_sumsq() + self.optimizer_e.reduce_and_sumsq()
+                    gn = self.optimizer.apply(total.clone())
+                    self.optimizer_e.lr = self.optimizer.lr
+                    self.optimizer_e.apply(total.clone())
                 grad_norms.append(gn)
             if self.world > 1:
                 dist.all_reduce(gb_loss, group=self.dp_group)

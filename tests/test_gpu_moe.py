@@ -1,0 +1,78 @@
+"""Grouped GEMM and the MoE layer on a GPU against a plain fp32 per-expert reference."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_mlp(xs, counts, gate_up, down):
+    outs, s = [], 0
+    for e, c in enumerate(counts):
+        xe = xs[s : s + c].float()
+        h = xe @ gate_up[e].float().t()
+        f = h.shape[1] // 2
+        a = torch.nn.functional.silu(h[:, :f]) * h[:, f:]
+        outs.append(a.to(torch.bfloat16).float() @ down[e].float().t())
+        s += c
+    return torch.cat(outs, 0)
+
+
+@pytest.mark.parametrize("counts", [[130, 0, 77, 256, 1, 0, 300, 5], [0, 0, 0, 64], [128, 128]])
+def test_grouped_expert_mlp_forward_backward(native_lib, counts):
+    from rl_b200.ops.lib import check_status
+    from rl_b200.ops.moe_ops import grouped_expert_mlp
+
+    torch.manual_seed(0)
+    E, d, f = len(counts), 256, 192
+    n = sum(counts)
+    xs = (torch.randn(n, d, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    gu = (torch.randn(E, 2 * f, d, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    dn = (torch.randn(E, d, f, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    cnt = torch.tensor(counts, device="cuda")
+    y = grouped_expert_mlp(xs, cnt, gu, dn)
+    g = torch.randn_like(y)
+    y.backward(g)
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    xr, gur, dnr = (t.detach().float().requires_grad_(True) for t in (xs, gu, dn))
+    yr = _ref_mlp(xr, counts, gur, dnr)
+    yr.backward(g.float())
+    tol = lambda ref: 3e-2 * ref.abs().max().item() + 1e-3  # noqa: E731
+    assert (y.float() - yr).abs().max().item() <= tol(yr)
+    assert (xs.grad.float() - xr.grad).abs().max().item() <= tol(xr.grad)
+    assert (gu.grad.float() - gur.grad).abs().max().item() <= tol(gur.grad)
+    assert (dn.grad.float() - dnr.grad).abs().max().item() <= tol(dnr.grad)
+    # experts without tokens get exactly zero weight gradient
+    for e, c in enumerate(counts):
+        if c == 0:
+            assert gu.grad[e].abs().max().item() == 0 and dn.grad[e].abs().max().item() == 0
+
+
+def test_moe_model_matches_fp32_reference(native_lib):
+    from rl_b200.models.config import preset
+    from rl_b200.models.transformer import PackedBatch, build_model
+    from rl_b200.ops.lib import check_status
+
+    cfg = preset("tiny-llama-oracle", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, norm_topk_prob=True,
+                 hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128, vocab_size=2048)
+    ref = build_model(cfg, dtype=torch.float32, seed=5)
+    m = build_model(cfg, device="cuda", dtype=torch.bfloat16, seed=5)
+    ids = torch.randint(0, cfg.vocab_size, (3, 40))
+    lens = torch.tensor([40, 25, 33])
+    bc = PackedBatch.from_padded(ids, lens)
+    bg = PackedBatch.from_padded(ids.cuda(), lens.cuda())
+    bg.input_ids = bg.input_ids.to(torch.int32)
+    lp, _ = m.next_token_logprobs(bg)
+    lp.sum().backward()
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    # a freshly initialised router is nearly uniform, so bf16 rounding flips many top-k choices: the reference replays the
+    # GPU model's routing and then has to agree on everything else
+    for lg, lr in zip(m.layers, ref.layers):
+        lr.mlp.forced_routing = lg.mlp.last_routing.cpu()
+    with torch.no_grad():
+        lp_ref, _ = ref.next_token_logprobs(bc)
+    assert (lp.detach().cpu() - lp_ref).abs().max().item() < 0.06
+    g = m.layers[0].mlp.gate_up_proj.grad
+    assert g is not None and torch.isfinite(g).all() and g.abs().sum().item() > 0

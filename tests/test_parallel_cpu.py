@@ -230,3 +230,89 @@ def test_context_parallel_worker_matches_single_rank():
         assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
         assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
         assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)
+
+
+def _moe_cfg():
+    from rl_b200.models.config import preset
+
+    return preset("tiny-llama-oracle", torch_dtype="float32", model_type="qwen3_moe", qk_norm=True, num_experts=4, num_experts_per_tok=2,
+                  moe_intermediate_size=32, norm_topk_prob=True)
+
+
+def _moe_data():
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+    g = torch.Generator().manual_seed(3)
+    return BatchedDataDict(input_ids=torch.randint(0, 2048, (8, 20), generator=g), input_lengths=torch.tensor([20, 17, 9, 20, 12, 20, 15, 8]),
+                           token_mask=torch.ones(8, 20), sample_mask=torch.ones(8))
+
+
+def _ep_train_worker(rank, world):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.policy.worker import PolicyWorker
+
+    cfg = _worker_cfg(expert_parallel_size=world)
+    cfg.update(train_global_batch_size=8, train_micro_batch_size=2)
+    w = PolicyWorker(cfg, model_cfg=_moe_cfg(), init_reference_model=True, seed=4)
+    assert w.flat_e is not None and w.optimizer_e is not None
+    data = _moe_data().slice(rank * 4, rank * 4 + 4)
+    lp = w.get_logprobs(data)["logprobs"]
+    outs = [w.train(data, NLLLossFn(), gbs=8, mbs=2) for _ in range(2)]
+    lp2 = w.get_logprobs(data)["logprobs"]
+    ref_lp = w.get_reference_policy_logprobs(data)["reference_logprobs"]
+    both = torch.stack([lp.sum(), lp2.sum(), ref_lp.sum()])
+    dist.all_reduce(both)
+    return dict(lp=both[0].item(), lp2=both[1].item(), ref=both[2].item(), loss=[float(o["loss"][0]) for o in outs],
+                gn=[float(o["grad_norm"][0]) for o in outs])
+
+
+def test_expert_parallel_worker_matches_single_rank():
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.parallel.state import reset_parallel
+    from rl_b200.policy.worker import PolicyWorker
+
+    reset_parallel()
+    cfg = _worker_cfg()
+    cfg.update(train_global_batch_size=8, train_micro_batch_size=2)
+    w = PolicyWorker(cfg, model_cfg=_moe_cfg(), init_reference_model=False, seed=4)
+    data = _moe_data()
+    ref = dict(lp=w.get_logprobs(data)["logprobs"].sum().item())
+    outs = [w.train(data, NLLLossFn(), gbs=8, mbs=2) for _ in range(2)]
+    ref.update(lp2=w.get_logprobs(data)["logprobs"].sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
+    out = _spawn(_ep_train_worker, 2)
+    for r, m in out.items():
+        assert m["lp"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)
+        assert m["ref"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)   # the reference copy keeps the initial weights
+        assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
+        assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
+        assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)
+
+
+def _ckpt_worker(rank, world, mode, path):
+    from rl_b200.policy.worker import PolicyWorker
+
+    par = dict(tensor_parallel_size=world) if mode == "tp" else (dict(pipeline_parallel_size=world) if mode == "pp" else dict(expert_parallel_size=world))
+    mc = _moe_cfg() if mode == "ep" else __import__("rl_b200.models.config", fromlist=["preset"]).preset("tiny-llama-oracle", torch_dtype="float32")
+    w = PolicyWorker(_worker_cfg(**par), model_cfg=mc, init_reference_model=False, seed=9)
+    w.save_checkpoint(os.path.join(path, "weights"), os.path.join(path, "optimizer"))
+    dist.barrier()
+    return sorted(os.listdir(os.path.join(path, "weights")))
+
+
+@pytest.mark.parametrize("mode", ["tp", "pp", "ep"])
+def test_model_parallel_checkpoint_loads_into_single_rank(tmp_path, mode):
+    from rl_b200.models.config import preset
+    from rl_b200.models.hf_io import load_pretrained
+    from rl_b200.models.transformer import build_model
+    from rl_b200.parallel.state import reset_parallel
+
+    reset_parallel()
+    out = _spawn(_ckpt_worker, 2, mode, str(tmp_path))
+    files = out[0]
+    assert "config.json" in files and any(f.endswith(".safetensors") for f in files)
+    mc = _moe_cfg() if mode == "ep" else preset("tiny-llama-oracle", torch_dtype="float32")
+    ref = build_model(mc, dtype=torch.float32, seed=9)
+    got = load_pretrained(str(tmp_path / "weights"), dtype=torch.float32)
+    for (n, a), (_, b) in zip(ref.named_parameters(), got.named_parameters()):
+        assert torch.equal(a, b), n
+    assert len(os.listdir(tmp_path / "optimizer")) == 2

@@ -30,6 +30,7 @@ from rl_b200.distributed.batched_data_dict import BatchedDataDict
 from rl_b200.experience.rollouts import run_multi_turn_rollout
 from rl_b200.utils.checkpoint import CheckpointManager
 from rl_b200.utils.logger import Logger
+from rl_b200.utils.profiling import maybe_gpu_profile_step
 from rl_b200.utils.timer import TimeoutChecker, Timer
 
 GRPO_DEFAULTS = dict(
@@ -349,6 +350,7 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
         for batch in dataloader:
             if total_steps >= g["max_num_steps"]:
                 break
+            maybe_gpu_profile_step(total_steps + 1, dist.get_rank() if dist.is_initialized() else 0)
             with timer.time("total_step_time"):
                 # ---- data
                 with timer.time("data_processing"):

@@ -64,6 +64,8 @@ __device__ unsigned long long g_tp_phase_ns[8];
 struct TpArgs {
   int mode, rank, world;
   unsigned int epoch;
+  unsigned int* epoch_ptr;  // scatter mode: when set, the call's epoch is *epoch_ptr + 1 and the kernel stores it back
+                            // (a launch recorded in a CUDA graph then advances the epoch on every replay)
   unsigned long long limit_ns;
   unsigned int* flags[MAX_TP];
   unsigned char* stage[MAX_TP];
@@ -253,6 +255,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (t.epoch_ptr) t.epoch = *reinterpret_cast<volatile unsigned int*>(t.epoch_ptr) + 1;
   const bool stamp = blockIdx.x == 0 && threadIdx.x == 0 && t.mode == MODE_SCATTER;
   if (stamp) g_tp_phase_ns[0] = globaltimer_ns();
   if (threadIdx.x == 0) {
@@ -491,6 +494,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __threadfence_system();
   grid.sync();
   if (stamp) g_tp_phase_ns[2] = globaltimer_ns();
+  if (stamp && t.epoch_ptr) *t.epoch_ptr = t.epoch;  // every CTA has read the old value before the grid sync
   if (blockIdx.x == 0) {
     if (warp == 0) {
       const bool b_ok = peer_barrier_warp(t, FLAG_END, status);
@@ -674,11 +678,11 @@ RLB_API int rlb_gemm_tp_gather(const void* a_local, long long lda_local, const v
 // out = reduce over ranks of (A[M, K] * op(B)) (+ residual), rows scattered: rank j receives rows
 // [j*rows_per_rank, (j+1)*rows_per_rank) (all_reduce = 0, M = world*rows_per_rank, out is [rows_per_rank, N]), or every
 // rank receives all M rows (all_reduce = 1, out is [M, N]). stage_ptrs[r]: rank r's staging buffer of
-// world * rows_out * N bf16 (one slot per source rank).
+// world * rows_out * N bf16 (one slot per source rank). `epoch_ptr` (device, may be null): see TpArgs.
 RLB_API int rlb_gemm_tp_scatter(const void* A, long long lda, const void* B, long long ldb, int b_mn, int M, int N, int K,
                                 int rows_per_rank, int all_reduce, void* out, long long ldo, const void* residual,
                                 long long ldr, void* const* stage_ptrs, void* const* flag_ptrs, int rank, int world,
-                                unsigned int epoch, double wait_limit_s, int* status, void* stream) {
+                                unsigned int epoch, void* epoch_ptr, double wait_limit_s, int* status, void* stream) {
   if (world < 2 || world > MAX_TP || M <= 0 || N <= 0 || K <= 0) return -2;
   if (!all_reduce && M != world * rows_per_rank) return -2;
   if ((lda % 8) || (ldb % 8) || (ldo % 8) || (N % 8) || (residual && (ldr % 8))) return -2;
@@ -688,6 +692,7 @@ RLB_API int rlb_gemm_tp_scatter(const void* A, long long lda, const void* B, lon
   TpArgs t;
   fill_common(t, stage_ptrs, flag_ptrs, rank, world, epoch, wait_limit_s, all_reduce ? M : rows_per_rank);
   t.mode = MODE_SCATTER;
+  t.epoch_ptr = static_cast<unsigned int*>(epoch_ptr);
   t.all_reduce = all_reduce;
   t.out = static_cast<__nv_bfloat16*>(out);
   t.ldo = ldo;

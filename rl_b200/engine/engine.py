@@ -337,7 +337,9 @@ class GenerationEngine:
         attn0 = model.layers[0].self_attn if len(model.layers) else None
         self.hq = attn0.hq if attn0 is not None else self.cfg.num_attention_heads
         self.hkv = attn0.hkv if attn0 is not None else self.cfg.num_key_value_heads
-        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe and self.tpw == 1
+        # tensor-parallel decode is captured too when the fused GEMM + all-reduce kernel (device-resident epoch) carries the
+        # collectives; NCCL broadcasts / all-gathers of the sampled tokens and logits are capturable as well
+        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe and (self.tpw == 1 or getattr(self.tp, "comm", None) is not None)
         self.logits_dtype = torch.float32 if logits_fp32 else model.dtype
         c = self.cfg
         if num_blocks is None:

@@ -69,7 +69,7 @@ def _bind():
     lib = _L.lib()
     if not _bound:
         lib.rlb_gemm_tp_gather.argtypes = [_P, _LL, _P, _LL, _I, _P, _LL, _P, _I, _I, _I, _P, _P, _I, _I, _U, _I, _D, _P, _P]
-        lib.rlb_gemm_tp_scatter.argtypes = [_P, _LL, _P, _LL, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _LL, _P, _P, _I, _I, _U, _D, _P, _P]
+        lib.rlb_gemm_tp_scatter.argtypes = [_P, _LL, _P, _LL, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _LL, _P, _P, _I, _I, _U, _P, _D, _P, _P]
         lib.rlb_gemm_tp_gather.restype = C.c_int
         lib.rlb_gemm_tp_scatter.restype = C.c_int
         _bound = True
@@ -96,7 +96,8 @@ class TPFusedComm:
         self.stage_a = None
         self.stage_c = None
         self.epoch_g = 0
-        self.epoch_s = 0
+        # the scatter kernel keeps its epoch in device memory, so launches replayed from a CUDA graph stay in step
+        self.epoch_s_dev = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
         if max_rows and max_cols:
             self._ensure("stage_a", max_rows * max_cols * 2)
             self._ensure("stage_c", max_rows * max_cols * 2)
@@ -146,11 +147,10 @@ class TPFusedComm:
         out = torch.empty((rows, N), dtype=BF16, device=a.device)
         if residual is not None:
             assert residual.shape == out.shape and residual.dtype == BF16 and residual.stride(1) == 1
-        self.epoch_s += 1
         rc = lib.rlb_gemm_tp_scatter(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), int(b_mn), M, N, K, rows, int(all_reduce),
                                      out.data_ptr(), out.stride(0), None if residual is None else residual.data_ptr(),
                                      0 if residual is None else residual.stride(0), st.table, self._sflags, self.rank, self.world,
-                                     self.epoch_s, float(self.wait_limit_s), _L.status_word(a.device).data_ptr(),
+                                     0, self.epoch_s_dev.data_ptr(), float(self.wait_limit_s), _L.status_word(a.device).data_ptr(),
                                      torch.cuda.current_stream().cuda_stream)
         _L.Counters.launches += 1
         if rc:

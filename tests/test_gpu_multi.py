@@ -235,3 +235,48 @@ def _refit_worker(rank, world, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_refit_reshard_kernel_matches_collective_twin(native_lib):
     mp.spawn(_refit_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _ep_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=0, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128, qk_norm=True, num_experts=8, num_experts_per_tok=2,
+                     moe_intermediate_size=256, norm_topk_prob=True)
+    g = torch.Generator().manual_seed(50 + rank)
+    ids = torch.randint(1, 4096, (4, 96), generator=g)
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([96, 70, 64, 33]), token_mask=torch.ones(4, 96), sample_mask=torch.ones(4))
+    res = {}
+    for mode in ("fused", "nccl"):
+        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=8, train_micro_batch_size=2, max_total_sequence_length=128,
+                              max_grad_norm=1.0, parallel=dict(expert_parallel_size=2), logprob_batch_size=4,
+                              optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.0))),
+                         model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, seed=3)
+        if mode == "nccl":
+            p.ep.comm = None
+        assert (p.ep.comm is not None) == (mode == "fused")
+        lp0 = p.get_logprobs(data)["logprobs"]
+        outs = [p.train(data, NLLLossFn(), gbs=8, mbs=2) for _ in range(2)]
+        lp1 = p.get_logprobs(data)["logprobs"]
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        res[mode] = (lp0, [float(o["loss"][0]) for o in outs], [float(o["grad_norm"][0]) for o in outs], lp1)
+    f, n = res["fused"], res["nccl"]
+    assert (f[0] - n[0]).abs().max().item() < 0.05
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[1], n[1])) < 5e-3, (f[1], n[1])
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[2], n[2])) < 3e-2, (f[2], n[2])
+    assert (f[3] - n[3]).abs().mean().item() < 0.05
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_fused_dispatch_vs_nccl(native_lib):
+    mp.spawn(_ep_worker, args=(2, _free_port()), nprocs=2, join=True)

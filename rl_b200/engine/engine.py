@@ -402,6 +402,28 @@ class GenerationEngine:
         z = F.gemm(h, self.model.output_weight, out=out if self.tpw == 1 else None, out_dtype=self.logits_dtype)
         return z if self.tpw == 1 else gather_cols(z, self.tp)
 
+    def _any_rank(self, ep, flag: bool) -> bool:
+        import torch.distributed as dist
+
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ep.group)
+        return bool(t.item())
+
+    @torch.no_grad()
+    def _dummy_forward(self, decode: bool) -> None:
+        """One forward pass over a single padding token (slot -1: nothing is written to the KV cache)."""
+        dev = self.device
+        idt = torch.int32 if self.native else torch.int64
+        ids = torch.zeros(1, dtype=idt, device=dev)
+        pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        slots = torch.full((1,), -1, dtype=torch.int64, device=dev)
+        if decode:
+            bt = torch.zeros((1, self.max_blocks_per_seq), dtype=torch.int32, device=dev)
+            self._decode_forward(ids, pos, slots, bt, torch.zeros(1, dtype=torch.int32, device=dev), 1, None)
+        else:
+            cu = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+            self._prefill_forward(PackedBatch(ids, pos, cu, 1), slots, torch.zeros(1, dtype=torch.int64, device=dev))
+
     def _agree(self, tok, lp):
         """All tp ranks must take the same scheduling decisions: rank 0's samples win."""
         if self.tpw > 1:
@@ -561,10 +583,28 @@ class GenerationEngine:
         dev = self.device
         st = self._static_buffers()
         last_logits: dict[int, torch.Tensor] = {}
-        while not self.sched.idle():
-            prefill, shared, decode, copies = self.sched.schedule()
-            if not prefill and not shared and not decode:
+        # Expert-parallel MoE layers exchange tokens between the ranks of the expert group in every forward pass, so those
+        # ranks must run the same sequence of forward passes although each serves its own requests: every iteration they
+        # agree on whether a decode and / or a prefill pass happens, and a rank without work of that kind runs it on one
+        # dummy token (no cache write, output discarded).
+        ep = getattr(self.model, "ep", None)
+        lock = ep is not None and ep.world > 1 and self.cfg.is_moe
+        while True:
+            idle = self.sched.idle()
+            if lock:
+                if not self._any_rank(ep, not idle):
+                    break
+            elif idle:
+                break
+            prefill, shared, decode, copies = self.sched.schedule() if not idle else ([], [], [], [])
+            if not idle and not prefill and not shared and not decode:
                 raise RuntimeError("scheduler made no progress (KV cache too small for a single request)")
+            need_decode = self._any_rank(ep, bool(decode)) if lock else bool(decode)
+            need_prefill = self._any_rank(ep, bool(prefill)) if lock else bool(prefill)
+            if need_decode and not decode:
+                self._dummy_forward(decode=True)
+            if need_prefill and not prefill:
+                self._dummy_forward(decode=False)
             # ---- decode the sequences that were already running
             if decode:
                 t0 = time.perf_counter()

@@ -68,7 +68,11 @@ def verify_right_padding(data: BatchedDataDict, pad_value: int = 0) -> tuple[boo
 class NativeGeneration:
     """Driver-facing generation object (one per GPU rank in the SPMD runtime)."""
 
-    def __init__(self, model, cfg: Optional[dict] = None, tokenizer=None):
+    def __init__(self, model, cfg: Optional[dict] = None, tokenizer=None, pool_group=None, pool_stride: int = 1):
+        """``pool_group``: the serving tensor-parallel group when it spans several data-parallel ranks of the trainer
+        (each holding different prompts); the prompts of one rank per ``pool_stride`` consecutive ranks are pooled so that
+        all ranks of the engine serve the same request set, and every rank gets its own results back."""
+        self.pool_group, self.pool_stride = pool_group, max(1, int(pool_stride))
         self.cfg = configure_generation_config(cfg, tokenizer)
         c = self.cfg
         self.tokenizer = tokenizer
@@ -112,7 +116,25 @@ class NativeGeneration:
         prompts = [ids_cpu[i, : lens_l[i]].tolist() for i in range(B)]
         sp = self._sampling(greedy)
         uids = data["rng_ids"].tolist() if "rng_ids" in data else None
-        recs = self.engine.generate(prompts, sp, request_uids=uids)
+        if self.pool_group is not None:
+            import torch.distributed as dist
+
+            S = dist.get_world_size(self.pool_group)
+            me = dist.get_rank(self.pool_group)
+            box = [None] * S
+            dist.all_gather_object(box, (prompts, uids), group=self.pool_group)
+            leaders = list(range(0, S, self.pool_stride))          # one rank per group of ranks holding the same data
+            pooled, pooled_uids, start = [], [], {}
+            for l in leaders:
+                start[l] = len(pooled)
+                pooled += box[l][0]
+                # request ids must stay unique inside the pooled batch
+                pooled_uids += box[l][1] if box[l][1] is not None else [(l << 24) | j for j in range(len(box[l][0]))]
+            allrecs = self.engine.generate(pooled, sp, request_uids=pooled_uids)
+            mine = (me // self.pool_stride) * self.pool_stride
+            recs = allrecs[start[mine] : start[mine] + B]
+        else:
+            recs = self.engine.generate(prompts, sp, request_uids=uids)
         stop_strings = data.get("stop_strings") or self.cfg.get("stop_strings")
         if stop_strings and self.tokenizer is not None:
             self._apply_stop_strings(recs, stop_strings)

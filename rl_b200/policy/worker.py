@@ -289,9 +289,40 @@ class PolicyWorker:
         if native_cfg.get("enforce_eager"):
             merged["use_cuda_graphs"] = False
         merged.setdefault("max_model_len", self.cfg["max_total_sequence_length"])
-        self.generation = NativeGeneration(self.model, merged, self.tokenizer)
+        gen_tp = int(native_cfg.get("tensor_parallel_size") or self.tp.world)
+        engine_model, pool_group, pool_stride = self.model, None, 1
+        if gen_tp != self.tp.world:
+            engine_model, pool_group, pool_stride = self._build_serving_layout(gen_tp)
+        self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride)
         self.temperature = float(self.generation.cfg["temperature"] or 1.0)
         return self.generation
+
+    def _build_serving_layout(self, gen_tp: int):
+        """The engine serves with a tensor-parallel size different from the trainer's: every rank gets a weight arena in
+        the serving layout, filled before each generation phase by the refit synchronizer (rl_b200/refit)."""
+        from rl_b200.parallel.tensor import TPFusedComm
+        from rl_b200.refit.synchronizer import WeightSynchronizer
+
+        st = self.pstate
+        assert st.pp * st.cp * st.ep == 1 and not self.model_cfg.is_moe, "re-sharding refit covers dense tensor/data-parallel layouts"
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        assert world % gen_tp == 0, "generation tensor-parallel size must divide the world size"
+        serve_group, comm = None, None
+        if gen_tp > 1:
+            me = dist.get_rank()
+            for g0 in range(0, world, gen_tp):  # collective: every rank creates every group
+                grp = dist.new_group(ranks=list(range(g0, g0 + gen_tp)))
+                if g0 <= me < g0 + gen_tp:
+                    serve_group = grp
+            if self.device.type == "cuda" and self.cfg.get("fused_tensor_parallel", True):
+                try:
+                    comm = TPFusedComm(serve_group, wait_limit_s=float(self.cfg.get("peer_wait_limit_s", 10.0)))
+                except Exception as e:
+                    print(f"[policy] fused serving kernels unavailable ({type(e).__name__}: {e}); using NCCL")
+        self.weight_synchronizer = WeightSynchronizer(self.model, self.model_cfg, gen_tp, group=None, serve_group=serve_group, serve_comm=comm)
+        # ranks of one serving group that hold different data (more serving than training tensor parallelism) pool prompts
+        pool = serve_group if gen_tp > self.tp.world else None
+        return self.weight_synchronizer.serving_model, pool, self.tp.world
 
     # ------------------------------------------------------------------ modes
     def prepare_for_training(self, *a, **k):

@@ -56,8 +56,11 @@ def test_moe_model_matches_fp32_reference(native_lib):
 
     cfg = preset("tiny-llama-oracle", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, norm_topk_prob=True,
                  hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128, vocab_size=2048)
-    ref = build_model(cfg, dtype=torch.float32, seed=5)
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+
     m = build_model(cfg, device="cuda", dtype=torch.bfloat16, seed=5)
+    ref = build_model(cfg, dtype=torch.float32, init=False)
+    load_hf_tensors(ref, {n: t.detach().float().cpu() for n, t in iter_hf_tensors(m)}.get)  # same (bf16-rounded) weights
     ids = torch.randint(0, cfg.vocab_size, (3, 40))
     lens = torch.tensor([40, 25, 33])
     bc = PackedBatch.from_padded(ids, lens)

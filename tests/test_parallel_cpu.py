@@ -355,3 +355,59 @@ def test_expert_parallel_generation_runs_in_lock_step():
         ids = torch.randint(0, 2048, (n, 10), generator=g)
         ref = gen.generate(BatchedDataDict(input_ids=ids, input_lengths=torch.full((n,), 10)), greedy=True)["output_ids"].tolist()
         assert out[rank] == ref
+
+
+def _reshard_gen_worker(rank, world, tp_train, tp_serve):
+    from rl_b200.algorithms.grpo import refit_policy_generation
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import preset
+    from rl_b200.policy.worker import PolicyWorker
+
+    cfg = _worker_cfg(tensor_parallel_size=tp_train)
+    cfg["generation"] = dict(max_new_tokens=8, temperature=1.0, stop_token_ids=[], kv_cache_tokens=2048, block_size=16, max_running=8,
+                             native_cfg=dict(tensor_parallel_size=tp_serve))
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    w = PolicyWorker(cfg, model_cfg=mc, init_reference_model=False, seed=4)
+    gen = w.build_generation()
+    dp_rank = rank // tp_train
+    g = torch.Generator().manual_seed(20 + dp_rank)
+    ids = torch.randint(0, 2048, (3, 10), generator=g)
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.full((3,), 10))
+    outs = []
+    for it in range(2):
+        refit_policy_generation(w, gen)
+        outs.append(gen.generate(data, greedy=True)["output_ids"].tolist())
+        gen.finish_generation()
+        if it == 0:  # change the trainer's weights: the next refit must carry them over
+            with torch.no_grad():
+                w.flat.flat.mul_(1.25)
+    return outs
+
+
+@pytest.mark.parametrize("tp_train,tp_serve", [(1, 2), (2, 1)])
+def test_generation_with_a_different_tensor_parallel_size(tp_train, tp_serve):
+    """Data-parallel training with tensor-parallel serving (prompts pooled inside the serving group) and the reverse: greedy
+    outputs equal those of a single-rank model, before and after a weight change + refit."""
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import preset
+    from rl_b200.parallel.state import reset_parallel
+    from rl_b200.policy.worker import PolicyWorker
+
+    out = _spawn(_reshard_gen_worker, 2, tp_train, tp_serve)
+    reset_parallel()
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    for rank in range(2):
+        cfg = _worker_cfg()
+        cfg["generation"] = dict(max_new_tokens=8, temperature=1.0, stop_token_ids=[], kv_cache_tokens=2048, block_size=16, max_running=8)
+        w = PolicyWorker(cfg, model_cfg=mc, init_reference_model=False, seed=4)
+        gen = w.build_generation()
+        g = torch.Generator().manual_seed(20 + rank // tp_train)
+        ids = torch.randint(0, 2048, (3, 10), generator=g)
+        data = BatchedDataDict(input_ids=ids, input_lengths=torch.full((3,), 10))
+        for it in range(2):
+            gen.prepare_for_generation()
+            ref = gen.generate(data, greedy=True)["output_ids"].tolist()
+            gen.finish_generation()
+            assert out[rank][it] == ref, (rank, it)
+            with torch.no_grad():
+                w.flat.flat.mul_(1.25)

@@ -104,3 +104,33 @@ def dequantize_mxfp8(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
         return out
     ds = torch.where(scales == 0, torch.ones((), dtype=torch.float32), torch.exp2(scales.float() - 127))
     return (q.float().reshape(R, C // 32, 32) * ds[..., None]).reshape(R, C).to(torch.bfloat16)
+
+
+# --------------------------------------------------------------------------------------------- MXFP8 GEMM
+register("rlb_gemm_mxfp8", [P, L, P, L, P, P, P, L, I, I, I, P, P])
+
+
+def swizzle_mx_scales(scales: torch.Tensor) -> torch.Tensor:
+    """Row-major E8M0 scales [R, K/32] -> the blocked layout the tensor core reads: [ceil(R/128), K/128, 512] bytes, where
+    row r of a 128-row block and 32-wide K group j of a 128-wide K block sit at byte (r % 32) * 16 + (r // 32) * 4 + j.
+    Rows beyond R are filled with scale byte 0."""
+    R, G = scales.shape
+    assert G % 4 == 0, "K must be a multiple of 128"
+    Rb = -(-R // 128)
+    s = torch.zeros((Rb * 128, G), dtype=torch.uint8, device=scales.device)
+    s[:R] = scales
+    s = s.view(Rb, 4, 32, G // 4, 4).permute(0, 3, 2, 1, 4)  # [Rb, Kb, r % 32, r // 32, j]
+    return s.reshape(Rb, G // 4, 512).contiguous()
+
+
+def gemm_mxfp8(a_q: torch.Tensor, a_sf: torch.Tensor, b_q: torch.Tensor, b_sf: torch.Tensor) -> torch.Tensor:
+    """C [M, N] bf16 = dequant(A) @ dequant(B)^T for MXFP8 operands: ``a_q`` [M, K] / ``b_q`` [N, K] e4m3 and their scales in
+    the blocked layout of :func:`swizzle_mx_scales`. The scales are applied by the tensor core (block-scaled MMA)."""
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    if not use_native(a_q):
+        raise RuntimeError("the MXFP8 GEMM needs the native library on a GPU")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a_q.device)
+    call("rlb_gemm_mxfp8", ptr(a_q), a_q.stride(0), ptr(b_q), b_q.stride(0), ptr(a_sf), ptr(b_sf), ptr(out), out.stride(0), M, N, K,
+         ptr(_L.status_word(a_q.device)), stream_ptr())
+    return out

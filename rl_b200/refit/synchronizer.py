@@ -71,6 +71,7 @@ class WeightSynchronizer:
             self._arena_ptrs = [self.arena.data_ptr()] * max(1, self.world)
         self.serving_model = build_serving_model(cfg, tp_serve, self.rank, self.arena, serve_group, serve_comm)
         self._descs = self._work = None
+        self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._num_work = 0
         self.last_bytes = 0
 
@@ -120,15 +121,16 @@ class WeightSynchronizer:
 
         if self._descs is None:
             self._prepare()
+        # Stream-ordered rendezvous (a one-element all-reduce) instead of host barriers: the first makes sure no engine of
+        # the group still reads its arena, the second that every peer's stores into this rank's arena have landed.
         if self.world > 1:
-            dist.barrier(group=self.group)  # no engine still reads its arena
+            dist.all_reduce(self._token, group=self.group)
         rc = _L.lib().rlb_refit_copy(self._descs.data_ptr(), self._work.data_ptr(), self._num_work, 0, torch.cuda.current_stream().cuda_stream)
         _L.Counters.launches += 1
         if rc:
             raise RuntimeError(f"rlb_refit_copy failed with code {rc}")
-        torch.cuda.synchronize(self.device)
         if self.world > 1:
-            dist.barrier(group=self.group)  # every peer's stores into this arena have landed
+            dist.all_reduce(self._token, group=self.group)
 
     # ------------------------------------------------------------------ collective twin / CPU path
     @torch.no_grad()

@@ -69,3 +69,35 @@ def test_native_mxfp8_matches_oracle(native_lib, shape):
     assert torch.equal(e, er)
     assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
     assert torch.equal(dequantize_mxfp8(q, e), dequantize_mxfp8(qr.cpu(), er.cpu()).cuda())
+
+
+def test_swizzled_scale_layout():
+    from rl_b200.ops.quant import swizzle_mx_scales
+
+    R, G = 200, 8  # two row blocks (second ragged), two K blocks
+    sc = (torch.arange(R * G) % 251).to(torch.uint8).view(R, G)
+    sw = swizzle_mx_scales(sc)
+    assert sw.shape == (2, 2, 512)
+    for r, g in [(0, 0), (33, 5), (127, 7), (128, 0), (199, 3)]:
+        blk, rr, kb, j = r // 128, r % 128, g // 4, g % 4
+        assert sw[blk, kb, (rr % 32) * 16 + (rr // 32) * 4 + j] == sc[r, g]
+    assert sw[1, 0, (72 % 32) * 16 + (72 // 32) * 4] == 0  # row 200 does not exist
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 512), (200, 264, 1024), (1024, 2048, 768)])
+def test_mxfp8_gemm_matches_dequantised_reference(native_lib, shape):
+    from rl_b200.ops.lib import check_status
+    from rl_b200.ops.quant import gemm_mxfp8, swizzle_mx_scales
+
+    M, N, K = shape
+    a = _w(M, K, seed=5, device="cuda")
+    b = _w(N, K, seed=6, device="cuda")
+    aq, asf = quantize_mxfp8(a)
+    bq, bsf = quantize_mxfp8(b)
+    c = gemm_mxfp8(aq, swizzle_mx_scales(asf), bq, swizzle_mx_scales(bsf))
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    ref = dequantize_mxfp8(aq, asf).float() @ dequantize_mxfp8(bq, bsf).float().t()
+    err = (c.float() - ref).abs().max().item()
+    assert err <= 1e-2 * ref.abs().max().item() + 1e-3, (err, ref.abs().max().item())

@@ -75,6 +75,32 @@ def bench_gemm(shapes=None):
     return rows
 
 
+def bench_mxfp8(shapes=None):
+    """MXFP8 block-scaled GEMM against the bf16 GEMM of the same shape (dense fp8 peak is 2x the bf16 peak)."""
+    from .quant import gemm_mxfp8, quantize_mxfp8, swizzle_mx_scales
+
+    peak_tf, _, how = _peaks()
+    shapes = shapes or [(8192, 6144, 4096), (8192, 28672, 4096), (8192, 4096, 14336), (8192, 2048, 768), (8192, 1536, 2048)]
+    rows = []
+    for M, N, K in shapes:
+        n_pool = max(2, min(6, L2_BYTES * 2 // (M * K + N * K + 2 * M * N) + 1))
+        As = [torch.randn(M, K, device="cuda", dtype=torch.bfloat16) for _ in range(n_pool)]
+        Bs = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(n_pool)]
+        qa = [quantize_mxfp8(a) for a in As]
+        qb = [quantize_mxfp8(b) for b in Bs]
+        sa = [swizzle_mx_scales(s) for _, s in qa]
+        sb = [swizzle_mx_scales(s) for _, s in qb]
+        ms = time_fn(lambda i: gemm_mxfp8(qa[i][0], sa[i], qb[i][0], sb[i]), n_pool)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms_bf16 = time_fn(lambda i: F.gemm(As[i], Bs[i], out=out), n_pool)
+        ms_q = time_fn(lambda i: quantize_mxfp8(As[i]), n_pool)
+        tf = 2.0 * M * N * K / ms / 1e9
+        rows.append(dict(kernel="gemm_mxfp8", M=M, N=N, K=K, ms=round(ms, 4), tflops=round(tf, 1), frac_of_bf16_peak=round(tf / peak_tf, 3),
+                         peak=how, bf16_gemm_ms=round(ms_bf16, 4), vs_bf16_gemm=round(ms_bf16 / ms, 3), quantize_a_ms=round(ms_q, 4)))
+        print(rows[-1], flush=True)
+    return rows
+
+
 def bench_memory_bound():
     _, hbm, how = _peaks()
     rows = []
@@ -119,6 +145,8 @@ def main(argv=None):
             M, N, K = (int(x) for x in a.gemm_shape.split(","))
             shapes = [(M, N, K, False, False)]
         out += bench_gemm(shapes)
+    if "mx" in which:
+        out += bench_mxfp8()
     if "mem" in which:
         out += bench_memory_bound()
     if a.json:

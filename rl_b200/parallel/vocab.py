@@ -124,3 +124,24 @@ def vocab_parallel_logprobs(h: torch.Tensor, w_shard: torch.Tensor, targets: tor
     if tp.world == 1:
         return F.lm_head_logprobs(h, w_shard, targets, temperature, want_entropy)
     return _VocabParallelLogprob.apply(h, w_shard, targets, int(vocab_start), 1.0 / temperature, want_entropy, tp)
+
+
+# --------------------------------------------------------------------------------------------- vocab-parallel argmax / top-k
+def vocab_parallel_topk(logits_shard: torch.Tensor, k: int, tp: TP, vocab_start: int):
+    """Top-k over a vocabulary that is sharded across the tensor-parallel group: every rank takes the top-k of its slice,
+    the candidates ([T, k] values + global ids per rank) are all-gathered and reduced to the global top-k
+    (nemo_rl/distributed/model_utils.py ``distributed_vocab_topk``). Returns (values [T, k], global ids [T, k])."""
+    kk = min(k, logits_shard.shape[-1])
+    v, i = torch.topk(logits_shard.float(), kk, dim=-1)
+    i = i + vocab_start
+    if tp.world == 1:
+        return v, i
+    allv = all_gather_rows(v.t().contiguous(), tp.group, tp.world).t()   # [T, tp * kk]
+    alli = all_gather_rows(i.t().contiguous(), tp.group, tp.world).t()
+    tv, pos = torch.topk(allv, min(k, allv.shape[-1]), dim=-1)
+    return tv, alli.gather(-1, pos)
+
+
+def vocab_parallel_argmax(logits_shard: torch.Tensor, tp: TP, vocab_start: int) -> torch.Tensor:
+    """Global argmax token id per row (greedy decoding over a sharded vocabulary)."""
+    return vocab_parallel_topk(logits_shard, 1, tp, vocab_start)[1][:, 0]

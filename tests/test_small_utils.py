@@ -1,0 +1,76 @@
+"""Collective helpers, packed weight broadcast, vocab-parallel top-k, routed-expert traces."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__))))
+from test_parallel_cpu import _spawn  # noqa: E402
+
+
+def test_pack_and_unpack_buckets():
+    from rl_b200.distributed.collectives import pack_tensors, unpack_bucket
+
+    ts = [("a", torch.arange(10, dtype=torch.float32)), ("b", torch.ones(3, 5, dtype=torch.bfloat16)), ("c", torch.arange(7, dtype=torch.int64)),
+          ("big", torch.randn(1000))]
+    got = {}
+    buckets = list(pack_tensors(ts, bucket_bytes=128))
+    assert len(buckets) >= 3
+    for manifest, buf in buckets:
+        assert all(off % 16 == 0 for _, _, _, off, _ in manifest)
+        for n, t in unpack_bucket(manifest, buf):
+            got[n] = t.clone()
+    for n, t in ts:
+        assert torch.equal(got[n], t) and got[n].dtype == t.dtype
+
+
+def _coll_worker(rank, world):
+    from rl_b200.distributed.collectives import gather_jagged_object_lists, packed_broadcast, rebalance_nd_tensor
+    from rl_b200.parallel.tensor import TP
+    from rl_b200.parallel.vocab import vocab_parallel_argmax, vocab_parallel_topk
+
+    t = torch.full((rank + 1, 3), float(rank))
+    full = rebalance_nd_tensor(t)
+    objs = gather_jagged_object_lists([f"r{rank}-{i}" for i in range(rank + 1)])
+    torch.manual_seed(0)
+    src = [("w", torch.randn(64, 8)), ("b", torch.arange(5))] if rank == 0 else None
+    recv = {n: x.clone() for n, x in packed_broadcast(src, 0, bucket_bytes=1024)}
+    z = torch.randn(6, 32, generator=torch.Generator().manual_seed(1))
+    tp = TP(None, rank, world)
+    v, i = vocab_parallel_topk(z[:, rank * 16 : (rank + 1) * 16], 5, tp, rank * 16)
+    rv, ri = torch.topk(z, 5, dim=-1)
+    am = vocab_parallel_argmax(z[:, rank * 16 : (rank + 1) * 16], tp, rank * 16)
+    return dict(full=full.tolist(), objs=objs, w=float(recv["w"].sum()), b=recv["b"].tolist(),
+                topk=bool(torch.equal(i, ri) and torch.allclose(v, rv)), argmax=bool(torch.equal(am, z.argmax(-1))))
+
+
+def test_collectives_packed_broadcast_and_vocab_topk():
+    out = _spawn(_coll_worker, 2)
+    torch.manual_seed(0)
+    w = torch.randn(64, 8)
+    for r in (0, 1):
+        assert out[r]["full"] == [[0.0] * 3, [1.0] * 3, [1.0] * 3]
+        assert out[r]["objs"] == ["r0-0", "r1-0", "r1-1"]
+        assert abs(out[r]["w"] - float(w.sum())) < 1e-5 and out[r]["b"] == [0, 1, 2, 3, 4]
+        assert out[r]["topk"] and out[r]["argmax"]
+
+
+def test_routing_trace_capture_and_replay():
+    from rl_b200.models.config import preset
+    from rl_b200.models.transformer import PackedBatch, build_model
+    from rl_b200.utils import routing_trace as R
+
+    cfg = preset("tiny-llama-oracle", torch_dtype="float32", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)
+    a, b = build_model(cfg, dtype=torch.float32, seed=1), build_model(cfg, dtype=torch.float32, seed=2)
+    batch = PackedBatch.from_padded(torch.randint(0, cfg.vocab_size, (2, 9)), torch.tensor([9, 6]))
+    a.hidden_states(batch)
+    tr = R.capture(a)
+    b.hidden_states(batch)
+    assert R.agreement(tr, R.capture(b)) < 0.9     # different routers choose differently
+    R.replay(b, tr)
+    b.hidden_states(batch)
+    assert R.agreement(tr, R.capture(b)) == 1.0
+    R.replay(b, None)
+    assert b.layers[0].mlp.forced_routing is None

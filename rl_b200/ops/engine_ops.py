@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -39,6 +40,9 @@ def decode_scratch_sizes(B: int, Hq: int, num_splits: int, D: int = 128) -> tupl
 
 def choose_splits(B: int, Hkv: int, max_len: int, block_size: int, sm_count: int = 148) -> int:
     """Enough KV splits to put ~2 CTAs on every SM, never finer than one cache block per split."""
+    forced = os.environ.get("RLB_DECODE_SPLITS")
+    if forced:
+        return max(1, int(forced))
     ctas = max(1, B * Hkv)
     want = max(1, (2 * sm_count + ctas - 1) // ctas)
     return int(max(1, min(want, max(1, max_len // max(block_size, 128)), 32)))

@@ -20,7 +20,7 @@ constexpr int PD_TOK = 64;                       // tokens per stage
 constexpr int PD_STAGES = 3;
 constexpr int PD_TILE = PD_TOK * PD_D * 2;       // 16 KB
 constexpr int PD_STAGE_BYTES = 2 * PD_TILE;      // K + V
-constexpr int PD_GS = 8;                         // query heads per consumer thread; smaller values trade registers for more warps (measured slower: 7.8 vs 7.2 ms per Llama-8B decode step at 2)
+constexpr int PD_GS = 4;                         // query heads per consumer thread: groups of 8 heads use two warp sets (no register spills); 2 was measured slower for groups of 4
 constexpr int PD_LANES = 8;                      // lanes per token
 constexpr int PD_GROUPS = 128 / PD_LANES;        // 16 tokens per consumer step
 constexpr int PD_DL = PD_D / PD_LANES;           // 16 dims per lane

@@ -34,6 +34,14 @@ def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
     rank, world = (worker.rank, worker.world)
     fmt = (fmt or "safetensors").lower()
     st = get_state()
+    if getattr(worker, "lora_cfg", None) is not None:
+        # LoRA: the frozen base goes out as a plain HF checkpoint, the adapters next to it in the PEFT file layout
+        if rank == 0:
+            from rl_b200.models.hf_io import save_lora_adapter
+
+            save_pretrained(worker.model, path)
+            save_lora_adapter(worker.model, path)
+        return
     if st.tp * st.pp * st.ep * st.cp > 1:
         # model-parallel layouts always write HF safetensors (one file set per pipeline stage / expert-parallel rank)
         if save_roles(st)[0]:

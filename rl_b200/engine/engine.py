@@ -391,10 +391,7 @@ class GenerationEngine:
     # ------------------------------------------------------------------ model forward (inference)
     def _layer_tail(self, layer, h, a):
         eps = self.cfg.rms_norm_eps
-        if self.tpw == 1:
-            h = F.linear(a, layer.self_attn.o_proj, None, h)
-        else:
-            h = row_linear(a, layer.self_attn.o_proj, h, self.tp)  # GEMM + all-reduce (+ residual) in one kernel
+        h = layer.self_attn.project_out(a, h)  # tp > 1: GEMM + all-reduce (+ residual) in one kernel; adds LoRA deltas
         return layer.mlp(F.rmsnorm(h, layer.post_attention_layernorm, eps), h)
 
     def _output_logits(self, h, out=None):

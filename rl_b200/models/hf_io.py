@@ -241,10 +241,20 @@ class _SafetensorsDir:
 
 
 def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None, strict: bool = True, tp=None, ep=None,
-                    pp_rank: int = 0, pp_size: int = 1, **cfg_overrides) -> CausalLM:
+                    pp_rank: int = 0, pp_size: int = 1, lora: Optional[dict] = None, **cfg_overrides) -> CausalLM:
     """Builds a model (or this rank's tensor / expert / pipeline shard of it) from an HF checkpoint directory."""
     cfg = ModelConfig.from_pretrained(path, **cfg_overrides)
-    model = CausalLM(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size)
+    model = CausalLM(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, lora=lora)
+    if lora:
+        from .transformer import LoRA
+
+        for name, mod in model.named_modules():
+            if isinstance(mod, LoRA):
+                g = torch.Generator(device=mod.lora_A.device)
+                g.manual_seed(hash(name) & 0x7FFFFFFF)
+                mod.reset(g)
+        if os.path.exists(os.path.join(path, "adapter_model.safetensors")):
+            load_lora_adapter(model, path)
     reader = _SafetensorsDir(path)
     get = reader.get
     if cfg.tie_word_embeddings or cfg.value_head:
@@ -257,4 +267,64 @@ def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None
     if cfg.value_head and "score.weight" in missing:
         with torch.no_grad():
             model.score.zero_()
+    return model
+
+
+# --------------------------------------------------------------------------------------------- LoRA adapters (PEFT layout)
+def iter_lora_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
+    """(PEFT tensor name, view) for every enabled adapter: ``base_model.model.<hf module>.lora_{A,B}.weight``."""
+    from .transformer import LoRA
+
+    for mod_name, mod in model.named_modules():
+        if not isinstance(mod, LoRA):
+            continue
+        li = int(mod_name.split(".")[1]) + model.layer_offset
+        parent = "self_attn" if ".self_attn." in mod_name else "mlp"
+        row = 0
+        for s, (seg, n) in enumerate(mod.segments):
+            if mod.enabled[s]:
+                base = f"base_model.model.model.layers.{li}.{parent}.{seg}"
+                yield f"{base}.lora_A.weight", mod.lora_A[s * mod.r : (s + 1) * mod.r]
+                yield f"{base}.lora_B.weight", mod.lora_B[row : row + n]
+            row += n
+
+
+def save_lora_adapter(model: CausalLM, path: str) -> None:
+    """Writes ``adapter_model.safetensors`` + ``adapter_config.json`` (the files PEFT loads)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    sd = {n: t.detach().cpu().contiguous() for n, t in iter_lora_tensors(model)}
+    save_file(sd, os.path.join(path, "adapter_model.safetensors"), metadata={"format": "pt"})
+    c = model.lora_cfg or {}
+    targets = sorted({n.split(".")[-3] for n in sd})
+    with open(os.path.join(path, "adapter_config.json"), "w") as f:
+        json.dump({"peft_type": "LORA", "r": int(c.get("dim", 8)), "lora_alpha": float(c.get("alpha", 32)), "lora_dropout": 0.0,
+                   "target_modules": targets, "bias": "none", "task_type": "CAUSAL_LM"}, f, indent=2)
+
+
+@torch.no_grad()
+def load_lora_adapter(model: CausalLM, path: str) -> None:
+    from safetensors import safe_open
+
+    fn = os.path.join(path, "adapter_model.safetensors")
+    with safe_open(fn, framework="pt") as f:
+        have = set(f.keys())
+        for n, dst in iter_lora_tensors(model):
+            if n in have:
+                dst.copy_(f.get_tensor(n).to(dst.dtype))
+
+
+@torch.no_grad()
+def merge_lora(model: CausalLM) -> CausalLM:
+    """Folds every adapter into its base weight (W += scale * B A) and switches the adapters off: the model then
+    behaves identically without them (export to a plain HF checkpoint, merged serving)."""
+    for layer in model.layers:
+        for owner, wname, lname in ((layer.self_attn, "qkv_proj", "qkv_lora"), (layer.self_attn, "o_proj", "o_lora"),
+                                    (layer.mlp, "gate_up_proj", "gate_up_lora"), (layer.mlp, "down_proj", "down_lora")):
+            lora = getattr(owner, lname, None)
+            if lora is not None:
+                w = getattr(owner, wname)
+                w.copy_(model.merged_weight(w, lora))
+                lora.lora_B.zero_()
     return model

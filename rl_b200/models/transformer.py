@@ -98,15 +98,60 @@ class FlatParams:
             yield n, o, k, s
 
 
+class LoRA(nn.Module):
+    """Low-rank adapters of one fused projection. The fused weight [N_total, K] is a stack of HF projections (segments);
+    every enabled segment s gets its own pair A_s [r, K], B_s [n_s, r] (PEFT-compatible), stored as ``lora_A`` [S*r, K] and
+    ``lora_B`` [N_total, r] (rows of disabled segments stay zero and frozen through a mask). ``delta(x)`` returns
+    scale * B_s A_s x per segment, concatenated along the output dimension
+    (LoRAConfig: nemo_rl/models/policy/__init__.py:95-105)."""
+
+    def __init__(self, segments: list[tuple[str, int]], in_features: int, cfg: dict, dtype, device):
+        super().__init__()
+        r = int(cfg.get("dim", 8))
+        self.r, self.scale = r, float(cfg.get("alpha", 32)) / r
+        targets = cfg.get("target_modules") or []
+        exclude = cfg.get("exclude_modules") or []
+        self.segments = segments
+        self.enabled = [(not targets or n in targets or "all-linear" in targets) and n not in exclude for n, _ in segments]
+        S, N = len(segments), sum(n for _, n in segments)
+        self.lora_A = nn.Parameter(torch.empty(S * r, in_features, dtype=dtype, device=device))
+        self.lora_B = nn.Parameter(torch.zeros(N, r, dtype=dtype, device=device))
+        self.active = True
+
+    @torch.no_grad()
+    def reset(self, gen: torch.Generator) -> None:
+        a = torch.randn(self.lora_A.shape, generator=gen, device=self.lora_A.device, dtype=torch.float32) / math.sqrt(self.lora_A.shape[1])
+        self.lora_A.copy_(a.to(self.lora_A.dtype))
+        self.lora_B.zero_()
+
+    def delta(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        if not self.active or not any(self.enabled):
+            return None
+        t = F.linear(x, self.lora_A)  # [T, S*r]
+        outs, row = [], 0
+        for s, (name, n) in enumerate(self.segments):
+            if self.enabled[s]:
+                outs.append(F.linear(t[:, s * self.r : (s + 1) * self.r].contiguous(), self.lora_B[row : row + n]) * self.scale)
+            else:
+                outs.append(torch.zeros((x.shape[0], n), dtype=x.dtype, device=x.device))
+            row += n
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
+
+
 class Attention(nn.Module):
     """Fused-QKV attention. With tensor parallelism this rank holds ``Hq/tp`` query and ``Hkv/tp`` key/value heads:
     ``qkv_proj`` is column-parallel (rows = local q, k, v heads), ``o_proj`` row-parallel."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, cp=None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, cp=None, lora: Optional[dict] = None):
         super().__init__()
         self.cfg = cfg
         self.tp = tp or TP()
         self.cp = cp if (cp is not None and cp.world > 1) else None
+        self.qkv_lora = self.o_lora = None
+        if lora:
+            assert self.tp.world == 1, "LoRA adapters are not tensor parallel"
+            self.qkv_lora = LoRA([("q_proj", cfg.q_size), ("k_proj", cfg.kv_size), ("v_proj", cfg.kv_size)], cfg.hidden_size, lora, dtype, device)
+            self.o_lora = LoRA([("o_proj", cfg.hidden_size)], cfg.q_size, lora, dtype, device)
         assert self.cp is None or self.tp.world == 1, "context parallelism and tensor parallelism are not combined"
         w = self.tp.world
         assert cfg.num_attention_heads % w == 0 and cfg.num_key_value_heads % w == 0, "heads must divide by the tensor-parallel size"
@@ -125,6 +170,10 @@ class Attention(nn.Module):
         """x [T, d] -> fused [T, (Hq+2Hkv)*D] with q/k normalised (Qwen3) and rotated."""
         c = self.cfg
         qkv = column_linear(x, self.qkv_proj, self.qkv_bias, self.tp)
+        if self.qkv_lora is not None:
+            d = self.qkv_lora.delta(x)
+            if d is not None:
+                qkv = qkv + d
         if c.qk_norm:
             qkv = F.head_rmsnorm(qkv, self.q_norm, 0, self.hq, c.head_dim, c.rms_norm_eps)
             qkv = F.head_rmsnorm(qkv, self.k_norm, self.q_local, self.hkv, c.head_dim, c.rms_norm_eps)
@@ -141,31 +190,55 @@ class Attention(nn.Module):
             return F.linear(a, self.o_proj, None, residual)
         qkv = self.project_qkv(x, positions, inv_freq)
         a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim)
-        return row_linear(a, self.o_proj, residual, self.tp)
+        return self.project_out(a, residual)
+
+    def project_out(self, a, residual):
+        y = row_linear(a, self.o_proj, residual, self.tp)
+        if self.o_lora is not None:
+            d = self.o_lora.delta(a)
+            if d is not None:
+                y = y + d
+        return y
 
 
 class DenseMLP(nn.Module):
     """SwiGLU MLP; ``gate_up_proj`` rows are [local gate | local up] (column-parallel), ``down_proj`` row-parallel."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, lora: Optional[dict] = None):
         super().__init__()
         self.tp = tp or TP()
         assert cfg.intermediate_size % self.tp.world == 0
         d, f = cfg.hidden_size, cfg.intermediate_size // self.tp.world
         self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
+        self.gate_up_lora = self.down_lora = None
+        if lora:
+            assert self.tp.world == 1, "LoRA adapters are not tensor parallel"
+            self.gate_up_lora = LoRA([("gate_proj", f), ("up_proj", f)], d, lora, dtype, device)
+            self.down_lora = LoRA([("down_proj", d)], f, lora, dtype, device)
 
     def forward(self, x, residual):
-        return row_linear(F.swiglu(column_linear(x, self.gate_up_proj, None, self.tp)), self.down_proj, residual, self.tp)
+        h = column_linear(x, self.gate_up_proj, None, self.tp)
+        if self.gate_up_lora is not None:
+            dl = self.gate_up_lora.delta(x)
+            if dl is not None:
+                h = h + dl
+        a = F.swiglu(h)
+        y = row_linear(a, self.down_proj, residual, self.tp)
+        if self.down_lora is not None:
+            dl = self.down_lora.delta(a)
+            if dl is not None:
+                y = y + dl
+        return y
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None, lora: Optional[dict] = None):
         super().__init__()
         self.cfg = cfg
         d = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device, tp, cp)
+        self.self_attn = Attention(cfg, dtype, device, tp, cp, lora)
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if cfg.is_moe:
             from .moe import MoEMLP
@@ -173,7 +246,7 @@ class DecoderLayer(nn.Module):
             assert tp is None or tp.world == 1, "MoE layers shard experts (ep), not tensors"
             self.mlp = MoEMLP(cfg, dtype, device, ep=ep)
         else:
-            self.mlp = DenseMLP(cfg, dtype, device, tp)
+            self.mlp = DenseMLP(cfg, dtype, device, tp, lora)
 
     def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
         eps = self.cfg.rms_norm_eps
@@ -242,9 +315,10 @@ class CausalLM(nn.Module):
 
     def __init__(self, cfg: ModelConfig, dtype: Optional[torch.dtype] = None, device="cpu", init: bool = True,
                  seed: int = 0, activation_checkpointing: bool = False, tp: Optional[TP] = None, ep=None,
-                 pp_rank: int = 0, pp_size: int = 1, cp=None):
+                 pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None):
         super().__init__()
         self.cfg = cfg
+        self.lora_cfg = dict(lora) if (lora and lora.get("enabled", True)) else None
         dtype = dtype or _dtype_of(cfg.torch_dtype)
         self.dtype = dtype
         self.tp = tp or TP()
@@ -266,7 +340,7 @@ class CausalLM(nn.Module):
             self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
         else:
             self.embed_tokens = None
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp) for _ in range(n_local)])
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg) for _ in range(n_local)])
         self.lm_head = None
         if self.last_stage:
             self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
@@ -307,6 +381,11 @@ class CausalLM(nn.Module):
                 p.fill_(1.0)
             elif name.endswith("bias"):
                 p.zero_()
+        for name, mod in self.named_modules():
+            if isinstance(mod, LoRA):
+                g = torch.Generator(device=mod.lora_A.device)
+                g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
+                mod.reset(g)
         for hf, dst, hs in iter_hf_shards(self):
             if hf.endswith("norm.weight") or hf.endswith("layernorm.weight") or hf.endswith(".bias"):
                 continue
@@ -333,6 +412,27 @@ class CausalLM(nn.Module):
         if include is None or self.flat is None:
             self.flat = fl
         return fl
+
+    @staticmethod
+    def is_lora_param(name: str) -> bool:
+        return name.endswith(".lora_A") or name.endswith(".lora_B")
+
+    def set_adapters(self, active: bool) -> None:
+        """Switches every LoRA adapter on or off (off = the frozen base model, i.e. the reference policy)."""
+        for mod in self.modules():
+            if isinstance(mod, LoRA):
+                mod.active = active
+
+    @torch.no_grad()
+    def merged_weight(self, fused: torch.Tensor, lora: "LoRA") -> torch.Tensor:
+        """W + scale * B A for a fused projection (export / merged serving)."""
+        w = fused.float().clone()
+        row = 0
+        for s, (_, n) in enumerate(lora.segments):
+            if lora.enabled[s]:
+                w[row : row + n] += lora.scale * (lora.lora_B[row : row + n].float() @ lora.lora_A[s * lora.r : (s + 1) * lora.r].float())
+            row += n
+        return w.to(fused.dtype)
 
     @staticmethod
     def is_expert_param(name: str) -> bool:
@@ -435,6 +535,6 @@ class CausalLM(nn.Module):
 
 def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
                 activation_checkpointing: bool = False, init: bool = True, tp: Optional[TP] = None, ep=None,
-                pp_rank: int = 0, pp_size: int = 1, cp=None) -> CausalLM:
+                pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None) -> CausalLM:
     return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
-                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp)
+                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp, lora=lora)

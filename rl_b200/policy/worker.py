@@ -148,19 +148,22 @@ class PolicyWorker:
         from rl_b200.parallel.context import CP
 
         self.cp = CP.from_state(st)
+        lora = cfg.get("lora_cfg") or (cfg.get("dtensor_cfg") or {}).get("lora_cfg") or ((cfg.get("megatron_cfg") or {}).get("peft"))
+        self.lora_cfg = dict(lora) if (lora and lora.get("enabled")) else None
         mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp, cp=self.cp)
         if weights_path:
             from rl_b200.models.hf_io import load_pretrained
 
-            self.model = load_pretrained(weights_path, device=self.device, dtype=dtype, **mp)
+            self.model = load_pretrained(weights_path, device=self.device, dtype=dtype, lora=self.lora_cfg, **mp)
             self.model.activation_checkpointing = act_ckpt
         else:
-            self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt, **mp)
+            self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt,
+                                     lora=self.lora_cfg, **mp)
         # On several GPUs of one node the flat parameter / gradient buffers live in peer-mapped memory so that the
         # optimizer step can run as one fused kernel over NVLink (rl_b200/csrc/comm.cu); NCCL is the fallback.
         model_parallel = st.tp * st.pp * st.cp * st.ep > 1
         if fused_comm is None and self.world > 1 and self.device.type == "cuda" and cfg.get("fused_optimizer", True) \
-                and dtype == torch.bfloat16 and init_optimizer and not model_parallel:
+                and dtype == torch.bfloat16 and init_optimizer and not model_parallel and self.lora_cfg is None:
             try:
                 from rl_b200.parallel.symmetric import FusedOptimizerComm
 
@@ -187,8 +190,18 @@ class PolicyWorker:
                 print(f"[policy] fused expert-parallel dispatch unavailable ({type(e).__name__}: {e}); using NCCL all-to-all")
         self.ep.comm = st.ep_comm
         dense = (lambda n: not CausalLM.is_expert_param(n)) if split_experts else None
+        self.flat_base = None
+        if self.lora_cfg is not None:
+            # LoRA: the base weights are frozen (no gradient buffer, no optimizer state, and they double as the reference
+            # policy with the adapters switched off); only the adapters are trained
+            assert not split_experts, "LoRA with expert parallelism is not supported"
+            self.flat_base = self.model.flatten_parameters(align=256, include=lambda n: not CausalLM.is_lora_param(n))
+            for p_ in self.flat_base.params:
+                p_.requires_grad_(False)
+            dense = CausalLM.is_lora_param
         self.flat = self.model.flatten_parameters(align=256 * max(1, self.world),
-                                                  allocator=fused_comm.alloc_params if fused_comm is not None else None, include=dense)
+                                                  allocator=fused_comm.alloc_params if (fused_comm is not None and self.lora_cfg is None) else None,
+                                                  include=dense)
         self.flat_e = None
         e_group, e_world = None, 1
         if split_experts:
@@ -196,7 +209,8 @@ class PolicyWorker:
             self.flat_e = self.model.flatten_parameters(align=256 * max(1, e_world), include=CausalLM.is_expert_param)
         self.ref_flat: Optional[torch.Tensor] = None
         self.ref_flat_e: Optional[torch.Tensor] = None
-        if init_reference_model:
+        self._has_reference = bool(init_reference_model)
+        if init_reference_model and self.lora_cfg is None:
             # the reference policy stays resident in HBM as a second flat buffer (no CPU swap)
             self.ref_flat = self.flat.flat.clone()
             if self.flat_e is not None:
@@ -343,7 +357,15 @@ class PolicyWorker:
 
     @contextlib.contextmanager
     def use_reference_weights(self):
-        """Runs the model on the reference policy's weights by re-pointing every parameter at the second buffer."""
+        """Runs the model on the reference policy's weights by re-pointing every parameter at the second buffer (LoRA:
+        by switching the adapters off)."""
+        if self.lora_cfg is not None:
+            self.model.set_adapters(False)
+            try:
+                yield
+            finally:
+                self.model.set_adapters(True)
+            return
         assert self.ref_flat is not None, "the worker was built without a reference model"
         pairs = [(self.flat, self.ref_flat)] + ([(self.flat_e, self.ref_flat_e)] if self.flat_e is not None else [])
         try:

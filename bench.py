@@ -43,8 +43,11 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--max-new-tokens", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (makes the run invalid as a benchmark)")
-    ap.add_argument("--train-mb-tokens", type=int, default=10240)
+    ap.add_argument("--train-mb-tokens", type=int, default=0, help="tokens per training micro-batch (0: 5120 on 1 GPU, 10240 otherwise)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--act-ckpt", default="auto", choices=["auto", "on", "off"],
+                    help="activation checkpointing in training (auto = off: with 5120-token micro-batches the activations of "
+                         "Llama-3.1-8B fit next to the unsharded optimizer state even on 1 GPU)")
     return ap.parse_args()
 
 
@@ -167,6 +170,7 @@ def main() -> int:
     seqs_per_gpu = args.prompts_per_gpu * n_gen
     max_len = args.prompt_len + args.max_new_tokens
     steps_needed = args.warmup + 2 * args.steps + 2
+    mb_tokens = args.train_mb_tokens or (5120 if world == 1 else 10240)
     cfg = {
         "grpo": dict(num_prompts_per_step=n_prompts, num_generations_per_prompt=n_gen, max_num_steps=10**9, val_period=0, seed=0,
                      normalize_rewards=True, use_leave_one_out_baseline=True),
@@ -174,8 +178,8 @@ def main() -> int:
         "policy": dict(
             model_name=None, precision="bfloat16", train_global_batch_size=seqs_per_gpu * world, train_micro_batch_size=4,
             logprob_batch_size=8, max_total_sequence_length=max_len, max_grad_norm=1.0,
-            activation_checkpointing=(world == 1), grad_dtype="float32",
-            sequence_packing=dict(enabled=True, train_mb_tokens=args.train_mb_tokens, logprob_mb_tokens=2 * args.train_mb_tokens,
+            activation_checkpointing=(args.act_ckpt == "on"), grad_dtype="float32",
+            sequence_packing=dict(enabled=True, train_mb_tokens=mb_tokens, logprob_mb_tokens=20480,
                                   algorithm="modified_first_fit_decreasing"),
             optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=3e-7, weight_decay=0.01, betas=[0.9, 0.999], eps=1e-8)),
             generation=dict(max_new_tokens=args.max_new_tokens, temperature=1.0, top_p=1.0, top_k=None, stop_token_ids=[],

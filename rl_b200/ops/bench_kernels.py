@@ -101,6 +101,48 @@ def bench_mxfp8(shapes=None):
     return rows
 
 
+def bench_grouped():
+    """Grouped expert MLP GEMMs (Qwen3-30B-A3B: 16 local experts, d 2048, expert ffn 768) against a per-expert loop of
+    library GEMMs (torch.matmul), forward gate_up + down, uneven expert loads."""
+    from .moe_ops import ExpertLayout, grouped_linear
+
+    peak_tf, _, how = _peaks()
+    rows = []
+    E, d, f = 16, 2048, 768
+    for total in (16384, 65536):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        w = torch.rand(E, generator=g, device="cuda") + 0.25
+        counts = torch.floor(w / w.sum() * total).to(torch.int64)
+        counts[0] += total - counts.sum()
+        xs = torch.randn(total, d, device="cuda", dtype=torch.bfloat16)
+        gu = torch.randn(E, 2 * f, d, device="cuda", dtype=torch.bfloat16) * 0.02
+        dn = torch.randn(E, d, f, device="cuda", dtype=torch.bfloat16) * 0.02
+        lay = ExpertLayout(counts, total)
+        xp = torch.zeros((lay.mpad, d), dtype=torch.bfloat16, device="cuda").index_copy(0, lay.dest, xs)
+        ap = torch.randn(lay.mpad, f, device="cuda", dtype=torch.bfloat16)
+        cl = counts.tolist()
+
+        def ours(i):
+            with torch.no_grad():
+                grouped_linear(xp, gu, lay)
+                grouped_linear(ap, dn, lay)
+
+        def lib(i):
+            s0 = 0
+            for e, c in enumerate(cl):
+                torch.matmul(xs[s0 : s0 + c], gu[e].t())
+                torch.matmul(ap[s0 : s0 + c], dn[e].t())
+                s0 += c
+
+        ms, ms_lib = time_fn(ours, 1), time_fn(lib, 1)
+        flops = 2.0 * total * d * 2 * f + 2.0 * total * f * d
+        rows.append(dict(kernel="gemm_grouped(gate_up+down)", experts=E, rows=total, d=d, f=f, ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                         frac_of_peak=round(flops / ms / 1e9 / peak_tf, 3), peak=how, per_expert_loop_ms=round(ms_lib, 4),
+                         vs_loop=round(ms_lib / ms, 3)))
+        print(rows[-1], flush=True)
+    return rows
+
+
 def bench_memory_bound():
     _, hbm, how = _peaks()
     rows = []
@@ -147,6 +189,8 @@ def main(argv=None):
         out += bench_gemm(shapes)
     if "mx" in which:
         out += bench_mxfp8()
+    if "grouped" in which:
+        out += bench_grouped()
     if "mem" in which:
         out += bench_memory_bound()
     if a.json:

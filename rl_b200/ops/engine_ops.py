@@ -80,8 +80,15 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
             scratch = (torch.empty(no, dtype=torch.float32, device=q.device),
                        torch.empty(nml, dtype=torch.float32, device=q.device))
         po, pml = scratch
+    kernel = os.environ.get("RLB_DECODE_KERNEL", "mma")
+    if kernel == "mma" and D == 128 and Hq // Hkv <= 8 and (block_size in (16, 32, 64) or block_size % 128 == 0):
+        # tensor-core flash-decoding kernel (tcgen05: QK^T and PV as MMAs over 128-token tiles)
+        call("rlb_paged_decode_mma", ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache), k_cache.shape[0], ptr(block_table),
+             block_table.stride(0), ptr(seq_lens), B, Hq, Hkv, D, block_size, scale, num_splits, ptr(po), ptr(pml), ptr(out),
+             out.stride(0), ptr(_L.status_word(q.device)), stream_ptr())
+        return out
     if block_size in (16, 32) or block_size % 64 == 0:
-        # TMA-pipelined kernel (the plain-load kernel below remains for other block sizes)
+        # CUDA-core TMA-pipelined kernel (the plain-load kernel below remains for other block sizes)
         call("rlb_paged_decode_tma", ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache), k_cache.shape[0], ptr(block_table),
              block_table.stride(0), ptr(seq_lens), B, Hq, Hkv, D, block_size, scale, num_splits, ptr(po), ptr(pml), ptr(out),
              out.stride(0), ptr(_L.status_word(q.device)), stream_ptr())

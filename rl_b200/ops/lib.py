@@ -53,6 +53,7 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_kv_cache_write": [P, P, P, P, L, I, I, I, I, L, P],
     "rlb_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
     "rlb_paged_decode_tma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
+    "rlb_paged_decode_mma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
     "rlb_sample": [P, I, L, I, I, P, P, P, F, I, F, I, U64, U64, P, P, P, P, P],
     "rlb_block_copy": [P, P, P, P, I, L, P],
     "rlb_gather_rows": [P, P, P, L, I, L, L, P],

@@ -395,6 +395,25 @@ class PolicyWorker:
                 idx = list(range(s, min(n, s + mbs)))
                 yield data.slice(s, min(n, s + mbs)), idx
 
+    def _extra_passes(self, n_local: int) -> int:
+        """Expert parallelism: every forward pass exchanges tokens inside the expert group, so its ranks must run the same
+        number of passes although they hold different data. Returns how many dummy passes this rank has to add
+        (the reference equalises micro-batch counts with zero-weight dummies as well: nemo_rl/models/automodel/data.py:201-254)."""
+        if self.ep.world <= 1 or not self.model_cfg.is_moe:
+            return 0
+        t = torch.tensor([n_local], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ep.group)
+        return int(t.item()) - n_local
+
+    def _dummy_pass(self, backward: bool) -> None:
+        """One forward (+ backward) over a few padding tokens whose loss weight is zero."""
+        ids = torch.zeros((1, 8), dtype=torch.long)
+        batch, _ = self._pack(BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([8])))
+        with torch.set_grad_enabled(backward):
+            lp, _ = self.model.next_token_logprobs(batch, self.temperature)
+            if backward:
+                (lp.sum() * 0.0).backward()
+
     def _token_budget(self, kind: str) -> Optional[int]:
         sp = self.cfg.get("sequence_packing") or {}
         db = self.cfg.get("dynamic_batching") or {}
@@ -436,10 +455,14 @@ class PolicyWorker:
             for (batch, Smb, idx), lp in zip(items, lps):
                 out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
             return out
-        for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob")):
+        mbl = list(self._microbatches(data, mbs, self._token_budget("logprob")))
+        extra = self._extra_passes(len(mbl))  # agreed before the first pass: the count exchange is itself a collective
+        for mb, idx in mbl:
             batch, Smb = self._pack(mb)
             lp, _ = self.model.next_token_logprobs(batch, self.temperature)
             out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
+        for _ in range(extra):
+            self._dummy_pass(backward=False)
         return out
 
     def get_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
@@ -539,7 +562,10 @@ class PolicyWorker:
                 gb_loss, mbm, ntok = self._pipeline_global_batch(gb, mbs, budget, loss_fn, eval_mode, global_valid_seqs, global_valid_toks)
                 all_mb_metrics.extend(mbm)
                 total_tokens += ntok
-            for mb, _ in (self._microbatches(gb, mbs, budget) if self.pipeline is None else ()):
+            mbl = list(self._microbatches(gb, mbs, budget)) if self.pipeline is None else []
+            for _ in range(self._extra_passes(len(mbl)) if self.pipeline is None else 0):
+                self._dummy_pass(backward=not eval_mode)
+            for mb, _ in mbl:
                 batch, S = self._pack(mb)
                 mb_dev = BatchedDataDict({k: (to_device(v, self.device) if isinstance(v, torch.Tensor) else v)
                                           for k, v in mb.items() if k != "input_ids"})

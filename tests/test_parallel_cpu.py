@@ -411,3 +411,26 @@ def test_generation_with_a_different_tensor_parallel_size(tp_train, tp_serve):
             assert out[rank][it] == ref, (rank, it)
             with torch.no_grad():
                 w.flat.flat.mul_(1.25)
+
+
+def _ep_uneven_worker(rank, world):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.policy.worker import PolicyWorker
+
+    cfg = _worker_cfg(expert_parallel_size=world)
+    cfg.update(train_global_batch_size=6, train_micro_batch_size=1, logprob_batch_size=1)
+    w = PolicyWorker(cfg, model_cfg=_moe_cfg(), init_reference_model=False, seed=4)
+    n = 1 + 4 * rank  # rank 0 has one sample (one micro-batch), rank 1 five
+    g = torch.Generator().manual_seed(rank)
+    data = BatchedDataDict(input_ids=torch.randint(0, 2048, (n, 12), generator=g), input_lengths=torch.full((n,), 12),
+                           token_mask=torch.ones(n, 12), sample_mask=torch.ones(n))
+    lp = w.get_logprobs(data)["logprobs"]
+    out = w.train(data, NLLLossFn(), gbs=2 * n, mbs=1)   # one optimizer step over each rank's samples
+    return dict(lp=float(lp.sum()), loss=float(out["loss"][0]), gn=float(out["grad_norm"][0]))
+
+
+def test_expert_parallel_ranks_with_unequal_microbatch_counts_do_not_deadlock():
+    out = _spawn(_ep_uneven_worker, 2)
+    assert out[0]["loss"] == pytest.approx(out[1]["loss"]) and out[0]["gn"] == pytest.approx(out[1]["gn"], rel=1e-4)
+    assert all(abs(m["lp"]) > 0 for m in out.values())

@@ -299,6 +299,19 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf8_e4m3(int m, int n) {
          | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with rlb_launch_pdl may begin while its predecessor on the stream is still draining. It must run
+// pdl_wait() before its first access to global memory (the wait returns once the predecessor has completed and its
+// writes are visible); what stands before the wait (barrier init, TMEM allocation, descriptor prefetch) overlaps the
+// predecessor's tail. pdl_trigger() after the wait lets the successor start the same way. Both are no-ops in a kernel
+// that was launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+  pdl_wait();
+  pdl_trigger();
+}
+
 // ---------------------------------------------------------------- numerics
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -354,3 +367,23 @@ RlbEncodeTiledFn rlb_get_encode_tiled();
 int rlb_make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, int elem_bytes,
                      uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,
                      uint32_t box_outer, CUtensorMapSwizzle swizzle);
+
+// Whether kernels that support it are launched with programmatic stream serialization (RLB_PDL=0 turns it off).
+bool rlb_pdl_enabled();
+// Launches `kernel` so that it may overlap the tail of its predecessor (see pdl_wait). `extra` attributes (a cluster
+// dimension, for instance) are passed through.
+template <typename... KArgs, typename... Args>
+inline cudaError_t rlb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = rlb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -39,6 +39,7 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out,
                                    int d, long long x_stride, long long y_stride, float eps) {
+  pdl_sync();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * x_stride;
@@ -153,6 +154,7 @@ __global__ void colsum_kernel(const float* __restrict__ partial, int parts, int 
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos,
                             const float* __restrict__ inv_freq, long long rows, int heads, int D,
                             long long row_stride, float sign) {
+  pdl_sync();
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= rows * heads) return;
@@ -180,6 +182,7 @@ __global__ void head_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, con
                                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
                                         long long rows, int heads, int D, long long x_stride,
                                         long long y_stride, float eps) {
+  pdl_sync();
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= rows * heads) return;
@@ -240,6 +243,7 @@ __global__ void head_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, co
 // gu: [rows, 2F] (gate | up). y[rows, F] = silu(gate) * up.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y,
                                   long long rows, int F) {
+  pdl_sync();
   const long long vecs_per_row = F / 8;
   const long long total = rows * vecs_per_row;
   for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
@@ -281,6 +285,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
 // ------------------------------------------------------------------ embedding
 __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, long long rows, int d, int vocab) {
+  pdl_sync();
   const long long vecs_per_row = d / 8;
   const long long total = rows * vecs_per_row;
   for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
@@ -610,7 +615,7 @@ RLB_API int rlb_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
                             void* stream) {
   if (rows <= 0) return 0;
   if (d % 8 || x_stride % 8 || y_stride % 8) return -2;
-  rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), rms_threads(d), 0, S(stream)>>>(
+  rlb_launch_pdl(rmsnorm_fwd_kernel, dim3(static_cast<unsigned>(rows)), dim3(rms_threads(d)), 0, S(stream), 
       CBF(x), CBF(res), CBF(w), BF(y), BF(res_out), rstd, d, x_stride, y_stride, eps);
   return static_cast<int>(cudaGetLastError());
 }
@@ -641,7 +646,7 @@ RLB_API int rlb_rope(void* x, const int* pos, const float* inv_freq, long long r
   const long long warps = rows * heads;
   const int threads = 256;
   const long long blocks = (warps * 32 + threads - 1) / threads;
-  rope_kernel<<<static_cast<unsigned>(blocks), threads, 0, S(stream)>>>(BF(x), pos, inv_freq, rows, heads, D,
+  rlb_launch_pdl(rope_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, S(stream), BF(x), pos, inv_freq, rows, heads, D,
                                                                          row_stride, backward ? -1.f : 1.f);
   return static_cast<int>(cudaGetLastError());
 }
@@ -651,7 +656,7 @@ RLB_API int rlb_head_rmsnorm_fwd(const void* x, const void* w, void* y, float* r
   if (rows <= 0) return 0;
   if (D % 2) return -2;
   const long long blocks = (rows * heads * 32 + 255) / 256;
-  head_rmsnorm_fwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, S(stream)>>>(CBF(x), CBF(w), BF(y), rstd, rows,
+  rlb_launch_pdl(head_rmsnorm_fwd_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, S(stream), CBF(x), CBF(w), BF(y), rstd, rows,
                                                                                  heads, D, x_stride, y_stride, eps);
   return static_cast<int>(cudaGetLastError());
 }
@@ -668,7 +673,7 @@ RLB_API int rlb_head_rmsnorm_bwd(const void* dy, const void* x, const void* w, c
 RLB_API int rlb_swiglu_fwd(const void* gu, void* y, long long rows, int F, void* stream) {
   if (rows <= 0) return 0;
   if (F % 8) return -2;
-  swiglu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, S(stream)>>>(CBF(gu), BF(y), rows, F);
+  rlb_launch_pdl(swiglu_fwd_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, S(stream), CBF(gu), BF(y), rows, F);
   return static_cast<int>(cudaGetLastError());
 }
 RLB_API int rlb_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long rows, int F, void* stream) {
@@ -682,7 +687,7 @@ RLB_API int rlb_embedding_fwd(const int* ids, const void* table, void* out, long
                               void* stream) {
   if (rows <= 0) return 0;
   if (d % 8) return -2;
-  embedding_fwd_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, S(stream)>>>(ids, CBF(table), BF(out), rows, d,
+  rlb_launch_pdl(embedding_fwd_kernel, dim3(grid_for(rows * (d / 8), 256)), dim3(256), 0, S(stream), ids, CBF(table), BF(out), rows, d,
                                                                              vocab);
   return static_cast<int>(cudaGetLastError());
 }

@@ -48,6 +48,7 @@ struct SkinnyParams {
   long long ldr;
   int M, N, K;
   int out_fp32;
+  int w_static;  // W is not written by the kernel that precedes this one on the stream: its stream may start early
   int* status;
 };
 
@@ -102,6 +103,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     mbar_fence_init();
     fence_proxy_async();
   }
+  const bool have_work = kb_end > kb_begin && aligned;
+  // Weights that the preceding kernel cannot have written are requested before the dependency wait: the first ring
+  // stages fill while that kernel drains. The activations of the same stages follow after the wait.
+  int early = 0;
+  if (threadIdx.x == 0 && have_work) {
+    prefetch_tmap(&tmap_w);
+    prefetch_tmap(&tmap_x);
+    if (p.w_static) {
+      for (; early < Cfg::STAGES && kb_begin + early < kb_end; ++early) {
+        const uint32_t bar = smem_u32(&full_bar[early]);
+        mbar_arrive_expect_tx(bar, Cfg::STAGE);
+        tma_load_2d(smem_u32(smem + early * Cfg::STAGE), &tmap_w, bar, (kb_begin + early) * SK_BK, n_blk * SK_BM);
+      }
+    }
+  }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM);
     tmem_relinquish();
@@ -110,14 +126,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
-  const bool have_work = kb_end > kb_begin && aligned;
+  pdl_sync();  // everything above overlaps the tail of the previous kernel on the stream
 
   if (warp == 0) {
     if (lane == 0 && have_work) {
-      prefetch_tmap(&tmap_w);
-      prefetch_tmap(&tmap_x);
-      uint32_t stage = 0, phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      for (int e = 0; e < early; ++e)
+        tma_load_2d(smem_u32(smem + e * Cfg::STAGE) + Cfg::A_BYTES, &tmap_x, smem_u32(&full_bar[e]), (kb_begin + e) * SK_BK, 0);
+      uint32_t stage = early == Cfg::STAGES ? 0 : early, phase = early == Cfg::STAGES ? 1 : 0;
+      for (int kb = kb_begin + early; kb < kb_end; ++kb) {
         if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, RLB_ERR_WAIT_EMPTY)) break;
         const uint32_t bar = smem_u32(&full_bar[stage]);
         const uint32_t a_dst = smem_u32(smem + stage * Cfg::STAGE);
@@ -227,6 +243,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 }
 
 int g_sk_sms = 0;
+int g_sk_static_w = 0;
 
 template <int NT>
 int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, int split, cudaStream_t stream) {
@@ -244,13 +261,15 @@ int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyPara
   cfg.blockDim = dim3(SK_THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = split;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = rlb_pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return static_cast<int>(e);
 }
@@ -275,6 +294,15 @@ RLB_API int rlb_gemm_skinny_split(int N, int K) {
     best = s;
   }
   return best;
+}
+
+// While set, callers promise that the W operand of every skinny GEMM was not written by the kernel launched just before
+// it on the same stream (true for model weights during generation); the kernel then starts streaming W while that
+// kernel is still draining. Returns the previous value.
+RLB_API int rlb_gemm_skinny_static_weights(int on) {
+  const int prev = g_sk_static_w;
+  g_sk_static_w = on ? 1 : 0;
+  return prev;
 }
 
 // Y[M, N] = X[M, K] W[N, K]^T (+ bias) (+ residual); M <= 256. ldx / ldw / ldy / ldr in elements (multiples of 8;
@@ -305,6 +333,7 @@ RLB_API int rlb_gemm_skinny(const void* X, const void* W, void* Y, int M, int N,
   p.N = N;
   p.K = K;
   p.out_fp32 = out_fp32;
+  p.w_static = g_sk_static_w;
   p.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (NT) {

@@ -25,6 +25,8 @@
 // (nemo_rl/distributed/model_utils.py:2137-2316).
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <math.h>
 #include <stdio.h>
 
@@ -465,6 +467,15 @@ int make_operand_maps(const void* A, const void* B, int M, int N, int K, long lo
 }  // namespace
 
 // ---------------------------------------------------------------- host helpers (shared by all .cu files)
+bool rlb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("RLB_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 RlbEncodeTiledFn rlb_get_encode_tiled() {
   static RlbEncodeTiledFn fn = nullptr;
   if (!fn) {

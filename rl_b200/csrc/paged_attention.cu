@@ -22,6 +22,7 @@ using namespace rlb;
 __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ slots,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       long long T, int Hq, int Hkv, int D, int block_size, long long row_stride) {
+  pdl_sync();
   const int vec_per_row = Hkv * D / 8;
   const long long total = T * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -302,7 +303,7 @@ RLB_API int rlb_kv_cache_write(const void* qkv, const long long* slots, void* k_
   const long long total = T * (Hkv * D / 8);
   long long grid = (total + 255) / 256;
   if (grid > 148 * 8) grid = 148 * 8;
-  kv_cache_write_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  rlb_launch_pdl(kv_cache_write_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(qkv), slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
       reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride);
   return static_cast<int>(cudaGetLastError());

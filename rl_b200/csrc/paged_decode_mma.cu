@@ -81,16 +81,8 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-  const int G = p.G, Hq = p.Hkv * G;
-  const int len = p.seq_lens[seq];
-  const int bs = p.block_size;
-  const int per_split = ((len + p.num_splits - 1) / p.num_splits + DM_TOK - 1) / DM_TOK * DM_TOK;
-  const int t_begin = split * per_split;
-  const int t_end = min(len, t_begin + per_split);
-  const int n_tiles = t_end > t_begin ? (t_end - t_begin + DM_TOK - 1) / DM_TOK : 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
+  // Set-up that touches no global memory runs before the dependency wait and overlaps the previous kernel's tail.
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(k_full), 1);
     mbar_init(smem_u32(k_empty), 1);
@@ -103,7 +95,24 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     mbar_init(smem_u32(o_empty), 4);
     *abort_flag = 0;
     mbar_fence_init();
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
   }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), DM_TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_sync();
+
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int G = p.G, Hq = p.Hkv * G;
+  const int len = p.seq_lens[seq];
+  const int bs = p.block_size;
+  const int per_split = ((len + p.num_splits - 1) / p.num_splits + DM_TOK - 1) / DM_TOK * DM_TOK;
+  const int t_begin = split * per_split;
+  const int t_end = min(len, t_begin + per_split);
+  const int n_tiles = t_end > t_begin ? (t_end - t_begin + DM_TOK - 1) / DM_TOK : 0;
+
   // Q (pre-scaled) and a zeroed P^T, both in the swizzled K-major operand layout: 256 pieces of 16 bytes each
   for (int i = threadIdx.x; i < 2 * DM_QP_BYTES / 16; i += DM_THREADS) {
     uint4 val = make_uint4(0, 0, 0, 0);
@@ -126,14 +135,6 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     *reinterpret_cast<uint4*>(base + sw128_off(g, piece * 8, DM_N * 128)) = val;
   }
   fence_proxy_async();
-  if (warp == 0 && lane == 0) {
-    prefetch_tmap(&tmap_k);
-    prefetch_tmap(&tmap_v);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), DM_TMEM_COLS);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -315,6 +316,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
 
 __global__ void dm_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int num_splits, int Hq,
                                   __nv_bfloat16* __restrict__ out, long long out_stride) {
+  pdl_sync();
   const int seq = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
   const long long base = (static_cast<long long>(seq) * Hq + hq) * num_splits;
   float mm = -INFINITY;
@@ -373,10 +375,10 @@ RLB_API int rlb_paged_decode_mma(const void* q, long long q_stride, const void* 
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(B, Hkv, num_splits);
-  paged_decode_mma_kernel<<<grid, DM_THREADS, DM_SMEM, s>>>(tk, tv, p);
+  rlb_launch_pdl(paged_decode_mma_kernel, grid, dim3(DM_THREADS), DM_SMEM, s, tk, tv, p);
   if (num_splits > 1) {
     dim3 g2(B, Hq);
-    dm_combine_kernel<<<g2, DM_D, 0, s>>>(part_o, part_ml, num_splits, Hq, static_cast<__nv_bfloat16*>(out), out_stride);
+    rlb_launch_pdl(dm_combine_kernel, g2, dim3(DM_D), 0, s, part_o, part_ml, num_splits, Hq, static_cast<__nv_bfloat16*>(out), out_stride);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -13,6 +13,7 @@ position ``n = cached tokens``, writes its K/V into slot n and attends over n + 
 
 from __future__ import annotations
 
+import os
 import ctypes as C
 import time
 from dataclasses import dataclass, field
@@ -550,9 +551,13 @@ class GenerationEngine:
         saved = self.tp.sequence_parallel if self.tp is not None else False
         if self.tp is not None:
             self.tp.sequence_parallel = False
+        # no kernel of a generation phase writes a weight, so the decode GEMMs may start their weight stream early
+        prev_static = E.skinny_static_weights(os.environ.get("RLB_SKINNY_EARLY_WEIGHTS", "1") != "0") if self.native else 0
         try:
             return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids)
         finally:
+            if self.native:
+                E.skinny_static_weights(bool(prev_static))
             if self.tp is not None:
                 self.tp.sequence_parallel = saved
 

@@ -38,6 +38,14 @@ def decode_scratch_sizes(B: int, Hq: int, num_splits: int, D: int = 128) -> tupl
     return B * Hq * num_splits * D, B * Hq * num_splits * 2
 
 
+def skinny_static_weights(on: bool) -> int:
+    """Tells the decode GEMM whether its weight operand is never written by the kernel launched just before it (true during a
+    generation phase); returns the previous setting."""
+    from .lib import lib
+
+    return int(lib().rlb_gemm_skinny_static_weights(1 if on else 0))
+
+
 def choose_splits(B: int, Hkv: int, max_len: int, block_size: int, sm_count: int = 148) -> int:
     """Enough KV splits to put ~2 CTAs on every SM, never finer than one cache block per split."""
     forced = os.environ.get("RLB_DECODE_SPLITS")

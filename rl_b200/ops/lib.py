@@ -30,6 +30,7 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_gemm_num_n_tiles": [I],
     "rlb_gemm_skinny": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, P, P],
     "rlb_gemm_skinny_split": [I, I],
+    "rlb_gemm_skinny_static_weights": [I],
     "rlb_lm_head_logprob": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P, P, P, P],
     "rlb_logprob_combine": [P, P, P, P, I, I, P, P, P, P],
     "rlb_lm_head_partials": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P],

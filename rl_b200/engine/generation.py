@@ -171,3 +171,13 @@ class NativeGeneration:
 
     def stats(self) -> dict[str, Any]:
         return dict(self.engine.stats)
+
+    def serve_http(self, host: str = "127.0.0.1", port: int = 0, model_name: str = "policy"):
+        """Exposes this engine through the OpenAI-compatible front end (``generation.expose_http_server`` in the
+        reference's vLLM config); external agents then roll out against the weights the trainer keeps refitting. The
+        returned handle has ``base_url``, ``begin_weight_update`` / ``end_weight_update`` and ``stop``."""
+        from .http_server import ServerHandle, create_app
+
+        self._http = ServerHandle(create_app(self.engine, self.tokenizer, model_name=model_name,
+                                             default_max_tokens=int(self.cfg["max_new_tokens"])), host, port).start()
+        return self._http

@@ -1,0 +1,108 @@
+"""OpenAI-compatible front end of the engine and the failover router, on the CPU engine path."""
+
+import threading
+
+import pytest
+import requests
+import torch
+
+from rl_b200.data.tokenizers import ByteTokenizer
+from rl_b200.distributed.health import HealthPolicy, ShardState
+from rl_b200.engine.engine import GenerationEngine
+from rl_b200.engine.http_server import ServerHandle, create_app
+from rl_b200.engine.router import GenerationRouter, NoHealthyShardError, create_router_app
+from rl_b200.models.config import ModelConfig
+from rl_b200.models.transformer import CausalLM
+
+
+def _server(seed=1):
+    tok = ByteTokenizer(vocab_size=300)
+    mc = ModelConfig(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=seed)
+    eng = GenerationEngine(model, block_size=4, num_blocks=256, max_running=16, max_model_len=128, use_cuda_graphs=False)
+    return ServerHandle(create_app(eng, tok, model_name="tiny")).start(), tok
+
+
+def test_completions_token_in_token_out_and_batching():
+    srv, tok = _server()
+    try:
+        base = srv.base_url
+        assert requests.get(base + "/health").json()["status"] == "ok"
+        assert requests.get(base + "/v1/models").json()["data"][0]["id"] == "tiny"
+        ids = requests.post(base + "/tokenize", json={"prompt": "hello"}).json()
+        assert ids["tokens"] == tok.encode("hello") and ids["count"] == len(ids["tokens"])
+        body = dict(prompt="hello", max_tokens=5, n=3, logprobs=1, ignore_eos=True, temperature=0.7)
+        out = requests.post(base + "/v1/completions", json=body).json()
+        assert len(out["choices"]) == 3 and out["usage"]["completion_tokens"] == 15
+        for c in out["choices"]:
+            assert c["prompt_token_ids"] == tok.encode("hello") and len(c["token_ids"]) == 5
+            assert len(c["logprobs"]["token_logprobs"]) == 5 and all(x <= 0 for x in c["logprobs"]["token_logprobs"])
+            assert c["finish_reason"] == "length"
+        # token-in prompt, greedy: the same request twice gives the same tokens
+        g = dict(prompt=[5, 6, 7, 8], max_tokens=4, temperature=0, ignore_eos=True)
+        a = requests.post(base + "/v1/completions", json=g).json()["choices"][0]["token_ids"]
+        b = requests.post(base + "/v1/completions", json=g).json()["choices"][0]["token_ids"]
+        assert a == b and len(a) == 4
+        # concurrent clients share engine calls
+        res = []
+        ts = [threading.Thread(target=lambda: res.append(requests.post(base + "/v1/completions", json=g).json())) for _ in range(6)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert all(r["choices"][0]["token_ids"] == a for r in res)
+        chat = requests.post(base + "/v1/chat/completions", json=dict(messages=[{"role": "user", "content": "hi"}], max_tokens=3,
+                                                                       ignore_eos=True)).json()
+        assert chat["choices"][0]["message"]["role"] == "assistant" and len(chat["choices"][0]["token_ids"]) == 3
+        assert requests.post(base + "/v1/completions", json=dict(prompt=[])).status_code == 400
+    finally:
+        srv.stop()
+
+
+def test_weight_update_pauses_serving_and_bumps_version():
+    srv, _ = _server()
+    try:
+        assert srv.begin_weight_update()
+        got = []
+        t = threading.Thread(target=lambda: got.append(requests.post(srv.base_url + "/v1/completions",
+                                                                     json=dict(prompt=[1, 2], max_tokens=2, ignore_eos=True)).json()))
+        t.start()
+        t.join(0.5)
+        assert t.is_alive() and not got          # held back while the trainer owns the engine
+        srv.end_weight_update()
+        t.join(30)
+        assert got and got[0]["weight_version"] == 1
+    finally:
+        srv.stop()
+
+
+def test_router_fails_over_and_recovers():
+    a, _ = _server(1)
+    b, _ = _server(1)
+    router = GenerationRouter([a.base_url, b.base_url], HealthPolicy(suspect_after_failures=1, dead_after_failures=2),
+                              request_timeout_s=20)
+    body = dict(prompt=[3, 4, 5], max_tokens=3, temperature=0, ignore_eos=True)
+    try:
+        first = router.completions(**body)
+        assert len(first["choices"][0]["token_ids"]) == 3
+        a.stop()                                   # shard 0 goes away between requests
+        outs = [router.completions(**body) for _ in range(4)]
+        assert all(o["served_by"] == 1 for o in outs)
+        assert all(o["choices"][0]["token_ids"] == first["choices"][0]["token_ids"] for o in outs)
+        assert router.health.state(0) in (ShardState.SUSPECT, ShardState.DEAD) and router.stats["retries"] >= 1
+        while router.health.state(0) != ShardState.DEAD:
+            router.health.report_failure(0, "probe")
+        assert router.probe_once() == {0: False} and router.health.state(0) == ShardState.DEAD
+        # the router as a server: same API, fleet view
+        rs = ServerHandle(create_router_app(router)).start()
+        try:
+            out = requests.post(rs.base_url + "/v1/completions", json=body).json()
+            assert out["served_by"] == 1
+            fleet = requests.get(rs.base_url + "/fleet").json()
+            assert fleet["shards"][0]["state"] == "dead" and fleet["serviceable"]
+        finally:
+            rs._server.should_exit = True
+        b.stop()
+        with pytest.raises(NoHealthyShardError):
+            router.completions(**body)
+    finally:
+        router.stop()

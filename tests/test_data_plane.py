@@ -1,0 +1,148 @@
+"""Data plane (codec, adapters, pre-sharding) and the single-controller GRPO loop built on it."""
+
+import pytest
+import torch
+
+from rl_b200.algorithms import grpo
+from rl_b200.algorithms.single_controller import ControllerStalled, SingleController
+from rl_b200.data.datasets.synthetic import RandomTokenPromptDataset
+from rl_b200.data_plane import (LocalDataPlane, SampleMeta, TCPStoreDataPlane, batch_to_records, create_data_plane, decode_record,
+                                encode_record, preshard, records_to_batch)
+from rl_b200.distributed.batched_data_dict import BatchedDataDict
+from rl_b200.environments.synthetic import TokenFractionEnv
+from rl_b200.models.config import ModelConfig
+
+
+def test_codec_round_trip_and_field_selection():
+    rec = {"ids": torch.arange(7), "lp": torch.randn(7).to(torch.bfloat16), "flag": torch.tensor(True), "empty": torch.zeros(0, dtype=torch.float32),
+           "text": "héllo", "obj": {"a": [1, 2]}}
+    buf = encode_record(rec)
+    out = decode_record(buf)
+    assert out["text"] == "héllo" and out["obj"] == {"a": [1, 2]} and out["empty"].shape == (0,)
+    assert torch.equal(out["ids"], rec["ids"]) and torch.equal(out["lp"], rec["lp"]) and out["lp"].dtype == torch.bfloat16
+    assert set(decode_record(buf, {"ids"})) == {"ids"}
+    with pytest.raises(ValueError):
+        decode_record(b"garbage-bytes")
+
+
+def test_jagged_batch_round_trip_drops_padding():
+    lens = torch.tensor([3, 5, 1])
+    ids = torch.zeros(3, 5, dtype=torch.long)
+    for i, n in enumerate(lens.tolist()):
+        ids[i, :n] = torch.arange(1, n + 1)
+    b = BatchedDataDict(input_ids=ids, input_lengths=lens, token_mask=(ids > 0).float(), reward=torch.tensor([1.0, 0.0, 2.0]), name=["a", "b", "c"])
+    recs = batch_to_records(b)
+    assert [r["input_ids"].numel() for r in recs] == [3, 5, 1] and recs[2]["name"] == "c"
+    back = records_to_batch(recs[:2][::-1], pad_values={"input_ids": -1})
+    assert back["input_ids"].tolist() == [[1, 2, 3, 4, 5], [1, 2, 3, -1, -1]] and back["reward"].tolist() == [0.0, 1.0]
+    assert back["name"] == ["b", "a"]
+
+
+class _FakeStore:
+    """The subset of TCPStore the adapter uses."""
+
+    def __init__(self):
+        self.d = {}
+
+    def set(self, k, v):
+        self.d[k] = bytes(v)
+
+    def get(self, k):
+        return self.d[k]
+
+    def add(self, k, n):
+        self.d[k] = int(self.d.get(k, 0)) + n
+        return self.d[k]
+
+    def check(self, ks):
+        return all(k in self.d for k in ks)
+
+    def delete_key(self, k):
+        return self.d.pop(k, None) is not None
+
+
+@pytest.mark.parametrize("make", [lambda: LocalDataPlane(), lambda: TCPStoreDataPlane(_FakeStore())])
+def test_adapters_put_get_update_delete(make):
+    dp = make()
+    for i in range(4):
+        dp.put(f"traj/{i}", {"ids": torch.arange(i + 1), "r": float(i)}, SampleMeta(f"traj/{i}", num_tokens=i + 1, weight_version=i // 2, group=f"g{i // 2}"))
+    metas = dp.list_meta("traj/")
+    assert sorted(m.key for m in metas) == [f"traj/{i}" for i in range(4)] and {m.group for m in metas} == {"g0", "g1"}
+    got = dp.get(["traj/2", "traj/0"], ["ids"])
+    assert [g["ids"].numel() for g in got] == [3, 1] and "r" not in got[0]
+    dp.update("traj/0", {"adv": torch.ones(1)})
+    assert set(dp.get(["traj/0"])[0]) >= {"ids", "r", "adv"}
+    assert dp.delete(["traj/0", "traj/1", "nope"]) == 2
+    assert sorted(m.key for m in dp.list_meta()) == ["traj/2", "traj/3"]
+    with pytest.raises(KeyError):
+        dp.get(["traj/0"])
+
+
+def test_tcp_store_adapter_across_real_store():
+    import socket
+    from datetime import timedelta
+
+    import torch.distributed as dist
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = dist.TCPStore("127.0.0.1", port, None, True, timeout=timedelta(seconds=20), wait_for_workers=False)
+    client = dist.TCPStore("127.0.0.1", port, None, False, timeout=timedelta(seconds=20))
+    a, b = TCPStoreDataPlane(server), create_data_plane({"backend": "tcp_store"}, store=client)
+    a.put("k", {"x": torch.arange(5, dtype=torch.float32)})
+    assert b.get(["k"])[0]["x"].tolist() == [0, 1, 2, 3, 4] and [m.key for m in b.list_meta()] == ["k"]
+    assert b.delete(["k"]) == 1 and a.list_meta() == []
+
+
+def test_preshard_balances_tokens_and_keeps_groups():
+    metas = [SampleMeta(f"k{i}", num_tokens=n, group=f"g{i // 2}") for i, n in enumerate([100, 90, 10, 20, 50, 40, 30, 60])]
+    shards = preshard(metas, 2)
+    assert sorted(sum(shards, [])) == sorted(m.key for m in metas)
+    where = {k: r for r, ks in enumerate(shards) for k in ks}
+    assert all(where[f"k{2 * g}"] == where[f"k{2 * g + 1}"] for g in range(4))
+    load = [sum(m.num_tokens for m in metas if where[m.key] == r) for r in range(2)]
+    assert abs(load[0] - load[1]) <= 40
+    eq = preshard(metas, 4, keep_groups=False, equal_counts=True)
+    assert [len(x) for x in eq] == [2, 2, 2, 2]
+
+
+def _controller(tmp_path, mode, max_age=1, steps=4):
+    mc = ModelConfig(vocab_size=32, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    cfg = {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=4, max_num_steps=steps, val_period=0, seed=0),
+           "loss_fn": dict(use_importance_sampling_correction=True, reference_policy_kl_penalty=0.0),
+           "single_controller": dict(pump_mode=mode, max_trajectory_age_steps=max_age, rollout_ahead_batches=2, stall_timeout_s=120),
+           "policy": dict(precision="float32", train_global_batch_size=16, train_micro_batch_size=8, logprob_batch_size=16,
+                          max_total_sequence_length=48, max_grad_norm=1.0,
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=5e-3, weight_decay=0.0)),
+                          generation=dict(max_new_tokens=8, temperature=1.0, stop_token_ids=[], kv_cache_tokens=4096, block_size=8, max_running=32)),
+           "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    policy, gen, loader, _, loss_fn, logger, ck, ss, cfg = grpo.setup(cfg, None, ds, None, env, model_cfg=mc)
+    hist = []
+    sc = SingleController(policy, gen, loader, None, loss_fn, env, cfg, logger=logger, save_state=ss, step_callback=lambda s, m: hist.append(m["train"]))
+    return sc, hist
+
+
+@pytest.mark.parametrize("mode", ["interleaved", "threads"])
+def test_single_controller_trains_on_age_bounded_trajectories(tmp_path, mode):
+    sc, hist = _controller(tmp_path, mode)
+    sc.run()
+    assert len(hist) == 4 and sc.version == 4 and all(torch.isfinite(torch.tensor(h["loss"])) for h in hist)
+    assert max(h["trajectory_age"] for h in hist) <= 1
+    assert sc.stats["samples_trained"] == 4 * 16 and sc.stats["rollout_batches"] >= 4
+    sd = sc.state_dict()
+    assert sd["version"] == 4 and all(v >= 3 for _, v, _ in sd["pending"])   # what is still stored is at most one version old
+
+
+def test_single_controller_drops_stale_and_reports_stall(tmp_path):
+    sc, hist = _controller(tmp_path, "interleaved", max_age=0, steps=3)
+    sc.sc["rollout_ahead_batches"] = 3           # runs ahead further than the age bound allows
+    sc.run()
+    assert len(hist) == 3 and sc.stats["dropped_stale"] > 0 and all(h["trajectory_age"] == 0 for h in hist)
+    sc2, _ = _controller(tmp_path, "interleaved")
+    sc2._on_stall(999.0)
+    with pytest.raises(ControllerStalled):
+        sc2.run()

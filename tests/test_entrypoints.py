@@ -102,3 +102,10 @@ def test_run_sft_dpo_rm_eval(capsys):
                      "eval.k_value=2", "data.validation.dataset_name=arithmetic", "+data.validation.num_val_samples=4", "data.default.prompt_file=null"])
     out = capsys.readouterr().out
     assert "[sft] step 2:" in out and "[dpo] step 2:" in out and "[rm] step 2:" in out and "pass@2=" in out
+
+
+def test_run_grpo_single_controller_recipe(capsys):
+    from examples import run_grpo_single_controller
+
+    run_grpo_single_controller.main(["--config", f"{ROOT}/examples/configs/grpo_single_controller.yaml", "grpo.max_num_steps=2"])
+    assert "[single_controller] step 2:" in capsys.readouterr().out

@@ -124,6 +124,10 @@ def get_tokenizer(tokenizer_config: dict):
         from rl_b200.data.tokenizers import ByteTokenizer
 
         return ByteTokenizer(int(tokenizer_config.get("vocab_size", 512)))
+    if str(tokenizer_config.get("name", "")).lower() == "pair":
+        from rl_b200.data.tokenizers import PairTokenizer
+
+        return PairTokenizer(int(tokenizer_config.get("vocab_size", 1024)))
     from transformers import AutoTokenizer
 
     tok = AutoTokenizer.from_pretrained(tokenizer_config["name"], trust_remote_code=True)

@@ -223,3 +223,21 @@ class ConcatDataset:
         item = self.parts[k][int(i) - self.offsets[k]]
         item["idx"] = int(i)
         return item
+
+
+def load_text_corpus(data_cfg: dict) -> list[dict]:
+    """Plain-text corpus for off-policy distillation: ``{"text": ...}`` records.
+
+    ``dataset_name``: ``arithmetic_text`` (synthetic, offline), ``text`` (``path``: one document per line) or ``jsonl``
+    (``path``; ``text_key`` names the field, records with ``messages`` are kept as they are)."""
+    name = data_cfg.get("dataset_name", "arithmetic_text")
+    if name == "arithmetic_text":
+        ds = ArithmeticDataset(int(data_cfg.get("num_samples", 1024)), seed=int(data_cfg.get("seed", 0)))
+        return [{"text": f"{r['problem']} The answer is {r['expected_answer']}."} for r in ds.records]
+    if name == "text":
+        with open(data_cfg["path"]) as f:
+            return [{"text": l.rstrip("\n")} for l in f if l.strip()]
+    if name == "jsonl":
+        key = data_cfg.get("text_key", "text")
+        return [r if "messages" in r and key not in r else {"text": r[key]} for r in JsonlRecords(data_cfg["path"]).records]
+    raise ValueError(f"unknown text corpus {name!r}")

@@ -84,3 +84,47 @@ class ByteTokenizer:
             parts.append("<|assistant|>")
         text = "".join(parts)
         return self.encode(text) if tokenize else text
+
+
+class PairTokenizer(ByteTokenizer):
+    """Byte tokenizer with one merge rule: two adjacent lowercase ASCII letters form one token (ids from ``pair_base``
+    on, 26 x 26 of them). A second offline tokenisation of the same text with different boundaries, which is what
+    cross-tokenizer distillation needs to be exercised without tokenizer files."""
+
+    def __init__(self, vocab_size: int = 1024):
+        super().__init__(vocab_size)
+        self.pair_base = 256 + len(self.SPECIALS)
+        assert vocab_size >= self.pair_base + 26 * 26
+        self.name_or_path = "pair"
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
+        ids: list[int] = [self.bos_token_id] if add_special_tokens else []
+        i = 0
+        while i < len(text):
+            if text[i] == "<":
+                hit = next((s for s in self.SPECIALS if text.startswith(s, i)), None)
+                if hit is not None:
+                    ids.append(self._sp[hit])
+                    i += len(hit)
+                    continue
+            a = text[i]
+            b = text[i + 1] if i + 1 < len(text) else ""
+            if "a" <= a <= "z" and b and "a" <= b <= "z":
+                ids.append(self.pair_base + (ord(a) - 97) * 26 + (ord(b) - 97))
+                i += 2
+                continue
+            ids.extend(a.encode("utf-8"))
+            i += 1
+        return ids
+
+    def decode(self, ids, skip_special_tokens: bool = False) -> str:
+        if isinstance(ids, torch.Tensor):
+            ids = ids.tolist()
+        flat: list[int] = []
+        for t in ids:
+            if self.pair_base <= t < self.pair_base + 676:
+                p = t - self.pair_base
+                flat += [97 + p // 26, 97 + p % 26]
+            else:
+                flat.append(t)
+        return super().decode(flat, skip_special_tokens)

@@ -36,7 +36,7 @@ def model_cfg_for_tokenizer(cfg: dict, tokenizer):
     name = pcfg.get("model_name")
     if name in PRESETS:
         over = dict(pcfg.get("hf_config_overrides") or {})
-        if getattr(tokenizer, "name_or_path", None) == "byte":
+        if getattr(tokenizer, "name_or_path", None) in ("byte", "pair"):
             over.setdefault("vocab_size", len(tokenizer))
         return preset(name, **over)
     return None

@@ -109,3 +109,10 @@ def test_run_grpo_single_controller_recipe(capsys):
 
     run_grpo_single_controller.main(["--config", f"{ROOT}/examples/configs/grpo_single_controller.yaml", "grpo.max_num_steps=2"])
     assert "[single_controller] step 2:" in capsys.readouterr().out
+
+
+def test_run_xtoken_distillation_recipe(capsys):
+    from examples import run_xtoken_off_policy_distillation as run
+
+    run.main(["--config", f"{ROOT}/examples/configs/xtoken_distillation_offline.yaml", "distillation.max_num_steps=2", "data.num_samples=32"])
+    assert "[xtoken_distillation] step 2:" in capsys.readouterr().out

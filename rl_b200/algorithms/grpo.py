@@ -25,7 +25,7 @@ from rl_b200.algorithms.advantage_estimator import create_advantage_estimator
 from rl_b200.algorithms.loss.loss_functions import ClippedPGLossFn
 from rl_b200.algorithms.reward_functions import apply_reward_shaping, scale_rewards
 from rl_b200.algorithms.utils import calculate_baseline_and_std_per_prompt, compute_performance_metrics, set_seed
-from rl_b200.data.llm_message_utils import batched_message_log_to_flat_message
+from rl_b200.data.llm_message_utils import batched_message_log_to_flat_message, multimodal_fields
 from rl_b200.distributed.batched_data_dict import BatchedDataDict
 from rl_b200.experience.rollouts import run_multi_turn_rollout
 from rl_b200.utils.checkpoint import CheckpointManager
@@ -225,6 +225,7 @@ def build_train_data(batch: BatchedDataDict, pad_token_id: int, make_divisible_b
     return BatchedDataDict(
         input_ids=flat["token_ids"], input_lengths=lengths, token_mask=flat["token_loss_mask"].float(),
         sample_mask=batch["loss_multiplier"].float().clone(), generation_logprobs=flat["generation_logprobs"].float(),
+        **multimodal_fields(flat),
     )
 
 

@@ -8,7 +8,7 @@ import torch
 
 from rl_b200.distributed.batched_data_dict import BatchedDataDict
 
-from .llm_message_utils import add_loss_mask_to_message_log, batched_message_log_to_flat_message
+from .llm_message_utils import add_loss_mask_to_message_log, batched_message_log_to_flat_message, multimodal_fields
 
 
 def rl_collate_fn(batch: Sequence[dict]) -> BatchedDataDict:
@@ -40,7 +40,7 @@ def sft_collate_fn(batch: Sequence[dict], pad_token_id: int = 0, make_sequence_l
     flat, lengths = batched_message_log_to_flat_message(logs, {"token_ids": pad_token_id}, make_sequence_length_divisible_by)
     return BatchedDataDict(
         input_ids=flat["token_ids"], input_lengths=lengths, token_mask=flat["token_loss_mask"].float(),
-        sample_mask=torch.tensor([float(d.get("loss_multiplier", 1.0)) for d in batch]),
+        sample_mask=torch.tensor([float(d.get("loss_multiplier", 1.0)) for d in batch]), **multimodal_fields(flat),
     )
 
 

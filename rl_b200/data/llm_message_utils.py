@@ -57,6 +57,11 @@ def batched_message_log_to_flat_message(message_logs: Sequence[LLMMessageLogType
         tensor_keys |= {k for k, v in f.items() if isinstance(v, torch.Tensor)}
     for k in tensor_keys:
         proto = next(f[k] for f in flats if k in f)
+        if proto.dim() >= 2:   # per-sample rows of another modality (image patches): kept ragged, one entry per sample
+            from .multimodal_utils import PackedTensor
+
+            out[k] = PackedTensor([f.get(k) for f in flats])
+            continue
         pad = pad_value_dict.get(k, 0)
         buf = torch.full((len(flats), S), pad, dtype=proto.dtype)
         for i, f in enumerate(flats):
@@ -66,7 +71,17 @@ def batched_message_log_to_flat_message(message_logs: Sequence[LLMMessageLogType
         out[k] = buf
     for k in set().union(*[f.keys() for f in flats]) - tensor_keys if flats else ():
         out[k] = [f.get(k) for f in flats]
+    if "image_sizes" in out:   # per message lists of patch counts -> one list per sample
+        out["image_sizes"] = [[int(s) for per_msg in (row or []) for s in per_msg] for row in out["image_sizes"]]
     return out, lengths
+
+
+MULTIMODAL_KEYS = ("pixel_patches", "image_sizes")
+
+
+def multimodal_fields(flat: BatchedDataDict) -> dict[str, Any]:
+    """The image fields of a flattened batch (empty for text-only data), to be carried into train / generation batches."""
+    return {k: flat[k] for k in MULTIMODAL_KEYS if k in flat}
 
 
 def get_formatted_message_log(message_log: list[dict[str, str]], tokenizer, task_data_spec=None,

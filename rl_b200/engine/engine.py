@@ -310,6 +310,7 @@ class _Request:
     truncated: bool = False
     share_with: int = -1
     uid: int = 0  # keys the request's random stream: same uid and seed -> same draws on any rank / batch
+    mm: object = None  # (image patch rows, patches per image) of a vision-language prompt
 
 
 class GenerationEngine:
@@ -436,6 +437,8 @@ class GenerationEngine:
     def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor) -> torch.Tensor:
         m, c = self.model, self.cfg
         h = F.embedding(batch.input_ids, m.embed_tokens)
+        if hasattr(m, "merge_vision"):
+            h = m.merge_vision(h, batch.input_ids, getattr(batch, "mm", None))
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq)
@@ -544,9 +547,12 @@ class GenerationEngine:
 
     # ------------------------------------------------------------------ public API
     def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, max_new_tokens: Optional[Sequence[int]] = None,
-                 share_prefixes: bool = True, request_uids: Optional[Sequence[int]] = None) -> list[_Request]:
+                 share_prefixes: bool = True, request_uids: Optional[Sequence[int]] = None,
+                 mm_inputs: Optional[Sequence] = None) -> list[_Request]:
         """Runs all prompts to completion with continuous batching. Returns one record per prompt (in input order)
-        with the generated tokens, their log-probabilities and whether generation was cut by the length limit."""
+        with the generated tokens, their log-probabilities and whether generation was cut by the length limit.
+        ``mm_inputs``: per prompt ``(patches [n, patch_dim], [patches per image])`` or None, for vision-language models whose
+        prompts hold one image placeholder token per patch row."""
         # inference keeps all rows on every tensor-parallel rank (all-reduce form), whatever the training layout is
         saved = self.tp.sequence_parallel if self.tp is not None else False
         if self.tp is not None:
@@ -554,7 +560,7 @@ class GenerationEngine:
         # no kernel of a generation phase writes a weight, so the decode GEMMs may start their weight stream early
         prev_static = E.skinny_static_weights(os.environ.get("RLB_SKINNY_EARLY_WEIGHTS", "1") != "0") if self.native else 0
         try:
-            return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids)
+            return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids, mm_inputs)
         finally:
             if self.native:
                 E.skinny_static_weights(bool(prev_static))
@@ -562,7 +568,8 @@ class GenerationEngine:
                 self.tp.sequence_parallel = saved
 
     @torch.no_grad()
-    def _generate(self, prompts, sp: SamplingParams, max_new_tokens=None, share_prefixes: bool = True, request_uids=None) -> list[_Request]:
+    def _generate(self, prompts, sp: SamplingParams, max_new_tokens=None, share_prefixes: bool = True, request_uids=None,
+                  mm_inputs=None) -> list[_Request]:
         self.wake()
         self.model.eval()
         stop = set(int(t) for t in (sp.stop_token_ids or []))
@@ -573,13 +580,21 @@ class GenerationEngine:
             mx = int(max_new_tokens[i]) if max_new_tokens is not None else sp.max_new_tokens
             mx = max(1, min(mx, self.max_model_len - len(p)))
             share = -1
+            mm = mm_inputs[i] if mm_inputs is not None else None
+            if mm is not None and mm[0] is None:
+                mm = None
             if share_prefixes:
                 key = tuple(p)
+                if mm is not None:   # equal prompts share their prefix only if they show the same images
+                    from rl_b200.data.multimodal_utils import content_key
+
+                    key = (key, content_key(mm[0]))
                 if key in first_of:
                     share = first_of[key]
                 else:
                     first_of[key] = i
             reqs[i] = _Request(i, p, mx, share_with=share, uid=int(request_uids[i]) if request_uids is not None else i)
+            reqs[i].mm = mm
             if self.sched.add(i, len(p), mx, share) != 0:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
         dev = self.device
@@ -671,6 +686,9 @@ class GenerationEngine:
                     cu[1:] = lens_t.cumsum(0)
                     pos = torch.cat([torch.arange(L, dtype=torch.int32) for L in lens]).to(dev)
                     batch = PackedBatch(ids, pos, cu.to(dev), max(lens))
+                    mms = [reqs[sid].mm for sid in prefill if getattr(reqs[sid], "mm", None) is not None]
+                    if mms:
+                        batch.mm = dict(patches=_L.to_device(torch.cat([m[0] for m in mms]), dev), sizes=[int(x) for m in mms for x in m[1]])
                     last_idx = (cu[1:] - 1).to(dev)
                     logits = self._prefill_forward(batch, torch.cat(slots).to(dev), last_idx)
                     for j, sid in enumerate(prefill):

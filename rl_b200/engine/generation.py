@@ -116,6 +116,10 @@ class NativeGeneration:
         prompts = [ids_cpu[i, : lens_l[i]].tolist() for i in range(B)]
         sp = self._sampling(greedy)
         uids = data["rng_ids"].tolist() if "rng_ids" in data else None
+        mm = None
+        if "pixel_patches" in data:
+            mm = [(data["pixel_patches"][i], data["image_sizes"][i]) for i in range(B)]
+            assert self.pool_group is None, "vision inputs with pooled serving groups are not supported"
         if self.pool_group is not None:
             import torch.distributed as dist
 
@@ -134,7 +138,7 @@ class NativeGeneration:
             mine = (me // self.pool_stride) * self.pool_stride
             recs = allrecs[start[mine] : start[mine] + B]
         else:
-            recs = self.engine.generate(prompts, sp, request_uids=uids)
+            recs = self.engine.generate(prompts, sp, request_uids=uids, mm_inputs=mm)
         stop_strings = data.get("stop_strings") or self.cfg.get("stop_strings")
         if stop_strings and self.tokenizer is not None:
             self._apply_stop_strings(recs, stop_strings)

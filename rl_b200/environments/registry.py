@@ -15,6 +15,7 @@ _REGISTRY: dict[str, str] = {
     "code_jaccard": "rl_b200.environments.code_environment:CodeJaccardEnvironment",
     "reward_model": "rl_b200.environments.reward_model_environment:RewardModelEnvironment",
     "dapo": "rl_b200.environments.math_environment:MathEnvironment",
+    "vlm": "rl_b200.environments.vlm_environment:VLMEnvironment",
 }
 
 

@@ -15,16 +15,16 @@ from typing import Any, Optional
 
 import torch
 
-from rl_b200.data.llm_message_utils import batched_message_log_to_flat_message
+from rl_b200.data.llm_message_utils import batched_message_log_to_flat_message, multimodal_fields
 from rl_b200.distributed.batched_data_dict import BatchedDataDict
 from rl_b200.environments.interfaces import EnvironmentInterface, EnvironmentReturn
 
 
 def generate_responses(generation, flat_ids: torch.Tensor, input_lengths: torch.Tensor, batch: BatchedDataDict,
-                       tokenizer, greedy: bool = False, stop_strings=None):
+                       tokenizer, greedy: bool = False, stop_strings=None, multimodal: Optional[dict] = None):
     """Generates one continuation per row, appends it to every message log as an assistant message, and returns
     (batch, generated ids per sample, generation metrics)."""
-    gen_in = BatchedDataDict(input_ids=flat_ids, input_lengths=input_lengths)
+    gen_in = BatchedDataDict(input_ids=flat_ids, input_lengths=input_lengths, **(multimodal or {}))
     if stop_strings is not None:
         gen_in["stop_strings"] = stop_strings
     if "rng_ids" in batch:
@@ -94,7 +94,7 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
         sub["message_log"] = [batch["message_log"][i] for i in active]  # same list objects: appended in place
         flat, lens = batched_message_log_to_flat_message(sub["message_log"], {"token_ids": pad_token_id})
         ss = [stop_strings[i] for i in active] if stop_strings is not None else None
-        sub, generated, gm, out = generate_responses(generation, flat["token_ids"], lens, sub, tokenizer, greedy, ss)
+        sub, generated, gm, out = generate_responses(generation, flat["token_ids"], lens, sub, tokenizer, greedy, ss, multimodal_fields(flat))
         gen_metrics_acc["total_generated_tokens"] += gm["total_generated_tokens"]
         for j, i in enumerate(active):
             gen_tokens[i] += generated[j].numel()

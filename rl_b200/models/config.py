@@ -44,6 +44,8 @@ class ModelConfig:
     pad_token_id: Optional[int] = None
     torch_dtype: str = "bfloat16"
     value_head: bool = False           # critic / reward model: scalar head instead of the vocabulary projection
+    vision: Optional[dict] = None      # vision tower settings (models/vision.py); None: text-only model
+    image_token_id: Optional[int] = None
 
     @property
     def q_size(self) -> int:
@@ -79,6 +81,9 @@ class ModelConfig:
         d.pop("value_head")
         d.pop("qk_norm")
         d["architectures"] = [arch]
+        if self.vision is None:
+            d.pop("vision")
+            d.pop("image_token_id")
         if not self.is_moe:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob", "router_aux_loss_coef"):
                 d.pop(k)
@@ -113,6 +118,8 @@ class ModelConfig:
             eos_token_id=hf.get("eos_token_id"),
             pad_token_id=hf.get("pad_token_id"),
             torch_dtype=str(hf.get("torch_dtype", hf.get("dtype", "bfloat16"))),
+            vision=hf.get("vision"),
+            image_token_id=hf.get("image_token_id"),
         )
         for k, v in overrides.items():
             setattr(cfg, k, v)
@@ -188,6 +195,17 @@ PRESETS: dict[str, dict] = {
     "tiny-llama-oracle": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
                               num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
                               rms_norm_eps=1e-5, rope_theta=10000.0),
+    # tiny vision-language model for offline recipes and tests: the oracle language model behind a 2-layer ViT
+    "tiny-vlm": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
+                     num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
+                     rms_norm_eps=1e-5, rope_theta=10000.0, image_token_id=511,
+                     vision=dict(patch_size=4, channels=3, hidden_size=64, intermediate_size=128, num_layers=2, num_heads=4, max_patches=256)),
+    # Qwen2-VL-7B-shaped: Qwen2-7B language model, 32-layer ViT of width 1280 on 14 x 14 patches
+    "qwen2-vl-7b": dict(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                        num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                        rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=True, image_token_id=151655,
+                        vision=dict(patch_size=14, channels=3, hidden_size=1280, intermediate_size=5120, num_layers=32, num_heads=16,
+                                    max_patches=16384)),
 }
 
 

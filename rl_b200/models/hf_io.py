@@ -39,6 +39,13 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         elif not tied:
             vl = cfg.vocab_size // tp_size
             rows.append(("lm_head.weight", "lm_head", None, None, (0, tp_rank * vl, vl) if tp_size > 1 else None))
+    if cfg.vision is not None and first_stage:   # vision tower: replicated, stored under its own names
+        from .vision import vision_config
+
+        nv = vision_config(cfg)["num_layers"]
+        leaves = ["patch_embed", "pos_embed", "merger_norm", "merger_fc1", "merger_fc2"]
+        leaves += [f"blocks.{i}.{k}" for i in range(nv) for k in ("attn_norm", "qkv", "proj", "mlp_norm", "fc1", "fc2")]
+        rows += [(f"visual.{k}.weight", f"visual.{k}", None, None, None) for k in leaves]
     q, kv = cfg.q_size // tp_size, cfg.kv_size // tp_size
 
     def sl(dim, n):  # this rank's slice of a dimension of (global) length n * tp_size
@@ -244,7 +251,9 @@ def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None
                     pp_rank: int = 0, pp_size: int = 1, lora: Optional[dict] = None, **cfg_overrides) -> CausalLM:
     """Builds a model (or this rank's tensor / expert / pipeline shard of it) from an HF checkpoint directory."""
     cfg = ModelConfig.from_pretrained(path, **cfg_overrides)
-    model = CausalLM(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, lora=lora)
+    from .transformer import build_model
+
+    model = build_model(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, lora=lora)
     if lora:
         from .transformer import LoRA
 

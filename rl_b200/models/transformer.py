@@ -536,5 +536,8 @@ class CausalLM(nn.Module):
 def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
                 activation_checkpointing: bool = False, init: bool = True, tp: Optional[TP] = None, ep=None,
                 pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None) -> CausalLM:
-    return CausalLM(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
-                    tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp, lora=lora)
+    cls = CausalLM
+    if cfg.vision is not None:
+        from .vision import VLMCausalLM as cls
+    return cls(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
+               tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp, lora=lora)

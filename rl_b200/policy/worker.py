@@ -434,6 +434,10 @@ class PolicyWorker:
             batch = batch.pad_to_multiple(8 * self.tp.world)
         elif self.cp.world > 1:
             batch = batch.pad_to_multiple(8 * self.cp.world)
+        if "pixel_patches" in mb:   # vision-language batch: image patch rows in sample order (models/vision.py)
+            parts = [t for t in mb["pixel_patches"] if t is not None]
+            batch.mm = dict(patches=to_device(torch.cat(parts), self.device) if parts else None,
+                            sizes=[int(x) for row in mb["image_sizes"] for x in (row or [])])
         return batch, ids.shape[1]
 
     # ------------------------------------------------------------------ inference passes

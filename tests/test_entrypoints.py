@@ -116,3 +116,13 @@ def test_run_xtoken_distillation_recipe(capsys):
 
     run.main(["--config", f"{ROOT}/examples/configs/xtoken_distillation_offline.yaml", "distillation.max_num_steps=2", "data.num_samples=32"])
     assert "[xtoken_distillation] step 2:" in capsys.readouterr().out
+
+
+def test_run_vlm_sft_and_grpo_recipes(capsys):
+    from examples import run_vlm_grpo, run_vlm_sft
+
+    run_vlm_sft.main(["--config", f"{ROOT}/examples/configs/vlm_sft_offline.yaml", "sft.max_num_steps=2", "data.train.num_samples=32"])
+    run_vlm_grpo.main(["--config", f"{ROOT}/examples/configs/vlm_grpo_offline.yaml", "grpo.max_num_steps=1", "grpo.num_prompts_per_step=4",
+                       "policy.train_global_batch_size=16"])
+    out = capsys.readouterr().out
+    assert "[sft] step 2:" in out and "[grpo] step 1:" in out

@@ -106,3 +106,24 @@ def test_router_fails_over_and_recovers():
             router.completions(**body)
     finally:
         router.stop()
+
+
+def test_remote_environment_round_trip_and_server_loss():
+    from rl_b200.environments.registry import create_env
+    from rl_b200.environments.remote_environment import create_env_app
+    from rl_b200.environments.vlm_environment import VLMEnvironment
+
+    srv = ServerHandle(create_env_app(VLMEnvironment({}))).start()
+    env = create_env("remote", dict(url=srv.base_url, batch_size=2, max_retries=0, timeout_s=5))
+    logs = [[{"role": "user", "content": "colour?", "token_ids": torch.tensor([1, 2])}, {"role": "assistant", "content": c, "token_ids": torch.tensor([3])}]
+            for c in ("it is red", "blue", "maybe green")]
+    try:
+        out = env.step(logs, [{"ground_truth": "red"}, {"ground_truth": "red"}, {"ground_truth": "green"}])
+        assert out.rewards.tolist() == [1.0, 0.0, 1.0] and out.terminateds.all() and out.answers[1] == "blue"
+        assert requests.get(srv.base_url + "/health").json()["environment"] == "VLMEnvironment"
+    finally:
+        srv._server.should_exit = True
+        srv._thread.join(5)
+    with pytest.raises(ConnectionError):
+        env.step(logs[:1], [{"ground_truth": "red"}])
+    env.shutdown()

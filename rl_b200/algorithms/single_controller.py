@@ -69,7 +69,7 @@ class SingleController:
 
     # ------------------------------------------------------------------ rollout pump
     def _pending_batches(self) -> int:
-        return len({m.extra.get("batch") for m in self.plane.list_meta("traj/")})
+        return len({m.extra.get("batch") for m in self.plane.list_meta("done/")})
 
     def rollout_once(self) -> int:
         """One prompt batch -> trajectories -> data plane. Returns the number of samples stored (0: nothing to do)."""
@@ -105,6 +105,8 @@ class SingleController:
             key = f"traj/{b:08d}/{i:05d}"
             self.plane.put(key, r, SampleMeta(key, num_tokens=int(r["input_lengths"]), weight_version=version,
                                               group=f"{b}:{int(r['prompt_idx'])}", extra={"batch": b}))
+        # the batch becomes visible to the train pump only now that every sample of it is stored
+        self.plane.put(f"done/{b:08d}", {"n": len(recs)}, SampleMeta(f"done/{b:08d}", weight_version=version, extra={"batch": b}))
         self.stats["rollout_batches"] += 1
         self.stats["samples_stored"] += len(recs)
         self.watchdog.progress()
@@ -115,12 +117,15 @@ class SingleController:
         """The oldest stored batch that is young enough; batches that aged out are deleted."""
         max_age = int(self.sc["max_trajectory_age_steps"])
         by_batch: dict[int, list[SampleMeta]] = {}
+        done = {m.extra.get("batch") for m in self.plane.list_meta("done/")}
         for m in self.plane.list_meta("traj/"):
-            by_batch.setdefault(m.extra.get("batch"), []).append(m)
+            if m.extra.get("batch") in done:
+                by_batch.setdefault(m.extra.get("batch"), []).append(m)
         for b in sorted(by_batch):
             ms = by_batch[b]
             if self.version - min(m.weight_version for m in ms) > max_age:
                 self.stats["dropped_stale"] += self.plane.delete([m.key for m in ms])
+                self.plane.delete([f"done/{b:08d}"])
                 continue
             return sorted(ms, key=lambda m: m.key)
         return None
@@ -151,6 +156,7 @@ class SingleController:
             self._refit_needed = True
         age = self.version - 1 - min(order[k].weight_version for k in keys)
         self.plane.delete(keys)
+        self.plane.delete([f"done/{order[keys[0]].extra.get('batch'):08d}"])
         self.steps += 1
         self.stats["samples_trained"] += len(keys)
         metrics = _aggregate_train_metrics(res)

@@ -321,8 +321,11 @@ class GenerationEngine:
     def __init__(self, model: CausalLM, *, block_size: int = 64, num_blocks: Optional[int] = None,
                  kv_cache_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.5, max_running: int = 512,
                  max_prefill_tokens: int = 16384, max_model_len: int = 8192, use_cuda_graphs: bool = True,
-                 logits_fp32: bool = True, tokenizer=None):
+                 logits_fp32: bool = True, tokenizer=None, quantization: Optional[str] = None):
+        """``quantization``: None (bf16), ``"mxfp8"`` or ``"fp8"``: serve quantised copies of the linear weights
+        (see ``engine/quantized.py``); call :meth:`requantize` after the weights changed."""
         self.model = model
+        self.quantization = quantization if quantization not in (None, "", "bfloat16", "bf16", "none") else None
         self.cfg = model.cfg
         self.device = model.embed_tokens.device
         self.block_size = block_size
@@ -363,6 +366,15 @@ class GenerationEngine:
         self._step_counter = 0
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
+
+    def requantize(self) -> Optional[dict]:
+        """Refreshes the quantised weight copies from the (refitted) bf16 weights; no-op for a bf16 engine."""
+        if not self.quantization:
+            return None
+        from .quantized import quantize_model
+
+        assert self.tpw == 1, "low-precision rollout with a tensor-parallel engine is not supported"
+        return quantize_model(self.model, self.quantization)
 
     # ------------------------------------------------------------------ memory
     def wake(self) -> None:
@@ -560,6 +572,11 @@ class GenerationEngine:
         # no kernel of a generation phase writes a weight, so the decode GEMMs may start their weight stream early
         prev_static = E.skinny_static_weights(os.environ.get("RLB_SKINNY_EARLY_WEIGHTS", "1") != "0") if self.native else 0
         try:
+            if self.quantization:
+                from .quantized import quantized_inference
+
+                with quantized_inference(True):
+                    return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids, mm_inputs)
             return self._generate(prompts, sp, max_new_tokens, share_prefixes, request_uids, mm_inputs)
         finally:
             if self.native:

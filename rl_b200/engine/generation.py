@@ -34,6 +34,7 @@ GENERATION_DEFAULTS = dict(
     use_cuda_graphs=True,
     free_kv_cache_on_sleep=False,
     seed=0,
+    precision="bfloat16",   # rollout precision of the linear layers: bfloat16 | mxfp8 | fp8 (vllm_cfg.precision in the reference)
 )
 
 
@@ -81,12 +82,14 @@ class NativeGeneration:
             model, block_size=c["block_size"], kv_cache_tokens=c["kv_cache_tokens"],
             gpu_memory_utilization=c["gpu_memory_utilization"], max_running=c["max_running"],
             max_prefill_tokens=c["max_prefill_tokens"], max_model_len=c["max_model_len"] or 8192,
-            use_cuda_graphs=c["use_cuda_graphs"], tokenizer=tokenizer)
+            use_cuda_graphs=c["use_cuda_graphs"], tokenizer=tokenizer,
+            quantization=(c.get("native_cfg") or {}).get("precision") or (c.get("vllm_cfg") or {}).get("precision") or c.get("precision"))
         self._calls = 0
 
     # lifecycle hooks of the generation contract
     def prepare_for_generation(self, *args, **kw) -> bool:
         self.engine.wake()
+        self.last_quantization = self.engine.requantize()   # the weights may have moved since the last rollout
         return True
 
     def finish_generation(self, *args, **kw) -> bool:

@@ -127,6 +127,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
     ``residual`` (same shape as y) is added inside the GEMM epilogue, which saves one read-modify-write pass over
     the residual stream per projection."""
+    qz = getattr(w, "_rlb_q", None)
+    if qz is not None and not torch.is_grad_enabled():
+        from rl_b200.engine import quantized as _qz   # low-precision rollout: only inside the engine's generation phase
+
+        if _qz.is_active():
+            return _qz.quantized_linear(x, qz, bias, residual)
     if not use_native(x):
         y = tF.linear(x, w, bias)
         return y if residual is None else y + residual

@@ -69,11 +69,14 @@ def verify_right_padding(data: BatchedDataDict, pad_value: int = 0) -> tuple[boo
 class NativeGeneration:
     """Driver-facing generation object (one per GPU rank in the SPMD runtime)."""
 
-    def __init__(self, model, cfg: Optional[dict] = None, tokenizer=None, pool_group=None, pool_stride: int = 1):
+    def __init__(self, model, cfg: Optional[dict] = None, tokenizer=None, pool_group=None, pool_stride: int = 1, split_group=None):
         """``pool_group``: the serving tensor-parallel group when it spans several data-parallel ranks of the trainer
         (each holding different prompts); the prompts of one rank per ``pool_stride`` consecutive ranks are pooled so that
         all ranks of the engine serve the same request set, and every rank gets its own results back."""
         self.pool_group, self.pool_stride = pool_group, max(1, int(pool_stride))
+        # ``split_group``: ranks that hold the same prompts and complete serving weights (pipeline stages or context-parallel
+        # ranks of one replica): each generates every S-th prompt and the results are exchanged
+        self.split_group = split_group
         self.cfg = configure_generation_config(cfg, tokenizer)
         c = self.cfg
         self.tokenizer = tokenizer
@@ -140,6 +143,22 @@ class NativeGeneration:
             allrecs = self.engine.generate(pooled, sp, request_uids=pooled_uids)
             mine = (me // self.pool_stride) * self.pool_stride
             recs = allrecs[start[mine] : start[mine] + B]
+        elif self.split_group is not None:
+            import torch.distributed as dist
+
+            S, me = dist.get_world_size(self.split_group), dist.get_rank(self.split_group)
+            mine = list(range(me, B, S))
+            part = self.engine.generate([prompts[i] for i in mine], sp, request_uids=[uids[i] if uids is not None else i for i in mine],
+                                        mm_inputs=[mm[i] for i in mine] if mm is not None else None)
+            box = [None] * S
+            dist.all_gather_object(box, [(i, r.prompt, r.out_tokens, r.out_logprobs, r.truncated) for i, r in zip(mine, part)],
+                                   group=self.split_group)
+            from .engine import _Request
+
+            recs = [None] * B
+            for chunk in box:
+                for i, prompt, toks, lps, trunc in chunk:
+                    recs[i] = _Request(i, prompt, len(toks), out_tokens=toks, out_logprobs=lps, finished=True, truncated=trunc)
         else:
             recs = self.engine.generate(prompts, sp, request_uids=uids, mm_inputs=mm)
         stop_strings = data.get("stop_strings") or self.cfg.get("stop_strings")

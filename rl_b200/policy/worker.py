@@ -304,10 +304,23 @@ class PolicyWorker:
             merged["use_cuda_graphs"] = False
         merged.setdefault("max_model_len", self.cfg["max_total_sequence_length"])
         gen_tp = int(native_cfg.get("tensor_parallel_size") or self.tp.world)
-        engine_model, pool_group, pool_stride = self.model, None, 1
-        if gen_tp != self.tp.world:
+        engine_model, pool_group, pool_stride, split_group = self.model, None, 1, None
+        st = self.pstate
+        if st.pp > 1:
+            # every rank gets a serving copy of the whole model (the trainer's tensor-parallel layout), refreshed by packed
+            # broadcasts over the pipeline group; the stages of one replica hold the same prompts and share the work
+            from rl_b200.refit.packed_broadcast import PipelineWeightSynchronizer
+
+            assert gen_tp == self.tp.world and st.ep == 1 and not self.model_cfg.is_moe, \
+                "pipeline-parallel training serves with the trainer's tensor-parallel size (dense models)"
+            self.weight_synchronizer = PipelineWeightSynchronizer(self.model, self.model_cfg, st)
+            engine_model, split_group = self.weight_synchronizer.serving_model, st.pp_group
+        elif gen_tp != self.tp.world:
             engine_model, pool_group, pool_stride = self._build_serving_layout(gen_tp)
-        self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride)
+        elif st.cp > 1:
+            split_group = st.cp_group   # context-parallel ranks hold the same prompts and the same (full) weights
+        self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride,
+                                           split_group=split_group)
         self.temperature = float(self.generation.cfg["temperature"] or 1.0)
         return self.generation
 

@@ -22,7 +22,7 @@ def _free_port():
     return p
 
 
-def _run(rank, world, port, out_path, tp=1):
+def _run(rank, world, port, out_path, tp=1, pp=1, cp=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     torch.set_num_threads(2)
     if world > 1:
@@ -37,7 +37,7 @@ def _run(rank, world, port, out_path, tp=1):
         "grpo": dict(num_prompts_per_step=16, num_generations_per_prompt=4, max_num_steps=2, val_period=0, seed=0),
         "loss_fn": dict(reference_policy_kl_penalty=0.01),
         "policy": dict(precision="float32", train_global_batch_size=64, train_micro_batch_size=8, logprob_batch_size=16,
-                       max_total_sequence_length=128, max_grad_norm=1.0, parallel=dict(tensor_parallel_size=tp),
+                       max_total_sequence_length=128, max_grad_norm=1.0, parallel=dict(tensor_parallel_size=tp, pipeline_parallel_size=pp, context_parallel_size=cp),
                        optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.01)),
                        generation=dict(max_new_tokens=32, temperature=1.0, stop_token_ids=[], kv_cache_tokens=8192, block_size=16, max_running=64)),
         "logger": dict(log_dir=os.path.join(os.path.dirname(out_path), f"logs_w{world}")),
@@ -86,3 +86,19 @@ def test_grpo_oracle_tensor_parallel(tmp_path):
         assert x["reward"] == pytest.approx(y["reward"], abs=1e-9)
         assert x["loss"] == pytest.approx(y["loss"], rel=1e-3, abs=1e-6)
         assert x["grad_norm"] == pytest.approx(y["grad_norm"], rel=2e-3)
+
+
+@pytest.mark.parametrize("pp,cp", [(2, 1), (1, 2)])
+def test_grpo_oracle_pipeline_and_context_parallel(tmp_path, pp, cp):
+    """GRPO end to end with a pipeline- or context-parallel trainer: the stages (ranks) of the replica share the rollout
+    work, every rank serves a complete copy of the weights, and the run reproduces the single-rank numbers."""
+    p1, p2 = str(tmp_path / "w1.json"), str(tmp_path / "w2.json")
+    mp.spawn(_run, args=(1, _free_port(), p1), nprocs=1, join=True)
+    mp.spawn(_run, args=(2, _free_port(), p2, 1, pp, cp), nprocs=2, join=True)
+    a, b = json.load(open(p1)), json.load(open(p2))
+    assert len(a) == len(b) == 2
+    for x, y in zip(a, b):
+        assert y["token_mult_prob_error"] == pytest.approx(1.0, abs=1e-4)
+        assert x["reward"] == pytest.approx(y["reward"], abs=1e-9)
+        assert x["loss"] == pytest.approx(y["loss"], rel=1e-3, abs=1e-6)
+        assert x["grad_norm"] == pytest.approx(y["grad_norm"], rel=5e-3)

@@ -56,6 +56,28 @@ def choose_splits(B: int, Hkv: int, max_len: int, block_size: int, sm_count: int
     return int(max(1, min(want, max(1, max_len // max(block_size, 128)), 32)))
 
 
+def _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out, rows_per_chunk: int = 64):
+    """Decode attention for head dimensions the native kernels do not cover (they are built for 128): the paged keys and
+    values of a chunk of sequences are gathered through the block table and attended with batched matmuls. No host
+    synchronisation and static shapes, so it can be captured in a CUDA graph like the native path."""
+    B, nb = q.shape[0], block_table.shape[1]
+    bs, g = k_cache.shape[2], Hq // Hkv
+    T = nb * bs
+    ar = torch.arange(T, device=q.device)
+    for r0 in range(0, B, rows_per_chunk):
+        r1 = min(B, r0 + rows_per_chunk)
+        bt = block_table[r0:r1].long()
+        k = k_cache[bt].permute(0, 2, 1, 3, 4).reshape(r1 - r0, Hkv, T, D)
+        v = v_cache[bt].permute(0, 2, 1, 3, 4).reshape(r1 - r0, Hkv, T, D)
+        qb = (q[r0:r1, : Hq * D].reshape(r1 - r0, Hkv, g, D).float() * scale).to(k.dtype)
+        s_ = torch.matmul(qb, k.transpose(2, 3)).float()
+        live = ar[None, :] < seq_lens[r0:r1, None]
+        s_ = s_.masked_fill(~live[:, None, None, :], float("-inf"))
+        p = torch.nan_to_num(torch.softmax(s_, dim=-1), nan=0.0)   # rows without context (padding rows) give zeros
+        out[r0:r1] = torch.matmul(p.to(v.dtype), v).reshape(r1 - r0, Hq * D).to(out.dtype)
+    return out
+
+
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                  seq_lens: torch.Tensor, Hq: int, Hkv: int, D: int, *, scale: Optional[float] = None,
                  num_splits: int = 1, scratch: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
@@ -81,6 +103,8 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
             p = torch.softmax(qb @ k.transpose(1, 2), dim=-1)
             out[b] = (p @ v).reshape(Hq * D).to(out.dtype)
         return out
+    if D != 128:
+        return _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out)
     po = pml = None
     if num_splits > 1:
         if scratch is None:

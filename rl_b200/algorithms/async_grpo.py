@@ -93,7 +93,16 @@ def async_grpo_train(policy, generation, dataloader, tokenizer, loss_fn, task_to
     timer = Timer()
     pad = tokenizer.pad_token_id if tokenizer is not None and tokenizer.pad_token_id is not None else 0
     adv_estimator = create_advantage_estimator(g, cfg.get("loss_fn") or {})
-    buffer = buffer or ReplayBuffer(max_size=4 * (max_age + 1))
+    buffer = buffer if buffer is not None else ReplayBuffer(max_size=4 * (max_age + 1))
+    ck = cfg.get("checkpointing") or {}
+    resume = checkpointer.get_resume_paths() if (checkpointer is not None and checkpointer.enabled) else None
+    if resume and resume.get("replay_buffer") and len(buffer) == 0:
+        # trajectories that were collected but not yet trained on survive a restart (their age is still checked on sampling)
+        path = resume["replay_buffer"] if rank == 0 else f"{resume['replay_buffer']}.rank{rank}"
+        import os
+
+        if os.path.exists(path):
+            buffer.load_state_dict(torch.load(path, weights_only=False))
     use_ref = loss_fn.cfg["reference_policy_kl_penalty"] != 0 and policy.ref_flat is not None
     version = save_state.get("weight_version", 0)
     total_steps = save_state["total_steps"]
@@ -139,6 +148,8 @@ def async_grpo_train(policy, generation, dataloader, tokenizer, loss_fn, task_to
         metrics.update(reward=c["r"] / max(1.0, c["n"]), trajectory_age=float(item["age"]), buffer_size=float(len(buffer)),
                        dropped_stale=float(buffer.dropped_stale))
         save_state.update(current_step=total_steps, total_steps=total_steps, weight_version=version)
+        if checkpointer is not None and checkpointer.enabled and ck.get("save_period") and total_steps % ck["save_period"] == 0:
+            save_checkpoint(policy, dataloader, checkpointer, save_state, cfg, total_steps, extra_files={"replay_buffer.pt": buffer.state_dict()})
         timing = timer.get_timing_metrics("sum")
         if logger is not None:
             logger.log_metrics(metrics, total_steps, prefix="train")

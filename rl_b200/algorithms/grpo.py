@@ -19,6 +19,8 @@ from typing import Any, Callable, Optional
 
 import numpy as np
 import torch
+
+from rl_b200.distributed.ft_launcher import beat as _ft_beat
 import torch.distributed as dist
 
 from rl_b200.algorithms.advantage_estimator import create_advantage_estimator
@@ -476,6 +478,7 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
             last_metrics = {"train": metrics, "timing": timing, "performance": perf, "validation": val_metrics}
             if step_callback is not None:
                 step_callback(total_steps, last_metrics)
+            _ft_beat(total_steps)
             timer.reset()
             thr = g.get("stop_at_validation_threshold")
             if thr is not None and val_metrics and val_metrics.get("accuracy", -1e9) >= thr:
@@ -488,7 +491,9 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
 
 
 def save_checkpoint(policy, dataloader, checkpointer: CheckpointManager, save_state: dict, cfg: dict, step: int,
-                    val_metrics: Optional[dict] = None) -> None:
+                    val_metrics: Optional[dict] = None, extra_files: Optional[dict] = None) -> None:
+    """``extra_files``: name -> picklable object written beside the dataloader state by every data-parallel rank that owns
+    one (``replay_buffer.pt`` of the off-policy trainers; rank r > 0 writes ``name.rank{r}``)."""
     rank, world = _world()
     ck = cfg.get("checkpointing") or {}
     info = dict(save_state)
@@ -506,6 +511,10 @@ def save_checkpoint(policy, dataloader, checkpointer: CheckpointManager, save_st
         os.path.join(tmp, "policy", "optimizer") if ck.get("save_optimizer", True) else None,
         os.path.join(tmp, "policy", "tokenizer"),
         model_save_format=ck.get("model_save_format", "safetensors"))
+    for name, obj in (extra_files or {}).items():
+        torch.save(obj, os.path.join(tmp, name if rank == 0 else f"{name}.rank{rank}"))
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and extra_files:
+        dist.barrier()
     if _is_main():
         torch.save(dataloader.state_dict(), os.path.join(tmp, "train_dataloader.pt"))
         checkpointer.finalize_checkpoint(tmp)

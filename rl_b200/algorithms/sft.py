@@ -12,6 +12,8 @@ import os
 from typing import Callable, Optional
 
 import torch
+
+from rl_b200.distributed.ft_launcher import beat as _ft_beat
 import torch.distributed as dist
 
 from rl_b200.algorithms.grpo import _ShardedPromptLoader, _aggregate_train_metrics, _all_reduce_scalars, _is_main, _world, save_checkpoint
@@ -188,6 +190,7 @@ def _supervised_train(policy, loader, val_loader, loss_fn, logger, checkpointer,
             last = {"train": metrics, "timing": timing, "validation": val}
             if step_callback is not None:
                 step_callback(total_steps, last)
+            _ft_beat(total_steps)
             timer.reset()
             if must:
                 return last

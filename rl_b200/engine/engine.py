@@ -366,6 +366,8 @@ class GenerationEngine:
         self._step_counter = 0
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
+        img = getattr(self.cfg, "image_token_id", None)
+        self._banned_ids = torch.tensor([int(img)], dtype=torch.long, device=self.device) if img is not None else None
 
     def requantize(self) -> Optional[dict]:
         """Refreshes the quantised weight copies from the (refitted) bf16 weights; no-op for a bf16 engine."""
@@ -411,7 +413,10 @@ class GenerationEngine:
     def _output_logits(self, h, out=None):
         """[n, V] logits: the local vocabulary slice is projected here and the slices are gathered over the tp group."""
         z = F.gemm(h, self.model.output_weight, out=out if self.tpw == 1 else None, out_dtype=self.logits_dtype)
-        return z if self.tpw == 1 else gather_cols(z, self.tp)
+        z = z if self.tpw == 1 else gather_cols(z, self.tp)
+        if self._banned_ids is not None:   # placeholder tokens (image slots) are inputs only: never sampled
+            z.index_fill_(1, self._banned_ids, -1e30)
+        return z
 
     def _any_rank(self, ep, flag: bool) -> bool:
         import torch.distributed as dist

@@ -173,3 +173,43 @@ def test_rank_that_leaves_is_detected_on_the_host(tmp_path):
         p.join(60)
     msg = open(out).read()
     assert msg.startswith("3 ") and "ranks [1]" in msg
+
+
+def test_ft_launcher_restarts_on_crash_and_on_hang(tmp_path):
+    """Job-level supervision: a crash (non-zero exit) and a hang (stale heartbeat) both lead to a restart; the job, which
+    keeps its progress in a file as a checkpoint would, completes on a later attempt."""
+    import sys
+    import textwrap
+
+    from rl_b200.distributed.ft_launcher import run_with_restarts
+
+    script = tmp_path / "job.py"
+    state = tmp_path / "state.txt"
+    script.write_text(textwrap.dedent(f"""
+        import os, sys, time
+        sys.path.insert(0, {str(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))!r})
+        from rl_b200.distributed.ft_launcher import beat
+        state = {str(state)!r}
+        step = int(open(state).read()) if os.path.exists(state) else 0
+        attempt = int(os.environ["RLB_FT_ATTEMPT"])
+        while step < 6:
+            step += 1
+            open(state, "w").write(str(step))
+            beat(step)
+            if attempt == 0 and step == 2:
+                sys.exit(3)                      # crash
+            if attempt == 1 and step == 4:
+                time.sleep(600)                  # hang: no more heartbeats
+            time.sleep(0.05)
+    """))
+    logs = []
+    res = run_with_restarts([sys.executable, str(script)], max_restarts=3, initial_timeout_s=30, step_timeout_s=1.5, poll_s=0.1, grace_s=2,
+                            log=logs.append)
+    assert res.returncode == 0 and res.restarts == 2
+    assert "exit code 3" in res.reasons[0] and "no heartbeat" in res.reasons[1]
+    assert int(state.read_text()) == 6
+    # restart budget: a job that always fails gives up with its exit code
+    bad = tmp_path / "bad.py"
+    bad.write_text("import sys; sys.exit(5)")
+    res = run_with_restarts([sys.executable, str(bad)], max_restarts=1, poll_s=0.05, log=logs.append)
+    assert res.returncode == 5 and res.restarts == 1 and len(res.reasons) == 2

@@ -64,3 +64,29 @@ def test_async_grpo_ages_and_buffer(tmp_path):
     b2 = async_grpo.ReplayBuffer(4)
     b2.load_state_dict(buf.state_dict())
     assert len(b2) == 1
+
+
+def test_async_grpo_checkpoints_and_restores_its_replay_buffer(tmp_path):
+    import os
+
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+
+    def cfg():
+        return {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=4, max_num_steps=2, val_period=0, seed=0,
+                             async_grpo=dict(enabled=True, max_trajectory_age_steps=2)),
+                "loss_fn": dict(use_importance_sampling_correction=True, reference_policy_kl_penalty=0.0),
+                "policy": _policy_cfg(), "logger": dict(log_dir=str(tmp_path / "logs")),
+                "checkpointing": dict(enabled=True, checkpoint_dir=str(tmp_path / "ck"), save_period=2, keep_top_k=2, metric_name=None)}
+
+    policy, gen, loader, _, loss_fn, logger, ck, ss, c = grpo.setup(cfg(), None, ds, None, env, model_cfg=_mc())
+    async_grpo.async_grpo_train(policy, gen, loader, None, loss_fn, env, logger, ck, ss, c)
+    paths = ck.get_resume_paths()
+    assert paths["replay_buffer"] and os.path.exists(paths["replay_buffer"])
+    saved = torch.load(paths["replay_buffer"], weights_only=False)
+    assert len(saved["items"]) >= 1                               # collected ahead of training, not yet consumed
+    policy2, gen2, loader2, _, loss_fn2, logger2, ck2, ss2, c2 = grpo.setup(cfg(), None, ds, None, env, model_cfg=_mc())
+    buf = async_grpo.ReplayBuffer(12)
+    c2["grpo"]["max_num_steps"] = ss2["total_steps"]              # no further steps: only the restore path runs
+    async_grpo.async_grpo_train(policy2, gen2, loader2, None, loss_fn2, env, logger2, ck2, ss2, c2, buffer=buf)
+    assert len(buf) == len(saved["items"]) and ss2["total_steps"] == 2

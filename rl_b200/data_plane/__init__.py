@@ -2,6 +2,7 @@ from .adapters.local import LocalDataPlane
 from .adapters.tcp_store import TCPStoreDataPlane
 from .codec import batch_to_records, decode_record, encode_record, records_to_batch
 from .interfaces import DataPlaneClient, SampleMeta
+from .observability import ObservedDataPlane
 from .preshard import preshard
 
 
@@ -9,6 +10,8 @@ def create_data_plane(cfg=None, store=None) -> DataPlaneClient:
     """``cfg.backend``: ``local`` (default) or ``tcp_store`` (needs ``store`` or ``cfg.host`` / ``cfg.port`` / ``cfg.is_server``)."""
     cfg = dict(cfg or {})
     backend = cfg.get("backend", "local")
+    if cfg.pop("observe", False):
+        return ObservedDataPlane(create_data_plane(cfg, store))
     if backend in ("local", "noop"):
         return LocalDataPlane(cfg.get("capacity_bytes"))
     if backend == "tcp_store":

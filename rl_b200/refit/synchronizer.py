@@ -88,6 +88,13 @@ class WeightSynchronizer:
             src = params[op.src_param].data_ptr() + op.src_offset * es
             dst = self._arena_ptrs[op.dst_rank] + (self.layout[op.dst_param][0] + op.dst_offset) * es
             row_bytes = op.row_elems * es
+            # every copy is checked against the tensors it touches before anything reaches the device
+            src_end = op.src_offset + (op.rows - 1) * op.src_pitch + op.row_elems
+            dst_end = op.dst_offset + (op.rows - 1) * op.dst_pitch + op.row_elems
+            d_off, (d_r, d_c) = self.layout[op.dst_param]
+            if not (0 <= op.src_offset and src_end <= params[op.src_param].numel() and 0 <= op.dst_offset and dst_end <= d_r * d_c
+                    and d_off + dst_end <= self.arena_numel and 0 <= op.dst_rank < max(1, self.world)):
+                raise ValueError(f"refit op out of bounds: {op}")
             vec_ok = row_bytes % 16 == 0 and src % 16 == 0 and dst % 16 == 0 and (op.src_pitch * es) % 16 == 0 and (op.dst_pitch * es) % 16 == 0
             rows, sp, dp = op.rows, op.src_pitch * es, op.dst_pitch * es
             if rows > 1 and sp == row_bytes and dp == row_bytes:  # contiguous on both sides: one long row

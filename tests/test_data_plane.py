@@ -146,3 +146,12 @@ def test_single_controller_drops_stale_and_reports_stall(tmp_path):
     sc2._on_stall(999.0)
     with pytest.raises(ControllerStalled):
         sc2.run()
+
+
+def test_observed_data_plane_counts_events():
+    dp = create_data_plane({"backend": "local", "observe": True})
+    dp.put("a", {"x": torch.arange(3)})
+    dp.put("b", {"x": torch.arange(4)})
+    assert len(dp.get(["a", "b"])) == 2 and dp.delete(["a"]) == 1
+    st = dp.stats()
+    assert st["put_calls"] == 2 and st["get_items"] == 2 and st["delete_calls"] == 1 and st["resident_samples"] == 1 and st["get_seconds"] >= 0

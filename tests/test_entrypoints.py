@@ -72,7 +72,12 @@ def test_config_cli_and_refit_model(capsys):
     assert r["recv_bytes_per_rank"] == pytest.approx(16e9) and r["seconds"] == pytest.approx(0.02, rel=0.01)
 
 
-@pytest.mark.parametrize("yaml_name", sorted(f for f in os.listdir(os.path.join(ROOT, "examples", "configs")) if f.endswith(".yaml")))
+def _recipes():
+    base = os.path.join(ROOT, "examples", "configs")
+    return sorted(os.path.relpath(os.path.join(d, f), base) for d, _, fs in os.walk(base) for f in fs if f.endswith(".yaml") and "evals" not in d)
+
+
+@pytest.mark.parametrize("yaml_name", _recipes())
 def test_every_recipe_loads_and_resolves(yaml_name):
     from rl_b200.utils.config import load_config
 

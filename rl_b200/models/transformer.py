@@ -524,6 +524,41 @@ class CausalLM(nn.Module):
         log-softmax (vocabulary-parallel under tensor parallelism)."""
         return self.logprobs_from_hidden(self.hidden_states(batch, h_in), batch, temperature, want_entropy)
 
+    def next_token_logprobs_filtered(self, batch: PackedBatch, top_k: Optional[int], top_p: float, temperature: float = 1.0,
+                                     h_in: Optional[torch.Tensor] = None, chunk_rows: int = 2048) -> torch.Tensor:
+        """Log-probabilities under the sampler's *processed* distribution (temperature, then top-k / top-p): what the
+        importance ratio must use when rollouts were sampled with those filters
+        (nemo_rl/algorithms/logits_sampling_utils.py:112-285). The logits are materialised ``chunk_rows`` rows at a time;
+        with tensor parallelism the vocabulary slices of a chunk are gathered first."""
+        from rl_b200.algorithms.sampling_utils import apply_top_k_top_p
+
+        if self.cp is not None or (self.tp.world > 1 and self.tp.sequence_parallel):
+            raise NotImplementedError("top-k / top-p training log-probabilities need full rows on every rank (no sequence / context parallelism)")
+        h = self.hidden_states(batch, h_in)
+        ids = batch.input_ids.long()
+        T = ids.shape[0]
+        targets = torch.roll(ids, -1)
+        out = []
+        for r0 in range(0, T, chunk_rows):
+            hc = h[r0 : r0 + chunk_rows]
+            if self.tp.world == 1:
+                z = F.linear(hc, self.output_weight).float()
+            else:
+                from rl_b200.parallel.tensor import gather_cols
+
+                z = gather_cols(column_linear(hc, self.output_weight, None, self.tp), self.tp).float()
+            z = z / (temperature if temperature > 0 else 1.0)
+            z, _ = apply_top_k_top_p(z, top_k, top_p)
+            lp = torch.log_softmax(z, dim=-1).gather(-1, targets[r0 : r0 + chunk_rows, None])[:, 0]
+            out.append(torch.where(torch.isfinite(lp), lp, torch.full_like(lp, -1e4)))   # a token outside the kept set
+        lp_rows = torch.cat(out)
+        starts = batch.cu_seqlens[:-1].long()
+        is_start = torch.zeros(T, dtype=torch.bool, device=h.device)
+        is_start[starts[starts < T]] = True
+        logp = torch.zeros(T, dtype=torch.float32, device=h.device)
+        logp[1:] = torch.where(~is_start[1:], lp_rows[:-1], torch.zeros_like(lp_rows[:-1]))
+        return logp
+
     def values(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Scalar head output per token [T] (critic / reward model)."""
         h = self.hidden_states(batch, h_in)

@@ -239,9 +239,12 @@ class PolicyWorker:
                                            rows_of=lambda item: int(item[0].input_ids.numel()) // div)
         self.generation = None
         self.temperature = 1.0
+        self.train_top_k, self.train_top_p = None, 1.0   # the sampler's filters, mirrored in the training log-probabilities
         gen_cfg = cfg.get("generation") or {}
         if gen_cfg:
             self.temperature = float(gen_cfg.get("temperature", 1.0) or 1.0)
+            self.train_top_k = int(gen_cfg["top_k"]) if gen_cfg.get("top_k") else None
+            self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
         self.timers: dict[str, float] = {}
 
     # ------------------------------------------------------------------ model-parallel gradient bookkeeping
@@ -322,6 +325,8 @@ class PolicyWorker:
         self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride,
                                            split_group=split_group)
         self.temperature = float(self.generation.cfg["temperature"] or 1.0)
+        self.train_top_k = int(self.generation.cfg["top_k"]) if self.generation.cfg.get("top_k") else None
+        self.train_top_p = float(self.generation.cfg.get("top_p") or 1.0)
         return self.generation
 
     def _build_serving_layout(self, gen_tp: int):
@@ -427,6 +432,13 @@ class PolicyWorker:
             if backward:
                 (lp.sum() * 0.0).backward()
 
+    def _policy_logprobs(self, batch: PackedBatch, h_in=None) -> torch.Tensor:
+        """Per-token log-probabilities under the distribution the sampler draws from (temperature and, when the generation
+        config uses them, top-k / top-p)."""
+        if (self.train_top_k or 0) > 0 or self.train_top_p < 1.0:
+            return self.model.next_token_logprobs_filtered(batch, self.train_top_k, self.train_top_p, self.temperature, h_in=h_in)
+        return self.model.next_token_logprobs(batch, self.temperature, h_in=h_in)[0]
+
     def _token_budget(self, kind: str) -> Optional[int]:
         sp = self.cfg.get("sequence_packing") or {}
         db = self.cfg.get("dynamic_batching") or {}
@@ -465,7 +477,7 @@ class PolicyWorker:
 
             def stage(item, h_in):
                 if self.model.last_stage:
-                    return self.model.next_token_logprobs(item[0], self.temperature, h_in=h_in)[0]
+                    return self._policy_logprobs(item[0], h_in=h_in)
                 return self.model.hidden_states(item[0], h_in)
 
             lps = self.pipeline.forward_only(items, stage, lambda item: (int(item[0].input_ids.numel()),))
@@ -476,7 +488,7 @@ class PolicyWorker:
         extra = self._extra_passes(len(mbl))  # agreed before the first pass: the count exchange is itself a collective
         for mb, idx in mbl:
             batch, Smb = self._pack(mb)
-            lp, _ = self.model.next_token_logprobs(batch, self.temperature)
+            lp = self._policy_logprobs(batch)
             out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
         for _ in range(extra):
             self._dummy_pass(backward=False)
@@ -525,7 +537,7 @@ class PolicyWorker:
         """Model outputs in the form the loss wants. ``h_in``: the residual stream from the previous pipeline stage."""
         it = getattr(loss_fn, "input_type", LossInputType.LOGPROB)
         if it == LossInputType.LOGPROB:
-            lp, _ = self.model.next_token_logprobs(batch, self.temperature, h_in=h_in)
+            lp = self._policy_logprobs(batch, h_in=h_in)
             return {"next_token_logprobs": batch.unpack(lp, S)[:, 1:]}
         if it == LossInputType.VALUE:
             return {"values": batch.unpack(self.model.values(batch, h_in), S)}

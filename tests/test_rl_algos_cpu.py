@@ -90,3 +90,24 @@ def test_async_grpo_checkpoints_and_restores_its_replay_buffer(tmp_path):
     c2["grpo"]["max_num_steps"] = ss2["total_steps"]              # no further steps: only the restore path runs
     async_grpo.async_grpo_train(policy2, gen2, loader2, None, loss_fn2, env, logger2, ck2, ss2, c2, buffer=buf)
     assert len(buf) == len(saved["items"]) and ss2["total_steps"] == 2
+
+
+def test_training_logprobs_follow_the_samplers_top_k_and_top_p(tmp_path):
+    """Rollouts sampled with top-k / top-p: the trainer scores them under the same filtered distribution, so engine and
+    trainer agree token by token; without the filters on the training side they would not."""
+    ds = RandomTokenPromptDataset(64, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    pc = _policy_cfg()
+    pc["generation"].update(top_k=6, top_p=0.8)
+    cfg = {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=4, max_num_steps=2, val_period=0, seed=0),
+           "loss_fn": dict(reference_policy_kl_penalty=0.0), "policy": pc, "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    policy, gen, loader, _, loss_fn, logger, ck, ss, cfg = grpo.setup(cfg, None, ds, None, env, model_cfg=_mc())
+    assert policy.train_top_k == 6 and policy.train_top_p == 0.8
+    hist = []
+    grpo.grpo_train(policy, gen, loader, None, None, loss_fn, env, env, logger, ck, ss, cfg, step_callback=lambda s, m: hist.append(m["train"]))
+    assert all(abs(h["token_mult_prob_error"] - 1.0) < 1e-3 for h in hist)
+    policy.train_top_k, policy.train_top_p = None, 1.0          # unfiltered scoring of filtered samples: a visible gap
+    hist2 = []
+    cfg["grpo"].update(max_num_steps=3, max_num_epochs=5)
+    grpo.grpo_train(policy, gen, loader, None, None, loss_fn, env, env, logger, ck, ss, cfg, step_callback=lambda s, m: hist2.append(m["train"]))
+    assert hist2 and hist2[-1]["token_mult_prob_error"] > 1.05

@@ -141,3 +141,20 @@ def test_refit_verifier_and_fingerprint(tmp_path):
     p = tmp_path / "other.json"
     p.write_text(json.dumps(dict(a, torch="0.0")))
     assert fp.main(["--compare", str(p)]) == 1
+
+
+def test_model_diagnostics(tmp_path, capsys):
+    from rl_b200.models import hf_io
+    from rl_b200.models.config import preset
+    from rl_b200.models.transformer import build_model
+    from rl_b200.tools import model_diagnostics as md
+
+    assert md.main(["decode-vs-prefill", "--device", "cpu", "--new-tokens", "48"]) == 0
+    assert md.main(["max-len", "--device", "cpu"]) == 0
+    m = build_model(preset("tiny-llama-oracle", torch_dtype="float32"), dtype=torch.float32, seed=0)
+    with torch.no_grad():
+        m.embed_tokens[5].zero_()
+    hf_io.save_pretrained(m, str(tmp_path))
+    assert md.main(["embeddings", "--path", str(tmp_path)]) == 1
+    out = capsys.readouterr().out
+    assert '"zero_rows": [5]' in out and '"check": "max-len"' in out

@@ -145,3 +145,69 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
         "mean_total_reward": float(total_reward.mean()) if n else 0.0,
     }
     return batch, metrics
+
+
+def run_async_multi_turn_rollout(frontend, input_batch: BatchedDataDict, tokenizer, task_to_env: dict[str, EnvironmentInterface],
+                                 max_seq_len: int, max_rollout_turns: int = 1, sampling: Optional[dict] = None,
+                                 max_concurrency: int = 256) -> tuple[BatchedDataDict, dict[str, Any]]:
+    """Sample-level rollouts: every sample runs its own generate -> environment loop on a worker thread, so a sample whose
+    environment is slow (a tool call, a remote verifier) or that needs more turns does not hold the others back. The engine
+    sees the concurrent requests through ``frontend`` (a :class:`rl_b200.engine.http_server.BatchingFrontend`, or anything
+    with ``submit(prompt_ids, sampling) -> record``), which forms the batches. Same outputs as
+    :func:`run_multi_turn_rollout` (nemo_rl/experience/rollouts.py:1172, ``run_async_multi_turn_rollout``)."""
+    import concurrent.futures as cf
+
+    batch = input_batch
+    n = len(batch["message_log"])
+    sampling = dict(sampling or {})
+    total_reward = torch.zeros(n, dtype=torch.float32)
+    truncated = torch.zeros(n, dtype=torch.bool)
+    gen_tokens = torch.zeros(n, dtype=torch.long)
+    turns = torch.zeros(n, dtype=torch.long)
+    answers: list[Any] = [None] * n
+
+    def one(i: int) -> None:
+        log = batch["message_log"][i]
+        env = task_to_env[batch["task_name"][i]]
+        meta = batch["extra_env_info"][i]
+        for turn in range(max_rollout_turns):
+            prompt = torch.cat([m["token_ids"] for m in log]).tolist()
+            room = max_seq_len - len(prompt)
+            if room <= 0:
+                truncated[i] = True
+                return
+            sp = dict(sampling)
+            sp["max_new_tokens"] = min(int(sp.get("max_new_tokens", 256)), room)
+            rec = frontend.submit(prompt, sp)
+            toks = torch.tensor(rec.out_tokens, dtype=torch.long)
+            text = tokenizer.decode(rec.out_tokens, skip_special_tokens=True) if tokenizer is not None else ""
+            log.append({"role": "assistant", "content": text, "token_ids": toks,
+                        "generation_logprobs": torch.tensor(rec.out_logprobs, dtype=torch.float32)})
+            gen_tokens[i] += toks.numel()
+            turns[i] += 1
+            truncated[i] = bool(rec.truncated)
+            r = env.step([log], [meta])
+            rew = r.rewards[0]
+            total_reward[i] += float(rew.sum() if rew.dim() else rew)
+            meta = r.metadata[0]
+            batch["extra_env_info"][i] = meta
+            if r.answers is not None:
+                answers[i] = r.answers[0]
+            if bool(r.terminateds[0]) or turn + 1 >= max_rollout_turns:
+                return
+            ob = r.observations[0]
+            ids = tokenizer(ob["content"], add_special_tokens=False, return_tensors="pt")["input_ids"][0] if tokenizer is not None else torch.empty(0, dtype=torch.long)
+            if len(prompt) + toks.numel() + ids.numel() >= max_seq_len:
+                truncated[i] = True
+                return
+            log.append({"role": ob.get("role", "environment"), "content": ob["content"], "token_ids": ids})
+
+    with cf.ThreadPoolExecutor(max_workers=max(1, min(max_concurrency, n))) as pool:
+        for f in [pool.submit(one, i) for i in range(n)]:
+            f.result()   # re-raises a sample's failure
+    batch["total_reward"], batch["truncated"], batch["answers"], batch["generation_lengths"] = total_reward, truncated, answers, gen_tokens
+    batch["length"] = torch.tensor([sum(int(m["token_ids"].numel()) for m in log) for log in batch["message_log"]], dtype=torch.long)
+    metrics = {"total_turns": int(turns.sum()), "avg_turns_per_sample": float(turns.float().mean()) if n else 0.0,
+               "max_turns_per_sample": int(turns.max()) if n else 0, "truncation_rate": float(truncated.float().mean()) if n else 0.0,
+               "total_generated_tokens": int(gen_tokens.sum()), "mean_total_reward": float(total_reward.mean()) if n else 0.0}
+    return batch, metrics

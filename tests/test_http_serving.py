@@ -127,3 +127,44 @@ def test_remote_environment_round_trip_and_server_loss():
     with pytest.raises(ConnectionError):
         env.step(logs[:1], [{"ground_truth": "red"}])
     env.shutdown()
+
+
+def test_async_sample_level_rollout_through_the_batching_frontend():
+    """Every sample runs its own generate -> environment loop; samples need different numbers of turns."""
+    from rl_b200.data.collate import rl_collate_fn
+    from rl_b200.engine.http_server import BatchingFrontend
+    from rl_b200.environments.interfaces import EnvironmentReturn
+    from rl_b200.experience.rollouts import run_async_multi_turn_rollout
+
+    class CountdownEnv:
+        """Terminates a sample after ``turns`` assistant messages; reward 1 per turn."""
+
+        def step(self, logs, metas):
+            out_meta, term = [], []
+            for log, m in zip(logs, metas):
+                left = m["turns"] - 1
+                out_meta.append({"turns": left})
+                term.append(left <= 0)
+            n = len(logs)
+            return EnvironmentReturn([{"role": "environment", "content": "go on"}] * n, out_meta, [None] * n, torch.ones(n), torch.tensor(term), None)
+
+    tok = ByteTokenizer(vocab_size=300)
+    mc = ModelConfig(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    eng = GenerationEngine(CausalLM(mc, dtype=torch.float32, device="cpu", seed=2), block_size=4, num_blocks=512, max_running=16,
+                           max_model_len=256, use_cuda_graphs=False)
+    fe = BatchingFrontend(eng, batch_window_s=0.01)
+    try:
+        data = [{"message_log": [{"role": "user", "content": "x", "token_ids": torch.tensor([10 + i, 20, 30])}], "length": 3,
+                 "extra_env_info": {"turns": 1 + i % 3}, "task_name": "cd", "idx": i} for i in range(6)]
+        batch = rl_collate_fn(data)
+        out, m = run_async_multi_turn_rollout(fe, batch, tok, {"cd": CountdownEnv()}, max_seq_len=200, max_rollout_turns=4,
+                                              sampling=dict(max_new_tokens=5, temperature=1.0))
+        assert out["total_reward"].tolist() == [1.0, 2.0, 3.0, 1.0, 2.0, 3.0] and m["total_turns"] == 12
+        assert out["generation_lengths"].tolist() == [5, 10, 15, 5, 10, 15]
+        roles = [[x["role"] for x in log] for log in out["message_log"]]
+        assert roles[0] == ["user", "assistant"] and roles[2] == ["user", "assistant", "environment", "assistant", "environment", "assistant"]
+        assert all(x["generation_logprobs"].numel() == 5 for log in out["message_log"] for x in log if x["role"] == "assistant")
+        assert fe._calls < 12          # concurrent samples shared engine calls
+    finally:
+        fe.close()

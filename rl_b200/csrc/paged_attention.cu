@@ -42,6 +42,52 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, con
   }
 }
 
+// Rotary embedding of the q and k heads (in place, HF rotate_half convention) fused with the scatter of the rotated k and of
+// v into the paged cache: one warp per (token, head) of the fused [q | k | v] row. slot < 0: rotate only.
+__global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                     const long long* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache,
+                                     __nv_bfloat16* __restrict__ v_cache, long long T, int Hq, int Hkv, int D, int block_size,
+                                     long long row_stride) {
+  pdl_sync();
+  const int heads = Hq + 2 * Hkv;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= T * heads) return;
+  const long long t = wid / heads;
+  const int h = static_cast<int>(wid - t * heads);
+  __nv_bfloat16* p = qkv + t * row_stride + static_cast<long long>(h) * D;
+  const long long slot = slots[t];
+  __nv_bfloat16* dst = nullptr;
+  if (h >= Hq && slot >= 0) {
+    const long long blk = slot / block_size;
+    const int off = static_cast<int>(slot - blk * block_size);
+    const int kh = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
+    dst = (h < Hq + Hkv ? k_cache : v_cache) + ((blk * Hkv + kh) * block_size + off) * D;
+  }
+  if (h >= Hq + Hkv) {  // v: copy
+    if (dst)
+      for (int i = lane * 2; i < D; i += 64) *reinterpret_cast<uint32_t*>(dst + i) = *reinterpret_cast<const uint32_t*>(p + i);
+    return;
+  }
+  const float ps = static_cast<float>(pos[t]);
+  const int half = D >> 1;
+  for (int i = lane * 2; i < half; i += 64) {
+    const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p + i));
+    const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p + i + half));
+    float s0, c0, s1, c1;
+    sincosf(ps * inv_freq[i], &s0, &c0);
+    sincosf(ps * inv_freq[i + 1], &s1, &c1);
+    const uint32_t a = pack_bf16x2(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+    const uint32_t b = pack_bf16x2(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+    *reinterpret_cast<uint32_t*>(p + i) = a;
+    *reinterpret_cast<uint32_t*>(p + i + half) = b;
+    if (dst) {
+      *reinterpret_cast<uint32_t*>(dst + i) = a;
+      *reinterpret_cast<uint32_t*>(dst + i + half) = b;
+    }
+  }
+}
+
 constexpr int DEC_THREADS = 128;
 constexpr int LANES_PER_TOKEN = 8;
 constexpr int TOKENS_PER_WARP = 32 / LANES_PER_TOKEN;  // 4
@@ -306,6 +352,20 @@ RLB_API int rlb_kv_cache_write(const void* qkv, const long long* slots, void* k_
   rlb_launch_pdl(kv_cache_write_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(qkv), slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
       reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Rotates q and k of the fused rows in place and writes the rotated k and v into the paged cache (see rope_kv_write_kernel).
+RLB_API int rlb_rope_kv_cache_write(void* qkv, const int* pos, const float* inv_freq, const long long* slots, void* k_cache,
+                                    void* v_cache, long long T, int Hq, int Hkv, int D, int block_size, long long row_stride,
+                                    void* stream) {
+  if (T <= 0) return 0;
+  if (D % 4 || row_stride % 2) return -2;
+  const long long warps = T * (Hq + 2 * Hkv);
+  const long long blocks = (warps * 32 + 255) / 256;
+  rlb_launch_pdl(rope_kv_write_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                 reinterpret_cast<__nv_bfloat16*>(qkv), pos, inv_freq, slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
+                 reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride);
   return static_cast<int>(cudaGetLastError());
 }
 

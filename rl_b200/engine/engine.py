@@ -458,8 +458,8 @@ class GenerationEngine:
             h = m.merge_vision(h, batch.input_ids, getattr(batch, "mm", None))
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
-            qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq)
-            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq, apply_rope=False)
+            qkv = E.rope_kv_cache_write(qkv, batch.positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
             a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, self.hq, self.hkv, c.head_dim)
             h = self._layer_tail(layer, h, a)
         hl = E.gather_rows(h, last_idx.to(torch.int32))
@@ -472,8 +472,8 @@ class GenerationEngine:
         h = F.embedding(ids, m.embed_tokens)
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
-            qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq)
-            E.kv_cache_write(qkv, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
+            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
             a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, self.hq,
                                self.hkv, c.head_dim, num_splits=num_splits, scratch=scratch)
             h = self._layer_tail(layer, h, a)

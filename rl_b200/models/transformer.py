@@ -166,8 +166,9 @@ class Attention(nn.Module):
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
 
-    def project_qkv(self, x, positions, inv_freq):
-        """x [T, d] -> fused [T, (Hq+2Hkv)*D] with q/k normalised (Qwen3) and rotated."""
+    def project_qkv(self, x, positions, inv_freq, apply_rope: bool = True):
+        """x [T, d] -> fused [T, (Hq+2Hkv)*D] with q/k normalised (Qwen3) and rotated (``apply_rope=False``: the caller
+        rotates, e.g. fused with the KV-cache write of the generation engine)."""
         c = self.cfg
         qkv = column_linear(x, self.qkv_proj, self.qkv_bias, self.tp)
         if self.qkv_lora is not None:
@@ -177,6 +178,8 @@ class Attention(nn.Module):
         if c.qk_norm:
             qkv = F.head_rmsnorm(qkv, self.q_norm, 0, self.hq, c.head_dim, c.rms_norm_eps)
             qkv = F.head_rmsnorm(qkv, self.k_norm, self.q_local, self.hkv, c.head_dim, c.rms_norm_eps)
+        if not apply_rope:
+            return qkv
         return F.rope(qkv, positions, inv_freq, self.hq + self.hkv, c.head_dim)
 
     def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen):

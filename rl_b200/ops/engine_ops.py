@@ -34,6 +34,21 @@ def kv_cache_write(qkv: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor
          block_size, qkv.stride(0), stream_ptr())
 
 
+def rope_kv_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor,
+                        v_cache: torch.Tensor, Hq: int, Hkv: int, D: int) -> torch.Tensor:
+    """Rotary embedding of q and k (in place on CUDA) and the cache scatter of k and v in one launch; returns the rotated
+    fused rows."""
+    if not use_native(qkv):
+        from rl_b200.ops import functional as F
+
+        qkv = F.rope(qkv, positions, inv_freq, Hq + Hkv, D)
+        kv_cache_write(qkv, slots, k_cache, v_cache, Hq, Hkv, D)
+        return qkv
+    call("rlb_rope_kv_cache_write", ptr(qkv), ptr(positions.to(torch.int32)), ptr(inv_freq), ptr(slots), ptr(k_cache), ptr(v_cache),
+         qkv.shape[0], Hq, Hkv, D, k_cache.shape[2], qkv.stride(0), stream_ptr())
+    return qkv
+
+
 def decode_scratch_sizes(B: int, Hq: int, num_splits: int, D: int = 128) -> tuple[int, int]:
     return B * Hq * num_splits * D, B * Hq * num_splits * 2
 

@@ -21,7 +21,8 @@ using namespace rlb;
 // qkv: [T, (Hq + 2*Hkv) * D] with layout [q | k | v]; slot[t] = block * block_size + offset, <0: skip.
 __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ slots,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                      long long T, int Hq, int Hkv, int D, int block_size, long long row_stride) {
+                                      long long T, int Hq, int Hkv, int D, int block_size, long long row_stride,
+                                      long long num_slots, int* status) {
   pdl_sync();
   const int vec_per_row = Hkv * D / 8;
   const long long total = T * vec_per_row;
@@ -32,6 +33,10 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, con
     const int h = r / D, d = r - h * D;
     const long long slot = slots[t];
     if (slot < 0) continue;
+    if (slot >= num_slots) {  // a slot outside the cache is recorded and skipped, never written
+      if (status) atomicCAS(status, 0, RLB_ERR_BAD_ARG);
+      continue;
+    }
     const long long blk = slot / block_size;
     const int off = static_cast<int>(slot - blk * block_size);
     const long long dst = ((blk * Hkv + h) * block_size + off) * D + d;
@@ -47,7 +52,7 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, con
 __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                      const long long* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache,
                                      __nv_bfloat16* __restrict__ v_cache, long long T, int Hq, int Hkv, int D, int block_size,
-                                     long long row_stride) {
+                                     long long row_stride, long long num_slots, int* status) {
   pdl_sync();
   const int heads = Hq + 2 * Hkv;
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -58,7 +63,9 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
   __nv_bfloat16* p = qkv + t * row_stride + static_cast<long long>(h) * D;
   const long long slot = slots[t];
   __nv_bfloat16* dst = nullptr;
-  if (h >= Hq && slot >= 0) {
+  if (slot >= num_slots && h >= Hq) {  // outside the cache: recorded, rotated in place, not written
+    if (status && lane == 0) atomicCAS(status, 0, RLB_ERR_BAD_ARG);
+  } else if (h >= Hq && slot >= 0) {
     const long long blk = slot / block_size;
     const int off = static_cast<int>(slot - blk * block_size);
     const int kh = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
@@ -343,7 +350,8 @@ RLB_API int rlb_gather_rows(const void* x, const int* idx, void* out, long long 
 }
 
 RLB_API int rlb_kv_cache_write(const void* qkv, const long long* slots, void* k_cache, void* v_cache, long long T,
-                               int Hq, int Hkv, int D, int block_size, long long row_stride, void* stream) {
+                               int Hq, int Hkv, int D, int block_size, long long row_stride, long long num_blocks, int* status,
+                               void* stream) {
   if (T <= 0) return 0;
   if (D % 8 || row_stride % 8) return -2;
   const long long total = T * (Hkv * D / 8);
@@ -351,21 +359,21 @@ RLB_API int rlb_kv_cache_write(const void* qkv, const long long* slots, void* k_
   if (grid > 148 * 8) grid = 148 * 8;
   rlb_launch_pdl(kv_cache_write_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(qkv), slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
-      reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride);
+      reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride, num_blocks * block_size, status);
   return static_cast<int>(cudaGetLastError());
 }
 
 // Rotates q and k of the fused rows in place and writes the rotated k and v into the paged cache (see rope_kv_write_kernel).
 RLB_API int rlb_rope_kv_cache_write(void* qkv, const int* pos, const float* inv_freq, const long long* slots, void* k_cache,
                                     void* v_cache, long long T, int Hq, int Hkv, int D, int block_size, long long row_stride,
-                                    void* stream) {
+                                    long long num_blocks, int* status, void* stream) {
   if (T <= 0) return 0;
   if (D % 4 || row_stride % 2) return -2;
   const long long warps = T * (Hq + 2 * Hkv);
   const long long blocks = (warps * 32 + 255) / 256;
   rlb_launch_pdl(rope_kv_write_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
                  reinterpret_cast<__nv_bfloat16*>(qkv), pos, inv_freq, slots, reinterpret_cast<__nv_bfloat16*>(k_cache),
-                 reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride);
+                 reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, block_size, row_stride, num_blocks * block_size, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -31,7 +31,7 @@ def kv_cache_write(qkv: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor
         v_cache[blk, :, off] = v[ok]
         return
     call("rlb_kv_cache_write", ptr(qkv), ptr(slots), ptr(k_cache), ptr(v_cache), qkv.shape[0], Hq, Hkv, D,
-         block_size, qkv.stride(0), stream_ptr())
+         block_size, qkv.stride(0), k_cache.shape[0], ptr(_L.status_word(qkv.device)), stream_ptr())
 
 
 def rope_kv_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor,
@@ -45,7 +45,7 @@ def rope_kv_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: to
         kv_cache_write(qkv, slots, k_cache, v_cache, Hq, Hkv, D)
         return qkv
     call("rlb_rope_kv_cache_write", ptr(qkv), ptr(positions.to(torch.int32)), ptr(inv_freq), ptr(slots), ptr(k_cache), ptr(v_cache),
-         qkv.shape[0], Hq, Hkv, D, k_cache.shape[2], qkv.stride(0), stream_ptr())
+         qkv.shape[0], Hq, Hkv, D, k_cache.shape[2], qkv.stride(0), k_cache.shape[0], ptr(_L.status_word(qkv.device)), stream_ptr())
     return qkv
 
 

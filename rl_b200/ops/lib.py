@@ -51,8 +51,8 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_clipped_pg": [P, P, P, P, P, P, L, F, F, F, F, I, F, F, I, I, F, F, I, I, I, F, P, P, P],
     "rlb_cast_f32_bf16": [P, P, L, P],
     "rlb_add_bf16": [P, P, P, L, P],
-    "rlb_kv_cache_write": [P, P, P, P, L, I, I, I, I, L, P],
-    "rlb_rope_kv_cache_write": [P, P, P, P, P, P, L, I, I, I, I, L, P],
+    "rlb_kv_cache_write": [P, P, P, P, L, I, I, I, I, L, L, P, P],
+    "rlb_rope_kv_cache_write": [P, P, P, P, P, P, L, I, I, I, I, L, L, P, P],
     "rlb_paged_decode": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
     "rlb_paged_decode_tma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
     "rlb_paged_decode_mma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],

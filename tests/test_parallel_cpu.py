@@ -434,3 +434,38 @@ def test_expert_parallel_ranks_with_unequal_microbatch_counts_do_not_deadlock():
     out = _spawn(_ep_uneven_worker, 2)
     assert out[0]["loss"] == pytest.approx(out[1]["loss"]) and out[0]["gn"] == pytest.approx(out[1]["gn"], rel=1e-4)
     assert all(abs(m["lp"]) > 0 for m in out.values())
+
+
+def _sc_worker(rank, world):
+    """Single-controller GRPO on two data-parallel ranks: every rank runs its own pumps in the fixed interleaved order."""
+    from rl_b200.algorithms import grpo
+    from rl_b200.algorithms.single_controller import SingleController
+    from rl_b200.data.datasets.synthetic import RandomTokenPromptDataset
+    from rl_b200.environments.synthetic import TokenFractionEnv
+    from rl_b200.models.config import preset
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    ds = RandomTokenPromptDataset(128, 4, 8, 2048, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    cfg = {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=2, max_num_steps=3, val_period=0, seed=0),
+           "loss_fn": dict(use_importance_sampling_correction=True, reference_policy_kl_penalty=0.0),
+           "single_controller": dict(pump_mode="interleaved", max_trajectory_age_steps=1, rollout_ahead_batches=2),
+           "policy": dict(precision="float32", train_global_batch_size=8, train_micro_batch_size=2, logprob_batch_size=4,
+                          max_total_sequence_length=48, max_grad_norm=1.0, optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3)),
+                          generation=dict(max_new_tokens=6, temperature=1.0, stop_token_ids=[], kv_cache_tokens=2048, block_size=8, max_running=16)),
+           "logger": dict(log_dir=f"/tmp/rlb_sc_test_{os.getpid()}"), "checkpointing": dict(enabled=False)}
+    policy, gen, loader, _, loss_fn, logger, ck, ss, cfg = grpo.setup(cfg, None, ds, None, env, model_cfg=mc)
+    hist = []
+    sc = SingleController(policy, gen, loader, None, loss_fn, env, cfg, logger=logger, save_state=ss, step_callback=lambda s, m: hist.append(m["train"]))
+    sc.run()
+    w = next(policy.model.parameters()).detach().double().sum().item()
+    return dict(steps=len(hist), loss=[h["loss"] for h in hist], gn=[h["grad_norm"] for h in hist], ages=[h["trajectory_age"] for h in hist], w=w,
+                trained=sc.stats["samples_trained"])
+
+
+def test_single_controller_on_two_ranks_stays_in_lock_step():
+    out = _spawn(_sc_worker, 2)
+    a, b = out[0], out[1]
+    assert a["steps"] == b["steps"] == 3 and a["trained"] == b["trained"] == 3 * 4
+    assert a["loss"] == pytest.approx(b["loss"]) and a["gn"] == pytest.approx(b["gn"])     # global-batch metrics agree
+    assert a["w"] == pytest.approx(b["w"], rel=1e-12) and max(a["ages"]) <= 1             # replicas hold the same weights

@@ -92,11 +92,19 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
 __global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ src, long long lds,
                                                           __nv_fp8_storage_t* __restrict__ dst, long long ldd,
                                                           unsigned char* __restrict__ scales, long long ldsc, int R,
-                                                          int groups) {
+                                                          int groups, int blocked, int R_pad) {
+  // blocked: scales go straight into the layout the block-scaled MMA reads (one 512-byte atom per 128 rows x 128 columns,
+  // byte (r % 32) * 16 + (r % 128 / 32) * 4 + g % 4); rows R..R_pad of the last atom row get scale byte 0.
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= static_cast<long long>(R) * groups) return;
+  if (gid >= static_cast<long long>(blocked ? R_pad : R) * groups) return;
   const long long r = gid / groups;
   const int g = static_cast<int>(gid - r * groups);
+  unsigned char* sc_out = blocked ? scales + ((r >> 7) * (groups >> 2) + (g >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (g & 3)
+                                  : scales + r * ldsc + g;
+  if (r >= R) {
+    *sc_out = 0;
+    return;
+  }
   const __nv_bfloat16* p = src + r * lds + g * 32;
   float v[32];
   float amax = 0.f;
@@ -112,7 +120,7 @@ __global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* _
   unsigned char e;
   const float ds = pow2_ceil_descale(amax / FP8_MAX, &e);
   const float scale = 1.f / ds;
-  scales[r * ldsc + g] = e;
+  *sc_out = e;
   unsigned char b[32];
 #pragma unroll
   for (int k = 0; k < 32; ++k) b[k] = __nv_cvt_float_to_fp8(fminf(fmaxf(v[k] * scale, -FP8_MAX), FP8_MAX), __NV_SATFINITE, __NV_E4M3);
@@ -167,7 +175,21 @@ RLB_API int rlb_quant_mxfp8(const void* src, long long lds, void* dst, long long
   const long long n = static_cast<long long>(R) * (C / 32);
   quant_mxfp8_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src), lds, static_cast<__nv_fp8_storage_t*>(dst), ldd,
-      static_cast<unsigned char*>(scales), ldsc, R, C / 32);
+      static_cast<unsigned char*>(scales), ldsc, R, C / 32, 0, R);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same quantisation with the scales written in the blocked layout of the MXFP8 GEMM: `scales` holds
+// ceil(R / 128) * (C / 128) atoms of 512 bytes. C must be a multiple of 128.
+RLB_API int rlb_quant_mxfp8_blocked(const void* src, long long lds, void* dst, long long ldd, void* scales, int R, int C,
+                                    void* stream) {
+  if (R <= 0 || C <= 0) return 0;
+  if ((C % 128) || (lds % 8) || (ldd % 16) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -2;
+  const int R_pad = (R + 127) / 128 * 128;
+  const long long n = static_cast<long long>(R_pad) * (C / 32);
+  quant_mxfp8_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), lds, static_cast<__nv_fp8_storage_t*>(dst), ldd,
+      static_cast<unsigned char*>(scales), 0, R, C / 32, 1, R_pad);
   return static_cast<int>(cudaGetLastError());
 }
 

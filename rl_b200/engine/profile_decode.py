@@ -29,6 +29,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--distinct-prompts", action="store_true", help="no prefix sharing between the prompts")
+    ap.add_argument("--quantization", default="", help="mxfp8 | fp8: serve quantised copies of the linear weights (low-precision rollout)")
     a = ap.parse_args(argv)
     mc = preset(a.model)
     if a.layers:
@@ -36,7 +37,8 @@ def main(argv=None):
     dev = torch.device("cuda", 0)
     model = CausalLM(mc, dtype=torch.bfloat16, device=dev, seed=0)
     eng = GenerationEngine(model, block_size=64, kv_cache_tokens=a.batch * (a.context + a.steps + 64), max_running=max(64, a.batch),
-                           max_model_len=a.context + a.steps + 64, use_cuda_graphs=not a.eager)
+                           max_model_len=a.context + a.steps + 64, use_cuda_graphs=not a.eager, quantization=a.quantization or None)
+    quant = eng.requantize()
     g = torch.Generator().manual_seed(0)
     n_unique = a.batch if a.distinct_prompts else max(1, a.batch // 8)
     uniq = [torch.randint(0, mc.vocab_size, (a.context,), generator=g).tolist() for _ in range(n_unique)]
@@ -53,7 +55,7 @@ def main(argv=None):
     wall = time.perf_counter() - t0
     st = eng.stats
     out = dict(model=a.model, layers=mc.num_hidden_layers, batch=a.batch, context=a.context, steps=st["decode_steps"],
-               graphs=not a.eager, wall_s=round(wall, 4), prefill_s=round(st["prefill_s"], 4),
+               graphs=not a.eager, quantization=a.quantization or "bf16", quantized_bytes=(quant or {}).get("quantized_bytes"), wall_s=round(wall, 4), prefill_s=round(st["prefill_s"], 4),
                decode_ms_per_step=round(1e3 * st["decode_s"] / max(1, st["decode_steps"]), 4),
                weight_stream_floor_ms=round(mc.num_parameters() * 2 / 6.5e12 * 1e3, 3))
     print(json.dumps(out), flush=True)

@@ -86,8 +86,8 @@ def quantized_linear(x: torch.Tensor, qz, bias: Optional[torch.Tensor], residual
     if kind == "mxfp8":
         if x2.is_cuda:
             xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
-            xq, xs = Q.quantize_mxfp8(xb.contiguous())
-            y = Q.gemm_mxfp8(xq, Q.swizzle_mx_scales(xs), q, s)
+            xq, xs = Q.quantize_mxfp8_blocked(xb.contiguous())   # scales land in the tensor core's layout directly
+            y = Q.gemm_mxfp8(xq, xs, q, s)
         else:
             xq, xs = Q.quantize_mxfp8_ref(x2.to(torch.bfloat16))
             y = Q.dequantize_mxfp8(xq, xs).float() @ Q.dequantize_mxfp8(q, s).float().t()

@@ -19,6 +19,7 @@ E4M3 = torch.float8_e4m3fn
 
 register("rlb_quant_fp8_block128", [P, L, P, L, P, I, I, I, _F, P])
 register("rlb_quant_mxfp8", [P, L, P, L, P, L, I, I, P])
+register("rlb_quant_mxfp8_blocked", [P, L, P, L, P, I, I, P])
 register("rlb_dequant_fp8_block128", [P, L, P, P, L, I, I, P])
 register("rlb_dequant_mxfp8", [P, L, P, L, P, L, I, I, P])
 
@@ -93,6 +94,16 @@ def quantize_mxfp8(w: torch.Tensor):
     q = torch.empty((R, C), dtype=E4M3, device=w.device)
     sc = torch.empty((R, C // 32), dtype=torch.uint8, device=w.device)
     call("rlb_quant_mxfp8", ptr(w), w.stride(0), ptr(q), q.stride(0), ptr(sc), sc.stride(0), R, C, stream_ptr())
+    return q, sc
+
+
+def quantize_mxfp8_blocked(w: torch.Tensor):
+    """bf16 [R, C] (C % 128 == 0, CUDA) -> (e4m3 [R, C], scales in the blocked layout of :func:`swizzle_mx_scales`), in one
+    kernel: what the activation side of an MXFP8 linear needs on every call."""
+    R, C = w.shape
+    q = torch.empty((R, C), dtype=torch.float8_e4m3fn, device=w.device)
+    sc = torch.empty((-(-R // 128), C // 128, 512), dtype=torch.uint8, device=w.device)
+    call("rlb_quant_mxfp8_blocked", ptr(w), w.stride(0), ptr(q), q.stride(0), ptr(sc), R, C, stream_ptr())
     return q, sc
 
 

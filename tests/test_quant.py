@@ -71,6 +71,19 @@ def test_native_mxfp8_matches_oracle(native_lib, shape):
     assert torch.equal(dequantize_mxfp8(q, e), dequantize_mxfp8(qr.cpu(), er.cpu()).cuda())
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(64, 256), (200, 1024), (777, 2048)])
+def test_native_mxfp8_blocked_scales_match_the_swizzled_oracle(native_lib, shape):
+    from rl_b200.ops.quant import quantize_mxfp8_blocked, swizzle_mx_scales
+
+    w = _w(*shape, seed=5, device="cuda")
+    q, sb = quantize_mxfp8_blocked(w)
+    qr, er = quantize_mxfp8(w)
+    torch.cuda.synchronize()
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    assert torch.equal(sb, swizzle_mx_scales(er))
+
+
 def test_swizzled_scale_layout():
     from rl_b200.ops.quant import swizzle_mx_scales
 

@@ -365,6 +365,10 @@ class GenerationEngine:
         self._static: Optional[dict] = None
         self._step_counter = 0
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
+        # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
+        # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
+        self.collect_timeline = False
+        self.timeline: list[tuple[float, int, int, int]] = []
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
         img = getattr(self.cfg, "image_token_id", None)
         self._banned_ids = torch.tensor([int(img)], dtype=torch.long, device=self.device) if img is not None else None
@@ -621,6 +625,7 @@ class GenerationEngine:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
         dev = self.device
         st = self._static_buffers()
+        t_begin = time.perf_counter()
         last_logits: dict[int, torch.Tensor] = {}
         # Expert-parallel MoE layers exchange tokens between the ranks of the expert group in every forward pass, so those
         # ranks must run the same sequence of forward passes although each serves its own requests: every iteration they
@@ -636,6 +641,9 @@ class GenerationEngine:
             elif idle:
                 break
             prefill, shared, decode, copies = self.sched.schedule() if not idle else ([], [], [], [])
+            if self.collect_timeline:
+                self.timeline.append((time.perf_counter() - t_begin, len(decode), len(prefill) + len(shared),
+                                      sum(1 for r in reqs.values() if not r.finished)))
             if not idle and not prefill and not shared and not decode:
                 raise RuntimeError("scheduler made no progress (KV cache too small for a single request)")
             need_decode = self._any_rank(ep, bool(decode)) if lock else bool(decode)

@@ -93,3 +93,16 @@ def test_engine_cpu_logprobs_match_model():
     stop = recs[2].out_tokens[2]
     again = eng.generate([prompts[2]], SamplingParams(max_new_tokens=6, stop_token_ids=[stop], seed=3, temperature=0.8))
     assert len(again[0].out_tokens) <= 6
+
+
+def test_engine_timeline_records_in_flight_batch_sizes():
+    torch.manual_seed(0)
+    mc = ModelConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    eng = GenerationEngine(CausalLM(mc, dtype=torch.float32, device="cpu", seed=1), block_size=4, num_blocks=64, max_running=2,
+                           max_model_len=64, use_cuda_graphs=False)
+    eng.collect_timeline = True
+    eng.generate([[1, 2, 3], [4, 5], [6, 7, 8, 9]], SamplingParams(max_new_tokens=5, stop_token_ids=[], seed=3), max_new_tokens=[5, 2, 3])
+    tl = eng.timeline
+    assert tl and max(x[1] for x in tl) <= 2 and tl[0][3] == 3 and tl[-1][3] >= 1      # never more than max_running decoding
+    assert all(a[0] <= b[0] for a, b in zip(tl, tl[1:])) and sum(x[2] for x in tl) == 3   # every request prefilled once

@@ -86,3 +86,36 @@ def test_vlm_sft_and_generation_on_gpu(tmp_path):
     lp = policy.get_logprobs(data)["logprobs"]
     mask = out["logprobs"] != 0
     assert (lp - out["logprobs"]).abs()[mask].mean().item() < 0.05
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,bs", [(128, 8, 2, 16), (64, 4, 4, 32)])
+def test_fused_rope_kv_write_matches_fp32_reference(D, Hq, Hkv, bs):
+    """The fused kernel against a plain PyTorch fp32 restatement: rotate q and k (rotate_half convention), scatter k and v."""
+    from rl_b200.models.config import ModelConfig, rope_inv_freq
+    from rl_b200.ops import engine_ops as E
+
+    torch.manual_seed(0)
+    T, nblk = 37, 12
+    dev = torch.device("cuda", 0)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev, dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device=dev, dtype=torch.int32)
+    mc = ModelConfig(vocab_size=64, hidden_size=Hq * D, intermediate_size=64, num_hidden_layers=1, num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D)
+    inv = rope_inv_freq(mc, dev)
+    slots = torch.randperm(nblk * bs, device=dev)[:T].to(torch.int64)
+    slots[5] = -1                                       # a padding row: rotated, not written
+    kc = torch.zeros(nblk, Hkv, bs, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    x = qkv.float().view(T, Hq + 2 * Hkv, D)
+    ang = pos.float()[:, None] * inv.float()[None, :]
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1)[:, None], torch.cat([ang.sin(), ang.sin()], -1)[:, None]
+    rot = torch.cat([-x[..., D // 2 :], x[..., : D // 2]], -1)
+    want = x.clone()
+    want[:, : Hq + Hkv] = (x * cos + rot * sin)[:, : Hq + Hkv]
+    out = E.rope_kv_cache_write(qkv.clone(), pos, inv, slots, kc, vc, Hq, Hkv, D)
+    torch.cuda.synchronize()
+    assert (out.float().view(T, -1, D) - want).abs().max().item() < 0.04       # bf16 rounding of values up to ~4
+    ok = slots >= 0
+    blk, off = (slots[ok] // bs).long(), (slots[ok] % bs).long()
+    assert torch.equal(kc[blk, :, off], out.view(T, -1, D)[ok][:, Hq : Hq + Hkv])
+    assert torch.equal(vc[blk, :, off], qkv.view(T, -1, D)[ok][:, Hq + Hkv :])
+    assert int((kc.abs().sum((1, 3)) > 0).sum()) == int(ok.sum())             # nothing else was touched

@@ -367,6 +367,10 @@ class GenerationEngine:
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
         # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
+        self._ev = ([torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                    if (self.device.type == "cuda" and os.environ.get("RLB_ENGINE_DEVICE_TIME", "0") == "1") else None)
+        self._ev_pending = False
+        self.stats["decode_device_s"] = 0.0
         self.collect_timeline = False
         self.timeline: list[tuple[float, int, int, int]] = []
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
@@ -486,31 +490,36 @@ class GenerationEngine:
 
     # ------------------------------------------------------------------ decode step (eager or CUDA graph)
     def _static_buffers(self):
+        """Fixed-address inputs and outputs of the decode step. All inputs live in one device blob mirrored by one pinned host
+        blob, so a step uploads them with a single copy; the sampled tokens and their log-probabilities share one output blob
+        and come back with a single copy."""
         if self._static is None:
-            B = self.max_running
+            B, MB = self.max_running, self.max_blocks_per_seq
             dev = self.device
-            self._static = dict(
-                ids=torch.zeros(B, dtype=torch.int32, device=dev),
-                positions=torch.zeros(B, dtype=torch.int32, device=dev),
-                slots=torch.full((B,), -1, dtype=torch.int64, device=dev),
-                block_table=torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32, device=dev),
-                seq_lens=torch.zeros(B, dtype=torch.int32, device=dev),
-                temps=torch.ones(B, dtype=torch.float32, device=dev),
-                top_ks=torch.zeros(B, dtype=torch.int32, device=dev),
-                top_ps=torch.ones(B, dtype=torch.float32, device=dev),
-                step=torch.zeros(1, dtype=torch.int64, device=dev),
-                keys=torch.zeros(B, dtype=torch.int64, device=dev),
-                tok=torch.zeros(B, dtype=torch.int32, device=dev),
-                lp=torch.zeros(B, dtype=torch.float32, device=dev),
-                host=dict(
-                    ids=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
-                    positions=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
-                    slots=torch.zeros(B, dtype=torch.int64).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int64),
-                    block_table=torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros((B, self.max_blocks_per_seq), dtype=torch.int32),
-                    seq_lens=torch.zeros(B, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int32),
-                    keys=torch.zeros(B, dtype=torch.int64).pin_memory() if dev.type == "cuda" else torch.zeros(B, dtype=torch.int64),
-                ),
-            )
+            fields = [("slots", torch.int64, (B,)), ("keys", torch.int64, (B,)), ("ids", torch.int32, (B,)), ("positions", torch.int32, (B,)),
+                      ("seq_lens", torch.int32, (B,)), ("block_table", torch.int32, (B, MB))]
+            offs, total = {}, 0
+            for name, dt, shape in fields:
+                n = 1
+                for x in shape:
+                    n *= x
+                offs[name] = (total, n * torch.empty((), dtype=dt).element_size(), dt, shape)
+                total += -(-offs[name][1] // 16) * 16
+            blob = torch.zeros(total, dtype=torch.uint8, device=dev)
+            host_blob = torch.zeros(total, dtype=torch.uint8)
+            if dev.type == "cuda":
+                host_blob = host_blob.pin_memory()
+            out_blob = torch.zeros(2 * B, dtype=torch.int32, device=dev)
+
+            def views(buf):
+                return {name: buf[o : o + nb].view(dt).view(shape) for name, (o, nb, dt, shape) in offs.items()}
+
+            self._static = dict(views(blob), blob=blob, host_blob=host_blob, host=views(host_blob), out_blob=out_blob,
+                                tok=out_blob[:B], lp=out_blob[B:].view(torch.float32),
+                                temps=torch.ones(B, dtype=torch.float32, device=dev), top_ks=torch.zeros(B, dtype=torch.int32, device=dev),
+                                top_ps=torch.ones(B, dtype=torch.float32, device=dev))
+            self._static["slots"].fill_(-1)
+            self._static["host"]["slots"].fill_(-1)
         return self._static
 
     def _bucket(self, n: int) -> int:
@@ -558,7 +567,12 @@ class GenerationEngine:
                     self._decode_body(st, B, sp, num_splits, scratch)
                 g = (graph, scratch, _L.Counters.launches - before)
                 self._graphs[key] = g
+            if self._ev is not None:   # device time of the replay alone (the step's host work shows as decode_s minus this)
+                self._ev[0].record()
             g[0].replay()
+            if self._ev is not None:
+                self._ev[1].record()
+                self._ev_pending = True
             _L.Counters.graph_replayed(g[2])
         else:
             no, nml = E.decode_scratch_sizes(B, self.hq, num_splits, c.head_dim)
@@ -680,13 +694,19 @@ class GenerationEngine:
                     hb["positions"][n:B] = 0
                     hb["block_table"][n:B] = 0
                     hb["keys"][n:B] = 0
-                for k in ("ids", "positions", "slots", "block_table", "seq_lens", "keys"):
-                    st[k][:B].copy_(hb[k][:B], non_blocking=True)
-                    _L.Counters.h2d_bytes += hb[k][:B].numel() * hb[k].element_size()
+                st["blob"].copy_(st["host_blob"], non_blocking=True)   # all inputs of the step in one upload
+                _L.Counters.h2d_bytes += st["host_blob"].numel()
                 self._step_counter += 1
-                st["step"].fill_(self._step_counter)
                 tok, lp = self._run_decode(n, sp, max_ctx)
-                tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
+                if tok.data_ptr() == st["tok"].data_ptr():   # graph / native path: tokens and log-probabilities in one download
+                    both = _L.to_host(st["out_blob"])
+                    Bm = self.max_running
+                    tok_h, lp_h = both[:n].tolist(), both[Bm : Bm + n].view(torch.float32).tolist()
+                else:
+                    tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
+                if self._ev_pending:   # the copies above synchronised the stream: the events are complete
+                    self.stats["decode_device_s"] += self._ev[0].elapsed_time(self._ev[1]) * 1e-3
+                    self._ev_pending = False
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(decode, fin)
                 for j, sid in enumerate(decode):

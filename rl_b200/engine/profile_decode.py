@@ -57,6 +57,7 @@ def main(argv=None):
     out = dict(model=a.model, layers=mc.num_hidden_layers, batch=a.batch, context=a.context, steps=st["decode_steps"],
                graphs=not a.eager, quantization=a.quantization or "bf16", quantized_bytes=(quant or {}).get("quantized_bytes"), wall_s=round(wall, 4), prefill_s=round(st["prefill_s"], 4),
                decode_ms_per_step=round(1e3 * st["decode_s"] / max(1, st["decode_steps"]), 4),
+               decode_device_ms_per_step=round(1e3 * st.get("decode_device_s", 0.0) / max(1, st["decode_steps"]), 4),
                weight_stream_floor_ms=round(mc.num_parameters() * 2 / 6.5e12 * 1e3, 3))
     print(json.dumps(out), flush=True)
 

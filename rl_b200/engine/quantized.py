@@ -67,6 +67,15 @@ def quantize_model(model, kind: str) -> dict:
             cur[2].copy_(s)
         else:
             p._rlb_q = (kind, q, s)
+        if kind == "fp8" and w.is_cuda:
+            # No block-128 FP8 GEMM exists here: the rollout computes with the fp8-rounded weights expanded to bf16 once per
+            # refit (same numbers as expanding on every call, at the bf16 kernels' speed; costs a bf16 copy per weight).
+            wd = Q.dequantize_fp8_blockwise(p._rlb_q[1], p._rlb_q[2])
+            old = getattr(p, "_rlb_q_bf16", None)
+            if old is not None and old.shape == wd.shape:
+                old.copy_(wd)
+            else:
+                p._rlb_q_bf16 = wd
         n += 1
         raw += w.numel() * 2
         packed += q.numel() * q.element_size() + s.numel() * s.element_size()
@@ -77,9 +86,11 @@ def clear_model(model) -> None:
     for p in model.parameters():
         if hasattr(p, "_rlb_q"):
             del p._rlb_q
+        if hasattr(p, "_rlb_q_bf16"):
+            del p._rlb_q_bf16
 
 
-def quantized_linear(x: torch.Tensor, qz, bias: Optional[torch.Tensor], residual: Optional[torch.Tensor]) -> torch.Tensor:
+def quantized_linear(x: torch.Tensor, qz, bias: Optional[torch.Tensor], residual: Optional[torch.Tensor], expanded=None) -> torch.Tensor:
     kind, q, s = qz
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -92,7 +103,7 @@ def quantized_linear(x: torch.Tensor, qz, bias: Optional[torch.Tensor], residual
             xq, xs = Q.quantize_mxfp8_ref(x2.to(torch.bfloat16))
             y = Q.dequantize_mxfp8(xq, xs).float() @ Q.dequantize_mxfp8(q, s).float().t()
     else:
-        w = Q.dequantize_fp8_blockwise(q, s)
+        w = expanded if expanded is not None else Q.dequantize_fp8_blockwise(q, s)
         if x2.is_cuda:
             from rl_b200.ops import functional as F
 

@@ -132,7 +132,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         from rl_b200.engine import quantized as _qz   # low-precision rollout: only inside the engine's generation phase
 
         if _qz.is_active():
-            return _qz.quantized_linear(x, qz, bias, residual)
+            return _qz.quantized_linear(x, qz, bias, residual, getattr(w, "_rlb_q_bf16", None))
     if not use_native(x):
         y = tF.linear(x, w, bias)
         return y if residual is None else y + residual

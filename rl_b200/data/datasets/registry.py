@@ -30,6 +30,10 @@ HF_SETS: dict[str, tuple] = {
     "gsm8k": ("openai/gsm8k", "main", "train", "test", {"question": "problem", "answer": "expected_answer"}, "math_data_processor"),
     "GPQA": ("Idavidrein/gpqa", "gpqa_diamond", "train", None, {}, "multichoice_qa_processor"),
     "MMLU": ("cais/mmlu", "all", "test", None, {"choices": "options"}, "multichoice_qa_processor"),
+    "MMLU-Pro": ("TIGER-Lab/MMLU-Pro", None, "test", "validation", {}, "multichoice_qa_processor"),
+    "hendrycks_math": ("EleutherAI/hendrycks_math", "algebra", "train", "test", {"problem": "problem", "solution": "expected_answer"}, "math_data_processor"),
+    "NuminaMath": ("AI-MO/NuminaMath-CoT", None, "train", "test", {"problem": "problem", "solution": "expected_answer"}, "math_data_processor"),
+    "Nemotron-Post-Training-v1-math": ("nvidia/Nemotron-Post-Training-Dataset-v1", None, "math", None, {}, "sft_processor"),
     "squad": ("rajpurkar/squad", None, "train", "validation", {}, "sft_processor"),
     "tulu3_sft_mixture": ("allenai/tulu-3-sft-mixture", None, "train", None, {}, "sft_processor"),
     "openai_format": (None, None, "train", None, {}, "sft_processor"),

@@ -74,3 +74,19 @@ def test_synchronizer_cpu_twin_builds_serving_model():
         train.norm.mul_(1.5)
     ws.sync_weights()
     assert torch.equal(ws.serving_model.logits(b), train.logits(b))
+
+
+def test_packed_broadcast_pack_unpack_round_trip():
+    """Byte-exact packing of mixed-dtype tensors into one buffer (each padded to 16 bytes) and back."""
+    from rl_b200.refit.packed_broadcast import _buckets, pack, unpack
+
+    torch.manual_seed(0)
+    ts = [("a", torch.randn(3, 5).to(torch.bfloat16)), ("b", torch.arange(7, dtype=torch.int64)), ("c", torch.randn(2, 2, 2)),
+          ("d", torch.zeros(0, dtype=torch.float32)), ("e", torch.randn(1).to(torch.float16))]
+    buf = pack([t for _, t in ts], "cpu")
+    assert buf.dtype == torch.uint8 and buf.numel() % 16 == 0
+    out = dict(unpack(buf, [(n, tuple(t.shape), t.dtype) for n, t in ts]))
+    for n, t in ts:
+        assert out[n].dtype == t.dtype and out[n].shape == t.shape and torch.equal(out[n].view(torch.uint8), t.contiguous().view(torch.uint8))
+    groups = list(_buckets(ts, bucket_bytes=64))
+    assert [n for g in groups for n, _ in g] == ["a", "b", "c", "d", "e"] and len(groups) >= 2

@@ -16,6 +16,8 @@ _REGISTRY: dict[str, str] = {
     "reward_model": "rl_b200.environments.reward_model_environment:RewardModelEnvironment",
     "dapo": "rl_b200.environments.math_environment:MathEnvironment",
     "vlm": "rl_b200.environments.vlm_environment:VLMEnvironment",
+    "tool": "rl_b200.environments.tool_environment:ToolEnvironment",
+    "retriever": "rl_b200.environments.tool_environment:ToolEnvironment",
     "remote": "rl_b200.environments.remote_environment:RemoteEnvironment",
     "nemo_gym": "rl_b200.environments.remote_environment:RemoteEnvironment",
 }

@@ -68,3 +68,32 @@ def test_named_sharding_axes():
     assert ns.get_ranks(dp=1) == [4, 5, 6, 7] and ns.get_ranks(dp=0, tp=2) == [2] and ns.get_ranks(dp=0, pp=0, cp=0, tp=2) == 2
     assert ns.axis_groups("tp") == [[0, 1, 2, 3], [4, 5, 6, 7]] and ns.axis_groups("dp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
     assert ns.group_of(6, "dp") == [2, 6]
+
+
+def test_tool_environment_runs_calls_and_scores_final_answers():
+    import pytest as _pytest
+
+    from rl_b200.environments.registry import create_env
+    from rl_b200.environments.tool_environment import keyword_retrieve, safe_eval
+
+    assert safe_eval("2 * (3 + 4) - 10 / 4") == 11.5 and safe_eval("-2 ** 3") == -8
+    for bad in ("__import__('os')", "a + 1", "2 ** 1000", "(1).real"):
+        with _pytest.raises((ValueError, SyntaxError)):
+            safe_eval(bad)
+    docs = ["The capital of France is Paris.", "Blackwell GPUs have tensor memory.", "Paris has the Louvre."]
+    assert keyword_retrieve("capital France", docs, 1) == [docs[0]] and keyword_retrieve("zzz", docs) == []
+    env = create_env("tool", {"documents": docs, "max_tool_calls": 2})
+    logs = [[{"role": "user", "content": "12*12?"}, {"role": "assistant", "content": '<tool_call>{"name": "calculator", "arguments": {"expression": "12*12"}}</tool_call>'}],
+            [{"role": "user", "content": "capital?"}, {"role": "assistant", "content": '<tool_call>{"name": "retrieve", "arguments": {"query": "capital of France"}}</tool_call>'}],
+            [{"role": "user", "content": "q"}, {"role": "assistant", "content": r"The answer is \boxed{144}"}],
+            [{"role": "user", "content": "q"}, {"role": "assistant", "content": "<tool_call>not json</tool_call>"}]]
+    metas = [{"ground_truth": "144"}, {"ground_truth": "Paris"}, {"ground_truth": "144"}, {"ground_truth": "1"}]
+    out = env.step(logs, metas)
+    assert out.terminateds.tolist() == [False, False, True, False] and out.rewards.tolist() == [0.0, 0.0, 1.0, 0.0]
+    assert '"result": 144' in out.observations[0]["content"] and "Paris" in out.observations[1]["content"] and "error" in out.observations[3]["content"]
+    assert out.metadata[0]["tool_calls"] == 1 and out.answers[2] == "144"
+    # second turn of sample 0: final answer after the tool response; the call budget ends sample 3
+    logs[0] += [out.observations[0], {"role": "assistant", "content": r"\boxed{144}"}]
+    logs[3] += [out.observations[3], {"role": "assistant", "content": "<tool_call>{}</tool_call>"}]
+    out2 = env.step([logs[0], logs[3]], [out.metadata[0], dict(out.metadata[3], tool_calls=2)])
+    assert out2.terminateds.tolist() == [True, True] and out2.rewards.tolist() == [1.0, 0.0]

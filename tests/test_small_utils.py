@@ -74,3 +74,19 @@ def test_routing_trace_capture_and_replay():
     assert R.agreement(tr, R.capture(b)) == 1.0
     R.replay(b, None)
     assert b.layers[0].mlp.forced_routing is None
+
+
+def test_worker_and_generation_satisfy_the_interfaces():
+    import torch
+
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.policy.interfaces import ColocatablePolicyInterface, GenerationInterface, PolicyInterface, ValueInterface
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=8, torch_dtype="float32")
+    w = PolicyWorker(dict(precision="float32", train_global_batch_size=2, train_micro_batch_size=1, max_total_sequence_length=32,
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3)),
+                          generation=dict(max_new_tokens=4, kv_cache_tokens=256, block_size=4, max_running=4)), model_cfg=mc, init_reference_model=False)
+    assert isinstance(w, PolicyInterface) and isinstance(w, ColocatablePolicyInterface) and isinstance(w, ValueInterface)
+    assert isinstance(w.build_generation(), GenerationInterface) and not isinstance(object(), PolicyInterface)

@@ -143,3 +143,86 @@ def ppo_train(policy, value, generation, loader, tokenizer, policy_loss, value_l
         epoch += 1
         save_state["current_epoch"] = epoch
     return last
+
+
+def async_ppo_train(policy, value, generation, loader, tokenizer, policy_loss, value_loss, task_to_env, logger, checkpointer, save_state,
+                    cfg, step_callback: Optional[Callable] = None, buffer=None) -> dict:
+    """Off-policy PPO: rollouts run ahead of training by up to ``ppo.async_ppo.max_trajectory_age_steps`` weight versions (the
+    replay buffer and staleness rules of :mod:`rl_b200.algorithms.async_grpo`); values and GAE are computed with the critic
+    that is current when a trajectory is trained on, and the policy loss corrects for the stale sampler through its
+    importance-sampling term. Counterpart of ``async_ppo_train`` (nemo_rl/algorithms/ppo.py:2062)."""
+    from rl_b200.algorithms.async_grpo import ReplayBuffer
+
+    p, pcfg = cfg["ppo"], cfg["policy"]
+    a = dict(max_trajectory_age_steps=1)
+    a.update(p.get("async_ppo") or {})
+    max_age = int(a["max_trajectory_age_steps"])
+    assert policy_loss.cfg["use_importance_sampling_correction"] or max_age == 0, \
+        "off-policy trajectories need loss_fn.use_importance_sampling_correction=true"
+    timer = Timer()
+    pad = tokenizer.pad_token_id if tokenizer is not None and tokenizer.pad_token_id is not None else 0
+    gae = GAEAdvantageEstimator({"gamma": p["gamma"], "lambda": p["gae_lambda"], "lambda_critic": p["lambda_critic"] or p["gae_lambda"],
+                                 "length_adaptive_alpha": p["length_adaptive_alpha"], "normalize_advantages": p["normalize_advantages"]})
+    n_gen = p["num_generations_per_prompt"]
+    use_ref = policy_loss.cfg["reference_policy_kl_penalty"] != 0
+    buffer = buffer if buffer is not None else ReplayBuffer(max_size=4 * (max_age + 1))
+    version = save_state.get("weight_version", 0)
+    total_steps = save_state["total_steps"]
+    it = iter(loader)
+    next_target, exhausted, last = total_steps, False, {}
+    while total_steps < p["max_num_steps"]:
+        with timer.time("total_step_time"):
+            refit_policy_generation(policy, generation, timer)
+            while not exhausted and next_target <= total_steps + max_age and len(buffer) < buffer.max_size:
+                try:
+                    batch = next(it)
+                except StopIteration:
+                    exhausted = True
+                    break
+                repeated = batch.repeat_interleave(n_gen)
+                repeated["message_log"] = [[dict(m) for m in log] for log in repeated["message_log"]]
+                repeated["rng_ids"] = repeated["idx"] * n_gen + torch.arange(n_gen).repeat(batch.size)
+                pf, _ = batched_message_log_to_flat_message(repeated["message_log"], {"token_ids": pad})
+                repeated["_prompt_ids"] = pf["token_ids"]
+                with timer.time("generation"):
+                    repeated, _ = run_multi_turn_rollout(generation, repeated, tokenizer, task_to_env, pcfg["max_total_sequence_length"],
+                                                         p["max_rollout_turns"], pad_token_id=pad)
+                buffer.push(repeated, version, next_target)
+                next_target += 1
+            generation.finish_generation()
+            item = buffer.sample(version, max_age)
+            if item is None:
+                break
+            repeated = apply_reward_shaping(scale_rewards(item["batch"], p.get("reward_scaling")), p.get("reward_shaping"))
+            rewards = repeated["total_reward"].float()
+            train_data = build_train_data(repeated, pad)
+            policy.prepare_for_lp_inference()
+            train_data["prev_logprobs"] = policy.get_logprobs(train_data)["logprobs"]
+            train_data["reference_policy_logprobs"] = (policy.get_reference_policy_logprobs(train_data)["reference_logprobs"]
+                                                       if use_ref else torch.zeros_like(train_data["prev_logprobs"]))
+            old_values = value.score(train_data)["values"]
+            adv, returns = gae.compute_advantage(repeated["_prompt_ids"], rewards, train_data["token_mask"], values=old_values)
+            train_data["advantages"], train_data["returns"], train_data["old_values"] = adv, returns, old_values
+            res = None
+            if total_steps >= p["num_value_warmup_steps"]:
+                policy.prepare_for_training()
+                res = policy.train(train_data, policy_loss, gbs=pcfg["train_global_batch_size"], mbs=pcfg["train_micro_batch_size"])
+                version += 1
+            value.prepare_for_training()
+            vres = value.train(train_data, value_loss, gbs=pcfg["train_global_batch_size"], mbs=pcfg["train_micro_batch_size"])
+        total_steps += 1
+        metrics = _aggregate_train_metrics(res) if res is not None else {}
+        metrics.update({f"value_{k}": v for k, v in _aggregate_train_metrics(vres).items() if k in ("loss", "grad_norm")})
+        c = _all_reduce_scalars({"r": float(rewards.sum()), "n": float(rewards.numel())})
+        metrics.update(reward=c["r"] / max(1.0, c["n"]), trajectory_age=float(item["age"]), buffer_size=float(len(buffer)))
+        save_state.update(current_step=total_steps, total_steps=total_steps, weight_version=version)
+        if logger is not None:
+            logger.log_metrics(metrics, total_steps, prefix="train")
+        if _is_main():
+            print(f"[async_ppo] step {total_steps}: reward={metrics['reward']:.4f} value_loss={metrics.get('value_loss', float('nan')):.5f} "
+                  f"age={item['age']} buffer={len(buffer)}", flush=True)
+        last = {"train": metrics, "timing": timer.get_timing_metrics("sum")}
+        if step_callback is not None:
+            step_callback(total_steps, last)
+        timer.reset()
+    return last

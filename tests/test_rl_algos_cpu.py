@@ -111,3 +111,16 @@ def test_training_logprobs_follow_the_samplers_top_k_and_top_p(tmp_path):
     cfg["grpo"].update(max_num_steps=3, max_num_epochs=5)
     grpo.grpo_train(policy, gen, loader, None, None, loss_fn, env, env, logger, ck, ss, cfg, step_callback=lambda s, m: hist2.append(m["train"]))
     assert hist2 and hist2[-1]["token_mult_prob_error"] > 1.05
+
+
+def test_async_ppo_trains_on_stale_trajectories(tmp_path):
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    cfg = {"ppo": dict(num_prompts_per_step=8, num_generations_per_prompt=1, max_num_steps=4, seed=0, async_ppo=dict(max_trajectory_age_steps=2)),
+           "loss_fn": dict(use_importance_sampling_correction=True), "policy": _policy_cfg(), "logger": dict(log_dir=str(tmp_path)),
+           "checkpointing": dict(enabled=False)}
+    policy, value, gen, loader, pl, vl, logger, ck, ss, cfg = ppo.setup(cfg, None, ds, None, env, model_cfg=_mc())
+    hist = []
+    ppo.async_ppo_train(policy, value, gen, loader, None, pl, vl, env, logger, ck, ss, cfg, step_callback=lambda s, m: hist.append(m["train"]))
+    assert len(hist) == 4 and max(h["trajectory_age"] for h in hist) >= 1 and max(h["trajectory_age"] for h in hist) <= 2
+    assert all(torch.isfinite(torch.tensor(h["value_loss"])) for h in hist) and ss["weight_version"] == 4

@@ -23,7 +23,8 @@ def main(argv=None):
     policy, value, generation, loader, ploss, vloss, logger, ck, save_state, cfg = ppo.setup(cfg, tokenizer, dataset, val_dataset, task_to_env,
                                                                                            model_cfg=mc)
     try:
-        ppo.ppo_train(policy, value, generation, loader, tokenizer, ploss, vloss, task_to_env, logger, ck, save_state, cfg)
+        trainer = ppo.async_ppo_train if (cfg["ppo"].get("async_ppo") or {}).get("enabled") else ppo.ppo_train
+        trainer(policy, value, generation, loader, tokenizer, ploss, vloss, task_to_env, logger, ck, save_state, cfg)
     finally:
         for env in task_to_env.values():
             env.shutdown()

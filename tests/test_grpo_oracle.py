@@ -88,13 +88,14 @@ def test_grpo_oracle_tensor_parallel(tmp_path):
         assert x["grad_norm"] == pytest.approx(y["grad_norm"], rel=2e-3)
 
 
-@pytest.mark.parametrize("pp,cp", [(2, 1), (1, 2)])
-def test_grpo_oracle_pipeline_and_context_parallel(tmp_path, pp, cp):
+@pytest.mark.parametrize("pp,cp,tp", [(2, 1, 1), (1, 2, 1), (2, 1, 2)])
+def test_grpo_oracle_pipeline_and_context_parallel(tmp_path, pp, cp, tp):
     """GRPO end to end with a pipeline- or context-parallel trainer: the stages (ranks) of the replica share the rollout
     work, every rank serves a complete copy of the weights, and the run reproduces the single-rank numbers."""
     p1, p2 = str(tmp_path / "w1.json"), str(tmp_path / "w2.json")
     mp.spawn(_run, args=(1, _free_port(), p1), nprocs=1, join=True)
-    mp.spawn(_run, args=(2, _free_port(), p2, 1, pp, cp), nprocs=2, join=True)
+    world = pp * cp * tp
+    mp.spawn(_run, args=(world, _free_port(), p2, tp, pp, cp), nprocs=world, join=True)
     a, b = json.load(open(p1)), json.load(open(p2))
     assert len(a) == len(b) == 2
     for x, y in zip(a, b):

@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (makes the run invalid as a benchmark)")
     ap.add_argument("--train-mb-tokens", type=int, default=0, help="tokens per training micro-batch (0: 5120 on 1 GPU, 10240 otherwise)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size of the trainer and the engine (with sequence parallelism); "
+                    "the headline configuration is --tp 1")
     ap.add_argument("--act-ckpt", default="auto", choices=["auto", "on", "off"],
                     help="activation checkpointing in training (auto = off: with 5120-token micro-batches the activations of "
                          "Llama-3.1-8B fit next to the unsharded optimizer state even on 1 GPU)")
@@ -177,13 +179,14 @@ def main() -> int:
         "loss_fn": dict(reference_policy_kl_penalty=0.01, ratio_clip_min=0.2, ratio_clip_max=0.2),
         "policy": dict(
             model_name=None, precision="bfloat16", train_global_batch_size=seqs_per_gpu * world, train_micro_batch_size=4,
+            parallel=dict(tensor_parallel_size=args.tp, sequence_parallel=args.tp > 1),
             logprob_batch_size=8, max_total_sequence_length=max_len, max_grad_norm=1.0,
             activation_checkpointing=(args.act_ckpt == "on"), grad_dtype="float32",
             sequence_packing=dict(enabled=True, train_mb_tokens=mb_tokens, logprob_mb_tokens=20480,
                                   algorithm="modified_first_fit_decreasing"),
             optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=3e-7, weight_decay=0.01, betas=[0.9, 0.999], eps=1e-8)),
             generation=dict(max_new_tokens=args.max_new_tokens, temperature=1.0, top_p=1.0, top_k=None, stop_token_ids=[],
-                            kv_cache_tokens=seqs_per_gpu * (max_len + 64), block_size=64, max_running=max(64, seqs_per_gpu),
+                            kv_cache_tokens=seqs_per_gpu * args.tp * (max_len + 64), block_size=64, max_running=max(64, seqs_per_gpu * args.tp),
                             max_prefill_tokens=16384, free_kv_cache_on_sleep=False),
         ),
         "logger": dict(log_dir=os.path.join(REPO, "gpurun_out", "bench_logs")),
@@ -280,7 +283,7 @@ def main() -> int:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
     dev_ms_max, e2e_s_max = float(mx[0]), float(mx[1])
-    total_tokens = float(sm[2])  # all ranks, all timed steps
+    total_tokens = float(sm[2]) / args.tp  # all data-parallel ranks, all timed steps (the ranks of a tensor-parallel group share their data)
     ms_per_step = dev_ms_max / args.steps
     value = total_tokens / (dev_ms_max / 1e3)
     if rank == 0:
@@ -302,7 +305,8 @@ def main() -> int:
                 "global_batch": seqs_per_gpu * world, "seq_len": max_len,
                 "prompts_per_step": n_prompts, "generations_per_prompt": n_gen, "prompt_len": args.prompt_len,
                 "max_new_tokens": args.max_new_tokens,
-                "parallelism": f"dp{world} (resident bf16 params, optimizer state sharded {world}-way, generation TP1 colocated)",
+                "parallelism": (f"dp{world} (resident bf16 params, optimizer state sharded {world}-way, generation TP1 colocated)" if args.tp == 1 else
+                                f"tp{args.tp} x dp{world // args.tp} (sequence parallel, fused peer-memory TP kernels, generation TP{args.tp} colocated)"),
                 "l2": "inputs larger than L2 (16 GB of weights streamed every pass)",
             },
             "tokens_per_sec_per_gpu": round(value / world, 1),

@@ -15,6 +15,14 @@ def gpu_numa_node(gpu_index: int) -> Optional[int]:
         import pynvml
 
         pynvml.nvmlInit()
+        try:   # a process-local CUDA ordinal maps to the NVML index through CUDA_VISIBLE_DEVICES (numeric entries)
+            from rl_b200.utils.nvml import device_id_to_physical
+
+            phys = device_id_to_physical(gpu_index)
+            if 0 <= phys < pynvml.nvmlDeviceGetCount():
+                gpu_index = phys
+        except Exception:
+            pass
         h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
         bus = pynvml.nvmlDeviceGetPciInfo(h).busId
         bus = bus.decode() if isinstance(bus, bytes) else bus

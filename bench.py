@@ -143,8 +143,8 @@ def main() -> int:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if os.environ.get("RLB_BIND_NUMA", "1") != "0":
-        # every rank's host loop (scheduler, table uploads) stays on the cores and memory next to its GPU
+    if os.environ.get("RLB_BIND_NUMA", "0") == "1":
+        # optional: keep every rank's host loop (scheduler, table uploads) on the cores and memory next to its GPU
         try:
             from rl_b200.distributed.numa import bind_to_gpu_numa_node
 

@@ -329,7 +329,18 @@ def main() -> int:
                           "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])}
         print(json.dumps(out), flush=True)
     if world > 1:
+        try:
+            gen.shutdown()   # drops the captured decode graphs before the communicators go away
+        except Exception:
+            pass
+        torch.cuda.synchronize()
         dist.barrier()
+        if args.tp > 1:
+            # a tensor-parallel engine captures NCCL broadcasts in its decode graphs; tearing the process groups down after
+            # that was seen to stall in the NCCL watchdog, so these ranks leave without the teardown (all work is complete)
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
     return 0
 

@@ -24,6 +24,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -43,7 +44,7 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--max-new-tokens", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (makes the run invalid as a benchmark)")
-    ap.add_argument("--train-mb-tokens", type=int, default=0, help="tokens per training micro-batch (0: 5120 on 1 GPU, 10240 otherwise)")
+    ap.add_argument("--train-mb-tokens", type=int, default=5120, help="tokens per training micro-batch (the same at every N)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size of the trainer and the engine (with sequence parallelism); "
                     "the headline configuration is --tp 1")
@@ -143,8 +144,8 @@ def main() -> int:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if os.environ.get("RLB_BIND_NUMA", "0") == "1":
-        # optional: keep every rank's host loop (scheduler, table uploads) on the cores and memory next to its GPU
+    if os.environ.get("RLB_BIND_NUMA", "1") == "1":
+        # keep every rank's host loop (scheduler, table uploads) on the cores and memory next to its GPU
         try:
             from rl_b200.distributed.numa import bind_to_gpu_numa_node
 
@@ -180,7 +181,7 @@ def main() -> int:
     seqs_per_gpu = args.prompts_per_gpu * n_gen
     max_len = args.prompt_len + args.max_new_tokens
     steps_needed = args.warmup + 2 * args.steps + 2
-    mb_tokens = args.train_mb_tokens or (5120 if world == 1 else 10240)
+    mb_tokens = args.train_mb_tokens
     cfg = {
         "grpo": dict(num_prompts_per_step=n_prompts, num_generations_per_prompt=n_gen, max_num_steps=10**9, val_period=0, seed=0,
                      normalize_rewards=True, use_leave_one_out_baseline=True),
@@ -197,7 +198,7 @@ def main() -> int:
                             kv_cache_tokens=seqs_per_gpu * args.tp * (max_len + 64), block_size=64, max_running=max(64, seqs_per_gpu * args.tp),
                             max_prefill_tokens=16384, free_kv_cache_on_sleep=False),
         ),
-        "logger": dict(log_dir=os.path.join(REPO, "gpurun_out", "bench_logs")),
+        "logger": dict(log_dir=tempfile.mkdtemp(prefix="rlb_bench_logs_")),
         "checkpointing": dict(enabled=False),
         "data": dict(shuffle=False),
     }

@@ -55,15 +55,40 @@ class GDPOAdvantageEstimator:
                 a = torch.where(std > 0, a / (std + 1e-6), a)
             total = total + w[k] * a
         if self.normalize_rewards and total.numel() > 1:
-            total = (total - total.mean()) / (total.std() + 1e-6)
+            # batch statistics over every data-parallel rank's samples (unbiased std, as torch.std)
+            mean, var, n = _global_masked_moments(total, torch.ones_like(total), kw.get("dp_group"))
+            std = (var * n / max(n - 1.0, 1.0)).sqrt()
+            total = (total - mean) / (std + 1e-6)
         return total.unsqueeze(-1).expand(mask.shape).clone()
 
 
+def _global_masked_moments(x: torch.Tensor, mask: torch.Tensor, group=None):
+    """Mean and biased variance of ``x`` over the masked entries of EVERY data-parallel rank (one all-reduce of
+    sum / sum of squares / count), so that whitening does not depend on how the batch is split over ranks."""
+    import torch.distributed as dist
+
+    m = mask.to(torch.float64)
+    xd = x.to(torch.float64)
+    stats = torch.stack([(xd * m).sum(), (xd * xd * m).sum(), m.sum()])
+    if group != "self" and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        buf = stats.cuda() if dist.get_backend(group) == "nccl" else stats.cpu()
+        dist.all_reduce(buf, group=group)
+        stats = buf.to(x.device)
+    n = stats[2].clamp(min=1.0)
+    mean = stats[0] / n
+    var = (stats[1] / n - mean * mean).clamp(min=0.0)
+    return mean.to(x.dtype), var.to(x.dtype), float(stats[2])
+
+
 class ReinforcePlusPlusAdvantageEstimator:
-    """Reinforce++: optional per-prompt mean baseline, then whitening over all valid tokens of the batch."""
+    """Reinforce++: optional per-prompt mean baseline, a per-token KL penalty subtracted from the reward
+    (``use_kl_in_reward``), then whitening over all valid tokens of the global batch with the biased variance
+    clamped at 1e-8 (nemo_rl/algorithms/advantage_estimator.py:233-265). ``kl_reward_to_go: true`` (off by default, an
+    extension) charges each token with the penalties of the tokens after it as well."""
 
     def __init__(self, cfg: dict, loss_cfg: Optional[dict] = None):
         self.minus_baseline = cfg.get("minus_baseline", True)
+        self.reward_to_go = bool(cfg.get("kl_reward_to_go", False))
         self.loss_cfg = loss_cfg or {}
 
     def compute_advantage(self, prompt_ids, rewards, mask, logprobs_policy=None, logprobs_reference=None, **kw):
@@ -78,13 +103,12 @@ class ReinforcePlusPlusAdvantageEstimator:
 
             kl = calculate_kl(logprobs_policy, logprobs_reference, self.loss_cfg.get("reference_policy_kl_type", "k3"))
             beta = self.loss_cfg.get("reference_policy_kl_penalty", 0.0)
-            # reward-to-go of the per-token KL penalty
-            pen = (-beta * kl * mask).flip(-1).cumsum(-1).flip(-1)
-            adv = adv + pen
-        m = mask.to(adv.dtype)
-        mean = masked_mean(adv, m)
-        var = masked_var(adv, m)
-        return (adv - mean) * torch.rsqrt(var + 1e-8)
+            pen = beta * kl
+            if self.reward_to_go:
+                pen = (pen * mask).flip(-1).cumsum(-1).flip(-1)
+            adv = adv - pen
+        mean, var, _ = _global_masked_moments(adv, mask, kw.get("dp_group"))
+        return (adv - mean) * var.clamp(min=1e-8).rsqrt()
 
 
 class RawAdvantageEstimator:

@@ -91,6 +91,17 @@ def _dp_group():
     return None
 
 
+def _agree_any(flag: bool) -> bool:
+    """True on every rank of the job if ``flag`` is true on any rank (world group, MAX)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return bool(flag)
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32)
+    if torch.cuda.is_available() and dist.get_backend() == "nccl":
+        t = t.cuda()
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return bool(t.item())
+
+
 def _is_main() -> bool:
     return not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0
 
@@ -418,7 +429,7 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                     adv = adv_estimator.compute_advantage(
                         prompt_ids, rewards, tm, valid_mask=torch.ones_like(rewards),
                         reward_components=repeated.get("reward_components"), logprobs_policy=train_data["prev_logprobs"],
-                        logprobs_reference=train_data["reference_policy_logprobs"])
+                        logprobs_reference=train_data["reference_policy_logprobs"], dp_group=_dp_group())
                     if isinstance(adv, tuple):
                         adv = adv[0]
                     lo, hi = g["advantage_clip_low"], g["advantage_clip_high"]
@@ -461,7 +472,8 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                                                generated_tokens=int(counts["generated_tokens"]))
             timeout.mark_iteration()
             ck = cfg.get("checkpointing") or {}
-            must = timeout.check_save()
+            # every rank must take the same branch: saving is collective, and each rank's wall clock differs
+            must = _agree_any(timeout.check_save())
             if checkpointer.enabled and (is_last or must or (ck.get("save_period") and total_steps % ck["save_period"] == 0)):
                 with timer.time("checkpointing"):
                     save_checkpoint(policy, dataloader, checkpointer, save_state, cfg, total_steps, val_metrics)
@@ -513,7 +525,8 @@ def save_checkpoint(policy, dataloader, checkpointer: CheckpointManager, save_st
         model_save_format=ck.get("model_save_format", "safetensors"))
     for name, obj in (extra_files or {}).items():
         torch.save(obj, os.path.join(tmp, name if rank == 0 else f"{name}.rank{rank}"))
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1 and extra_files:
+    # all ranks of the job (tensor / pipeline / expert ranks included) have written their shards before the rename
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.barrier()
     if _is_main():
         torch.save(dataloader.state_dict(), os.path.join(tmp, "train_dataloader.pt"))

@@ -16,7 +16,7 @@ import torch
 from rl_b200.distributed.ft_launcher import beat as _ft_beat
 import torch.distributed as dist
 
-from rl_b200.algorithms.grpo import _ShardedPromptLoader, _aggregate_train_metrics, _all_reduce_scalars, _is_main, _world, save_checkpoint
+from rl_b200.algorithms.grpo import _ShardedPromptLoader, _aggregate_train_metrics, _agree_any, _all_reduce_scalars, _is_main, _world, save_checkpoint
 from rl_b200.algorithms.loss.loss_functions import DPOLossFn, NLLLossFn, PreferenceLossFn
 from rl_b200.algorithms.utils import set_seed
 from rl_b200.distributed.batched_data_dict import BatchedDataDict
@@ -176,7 +176,7 @@ def _supervised_train(policy, loader, val_loader, loss_fn, logger, checkpointer,
                               consumed_samples=save_state["consumed_samples"] + int(tok["n"]))
             timing = timer.get_timing_metrics("sum")
             timeout.mark_iteration()
-            must = timeout.check_save()
+            must = _agree_any(timeout.check_save())   # collective decision: saving is collective
             ck = cfg.get("checkpointing") or {}
             if checkpointer.enabled and (is_last or must or (ck.get("save_period") and total_steps % ck["save_period"] == 0)):
                 save_checkpoint(policy, loader, checkpointer, save_state, cfg, total_steps, val)

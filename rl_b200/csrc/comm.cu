@@ -76,6 +76,7 @@ struct FusedOptimArgs {
   unsigned int epoch;     // grows by one per call
   unsigned long long limit_ns;
   float* sumsq_local;     // [1] scratch, zeroed by the kernel
+  int* abort_word;        // [1] scratch: set when a peer barrier ran out, read by the whole grid after the next grid.sync
   float* norm_out;        // [1] global gradient norm
   int* status;
 };
@@ -99,12 +100,18 @@ __global__ void __launch_bounds__(512, 1) fused_optim_kernel(FusedOptimArgs a) {
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
 
+  // A peer barrier that runs out aborts the whole grid at the next grid-wide synchronisation: the status word holds
+  // RLB_ERR_WAIT_PEER, and parameters, moments and every peer's buffers are left exactly as they were (a failure after
+  // pass 1 leaves the locally reduced gradient shard behind, nothing else).
   // stage 0: every rank's gradients are complete
   if (blockIdx.x == 0) {
     if (threadIdx.x == 0) *a.sumsq_local = 0.f;
-    peer_barrier(a.peers, a.rank, a.world, 0, a.epoch, a.limit_ns, a.status);
+    const bool ok = peer_barrier(a.peers, a.rank, a.world, 0, a.epoch, a.limit_ns, a.status);
+    if (threadIdx.x == 0) *a.abort_word = ok ? 0 : 1;
+    __threadfence();
   }
   grid.sync();
+  if (*reinterpret_cast<volatile int*>(a.abort_word)) return;
 
   // pass 1: pull-reduce my shard from all peers (fixed order), keep it locally, accumulate the sum of squares
   float ss = 0.f;
@@ -130,8 +137,9 @@ __global__ void __launch_bounds__(512, 1) fused_optim_kernel(FusedOptimArgs a) {
     if (threadIdx.x < a.world) a.peers.slots[threadIdx.x][a.rank] = *a.sumsq_local;
     __threadfence_system();
     __syncthreads();
-    peer_barrier(a.peers, a.rank, a.world, 1, a.epoch, a.limit_ns, a.status);
-    if (threadIdx.x == 0) {
+    const bool ok = peer_barrier(a.peers, a.rank, a.world, 1, a.epoch, a.limit_ns, a.status);
+    if (threadIdx.x == 0 && !ok) *a.abort_word = 1;
+    if (threadIdx.x == 0 && ok) {
       float total = 0.f;
       for (int r = 0; r < a.world; ++r) total += reinterpret_cast<volatile float*>(a.peers.slots[a.rank])[r];
       const float norm = sqrtf(total) / a.grad_div;
@@ -141,7 +149,9 @@ __global__ void __launch_bounds__(512, 1) fused_optim_kernel(FusedOptimArgs a) {
       *a.sumsq_local = scale;  // broadcast to the grid through global memory
     }
   }
+  __threadfence();
   grid.sync();
+  if (*reinterpret_cast<volatile int*>(a.abort_word)) return;
   if (threadIdx.x == 0) s_scale = *reinterpret_cast<volatile float*>(a.sumsq_local);
   __syncthreads();
   const float gs = s_scale;
@@ -245,7 +255,7 @@ RLB_API int rlb_symm_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemH
 RLB_API int rlb_symm_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
 
 // One fused optimizer step. Pointer tables have `world` entries, entry `rank` being this rank's own buffer.
-// flags: uint32 [4][8] per rank (zero-initialised symmetric memory); slots: float [8] per rank.
+// flags: uint32 [4][8] per rank (zero-initialised symmetric memory); slots: float [8] per rank; sumsq_scratch: 2 floats.
 RLB_API int rlb_fused_optim_step(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs,
                                  void* const* slot_ptrs, int rank, int world, long long shard_n, void* p_lo, float* m,
                                  float* v, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
@@ -278,6 +288,7 @@ RLB_API int rlb_fused_optim_step(void* const* grad_ptrs, void* const* param_ptrs
   a.epoch = epoch;
   a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
   a.sumsq_local = sumsq_scratch;
+  a.abort_word = reinterpret_cast<int*>(sumsq_scratch + 1);
   a.norm_out = norm_out;
   a.status = status;
   const int grid = coop_grid(reinterpret_cast<const void*>(fused_optim_kernel), 512);

@@ -24,6 +24,7 @@ enum RlbStatus : int {
   RLB_ERR_WAIT_FLAG = 5,        // wait on a flag written by another CTA or GPU
   RLB_ERR_BAD_ARG = 6,
   RLB_ERR_WAIT_PEER = 7,        // wait on a peer GPU's signal
+  RLB_ERR_BOUNDS = 8,           // a build with -DRLB_DEBUG_BOUNDS saw an index outside its buffer (the access was skipped)
 };
 
 namespace rlb {
@@ -86,7 +87,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait. `abort_flag` is a shared-memory word that any role of the CTA sets when its own
 // wait ran out, so that the others stop early instead of each waiting out the full limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -94,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if (((++polls) & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;

@@ -436,7 +436,7 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
     float kl = 0.f;
     if (a.kl_beta != 0.f && ref) {
       float logr = ref[i] - c;
-      const bool inside = fabsf(logr) < a.kl_in_clamp;
+      const bool inside = fabsf(logr) <= a.kl_in_clamp;  // same test as `logr == clamp(logr)`
       logr = fminf(fmaxf(logr, -a.kl_in_clamp), a.kl_in_clamp);
       float dkl_dc;  // d kl / d curr through logr (zero where the input clamp is active)
       if (a.kl_type == 1) {
@@ -453,8 +453,12 @@ __global__ void clipped_pg_kernel(const float* __restrict__ curr, const float* _
       if (!inside) dkl_dc = 0.f;
       float wkl = 1.f;  // exp(curr - curr.detach()) = 1 in value, gradient kl * 1
       if (a.on_policy_kl_approx) wkl = __expf(c - gn);
+      if (!isfinite(wkl)) wkl = 0.f;  // nan_to_num(nan = 0, +-inf = 0) on the weight
+      // product rule; d wkl / d curr = wkl in both cases, except where the input clamp is active: there the weight is
+      // detached, so the clamp suppresses the score-function term as well
+      const float dw_dc = inside ? wkl : 0.f;
       float klw = kl * wkl;
-      float dklw = dkl_dc * wkl + kl * wkl;  // product rule; d wkl / d curr = wkl in both cases
+      float dklw = dkl_dc * wkl + kl * dw_dc;
       if (isnan(klw)) {
         klw = 0.f;
         dklw = 0.f;
@@ -793,6 +797,15 @@ RLB_API int rlb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w,
   if (rows <= 0) return 0;
   if (d <= 0 || d % 8 || x_stride % 8 || dy_stride % 8) return RLB_STATIC_ERR_BAD_SHAPE;
   if (d > RLB_RMSNORM_STATIC_MAX_D) return RLB_STATIC_ERR_TOO_LARGE;
+  // The kernels use 16-byte vector loads and stores on every operand and index rows with int: refuse what would
+  // otherwise reach the device as a misaligned address or a truncated row count.
+  if (x_stride < d || dy_stride < d || rows > 2147483647ll) return RLB_STATIC_ERR_BAD_SHAPE;
+  const void* vec_ptrs[4] = {dy, x, w, dx};  // bf16 operands: 16-byte vector access
+  for (const void* q : vec_ptrs)
+    if (q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15u)) return RLB_STATIC_ERR_BAD_SHAPE;
+  if (rstd == nullptr || dw_f32 == nullptr || (reinterpret_cast<uintptr_t>(rstd) & 3u) ||
+      (reinterpret_cast<uintptr_t>(dw_f32) & 3u))
+    return RLB_STATIC_ERR_BAD_SHAPE;
   float* scratch = nullptr;
   const int rc = rmsnorm_static_scratch(&scratch);
   if (rc) return rc;
@@ -809,7 +822,7 @@ RLB_API int rlb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w,
 RLB_API const char* rlb_rmsnorm_bwd_static_strerror(int code) {
   switch (code) {
     case 0: return "ok";
-    case RLB_STATIC_ERR_BAD_SHAPE: return "d and the strides must be positive multiples of 8 elements";
+    case RLB_STATIC_ERR_BAD_SHAPE: return "d and the strides must be positive multiples of 8 elements (strides >= d, rows < 2^31), dy / x / w / dx non-null and 16-byte aligned, rstd / dw_f32 non-null";
     case RLB_STATIC_ERR_TOO_LARGE: return "d exceeds RLB_RMSNORM_STATIC_MAX_D (8192): use rlb_rmsnorm_bwd with caller scratch";
     case RLB_STATIC_ERR_NO_SYMBOL: return "the static scratch array's device address could not be resolved";
     default: return code > 0 ? "CUDA error (see cudaGetErrorString)" : "unknown code";

@@ -255,6 +255,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // on-chip waits follow the call's limit, so a call with a short limit gives up everywhere within that time
+  const unsigned long long bar_limit = t.limit_ns < kWaitLimitNs ? t.limit_ns : kWaitLimitNs;
   if (t.epoch_ptr) t.epoch = *reinterpret_cast<volatile unsigned int*>(t.epoch_ptr) + 1;
   const bool stamp = blockIdx.x == 0 && threadIdx.x == 0 && t.mode == MODE_SCATTER;
   if (stamp) g_tp_phase_ns[0] = globaltimer_ns();
@@ -328,7 +330,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
         for (int kb = 0; kb < num_k; ++kb) {
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, status, RLB_ERR_WAIT_EMPTY)) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, status, RLB_ERR_WAIT_EMPTY, bar_limit)) {
             ok = false;
             break;
           }
@@ -360,11 +362,11 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
-        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, abort_flag, status, RLB_ERR_WAIT_TMEM_EMPTY)) break;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, abort_flag, status, RLB_ERR_WAIT_TMEM_EMPTY, bar_limit)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, status, RLB_ERR_WAIT_FULL)) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, status, RLB_ERR_WAIT_FULL, bar_limit)) {
             ok = false;
             break;
           }
@@ -401,6 +403,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool go = true;
       if (lane == 0) go = wait_flag(my_flags + FLAG_GO, t.epoch, t.limit_ns, false, status, RLB_ERR_WAIT_FLAG);
       ok = __shfl_sync(0xffffffffu, go, 0);
+      // the producer and MMA roles of this CTA depend on this one: tell them to stop instead of letting each wait out
+      // its own limit on a barrier that will never complete
+      if (!ok && lane == 0) *abort_flag = 1;
     }
     const int rows_out = t.all_reduce ? M : t.rows_per_rank;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas, ++local_tile) {
@@ -408,7 +413,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tile_coords(tile, num_m, num_n, m_rot, m_blk, n_blk);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag, status, RLB_ERR_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag, status, RLB_ERR_WAIT_TMEM_FULL, bar_limit)) break;
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < M;

@@ -15,6 +15,8 @@
 //    about 9.7 MB) from load until the process exits, whether or not this entry point is ever called.
 //  * d must be a multiple of 8 and at most RLB_RMSNORM_STATIC_MAX_D; larger shapes are refused with
 //    RLB_STATIC_ERR_TOO_LARGE (nothing is launched). rlb_rmsnorm_bwd_static_strerror turns a code into text.
+//  * dy, x, w and dx must be non-null and 16-byte aligned, the strides multiples of 8 and at least d, rows below 2^31,
+//    rstd and dw_f32 non-null fp32 pointers: anything else returns RLB_STATIC_ERR_BAD_SHAPE and launches nothing.
 //  * The first call on each device looks up the array's device address (with that device current). Make that first
 //    call from ordinary, non-capturing code before any stream capture is started on the device.
 //  * All calls share the one array and it keeps the previous call's contents. Each call overwrites every element it

@@ -113,35 +113,45 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
   for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, ldz(z, i));
   mx = block_max(mx, red);
 
-  // threshold from top-k / top-p (on raw logits; scaling by 1/T > 0 keeps the order)
+  // Threshold from top-k / top-p (on raw logits; scaling by 1/T > 0 keeps the order). The filters compose the way the
+  // train-side filter and vLLM apply them: top-k first, then the nucleus inside the renormalised top-k set. Both are a
+  // bisection on the ordered-uint image of fp32; invariant: `lo` satisfies the predicate.
   float thr = -INFINITY;
   const bool need_k = top_k > 0 && top_k < V;
   const bool need_p = top_p < 1.f;
-  if (need_k || need_p) {
-    float total = 0.f;
-    if (need_p) {
-      for (int i = threadIdx.x; i < V; i += blockDim.x) total += __expf((ldz(z, i) - mx) * inv_t);
-      total = block_sum(total, red);
-    }
-    // Largest threshold x with count(z >= x) >= k and mass(z >= x) >= top_p * total, i.e. the smallest
-    // kept logit. Bisection on the ordered-uint image; invariant: `lo` satisfies the predicate.
+  if (need_k) {
+    // x_k = largest x with count(z >= x) >= k, i.e. the k-th largest logit (ties at x_k are all kept)
     uint32_t lo = 0u, hi = f2ord(mx);
-    // predicate(hi = max) may already hold (e.g. top_k = 1)
     while (lo < hi) {
       const uint32_t mid = lo + ((hi - lo + 1u) >> 1);
       const float x = ord2f(mid);
-      float cnt = 0.f, mass = 0.f;
+      float cnt = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) cnt += (ldz(z, i) >= x) ? 1.f : 0.f;
+      cnt = block_sum(cnt, red);
+      if (cnt >= static_cast<float>(top_k)) lo = mid;
+      else hi = mid - 1u;
+    }
+    thr = ord2f(lo);
+  }
+  if (need_p) {
+    // mass of the set that survived top-k, then x_p = largest x >= x_k with mass(z >= x) >= top_p * that mass
+    float total = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = ldz(z, i);
+      if (v >= thr) total += __expf((v - mx) * inv_t);
+    }
+    total = block_sum(total, red);
+    uint32_t lo = need_k ? f2ord(thr) : 0u, hi = f2ord(mx);
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo + 1u) >> 1);
+      const float x = ord2f(mid);
+      float mass = 0.f;
       for (int i = threadIdx.x; i < V; i += blockDim.x) {
         const float v = ldz(z, i);
-        if (v >= x) {
-          cnt += 1.f;
-          if (need_p) mass += __expf((v - mx) * inv_t);
-        }
+        if (v >= x) mass += __expf((v - mx) * inv_t);
       }
-      cnt = block_sum(cnt, red);
-      if (need_p) mass = block_sum(mass, red);
-      const bool ok = (!need_k || cnt >= static_cast<float>(top_k)) && (!need_p || mass >= top_p * total);
-      if (ok) lo = mid;
+      mass = block_sum(mass, red);
+      if (mass >= top_p * total) lo = mid;
       else hi = mid - 1u;
     }
     thr = ord2f(lo);

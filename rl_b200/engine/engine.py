@@ -773,4 +773,6 @@ class GenerationEngine:
                         del last_logits[sid]
                 self.stats["generated_tokens"] += len(new)
                 self.stats["prefill_s"] += time.perf_counter() - t0
+        if self.native:   # every token download above synchronised the stream
+            _L.raise_on_status("GenerationEngine.generate", self.device)
         return [reqs[i] for i in range(len(prompts))]

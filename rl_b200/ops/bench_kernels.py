@@ -174,30 +174,17 @@ def bench_memory_bound():
 
 
 def bench_weight_stream():
-    """Decode GEMMs at M = 64 tokens against the bare weight stream of the same access pattern (``csrc/stream_probe.cu``):
-    the probe is the ceiling for a kernel that pulls W through TMA boxes of [128 x 64]; the GEMM's distance from it is what
-    MMA issue, epilogue, prologue and (for small N) the split-K reduction cost."""
-    from . import lib as _L
-    from .lib import call, ptr, stream_ptr
-
-    _L.register("rlb_stream_probe", [_L.P, _L.L, _L.I, _L.I, _L.I, _L.I, _L.I, _L.I, _L.P, _L.P, _L.P])
+    """Decode GEMMs at M = 64 tokens against the ideal time of streaming their weights once at the measured copy bandwidth."""
     _, hbm, how = _peaks()
     rows = []
-    sink = torch.zeros(1, dtype=torch.int64, device="cuda")
     for N, K in ((28672, 4096), (4096, 14336), (6144, 4096), (4096, 4096), (128256, 4096)):
         n_pool = max(2, min(8, L2_BYTES * 2 // (N * K * 2) + 1))
         Ws = [torch.randn((N, K), device="cuda", dtype=torch.bfloat16) for _ in range(n_pool)]
         x = torch.randn((64, K), device="cuda", dtype=torch.bfloat16)
         gb = N * K * 2 / 1e9
-        for name, rows_, kboxes, stages, grid in (("boxes 128x64, 4 stages, one CTA per row tile", 128, 1, 4, 0),
-                                                  ("boxes 64x64 x4, 3 stages, 296 persistent CTAs", 64, 4, 3, 296)):
-            ms = time_fn(lambda i: call("rlb_stream_probe", ptr(Ws[i]), K, N, K, rows_, kboxes, stages, grid, ptr(sink),
-                                        ptr(_L.status_word(sink.device)), stream_ptr()), n_pool, iters=30)
-            rows.append(dict(kernel="weight_stream_probe", variant=name, N=N, K=K, us=round(ms * 1e3, 2), gbs=round(gb / ms * 1e3, 1),
-                             frac_of_hbm=round(gb / ms * 1e3 / hbm, 3), peak=how))
         ms = time_fn(lambda i: F.gemm(x, Ws[i]), n_pool, iters=30)
-        rows.append(dict(kernel="gemm_skinny_M64", N=N, K=K, us=round(ms * 1e3, 2), gbs=round(gb / ms * 1e3, 1),
-                         frac_of_hbm=round(gb / ms * 1e3 / hbm, 3), peak=how))
+        rows.append(dict(kernel="gemm_skinny_M64", N=N, K=K, us=round(ms * 1e3, 2), ideal_us=round(gb / hbm * 1e6, 2),
+                         gbs=round(gb / ms * 1e3, 1), frac_of_hbm=round(gb / ms * 1e3 / hbm, 3), peak=how))
         del Ws
         torch.cuda.empty_cache()
     for r in rows:

@@ -129,6 +129,27 @@ def check_status(device=None) -> int:
     return v
 
 
+STATUS_NAMES = {1: "RLB_ERR_WAIT_FULL (a consumer waited for a TMA-filled stage)",
+                2: "RLB_ERR_WAIT_EMPTY (a producer waited for a free stage)",
+                3: "RLB_ERR_WAIT_TMEM_FULL (an epilogue waited for an accumulator)",
+                4: "RLB_ERR_WAIT_TMEM_EMPTY (an MMA warp waited for a drained accumulator)",
+                5: "RLB_ERR_WAIT_FLAG (a wait on a flag written by another CTA)",
+                6: "RLB_ERR_BAD_ARG (a kernel refused its arguments)",
+                7: "RLB_ERR_WAIT_PEER (a wait on a peer GPU's signal)",
+                8: "RLB_ERR_BOUNDS (a debug-bounds build saw an index outside its buffer)"}
+
+
+def raise_on_status(where: str, device=None) -> None:
+    """Reads the status word where the host synchronises anyway (token download, gradient norm, end of a refit) and
+    raises if a kernel gave up a bounded wait: its outputs are not to be trusted and the step must not continue."""
+    if not torch.cuda.is_available():
+        return
+    code = check_status(device)
+    if code:
+        raise NativeLibraryError(f"{where}: a kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown code')}; "
+                                 "its outputs are incomplete (the CUDA context is still usable)")
+
+
 class Counters:
     """Process-wide counts of native kernel launches and host<->device bytes, for benchmark reporting.
 

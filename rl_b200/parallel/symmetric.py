@@ -107,7 +107,7 @@ class SymmetricBuffer:
 class FusedOptimizerComm:
     """Owns the peer-mapped parameter / gradient buffers and runs the one-kernel optimizer step."""
 
-    def __init__(self, group=None, wait_limit_s: float = 2.0):
+    def __init__(self, group=None, wait_limit_s: float = 20.0):
         self.group = group
         self.wait_limit_s = wait_limit_s
         self.epoch = 0
@@ -117,7 +117,7 @@ class FusedOptimizerComm:
         self.rank, self.world = self.ctrl.rank, self.ctrl.world
         self._slots_table = (_P * self.world)(*[p + 1024 for p in self.ctrl.peer_ptrs])
         dev = self.ctrl.device
-        self._scratch = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._scratch = torch.zeros(2, dtype=torch.float32, device=dev)   # partial sum of squares, abort word
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
 
     # allocators handed to FlatParams so that the flat buffers live in peer-mapped memory
@@ -136,9 +136,8 @@ class FusedOptimizerComm:
     def step(self, opt, grad_div: float = 1.0) -> torch.Tensor:
         """reduce-scatter + clip + AdamW + all-gather in one cooperative kernel (see rl_b200/csrc/comm.cu)."""
         lib = _bind()
-        if self.world > 1:
-            # absorbs step-time skew between ranks on the host side, so the in-kernel waits only see microseconds
-            dist.barrier(group=self.group)
+        # No host-side rendezvous: the kernel's first flag barrier absorbs the step-time skew between the ranks (its
+        # limit, wait_limit_s, is sized for that skew, not for microseconds).
         self.epoch += 1
         rc = lib.rlb_fused_optim_step(
             self.grad_buf.table, self.param_buf.table, self.ctrl.table, self._slots_table, self.rank, self.world,

@@ -27,6 +27,7 @@ from rl_b200.distributed.batched_data_dict import BatchedDataDict
 from rl_b200.models.config import ModelConfig, preset
 from rl_b200.models.transformer import CausalLM, PackedBatch, build_model
 from rl_b200.policy.optimizer import LRSchedule, ShardedAdamW, build_optimizer
+from rl_b200.ops import lib as _L
 from rl_b200.ops.lib import to_device, to_host
 from rl_b200.utils.flops import transformer_flops
 
@@ -167,7 +168,7 @@ class PolicyWorker:
             try:
                 from rl_b200.parallel.symmetric import FusedOptimizerComm
 
-                fused_comm = FusedOptimizerComm(dp_group, wait_limit_s=float(cfg.get("peer_wait_limit_s", 2.0)))
+                fused_comm = FusedOptimizerComm(dp_group, wait_limit_s=float(cfg.get("peer_wait_limit_s", 20.0)))
             except Exception as e:  # no peer access between these GPUs: keep NCCL
                 if self.rank == 0:
                     print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
@@ -492,6 +493,8 @@ class PolicyWorker:
             out[torch.as_tensor(idx), :Smb] = to_host(batch.unpack(lp, Smb))
         for _ in range(extra):
             self._dummy_pass(backward=False)
+        if self.device.type == "cuda":   # the downloads above synchronised the stream
+            _L.raise_on_status("PolicyWorker log-probability pass", self.device)
         return out
 
     def get_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
@@ -630,6 +633,7 @@ class PolicyWorker:
             self.scheduler.step()  # once per train() call
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+            _L.raise_on_status("PolicyWorker.train", self.device)   # a kernel that gave up a wait left garbage behind
         elapsed = time.perf_counter() - t_start
         mb_metrics: dict[str, list] = {}
         for m in all_mb_metrics:

@@ -215,6 +215,40 @@ def test_sampling_distribution_and_filters(native_lib):
     assert len(tok.unique()) == keep
 
 
+def test_sampling_top_k_then_top_p(native_lib):
+    """Both filters on: top-k first, then the nucleus inside the renormalised top-k set (same kept set and the same
+    log-probabilities as the CPU statement of the sampler)."""
+    from rl_b200.ops.engine_ops import sample
+
+    V, n = 64, 4000
+    probs = torch.full((V,), 0.01 / (V - 3))
+    probs[:3] = torch.tensor([0.95, 0.03, 0.01])
+    peaked = probs.log()
+    # a flatter row: top_k = 6 keeps 6 tokens, top_p = 0.7 of THEIR mass cuts further
+    torch.manual_seed(5)
+    flat = torch.randn(V)
+    for base, k, p_ in ((peaked, 3, 0.9), (flat, 6, 0.7), (flat, 10, 0.5)):
+        logits = base[None].repeat(n, 1).contiguous()
+        tok_c, lp_c = sample(logits, top_k=k, top_p=p_, seed=1)           # CPU statement
+        full = torch.log_softmax(base, -1)
+        kth = torch.topk(base, k).values[-1]
+        zk = base.masked_fill(base < kth, float("-inf"))
+        sz, si = torch.sort(zk, descending=True)
+        pr = torch.softmax(sz, -1)
+        keep = si[((pr.cumsum(0) - pr) < p_)]
+        ref_lp = torch.log_softmax(base[keep], -1)
+        idx = {int(t): i for i, t in enumerate(keep.tolist())}
+        tok, lp = sample(logits.cuda(), top_k=k, top_p=p_, seed=9, step=0)
+        seen = set(tok.unique().tolist())
+        assert seen <= set(keep.tolist()), (seen, keep.tolist())
+        if len(keep) <= 4:
+            assert seen == set(keep.tolist())
+        want = torch.tensor([ref_lp[idx[int(t)]].item() for t in tok[:200].tolist()])
+        assert (lp[:200].cpu() - want).abs().max().item() < 1e-3
+        assert set(tok_c.unique().tolist()) <= set(keep.tolist())
+        del full
+
+
 @pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 2)])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("bs", [16, 64, 128, 48])
@@ -256,3 +290,47 @@ def test_kv_cache_write(native_lib):
     kr, vr = torch.zeros_like(kc).cpu(), torch.zeros_like(vc).cpu()
     E.kv_cache_write(qkv.cpu(), slots.cpu(), kr, vr, Hq, Hkv, D)
     assert torch.equal(kc.cpu(), kr) and torch.equal(vc.cpu(), vr)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(reference_policy_kl_penalty=0.05),
+    dict(reference_policy_kl_penalty=0.05, reference_policy_kl_type="k2", ratio_clip_c=3.0),
+    dict(reference_policy_kl_penalty=0.1, use_on_policy_kl_approximation=True, use_importance_sampling_correction=True,
+         truncated_importance_sampling_ratio=2.0, truncated_importance_sampling_type="tis"),
+    # custom clamps: the input clamp is active on some tokens (weight detached there), no output clamp
+    dict(reference_policy_kl_penalty=0.1, kl_input_clamp_value=0.5, kl_output_clamp_value=None,
+         use_on_policy_kl_approximation=True),
+    dict(reference_policy_kl_penalty=0.1, kl_input_clamp_value=0.5, kl_output_clamp_value=None, reference_policy_kl_type="k1"),
+    dict(reference_policy_kl_penalty=0.0, use_cispo=True),
+])
+def test_fused_clipped_pg_matches_pytorch_statement(native_lib, cfg):
+    """Loss value, metrics and d loss / d logprob of the fused kernel against the PyTorch statement of the same loss."""
+    from rl_b200.algorithms.loss.loss_functions import ClippedPGLossFn
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+    g = torch.Generator().manual_seed(3)
+    B, S = 6, 40
+    tm = torch.ones(B, S)
+    tm[:, :5] = 0
+    prev = -torch.rand(B, S, generator=g) * 3
+    data = BatchedDataDict(token_mask=tm, sample_mask=torch.tensor([1.0, 1, 1, 0, 1, 1]), advantages=torch.randn(B, S, generator=g),
+                           prev_logprobs=prev, generation_logprobs=prev + 0.05 * torch.randn(B, S, generator=g),
+                           reference_policy_logprobs=prev + 1.5 * torch.randn(B, S, generator=g)).to("cuda")
+    fn = ClippedPGLossFn(cfg)
+    base = (prev[:, 1:] + 0.4 * torch.randn(B, S - 1, generator=g)).cuda()
+    mask = data["token_mask"][:, 1:] * data["sample_mask"][:, None]
+    N = mask.sum()
+    c1 = base.clone().requires_grad_()
+    assert fn._can_fuse(c1, data)
+    l1, m1 = fn(c1, data, torch.tensor(5.0), N)
+    l1.backward()
+    c2 = base.clone().requires_grad_()
+    args = (c2, data["prev_logprobs"][:, 1:], data["generation_logprobs"][:, 1:],
+            data["reference_policy_logprobs"][:, 1:] if fn.cfg["reference_policy_kl_penalty"] != 0 else None,
+            data["advantages"][:, 1:], data["token_mask"][:, 1:], data["sample_mask"], mask, data, torch.tensor(5.0), N)
+    l2, m2 = fn._reference(*args)
+    l2.backward()
+    assert l1.item() == pytest.approx(l2.item(), rel=2e-4, abs=1e-6)
+    assert (c1.grad - c2.grad).abs().max().item() <= 2e-4 * c2.grad.abs().max().item() + 1e-8
+    for k in ("probs_ratio", "kl_penalty", "token_mult_prob_error"):
+        assert m1[k] == pytest.approx(m2[k], rel=1e-3, abs=1e-6), k

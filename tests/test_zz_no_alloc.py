@@ -55,9 +55,13 @@ def test_static_scratch_matches_regular_entry_point(native_lib):
         dx = torch.empty((rows, d), dtype=torch.bfloat16, device="cuda")
         dw = torch.empty(d, dtype=torch.float32, device="cuda")
         torch.cuda.synchronize()
+        free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 0, rows, d, d, d, stream)
         assert rc == 0, strerror(rc)
         torch.cuda.synchronize()
+        # the property the entry point exists for: neither the driver nor torch's allocator handed out memory
+        assert torch.cuda.memory_allocated() == held_before
+        assert torch.cuda.mem_get_info()[0] >= free_before
         err_dx = (dx.float() - dx_ref.float()).abs().max().item() / (dx_ref.float().abs().max().item() + 1e-6)
         err_dw = (dw - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
         assert err_dx < 1e-2 and err_dw < 1e-2, (err_dx, err_dw)
@@ -76,3 +80,22 @@ def test_static_scratch_rejects_oversize(native_lib):
     assert rc == -5 and b"8192" in strerror(rc)
     rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), t.data_ptr(), f.data_ptr(), 0, 1, 12, 12, 12, 0)
     assert rc == -2
+
+
+def test_static_scratch_rejects_bad_pointers(native_lib):
+    """A misaligned or null operand is refused on the host: nothing reaches the 16-byte vector loads."""
+    fn, strerror = _bind(native_lib)
+    d = 64
+    buf = torch.zeros(4 * d + 8, device="cuda", dtype=torch.bfloat16)
+    good, odd = buf[:d], buf[1 : d + 1]          # odd starts 2 bytes past a 16-byte boundary
+    f = torch.zeros(d, device="cuda")
+    args = lambda dy, x, w, dx: (dy, x, w, f.data_ptr(), dx, f.data_ptr(), 0, 1, d, d, d, 0)
+    g = good.data_ptr()
+    assert fn(*args(g, g, g, g)) == 0
+    for bad in (args(odd.data_ptr(), g, g, g), args(g, odd.data_ptr(), g, g), args(g, g, odd.data_ptr(), g),
+                args(g, g, g, odd.data_ptr()), args(None, g, g, g)):
+        assert fn(*bad) == -2
+    assert fn(g, g, g, f.data_ptr(), g, f.data_ptr(), 0, 1, d, d - 8, d, 0) == -2   # stride shorter than a row
+    assert fn(g, g, g, f.data_ptr(), g, f.data_ptr(), 0, 2**31, d, d, d, 0) == -2   # rows do not fit an int
+    torch.cuda.synchronize()
+    assert b"aligned" in strerror(-2)

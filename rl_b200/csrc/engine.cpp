@@ -44,6 +44,8 @@ struct Engine {
   std::vector<long long> running;
   long long clock = 0;
   long long n_preempt = 0;
+  int lookahead = 1;   // decode steps the host wants to run between two visits (multi-step decode)
+  int window = 1;      // steps granted by the last schedule() call
   // scratch of the last schedule() call
   std::vector<long long> prefill_ids, decode_ids, shared_ids;
   std::vector<int> copy_src, copy_dst;
@@ -131,10 +133,24 @@ RLB_API int rlb_engine_schedule(void* h, int* n_prefill, int* n_shared, int* n_d
   // 1. decode slots for the running set (oldest first so that preemption hits the youngest)
   std::sort(e->running.begin(), e->running.end(),
             [&](long long a, long long b) { return e->seqs[a].arrival < e->seqs[b].arrival; });
+  // Multi-step decode: every running sequence gets room for `window` more tokens (never beyond its own limit), so that
+  // the device can run that many steps from the block table alone. When the free blocks do not cover the full
+  // look-ahead for everybody, this call falls back to single steps (and to preemption if even those do not fit).
+  int want = e->lookahead;
+  if (want > 1) {
+    long long need = 0;
+    for (long long id : e->running) {
+      const Seq& s = e->seqs[id];
+      const int rem = std::max(1, s.max_new - s.num_generated);
+      need += std::max(0, e->blocks_for(s.num_tokens + std::min(want, rem)) - static_cast<int>(s.blocks.size()));
+    }
+    if (need > static_cast<long long>(e->free_list.size())) want = 1;
+  }
+  e->window = want;
   size_t i = 0;
   while (i < e->running.size()) {
     Seq& s = e->seqs[e->running[i]];
-    if (e->ensure_capacity(s, s.num_tokens + 1)) {
+    if (e->ensure_capacity(s, s.num_tokens + std::min(want, std::max(1, s.max_new - s.num_generated)))) {
       ++i;
       continue;
     }
@@ -265,6 +281,38 @@ RLB_API int rlb_engine_commit(void* h, const long long* ids, int n, int* finishe
     Seq& s = it->second;
     ++s.num_tokens;
     ++s.num_generated;
+    bool done = finished[i] != 0;
+    if (!done && s.num_generated >= s.max_new) {
+      done = true;
+      finished[i] = 2;
+    }
+    if (done) {
+      e->release_seq(s);
+      s.state = FINISHED;
+      e->running.erase(std::remove(e->running.begin(), e->running.end(), s.id), e->running.end());
+      e->seqs.erase(it);
+      ++retired;
+    }
+  }
+  return retired;
+}
+
+// Multi-step decode: sets how many decode steps the next schedule() calls should reserve blocks for (>= 1).
+RLB_API void rlb_engine_set_lookahead(void* h, int steps) { static_cast<Engine*>(h)->lookahead = steps < 1 ? 1 : steps; }
+// Steps granted by the last schedule() call (the look-ahead, or 1 when blocks were short).
+RLB_API int rlb_engine_window(void* h) { return static_cast<Engine*>(h)->window; }
+
+// Records counts[i] generated tokens for every id (the result of a window of decode steps). finished[i] != 0 retires
+// the sequence; one that reached its limit is retired too and gets finished[i] = 2. Returns the number retired.
+RLB_API int rlb_engine_commit_n(void* h, const long long* ids, int n, const int* counts, int* finished) {
+  Engine* e = static_cast<Engine*>(h);
+  int retired = 0;
+  for (int i = 0; i < n; ++i) {
+    auto it = e->seqs.find(ids[i]);
+    if (it == e->seqs.end()) continue;
+    Seq& s = it->second;
+    s.num_tokens += counts[i];
+    s.num_generated += counts[i];
     bool done = finished[i] != 0;
     if (!done && s.num_generated >= s.max_new) {
       done = true;

@@ -213,3 +213,87 @@ RLB_API int rlb_sample(const void* logits, int dtype, long long row_stride, int 
                                                     seed, step, step_ptr, row_keys, out_tok, out_logprob);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------- device-resident decode state
+// After a decode step has sampled one token per row, this kernel advances the engine's step inputs in place so that
+// the next step can run without the host: the sampled token becomes the next input id, position / context length /
+// random-stream key grow by one, the KV slot of the next token is looked up in the (pre-extended) block table, stop
+// tokens and the per-row length limit retire a row (no further cache writes, empty context), and the token and its
+// log-probability are appended to the window's output arrays. The host reads the outputs once per window of steps.
+namespace {
+struct AdvanceArgs {
+  const int* tok;            // [B] sampled this step
+  const float* lp;           // [B]
+  int* ids;                  // [B] next step's input ids
+  int* positions;            // [B]
+  int* seq_lens;             // [B]
+  long long* slots;          // [B] KV slot of the next step's token, -1: no write
+  long long* keys;           // [B] random-stream keys
+  const int* block_table;    // [B, bt_stride]
+  int bt_stride;
+  int* active;               // [B] 1 while the row still generates
+  int* remaining;            // [B] tokens the row may still generate
+  int* produced;             // [B] tokens appended to the outputs in this window
+  const int* stop_ids;       // [n_stop]
+  int n_stop;
+  int* out_tok;              // [window, out_stride]
+  float* out_lp;             // [window, out_stride]
+  int out_stride;
+  int max_window;
+  int* win_step;             // [1] index of this step inside the window; incremented here
+  int B, block_size;
+};
+
+__global__ void __launch_bounds__(1024) decode_advance_kernel(AdvanceArgs a) {
+  pdl_wait();
+  const int j = *a.win_step;
+  for (int b = threadIdx.x; b < a.B; b += blockDim.x) {
+    if (!a.active[b] || j >= a.max_window) {
+      if (j == 0) a.produced[b] = 0;   // a row that is inactive from the start of the window produced nothing
+      a.slots[b] = -1;
+      continue;
+    }
+    const int t = a.tok[b];
+    a.out_tok[static_cast<long long>(j) * a.out_stride + b] = t;
+    a.out_lp[static_cast<long long>(j) * a.out_stride + b] = a.lp[b];
+    a.produced[b] = j + 1;
+    const int rem = a.remaining[b] - 1;
+    a.remaining[b] = rem;
+    bool stop = rem <= 0;
+    for (int s = 0; s < a.n_stop; ++s) stop |= (a.stop_ids[s] == t);
+    if (stop) {
+      a.active[b] = 0;
+      a.slots[b] = -1;
+      a.seq_lens[b] = 0;
+      a.ids[b] = 0;
+      a.positions[b] = 0;
+    } else {
+      const int pos = a.positions[b] + 1;
+      a.ids[b] = t;
+      a.positions[b] = pos;
+      a.seq_lens[b] = pos + 1;
+      a.keys[b] += 1;
+      const int blk = pos / a.block_size;
+      a.slots[b] = blk < a.bt_stride
+                       ? static_cast<long long>(a.block_table[static_cast<long long>(b) * a.bt_stride + blk]) * a.block_size + pos % a.block_size
+                       : -1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *a.win_step = j + 1;
+}
+}  // namespace
+
+// Advances the decode-step inputs of B rows after sampling (see above). All pointers are device memory; `win_step`
+// must be zeroed by the host at the start of every window of at most `max_window` steps.
+RLB_API int rlb_decode_advance(const int* tok, const float* lp, int* ids, int* positions, int* seq_lens, long long* slots,
+                               long long* keys, const int* block_table, int bt_stride, int* active, int* remaining,
+                               int* produced, const int* stop_ids, int n_stop, int* out_tok, float* out_lp, int out_stride,
+                               int max_window, int* win_step, int B, int block_size, void* stream) {
+  if (B <= 0) return 0;
+  if (block_size <= 0 || bt_stride <= 0 || out_stride < B || max_window <= 0) return -2;
+  AdvanceArgs a{tok, lp, ids, positions, seq_lens, slots, keys, block_table, bt_stride, active, remaining, produced,
+                stop_ids, n_stop, out_tok, out_lp, out_stride, max_window, win_step, B, block_size};
+  const int threads = B >= 1024 ? 1024 : ((B + 31) / 32) * 32;
+  return static_cast<int>(rlb_launch_pdl(decode_advance_kernel, dim3(1), dim3(threads), 0, static_cast<cudaStream_t>(stream), a));
+}

@@ -43,6 +43,9 @@ _ENGINE_SIGS = {
     "rlb_engine_commit": ([_P, _P, _I, _P], _I),
     "rlb_engine_commit_first": ([_P, _P, _I, _P], _I),
     "rlb_engine_reset": ([_P], None),
+    "rlb_engine_set_lookahead": ([_P, _I], None),
+    "rlb_engine_window": ([_P], _I),
+    "rlb_engine_commit_n": ([_P, _P, _I, _P, _P], _I),
 }
 _bound = False
 
@@ -276,6 +279,21 @@ class _NativeScheduler:
         (self.lib.rlb_engine_commit_first if first else self.lib.rlb_engine_commit)(self.h, arr, n, fin)
         return list(fin)
 
+    def set_lookahead(self, steps: int) -> None:
+        self.lib.rlb_engine_set_lookahead(self.h, int(steps))
+
+    @property
+    def window(self) -> int:
+        return self.lib.rlb_engine_window(self.h)
+
+    def commit_n(self, ids, counts, finished):
+        n = len(ids)
+        arr = (_LL * n)(*ids)
+        cnt = (_I * n)(*[int(x) for x in counts])
+        fin = (_I * n)(*[int(x) for x in finished])
+        self.lib.rlb_engine_commit_n(self.h, arr, n, cnt, fin)
+        return list(fin)
+
     @property
     def num_free_blocks(self):
         return self.lib.rlb_engine_num_free_blocks(self.h)
@@ -317,11 +335,12 @@ class GenerationEngine:
     """Generates continuations for batches of token prompts with the model's current weights."""
 
     BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+    MAX_STOP_IDS = 256   # stop token ids checked on the device after every decode step
 
     def __init__(self, model: CausalLM, *, block_size: int = 64, num_blocks: Optional[int] = None,
                  kv_cache_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.5, max_running: int = 512,
                  max_prefill_tokens: int = 16384, max_model_len: int = 8192, use_cuda_graphs: bool = True,
-                 logits_fp32: bool = True, tokenizer=None, quantization: Optional[str] = None):
+                 logits_fp32: bool = True, tokenizer=None, quantization: Optional[str] = None, decode_window: int = 16):
         """``quantization``: None (bf16), ``"mxfp8"`` or ``"fp8"``: serve quantised copies of the linear weights
         (see ``engine/quantized.py``); call :meth:`requantize` after the weights changed."""
         self.model = model
@@ -361,9 +380,16 @@ class GenerationEngine:
         self.v_cache: Optional[list[torch.Tensor]] = None
         sched_cls = _NativeScheduler if _L.available() else _PyScheduler
         self.sched = sched_cls(self.num_blocks, block_size, max_running, max_prefill_tokens)
+        # Multi-step decode (native path): the step inputs live on the device and a small kernel advances them after
+        # sampling, so the host visits only every `decode_window` steps (one upload of the tables, that many graph
+        # replays, one download of the window's tokens). 1 restores a host visit per step.
+        self.decode_window = max(1, int(os.environ.get("RLB_DECODE_WINDOW", decode_window))) if self.native else 1
+        if self.decode_window > 1 and isinstance(self.sched, _NativeScheduler):
+            self.sched.set_lookahead(self.decode_window)
         self._graphs: dict[int, tuple] = {}
         self._static: Optional[dict] = None
         self._step_counter = 0
+        self._n_stop = 0
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
         # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
@@ -495,9 +521,11 @@ class GenerationEngine:
         and come back with a single copy."""
         if self._static is None:
             B, MB = self.max_running, self.max_blocks_per_seq
+            W = self.decode_window
             dev = self.device
             fields = [("slots", torch.int64, (B,)), ("keys", torch.int64, (B,)), ("ids", torch.int32, (B,)), ("positions", torch.int32, (B,)),
-                      ("seq_lens", torch.int32, (B,)), ("block_table", torch.int32, (B, MB))]
+                      ("seq_lens", torch.int32, (B,)), ("active", torch.int32, (B,)), ("remaining", torch.int32, (B,)),
+                      ("win_step", torch.int32, (4,)), ("stop_ids", torch.int32, (self.MAX_STOP_IDS,)), ("block_table", torch.int32, (B, MB))]
             offs, total = {}, 0
             for name, dt, shape in fields:
                 n = 1
@@ -509,13 +537,17 @@ class GenerationEngine:
             host_blob = torch.zeros(total, dtype=torch.uint8)
             if dev.type == "cuda":
                 host_blob = host_blob.pin_memory()
-            out_blob = torch.zeros(2 * B, dtype=torch.int32, device=dev)
+            # outputs of a window: [tokens produced per row | sampled tokens, step-major | their log-probabilities]
+            out_blob = torch.zeros(B + 2 * W * B, dtype=torch.int32, device=dev)
+            step_out = torch.zeros(2 * B, dtype=torch.int32, device=dev)   # the current step's samples
 
             def views(buf):
                 return {name: buf[o : o + nb].view(dt).view(shape) for name, (o, nb, dt, shape) in offs.items()}
 
             self._static = dict(views(blob), blob=blob, host_blob=host_blob, host=views(host_blob), out_blob=out_blob,
-                                tok=out_blob[:B], lp=out_blob[B:].view(torch.float32),
+                                produced=out_blob[:B], out_tok=out_blob[B : B + W * B].view(W, B),
+                                out_lp=out_blob[B + W * B :].view(torch.float32).view(W, B),
+                                tok=step_out[:B], lp=step_out[B:].view(torch.float32),
                                 temps=torch.ones(B, dtype=torch.float32, device=dev), top_ks=torch.zeros(B, dtype=torch.int32, device=dev),
                                 top_ps=torch.ones(B, dtype=torch.float32, device=dev))
             self._static["slots"].fill_(-1)
@@ -534,9 +566,12 @@ class GenerationEngine:
         E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=sp.seed,
                  row_keys=st["keys"][:B], out=(st["tok"][:B], st["lp"][:B]))
         self._agree(st["tok"][:B], st["lp"][:B])
+        if self.native:
+            E.decode_advance(st, B, self.block_size, self.decode_window, self._n_stop)
         return logits
 
-    def _run_decode(self, n: int, sp: SamplingParams, max_ctx: int):
+    def _run_decode(self, n: int, sp: SamplingParams, max_ctx: int, steps: int = 1):
+        """Runs ``steps`` decode steps back to back from the device-resident step inputs (native path)."""
         st = self._static_buffers()
         B = self._bucket(n)
         c = self.cfg
@@ -548,7 +583,7 @@ class GenerationEngine:
                                seed=sp.seed, row_keys=st["keys"][:n])
             tok, lp = self._agree(tok, lp)
             return tok[:n], lp[:n]
-        key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed)
+        key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed, self._n_stop)
         if self.use_graphs:
             g = self._graphs.get(key)
             if g is None:
@@ -567,18 +602,80 @@ class GenerationEngine:
                     self._decode_body(st, B, sp, num_splits, scratch)
                 g = (graph, scratch, _L.Counters.launches - before)
                 self._graphs[key] = g
-            if self._ev is not None:   # device time of the replay alone (the step's host work shows as decode_s minus this)
+            if self._ev is not None:   # device time of the replays alone (the window's host work shows as decode_s minus this)
                 self._ev[0].record()
-            g[0].replay()
+            for _ in range(steps):
+                g[0].replay()
             if self._ev is not None:
                 self._ev[1].record()
                 self._ev_pending = True
-            _L.Counters.graph_replayed(g[2])
+            _L.Counters.graph_replayed(g[2] * steps)
         else:
             no, nml = E.decode_scratch_sizes(B, self.hq, num_splits, c.head_dim)
             scratch = (torch.empty(no, dtype=torch.float32, device=self.device), torch.empty(nml, dtype=torch.float32, device=self.device)) if num_splits > 1 else None
-            self._decode_body(st, B, sp, num_splits, scratch)
+            for _ in range(steps):
+                self._decode_body(st, B, sp, num_splits, scratch)
         return st["tok"][:n], st["lp"][:n]
+
+    def _decode_window_native(self, decode, reqs, sp: SamplingParams, stop: set, st) -> None:
+        """One window of decode steps for the running sequences: upload the step inputs and block tables once, run up to
+        ``decode_window`` steps on the device (each step's sampled token feeds the next through the advance kernel, stop
+        tokens and length limits retire rows on the device), then read all tokens of the window with one copy."""
+        t0 = time.perf_counter()
+        n = len(decode)
+        hb = st["host"]
+        self.sched.tables(decode, self.max_blocks_per_seq, out=(hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n]))
+        ctx = hb["seq_lens"][:n]
+        hb["positions"][:n] = ctx
+        max_ctx = int(ctx.max()) + 1
+        hb["seq_lens"][:n] += 1
+        ids_np, keys_np, rem_np = hb["ids"].numpy(), hb["keys"].numpy(), hb["remaining"].numpy()
+        max_rem = 1
+        for j, sid in enumerate(decode):
+            r = reqs[sid]
+            ids_np[j] = r.out_tokens[-1]
+            keys_np[j] = (r.uid << 20) | len(r.out_tokens)
+            rem_np[j] = r.max_new - len(r.out_tokens)
+            max_rem = max(max_rem, int(rem_np[j]))
+        hb["active"][:n] = 1
+        hb["win_step"][0] = 0
+        B = self._bucket(n)
+        if B > n:  # padding rows: never active, no cache write, empty context
+            for name in ("seq_lens", "ids", "positions", "keys", "active", "remaining"):
+                hb[name][n:B] = 0
+            hb["slots"][n:B] = -1
+            hb["block_table"][n:B] = 0
+        steps = max(1, min(self.sched.window if isinstance(self.sched, _NativeScheduler) else 1, self.decode_window, max_rem))
+        st["blob"].copy_(st["host_blob"], non_blocking=True)   # all inputs of the window in one upload
+        _L.Counters.h2d_bytes += st["host_blob"].numel()
+        self._step_counter += steps
+        self._run_decode(n, sp, max_ctx, steps)
+        both = _L.to_host(st["out_blob"])   # one download for the window; synchronises the stream
+        if self._ev_pending:
+            self.stats["decode_device_s"] += self._ev[0].elapsed_time(self._ev[1]) * 1e-3
+            self._ev_pending = False
+        Bm, W = self.max_running, self.decode_window
+        prod = both[:n].tolist()
+        toks = both[Bm : Bm + W * Bm].view(W, Bm)
+        lps = both[Bm + W * Bm :].view(torch.float32).view(W, Bm)
+        fin = [0] * n
+        for j, sid in enumerate(decode):
+            c = prod[j]
+            if c <= 0:
+                raise _L.NativeLibraryError(f"decode window produced no token for request {sid}")
+            r = reqs[sid]
+            r.out_tokens.extend(toks[:c, j].tolist())
+            r.out_logprobs.extend(lps[:c, j].tolist())
+            fin[j] = 1 if r.out_tokens[-1] in stop else 0
+        fin = self.sched.commit_n(decode, prod, fin)
+        for j, sid in enumerate(decode):
+            if fin[j]:
+                r = reqs[sid]
+                r.finished = True
+                r.truncated = fin[j] == 2 and r.out_tokens[-1] not in stop
+        self.stats["decode_steps"] += steps
+        self.stats["generated_tokens"] += sum(prod)
+        self.stats["decode_s"] += time.perf_counter() - t0
 
     # ------------------------------------------------------------------ public API
     def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, max_new_tokens: Optional[Sequence[int]] = None,
@@ -639,6 +736,12 @@ class GenerationEngine:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
         dev = self.device
         st = self._static_buffers()
+        if self.native and len(stop) > self.MAX_STOP_IDS:
+            raise ValueError(f"at most {self.MAX_STOP_IDS} stop token ids are supported")
+        self._n_stop = len(stop)
+        st["host"]["stop_ids"].zero_()
+        if stop and self.native:
+            st["host"]["stop_ids"][: len(stop)] = torch.tensor(sorted(stop), dtype=torch.int32)
         t_begin = time.perf_counter()
         last_logits: dict[int, torch.Tensor] = {}
         # Expert-parallel MoE layers exchange tokens between the ranks of the expert group in every forward pass, so those
@@ -667,17 +770,15 @@ class GenerationEngine:
             if need_prefill and not prefill:
                 self._dummy_forward(decode=False)
             # ---- decode the sequences that were already running
-            if decode:
+            if decode and self.native:
+                self._decode_window_native(decode, reqs, sp, stop, st)
+            elif decode:
                 t0 = time.perf_counter()
                 n = len(decode)
                 hb = st["host"]
-                if isinstance(self.sched, _NativeScheduler):
-                    self.sched.tables(decode, self.max_blocks_per_seq, out=(hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n]))
-                    ctx = hb["seq_lens"][:n]
-                else:
-                    bt, ctx_t, sl = self.sched.tables(decode, self.max_blocks_per_seq)
-                    hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n] = bt, ctx_t, sl
-                    ctx = hb["seq_lens"][:n]
+                bt, ctx_t, sl = self.sched.tables(decode, self.max_blocks_per_seq)
+                hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n] = bt, ctx_t, sl
+                ctx = hb["seq_lens"][:n]
                 hb["positions"][:n] = ctx
                 max_ctx = int(ctx.max()) + 1
                 hb["seq_lens"][:n] += 1
@@ -686,27 +787,10 @@ class GenerationEngine:
                     r = reqs[sid]
                     ids_np[j] = r.out_tokens[-1]
                     keys_np[j] = (r.uid << 20) | len(r.out_tokens)
-                B = self._bucket(n)
-                if B > n:  # padding rows: no cache write, empty context
-                    hb["slots"][n:B] = -1
-                    hb["seq_lens"][n:B] = 0
-                    hb["ids"][n:B] = 0
-                    hb["positions"][n:B] = 0
-                    hb["block_table"][n:B] = 0
-                    hb["keys"][n:B] = 0
-                st["blob"].copy_(st["host_blob"], non_blocking=True)   # all inputs of the step in one upload
-                _L.Counters.h2d_bytes += st["host_blob"].numel()
+                st["blob"].copy_(st["host_blob"], non_blocking=True)
                 self._step_counter += 1
                 tok, lp = self._run_decode(n, sp, max_ctx)
-                if tok.data_ptr() == st["tok"].data_ptr():   # graph / native path: tokens and log-probabilities in one download
-                    both = _L.to_host(st["out_blob"])
-                    Bm = self.max_running
-                    tok_h, lp_h = both[:n].tolist(), both[Bm : Bm + n].view(torch.float32).tolist()
-                else:
-                    tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
-                if self._ev_pending:   # the copies above synchronised the stream: the events are complete
-                    self.stats["decode_device_s"] += self._ev[0].elapsed_time(self._ev[1]) * 1e-3
-                    self._ev_pending = False
+                tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
                 fin = self.sched.commit(decode, fin)
                 for j, sid in enumerate(decode):

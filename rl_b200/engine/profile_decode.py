@@ -29,6 +29,9 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--distinct-prompts", action="store_true", help="no prefix sharing between the prompts")
+    ap.add_argument("--trace", type=int, default=0, help="after the timed run, trace this many decode windows with the CUDA "
+                    "activity profiler and print, per kernel, the mean duration and the mean gap to the kernel before it "
+                    "(shares only: durations taken under a profiler are not benchmark figures)")
     ap.add_argument("--quantization", default="", help="mxfp8 | fp8: serve quantised copies of the linear weights (low-precision rollout)")
     a = ap.parse_args(argv)
     mc = preset(a.model)
@@ -60,7 +63,49 @@ def main(argv=None):
                decode_device_ms_per_step=round(1e3 * st.get("decode_device_s", 0.0) / max(1, st["decode_steps"]), 4),
                weight_stream_floor_ms=round(mc.num_parameters() * 2 / 6.5e12 * 1e3, 3))
     print(json.dumps(out), flush=True)
+    if a.trace:
+        trace_kernels(eng, prompts, a.trace)
 
+
+def trace_kernels(eng, prompts, windows: int) -> None:
+    """Kernel timeline of a few decode windows (graph replays included) from the CUDA activity profiler: per kernel
+    name the launches, the mean duration and the mean idle gap between the end of the previous kernel and its start
+    (negative: it overlapped its predecessor through programmatic dependent launch)."""
+    from collections import defaultdict
+
+    from torch.profiler import ProfilerActivity, profile
+
+    eng.sleep(free_kv_cache=False)
+    steps = windows * eng.decode_window
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        eng.generate(prompts, SamplingParams(max_new_tokens=steps + 1, stop_token_ids=[], seed=2))
+        torch.cuda.synchronize()
+    import os
+    import tempfile
+
+    path = os.path.join(tempfile.mkdtemp(prefix="rlb_trace_"), "trace.json")
+    prof.export_chrome_trace(path)
+    with open(path) as f:
+        events = json.load(f)["traceEvents"]
+    evs = sorted((e for e in events if e.get("cat") == "kernel"), key=lambda e: e["ts"])
+    # keep the decode part: drop everything up to the last flash-attention (prefill) kernel
+    last_prefill = max((i for i, e in enumerate(evs) if "flash_fwd" in e["name"]), default=-1)
+    evs = evs[last_prefill + 1:]
+    agg = defaultdict(lambda: [0, 0.0, 0.0])
+    prev_end = None
+    for e in evs:
+        st, en = e["ts"], e["ts"] + e["dur"]
+        grid = (e.get("args") or {}).get("grid")
+        k = e["name"].split("(")[0][-48:] + f" grid={grid[0] if grid else '?'}"
+        agg[k][0] += 1
+        agg[k][1] += en - st
+        if prev_end is not None:
+            agg[k][2] += st - prev_end
+        prev_end = max(prev_end or en, en)
+    span = (evs[-1]["ts"] + evs[-1]["dur"] - evs[0]["ts"]) if evs else 0.0
+    print(f"traced {len(evs)} kernels over {span / 1e3:.2f} ms ({steps} decode steps requested)")
+    for k, (n, dur, gap) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"{k:64s} n={n:6d} mean_us={dur / n:8.2f} mean_gap_us={gap / n:7.2f} share={dur / max(span, 1e-9):6.3f}")
 
 if __name__ == "__main__":
     main()

@@ -195,6 +195,16 @@ def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, to
     return tok, lp
 
 
+def decode_advance(st: dict, B: int, block_size: int, max_window: int, n_stop: int) -> None:
+    """Advances the device-resident decode-step inputs of ``B`` rows after sampling (``rlb_decode_advance``): ``st`` is the
+    engine's dict of fixed-address step tensors."""
+    bt = st["block_table"]
+    call("rlb_decode_advance", ptr(st["tok"]), ptr(st["lp"]), ptr(st["ids"]), ptr(st["positions"]), ptr(st["seq_lens"]),
+         ptr(st["slots"]), ptr(st["keys"]), ptr(bt), bt.stride(0), ptr(st["active"]), ptr(st["remaining"]), ptr(st["produced"]),
+         ptr(st["stop_ids"]), int(n_stop), ptr(st["out_tok"]), ptr(st["out_lp"]), st["out_tok"].stride(0), int(max_window),
+         ptr(st["win_step"]), B, int(block_size), stream_ptr())
+
+
 def block_copy(k_cache: torch.Tensor, v_cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
     """Copies whole cache blocks ``src[i] -> dst[i]`` in both caches (copy-on-write of a shared prompt's tail block)."""
     n = src.numel()

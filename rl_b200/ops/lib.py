@@ -57,6 +57,7 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_paged_decode_tma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
     "rlb_paged_decode_mma": [P, L, P, P, I, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P, P],
     "rlb_sample": [P, I, L, I, I, P, P, P, F, I, F, I, U64, U64, P, P, P, P, P],
+    "rlb_decode_advance": [P, P, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, P, I, I, P],
     "rlb_block_copy": [P, P, P, P, I, L, P],
     "rlb_gather_rows": [P, P, P, L, I, L, L, P],
 }

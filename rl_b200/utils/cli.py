@@ -17,6 +17,7 @@ def bootstrap(default_config: str, argv: Optional[list[str]] = None, backend: Op
     cfg = load_config(path or default_config, overrides)
     for k, v in (cfg.get("env_vars") or {}).items():  # YAML env_vars override the shell (docs/design-docs/env-vars.md:5-31)
         os.environ[str(k)] = str(v)
+    validate_recipe(cfg, quiet=int(os.environ.get("RANK", "0")) != 0)
     rank, world, device = init_distributed(backend or (cfg.get("cluster") or {}).get("backend"))
     if rank == 0:
         print(f"Loaded configuration from {path or default_config}")
@@ -40,3 +41,19 @@ def model_cfg_for_tokenizer(cfg: dict, tokenizer):
             over.setdefault("vocab_size", len(tokenizer))
         return preset(name, **over)
     return None
+
+
+def infer_algorithm(cfg: dict) -> str:
+    """Which algorithm's schema a recipe follows, from the sections it contains."""
+    for name in ("ppo", "distillation", "dpo", "rm", "sft", "grpo", "eval"):
+        if name in cfg:
+            return name
+    return "grpo"
+
+
+def validate_recipe(cfg: dict, quiet: bool = False):
+    """Typed validation of a loaded recipe (rl_b200/config/schema.py): wrong types and missing required keys stop the
+    run, keys that nothing reads are listed once with the closest known key."""
+    from rl_b200.config.schema import validate_master_config
+
+    return validate_master_config(cfg, infer_algorithm(cfg), strict=os.environ.get("RLB_STRICT_CONFIG", "0") == "1", quiet=quiet)

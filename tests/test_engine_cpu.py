@@ -106,3 +106,39 @@ def test_engine_timeline_records_in_flight_batch_sizes():
     tl = eng.timeline
     assert tl and max(x[1] for x in tl) <= 2 and tl[0][3] == 3 and tl[-1][3] >= 1      # never more than max_running decoding
     assert all(a[0] <= b[0] for a, b in zip(tl, tl[1:])) and sum(x[2] for x in tl) == 3   # every request prefilled once
+
+
+@pytest.mark.skipif(not L.available(), reason="native library not built")
+def test_native_scheduler_lookahead_reserves_blocks_for_a_window():
+    """Multi-step decode: schedule() reserves blocks for ``lookahead`` more tokens per running sequence (never beyond its
+    limit), commit_n records a window's tokens, and a cache too small for the look-ahead falls back to single steps."""
+    s = _NativeScheduler(num_blocks=32, block_size=16, max_running=4, max_prefill_tokens=0)
+    s.set_lookahead(8)
+    s.add(0, 30, 20, -1)
+    s.add(1, 10, 3, -1)
+    pf, sh, dc, cp = s.schedule()
+    assert pf == [0, 1] and not dc
+    s.commit(pf, [0, 0], first=True)
+    pf, sh, dc, cp = s.schedule()
+    assert dc == [0, 1] and s.window == 8
+    bt, ctx, slots = s.tables(dc, 8)
+    assert ctx.tolist() == [30, 10]
+    # sequence 0 holds 30 tokens and may write 8 more: 38 tokens need 3 blocks; sequence 1 has 2 steps left: 12 tokens, 1 block
+    assert (bt[0, :3] >= 0).all() and len(set(bt[0, :3].tolist())) == 3
+    fin = s.commit_n(dc, [8, 2], [0, 0])
+    assert fin == [0, 2]   # the second sequence reached its limit of 3 generated tokens
+    pf, sh, dc, cp = s.schedule()
+    assert dc == [0]
+    bt, ctx, _ = s.tables(dc, 8)
+    assert ctx.tolist() == [38]
+    fin = s.commit_n(dc, [8], [1])   # a stop token ends it
+    assert fin == [1] and s.idle() and s.num_free_blocks == 32
+    # a cache that cannot hold the look-ahead for everybody grants single steps
+    t = _NativeScheduler(num_blocks=4, block_size=16, max_running=4, max_prefill_tokens=0)
+    t.set_lookahead(64)
+    t.add(0, 15, 40, -1)
+    t.add(1, 15, 40, -1)
+    pf, *_ = t.schedule()
+    t.commit(pf, [0, 0], first=True)
+    t.schedule()
+    assert t.window == 1

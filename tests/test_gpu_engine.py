@@ -126,3 +126,32 @@ def test_model_matches_fp32_reference(native_lib):
         ga, gb = a.grad.float().cpu(), b.grad
         denom = gb.abs().max().item() + 1e-6
         assert (ga - gb).abs().max().item() / denom < 0.08, n
+
+
+def test_windowed_decode_matches_single_step_decode(native_lib):
+    """The device-resident multi-step decode (the host looks once per window) must produce exactly the tokens and
+    log-probabilities of one host visit per step: same seeds, ragged length limits, a stop token in the vocabulary."""
+    from rl_b200.engine.engine import GenerationEngine, SamplingParams
+    from rl_b200.ops.lib import check_status
+
+    policy, _ = _policy()
+    torch.manual_seed(1)
+    prompts = [torch.randint(1, 8192, (int(n),)).tolist() for n in torch.randint(5, 60, (11,))]
+    limits = [3, 40, 17, 16, 1, 33, 40, 2, 25, 40, 31]
+    outs = []
+    for window in (1, 16, 5):
+        eng = GenerationEngine(policy.model, block_size=16, kv_cache_tokens=8192, max_running=8, max_model_len=512, decode_window=window)
+        assert eng.decode_window == window
+        # a sampled id below 200 ends a sequence: some rows stop in the middle of a window
+        sp = SamplingParams(temperature=1.0, max_new_tokens=40, stop_token_ids=list(range(200)), seed=5)
+        recs = eng.generate(prompts, sp, max_new_tokens=limits)
+        assert check_status() == 0
+        outs.append([(r.out_tokens, r.out_logprobs, r.truncated) for r in recs])
+        steps = eng.stats["decode_steps"]
+        eng.sleep(True)
+    for a, b in zip(outs[0], outs[1]):
+        assert a[0] == b[0] and a[2] == b[2]
+        assert max(abs(x - y) for x, y in zip(a[1], b[1])) < 1e-5
+    assert [o[0] for o in outs[0]] == [o[0] for o in outs[2]]
+    assert any(len(o[0]) < lim for o, lim in zip(outs[0], limits))      # some row hit a stop token
+    assert any(len(o[0]) == lim and o[2] for o, lim in zip(outs[0], limits))   # some row ran into its limit

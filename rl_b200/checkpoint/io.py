@@ -3,10 +3,13 @@
 * ``safetensors`` (default): rank 0 writes the HF layout (every rank holds the full bf16 parameters), so the result
   loads in ``transformers`` and in this package alike. With expert parallelism each rank writes its own experts.
 * ``torch_save``: one ``model.pt`` state dict in HF names.
-* ``dcp``: ``torch.distributed.checkpoint`` of the flat parameter shard per rank (``ModelState`` / ``OptimizerState``
-  style keys), the format of nemo_rl/utils/native_checkpoint.py:68-238; ``convert_dcp_to_hf`` rebuilds HF tensors.
+* ``dcp``: ``torch.distributed.checkpoint`` with one entry per HF parameter name (``model.<name>``,
+  ``optim.optim.state.<name>.exp_avg`` ...), the on-disk form of nemo_rl/utils/native_checkpoint.py:68-238: written at N
+  ranks it loads at any other N, and a checkpoint of the reference's DTensor worker loads here
+  (``rl_b200/checkpoint/dcp_state.py``); ``convert_dcp_to_hf`` rebuilds HF tensors from either.
 
-Optimizer state is always sharded: every rank writes ``optimizer/rank_<r>.pt`` (moments + master remainder).
+Optimizer state: ``dcp`` writes per-parameter moments next to the weights; the other formats write one
+``optimizer/rank_<r>.pt`` per rank (moments + master remainder), tied to the layout that wrote it.
 """
 
 from __future__ import annotations
@@ -48,22 +51,11 @@ def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
             save_pretrained(worker.model, path)
         return
     if fmt == "dcp":
-        import torch.distributed.checkpoint as dcp
+        # one entry per HF parameter name, row-sharded over the saving ranks: loads at any world size, and in the
+        # reference's DTensor worker (rl_b200/checkpoint/dcp_state.py)
+        from rl_b200.checkpoint.dcp_state import save_model
 
-        os.makedirs(path, exist_ok=True)
-        opt = worker.optimizer
-        lo, hi = (opt.lo, opt.hi) if opt is not None else (0, worker.flat.padded)
-        state = {"model": {f"flat.rank{rank}": worker.flat.flat[lo:hi].detach().clone()}}
-        if world > 1:
-            dcp.save(state, checkpoint_id=path)
-        else:
-            dcp.save(state, checkpoint_id=path, no_dist=True)
-        if rank == 0:
-            meta = {"names": worker.flat.names, "offsets": worker.flat.offsets, "numels": worker.flat.numels,
-                    "shapes": [list(s) for s in worker.flat.shapes], "padded": worker.flat.padded, "world": world,
-                    "dtype": str(worker.flat.flat.dtype)}
-            json.dump(meta, open(os.path.join(path, "flat_layout.json"), "w"))
-            worker.model_cfg.save_pretrained(path)
+        save_model(worker, path)
         return
     if rank != 0:
         return
@@ -81,7 +73,14 @@ def load_weights(worker, path: str) -> None:
     from rl_b200.models.hf_io import _SafetensorsDir, load_hf_tensors
 
     rank, world = (worker.rank, worker.world)
-    if os.path.exists(os.path.join(path, "flat_layout.json")):
+    from rl_b200.checkpoint.dcp_state import is_per_parameter_checkpoint
+
+    if is_per_parameter_checkpoint(path):
+        from rl_b200.checkpoint.dcp_state import load_model
+
+        load_model(worker, path)
+        return
+    if os.path.exists(os.path.join(path, "flat_layout.json")):   # flat-shard DCP of earlier versions (same world size only)
         import torch.distributed.checkpoint as dcp
 
         meta = json.load(open(os.path.join(path, "flat_layout.json")))
@@ -106,8 +105,17 @@ def _global_rank() -> int:
     return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
 
 
-def save_optimizer_shard(worker, path: str) -> None:
-    """One file per rank (named by the global rank: optimizer shards are tied to the whole parallel layout)."""
+def save_optimizer_shard(worker, path: str, fmt: str = "safetensors") -> None:
+    """One file per rank (named by the global rank: optimizer shards are tied to the whole parallel layout), or with
+    ``fmt = "dcp"`` on a data-parallel layout a torch-DCP directory with per-parameter entries that loads at any world size."""
+    from rl_b200.parallel.state import get_state
+
+    st = get_state()
+    if (fmt or "").lower() == "dcp" and st.tp * st.pp * st.ep * st.cp == 1 and getattr(worker, "lora_cfg", None) is None:
+        from rl_b200.checkpoint.dcp_state import save_optimizer
+
+        save_optimizer(worker, path)
+        return
     os.makedirs(path, exist_ok=True)
     sd = {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in worker.optimizer.state_dict().items()}
     sd["scheduler"] = worker.scheduler.state_dict() if worker.scheduler is not None else None
@@ -117,6 +125,13 @@ def save_optimizer_shard(worker, path: str) -> None:
 
 
 def load_optimizer_shard(worker, path: str) -> None:
+    from rl_b200.checkpoint.dcp_state import is_per_parameter_checkpoint
+
+    if is_per_parameter_checkpoint(path):
+        from rl_b200.checkpoint.dcp_state import load_optimizer
+
+        load_optimizer(worker, path)
+        return
     f = os.path.join(path, f"rank_{_global_rank()}.pt")
     sd = torch.load(f, map_location=worker.device, weights_only=False)
     worker.optimizer.load_state_dict(sd)
@@ -134,6 +149,10 @@ def convert_dcp_to_hf(dcp_path: str, hf_path: str) -> str:
     from rl_b200.models.hf_io import save_pretrained
     from rl_b200.models.transformer import CausalLM
 
+    from rl_b200.checkpoint.dcp_state import dcp_to_hf, is_per_parameter_checkpoint
+
+    if is_per_parameter_checkpoint(dcp_path):
+        return dcp_to_hf(dcp_path, hf_path)
     meta = json.load(open(os.path.join(dcp_path, "flat_layout.json")))
     cfg = ModelConfig.from_pretrained(dcp_path)
     dtype = getattr(torch, meta["dtype"].replace("torch.", ""))

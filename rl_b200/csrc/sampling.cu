@@ -108,10 +108,13 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
   if (temp <= 0.f) temp = 1.f;
   const float inv_t = 1.f / temp;
 
-  // pass 1: maximum
+  const bool filtered = (top_k > 0 && top_k < V) || top_p < 1.f;
+  // pass 1: maximum (only the filters need it up front; the unfiltered draw below finds it on the way)
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, ldz(z, i));
-  mx = block_max(mx, red);
+  if (filtered) {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, ldz(z, i));
+    mx = block_max(mx, red);
+  }
 
   // Threshold from top-k / top-p (on raw logits; scaling by 1/T > 0 keeps the order). The filters compose the way the
   // train-side filter and vLLM apply them: top-k first, then the nucleus inside the renormalised top-k set. Both are a
@@ -157,29 +160,56 @@ sample_kernel(const T* __restrict__ logits, long long row_stride, int V, const f
     thr = ord2f(lo);
   }
 
-  // pass 2: normaliser over the kept set, and the draw
+  // final pass: normaliser over the kept set, and the draw. Without filters this is the only pass over the row: every
+  // thread keeps a running maximum with a rescaled running sum (online softmax), and the Gumbel key needs no maximum.
   float sum = 0.f;
+  float m_t = -INFINITY;
   ArgBest best{-INFINITY, 0x7fffffff};
   const uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  // fp32 rows that start on a 16-byte boundary are read four logits at a time
+  const bool vec4 = sizeof(T) == 4 && (reinterpret_cast<uintptr_t>(z) & 15u) == 0;
   for (int i4 = threadIdx.x * 4; i4 < V; i4 += blockDim.x * 4) {
     uint32_t rnd[4] = {0, 0, 0, 0};
     if (!is_greedy)
       philox4x32(static_cast<uint32_t>(i4 >> 2), row_keys ? static_cast<uint32_t>(rk) : static_cast<uint32_t>(row),
                  row_keys ? static_cast<uint32_t>(rk >> 32) : static_cast<uint32_t>(step),
                  row_keys ? 0x5eedu : static_cast<uint32_t>(step >> 32), k0, k1, rnd);
+    float vals[4];
+    if (vec4 && i4 + 3 < V) {
+      const float4 q = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(z) + i4);
+      vals[0] = q.x; vals[1] = q.y; vals[2] = q.z; vals[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vals[j] = i4 + j < V ? ldz(z, i4 + j) : -INFINITY;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int i = i4 + j;
       if (i < V) {
-        const float v = ldz(z, i);
-        if (v >= thr) {
-          const float s = (v - mx) * inv_t;
-          sum += __expf(s);
-          const float key = is_greedy ? v : s + gumbel_from_bits(rnd[j]);
+        const float v = vals[j];
+        if (filtered) {
+          if (v >= thr) {
+            const float s = (v - mx) * inv_t;
+            sum += __expf(s);
+            const float key = is_greedy ? v : s + gumbel_from_bits(rnd[j]);
+            best = better(best, ArgBest{key, i});
+          }
+        } else if (v > -INFINITY) {
+          if (v > m_t) {
+            sum = sum * __expf((m_t - v) * inv_t) + 1.f;
+            m_t = v;
+          } else {
+            sum += __expf((v - m_t) * inv_t);
+          }
+          const float key = is_greedy ? v : v * inv_t + gumbel_from_bits(rnd[j]);
           best = better(best, ArgBest{key, i});
         }
       }
     }
+  }
+  if (!filtered) {
+    mx = block_max(m_t, red);
+    sum = m_t > -INFINITY ? sum * __expf((m_t - mx) * inv_t) : 0.f;
   }
   sum = block_sum(sum, red);
   best = block_argmax(best, redb);

@@ -500,8 +500,59 @@ class GenerationEngine:
         hl = F.rmsnorm(hl, m.norm, c.rms_norm_eps)
         return self._output_logits(hl)
 
+    def _can_fuse_decode(self, n: int) -> bool:
+        """The decode step with RMSNorm and SwiGLU folded into the projections' epilogues (7 kernels per layer instead of
+        10) covers dense bf16 layers on one GPU; everything else takes the layer-by-layer path below."""
+        c = self.cfg
+        if not (self.native and self.tpw == 1 and not self.quantization and not c.is_moe and n <= 256
+                and os.environ.get("RLB_FUSED_DECODE", "1") != "0"):
+            return False
+        if c.hidden_size % 128 or c.intermediate_size % 64 or not len(self.model.layers):
+            return False
+        l0 = self.model.layers[0]
+        return getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
+
+    @torch.no_grad()
+    def _decode_forward_fused(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
+        """Decode step whose norms ride in the GEMM epilogues: the projection that produces the residual stream also
+        writes ``h * w_norm`` and per-tile sums of squares, the next projection scales its rows by the reciprocal RMS, and
+        gate_up applies SwiGLU itself (``rlb_gemm_skinny_fused``)."""
+        m, c = self.model, self.cfg
+        eps = c.rms_norm_eps
+        n, d = ids.shape[0], c.hidden_size
+        tiles = (d + 127) // 128
+        dev = ids.device
+        hw = torch.empty((n, d), dtype=m.dtype, device=dev)
+        hw2 = torch.empty((n, d), dtype=m.dtype, device=dev)
+        ssq = torch.empty((tiles, 256), dtype=torch.float32, device=dev)
+        ssq2 = torch.empty((tiles, 256), dtype=torch.float32, device=dev)
+        h = F.embedding(ids, m.embed_tokens)
+        L = len(m.layers)
+        for li, layer in enumerate(m.layers):
+            at = layer.self_attn
+            if li == 0:   # the embedding has no epilogue to leave the statistics: one plain norm per step
+                qkv = E.skinny_linear(F.rmsnorm(h, layer.input_layernorm, eps), at.qkv_proj, bias=at.qkv_bias)
+            else:
+                qkv = E.skinny_linear(hw, at.qkv_proj, bias=at.qkv_bias, ssq_in=ssq, eps=eps)
+            if c.qk_norm:
+                qkv = F.head_rmsnorm(qkv, at.q_norm, 0, at.hq, c.head_dim, eps)
+                qkv = F.head_rmsnorm(qkv, at.k_norm, at.q_local, at.hkv, c.head_dim, eps)
+            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, self.hq, self.hkv, c.head_dim,
+                               num_splits=num_splits, scratch=scratch)
+            h = E.skinny_linear(a, at.o_proj, residual=h, ssq_out=ssq2, norm_w=layer.post_attention_layernorm, out2=hw2)
+            act = E.skinny_linear(hw2, layer.mlp.gate_up_proj, ssq_in=ssq2, eps=eps, swiglu=True)
+            next_w = m.layers[li + 1].input_layernorm if li + 1 < L else m.norm
+            h = E.skinny_linear(act, layer.mlp.down_proj, residual=h, ssq_out=ssq, norm_w=next_w, out2=hw)
+        z = E.skinny_linear(hw, m.output_weight, out=logits_out, out_dtype=self.logits_dtype, ssq_in=ssq, eps=eps)
+        if self._banned_ids is not None:
+            z.index_fill_(1, self._banned_ids, -1e30)
+        return z
+
     @torch.no_grad()
     def _decode_forward(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
+        if self._can_fuse_decode(ids.shape[0]):
+            return self._decode_forward_fused(ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out)
         m, c = self.model, self.cfg
         h = F.embedding(ids, m.embed_tokens)
         for li, layer in enumerate(m.layers):

@@ -32,6 +32,7 @@ def main(argv=None):
     ap.add_argument("--trace", type=int, default=0, help="after the timed run, trace this many decode windows with the CUDA "
                     "activity profiler and print, per kernel, the mean duration and the mean gap to the kernel before it "
                     "(shares only: durations taken under a profiler are not benchmark figures)")
+    ap.add_argument("--trace-out", default="", help="write the traced (kernel, start us, duration us) list to this JSON file")
     ap.add_argument("--quantization", default="", help="mxfp8 | fp8: serve quantised copies of the linear weights (low-precision rollout)")
     a = ap.parse_args(argv)
     mc = preset(a.model)
@@ -64,10 +65,10 @@ def main(argv=None):
                weight_stream_floor_ms=round(mc.num_parameters() * 2 / 6.5e12 * 1e3, 3))
     print(json.dumps(out), flush=True)
     if a.trace:
-        trace_kernels(eng, prompts, a.trace)
+        trace_kernels(eng, prompts, a.trace, a.trace_out)
 
 
-def trace_kernels(eng, prompts, windows: int) -> None:
+def trace_kernels(eng, prompts, windows: int, out_path: str = "") -> None:
     """Kernel timeline of a few decode windows (graph replays included) from the CUDA activity profiler: per kernel
     name the launches, the mean duration and the mean idle gap between the end of the previous kernel and its start
     (negative: it overlapped its predecessor through programmatic dependent launch)."""
@@ -91,21 +92,31 @@ def trace_kernels(eng, prompts, windows: int) -> None:
     # keep the decode part: drop everything up to the last flash-attention (prefill) kernel
     last_prefill = max((i for i, e in enumerate(evs) if "flash_fwd" in e["name"]), default=-1)
     evs = evs[last_prefill + 1:]
+    import re
+
     agg = defaultdict(lambda: [0, 0.0, 0.0])
     prev_end = None
+    rows = []
     for e in evs:
         st, en = e["ts"], e["ts"] + e["dur"]
         grid = (e.get("args") or {}).get("grid")
-        k = e["name"].split("(")[0][-48:] + f" grid={grid[0] if grid else '?'}"
+        m = re.search(r"(\w+_kernel|\w+Kernel\w*|\w+_kern\w*)", e["name"])
+        k = (m.group(1) if m else e["name"][:40]) + f" grid={grid[0] if grid else '?'}"
+        # kernels launched with programmatic dependent launch start (and block) while their predecessor still runs, so the
+        # raw duration overstates them: the exclusive time is what the kernel adds after its predecessor has ended
+        excl = en - max(st, prev_end) if prev_end is not None else en - st
         agg[k][0] += 1
         agg[k][1] += en - st
-        if prev_end is not None:
-            agg[k][2] += st - prev_end
+        agg[k][2] += max(excl, 0.0)
+        rows.append((k, st, e["dur"]))
         prev_end = max(prev_end or en, en)
     span = (evs[-1]["ts"] + evs[-1]["dur"] - evs[0]["ts"]) if evs else 0.0
     print(f"traced {len(evs)} kernels over {span / 1e3:.2f} ms ({steps} decode steps requested)")
-    for k, (n, dur, gap) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
-        print(f"{k:64s} n={n:6d} mean_us={dur / n:8.2f} mean_gap_us={gap / n:7.2f} share={dur / max(span, 1e-9):6.3f}")
+    for k, (n, dur, excl) in sorted(agg.items(), key=lambda kv: -kv[1][2]):
+        print(f"{k:56s} n={n:6d} mean_us={dur / n:8.2f} exclusive_us={excl / n:8.2f} share={excl / max(span, 1e-9):6.3f}")
+    if out_path:
+        with open(out_path, "w") as f:
+            json.dump(rows[:20000], f)
 
 if __name__ == "__main__":
     main()

@@ -195,6 +195,54 @@ def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int = 0, to
     return tok, lp
 
 
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+                  bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                  ssq_in: Optional[torch.Tensor] = None, eps: float = 1e-6, ssq_out: Optional[torch.Tensor] = None,
+                  norm_w: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """Decode-sized projection (at most 256 rows) with the epilogue fusions of ``rlb_gemm_skinny_fused``.
+
+    ``ssq_in`` [tiles, stride]: ``x`` is ``h * w_norm`` and the output rows are scaled by the reciprocal RMS of ``h`` built
+    from these partial sums (RMSNorm folded into the projection). ``ssq_out`` + ``norm_w`` + ``out2``: also writes
+    ``out2 = y * norm_w`` and the partial sums of squares of ``y`` for the next norm. ``swiglu``: ``w`` is [gate | up] and the
+    result is ``silu(x gate^T) * (x up^T)``. CPU tensors run the fp32 statement of the same math."""
+    M, K = x.shape
+    N = w.shape[0] // 2 if swiglu else w.shape[0]
+    if not use_native(x):
+        xf = x.float()
+        y = xf @ w.float().t()
+        if ssq_in is not None:
+            y = y * torch.rsqrt(ssq_in[:, :M].sum(0) / K + eps)[:, None]
+        if swiglu:
+            y = torch.nn.functional.silu(y[:, :N]) * y[:, N:]
+        if bias is not None:
+            y = y + bias.float()
+        if residual is not None:
+            y = y + residual.float()
+        y = y.to(out_dtype)
+        if ssq_out is not None:
+            yf = y.float()
+            out2.copy_((yf * norm_w.float()).to(out2.dtype))
+            tiles = (N + 127) // 128
+            pad = torch.zeros((M, tiles * 128), dtype=torch.float32)
+            pad[:, :N] = yf * yf
+            ssq_out[:tiles, :M] = pad.view(M, tiles, 128).sum(-1).t()
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
+    call("rlb_gemm_skinny_fused", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+         int(out.dtype == torch.float32), ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0, 0,
+         ptr(ssq_in), ssq_in.shape[0] if ssq_in is not None else 0, ssq_in.stride(0) if ssq_in is not None else 0, float(eps),
+         ptr(ssq_out), ssq_out.stride(0) if ssq_out is not None else 0, ptr(norm_w), ptr(out2),
+         out2.stride(0) if out2 is not None else 0, int(swiglu), ptr(_L.status_word(x.device)), stream_ptr())
+    return out
+
+
 def decode_advance(st: dict, B: int, block_size: int, max_window: int, n_stop: int) -> None:
     """Advances the device-resident decode-step inputs of ``B`` rows after sampling (``rlb_decode_advance``): ``st`` is the
     engine's dict of fixed-address step tensors."""

@@ -29,6 +29,7 @@ _SIGS: dict[str, list[Any]] = {
     "rlb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, P, P, L, P, I, P],
     "rlb_gemm_num_n_tiles": [I],
     "rlb_gemm_skinny": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, P, P],
+    "rlb_gemm_skinny_fused": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, P, I, L, F, P, L, P, P, L, I, P, P],
     "rlb_gemm_skinny_split": [I, I],
     "rlb_gemm_skinny_static_weights": [I],
     "rlb_lm_head_logprob": [P, P, I, I, I, L, L, P, F, P, P, P, P, P, P, P, P, P],

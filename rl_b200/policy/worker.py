@@ -711,7 +711,7 @@ class PolicyWorker:
 
         save_weights(self, weights_path, model_save_format)
         if optimizer_path and self.optimizer is not None:
-            save_optimizer_shard(self, optimizer_path)
+            save_optimizer_shard(self, optimizer_path, model_save_format)
         if tokenizer_path and self.tokenizer is not None and self.rank == 0:
             self.tokenizer.save_pretrained(tokenizer_path)
         if self.world > 1:

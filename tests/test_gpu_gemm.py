@@ -140,3 +140,48 @@ def test_skinny_split_values(native_lib):
         assert _rel_err(y, ref) < 1e-2, split
         outs.append(y)
     assert lib().rlb_gemm_skinny_split(4096, 4096) in (1, 2, 4, 8)
+
+
+@pytest.mark.parametrize("M", [5, 64, 130])
+def test_skinny_gemm_epilogue_fusions_match_fp32_reference(native_lib, M):
+    """RMSNorm folded into two projections (producer writes h * w and per-tile sums of squares, consumer scales its rows)
+    and SwiGLU in the gate_up epilogue, against the fp32 statement of norm -> linear -> swiglu -> linear."""
+    from rl_b200.ops.engine_ops import skinny_linear
+    from rl_b200.ops.lib import check_status
+
+    torch.manual_seed(M)
+    d, f, eps = 512, 1408, 1e-5
+    dev = "cuda"
+    a = torch.randn(M, d, device=dev).to(torch.bfloat16)
+    res = torch.randn(M, d, device=dev).to(torch.bfloat16)
+    w_o = (torch.randn(d, d, device=dev) / d**0.5).to(torch.bfloat16)
+    w_norm = (1 + 0.1 * torch.randn(d, device=dev)).to(torch.bfloat16)
+    w_gu = (torch.randn(2 * f, d, device=dev) / d**0.5).to(torch.bfloat16)
+    w_dn = (torch.randn(d, f, device=dev) / f**0.5).to(torch.bfloat16)
+    tiles = d // 128
+    ssq = torch.zeros((tiles, 256), device=dev)
+    hw = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+    # producer: h = a W_o^T + res, plus h * w_norm and the per-tile sums of squares
+    h = skinny_linear(a, w_o, residual=res, ssq_out=ssq, norm_w=w_norm, out2=hw)
+    h_ref = (a.float() @ w_o.float().t() + res.float())
+    assert (h.float() - h_ref).abs().max().item() < 3e-2 * h_ref.abs().max().item()
+    hb = h.float()
+    assert torch.allclose(ssq[:, :M].sum(0), (hb * hb).sum(-1), rtol=1e-4)
+    assert (hw.float() - hb * w_norm.float()).abs().max().item() < 2e-2 * hb.abs().max().item()
+    # consumer with SwiGLU: silu(norm(h) Wg^T) * (norm(h) Wu^T)
+    act = skinny_linear(hw, w_gu, ssq_in=ssq, eps=eps, swiglu=True)
+    xn = hb * torch.rsqrt((hb * hb).mean(-1, keepdim=True) + eps) * w_norm.float()
+    gu = xn @ w_gu.float().t()
+    act_ref = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+    assert act.shape == (M, f)
+    assert (act.float() - act_ref).abs().max().item() < 3e-2 * act_ref.abs().max().item() + 1e-3
+    # consumer without SwiGLU, fp32 output and a bias (lm_head / qkv form)
+    bias = torch.randn(d, device=dev)
+    y = skinny_linear(hw, w_o, ssq_in=ssq, eps=eps, bias=bias, out_dtype=torch.float32)
+    y_ref = xn @ w_o.float().t() + bias
+    assert (y - y_ref).abs().max().item() < 2e-2 * y_ref.abs().max().item()
+    # and the down projection closes the loop with the next norm's hand-off
+    h2 = skinny_linear(act, w_dn, residual=h, ssq_out=ssq, norm_w=w_norm, out2=hw)
+    h2_ref = act.float() @ w_dn.float().t() + hb
+    assert (h2.float() - h2_ref).abs().max().item() < 3e-2 * h2_ref.abs().max().item()
+    assert check_status() == 0

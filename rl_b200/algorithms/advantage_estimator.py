@@ -184,9 +184,18 @@ class OPDAdvantageEstimator:
         self.reward_coef = cfg.get("reward_coef", 0.0)
         self.inner = GRPOAdvantageEstimator(cfg) if self.reward_coef else None
 
-    def compute_advantage(self, prompt_ids, rewards, mask, teacher_logprobs=None, logprobs_policy=None, **kw):
-        assert teacher_logprobs is not None and logprobs_policy is not None
-        adv = self.coef * (teacher_logprobs - logprobs_policy).detach() * mask
+    def compute_advantage(self, prompt_ids, rewards, mask, teacher_logprobs=None, logprobs_policy=None, prev_logprobs=None, **kw):
+        student = logprobs_policy if logprobs_policy is not None else prev_logprobs
+        assert teacher_logprobs is not None and student is not None
+        gap = (teacher_logprobs - student).detach()
+        adv = self.coef * gap * mask
+        n = mask.sum().clamp(min=1)
+        mean = (adv * mask).sum() / n
+        self.last_metrics = {
+            "on_policy_distillation/teacher_student_logprob_gap_mean": float((gap * mask).sum() / n),
+            "on_policy_distillation/adv_mean": float(mean),
+            "on_policy_distillation/adv_std": float((((adv - mean) ** 2 * mask).sum() / n).sqrt()),
+        }
         if self.inner is not None:
             adv = adv + self.reward_coef * self.inner.compute_advantage(prompt_ids, rewards, mask, **kw)
         return adv

@@ -1,7 +1,7 @@
 """Reward shaping applied after the environments score a batch (nemo_rl/algorithms/reward_functions.py:24-171).
 
 * DAPO over-long shaping: responses longer than ``max_response_length - overlong_buffer_length`` lose reward linearly,
-  down to ``-overlong_buffer_penalty`` at ``max_response_length``.
+  ``-overlong_buffer_penalty`` at ``max_response_length`` and more beyond it.
 * Stop-properly penalty: truncated responses are scaled by ``stop_properly_penalty_coef`` (0 zeroes them, 1 keeps).
 """
 
@@ -23,7 +23,8 @@ def apply_reward_shaping(batch, cfg: Optional[dict]):
         return batch
     rewards = batch["total_reward"].clone().float()
     batch["unshaped_reward"] = batch["total_reward"].clone()
-    gen_len = batch["generation_lengths"].float()
+    gen_len = batch["response_token_lengths"] if "response_token_lengths" in batch else batch["generation_lengths"]
+    gen_len = torch.as_tensor(gen_len).float()
     coef = c["stop_properly_penalty_coef"]
     if coef is not None:
         assert 0.0 <= coef <= 1.0, "stop_properly_penalty_coef must lie in [0, 1]"
@@ -36,7 +37,7 @@ def apply_reward_shaping(batch, cfg: Optional[dict]):
         assert 0 < buf <= L, "overlong_buffer_length must lie in (0, max_response_length]"
         expected = L - buf
         excess = (gen_len - expected).clamp(min=0)
-        rewards = rewards - (excess / buf).clamp(max=1.0) * pen
+        rewards = rewards - excess / buf * pen   # no cap beyond max_response_length: the penalty keeps growing
     batch["total_reward"] = rewards
     return batch
 

@@ -1,12 +1,14 @@
-"""Headline benchmark: one GRPO step (generation + refit + log-probabilities + training) on the Llama-3.1-8B
-architecture, N GPUs of one node, synthetic prompts, random-init weights.
+"""Benchmarks of the GRPO step on one node of N GPUs, synthetic prompts, random-init weights.
 
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched once per GPU by torch.distributed.run)
+    python bench.py --config qwen3-32b-tp4dp2 --gpus 8 ...   (other model / layout configurations, see CONFIGS)
+    python bench.py --config refit-sweep --gpus 8            (weight re-shard times, trainer layout -> serving layouts)
     python bench.py --impl reference ...                     (the unmodified reference, when it can be installed)
 
-Work per step and per GPU is fixed (weak scaling): 8 prompts x 8 generations, prompts of 256 random tokens, 1024
-generated tokens each (stop tokens disabled so every response runs to the limit), one optimizer step over the global
-batch of 64*N sequences. At N = 8 this is the 64 prompts x 8 generations configuration.
+Default (headline) configuration ``llama8b-dp``: one GRPO step (generation + refit + log-probabilities + training) on
+the Llama-3.1-8B architecture. Work per step and per GPU is fixed (weak scaling): 8 prompts x 8 generations, prompts of
+256 random tokens, 1024 generated tokens each (stop tokens disabled so every response runs to the limit), one optimizer
+step over the global batch of 64*N sequences. At N = 8 this is the 64 prompts x 8 generations configuration.
 
 Two timed regions, K steps each:
   * device: the phases called directly, bracketed by CUDA events on the launching stream (max over ranks);
@@ -32,26 +34,49 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 
+# Named configurations. ``llama8b-dp`` is the headline; the others are the larger model / layout configurations of the
+# same benchmark family (one 8-GPU node). Values a flag also sets are defaults that the flag overrides.
+CONFIGS = {
+    "llama8b-dp": dict(model="llama3.1-8b", tp=1, ep=1, gen_tp=0, prompts_per_gpu=8, generations=8, prompt_len=256, max_new_tokens=1024,
+                       train_mb_tokens=5120, logprob_mb_tokens=20480, act_ckpt="off"),
+    # Qwen3-32B: TP4 x DP2 training with sequence parallelism, generation TP2 x 4 engines, fused vocabulary-parallel lm_head
+    "qwen3-32b-tp4dp2": dict(model="qwen3-32b", tp=4, ep=1, gen_tp=2, prompts_per_gpu=2, generations=8, prompt_len=512, max_new_tokens=3584,
+                             train_mb_tokens=8192, logprob_mb_tokens=16384, act_ckpt="on"),
+    # Qwen3-30B-A3B: expert parallel over all GPUs, dense parts data parallel
+    "qwen3-30b-a3b-ep8": dict(model="qwen3-30b-a3b", tp=1, ep=0, gen_tp=0, prompts_per_gpu=4, generations=8, prompt_len=512, max_new_tokens=2048,
+                              train_mb_tokens=8192, logprob_mb_tokens=16384, act_ckpt="on"),
+    "refit-sweep": dict(),
+}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="llama3.1-8b")
-    ap.add_argument("--prompts-per-gpu", type=int, default=8)
-    ap.add_argument("--generations", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=256)
-    ap.add_argument("--max-new-tokens", type=int, default=1024)
+    ap.add_argument("--config", default="llama8b-dp", choices=sorted(CONFIGS))
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--prompts-per-gpu", type=int, default=None)
+    ap.add_argument("--generations", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--max-new-tokens", type=int, default=None)
+    ap.add_argument("--gen-tp", type=int, default=None, help="tensor-parallel size of the generation engines (0: the trainer's)")
+    ap.add_argument("--ep", type=int, default=None, help="expert-parallel size (0: all GPUs)")
+    ap.add_argument("--logprob-mb-tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (makes the run invalid as a benchmark)")
-    ap.add_argument("--train-mb-tokens", type=int, default=5120, help="tokens per training micro-batch (the same at every N)")
+    ap.add_argument("--train-mb-tokens", type=int, default=None, help="tokens per training micro-batch (the same at every N)")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size of the trainer and the engine (with sequence parallelism); "
+    ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size of the trainer (with sequence parallelism); "
                     "the headline configuration is --tp 1")
-    ap.add_argument("--act-ckpt", default="auto", choices=["auto", "on", "off"],
-                    help="activation checkpointing in training (auto = off: with 5120-token micro-batches the activations of "
+    ap.add_argument("--act-ckpt", default=None, choices=["on", "off"],
+                    help="activation checkpointing in training (headline: off, with 5120-token micro-batches the activations of "
                          "Llama-3.1-8B fit next to the unsharded optimizer state even on 1 GPU)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    for k, v in CONFIGS[args.config].items():   # flags left unset take the configuration's values
+        if getattr(args, k, None) is None:
+            setattr(args, k, v)
+    return args
 
 
 def reference_arm(args) -> int:
@@ -133,6 +158,10 @@ def main() -> int:
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config == "refit-sweep":
+        from rl_b200.refit.bench_refit import sweep_main
+
+        return sweep_main(steps=args.steps, warmup=args.warmup)
 
     import torch
     import torch.distributed as dist
@@ -182,21 +211,24 @@ def main() -> int:
     max_len = args.prompt_len + args.max_new_tokens
     steps_needed = args.warmup + 2 * args.steps + 2
     mb_tokens = args.train_mb_tokens
+    gen_tp = args.gen_tp or args.tp   # every engine of gen_tp ranks serves the sequences of gen_tp GPUs
     cfg = {
         "grpo": dict(num_prompts_per_step=n_prompts, num_generations_per_prompt=n_gen, max_num_steps=10**9, val_period=0, seed=0,
                      normalize_rewards=True, use_leave_one_out_baseline=True),
         "loss_fn": dict(reference_policy_kl_penalty=0.01, ratio_clip_min=0.2, ratio_clip_max=0.2),
         "policy": dict(
             model_name=None, precision="bfloat16", train_global_batch_size=seqs_per_gpu * world, train_micro_batch_size=4,
-            parallel=dict(tensor_parallel_size=args.tp, sequence_parallel=args.tp > 1),
+            parallel=dict(tensor_parallel_size=args.tp, sequence_parallel=args.tp > 1,
+                          expert_parallel_size=(world if args.ep == 0 else args.ep) if mc.is_moe else 1),
             logprob_batch_size=8, max_total_sequence_length=max_len, max_grad_norm=1.0,
             activation_checkpointing=(args.act_ckpt == "on"), grad_dtype="float32",
-            sequence_packing=dict(enabled=True, train_mb_tokens=mb_tokens, logprob_mb_tokens=20480,
+            sequence_packing=dict(enabled=True, train_mb_tokens=mb_tokens, logprob_mb_tokens=args.logprob_mb_tokens,
                                   algorithm="modified_first_fit_decreasing"),
             optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=3e-7, weight_decay=0.01, betas=[0.9, 0.999], eps=1e-8)),
             generation=dict(max_new_tokens=args.max_new_tokens, temperature=1.0, top_p=1.0, top_k=None, stop_token_ids=[],
-                            kv_cache_tokens=seqs_per_gpu * args.tp * (max_len + 64), block_size=64, max_running=max(64, seqs_per_gpu * args.tp),
-                            max_prefill_tokens=16384, free_kv_cache_on_sleep=False),
+                            kv_cache_tokens=seqs_per_gpu * gen_tp * (max_len + 64), block_size=64, max_running=max(64, seqs_per_gpu * gen_tp),
+                            max_prefill_tokens=16384, free_kv_cache_on_sleep=False,
+                            **({"native_cfg": {"tensor_parallel_size": gen_tp}} if gen_tp != args.tp else {})),
         ),
         "logger": dict(log_dir=tempfile.mkdtemp(prefix="rlb_bench_logs_")),
         "checkpointing": dict(enabled=False),
@@ -283,14 +315,19 @@ def main() -> int:
         e2e = dict(seconds=e2e_s, h2d=L.Counters.h2d_bytes // args.steps, d2h=L.Counters.d2h_bytes // args.steps)
 
     # ---------------------------------------------------------------- reduce over ranks
+    status = L.check_status()
     stats = torch.tensor([dev_ms, e2e["seconds"] if e2e else 0.0, float(sum(tokens_per_step)), float(launches), mult_prob_err] +
                          [phase_ms[k] for k in ("generation", "refit", "logprobs", "training")], dtype=torch.float64, device=dev)
     PH = 5  # index of the first phase entry
     mx = stats.clone()
     sm = stats.clone()
+    mn = stats.clone()
+    st_all = torch.tensor([float(status)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        dist.all_reduce(st_all, op=dist.ReduceOp.MAX)
     dev_ms_max, e2e_s_max = float(mx[0]), float(mx[1])
     total_tokens = float(sm[2]) / args.tp  # all data-parallel ranks, all timed steps (the ranks of a tensor-parallel group share their data)
     ms_per_step = dev_ms_max / args.steps
@@ -314,13 +351,20 @@ def main() -> int:
                 "global_batch": seqs_per_gpu * world, "seq_len": max_len,
                 "prompts_per_step": n_prompts, "generations_per_prompt": n_gen, "prompt_len": args.prompt_len,
                 "max_new_tokens": args.max_new_tokens,
-                "parallelism": (f"dp{world} (resident bf16 params, optimizer state sharded {world}-way, generation TP1 colocated)" if args.tp == 1 else
-                                f"tp{args.tp} x dp{world // args.tp} (sequence parallel, fused peer-memory TP kernels, generation TP{args.tp} colocated)"),
+                "name": args.config,
+                "parallelism": (f"ep{world if args.ep == 0 else args.ep} experts, dense parts dp{world} (fused peer-memory dispatch / combine, generation colocated)" if mc.is_moe else
+                                f"dp{world} (resident bf16 params, optimizer state sharded {world}-way, generation TP1 colocated)" if args.tp == 1 else
+                                f"tp{args.tp} x dp{world // args.tp} (sequence parallel, fused peer-memory TP kernels, generation TP{gen_tp} x {world // gen_tp} engines colocated)"),
+                "train_mb_tokens": mb_tokens,
                 "l2": "inputs larger than L2 (16 GB of weights streamed every pass)",
             },
             "tokens_per_sec_per_gpu": round(value / world, 1),
             "step_split_ms": {k: round(float(mx[PH + i]) / args.steps, 2) for i, k in enumerate(("generation", "refit", "logprobs", "training"))},
-            "token_mult_prob_error": round(float(sm[4]), 5),  # per-rank partial means sum to the global mean
+            # per-rank partial means sum to the global mean; the ranks of a tensor-parallel group hold the same data
+            "token_mult_prob_error": round(float(sm[4]) / args.tp, 5),
+            "generation_ms_per_rank": {"min": round(float(mn[PH]) / args.steps, 2), "max": round(float(mx[PH]) / args.steps, 2)},
+            "optimizer_path": "fused_peer" if getattr(policy, "fused_comm", None) is not None and world // args.tp > 1 else ("local" if world // args.tp == 1 else "nccl"),
+            "status": int(st_all[0]),
             "clocks": clocks,
             "gpu_launches": int(float(mx[3])),
             "impl": "ours",
@@ -334,14 +378,11 @@ def main() -> int:
             gen.shutdown()   # drops the captured decode graphs before the communicators go away
         except Exception:
             pass
+        import gc
+
+        gc.collect()   # captured graphs are gone before the communicators are
         torch.cuda.synchronize()
         dist.barrier()
-        if args.tp > 1:
-            # a tensor-parallel engine captures NCCL broadcasts in its decode graphs; tearing the process groups down after
-            # that was seen to stall in the NCCL watchdog, so these ranks leave without the teardown (all work is complete)
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
         dist.destroy_process_group()
     return 0
 

@@ -221,6 +221,60 @@ __global__ void __launch_bounds__(512, 1) p2p_allgather_kernel(GatherArgs a) {
   }
 }
 
+// Column all-gather for tensor-parallel logits: every rank holds a [rows, cols_local] slice and needs the full
+// [rows, world * cols_local] matrix. One cooperative kernel per rank, safe to record in a CUDA graph:
+//   1. the local slice is copied into this rank's symmetric staging buffer, half (epoch & 1);
+//   2. flag barrier: every rank has published its slice of this call (and so has finished reading the previous call's);
+//   3. every rank pulls all slices (its own included) into its output with plain peer loads.
+// The call's epoch lives in device memory (*epoch_ptr + 1, stored back), so replays of a captured launch stay in step;
+// the two staging halves make the closing barrier unnecessary: a fast rank can only overwrite the half that every
+// rank finished reading before it passed the barrier of the call in between.
+struct GatherColsArgs {
+  const uint4* local;            // [rows, row_vecs] 16-byte vectors of this rank's slice (dense)
+  uint4* stage[MAX_RANKS];       // per rank: 2 halves of rows * row_vecs vectors
+  unsigned int* flags[MAX_RANKS];
+  uint4* out;                    // [rows, out_stride_vecs]
+  long long out_stride_vecs;
+  int rows, row_vecs;
+  int rank, world;
+  unsigned int* epoch_ptr;
+  unsigned long long limit_ns;
+  int* abort_word;
+  int* status;
+};
+__global__ void __launch_bounds__(512, 1) p2p_gather_cols_kernel(GatherColsArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(a.epoch_ptr) + 1;
+  const long long n = static_cast<long long>(a.rows) * a.row_vecs;
+  const long long half = (epoch & 1u) ? n : 0;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  uint4* mine = a.stage[a.rank] + half;
+  for (long long i = tid; i < n; i += nthreads) mine[i] = a.local[i];
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    PeerTable t;
+    for (int r = 0; r < MAX_RANKS; ++r) t.flags[r] = a.flags[r];
+    const bool ok = peer_barrier(t, a.rank, a.world, 0, epoch, a.limit_ns, a.status);
+    if (threadIdx.x == 0) {
+      *a.abort_word = ok ? 0 : 1;
+      *a.epoch_ptr = epoch;   // every CTA read the old value before the grid barrier above
+    }
+    __threadfence();
+  }
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(a.abort_word)) return;   // a peer did not arrive: the output is left alone
+  for (int p = 0; p < a.world; ++p) {
+    const int r = (a.rank + p) % a.world;  // start with the local slice, stagger the peers
+    const uint4* src = a.stage[r] + half;
+    for (long long i = tid; i < n; i += nthreads) {
+      const long long row = i / a.row_vecs, c = i - row * a.row_vecs;
+      a.out[row * a.out_stride_vecs + static_cast<long long>(r) * a.row_vecs + c] = src[i];
+    }
+  }
+}
+
 int coop_grid(const void* kernel, int threads) {
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
@@ -318,5 +372,37 @@ RLB_API int rlb_p2p_allgather(void* const* src_ptrs, void* dst, void* const* fla
   const int grid = coop_grid(reinterpret_cast<const void*>(p2p_allgather_kernel), 512);
   void* args[] = {&a};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_allgather_kernel), dim3(grid),
+                                                      dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
+}
+
+// out[rows, world * cols] = concatenation over ranks of their `local` [rows, cols] slices (see p2p_gather_cols_kernel).
+// row_bytes = cols * element size, a multiple of 16; stage_ptrs[r]: rank r's staging of 2 * rows * row_bytes bytes;
+// flag_ptrs[r]: 8 zero-initialised uint32 words of symmetric memory; epoch_ptr: device uint32 (starts at 0);
+// scratch: one device int.
+RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void* const* flag_ptrs, void* out,
+                                long long out_stride_bytes, int rows, int row_bytes, int rank, int world, void* epoch_ptr,
+                                double wait_limit_s, int* scratch, int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rows <= 0 || row_bytes <= 0 || (row_bytes % 16) || (out_stride_bytes % 16)) return -2;
+  if ((reinterpret_cast<uintptr_t>(local) | reinterpret_cast<uintptr_t>(out)) & 15) return -3;
+  GatherColsArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int r = 0; r < world; ++r) {
+    a.stage[r] = static_cast<uint4*>(stage_ptrs[r]);
+    a.flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
+  }
+  a.local = static_cast<const uint4*>(local);
+  a.out = static_cast<uint4*>(out);
+  a.out_stride_vecs = out_stride_bytes / 16;
+  a.rows = rows;
+  a.row_vecs = row_bytes / 16;
+  a.rank = rank;
+  a.world = world;
+  a.epoch_ptr = static_cast<unsigned int*>(epoch_ptr);
+  a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
+  a.abort_word = scratch;
+  a.status = status;
+  const int grid = coop_grid(reinterpret_cast<const void*>(p2p_gather_cols_kernel), 512);
+  void* args[] = {&a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_gather_cols_kernel), dim3(grid),
                                                       dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
 }

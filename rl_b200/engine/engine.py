@@ -447,7 +447,10 @@ class GenerationEngine:
     def _output_logits(self, h, out=None):
         """[n, V] logits: the local vocabulary slice is projected here and the slices are gathered over the tp group."""
         z = F.gemm(h, self.model.output_weight, out=out if self.tpw == 1 else None, out_dtype=self.logits_dtype)
-        z = z if self.tpw == 1 else gather_cols(z, self.tp)
+        if self.tpw > 1:
+            comm = getattr(self.tp, "comm", None)
+            # peer-memory column gather (no NCCL inside the captured decode step); NCCL / gloo twin otherwise
+            z = comm.gather_cols(z) if (comm is not None and self.native and z.shape[0] <= 1024) else gather_cols(z, self.tp)
         if self._banned_ids is not None:   # placeholder tokens (image slots) are inputs only: never sampled
             z.index_fill_(1, self._banned_ids, -1e30)
         return z
@@ -475,8 +478,11 @@ class GenerationEngine:
             self._prefill_forward(PackedBatch(ids, pos, cu, 1), slots, torch.zeros(1, dtype=torch.int64, device=dev))
 
     def _agree(self, tok, lp):
-        """All tp ranks must take the same scheduling decisions: rank 0's samples win."""
-        if self.tpw > 1:
+        """All tp ranks must take the same scheduling decisions. After the logits gather every rank holds bit-identical
+        logits (the gather copies, the all-reduce GEMMs sum in a fixed rank order) and the sampler's random stream is keyed
+        by (seed, request, position), so every rank draws the same token without talking to the others. The broadcast of
+        rank 0's samples is kept as an option (``RLB_TP_AGREE=1``) for back ends whose reductions are not bit-reproducible."""
+        if self.tpw > 1 and os.environ.get("RLB_TP_AGREE", "0") == "1":
             import torch.distributed as dist
 
             src = dist.get_global_rank(self.tp.group, 0) if self.tp.group is not None else 0

@@ -70,6 +70,8 @@ def _bind():
     if not _bound:
         lib.rlb_gemm_tp_gather.argtypes = [_P, _LL, _P, _LL, _I, _P, _LL, _P, _I, _I, _I, _P, _P, _I, _I, _U, _I, _D, _P, _P]
         lib.rlb_gemm_tp_scatter.argtypes = [_P, _LL, _P, _LL, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _LL, _P, _P, _I, _I, _U, _P, _D, _P, _P]
+        lib.rlb_p2p_gather_cols.argtypes = [_P, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _D, _P, _P, _P]
+        lib.rlb_p2p_gather_cols.restype = C.c_int
         lib.rlb_gemm_tp_gather.restype = C.c_int
         lib.rlb_gemm_tp_scatter.restype = C.c_int
         _bound = True
@@ -89,10 +91,14 @@ class TPFusedComm:
         self.group = group
         self.wait_limit_s = wait_limit_s
         self.pushers = pushers
-        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256
+        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256, column-gather flags at 512
         self.rank, self.world = self.ctrl.rank, self.ctrl.world
         self._gflags = (_P * self.world)(*self.ctrl.peer_ptrs)
         self._sflags = (_P * self.world)(*[p + 256 for p in self.ctrl.peer_ptrs])
+        self._cflags = (_P * self.world)(*[p + 512 for p in self.ctrl.peer_ptrs])
+        self.stage_l = None
+        self.epoch_c_dev = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
+        self._c_scratch = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
         self.stage_a = None
         self.stage_c = None
         self.epoch_g = 0
@@ -157,6 +163,26 @@ class TPFusedComm:
             raise RuntimeError(f"rlb_gemm_tp_scatter failed with code {rc}")
         return out
 
+    def gather_cols(self, z_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """[rows, world * n] from every rank's [rows, n] column slice over peer memory (vocabulary-parallel logits at
+        decode time). No NCCL call and a device-resident epoch: the launch can be recorded in a CUDA graph."""
+        lib = _bind()
+        rows, n = z_local.shape
+        z_local = z_local.contiguous()
+        row_bytes = n * z_local.element_size()
+        assert row_bytes % 16 == 0, "column slices must be a multiple of 16 bytes wide"
+        st = self._ensure("stage_l", 2 * rows * row_bytes)
+        if out is None:
+            out = torch.empty((rows, self.world * n), dtype=z_local.dtype, device=z_local.device)
+        rc = lib.rlb_p2p_gather_cols(z_local.data_ptr(), st.table, self._cflags, out.data_ptr(), out.stride(0) * out.element_size(),
+                                     rows, row_bytes, self.rank, self.world, self.epoch_c_dev.data_ptr(), float(self.wait_limit_s),
+                                     self._c_scratch.data_ptr(), _L.status_word(z_local.device).data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+        _L.Counters.launches += 1
+        if rc:
+            raise RuntimeError(f"rlb_p2p_gather_cols failed with code {rc}")
+        return out
+
     @staticmethod
     def phase_times_us() -> list[float]:
         """Durations (us) of the phases of the last ``scatter_gemm`` launch on this GPU, measured by CTA 0:
@@ -171,7 +197,7 @@ class TPFusedComm:
         return [(buf[i + 1] - buf[i]) / 1e3 for i in range(4)]
 
     def close(self):
-        for b in (self.stage_a, self.stage_c, self.ctrl):
+        for b in (self.stage_a, self.stage_c, self.stage_l, self.ctrl):
             if b is not None:
                 b.close()
 

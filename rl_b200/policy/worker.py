@@ -320,7 +320,7 @@ class PolicyWorker:
             self.weight_synchronizer = PipelineWeightSynchronizer(self.model, self.model_cfg, st)
             engine_model, split_group = self.weight_synchronizer.serving_model, st.pp_group
         elif gen_tp != self.tp.world:
-            engine_model, pool_group, pool_stride = self._build_serving_layout(gen_tp)
+            engine_model, pool_group, pool_stride, split_group = self._build_serving_layout(gen_tp)
         elif st.cp > 1:
             split_group = st.cp_group   # context-parallel ranks hold the same prompts and the same (full) weights
         self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride,
@@ -355,7 +355,18 @@ class PolicyWorker:
         self.weight_synchronizer = WeightSynchronizer(self.model, self.model_cfg, gen_tp, group=None, serve_group=serve_group, serve_comm=comm)
         # ranks of one serving group that hold different data (more serving than training tensor parallelism) pool prompts
         pool = serve_group if gen_tp > self.tp.world else None
-        return self.weight_synchronizer.serving_model, pool, self.tp.world
+        # fewer serving than training tensor-parallel ranks: the tp / gen_tp engines inside one training group hold the
+        # same prompts and complete weights, so they split the prompts (rank j of every engine forms one split group)
+        split = None
+        ttp = self.tp.world
+        if gen_tp < ttp and world > 1:
+            me = dist.get_rank()
+            for g0 in range(0, world, ttp):   # collective: every rank creates every group
+                for j in range(gen_tp):
+                    grp = dist.new_group(ranks=[g0 + j + k * gen_tp for k in range(ttp // gen_tp)])
+                    if g0 <= me < g0 + ttp and (me - g0) % gen_tp == j:
+                        split = grp
+        return self.weight_synchronizer.serving_model, pool, self.tp.world, split
 
     # ------------------------------------------------------------------ modes
     def prepare_for_training(self, *a, **k):

@@ -82,5 +82,69 @@ def main():
         dist.destroy_process_group()
 
 
+def sweep_main(steps: int = 3, warmup: int = 2, models=("llama3.1-8b", "qwen3-32b"), json_path: str = "") -> int:
+    """The refit sweep of ``bench.py --config refit-sweep``: the trainer's layout on all ranks of the node (data parallel,
+    resident bf16 parameters) -> serving layouts TP 1 / 2 / 4 / 8, for the 8B and 32B dense architectures, in bf16 and
+    with FP8 block-128 quantisation. Rank 0 prints one JSON line whose ``rows`` hold, per case, the device time of one
+    refit (max over ranks), the bytes written per rank, the bytes that crossed NVLink and the effective rate."""
+    from rl_b200.engine.quantized import quantize_model
+    from rl_b200.ops import lib as _L
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _L.lib()
+    rows = []
+    for name in models:
+        cfg = preset(name)
+        train = build_model(cfg, device=f"cuda:{local}", dtype=torch.bfloat16, init=False, tp=TP(None, 0, 1))
+        for ts in (1, 2, 4, 8):
+            if ts > world or world % ts:
+                continue
+            ws = WeightSynchronizer(train, cfg, ts)
+            ms = _time(ws.sync_weights, iters=max(1, steps), warmup=max(1, warmup))
+            sent, recv = ws.plan.bytes_over_link(rank)
+            row = dict(model=name, world=world, train_layout=f"dp{world} (resident parameters)", serve_tp=ts, precision="bf16",
+                       refit_ms=round(ms, 3), bytes_written_per_rank=int(ws.last_bytes), nvlink_bytes_per_rank=int(sent + recv),
+                       write_gbs=round(ws.last_bytes / ms / 1e6, 1),
+                       colocated_handoff_ms=0.0 if ts == 1 else None)
+            rows.append(row)
+            # FP8 block-128: the serving copy is quantised as it is refreshed
+            fused = getattr(ws, "sync_weights_fp8", None)
+            if fused is not None:
+                ms8 = _time(fused, iters=max(1, steps), warmup=max(1, warmup))
+                how = "one kernel: bf16 tile -> amax -> e4m3 + scale into the serving arena"
+            else:
+                def two_pass():
+                    ws.sync_weights()
+                    quantize_model(ws.serving_model, "fp8")
+                ms8 = _time(two_pass, iters=max(1, steps), warmup=max(1, warmup))
+                how = "two passes: bf16 re-shard copy, then block-128 quantisation of the serving copy"
+            rows.append(dict(row, precision="fp8-block128", refit_ms=round(ms8, 3), write_gbs=None, how=how,
+                             read_gbs=round(ws.last_bytes / ms8 / 1e6, 1)))
+            ws.close()
+            del ws
+            torch.cuda.empty_cache()
+        del train
+        torch.cuda.empty_cache()
+    status = _L.check_status()
+    if rank == 0:
+        out = dict(metric="refit_seconds (trainer layout -> serving layout, device time, max over ranks)", unit="ms", n_gpus=world,
+                   steps=steps, warmup=warmup, config=dict(name="refit-sweep"), rows=rows, status=status, impl="ours",
+                   note="data-parallel training keeps complete bf16 parameters on every rank, so every serving shard is cut from the "
+                        "rank's own copy: no byte crosses NVLink and the rate is local HBM traffic")
+        print(json.dumps(out), flush=True)
+        if json_path:
+            with open(json_path, "w") as f:
+                json.dump(out, f, indent=1)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 if __name__ == "__main__":
     main()

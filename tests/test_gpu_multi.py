@@ -1,5 +1,7 @@
-"""Two-GPU tests (skipped on a single GPU): the fused peer-memory optimizer step against its NCCL twin, and the P2P
-all-gather. Ranks are child processes; NVLS is disabled for NCCL so that a failing rank cannot disturb its peer."""
+"""Multi-GPU tests on 2 and 4 GPUs (each skipped where the box has fewer): the fused peer-memory optimizer step, the
+tensor-parallel GEMM + collective kernels, the peer-memory logits gather, the refit re-shard kernel and the expert-parallel
+dispatch, each against its NCCL twin. Ranks are child processes; NVLS is disabled for NCCL so that a failing rank cannot
+disturb its peers."""
 
 import os
 import socket
@@ -34,7 +36,7 @@ def _worker(rank, world, port, fused):
                      num_attention_heads=4, num_key_value_heads=2, head_dim=128)
     results = {}
     for mode in ("fused", "nccl"):
-        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=8, train_micro_batch_size=4, max_total_sequence_length=128,
+        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=4 * world, train_micro_batch_size=4, max_total_sequence_length=128,
                               fused_optimizer=(mode == "fused"), max_grad_norm=0.5,
                               optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.1))),
                          model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, seed=11)
@@ -44,7 +46,7 @@ def _worker(rank, world, port, fused):
         data = BatchedDataDict(input_ids=ids, input_lengths=torch.full((4,), 64), token_mask=torch.ones(4, 64), sample_mask=torch.ones(4))
         norms = []
         for _ in range(3):
-            out = p.train(data, NLLLossFn(), gbs=8, mbs=4)
+            out = p.train(data, NLLLossFn(), gbs=4 * world, mbs=4)
             norms.append(float(out["grad_norm"][0]))
         torch.cuda.synchronize()
         assert check_status() == 0
@@ -63,9 +65,15 @@ def _worker(rank, world, port, fused):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_optimizer_matches_nccl(native_lib):
-    mp.spawn(_worker, args=(2, _free_port(), True), nprocs=2, join=True)
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_optimizer_matches_nccl(native_lib, world):
+    _need(world)
+    mp.spawn(_worker, args=(world, _free_port(), True), nprocs=world, join=True)
 
 
 def _tp_kernel_worker(rank, world, port):
@@ -128,14 +136,25 @@ def _tp_kernel_worker(rank, world, port):
         other = out3.clone()
         dist.broadcast(other, src=0)
         assert torch.equal(out3, other)
+    # column gather over peer memory (vocabulary-parallel logits), fp32 and bf16, repeated calls (device-resident epoch,
+    # alternating staging halves) and a changing row count
+    for it, (rows, n, dt) in enumerate([(48, 1024, torch.float32), (48, 1024, torch.float32), (64, 520, torch.bfloat16), (5, 1024, torch.float32)]):
+        z = (torch.randn(rows, n, generator=g, device=dev) + rank).to(dt)
+        full = comm.gather_cols(z)
+        parts = [torch.empty_like(z) for _ in range(world)]
+        dist.all_gather(parts, z)
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        assert torch.equal(full, torch.cat(parts, dim=1)), ("gather_cols", it)
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_tensor_parallel_gemms(native_lib):
-    mp.spawn(_tp_kernel_worker, args=(2, _free_port()), nprocs=2, join=True)
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_tensor_parallel_gemms(native_lib, world):
+    _need(world)
+    mp.spawn(_tp_kernel_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 def _tp_train_worker(rank, world, port):
@@ -148,8 +167,8 @@ def _tp_train_worker(rank, world, port):
     from rl_b200.ops.lib import check_status
     from rl_b200.policy.worker import PolicyWorker
 
-    mc = ModelConfig(model_type="llama", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
-                     num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    mc = ModelConfig(model_type="llama", vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
+                     num_attention_heads=8, num_key_value_heads=4, head_dim=128)
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(1, 4096, (8, 96), generator=g)
     data = BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([96, 80, 64, 96, 33, 70, 96, 51]), token_mask=torch.ones(8, 96),
@@ -157,7 +176,7 @@ def _tp_train_worker(rank, world, port):
     res = {}
     for mode in ("fused", "nccl"):
         p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=8, train_micro_batch_size=4, max_total_sequence_length=128,
-                              fused_tensor_parallel=(mode == "fused"), max_grad_norm=1.0, parallel=dict(tensor_parallel_size=2),
+                              fused_tensor_parallel=(mode == "fused"), max_grad_norm=1.0, parallel=dict(tensor_parallel_size=world),
                               optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.0)),
                               generation=dict(max_new_tokens=16, temperature=1.0, stop_token_ids=[], kv_cache_tokens=4096, block_size=16,
                                               max_running=16)),
@@ -188,9 +207,10 @@ def _tp_train_worker(rank, world, port):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tensor_parallel_worker_fused_vs_nccl(native_lib):
-    mp.spawn(_tp_train_worker, args=(2, _free_port()), nprocs=2, join=True)
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_worker_fused_vs_nccl(native_lib, world):
+    _need(world)
+    mp.spawn(_tp_train_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 def _refit_worker(rank, world, port):
@@ -202,10 +222,11 @@ def _refit_worker(rank, world, port):
     from rl_b200.parallel.tensor import TP
     from rl_b200.refit.synchronizer import WeightSynchronizer
 
-    mc = ModelConfig(model_type="qwen3", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
-                     num_attention_heads=4, num_key_value_heads=2, head_dim=128, qk_norm=True, tie_word_embeddings=False)
+    mc = ModelConfig(model_type="qwen3", vocab_size=4096, hidden_size=512, intermediate_size=1536, num_hidden_layers=2,
+                     num_attention_heads=8, num_key_value_heads=4, head_dim=128, qk_norm=True, tie_word_embeddings=False)
     dev = f"cuda:{rank}"
-    for tp_train, tp_serve in ((2, 1), (1, 2)):
+    combos = ((2, 1), (1, 2)) if world == 2 else ((4, 1), (1, 4), (2, 4), (4, 2), (1, 2))
+    for tp_train, tp_serve in combos:
         tp = TP(None, rank % tp_train, tp_train)
         train = build_model(mc, device=dev, dtype=torch.bfloat16, seed=21, tp=tp)
         ws = WeightSynchronizer(train, mc, tp_serve)
@@ -232,9 +253,10 @@ def _refit_worker(rank, world, port):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_refit_reshard_kernel_matches_collective_twin(native_lib):
-    mp.spawn(_refit_worker, args=(2, _free_port()), nprocs=2, join=True)
+@pytest.mark.parametrize("world", [2, 4])
+def test_refit_reshard_kernel_matches_collective_twin(native_lib, world):
+    _need(world)
+    mp.spawn(_refit_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 def _ep_worker(rank, world, port):
@@ -255,15 +277,15 @@ def _ep_worker(rank, world, port):
     data = BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([96, 70, 64, 33]), token_mask=torch.ones(4, 96), sample_mask=torch.ones(4))
     res = {}
     for mode in ("fused", "nccl"):
-        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=8, train_micro_batch_size=2, max_total_sequence_length=128,
-                              max_grad_norm=1.0, parallel=dict(expert_parallel_size=2), logprob_batch_size=4,
+        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=4 * world, train_micro_batch_size=2, max_total_sequence_length=128,
+                              max_grad_norm=1.0, parallel=dict(expert_parallel_size=world), logprob_batch_size=4,
                               optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.0))),
                          model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, seed=3)
         if mode == "nccl":
             p.ep.comm = None
         assert (p.ep.comm is not None) == (mode == "fused")
         lp0 = p.get_logprobs(data)["logprobs"]
-        outs = [p.train(data, NLLLossFn(), gbs=8, mbs=2) for _ in range(2)]
+        outs = [p.train(data, NLLLossFn(), gbs=4 * world, mbs=2) for _ in range(2)]
         lp1 = p.get_logprobs(data)["logprobs"]
         torch.cuda.synchronize()
         assert check_status() == 0
@@ -277,6 +299,7 @@ def _ep_worker(rank, world, port):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_fused_dispatch_vs_nccl(native_lib):
-    mp.spawn(_ep_worker, args=(2, _free_port()), nprocs=2, join=True)
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_fused_dispatch_vs_nccl(native_lib, world):
+    _need(world)
+    mp.spawn(_ep_worker, args=(world, _free_port()), nprocs=world, join=True)

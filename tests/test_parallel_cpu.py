@@ -376,8 +376,13 @@ def _reshard_gen_worker(rank, world, tp_train, tp_serve):
     outs = []
     for it in range(2):
         refit_policy_generation(w, gen)
+        before = gen.engine.stats["generated_tokens"]
         outs.append(gen.generate(data, greedy=True)["output_ids"].tolist())
         gen.finish_generation()
+        if tp_serve < tp_train:
+            # the engines inside one training group hold the same prompts and split them: this rank generated its share only
+            mine = len(range(rank % tp_train // tp_serve, 3, tp_train // tp_serve))
+            assert gen.engine.stats["generated_tokens"] - before == mine * 8, (rank, mine)
         if it == 0:  # change the trainer's weights: the next refit must carry them over
             with torch.no_grad():
                 w.flat.flat.mul_(1.25)

@@ -116,7 +116,9 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            # one sample per second: every query takes driver locks that the decode phase's launches contend for, and a
+            # 5 Hz poll was measured to stretch generation by ~15 %
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "1000",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -290,6 +292,8 @@ def main() -> int:
     sampler = ClockSampler(local_rank)
     sampler.start()
     L.Counters.reset()
+    for k in gen.engine.stats:
+        gen.engine.stats[k] = 0
     barrier_sync()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
@@ -299,6 +303,7 @@ def main() -> int:
     barrier_sync()
     dev_ms = t0.elapsed_time(t1)
     launches = L.Counters.launches
+    eng = dict(gen.engine.stats)
     clocks = sampler.stop()
 
     # ---------------------------------------------------------------- end-to-end region (public API)
@@ -365,6 +370,9 @@ def main() -> int:
             "generation_ms_per_rank": {"min": round(float(mn[PH]) / args.steps, 2), "max": round(float(mx[PH]) / args.steps, 2)},
             "optimizer_path": "fused_peer" if getattr(policy, "fused_comm", None) is not None and world // args.tp > 1 else ("local" if world // args.tp == 1 else "nccl"),
             "status": int(st_all[0]),
+            "engine_rank0": {"decode_ms_per_step": round(1e3 * eng["decode_s"] / max(1, eng["decode_steps"]), 3),
+                             "decode_steps": int(eng["decode_steps"]) // args.steps, "prefill_ms": round(1e3 * eng["prefill_s"] / args.steps, 1),
+                             "decode_window": gen.engine.decode_window, "captured_graphs": len(gen.engine._graphs)},
             "clocks": clocks,
             "gpu_launches": int(float(mx[3])),
             "impl": "ours",

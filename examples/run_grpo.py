@@ -23,6 +23,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def main(argv=None):
     cfg, rank, world, device, tokenizer = bootstrap(os.path.join(HERE, "configs", "grpo_math_1B.yaml"), argv)
     dataset, val_dataset, task_to_env, val_task_to_env = setup_response_data(tokenizer, cfg["data"], cfg.get("env"))
+    from rl_b200.distributed.roles import current_layout
+
+    layout = current_layout()
+    if layout is not None and layout.role != "colocated":
+        # split job (policy.generation.colocated.enabled: false): generation ranks serve, training ranks train, concurrently
+        return _run_split(cfg, layout, tokenizer, dataset, task_to_env, val_task_to_env)
     policy, generation, loader, val_loader, loss_fn, logger, checkpointer, save_state, cfg = grpo.setup(
         cfg, tokenizer, dataset, val_dataset, task_to_env, val_task_to_env, model_cfg=model_cfg_for_tokenizer(cfg, tokenizer))
     try:
@@ -33,6 +39,25 @@ def main(argv=None):
         else:
             grpo.grpo_train(policy, generation, loader, val_loader, tokenizer, loss_fn, task_to_env, val_task_to_env, logger,
                             checkpointer, save_state, cfg)
+    finally:
+        for env in {id(e): e for e in list(task_to_env.values()) + list(val_task_to_env.values())}.values():
+            env.shutdown()
+        shutdown_distributed()
+
+
+def _run_split(cfg, layout, tokenizer, dataset, task_to_env, val_task_to_env):
+    from rl_b200.algorithms import noncolocated as nc
+
+    mc = model_cfg_for_tokenizer(cfg, tokenizer)
+    try:
+        if layout.role == "generation":
+            generation = nc.build_generation_rank(cfg, tokenizer, mc, layout.device)
+            stats = nc.generation_service(layout, cfg, generation, dataset, tokenizer, task_to_env)
+            print(f"[generation rank {layout.role_rank}] {stats}", flush=True)
+        else:
+            policy, _, _, _, loss_fn, logger, checkpointer, save_state, cfg = grpo.setup(
+                cfg, tokenizer, dataset, None, task_to_env, val_task_to_env, model_cfg=mc, build_generation=False)
+            nc.noncolocated_grpo_train(policy, layout, loss_fn, logger, checkpointer, save_state, cfg, tokenizer)
     finally:
         for env in {id(e): e for e in list(task_to_env.values()) + list(val_task_to_env.values())}.values():
             env.shutdown()

@@ -3,9 +3,10 @@ them, an age bound on what may be trained on, and importance-sampling correction
 
 Semantics follow nemo_rl/algorithms/grpo.py:4074-5462 and async_utils/replay_buffer.py:40: trajectories are produced
 for a *target* training step, at most ``max_trajectory_age_steps`` versions behind the weights that train on them;
-samples older than that are dropped; the buffer state is checkpointable. In this SPMD runtime generation and training
-share the GPUs, so collection runs ahead in bursts between optimizer steps instead of on separate devices; the data
-path, staleness accounting and loss are the same.
+samples older than that are dropped; the buffer state is checkpointable. This module is the COLOCATED form: generation
+and training share the GPUs, so collection runs ahead in bursts between optimizer steps; the data path, staleness
+accounting and loss are those of the split form. With ``policy.generation.colocated.enabled: false`` the job is split into
+training and generation ranks that run at the same time: ``rl_b200/algorithms/noncolocated.py``.
 """
 
 from __future__ import annotations

@@ -164,7 +164,7 @@ def default_save_state() -> dict:
 
 
 def setup(master_config: dict, tokenizer, dataset, val_dataset, task_to_env: dict, val_task_to_env: Optional[dict] = None,
-          model_cfg=None, policy=None):
+          model_cfg=None, policy=None, build_generation: bool = True):
     """Builds everything ``grpo_train`` needs: policy worker (+ colocated engine), loaders, loss, logger, checkpointer.
 
     Returns ``(policy, generation, dataloader, val_dataloader, loss_fn, logger, checkpointer, save_state, master_config)``.
@@ -206,7 +206,8 @@ def setup(master_config: dict, tokenizer, dataset, val_dataset, task_to_env: dic
                               weights_path=None)
         if resume and resume.get("weights"):
             policy.load_checkpoint(resume["weights"], resume.get("optimizer"))
-    generation = policy.build_generation(pcfg.get("generation"))
+    # training ranks of a split job have no engine: generation runs on other ranks (rl_b200/algorithms/noncolocated.py)
+    generation = policy.build_generation(pcfg.get("generation")) if build_generation else None
     loss_fn = ClippedPGLossFn(cfg.get("loss_fn"))
     return policy, generation, loader, val_loader, loss_fn, logger, checkpointer, save_state, cfg
 

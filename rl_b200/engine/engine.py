@@ -336,6 +336,13 @@ class GenerationEngine:
 
     BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
     MAX_STOP_IDS = 256   # stop token ids checked on the device after every decode step
+    BASE_SEED = 0x5EED   # constant sampler seed; what varies per call and per request travels in the row keys
+
+    @staticmethod
+    def _row_key(r, sp) -> int:
+        """Random-stream key of a request's next token: call seed (20 bits) | request uid | position (20 bits). The
+        decode kernels add one per generated token, so consecutive tokens of a request get consecutive keys."""
+        return (((int(sp.seed) * 0x9E3779B1) & 0xFFFFF) << 43) ^ ((int(r.uid) << 20) | len(r.out_tokens))
 
     def __init__(self, model: CausalLM, *, block_size: int = 64, num_blocks: Optional[int] = None,
                  kv_cache_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.5, max_running: int = 512,
@@ -390,6 +397,7 @@ class GenerationEngine:
         self._static: Optional[dict] = None
         self._step_counter = 0
         self._n_stop = 0
+        self.window_hook = None   # optional callable run at every host visit of the generate loop
         self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
         # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
@@ -620,7 +628,7 @@ class GenerationEngine:
     def _decode_body(self, st, B, sp: SamplingParams, num_splits, scratch):
         logits = self._decode_forward(st["ids"][:B], st["positions"][:B], st["slots"][:B], st["block_table"][:B],
                                       st["seq_lens"][:B], num_splits, scratch)
-        E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=sp.seed,
+        E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=self.BASE_SEED,
                  row_keys=st["keys"][:B], out=(st["tok"][:B], st["lp"][:B]))
         self._agree(st["tok"][:B], st["lp"][:B])
         if self.native:
@@ -637,10 +645,12 @@ class GenerationEngine:
             logits = self._decode_forward(st["ids"][:n].long(), st["positions"][:n], st["slots"][:n], st["block_table"][:n],
                                           st["seq_lens"][:n], 1, None)
             tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy,
-                               seed=sp.seed, row_keys=st["keys"][:n])
+                               seed=self.BASE_SEED, row_keys=st["keys"][:n])
             tok, lp = self._agree(tok, lp)
             return tok[:n], lp[:n]
-        key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, sp.seed, self._n_stop)
+        # the per-call seed is not part of the key: it reaches the sampler through the row keys (device memory), so one
+        # captured graph serves every generate call with the same sampling parameters
+        key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, self._n_stop)
         if self.use_graphs:
             g = self._graphs.get(key)
             if g is None:
@@ -691,7 +701,7 @@ class GenerationEngine:
         for j, sid in enumerate(decode):
             r = reqs[sid]
             ids_np[j] = r.out_tokens[-1]
-            keys_np[j] = (r.uid << 20) | len(r.out_tokens)
+            keys_np[j] = self._row_key(r, sp)
             rem_np[j] = r.max_new - len(r.out_tokens)
             max_rem = max(max_rem, int(rem_np[j]))
         hb["active"][:n] = 1
@@ -808,6 +818,8 @@ class GenerationEngine:
         ep = getattr(self.model, "ep", None)
         lock = ep is not None and ep.world > 1 and self.cfg.is_moe
         while True:
+            if self.window_hook is not None:   # between two host visits (e.g. an in-flight weight update)
+                self.window_hook()
             idle = self.sched.idle()
             if lock:
                 if not self._any_rank(ep, not idle):
@@ -843,7 +855,7 @@ class GenerationEngine:
                 for j, sid in enumerate(decode):
                     r = reqs[sid]
                     ids_np[j] = r.out_tokens[-1]
-                    keys_np[j] = (r.uid << 20) | len(r.out_tokens)
+                    keys_np[j] = self._row_key(r, sp)
                 st["blob"].copy_(st["host_blob"], non_blocking=True)
                 self._step_counter += 1
                 tok, lp = self._run_decode(n, sp, max_ctx)
@@ -893,9 +905,9 @@ class GenerationEngine:
                 new = list(prefill) + list(shared)
                 rows = torch.stack([last_logits[sid] if sid in last_logits else last_logits[reqs[sid].share_with] for sid in new])
                 self._step_counter += 1
-                keys_new = torch.tensor([(reqs[sid].uid << 20) | len(reqs[sid].out_tokens) for sid in new], dtype=torch.int64, device=dev)
+                keys_new = torch.tensor([self._row_key(reqs[sid], sp) for sid in new], dtype=torch.int64, device=dev)
                 tok, lp = E.sample(rows.contiguous(), temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p,
-                                   greedy=sp.greedy, seed=sp.seed, row_keys=keys_new)
+                                   greedy=sp.greedy, seed=self.BASE_SEED, row_keys=keys_new)
                 tok, lp = self._agree(tok, lp)
                 tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]

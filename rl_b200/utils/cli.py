@@ -18,7 +18,11 @@ def bootstrap(default_config: str, argv: Optional[list[str]] = None, backend: Op
     for k, v in (cfg.get("env_vars") or {}).items():  # YAML env_vars override the shell (docs/design-docs/env-vars.md:5-31)
         os.environ[str(k)] = str(v)
     validate_recipe(cfg, quiet=int(os.environ.get("RANK", "0")) != 0)
-    rank, world, device = init_distributed(backend or (cfg.get("cluster") or {}).get("backend"))
+    from rl_b200.distributed import roles
+
+    layout = roles.init_roles(cfg, backend or (cfg.get("cluster") or {}).get("backend"))
+    roles.set_current_layout(layout)
+    rank, world, device = layout.role_rank, layout.role_world, layout.device   # coordinates inside this rank's own set
     if rank == 0:
         print(f"Loaded configuration from {path or default_config}")
         pprint.pprint(cfg, width=140, compact=True)

@@ -64,6 +64,9 @@ def parse():
     ap.add_argument("--gen-tp", type=int, default=None, help="tensor-parallel size of the generation engines (0: the trainer's)")
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size (0: all GPUs)")
     ap.add_argument("--logprob-mb-tokens", type=int, default=None)
+    ap.add_argument("--sharding", default="optimizer", choices=["optimizer", "full"],
+                    help="data-parallel sharding: optimizer state only (resident parameters, the headline) or full (ZeRO-3: "
+                         "parameters and gradients sharded too, gathered per layer)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (makes the run invalid as a benchmark)")
     ap.add_argument("--train-mb-tokens", type=int, default=None, help="tokens per training micro-batch (the same at every N)")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -220,7 +223,7 @@ def main() -> int:
         "loss_fn": dict(reference_policy_kl_penalty=0.01, ratio_clip_min=0.2, ratio_clip_max=0.2),
         "policy": dict(
             model_name=None, precision="bfloat16", train_global_batch_size=seqs_per_gpu * world, train_micro_batch_size=4,
-            parallel=dict(tensor_parallel_size=args.tp, sequence_parallel=args.tp > 1,
+            parallel=dict(tensor_parallel_size=args.tp, sequence_parallel=args.tp > 1, data_parallel_sharding=args.sharding,
                           expert_parallel_size=(world if args.ep == 0 else args.ep) if mc.is_moe else 1),
             logprob_batch_size=8, max_total_sequence_length=max_len, max_grad_norm=1.0,
             activation_checkpointing=(args.act_ckpt == "on"), grad_dtype="float32",
@@ -360,7 +363,7 @@ def main() -> int:
                 "parallelism": (f"ep{world if args.ep == 0 else args.ep} experts, dense parts dp{world} (fused peer-memory dispatch / combine, generation colocated)" if mc.is_moe else
                                 f"dp{world} (resident bf16 params, optimizer state sharded {world}-way, generation TP1 colocated)" if args.tp == 1 else
                                 f"tp{args.tp} x dp{world // args.tp} (sequence parallel, fused peer-memory TP kernels, generation TP{gen_tp} x {world // gen_tp} engines colocated)"),
-                "train_mb_tokens": mb_tokens,
+                "train_mb_tokens": mb_tokens, "data_parallel_sharding": args.sharding,
                 "l2": "inputs larger than L2 (16 GB of weights streamed every pass)",
             },
             "tokens_per_sec_per_gpu": round(value / world, 1),

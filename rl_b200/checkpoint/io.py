@@ -37,6 +37,21 @@ def save_weights(worker, path: str, fmt: str = "safetensors") -> None:
     rank, world = (worker.rank, worker.world)
     fmt = (fmt or "safetensors").lower()
     st = get_state()
+    if getattr(worker, "sharder", None) is not None:
+        # fully sharded parameters: tensors are gathered unit by unit; rank 0 writes them out (HF safetensors)
+        from rl_b200.parallel.fsdp import iter_hf_tensors_sharded
+
+        sd = {}
+        for n, t in iter_hf_tensors_sharded(worker.model, worker.sharder):
+            if rank == 0:
+                sd[n] = t.detach().to("cpu", copy=True)
+        if rank == 0:
+            from safetensors.torch import save_file
+
+            os.makedirs(path, exist_ok=True)
+            save_file(sd, os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
+            worker.model_cfg.save_pretrained(path)
+        return
     if getattr(worker, "lora_cfg", None) is not None:
         # LoRA: the frozen base goes out as a plain HF checkpoint, the adapters next to it in the PEFT file layout
         if rank == 0:
@@ -73,6 +88,24 @@ def load_weights(worker, path: str) -> None:
     from rl_b200.models.hf_io import _SafetensorsDir, load_hf_tensors
 
     rank, world = (worker.rank, worker.world)
+    if getattr(worker, "sharder", None) is not None:
+        from rl_b200.models.hf_io import _SafetensorsDir, _model_map
+
+        reader = _SafetensorsDir(path)
+        by_param = {}
+        for hf, loc, rows, e, hs in _model_map(worker.model):
+            by_param.setdefault(loc, []).append((hf, rows))
+
+        def get(name):   # full local parameter assembled from its HF pieces
+            parts = by_param.get(name)
+            if not parts:
+                return None
+            if len(parts) == 1 and parts[0][1] is None:
+                return reader.get(parts[0][0])
+            return torch.cat([reader.get(hf) for hf, _ in sorted(parts, key=lambda x: x[1][0])], dim=0)
+
+        worker.sharder.load_full_params(get)
+        return
     from rl_b200.checkpoint.dcp_state import is_per_parameter_checkpoint
 
     if is_per_parameter_checkpoint(path):

@@ -275,6 +275,30 @@ __global__ void __launch_bounds__(512, 1) p2p_gather_cols_kernel(GatherColsArgs 
   }
 }
 
+// Pull gather for fully sharded parameters: dst[r * n .. (r + 1) * n) = peer r's shard[off .. off + n) for every rank r.
+// An ordinary (non-cooperative) launch of a few CTAs, meant for a side stream: the peers' shards do not change while a
+// forward / backward pass runs, so no flag is needed, and the copy shares the GPU with the GEMMs of the previous unit
+// instead of waiting for all SMs like the cooperative kernels above. Plain peer loads, four vectors in flight per thread.
+__global__ void __launch_bounds__(512) p2p_pull_kernel(PeerTable t, long long src_off16, uint4* __restrict__ dst, long long n16,
+                                                       int rank, int world) {
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int p = 0; p < world; ++p) {
+    const int r = (rank + p) % world;   // the local slice first, then the peers, staggered by rank
+    const uint4* src = reinterpret_cast<const uint4*>(t.param[r]) + src_off16;
+    uint4* out = dst + static_cast<long long>(r) * n16;
+    for (long long i0 = tid; i0 < n16; i0 += 4 * nthreads) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * nthreads < n16) v[u] = src[i0 + u * nthreads];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * nthreads < n16) out[i0 + u * nthreads] = v[u];
+    }
+  }
+}
+
 int coop_grid(const void* kernel, int threads) {
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
@@ -405,4 +429,21 @@ RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void
   void* args[] = {&a};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_gather_cols_kernel), dim3(grid),
                                                       dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
+}
+
+// dst[r * bytes_per_rank ...] = (shard_ptrs[r] + src_offset_bytes)[0 .. bytes_per_rank) for r < world, with `ctas` CTAs
+// (0: 24). Offsets and sizes are multiples of 16 bytes. No synchronisation between ranks: the caller guarantees that the
+// peers' shards are stable for the duration of the call (see p2p_pull_kernel).
+RLB_API int rlb_p2p_pull(void* const* shard_ptrs, long long src_offset_bytes, void* dst, long long bytes_per_rank, int rank,
+                         int world, int ctas, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (src_offset_bytes % 16) || (bytes_per_rank % 16) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return -2;
+  if (bytes_per_rank == 0) return 0;
+  PeerTable t;
+  memset(&t, 0, sizeof(t));
+  for (int r = 0; r < world; ++r) t.param[r] = static_cast<__nv_bfloat16*>(shard_ptrs[r]);
+  if (ctas <= 0) ctas = 24;
+  p2p_pull_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, src_offset_bytes / 16, static_cast<uint4*>(dst),
+                                                                      bytes_per_rank / 16, rank, world);
+  return static_cast<int>(cudaGetLastError());
 }

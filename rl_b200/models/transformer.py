@@ -358,6 +358,9 @@ class CausalLM(nn.Module):
         if init:
             self.reset_parameters(seed)
         self.flat: Optional[FlatParams] = None
+        # fully sharded parameters (rl_b200/parallel/fsdp.py): when set, every unit of the model (embedding, each layer,
+        # the head) runs through ``sharder.run`` which gathers its parameters for the duration of the call
+        self.sharder = None
 
     # ------------------------------------------------------------------ parameters
     _TP_SHARDED = ("qkv_proj", "qkv_bias", "o_proj", "gate_up_proj", "down_proj", "lm_head")
@@ -453,6 +456,8 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def embed(self, batch: PackedBatch) -> torch.Tensor:
+        if self.sharder is not None:
+            return self.sharder.run("embed", lambda: F.embedding(batch.input_ids, self.embed_tokens))
         if self.tp.world > 1 and self.tp.sequence_parallel:
             # each rank embeds its own rows: like every replicated parameter under sequence parallelism, the table's
             # gradient is a partial sum that the worker all-reduces over the tensor-parallel group
@@ -465,6 +470,10 @@ class CausalLM(nn.Module):
 
     def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         inv_freq = self.inv_freq
+        if self.sharder is not None:
+            for i, layer in enumerate(self.layers):
+                h = self.sharder.run(f"layer{i}", lambda x, L=layer: L(x, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen), h)
+            return h
         for layer in self.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = ckpt.checkpoint(layer, h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen, use_reentrant=False)
@@ -477,10 +486,15 @@ class CausalLM(nn.Module):
         the next stage. Rows are this rank's sequence-parallel shard when ``tp.sequence_parallel``."""
         h = self.embed(batch) if self.first_stage else h_in
         h = self.run_layers(h, batch)
+        if self.sharder is not None:
+            return self.sharder.run("head", lambda x: F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), h)
         return F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.last_stage else h
 
     def logits(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """[T, V] logits in fp32 (small models, tests and the distillation / top-k paths)."""
+        if self.sharder is not None:
+            h = self.run_layers(self.embed(batch), batch)
+            return self.sharder.run("head", lambda x: F.linear(F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), self.output_weight).float(), h)
         h = self.hidden_states(batch, h_in)
         if self.tp.world == 1:
             return F.linear(h, self.output_weight).float()
@@ -525,6 +539,13 @@ class CausalLM(nn.Module):
                             h_in: Optional[torch.Tensor] = None):
         """Log-probability of each token given its prefix ([T] fp32, entropy [T] or None), through the fused projection +
         log-softmax (vocabulary-parallel under tensor parallelism)."""
+        if self.sharder is not None:
+            # the final norm and the output projection belong to one unit: they run inside one gather
+            h = self.run_layers(self.embed(batch), batch)
+            eps = self.cfg.rms_norm_eps
+            if want_entropy:
+                return self.sharder.run("head", lambda x: self.logprobs_from_hidden(F.rmsnorm(x, self.norm, eps), batch, temperature, True), h)
+            return self.sharder.run("head", lambda x: self.logprobs_from_hidden(F.rmsnorm(x, self.norm, eps), batch, temperature, False)[0], h), None
         return self.logprobs_from_hidden(self.hidden_states(batch, h_in), batch, temperature, want_entropy)
 
     def next_token_logprobs_filtered(self, batch: PackedBatch, top_k: Optional[int], top_p: float, temperature: float = 1.0,
@@ -535,8 +556,9 @@ class CausalLM(nn.Module):
         with tensor parallelism the vocabulary slices of a chunk are gathered first."""
         from rl_b200.algorithms.sampling_utils import apply_top_k_top_p
 
-        if self.cp is not None or (self.tp.world > 1 and self.tp.sequence_parallel):
-            raise NotImplementedError("top-k / top-p training log-probabilities need full rows on every rank (no sequence / context parallelism)")
+        if self.cp is not None or (self.tp.world > 1 and self.tp.sequence_parallel) or self.sharder is not None:
+            raise NotImplementedError("top-k / top-p training log-probabilities need full rows and resident weights on every rank "
+                                      "(no sequence / context parallelism, no fully sharded parameters)")
         h = self.hidden_states(batch, h_in)
         ids = batch.input_ids.long()
         T = ids.shape[0]
@@ -564,6 +586,9 @@ class CausalLM(nn.Module):
 
     def values(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Scalar head output per token [T] (critic / reward model)."""
+        if self.sharder is not None:
+            h = self.run_layers(self.embed(batch), batch)
+            return self.sharder.run("head", lambda x: F.linear(F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), self.score).float()[:, 0], h)
         h = self.hidden_states(batch, h_in)
         v = F.linear(h, self.score).float()[:, 0]
         if self.cp is not None:

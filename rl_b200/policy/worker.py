@@ -173,6 +173,11 @@ class PolicyWorker:
                 if self.rank == 0:
                     print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
                 fused_comm = None
+        par_cfg = cfg.get("parallel") or {}
+        self.full_sharding = (par_cfg.get("data_parallel_sharding") or dtc.get("data_parallel_sharding") or "optimizer") == "full"
+        if self.full_sharding:
+            return self._init_fully_sharded(cfg, st, dp_group, dtype, init_optimizer, init_reference_model)
+        self.sharder = None
         self.fused_comm = fused_comm
         # expert-parallel MoE: expert weights differ between the ranks of an expert-parallel group, so they live in their
         # own flat buffer whose gradients are reduced (and optimizer state sharded) over the ranks holding the SAME experts
@@ -248,6 +253,44 @@ class PolicyWorker:
             self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
         self.timers: dict[str, float] = {}
 
+    # ------------------------------------------------------------------ fully sharded parameters (ZeRO-3)
+    def _init_fully_sharded(self, cfg, st, dp_group, dtype, init_optimizer: bool, init_reference_model: bool) -> None:
+        """``parallel.data_parallel_sharding: full``: parameters, gradients and optimizer state are all sharded over the
+        data-parallel ranks; units of the model are gathered on use (rl_b200/parallel/fsdp.py)."""
+        from rl_b200.parallel.fsdp import ParamSharder, ShardOptimizer
+
+        assert st.tp * st.pp * st.cp * st.ep == 1 and self.lora_cfg is None, "fully sharded parameters: data-parallel dense models"
+        self.fused_comm = None
+        self.sharder = ParamSharder(self.model, group=dp_group if self.world > 1 else "self",
+                                    wait_limit_s=float(cfg.get("peer_wait_limit_s", 20.0)))
+        self.model.sharder = self.sharder
+        self.flat = self.flat_e = self.flat_base = None
+        self.ref_flat = self.ref_flat_e = None
+        self.ref_shard = self.sharder.p_shard.clone() if init_reference_model else None
+        self._has_reference = bool(init_reference_model)
+        self.optimizer = self.optimizer_e = self.scheduler = None
+        if init_optimizer:
+            spec = cfg.get("optimizer") or {}
+            kw = dict(spec.get("kwargs") or {})
+            self.optimizer = ShardOptimizer(self.sharder, lr=float(kw.get("lr", 1e-5)), betas=tuple(kw.get("betas", (0.9, 0.999))),
+                                            eps=float(kw.get("eps", 1e-8)), weight_decay=float(kw.get("weight_decay", 0.01)),
+                                            max_grad_norm=cfg.get("max_grad_norm"))
+            self.scheduler = LRSchedule(self.optimizer, cfg.get("scheduler"))
+        if self.world > 1:
+            dist.barrier(group=dp_group)   # every shard is filled before anybody pulls from it
+        self._replicated_runs = []
+        self._tied_pp = False
+        self.pipeline = None
+        self.generation = None
+        self.temperature = 1.0
+        self.train_top_k, self.train_top_p = None, 1.0
+        gen_cfg = cfg.get("generation") or {}
+        if gen_cfg:
+            self.temperature = float(gen_cfg.get("temperature", 1.0) or 1.0)
+            self.train_top_k = int(gen_cfg["top_k"]) if gen_cfg.get("top_k") else None
+            self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
+        self.timers = {}
+
     # ------------------------------------------------------------------ model-parallel gradient bookkeeping
     def _configure_model_parallel_grads(self) -> None:
         """Tells the optimizer which flat ranges are replicated over the tensor-parallel group (their squared norm counts
@@ -282,7 +325,7 @@ class PolicyWorker:
     def _sync_replicated_grads(self) -> None:
         """Sequence parallelism: every tp rank saw only its rows, so gradients of replicated parameters are partial."""
         st = self.pstate
-        if self.flat.grad is None:
+        if self.flat is None or self.flat.grad is None:
             return
         if st.tp > 1 and st.sequence_parallel:
             self.flat.fold_autograd_grads()
@@ -310,7 +353,15 @@ class PolicyWorker:
         gen_tp = int(native_cfg.get("tensor_parallel_size") or self.tp.world)
         engine_model, pool_group, pool_stride, split_group = self.model, None, 1, None
         st = self.pstate
-        if st.pp > 1:
+        if getattr(self, "sharder", None) is not None:
+            # fully sharded trainer: the engine serves its own copy in the serving layout, rebuilt at every refit
+            from rl_b200.parallel.fsdp import ShardedServingSync
+
+            gen_tp = int(native_cfg.get("tensor_parallel_size") or 1)
+            serve_group, comm, pool_group = self._serving_groups(gen_tp)
+            self.weight_synchronizer = ShardedServingSync(self, gen_tp, serve_group, comm)
+            engine_model, pool_stride = self.weight_synchronizer.serving_model, 1
+        elif st.pp > 1:
             # every rank gets a serving copy of the whole model (the trainer's tensor-parallel layout), refreshed by packed
             # broadcasts over the pipeline group; the stages of one replica hold the same prompts and share the work
             from rl_b200.refit.packed_broadcast import PipelineWeightSynchronizer
@@ -329,6 +380,26 @@ class PolicyWorker:
         self.train_top_k = int(self.generation.cfg["top_k"]) if self.generation.cfg.get("top_k") else None
         self.train_top_p = float(self.generation.cfg.get("top_p") or 1.0)
         return self.generation
+
+    def _serving_groups(self, gen_tp: int):
+        """(serving tensor-parallel group, fused comm, pool group) for engines of ``gen_tp`` ranks cut from the job."""
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        serve_group, comm = None, None
+        if gen_tp > 1:
+            assert world % gen_tp == 0, "generation tensor-parallel size must divide the world size"
+            me = dist.get_rank()
+            for g0 in range(0, world, gen_tp):  # collective: every rank creates every group
+                grp = dist.new_group(ranks=list(range(g0, g0 + gen_tp)))
+                if g0 <= me < g0 + gen_tp:
+                    serve_group = grp
+            if self.device.type == "cuda" and self.cfg.get("fused_tensor_parallel", True):
+                try:
+                    from rl_b200.parallel.tensor import TPFusedComm
+
+                    comm = TPFusedComm(serve_group, wait_limit_s=float(self.cfg.get("peer_wait_limit_s", 10.0)))
+                except Exception as e:
+                    print(f"[policy] fused serving kernels unavailable ({type(e).__name__}: {e}); using NCCL")
+        return serve_group, comm, (serve_group if gen_tp > 1 else None)
 
     def _build_serving_layout(self, gen_tp: int):
         """The engine serves with a tensor-parallel size different from the trainer's: every rank gets a weight arena in
@@ -395,6 +466,11 @@ class PolicyWorker:
                 yield
             finally:
                 self.model.set_adapters(True)
+            return
+        if getattr(self, "sharder", None) is not None:
+            assert self.ref_shard is not None, "the worker was built without a reference model"
+            with self.sharder.use_shard(self.ref_shard):
+                yield
             return
         assert self.ref_flat is not None, "the worker was built without a reference model"
         pairs = [(self.flat, self.ref_flat)] + ([(self.flat_e, self.ref_flat_e)] if self.flat_e is not None else [])

@@ -227,7 +227,13 @@ def _refit_worker(rank, world, port):
     dev = f"cuda:{rank}"
     combos = ((2, 1), (1, 2)) if world == 2 else ((4, 1), (1, 4), (2, 4), (4, 2), (1, 2))
     for tp_train, tp_serve in combos:
-        tp = TP(None, rank % tp_train, tp_train)
+        tp_group = None
+        if 1 < tp_train < world:   # the trainer's tensor-parallel groups inside the job (collective: every rank makes every group)
+            for g0 in range(0, world, tp_train):
+                grp = dist.new_group(ranks=list(range(g0, g0 + tp_train)))
+                if g0 <= rank < g0 + tp_train:
+                    tp_group = grp
+        tp = TP(tp_group, rank % tp_train, tp_train)
         train = build_model(mc, device=dev, dtype=torch.bfloat16, seed=21, tp=tp)
         ws = WeightSynchronizer(train, mc, tp_serve)
         for it in range(2):
@@ -303,3 +309,110 @@ def _ep_worker(rank, world, port):
 def test_expert_parallel_fused_dispatch_vs_nccl(native_lib, world):
     _need(world)
     mp.spawn(_ep_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _split_job_worker(rank, world, port, steps):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      NCCL_NVLS_ENABLE="0")
+    from rl_b200.algorithms import grpo, noncolocated as nc
+    from rl_b200.data.datasets.synthetic import RandomTokenPromptDataset
+    from rl_b200.distributed.roles import init_roles
+    from rl_b200.environments.synthetic import HashParityEnv
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+
+    g = world // 2
+    cfg = {
+        "grpo": dict(num_prompts_per_step=4 * (world - g), num_generations_per_prompt=2, max_num_steps=steps, seed=3, val_period=0,
+                     async_grpo=dict(enabled=True, max_trajectory_age_steps=1, in_flight_weight_updates=True, generation_ranks=g)),
+        "loss_fn": dict(reference_policy_kl_penalty=0.0, use_importance_sampling_correction=True),
+        "policy": dict(model_name=None, precision="bfloat16", train_global_batch_size=8 * (world - g), train_micro_batch_size=4,
+                       max_total_sequence_length=96, optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-4, weight_decay=0.0)),
+                       generation=dict(max_new_tokens=24, temperature=1.0, stop_token_ids=[], kv_cache_tokens=8192, block_size=16, max_running=16)),
+        "checkpointing": dict(enabled=False), "logger": dict(log_dir=f"/tmp/rlb_split_logs_{os.getpid()}"), "data": dict(shuffle=False),
+    }
+    layout = init_roles(cfg)
+    mc = ModelConfig(model_type="llama", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    ds = RandomTokenPromptDataset(cfg["grpo"]["num_prompts_per_step"] * (steps + 2), 12, 24, mc.vocab_size, seed=1, task_name="synthetic")
+    env = {"synthetic": HashParityEnv()}
+    if layout.role == "generation":
+        gen = nc.build_generation_rank(cfg, None, mc, layout.device)
+        stats = nc.generation_service(layout, cfg, gen, ds, None, env)
+        assert stats["shards"] >= 1 and stats["weight_updates"] >= 2 and stats["final_version"] == steps + 1, stats
+    else:
+        policy, _, _, _, loss_fn, logger, ck, save_state, cfg = grpo.setup(cfg, None, ds, None, env, model_cfg=mc, build_generation=False)
+        seen = []
+        nc.noncolocated_grpo_train(policy, layout, loss_fn, None, ck, save_state, cfg, None,
+                                   step_callback=lambda s, m: seen.append((s, m["train"]["trajectory_age"], m["train"]["loss"])))
+        assert [s for s, _, _ in seen] == list(range(1, steps + 1)) and all(0 <= a <= 1 for _, a, _ in seen), seen
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_split_job_trains_while_generating_on_gpus(native_lib, world):
+    """Asynchronous GRPO with half of the GPUs training and half generating (weights over a raw NCCL communicator,
+    trajectories through the TCP store)."""
+    _need(world)
+    mp.spawn(_split_job_worker, args=(world, _free_port(), 3), nprocs=world, join=True)
+
+
+def _fsdp_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(model_type="llama", vocab_size=4096, hidden_size=512, intermediate_size=1408, num_hidden_layers=3,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    g = torch.Generator().manual_seed(100 + rank)
+    ids = torch.randint(1, 4096, (4, 64), generator=g)
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.tensor([64, 40, 64, 25]), token_mask=torch.ones(4, 64), sample_mask=torch.ones(4))
+    res = {}
+    for mode in ("full", "optimizer"):
+        p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=4 * world, train_micro_batch_size=2, max_total_sequence_length=128,
+                              max_grad_norm=0.5, parallel=dict(data_parallel_sharding=mode),
+                              optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3, weight_decay=0.1)),
+                              generation=dict(max_new_tokens=8, stop_token_ids=[], kv_cache_tokens=4096, block_size=16, max_running=8)),
+                         model_cfg=mc, device=f"cuda:{rank}", init_reference_model=True, seed=11)
+        lp0 = p.get_logprobs(data)["logprobs"]
+        outs = [p.train(data, NLLLossFn(), gbs=4 * world, mbs=2) for _ in range(3)]
+        lp1 = p.get_logprobs(data)["logprobs"]
+        ref = p.get_reference_policy_logprobs(data)["reference_logprobs"]
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        if mode == "full":
+            sh = p.sharder
+            assert sh._peer is not None and sh.stats["prefetch_hits"] > 0      # peer pull kernel, next unit gathered ahead
+            assert all(q.numel() == 0 for q in p.model.parameters())
+            gen = p.build_generation()
+            from rl_b200.algorithms.grpo import refit_policy_generation
+
+            refit_policy_generation(p, gen)
+            out = gen.generate(BatchedDataDict(input_ids=ids[:, :16], input_lengths=torch.full((4,), 16)))
+            gen.finish_generation()
+            assert (out["generation_lengths"] == 8).all()
+        res[mode] = (lp0, [float(o["loss"][0]) for o in outs], [float(o["grad_norm"][0]) for o in outs], lp1, ref)
+    f, n = res["full"], res["optimizer"]
+    assert (f[0] - n[0]).abs().max().item() < 1e-3
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[1], n[1])) < 3e-3, (f[1], n[1])
+    assert max(abs(a - b) / abs(b) for a, b in zip(f[2], n[2])) < 2e-2, (f[2], n[2])
+    assert (f[3] - n[3]).abs().mean().item() < 0.03
+    assert (f[4] - f[0]).abs().max().item() < 1e-3          # the reference shard did not move
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fully_sharded_parameters_match_resident_mode(native_lib, world):
+    """ZeRO-3 mode (parameters gathered per unit with the peer pull kernel, gradients reduce-scattered per unit) against
+    the resident-parameter mode on the same data."""
+    _need(world)
+    mp.spawn(_fsdp_worker, args=(world, _free_port()), nprocs=world, join=True)

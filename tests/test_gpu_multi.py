@@ -247,7 +247,11 @@ def _refit_worker(rank, world, port):
             torch.cuda.synchronize()
             assert torch.equal(got, ws.arena), (tp_train, tp_serve, it)
         sent, recv = ws.plan.bytes_over_link(rank)
-        assert (sent == 0) == (tp_train == 1)
+        if tp_train == 1:
+            assert sent == 0       # data-parallel training: every serving shard is cut from the rank's own copy
+        tot = torch.tensor([float(sent)], device=dev)
+        dist.all_reduce(tot)
+        assert (tot.item() > 0) == (tp_train > 1)
         if tp_serve == 1:  # the serving model is a complete model: it runs on its own
             ids = torch.randint(0, 4096, (2, 32), device=dev)
             b = PackedBatch.from_padded(ids, torch.tensor([32, 20], device=dev))

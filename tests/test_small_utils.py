@@ -3,6 +3,7 @@
 import os
 import sys
 
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -90,3 +91,36 @@ def test_worker_and_generation_satisfy_the_interfaces():
                           generation=dict(max_new_tokens=4, kv_cache_tokens=256, block_size=4, max_running=4)), model_cfg=mc, init_reference_model=False)
     assert isinstance(w, PolicyInterface) and isinstance(w, ColocatablePolicyInterface) and isinstance(w, ValueInterface)
     assert isinstance(w.build_generation(), GenerationInterface) and not isinstance(object(), PolicyInterface)
+
+
+def test_flops_formulas_per_architecture():
+    """Component arithmetic checked by hand on small shapes, and the families against each other."""
+    from rl_b200.utils import flops as FL
+
+    # one layer, d = 8, 2 heads of 4, 1 kv head, seq 4: projections 2*4*8*(8+8) + 2*4*8*8 = 1536, causal core 2*2*16*8/2 = 256
+    assert FL.attention_flops(4, 8, 2, 1, 4) == 1536 + 256
+    assert FL.attention_flops(4, 8, 2, 1, 4, causal=False) == 1536 + 512
+    assert FL.mlp_flops(4, 8, 16) == 2 * 4 * 8 * 16 * 3 and FL.mlp_flops(4, 8, 16, gated=False) == 2 * 4 * 8 * 16 * 2
+    assert FL.moe_flops(4, 8, 16, 2, 8) == 2 * 4 * 8 * 8 + 2 * FL.mlp_flops(4, 8, 16)
+    llama = dict(model_type="llama", hidden_size=8, num_hidden_layers=3, num_attention_heads=2, num_key_value_heads=1, head_dim=4,
+                 intermediate_size=16, vocab_size=32)
+    want = 3 * (FL.attention_flops(4, 8, 2, 1, 4) + FL.mlp_flops(4, 8, 16)) + 2 * 4 * 8 * 32
+    assert FL.model_flops(llama, 4, backward=False) == want and FL.model_flops(llama, 4, batch=5) == 15 * want
+    moe = dict(llama, model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=4)
+    assert FL.model_flops(moe, 4, backward=False) == 3 * (FL.attention_flops(4, 8, 2, 1, 4) + FL.moe_flops(4, 8, 4, 2, 8)) + 2 * 4 * 8 * 32
+    ds = dict(model_type="deepseek_v3", hidden_size=16, num_hidden_layers=4, num_attention_heads=2, q_lora_rank=8, kv_lora_rank=4,
+              qk_nope_head_dim=4, qk_rope_head_dim=2, v_head_dim=4, first_k_dense_replace=1, intermediate_size=32, moe_intermediate_size=8,
+              n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, vocab_size=64)
+    attn = FL.mla_attention_flops(4, 16, 2, 8, 4, 4, 2, 4)
+    want = 4 * attn + FL.mlp_flops(4, 16, 32) + 3 * FL.moe_flops(4, 16, 8, 2, 8, 8) + 2 * 4 * 16 * 64
+    assert FL.model_flops(ds, 4, backward=False) == want
+    hyb = dict(model_type="nemotron_h", hidden_size=16, hybrid_override_pattern="M*-M", num_attention_heads=2, num_key_value_heads=1, head_dim=8,
+               mamba_num_heads=4, mamba_head_dim=8, ssm_state_size=8, n_groups=2, conv_kernel=4, intermediate_size=32, vocab_size=64)
+    assert FL.model_flops(hyb, 4, backward=False) == (2 * FL.mamba2_flops(4, 16, 32, 8, 2, 4, 4) + FL.attention_flops(4, 16, 2, 1, 8)
+                                                       + FL.mlp_flops(4, 16, 32, gated=False) + 2 * 4 * 16 * 64)
+    # the packed-batch estimate used for MFU agrees with the per-sequence formula on a dense model
+    from rl_b200.models.config import ModelConfig
+
+    mc = ModelConfig(model_type="llama", vocab_size=32, hidden_size=8, intermediate_size=16, num_hidden_layers=3, num_attention_heads=2,
+                     num_key_value_heads=1, head_dim=4)
+    assert FL.transformer_flops(mc, 4, 4, backward=False) == pytest.approx(FL.model_flops(llama, 4, backward=False))

@@ -33,6 +33,8 @@ struct Seq {
   bool prefilled = false;
   long long arrival = 0;
   std::vector<int> blocks;
+  std::vector<unsigned long long> hashes;  // content hash of every full block of the prompt (chained: covers the prefix)
+  int cached_prefix = 0;                   // tokens of the current admission whose K/V were found in the prefix cache
 };
 
 struct Engine {
@@ -46,20 +48,62 @@ struct Engine {
   long long n_preempt = 0;
   int lookahead = 1;   // decode steps the host wants to run between two visits (multi-step decode)
   int window = 1;      // steps granted by the last schedule() call
+  // Prefix cache: full prompt blocks are registered under the hash of the token prefix they end. A registered block whose
+  // last user has finished keeps its contents and waits in `cached_free` (oldest first) until a request with the same
+  // prefix takes it over again or the allocator runs out of plain free blocks and evicts it.
+  std::unordered_map<unsigned long long, int> cache_table;   // prefix hash -> block
+  std::vector<unsigned long long> block_hash;                // per block: its hash (valid when block_cached)
+  std::vector<char> block_cached;
+  std::deque<int> cached_free;
+  long long cache_hits = 0, cache_queries = 0, cache_evictions = 0;
   // scratch of the last schedule() call
   std::vector<long long> prefill_ids, decode_ids, shared_ids;
   std::vector<int> copy_src, copy_dst;
 
   int blocks_for(int tokens) const { return (tokens + block_size - 1) / block_size; }
+  int available_blocks() const { return static_cast<int>(free_list.size() + cached_free.size()); }
+  void forget_block(int b) {
+    if (block_cached[b]) {
+      auto it = cache_table.find(block_hash[b]);
+      if (it != cache_table.end() && it->second == b) cache_table.erase(it);
+      block_cached[b] = 0;
+    }
+  }
   int alloc_block() {
-    if (free_list.empty()) return -1;
-    int b = free_list.back();
-    free_list.pop_back();
+    int b;
+    if (!free_list.empty()) {
+      b = free_list.back();
+      free_list.pop_back();
+    } else if (!cached_free.empty()) {
+      b = cached_free.front();   // evict the block that has been unused for the longest time
+      cached_free.pop_front();
+      forget_block(b);
+      ++cache_evictions;
+    } else {
+      return -1;
+    }
     refcount[b] = 1;
     return b;
   }
   void release_block(int b) {
-    if (--refcount[b] == 0) free_list.push_back(b);
+    if (--refcount[b] == 0) {
+      if (block_cached[b]) cached_free.push_back(b);
+      else free_list.push_back(b);
+    }
+  }
+  // Takes a cached block into use again (it may be waiting in cached_free or be shared with a running sequence).
+  void retain_cached(int b) {
+    if (refcount[b] == 0) {
+      auto it = std::find(cached_free.begin(), cached_free.end(), b);
+      if (it != cached_free.end()) cached_free.erase(it);
+    }
+    ++refcount[b];
+  }
+  void register_block(int b, unsigned long long h) {
+    if (block_cached[b] || cache_table.count(h)) return;
+    cache_table[h] = b;
+    block_hash[b] = h;
+    block_cached[b] = 1;
   }
   void release_seq(Seq& s) {
     for (int b : s.blocks) release_block(b);
@@ -69,7 +113,7 @@ struct Engine {
   bool ensure_capacity(Seq& s, int tokens) {
     const int need = blocks_for(tokens) - static_cast<int>(s.blocks.size());
     if (need <= 0) return true;
-    if (static_cast<int>(free_list.size()) < need) return false;
+    if (available_blocks() < need) return false;
     for (int i = 0; i < need; ++i) s.blocks.push_back(alloc_block());
     return true;
   }
@@ -85,6 +129,8 @@ RLB_API void* rlb_engine_create(int num_blocks, int block_size, int max_running,
   e->max_running = max_running;
   e->max_prefill_tokens = max_prefill_tokens > 0 ? max_prefill_tokens : (1 << 30);
   e->refcount.assign(num_blocks, 0);
+  e->block_hash.assign(num_blocks, 0ull);
+  e->block_cached.assign(num_blocks, 0);
   e->free_list.reserve(num_blocks);
   for (int b = num_blocks - 1; b >= 0; --b) e->free_list.push_back(b);
   return e;
@@ -92,7 +138,7 @@ RLB_API void* rlb_engine_create(int num_blocks, int block_size, int max_running,
 
 RLB_API void rlb_engine_destroy(void* h) { delete static_cast<Engine*>(h); }
 
-RLB_API int rlb_engine_num_free_blocks(void* h) { return static_cast<int>(static_cast<Engine*>(h)->free_list.size()); }
+RLB_API int rlb_engine_num_free_blocks(void* h) { return static_cast<Engine*>(h)->available_blocks(); }
 RLB_API int rlb_engine_num_running(void* h) { return static_cast<int>(static_cast<Engine*>(h)->running.size()); }
 RLB_API int rlb_engine_num_waiting(void* h) { return static_cast<int>(static_cast<Engine*>(h)->waiting.size()); }
 RLB_API long long rlb_engine_num_preemptions(void* h) { return static_cast<Engine*>(h)->n_preempt; }
@@ -144,7 +190,7 @@ RLB_API int rlb_engine_schedule(void* h, int* n_prefill, int* n_shared, int* n_d
       const int rem = std::max(1, s.max_new - s.num_generated);
       need += std::max(0, e->blocks_for(s.num_tokens + std::min(want, rem)) - static_cast<int>(s.blocks.size()));
     }
-    if (need > static_cast<long long>(e->free_list.size())) want = 1;
+    if (need > static_cast<long long>(e->available_blocks())) want = 1;
   }
   e->window = want;
   size_t i = 0;
@@ -187,7 +233,7 @@ RLB_API int rlb_engine_schedule(void* h, int* n_prefill, int* n_shared, int* n_d
       const int full = s.prompt_len / e->block_size;
       const int total = e->blocks_for(s.prompt_len + 1);
       const int fresh = total - full;
-      if (static_cast<int>(e->free_list.size()) < fresh) break;
+      if (e->available_blocks() < fresh) break;
       for (int b = 0; b < full; ++b) {
         s.blocks.push_back(partner->blocks[b]);
         ++e->refcount[partner->blocks[b]];
@@ -202,9 +248,32 @@ RLB_API int rlb_engine_schedule(void* h, int* n_prefill, int* n_shared, int* n_d
       s.state = RUNNING;
       e->shared_ids.push_back(id);
     } else {
-      if (prefill_tokens > 0 && prefill_tokens + context > e->max_prefill_tokens) break;
-      if (!e->ensure_capacity(s, context + 1)) break;
-      prefill_tokens += context;
+      // prefix cache: the longest run of leading full prompt blocks whose hashes are registered is taken over by
+      // reference; at least one token is always left to compute (its logits start the generation)
+      int hit = 0;
+      if (s.blocks.empty() && !s.hashes.empty()) {
+        const int max_blocks_hit = std::min(static_cast<int>(s.hashes.size()), (context - 1) / e->block_size);
+        ++e->cache_queries;
+        while (hit < max_blocks_hit) {
+          auto it = e->cache_table.find(s.hashes[hit]);
+          if (it == e->cache_table.end()) break;
+          ++hit;
+        }
+      }
+      const int fresh_tokens = context - hit * e->block_size;
+      if (prefill_tokens > 0 && prefill_tokens + fresh_tokens > e->max_prefill_tokens) break;
+      for (int b = 0; b < hit; ++b) {
+        const int blk = e->cache_table[s.hashes[b]];
+        e->retain_cached(blk);
+        s.blocks.push_back(blk);
+      }
+      if (!e->ensure_capacity(s, context + 1)) {
+        e->release_seq(s);   // gives the borrowed prefix back (it stays cached)
+        break;
+      }
+      if (hit) ++e->cache_hits;
+      s.cached_prefix = hit * e->block_size;
+      prefill_tokens += fresh_tokens;
       s.num_tokens = context;
       s.prefilled = true;  // true once this step's prefill kernels have run; partners see it from the next admission on
       s.state = RUNNING;
@@ -373,6 +442,43 @@ RLB_API void rlb_engine_reset(void* h) {
   e->waiting.clear();
   e->running.clear();
   e->free_list.clear();
+  e->cached_free.clear();
+  e->cache_table.clear();
   std::fill(e->refcount.begin(), e->refcount.end(), 0);
+  std::fill(e->block_cached.begin(), e->block_cached.end(), 0);
   for (int b = e->num_blocks - 1; b >= 0; --b) e->free_list.push_back(b);
+}
+
+// Prefix cache. `hashes[i]` identifies the content of the first (i + 1) * block_size prompt tokens of request `id` (the
+// caller chains them, so equal hashes mean equal prefixes). Set before the request is scheduled.
+RLB_API int rlb_engine_set_hashes(void* h, long long id, const unsigned long long* hashes, int n) {
+  Engine* e = static_cast<Engine*>(h);
+  auto it = e->seqs.find(id);
+  if (it == e->seqs.end() || n < 0) return -1;
+  it->second.hashes.assign(hashes, hashes + n);
+  return 0;
+}
+// Tokens of the request's current admission that came out of the prefix cache (a multiple of the block size).
+RLB_API int rlb_engine_cached_prefix(void* h, long long id) {
+  Engine* e = static_cast<Engine*>(h);
+  auto it = e->seqs.find(id);
+  return it == e->seqs.end() ? -1 : it->second.cached_prefix;
+}
+// Registers the full prompt blocks of a request whose prefill has run, so that later requests can take them over.
+RLB_API int rlb_engine_register_prefix(void* h, long long id) {
+  Engine* e = static_cast<Engine*>(h);
+  auto it = e->seqs.find(id);
+  if (it == e->seqs.end()) return -1;
+  Seq& s = it->second;
+  const int n = std::min(static_cast<int>(s.hashes.size()), std::min(static_cast<int>(s.blocks.size()), s.prompt_len / e->block_size));
+  for (int b = 0; b < n; ++b) e->register_block(s.blocks[b], s.hashes[b]);
+  return n;
+}
+// hits / queries / evictions of the prefix cache since creation.
+RLB_API void rlb_engine_cache_stats(void* h, long long* hits, long long* queries, long long* evictions, long long* cached_blocks) {
+  Engine* e = static_cast<Engine*>(h);
+  if (hits) *hits = e->cache_hits;
+  if (queries) *queries = e->cache_queries;
+  if (evictions) *evictions = e->cache_evictions;
+  if (cached_blocks) *cached_blocks = static_cast<long long>(e->cache_table.size());
 }

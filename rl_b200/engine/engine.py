@@ -46,6 +46,10 @@ _ENGINE_SIGS = {
     "rlb_engine_set_lookahead": ([_P, _I], None),
     "rlb_engine_window": ([_P], _I),
     "rlb_engine_commit_n": ([_P, _P, _I, _P, _P], _I),
+    "rlb_engine_set_hashes": ([_P, _LL, _P, _I], _I),
+    "rlb_engine_cached_prefix": ([_P, _LL], _I),
+    "rlb_engine_register_prefix": ([_P, _LL], _I),
+    "rlb_engine_cache_stats": ([_P, _P, _P, _P, _P], None),
 }
 _bound = False
 
@@ -282,6 +286,22 @@ class _NativeScheduler:
     def set_lookahead(self, steps: int) -> None:
         self.lib.rlb_engine_set_lookahead(self.h, int(steps))
 
+    # prefix cache (content-hashed prompt blocks kept across requests and generate calls)
+    def set_hashes(self, sid: int, hashes: list[int]) -> None:
+        arr = (C.c_ulonglong * max(1, len(hashes)))(*[h & 0xFFFFFFFFFFFFFFFF for h in hashes])
+        self.lib.rlb_engine_set_hashes(self.h, sid, arr, len(hashes))
+
+    def cached_prefix(self, sid: int) -> int:
+        return max(0, self.lib.rlb_engine_cached_prefix(self.h, sid))
+
+    def register_prefix(self, sid: int) -> int:
+        return self.lib.rlb_engine_register_prefix(self.h, sid)
+
+    def cache_stats(self) -> dict:
+        v = [_LL(0) for _ in range(4)]
+        self.lib.rlb_engine_cache_stats(self.h, *[C.byref(x) for x in v])
+        return dict(zip(("hits", "queries", "evictions", "cached_blocks"), (x.value for x in v)))
+
     @property
     def window(self) -> int:
         return self.lib.rlb_engine_window(self.h)
@@ -347,7 +367,8 @@ class GenerationEngine:
     def __init__(self, model: CausalLM, *, block_size: int = 64, num_blocks: Optional[int] = None,
                  kv_cache_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.5, max_running: int = 512,
                  max_prefill_tokens: int = 16384, max_model_len: int = 8192, use_cuda_graphs: bool = True,
-                 logits_fp32: bool = True, tokenizer=None, quantization: Optional[str] = None, decode_window: int = 16):
+                 logits_fp32: bool = True, tokenizer=None, quantization: Optional[str] = None, decode_window: int = 16,
+                 enable_prefix_caching: bool = True):
         """``quantization``: None (bf16), ``"mxfp8"`` or ``"fp8"``: serve quantised copies of the linear weights
         (see ``engine/quantized.py``); call :meth:`requantize` after the weights changed."""
         self.model = model
@@ -393,12 +414,16 @@ class GenerationEngine:
         self.decode_window = max(1, int(os.environ.get("RLB_DECODE_WINDOW", decode_window))) if self.native else 1
         if self.decode_window > 1 and isinstance(self.sched, _NativeScheduler):
             self.sched.set_lookahead(self.decode_window)
+        # Prefix cache: full prompt blocks stay addressable by the hash of the token prefix they end, across requests and
+        # generate calls (until the weights change: ``sleep`` resets it). A later prompt with the same prefix, e.g. the next
+        # turn of a multi-turn rollout, prefills only its new tokens.
+        self.prefix_caching = bool(enable_prefix_caching) and isinstance(self.sched, _NativeScheduler)
         self._graphs: dict[int, tuple] = {}
         self._static: Optional[dict] = None
         self._step_counter = 0
         self._n_stop = 0
         self.window_hook = None   # optional callable run at every host visit of the generate loop
-        self.stats = dict(prefill_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
+        self.stats = dict(prefill_tokens=0, cached_prefix_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
         # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
         self._ev = ([torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -684,6 +709,110 @@ class GenerationEngine:
                 self._decode_body(st, B, sp, num_splits, scratch)
         return st["tok"][:n], st["lp"][:n]
 
+    def _block_hashes(self, tokens: list[int]) -> list[int]:
+        """Chained content hashes of the full blocks of a prompt: entry i identifies tokens [0, (i + 1) * block_size)."""
+        bs, out, h = self.block_size, [], 0x9E3779B97F4A7C15
+        for i in range(len(tokens) // bs):
+            h = hash((h, tuple(tokens[i * bs : (i + 1) * bs]))) & 0xFFFFFFFFFFFFFFFF
+            out.append(h)
+        return out
+
+    def _prefill_plain(self, items, reqs, dev) -> dict:
+        """Whole prompts in one packed batch (nothing cached, nothing longer than the prefill budget)."""
+        toks, lens, slots = [], [], []
+        for sid, seq, _ in items:
+            toks.extend(seq)
+            lens.append(len(seq))
+            slots.append(self.sched.slots(sid, 0, len(seq)))
+        ids = _L.to_device(torch.tensor(toks, dtype=torch.int32 if self.native else torch.int64), dev)
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(lens, dtype=torch.int64).cumsum(0)
+        pos = torch.cat([torch.arange(L, dtype=torch.int32) for L in lens]).to(dev)
+        batch = PackedBatch(ids, pos, cu.to(dev), max(lens))
+        mms = [reqs[sid].mm for sid, _, _ in items if getattr(reqs[sid], "mm", None) is not None]
+        if mms:
+            batch.mm = dict(patches=_L.to_device(torch.cat([m[0] for m in mms]), dev), sizes=[int(x) for m in mms for x in m[1]])
+        logits = self._prefill_forward(batch, torch.cat(slots).to(dev), (cu[1:] - 1).to(dev))
+        self.stats["prefill_tokens"] += len(toks)
+        return {sid: logits[j] for j, (sid, _, _) in enumerate(items)}
+
+    def _prefill_with_prefix(self, items, dev, cap: int) -> dict:
+        """Prefill of prompts whose leading tokens are already in the KV cache (prefix-cache hits) and / or that are longer
+        than the prefill budget. Only the new tokens go through the projections and MLPs; their attention sees the cached
+        prefix through keys / values read back from the cache pages. A long prompt is cut into chunks of at most ``cap``
+        tokens that run one after the other, each attending to the chunks before it the same way (chunked prefill)."""
+        done = {sid: cached for sid, _, cached in items}
+        self.stats["cached_prefix_tokens"] += sum(done.values())
+        out: dict = {}
+        while True:
+            round_items, budget = [], cap
+            for sid, seq, _ in items:
+                left = len(seq) - done[sid]
+                if left <= 0 or budget <= 0:
+                    continue
+                n = min(left, budget)
+                round_items.append((sid, seq, done[sid], n))
+                budget -= n
+            if not round_items:
+                break
+            logits = self._prefill_round(round_items, dev)
+            for j, (sid, seq, p, n) in enumerate(round_items):
+                done[sid] = p + n
+                if done[sid] == len(seq):
+                    out[sid] = logits[j]
+                self.stats["prefill_tokens"] += n
+        return out
+
+    @torch.no_grad()
+    def _prefill_round(self, round_items, dev) -> torch.Tensor:
+        """One packed forward over the NEW tokens of several sequences: sequence i contributes tokens [p_i, p_i + n_i) and
+        attends to its p_i cached tokens. Returns the logits of every sequence's last new token."""
+        m, c = self.model, self.cfg
+        hq, hkv, D = self.hq, self.hkv, c.head_dim
+        idt = torch.int32 if self.native else torch.int64
+        toks, pos, new_slots, pre_slots, full_lens, new_idx, pre_idx, last = [], [], [], [], [], [], [], []
+        row = 0
+        for sid, seq, p, n in round_items:
+            toks.extend(seq[p : p + n])
+            pos.append(torch.arange(p, p + n, dtype=torch.int32))
+            new_slots.append(self.sched.slots(sid, p, n))
+            if p:
+                pre_slots.append(self.sched.slots(sid, 0, p))
+                pre_idx.append(torch.arange(row, row + p))
+            new_idx.append(torch.arange(row + p, row + p + n))
+            row += p + n
+            full_lens.append(p + n)
+            last.append(len(toks) - 1)
+        ids = _L.to_device(torch.tensor(toks, dtype=idt), dev)
+        positions = torch.cat(pos).to(dev)
+        slots = torch.cat(new_slots).to(dev)
+        new_rows = torch.cat(new_idx).to(dev)
+        cu = torch.zeros(len(full_lens) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(full_lens, dtype=torch.int64).cumsum(0)
+        cu = cu.to(dev)
+        if pre_slots:
+            ps = torch.cat(pre_slots).to(dev)
+            pre_rows = torch.cat(pre_idx).to(dev)
+            pre_blk, pre_off = ps // self.block_size, ps % self.block_size
+        total, W = row, (hq + 2 * hkv) * D
+        h = F.embedding(ids, m.embed_tokens)
+        for li, layer in enumerate(m.layers):
+            x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
+            qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
+            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], hq, hkv, D)
+            if pre_slots:
+                # rows of the cached prefix carry keys / values from the cache pages (already rotated) and a zero query
+                full = torch.zeros((total, W), dtype=qkv.dtype, device=dev)
+                full[new_rows] = qkv
+                full[pre_rows, hq * D : (hq + hkv) * D] = self.k_cache[li][pre_blk, :, pre_off, :].reshape(-1, hkv * D)
+                full[pre_rows, (hq + hkv) * D :] = self.v_cache[li][pre_blk, :, pre_off, :].reshape(-1, hkv * D)
+                a = F.attention_varlen(full, cu, max(full_lens), hq, hkv, D)[new_rows]
+            else:
+                a = F.attention_varlen(qkv, cu, max(full_lens), hq, hkv, D)
+            h = self._layer_tail(layer, h, a)
+        hl = E.gather_rows(h, torch.tensor(last, dtype=torch.int32, device=dev))
+        return self._output_logits(F.rmsnorm(hl, m.norm, c.rms_norm_eps))
+
     def _decode_window_native(self, decode, reqs, sp: SamplingParams, stop: set, st) -> None:
         """One window of decode steps for the running sequences: upload the step inputs and block tables once, run up to
         ``decode_window`` steps on the device (each step's sampled token feeds the next through the advance kernel, stop
@@ -801,6 +930,8 @@ class GenerationEngine:
             reqs[i].mm = mm
             if self.sched.add(i, len(p), mx, share) != 0:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
+            if self.prefix_caching and mm is None:
+                self.sched.set_hashes(i, self._block_hashes(p))
         dev = self.device
         st = self._static_buffers()
         if self.native and len(stop) > self.MAX_STOP_IDS:
@@ -876,27 +1007,22 @@ class GenerationEngine:
             if prefill or shared:
                 t0 = time.perf_counter()
                 if prefill:
-                    toks, lens, slots = [], [], []
+                    items = []
                     for sid in prefill:
                         r = reqs[sid]
-                        seq = r.prompt + r.out_tokens
-                        toks.extend(seq)
-                        lens.append(len(seq))
-                        slots.append(self.sched.slots(sid, 0, len(seq)))
-                    ids = _L.to_device(torch.tensor(toks, dtype=torch.int32 if self.native else torch.int64), dev)
-                    lens_t = torch.tensor(lens, dtype=torch.int64)
-                    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
-                    cu[1:] = lens_t.cumsum(0)
-                    pos = torch.cat([torch.arange(L, dtype=torch.int32) for L in lens]).to(dev)
-                    batch = PackedBatch(ids, pos, cu.to(dev), max(lens))
-                    mms = [reqs[sid].mm for sid in prefill if getattr(reqs[sid], "mm", None) is not None]
-                    if mms:
-                        batch.mm = dict(patches=_L.to_device(torch.cat([m[0] for m in mms]), dev), sizes=[int(x) for m in mms for x in m[1]])
-                    last_idx = (cu[1:] - 1).to(dev)
-                    logits = self._prefill_forward(batch, torch.cat(slots).to(dev), last_idx)
-                    for j, sid in enumerate(prefill):
-                        last_logits[sid] = logits[j]
-                    self.stats["prefill_tokens"] += len(toks)
+                        cached = self.sched.cached_prefix(sid) if self.prefix_caching else 0
+                        items.append((sid, r.prompt + r.out_tokens, cached))
+                    has_mm = any(getattr(reqs[sid], "mm", None) is not None for sid in prefill)
+                    cap = max(1, self.max_prefill_tokens)
+                    if has_mm or (all(c == 0 for _, _, c in items) and all(len(seq) <= cap for _, seq, _ in items)):
+                        logits = self._prefill_plain(items, reqs, dev)
+                    else:
+                        logits = self._prefill_with_prefix(items, dev, cap)
+                    for sid, row in logits.items():
+                        last_logits[sid] = row
+                    if self.prefix_caching:
+                        for sid in prefill:   # the prompt's full blocks can now serve later requests with the same prefix
+                            self.sched.register_prefix(sid)
                 if copies:
                     src = torch.tensor([a for a, _ in copies], dtype=torch.int32, device=dev)
                     dst = torch.tensor([b for _, b in copies], dtype=torch.int32, device=dev)

@@ -178,3 +178,45 @@ def test_fused_decode_step_matches_layer_by_layer_decode(native_lib, monkeypatch
     for a, b in zip(*outs):
         if a.out_tokens == b.out_tokens:
             assert max(abs(x - y) for x, y in zip(a.out_logprobs, b.out_logprobs)) < 0.08
+
+
+def test_prefix_cache_and_chunked_prefill_match_plain_prefill(native_lib):
+    """A second generate call whose prompts extend the first call's prompts (the next turn of a rollout) prefills only the
+    new tokens, and a prompt longer than the prefill budget runs in chunks; both give the tokens and log-probabilities of
+    a plain full prefill."""
+    from rl_b200.engine.engine import GenerationEngine, SamplingParams
+    from rl_b200.ops.lib import check_status
+
+    policy, _ = _policy(layers=2)
+    torch.manual_seed(4)
+    first = [torch.randint(1, 8192, (int(n),)).tolist() for n in (70, 33, 100)]
+    sp = SamplingParams(max_new_tokens=6, stop_token_ids=[], greedy=True, seed=0)
+
+    def run(prefix_cache, budget):
+        eng = GenerationEngine(policy.model, block_size=16, kv_cache_tokens=8192, max_running=8, max_model_len=512,
+                               max_prefill_tokens=budget, enable_prefix_caching=prefix_cache)
+        a = eng.generate(first, sp)
+        turn2 = [p + r.out_tokens + torch.randint(1, 8192, (9,), generator=torch.Generator().manual_seed(i)).tolist()
+                 for i, (p, r) in enumerate(zip(first, a))]
+        t0 = eng.stats["prefill_tokens"]
+        b = eng.generate(turn2, sp)
+        stats = dict(eng.stats, second_call_prefill=eng.stats["prefill_tokens"] - t0,
+                     cache=eng.sched.cache_stats() if prefix_cache else None)
+        assert check_status() == 0
+        eng.sleep(True)
+        return [(r.out_tokens, r.out_logprobs) for r in a + b], stats, [len(t) for t in turn2]
+
+    plain, st_plain, lens2 = run(False, 16384)
+    cached, st_cached, _ = run(True, 16384)
+    chunked, st_chunk, _ = run(False, 48)           # every prompt above 48 tokens is split into chunks
+    both, st_both, _ = run(True, 40)
+    for other in (cached, chunked, both):
+        for (t0, l0), (t1, l1) in zip(plain, other):
+            assert t0 == t1
+            assert max(abs(x - y) for x, y in zip(l0, l1)) < 0.05
+    # second call without the cache prefills whole prompts; with it only what lies beyond the cached full blocks
+    assert st_plain["second_call_prefill"] == sum(lens2)
+    want_new = sum(L - min((len(p) // 16) * 16, ((L - 1) // 16) * 16) for p, L in zip(first, lens2))
+    assert st_cached["second_call_prefill"] == want_new, (st_cached, want_new)
+    assert st_cached["cache"]["hits"] == 3 and st_cached["cached_prefix_tokens"] == sum(lens2) - want_new
+    assert st_both["second_call_prefill"] == want_new

@@ -148,8 +148,9 @@ def _ep_worker(rank, world):
     return dict(lp=float((got - ref).abs().max()), g=float((gl - gf[rank * per : (rank + 1) * per]).abs().max()))
 
 
-def test_expert_parallel_matches_local_experts():
-    out = _spawn(_ep_worker, 2)
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_matches_local_experts(world):
+    out = _spawn(_ep_worker, world)
     for r, m in out.items():
         assert m["lp"] < 2e-4 and m["g"] < 2e-3, (r, m)
 

@@ -133,7 +133,7 @@ DTENSOR = dict(enabled=F(bool), _v2=F(bool), cpu_offload=F(bool), sequence_paral
                tensor_parallel_size=F(int), context_parallel_size=F(int), expert_parallel_size=F(int), custom_parallel_plan=F(str),
                clear_cache_every_n_steps=F(int), lora_cfg=F(dict, sub=LORA), env_vars=F(dict), automodel_kwargs=F(dict),
                data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int), defer_fsdp_grad_sync=F(bool),
-               moe_parallelizer=F(dict))
+               moe_parallelizer=F(dict), fp8_cfg=F(dict, sub=FP8))
 
 FP8 = dict(enabled=F(bool), fp8=F(str, choices=("e4m3", "hybrid")), fp8_recipe=F(str, choices=("mxfp8", "blockwise", "tensorwise", "delayed")),
            fp8_param=F(bool), force_clear_fp8_caches=F(bool))

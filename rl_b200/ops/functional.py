@@ -121,6 +121,125 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db, dres
 
 
+# --------------------------------------------------------------------------------------- MXFP8 training linear
+class Fp8Training:
+    """Process-wide switch for block-scaled FP8 training of the linear layers (``policy.fp8_cfg`` /
+    ``megatron_cfg.fp8_cfg`` with ``fp8_recipe: mxfp8``; nemo_rl/models/policy/__init__.py:290-306,
+    nemo_rl/models/megatron/setup.py:1131-1178). Master weights, gradients and the optimizer stay bf16 / fp32; only the
+    three GEMMs of a linear layer (forward, input gradient, weight gradient) take MXFP8 operands (e4m3 with one E8M0
+    scale per 32 elements along the contraction dimension), each quantised along the dimension that GEMM contracts.
+    ``epoch`` must be advanced whenever the weights change (after an optimizer step) so that cached weight copies are
+    re-quantised."""
+
+    enabled = False
+    epoch = 0
+    stats = dict(fwd=0, dgrad=0, wgrad=0, weight_quantisations=0)
+
+    @classmethod
+    def configure(cls, cfg: Optional[dict]) -> bool:
+        c = cfg or {}
+        cls.enabled = bool(c.get("enabled")) and c.get("fp8_recipe", "mxfp8") in ("mxfp8", "blockwise")
+        return cls.enabled
+
+    @classmethod
+    def weights_changed(cls) -> None:
+        cls.epoch += 1
+
+
+def _mx_fake(x: torch.Tensor) -> torch.Tensor:
+    """CPU statement of MXFP8 rounding along the last dimension (quantise, de-quantise)."""
+    from . import quant as Q
+
+    R, C = x.shape
+    pad = (-C) % 32
+    xp = tF.pad(x.float(), (0, pad)) if pad else x.float()
+    q, e = Q.quantize_mxfp8_ref(xp.to(torch.bfloat16))
+    return Q.dequantize_mxfp8(q, e).float()[:, :C]
+
+
+def _mx_operand(t: torch.Tensor):
+    """bf16 [R, C] -> MXFP8 operand quantised along C; rows and columns are zero-padded to multiples of 128."""
+    from . import quant as Q
+
+    R, C = t.shape
+    pr, pc = (-R) % 128, (-C) % 128
+    if pr or pc:
+        t = tF.pad(t, (0, pc, 0, pr))
+    return Q.quantize_mxfp8_blocked(t.contiguous())
+
+
+def _mx_gemm(a: torch.Tensor, b: torch.Tensor, a_op=None, b_op=None) -> torch.Tensor:
+    """a [M, K] @ b[N, K]^T with both operands rounded to MXFP8 along K (block-scaled tensor-core GEMM on the GPU)."""
+    from . import quant as Q
+
+    M, N = a.shape[0], b.shape[0]
+    if not use_native(a):
+        return (_mx_fake(a) @ _mx_fake(b).t()).to(a.dtype)
+    aq, asf = a_op if a_op is not None else _mx_operand(a)
+    bq, bsf = b_op if b_op is not None else _mx_operand(b)
+    return Q.gemm_mxfp8(aq, asf, bq, bsf)[:M, :N]
+
+
+def _mx_weight(w: torch.Tensor, transposed: bool):
+    """Cached MXFP8 copy of a weight (or of its transpose), refreshed when ``Fp8Training.epoch`` moves."""
+    key = "_rlb_mx_t" if transposed else "_rlb_mx"
+    cur = getattr(w, key, None)
+    if cur is not None and cur[0] == Fp8Training.epoch:
+        return cur[1]
+    op = _mx_operand((w.detach().t() if transposed else w.detach()).contiguous())
+    setattr(w, key, (Fp8Training.epoch, op))
+    Fp8Training.stats["weight_quantisations"] += 1
+    return op
+
+
+class _MXLinear(torch.autograd.Function):
+    """y = x W^T with MXFP8 GEMMs in forward, input gradient and weight gradient (bf16 master weight, fp32 / bf16
+    gradient accumulation as in the bf16 path)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = x.reshape(-1, x.shape[-1])
+        native = use_native(x2)
+        y = _mx_gemm(x2, w, b_op=_mx_weight(w, False) if native else None)
+        Fp8Training.stats["fwd"] += 1
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        y = y.reshape(*x.shape[:-1], w.shape[0])
+        if residual is not None:
+            y = y + residual
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        native = use_native(dy2)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # dX [M, K] = dY [M, N] W [N, K]: contraction over N, so W is quantised along N (its transpose along the rows)
+            dx = _mx_gemm(dy2, w.t().contiguous() if not native else w, b_op=_mx_weight(w, True) if native else None)
+            if not native:
+                pass
+            dx = dx.reshape(x.shape)
+            Fp8Training.stats["dgrad"] += 1
+        if ctx.needs_input_grad[1]:
+            # dW [N, K] = dY^T [N, M] X [M, K]: contraction over the tokens
+            g = _mx_gemm(dy2.t().contiguous(), x2.t().contiguous())
+            Fp8Training.stats["wgrad"] += 1
+            main_grad = getattr(w, "main_grad", None)
+            if main_grad is not None:
+                main_grad.add_(g.to(main_grad.dtype))
+            else:
+                dw = g.to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0)
+        dres = dy if ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x @ w^T (+ bias) (+ residual); w is [out_features, in_features] as in ``nn.Linear``.
@@ -133,6 +252,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
         if _qz.is_active():
             return _qz.quantized_linear(x, qz, bias, residual, getattr(w, "_rlb_q_bf16", None))
+    if Fp8Training.enabled and torch.is_grad_enabled() and w.dim() == 2 and w.shape[0] % 16 == 0 and w.shape[1] % 32 == 0 \
+            and w.requires_grad and not getattr(w, "_rlb_keep_bf16", False):
+        return _MXLinear.apply(x, w, bias, residual)
     if not use_native(x):
         y = tF.linear(x, w, bias)
         return y if residual is None else y + residual

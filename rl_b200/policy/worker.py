@@ -28,6 +28,7 @@ from rl_b200.models.config import ModelConfig, preset
 from rl_b200.models.transformer import CausalLM, PackedBatch, build_model
 from rl_b200.policy.optimizer import LRSchedule, ShardedAdamW, build_optimizer
 from rl_b200.ops import lib as _L
+from rl_b200.ops.functional import Fp8Training as _Fn_fp8
 from rl_b200.ops.lib import to_device, to_host
 from rl_b200.utils.flops import transformer_flops
 
@@ -173,6 +174,16 @@ class PolicyWorker:
                 if self.rank == 0:
                     print(f"[policy] fused peer-memory optimizer unavailable ({type(e).__name__}: {e}); using NCCL")
                 fused_comm = None
+        # block-scaled FP8 training of the dense linear layers (policy.fp8_cfg / megatron_cfg.fp8_cfg, recipe mxfp8); the
+        # embedding, output head, router and norms stay in bf16
+        from rl_b200.ops import functional as _Fn
+
+        fp8_cfg = cfg.get("fp8_cfg") or (cfg.get("megatron_cfg") or {}).get("fp8_cfg") or (cfg.get("dtensor_cfg") or {}).get("fp8_cfg")
+        self.fp8_training = _Fn.Fp8Training.configure(fp8_cfg) if (fp8_cfg or _Fn.Fp8Training.enabled) else False
+        if self.fp8_training:
+            for n_, p_ in self.model.named_parameters():
+                if n_.endswith(("embed_tokens", "lm_head", "score", "router")) or ".mlp.router" in n_ or p_.dim() != 2:
+                    p_._rlb_keep_bf16 = True
         par_cfg = cfg.get("parallel") or {}
         self.full_sharding = (par_cfg.get("data_parallel_sharding") or dtc.get("data_parallel_sharding") or "optimizer") == "full"
         if self.full_sharding:
@@ -712,6 +723,8 @@ class PolicyWorker:
                     self.optimizer_e.lr = self.optimizer.lr
                     self.optimizer_e.apply(total.clone())
                 grad_norms.append(gn)
+                if getattr(self, "fp8_training", False):
+                    _Fn_fp8.weights_changed()   # cached MXFP8 copies of the weights are stale now
             if self.world > 1:
                 dist.all_reduce(gb_loss, group=self.dp_group)
                 gb_loss = gb_loss / cpw

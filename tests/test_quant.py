@@ -114,3 +114,30 @@ def test_mxfp8_gemm_matches_dequantised_reference(native_lib, shape):
     ref = dequantize_mxfp8(aq, asf).float() @ dequantize_mxfp8(bq, bsf).float().t()
     err = (c.float() - ref).abs().max().item()
     assert err <= 1e-2 * ref.abs().max().item() + 1e-3, (err, ref.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_mxfp8_training_linear_matches_quantised_statement(native_lib):
+    """Forward, input gradient and weight gradient of the MXFP8 training linear on the block-scaled tensor-core GEMM against
+    the CPU statement (operands rounded to e4m3 with one E8M0 scale per 32 elements along each GEMM's contraction)."""
+    from rl_b200.ops import functional as F
+    from rl_b200.ops.lib import check_status
+
+    torch.manual_seed(0)
+    M, K, N = 200, 256, 384          # the token count is not a multiple of 128: the weight-gradient GEMM pads it
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    dy = torch.randn(M, N).to(torch.bfloat16)
+    F.Fp8Training.configure(dict(enabled=True, fp8_recipe="mxfp8"))
+    try:
+        outs = {}
+        for dev in ("cpu", "cuda"):
+            xd, wd = x.to(dev).requires_grad_(), w.to(dev).requires_grad_()
+            y = F.linear(xd, wd)
+            y.backward(dy.to(dev))
+            outs[dev] = (y.detach().float().cpu(), xd.grad.float().cpu(), wd.grad.float().cpu())
+        for a, b, name in zip(outs["cpu"], outs["cuda"], ("y", "dx", "dw")):
+            assert (a - b).abs().max().item() <= 2e-2 * a.abs().max().item() + 1e-3, name
+        assert check_status() == 0
+    finally:
+        F.Fp8Training.configure(None)

@@ -187,9 +187,9 @@ class Attention(nn.Module):
         if self.cp is not None:
             from rl_b200.parallel.context import cp_attention_varlen
 
-            r0, r1 = self.cp.local_rows(positions.numel())
-            qkv = self.project_qkv(x, positions[r0:r1], inv_freq)
-            a = cp_attention_varlen(qkv, cu_seqlens, self.cp, self.hq, self.hkv, c.head_dim)
+            T = positions.numel()
+            qkv = self.project_qkv(x, positions[self.cp.local_index(T, positions.device)], inv_freq)
+            a = cp_attention_varlen(qkv, cu_seqlens, self.cp, self.hq, self.hkv, c.head_dim, total_rows=T)
             return F.linear(a, self.o_proj, None, residual)
         qkv = self.project_qkv(x, positions, inv_freq)
         a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim)
@@ -464,8 +464,8 @@ class CausalLM(nn.Module):
             rows = batch.input_ids.numel() // self.tp.world
             return F.embedding(batch.input_ids[self.tp.rank * rows : (self.tp.rank + 1) * rows], self.embed_tokens)
         if self.cp is not None:
-            r0, r1 = self.cp.local_rows(batch.input_ids.numel())
-            return F.embedding(batch.input_ids[r0:r1], self.embed_tokens)
+            # this rank's rows of the stream: two chunks, one early and one late (load-balanced under the causal mask)
+            return F.embedding(batch.input_ids[self.cp.local_index(batch.input_ids.numel(), batch.input_ids.device)], self.embed_tokens)
         return F.embedding(batch.input_ids, self.embed_tokens)
 
     def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
@@ -513,13 +513,11 @@ class CausalLM(nn.Module):
         targets = torch.roll(ids, -1)
         if self.cp is not None:
             # local rows are scored locally; the [T]-sized results are gathered (backward: each rank keeps its rows' share)
-            from rl_b200.parallel.tensor import TP as _TP
+            from rl_b200.parallel.context import gather_to_stream
 
-            r0, r1 = self.cp.local_rows(T)
-            lp_l, ent_l = F.lm_head_logprobs(h, self.output_weight, targets[r0:r1], temperature, want_entropy)
-            rows_tp = _TP(self.cp.group, self.cp.rank, self.cp.world)
-            lp_rows = gather_rows(lp_l, rows_tp)
-            ent_rows = gather_rows(ent_l, rows_tp) if want_entropy else None
+            lp_l, ent_l = F.lm_head_logprobs(h, self.output_weight, targets[self.cp.local_index(T, ids.device)], temperature, want_entropy)
+            lp_rows = gather_to_stream(lp_l, self.cp)
+            ent_rows = gather_to_stream(ent_l, self.cp) if want_entropy else None
         elif self.tp.world == 1:
             lp_rows, ent_rows = F.lm_head_logprobs(h, self.output_weight, targets, temperature, want_entropy)
         else:
@@ -592,7 +590,9 @@ class CausalLM(nn.Module):
         h = self.hidden_states(batch, h_in)
         v = F.linear(h, self.score).float()[:, 0]
         if self.cp is not None:
-            return gather_rows(v, TP(self.cp.group, self.cp.rank, self.cp.world))
+            from rl_b200.parallel.context import gather_to_stream
+
+            return gather_to_stream(v, self.cp)
         return gather_rows(v, self.tp) if self.tp.sequence_parallel else v
 
 

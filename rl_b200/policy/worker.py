@@ -557,7 +557,7 @@ class PolicyWorker:
         if self.tp.world > 1 and self.tp.sequence_parallel:
             batch = batch.pad_to_multiple(8 * self.tp.world)
         elif self.cp.world > 1:
-            batch = batch.pad_to_multiple(8 * self.cp.world)
+            batch = batch.pad_to_multiple(16 * self.cp.world)   # 2 cp chunks of whole 8-row groups
         if "pixel_patches" in mb:   # vision-language batch: image patch rows in sample order (models/vision.py)
             parts = [t for t in mb["pixel_patches"] if t is not None]
             batch.mm = dict(patches=to_device(torch.cat(parts), self.device) if parts else None,

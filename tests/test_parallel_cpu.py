@@ -223,9 +223,47 @@ def _cp_worker(rank, world):
     return dict(lp=lp.sum().item(), lp2=lp2.sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
 
 
-def test_context_parallel_worker_matches_single_rank():
+def _ring_worker(rank, world):
+    """Ring attention on the zig-zag shards of a packed stream against dense masked attention on the whole stream."""
+    from rl_b200.parallel.context import CP, cp_attention_varlen
+
+    torch.manual_seed(0)
+    hq, hkv, d, T = 4, 2, 8, 16 * world
+    cu = torch.tensor([0, 5, 5 + 3 * world, T - 2, T], dtype=torch.int32)
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, dtype=torch.float64)
+    g = torch.randn(T, hq * d, dtype=torch.float64)
+    cp = CP(None, rank, world)
+    idx = cp.local_index(T)
+    x = qkv[idx].clone().requires_grad_(True)
+    out = cp_attention_varlen(x, cu, cp, hq, hkv, d, total_rows=T)
+    (out * g[idx]).sum().backward()
+    # dense statement
+    xf = qkv.clone().requires_grad_(True)
+    q = xf[:, : hq * d].reshape(T, hq, d)
+    k = xf[:, hq * d : (hq + hkv) * d].reshape(T, hkv, d).repeat_interleave(hq // hkv, dim=1)
+    v = xf[:, (hq + hkv) * d :].reshape(T, hkv, d).repeat_interleave(hq // hkv, dim=1)
+    seq = torch.searchsorted(cu[1:].long(), torch.arange(T), right=True)
+    vis = (seq[:, None] == seq[None, :]) & (torch.arange(T)[None, :] <= torch.arange(T)[:, None])
+    s = torch.einsum("qhd,khd->hqk", q, k) * d ** -0.5
+    p = torch.softmax(s.masked_fill(~vis[None], float("-inf")), -1)
+    ref = torch.einsum("hqk,khd->qhd", p, v).reshape(T, hq * d)
+    (ref * g).sum().backward()
+    order = cp.stream_order(T)
+    return dict(fwd=(out.detach() - ref.detach()[idx]).abs().max().item(), bwd=(x.grad - xf.grad[idx]).abs().max().item(),
+                perm=bool(torch.equal(torch.cat([CP(None, r, world).local_index(T) for r in range(world)])[order], torch.arange(T))))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ring_attention_zigzag_matches_dense(world):
+    out = _spawn(_ring_worker, world)
+    for r, m in out.items():
+        assert m["fwd"] < 1e-5 and m["bwd"] < 1e-5 and m["perm"], (r, m)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_worker_matches_single_rank(world):
     ref = _single_reference(False)
-    out = _spawn(_cp_worker, 2)
+    out = _spawn(_cp_worker, world)
     for r, m in out.items():
         assert m["lp"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)
         assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)

@@ -218,7 +218,14 @@ def refit_policy_generation(policy, generation, timer: Optional[Timer] = None) -
     buffers, so only the engine's request state is reset; other layouts go through :mod:`rl_b200.refit`."""
     sync = getattr(policy, "weight_synchronizer", None)
     if sync is not None:
-        sync.sync_weights(timer)
+        eng = getattr(generation, "engine", None)
+        if getattr(eng, "quantization", None) == "fp8" and getattr(eng, "tpw", 1) == 1 and hasattr(sync, "sync_weights_fp8"):
+            # block-128 FP8 rollout: the re-shard pass quantises on the way (one read of the trainer's weights, fp8 bytes
+            # over NVLink) and the engine takes the quantised copies as they are
+            sync.sync_weights_fp8()
+            eng.quantized_by_refit = True
+        else:
+            sync.sync_weights(timer)
     generation.prepare_for_generation()
 
 

@@ -241,12 +241,14 @@ struct GatherColsArgs {
   unsigned long long limit_ns;
   int* abort_word;
   int* status;
+  long long half_vecs;           // offset of the second half of every stage
 };
 __global__ void __launch_bounds__(512, 1) p2p_gather_cols_kernel(GatherColsArgs a) {
   cg::grid_group grid = cg::this_grid();
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(a.epoch_ptr) + 1;
   const long long n = static_cast<long long>(a.rows) * a.row_vecs;
-  const long long half = (epoch & 1u) ? n : 0;
+  // the two halves sit at fixed offsets, whatever this call's size: consecutive calls of different sizes never overlap
+  const long long half = (epoch & 1u) ? a.half_vecs : 0;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   uint4* mine = a.stage[a.rank] + half;
@@ -400,13 +402,15 @@ RLB_API int rlb_p2p_allgather(void* const* src_ptrs, void* dst, void* const* fla
 }
 
 // out[rows, world * cols] = concatenation over ranks of their `local` [rows, cols] slices (see p2p_gather_cols_kernel).
-// row_bytes = cols * element size, a multiple of 16; stage_ptrs[r]: rank r's staging of 2 * rows * row_bytes bytes;
+// row_bytes = cols * element size, a multiple of 16; stage_ptrs[r]: rank r's staging of 2 * half_bytes bytes, with
+// half_bytes >= rows * row_bytes the same on every rank and in every call that shares the stage;
 // flag_ptrs[r]: 8 zero-initialised uint32 words of symmetric memory; epoch_ptr: device uint32 (starts at 0);
 // scratch: one device int.
 RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void* const* flag_ptrs, void* out,
                                 long long out_stride_bytes, int rows, int row_bytes, int rank, int world, void* epoch_ptr,
-                                double wait_limit_s, int* scratch, int* status, void* stream) {
+                                double wait_limit_s, int* scratch, int* status, long long half_bytes, void* stream) {
   if (world < 1 || world > MAX_RANKS || rows <= 0 || row_bytes <= 0 || (row_bytes % 16) || (out_stride_bytes % 16)) return -2;
+  if ((half_bytes % 16) || half_bytes < static_cast<long long>(rows) * row_bytes) return -2;
   if ((reinterpret_cast<uintptr_t>(local) | reinterpret_cast<uintptr_t>(out)) & 15) return -3;
   GatherColsArgs a;
   memset(&a, 0, sizeof(a));
@@ -425,6 +429,7 @@ RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void
   a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
   a.abort_word = scratch;
   a.status = status;
+  a.half_vecs = half_bytes / 16;
   const int grid = coop_grid(reinterpret_cast<const void*>(p2p_gather_cols_kernel), 512);
   void* args[] = {&a};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_gather_cols_kernel), dim3(grid),

@@ -391,7 +391,11 @@ class GenerationEngine:
         self.hkv = attn0.hkv if attn0 is not None else self.cfg.num_key_value_heads
         # tensor-parallel decode is captured too when the fused GEMM + all-reduce kernel (device-resident epoch) carries the
         # collectives; NCCL broadcasts / all-gathers of the sampled tokens and logits are capturable as well
-        self.use_graphs = use_cuda_graphs and self.native and not self.cfg.is_moe and (self.tpw == 1 or getattr(self.tp, "comm", None) is not None)
+        # mixture-of-experts decode is captured as well: its few-token layer (csrc/moe_decode.cu) has fixed shapes and no
+        # host visit, on one GPU or, with the peer-memory expert-parallel communicator, across the expert group
+        ep0 = getattr(model, "ep", None)
+        moe_ok = (not self.cfg.is_moe) or ep0 is None or ep0.world == 1 or getattr(ep0, "comm", None) is not None
+        self.use_graphs = use_cuda_graphs and self.native and moe_ok and (self.tpw == 1 or getattr(self.tp, "comm", None) is not None)
         self.logits_dtype = torch.float32 if logits_fp32 else model.dtype
         c = self.cfg
         if num_blocks is None:
@@ -419,6 +423,7 @@ class GenerationEngine:
         # turn of a multi-turn rollout, prefills only its new tokens.
         self.prefix_caching = bool(enable_prefix_caching) and isinstance(self.sched, _NativeScheduler)
         self._graphs: dict[int, tuple] = {}
+        self._agreed_bucket = 0
         self._static: Optional[dict] = None
         self._step_counter = 0
         self._n_stop = 0
@@ -440,6 +445,9 @@ class GenerationEngine:
         """Refreshes the quantised weight copies from the (refitted) bf16 weights; no-op for a bf16 engine."""
         if not self.quantization:
             return None
+        if getattr(self, "quantized_by_refit", False):   # the refit pass already left quantised copies on the weights
+            self.quantized_by_refit = False
+            return dict(tensors=0, by_refit=True)
         from .quantized import quantize_model
 
         assert self.tpw == 1, "low-precision rollout with a tensor-parallel engine is not supported"
@@ -488,12 +496,13 @@ class GenerationEngine:
             z.index_fill_(1, self._banned_ids, -1e30)
         return z
 
-    def _any_rank(self, ep, flag: bool) -> bool:
+    def _agree_max(self, ep, values: list[int]) -> list[int]:
+        """Element-wise maximum of a few integers over the expert-parallel group (one small all-reduce, one host read)."""
         import torch.distributed as dist
 
-        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=self.device)
+        t = torch.tensor(values, dtype=torch.int64, device=self.device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ep.group)
-        return bool(t.item())
+        return [int(x) for x in t.tolist()]
 
     @torch.no_grad()
     def _dummy_forward(self, decode: bool) -> None:
@@ -645,6 +654,8 @@ class GenerationEngine:
         return self._static
 
     def _bucket(self, n: int) -> int:
+        if self._agreed_bucket:   # expert-parallel ranks decode batches of one size (the largest any of them needs)
+            return max(self._agreed_bucket, n)
         for b in self.BUCKETS:
             if b >= n:
                 return min(b, self.max_running) if b <= self.max_running else n
@@ -676,7 +687,30 @@ class GenerationEngine:
         # the per-call seed is not part of the key: it reaches the sampler through the row keys (device memory), so one
         # captured graph serves every generate call with the same sampling parameters
         key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, self._n_stop)
-        if self.use_graphs:
+        use_graphs = self.use_graphs
+        ep = getattr(self.model, "ep", None)
+        if c.is_moe:
+            # the few-token MoE layer needs every expert-parallel rank to run the same batch size (the generate loop agreed
+            # on this bucket); larger batches take the dispatch / combine path, which is not captured
+            from rl_b200.ops.moe_ops import SMALL_MAX_COPIES
+
+            W = ep.world if ep is not None else 1
+            cap = SMALL_MAX_COPIES // (W * c.num_experts_per_tok)
+            fits = B <= min(cap, 256 if W == 1 else cap)
+            if W > 1:
+                ep.lockstep_max = min(cap, max(self.max_running, B))
+                ep.lockstep_tokens = B if (fits and getattr(ep, "comm", None) is not None and self._agreed_bucket) else 0
+                fits = ep.lockstep_tokens > 0
+            use_graphs = use_graphs and fits
+        try:
+            return self._run_decode_steps(n, B, sp, num_splits, key, use_graphs, steps, st)
+        finally:
+            if c.is_moe and ep is not None and ep.world > 1:
+                ep.lockstep_tokens = 0
+
+    def _run_decode_steps(self, n, B, sp, num_splits, key, use_graphs, steps, st):
+        c = self.cfg
+        if use_graphs:
             g = self._graphs.get(key)
             if g is None:
                 no, nml = E.decode_scratch_sizes(B, self.hq, num_splits, c.head_dim)
@@ -813,39 +847,53 @@ class GenerationEngine:
         hl = E.gather_rows(h, torch.tensor(last, dtype=torch.int32, device=dev))
         return self._output_logits(F.rmsnorm(hl, m.norm, c.rms_norm_eps))
 
-    def _decode_window_native(self, decode, reqs, sp: SamplingParams, stop: set, st) -> None:
+    def _window_steps(self, decode, reqs) -> int:
+        """How many decode steps the next window may run for these sequences: bounded by the blocks the scheduler reserved
+        ahead, the window size and the longest remaining budget."""
+        if not decode:
+            return 0
+        max_rem = max(1, max(reqs[sid].max_new - len(reqs[sid].out_tokens) for sid in decode))
+        return max(1, min(self.sched.window if isinstance(self.sched, _NativeScheduler) else 1, self.decode_window, max_rem))
+
+    def _decode_window_native(self, decode, reqs, sp: SamplingParams, stop: set, st, steps: Optional[int] = None) -> None:
         """One window of decode steps for the running sequences: upload the step inputs and block tables once, run up to
         ``decode_window`` steps on the device (each step's sampled token feeds the next through the advance kernel, stop
-        tokens and length limits retire rows on the device), then read all tokens of the window with one copy."""
+        tokens and length limits retire rows on the device), then read all tokens of the window with one copy.
+        ``steps``: the step count the ranks of an expert-parallel group agreed on (never above this rank's own bound); a
+        rank without running sequences takes part with a batch of inactive rows."""
         t0 = time.perf_counter()
         n = len(decode)
         hb = st["host"]
-        self.sched.tables(decode, self.max_blocks_per_seq, out=(hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n]))
-        ctx = hb["seq_lens"][:n]
-        hb["positions"][:n] = ctx
-        max_ctx = int(ctx.max()) + 1
-        hb["seq_lens"][:n] += 1
+        max_ctx = 1
+        if n:
+            self.sched.tables(decode, self.max_blocks_per_seq, out=(hb["block_table"][:n], hb["seq_lens"][:n], hb["slots"][:n]))
+            ctx = hb["seq_lens"][:n]
+            hb["positions"][:n] = ctx
+            max_ctx = int(ctx.max()) + 1
+            hb["seq_lens"][:n] += 1
         ids_np, keys_np, rem_np = hb["ids"].numpy(), hb["keys"].numpy(), hb["remaining"].numpy()
-        max_rem = 1
         for j, sid in enumerate(decode):
             r = reqs[sid]
             ids_np[j] = r.out_tokens[-1]
             keys_np[j] = self._row_key(r, sp)
             rem_np[j] = r.max_new - len(r.out_tokens)
-            max_rem = max(max_rem, int(rem_np[j]))
         hb["active"][:n] = 1
         hb["win_step"][0] = 0
-        B = self._bucket(n)
+        B = self._bucket(max(n, 1))
         if B > n:  # padding rows: never active, no cache write, empty context
             for name in ("seq_lens", "ids", "positions", "keys", "active", "remaining"):
                 hb[name][n:B] = 0
             hb["slots"][n:B] = -1
             hb["block_table"][n:B] = 0
-        steps = max(1, min(self.sched.window if isinstance(self.sched, _NativeScheduler) else 1, self.decode_window, max_rem))
+        if steps is None:
+            steps = self._window_steps(decode, reqs)
         st["blob"].copy_(st["host_blob"], non_blocking=True)   # all inputs of the window in one upload
         _L.Counters.h2d_bytes += st["host_blob"].numel()
         self._step_counter += steps
-        self._run_decode(n, sp, max_ctx, steps)
+        self._run_decode(max(n, 1), sp, max_ctx, steps)
+        if n == 0:
+            self.stats["decode_s"] += time.perf_counter() - t0
+            return
         both = _L.to_host(st["out_blob"])   # one download for the window; synchronises the stream
         if self._ev_pending:
             self.stats["decode_device_s"] += self._ev[0].elapsed_time(self._ev[1]) * 1e-3
@@ -952,10 +1000,7 @@ class GenerationEngine:
             if self.window_hook is not None:   # between two host visits (e.g. an in-flight weight update)
                 self.window_hook()
             idle = self.sched.idle()
-            if lock:
-                if not self._any_rank(ep, not idle):
-                    break
-            elif idle:
+            if not lock and idle:
                 break
             prefill, shared, decode, copies = self.sched.schedule() if not idle else ([], [], [], [])
             if self.collect_timeline:
@@ -963,15 +1008,31 @@ class GenerationEngine:
                                       sum(1 for r in reqs.values() if not r.finished)))
             if not idle and not prefill and not shared and not decode:
                 raise RuntimeError("scheduler made no progress (KV cache too small for a single request)")
-            need_decode = self._any_rank(ep, bool(decode)) if lock else bool(decode)
-            need_prefill = self._any_rank(ep, bool(prefill)) if lock else bool(prefill)
+            agreed_steps = None
+            if lock:
+                # one exchange per iteration: does anyone still work, decode, prefill; the largest decode batch (every rank
+                # pads to its bucket) and the smallest window any decoding rank can run
+                want = self._window_steps(decode, reqs) if (decode and self.native) else 0
+                v = self._agree_max(ep, [0 if idle else 1, len(decode), 1 if prefill else 0, -want if want else -(1 << 20)])
+                if v[0] == 0:
+                    break
+                need_decode, need_prefill = v[1] > 0, v[2] > 0
+                if need_decode and self.native:
+                    self._agreed_bucket = 0
+                    self._agreed_bucket = self._bucket(v[1])
+                    agreed_steps = max(1, -v[3])
+            else:
+                need_decode, need_prefill = bool(decode), bool(prefill)
             if need_decode and not decode:
-                self._dummy_forward(decode=True)
+                if self.native:
+                    self._decode_window_native([], reqs, sp, stop, st, agreed_steps)
+                else:
+                    self._dummy_forward(decode=True)
             if need_prefill and not prefill:
                 self._dummy_forward(decode=False)
             # ---- decode the sequences that were already running
             if decode and self.native:
-                self._decode_window_native(decode, reqs, sp, stop, st)
+                self._decode_window_native(decode, reqs, sp, stop, st, agreed_steps)
             elif decode:
                 t0 = time.perf_counter()
                 n = len(decode)

@@ -59,10 +59,49 @@ class MoEMLP(nn.Module):
             counts = torch.tensor(counts, dtype=torch.int64, device=xs.device)
         return grouped_expert_mlp(xs, counts, self.gate_up_proj, self.down_proj)
 
+    # ---- few-token path (decode steps): fixed shapes, no host visit, capturable in a CUDA graph
+    def _small_workspace(self, T: int):
+        """The shared :class:`rl_b200.ops.moe_ops.SmallTokenMoE` of this model's layers, or None when the call does not
+        qualify. With expert parallelism the caller must have declared (``ep.lockstep_tokens``) that every rank of the
+        group runs this layer with the same token count; only the generation engine's decode steps do."""
+        from rl_b200.ops import lib as _L
+        from rl_b200.ops import moe_ops as M
+
+        c = self.cfg
+        if torch.is_grad_enabled() or self.forced_routing is not None or not _L.available():
+            return None
+        W = self.ep_size
+        lock = int(getattr(self.ep, "lockstep_tokens", 0) or 0)
+        if W > 1 and (lock <= 0 or self.ep.comm is None):
+            return None
+        max_t = max(lock, int(getattr(self.ep, "lockstep_max", 0) or 0)) if W > 1 else min(256, M.SMALL_MAX_COPIES // c.num_experts_per_tok)
+        if T > max_t or W * max_t * c.num_experts_per_tok > M.SMALL_MAX_COPIES or c.hidden_size % 64 or c.moe_intermediate_size % 64 \
+                or self.local_experts > 256 or c.num_experts_per_tok > 16:
+            return None
+        # one workspace for all layers: on the expert-parallel handle they share, or per (device, shape) without one
+        key = (self.router.device, c.hidden_size, c.moe_intermediate_size, c.num_experts, c.num_experts_per_tok)
+        ws = getattr(self.ep, "_small_moe", None) if W > 1 else M.SMALL_WORKSPACES.get(key)
+        if ws is None or ws.maxT < max_t or ws.device != self.router.device:
+            if ws is not None:
+                ws.close()
+            ws = M.SmallTokenMoE(c.hidden_size, c.moe_intermediate_size, c.num_experts, c.num_experts_per_tok,
+                                 self.ep if W > 1 else None, max_t, self.router.device)
+            if W > 1:
+                self.ep._small_moe = ws
+            else:
+                M.SMALL_WORKSPACES[key] = ws
+        return ws
+
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.cfg
         T, d = x.shape
         k, E = c.num_experts_per_tok, c.num_experts
+        if x.is_cuda and x.dtype == torch.bfloat16 and T > 0:
+            ws = self._small_workspace(T)
+            if ws is not None:
+                out, idx = ws.forward(x, residual, self.router, self.gate_up_proj, self.down_proj, bool(c.norm_topk_prob))
+                self.last_routing = idx.clone()   # the workspace's copy is overwritten by the next layer
+                return out
         w, idx, _ = self.route(x)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)

@@ -75,6 +75,17 @@ def dequantize_fp8_blockwise(q: torch.Tensor, descale: torch.Tensor) -> torch.Te
     return (q.float() * ds).to(torch.bfloat16)
 
 
+def dequantize_fp8_blockwise_into(q: torch.Tensor, descale: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Expands block-128 FP8 into an existing bf16 matrix (the engine's weight buffer keeps its address)."""
+    R, C = q.shape
+    assert out.shape == q.shape and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    if use_native(q):
+        call("rlb_dequant_fp8_block128", ptr(q), q.stride(0), ptr(descale.contiguous()), ptr(out), out.stride(0), R, C, stream_ptr())
+    else:
+        out.copy_(dequantize_fp8_blockwise(q, descale))
+    return out
+
+
 def quantize_mxfp8_ref(w: torch.Tensor):
     R, C = w.shape
     assert C % 32 == 0

@@ -70,7 +70,7 @@ def _bind():
     if not _bound:
         lib.rlb_gemm_tp_gather.argtypes = [_P, _LL, _P, _LL, _I, _P, _LL, _P, _I, _I, _I, _P, _P, _I, _I, _U, _I, _D, _P, _P]
         lib.rlb_gemm_tp_scatter.argtypes = [_P, _LL, _P, _LL, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _LL, _P, _P, _I, _I, _U, _P, _D, _P, _P]
-        lib.rlb_p2p_gather_cols.argtypes = [_P, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _D, _P, _P, _P]
+        lib.rlb_p2p_gather_cols.argtypes = [_P, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _D, _P, _P, _LL, _P]
         lib.rlb_p2p_gather_cols.restype = C.c_int
         lib.rlb_gemm_tp_gather.restype = C.c_int
         lib.rlb_gemm_tp_scatter.restype = C.c_int
@@ -171,12 +171,15 @@ class TPFusedComm:
         z_local = z_local.contiguous()
         row_bytes = n * z_local.element_size()
         assert row_bytes % 16 == 0, "column slices must be a multiple of 16 bytes wide"
-        st = self._ensure("stage_l", 2 * rows * row_bytes)
+        # sized for 256 rows at the first call: decode batches of every bucket then share one stage whose two halves sit
+        # at fixed offsets (a captured graph keeps the stage's address, and calls of different sizes never overlap)
+        st = self._ensure("stage_l", 2 * max(rows, 256) * row_bytes)
+        half_bytes = (st.nbytes // 2) // 16 * 16
         if out is None:
             out = torch.empty((rows, self.world * n), dtype=z_local.dtype, device=z_local.device)
         rc = lib.rlb_p2p_gather_cols(z_local.data_ptr(), st.table, self._cflags, out.data_ptr(), out.stride(0) * out.element_size(),
                                      rows, row_bytes, self.rank, self.world, self.epoch_c_dev.data_ptr(), float(self.wait_limit_s),
-                                     self._c_scratch.data_ptr(), _L.status_word(z_local.device).data_ptr(),
+                                     self._c_scratch.data_ptr(), _L.status_word(z_local.device).data_ptr(), half_bytes,
                                      torch.cuda.current_stream().cuda_stream)
         _L.Counters.launches += 1
         if rc:

@@ -139,6 +139,147 @@ class WeightSynchronizer:
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
+    # ------------------------------------------------------------------ quantising push (FP8, 128 x 128 blocks)
+    def _prepare_fp8(self) -> None:
+        """Splits the plan: pieces of eligible linear weights made of whole 128 x 128 blocks go through the quantising
+        kernel into an FP8 arena (e4m3 bytes + one fp32 de-scale per block, per serving parameter); everything else
+        (norms, embeddings, the output head, ragged pieces) keeps the bf16 copy."""
+        from rl_b200.engine.quantized import _eligible
+        from rl_b200.ops import lib as _L
+
+        lib = _L.lib()
+        assert self.dtype == torch.bfloat16
+        params = dict(self.train_model.named_parameters())
+        serving = dict(self.serving_model.named_parameters())
+
+        def blocks_ok(op) -> bool:
+            _, (d_r, d_c) = self.layout[op.dst_param]
+            r0, c0 = divmod(op.dst_offset, op.dst_pitch)
+            return (op.dst_pitch == d_c and d_r % 128 == 0 and d_c % 128 == 0 and r0 % 128 == 0 and c0 % 128 == 0
+                    and op.rows % 128 == 0 and op.row_elems % 128 == 0 and op.src_offset % 8 == 0 and op.src_pitch % 8 == 0)
+
+        by_param: dict[str, list] = {}
+        for op in self.plan.ops:
+            by_param.setdefault(op.dst_param, []).append(op)
+        fused = {n for n, ops in by_param.items() if n in serving and _eligible(n, serving[n], "fp8") and all(blocks_ok(o) for o in ops)}
+        # FP8 arena layout (identical on every rank): per fused parameter its e4m3 bytes, then its de-scales
+        off, q_layout = 0, {}
+        for n in sorted(fused):
+            _, (r, c) = self.layout[n]
+            q_layout[n] = (off, off + r * c, r, c)
+            off += r * c + (r // 128) * (c // 128) * 4
+            off = -(-off // 256) * 256
+        self._q_bytes = max(off, 256)
+        if self.world > 1:
+            from rl_b200.parallel.symmetric import SymmetricBuffer
+
+            self._qsym = SymmetricBuffer(self._q_bytes, self.group)
+            q_arena, q_ptrs = self._qsym.tensor(torch.uint8, self._q_bytes), list(self._qsym.peer_ptrs)
+        else:
+            self._qsym = None
+            q_arena = torch.zeros(self._q_bytes, dtype=torch.uint8, device=self.device)
+            q_ptrs = [q_arena.data_ptr()]
+        self._q_arena = q_arena
+        self._q_views = {}
+        for n, (qo, so, r, c) in q_layout.items():
+            q = q_arena[qo : qo + r * c].view(torch.float8_e4m3fn).view(r, c)
+            sc = q_arena[so : so + (r // 128) * (c // 128) * 4].view(torch.float32).view(r // 128, c // 128)
+            self._q_views[n] = (q, sc)
+        # work lists
+        qdescs, qwork, descs_rest = [], [], []
+        es = 2
+        self._q_remote = set()           # fused parameters with at least one block pushed by another rank: expanded after the barrier
+        for op in self.plan.ops:
+            if op.dst_param in fused and op.src_rank != op.dst_rank and op.dst_rank == self.rank:
+                self._q_remote.add(op.dst_param)
+        BLOCKS_PER_ITEM = 8
+        total = 0
+        for op in self.plan.ops_from(self.rank):
+            if op.dst_param not in fused:
+                descs_rest.append(op)
+                continue
+            qo, so, r, c = q_layout[op.dst_param]
+            r0, c0 = divmod(op.dst_offset, op.dst_pitch)
+            src = params[op.src_param].data_ptr() + op.src_offset * es
+            dst_q = q_ptrs[op.dst_rank] + qo + op.dst_offset
+            dst_s = q_ptrs[op.dst_rank] + so + ((r0 // 128) * (c // 128) + c0 // 128) * 4
+            local = op.dst_rank == self.rank
+            dst_w = (self._arena_ptrs[op.dst_rank] + (self.layout[op.dst_param][0] + op.dst_offset) * es) if local else 0
+            src_end = op.src_offset + (op.rows - 1) * op.src_pitch + op.row_elems
+            if not (0 <= op.src_offset and src_end <= params[op.src_param].numel() and r0 + op.rows <= r and c0 + op.row_elems <= c
+                    and 0 <= op.dst_rank < max(1, self.world)):
+                raise ValueError(f"refit op out of bounds: {op}")
+            di = len(qdescs)
+            bc = op.row_elems // 128
+            qdescs.append(struct.pack("<QQQQqqii", src, dst_q, dst_s, dst_w, op.src_pitch, op.dst_pitch, c // 128, bc))
+            nb = (op.rows // 128) * bc
+            for f in range(0, nb, BLOCKS_PER_ITEM):
+                qwork.append(struct.pack("<iiii", di, f, min(BLOCKS_PER_ITEM, nb - f), 0))
+            total += op.rows * op.row_elems * es
+        assert lib.rlb_refit_qdesc_bytes() == 56 and lib.rlb_refit_qwork_bytes() == 16
+        self._qdescs = torch.frombuffer(bytearray(b"".join(qdescs) or b"\0" * 56), dtype=torch.uint8).to(self.device)
+        self._qwork = torch.frombuffer(bytearray(b"".join(qwork) or b"\0" * 16), dtype=torch.uint8).to(self.device)
+        self._num_qwork = len(qwork)
+        self._fp8_fused = fused
+        self._fp8_read_bytes = total
+        # the bf16 copies that remain: a second plan restricted to the other parameters
+        keep = self.plan
+        self.plan = type(keep)(keep.world, keep.tp_train, keep.tp_serve, [o for o in keep.ops if o.dst_param not in fused])
+        saved = (self._descs, self._work, self._num_work, self.last_bytes)
+        self._descs = None
+        self._prepare()
+        self._rest = (self._descs, self._work, self._num_work)
+        self._fp8_read_bytes += self.last_bytes
+        self._descs, self._work, self._num_work, self.last_bytes = saved
+        self.plan = keep
+        lib.rlb_refit_quant.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        lib.rlb_refit_quant.restype = C.c_int
+
+    def sync_weights_fp8(self) -> None:
+        """Refit with block-128 FP8 weights for the engine in one pass over the trainer's weights: linear weights are
+        quantised on the way (e4m3 + de-scales stored into the destination rank's FP8 arena; half the bytes of a bf16
+        push cross NVLink), the other tensors are copied. Afterwards every eligible serving parameter carries its quantised
+        form (``_rlb_q``) and the bf16 arena holds the fp8-rounded values the bf16 GEMMs compute with."""
+        if not self.native:
+            from rl_b200.engine.quantized import quantize_model
+
+            self.twin_sync()
+            quantize_model(self.serving_model, "fp8")
+            return
+        from rl_b200.ops import lib as _L
+        from rl_b200.ops import quant as Q
+
+        if getattr(self, "_qdescs", None) is None:
+            self._prepare_fp8()
+        lib = _L.lib()
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+        rd, rw, rn = self._rest
+        rc = lib.rlb_refit_copy(rd.data_ptr(), rw.data_ptr(), rn, 0, stream) if rn else 0
+        rc = rc or lib.rlb_refit_quant(self._qdescs.data_ptr(), self._qwork.data_ptr(), self._num_qwork, 0, stream)
+        _L.Counters.launches += 2
+        if rc:
+            raise RuntimeError(f"quantising refit failed with code {rc}")
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+        serving = dict(self.serving_model.named_parameters())
+        for n in self._fp8_fused:
+            q, sc = self._q_views[n]
+            p = serving[n]
+            if n in self._q_remote:      # blocks that arrived over NVLink as fp8: expand into the bf16 arena here
+                Q.dequantize_fp8_blockwise_into(q, sc, p.data)
+            p._rlb_q = ("fp8", q, sc)
+            p._rlb_q_bf16 = p.data
+        # eligible weights whose pieces were not whole blocks took the bf16 copy: quantise them in place
+        from rl_b200.engine.quantized import _eligible
+
+        for n, p in serving.items():
+            if n not in self._fp8_fused and _eligible(n, p, "fp8"):
+                q, sc = Q.quantize_fp8_blockwise(p.data)
+                p._rlb_q = ("fp8", q, sc)
+                p._rlb_q_bf16 = Q.dequantize_fp8_blockwise(q, sc)
+
     # ------------------------------------------------------------------ collective twin / CPU path
     @torch.no_grad()
     def twin_sync(self) -> None:
@@ -148,5 +289,8 @@ class WeightSynchronizer:
         load_hf_tensors(self.serving_model, full.get)
 
     def close(self) -> None:
+        if getattr(self, "_qsym", None) is not None:
+            self._qsym.close()
+            self._qsym = None
         if self._sym is not None:
             self._sym.close()

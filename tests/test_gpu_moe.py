@@ -79,3 +79,86 @@ def test_moe_model_matches_fp32_reference(native_lib):
     assert (lp.detach().cpu() - lp_ref).abs().max().item() < 0.06
     g = m.layers[0].mlp.gate_up_proj.grad
     assert g is not None and torch.isfinite(g).all() and g.abs().sum().item() > 0
+
+
+def test_route_topk_kernel_matches_torch(native_lib):
+    from rl_b200.ops.moe_ops import route_topk, route_topk_ref
+
+    torch.manual_seed(0)
+    for T, E, k, renorm in [(37, 128, 8, True), (5, 64, 2, False), (300, 8, 2, True), (64, 256, 16, True)]:
+        z = (torch.randn(T, E, device="cuda") * 2).to(torch.bfloat16)
+        w, idx = route_topk(z, k, renorm)
+        w_ref, idx_ref = route_topk_ref(z, k, renorm)
+        # equal probabilities (bf16 logits collide often) may be picked in another order: compare the weights, and the
+        # experts through the probabilities they carry
+        assert torch.allclose(w, w_ref, rtol=1e-4, atol=1e-6), (T, E, k)
+        p = torch.softmax(z.float(), -1)
+        assert torch.allclose(p.gather(1, idx.long()), p.gather(1, idx_ref.long()), rtol=1e-4, atol=1e-7)
+        assert (idx.sort(1).values[:, 1:] != idx.sort(1).values[:, :-1]).all()     # k distinct experts per token
+
+
+@pytest.mark.parametrize("T", [1, 48, 256])
+def test_small_token_moe_layer_matches_sorted_path(native_lib, T):
+    """The few-token layer (five kernels + two grouped GEMMs, no host visit) against the sort / scatter path of training."""
+    from rl_b200.models.config import preset
+    from rl_b200.models.moe import MoEMLP
+    from rl_b200.ops.lib import check_status
+
+    cfg = preset("tiny-llama-oracle", num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, norm_topk_prob=True, hidden_size=256)
+    torch.manual_seed(1)
+    m = MoEMLP(cfg, torch.bfloat16, "cuda")
+    with torch.no_grad():
+        m.router.copy_(torch.randn_like(m.router) * 0.5)
+        m.gate_up_proj.copy_(torch.randn_like(m.gate_up_proj) * 0.06)
+        m.down_proj.copy_(torch.randn_like(m.down_proj) * 0.06)
+    x = torch.randn(T, 256, device="cuda").to(torch.bfloat16)
+    res = torch.randn(T, 256, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        y_small = m(x, res)
+        idx_small = m.last_routing.clone()
+        assert m._small_workspace(T) is not None
+    with torch.enable_grad():   # the training path (the few-token path is inference only)
+        y_sorted = m(x, res).detach()
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    assert torch.equal(idx_small.long().sort(1).values, m.last_routing.long().sort(1).values)
+    # fp32 statement with the same routing
+    p = torch.softmax((x.float() @ m.router.float().t()).to(torch.bfloat16).float(), -1)
+    w = p.gather(1, idx_small.long())
+    w = w / w.sum(-1, keepdim=True)
+    ref = res.float().clone()
+    for t in range(T):
+        for j in range(cfg.num_experts_per_tok):
+            e = int(idx_small[t, j])
+            h = x[t].float() @ m.gate_up_proj[e].float().t()
+            a = (torch.nn.functional.silu(h[:128]) * h[128:]).to(torch.bfloat16).float()
+            ref[t] += w[t, j] * (a @ m.down_proj[e].float().t())
+    assert (y_small.float() - ref).abs().max().item() < 0.05, (y_small.float() - ref).abs().max().item()
+    assert (y_small.float() - y_sorted.float()).abs().max().item() < 0.05
+
+
+def test_moe_engine_decodes_from_cuda_graphs(native_lib):
+    """A mixture-of-experts model decodes through captured graphs and produces the tokens of the step-by-step engine."""
+    from rl_b200.engine.engine import GenerationEngine, SamplingParams
+    from rl_b200.models.config import preset
+    from rl_b200.models.transformer import build_model
+    from rl_b200.ops.lib import check_status
+
+    cfg = preset("tiny-llama-oracle", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, norm_topk_prob=True,
+                 hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128, vocab_size=2048)
+    m = build_model(cfg, device="cuda", dtype=torch.bfloat16, seed=7)
+    prompts = [[int(t) for t in torch.randint(1, 2048, (n,))] for n in (9, 17, 5, 30)]
+    sp = SamplingParams(max_new_tokens=24, greedy=True)
+    outs = {}
+    for graphs in (True, False):
+        eng = GenerationEngine(m, block_size=16, kv_cache_tokens=4096, max_running=8, use_cuda_graphs=graphs)
+        outs[graphs] = [(r.out_tokens, r.out_logprobs) for r in eng.generate(prompts, sp)]
+        if graphs:
+            assert eng.use_graphs and len(eng._graphs) >= 1
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    same = sum(a[0] == b[0] for a, b in zip(outs[True], outs[False]))
+    assert same >= 3, outs    # the same kernels run in both modes; a greedy near-tie may still split one sequence
+    for a, b in zip(outs[True], outs[False]):
+        if a[0] == b[0]:
+            assert max(abs(x - y) for x, y in zip(a[1], b[1])) < 0.05

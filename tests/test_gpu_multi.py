@@ -246,6 +246,22 @@ def _refit_worker(rank, world, port):
             ws.twin_sync()
             torch.cuda.synchronize()
             assert torch.equal(got, ws.arena), (tp_train, tp_serve, it)
+        # quantising refit: one kernel writes e4m3 + de-scales (over NVLink for remote pieces); the result must equal
+        # quantising the re-sharded bf16 copy afterwards
+        from rl_b200.ops import quant as Q
+
+        ws.twin_sync()
+        want = {n: Q.quantize_fp8_blockwise(p.data) for n, p in ws.serving_model.named_parameters()
+                if p.dim() == 2 and n.rsplit(".", 1)[-1] in ("qkv_proj", "o_proj", "gate_up_proj", "down_proj")}
+        ws.arena.zero_()
+        ws.sync_weights_fp8()
+        torch.cuda.synchronize()
+        assert len(ws._fp8_fused) == len(want) > 0, (tp_train, tp_serve, len(ws._fp8_fused), len(want))
+        for n, p in ws.serving_model.named_parameters():
+            if n in want:
+                kind, q, sc = p._rlb_q
+                assert torch.equal(q.view(torch.uint8), want[n][0].view(torch.uint8)) and torch.equal(sc, want[n][1]), (tp_train, tp_serve, n)
+                assert torch.equal(p._rlb_q_bf16, Q.dequantize_fp8_blockwise(q, sc)), n
         sent, recv = ws.plan.bytes_over_link(rank)
         if tp_train == 1:
             assert sent == 0       # data-parallel training: every serving shard is cut from the rank's own copy
@@ -318,6 +334,60 @@ def _ep_worker(rank, world, port):
 def test_expert_parallel_fused_dispatch_vs_nccl(native_lib, world):
     _need(world)
     mp.spawn(_ep_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _ep_gen_worker(rank, world, port):
+    """Expert-parallel generation with uneven work per rank: the captured few-token MoE path (peer-memory gather and
+    reduce, ranks in lock step) against the dispatch / combine path over NCCL, run eagerly."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=0, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128, qk_norm=True, num_experts=8, num_experts_per_tok=2,
+                     moe_intermediate_size=256, norm_topk_prob=True)
+    p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=4 * world, train_micro_batch_size=2, max_total_sequence_length=256,
+                          parallel=dict(expert_parallel_size=world),
+                          generation=dict(max_new_tokens=20 + 11 * rank, temperature=1.0, stop_token_ids=[], kv_cache_tokens=8192,
+                                          block_size=16, max_running=16),
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3))),
+                     model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, init_optimizer=False, seed=3)
+    g = torch.Generator().manual_seed(10 + rank)
+    n = 2 + 3 * rank
+    ids = torch.randint(1, 4096, (n, 24), generator=g)
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.full((n,), 24))
+    gen = p.build_generation()
+    gen.prepare_for_generation()
+    fast = gen.generate(data, greedy=True)
+    eng = gen.engine
+    assert eng.use_graphs and len(eng._graphs) >= 1, "the expert-parallel decode step was not captured"
+    comm, p.ep.comm = p.ep.comm, None          # NCCL all-to-all path: no peer kernels, no graphs
+    eng.use_graphs = False
+    slow = gen.generate(data, greedy=True)
+    p.ep.comm = comm
+    gen.finish_generation()
+    torch.cuda.synchronize()
+    assert check_status() == 0
+    a, b = fast["output_ids"], slow["output_ids"]
+    assert a.shape == b.shape
+    same = sum(int(torch.equal(x, y)) for x, y in zip(a, b))
+    assert same >= n - 1, (rank, same, n)      # a greedy near-tie may split one sequence
+    la, lb = fast["logprobs"], slow["logprobs"]
+    for x, y, u, v in zip(a, b, la, lb):
+        if torch.equal(x, y):
+            assert (u - v).abs().max().item() < 0.08
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_generation_graphs_vs_dispatch(native_lib, world):
+    _need(world)
+    mp.spawn(_ep_gen_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 def _split_job_worker(rank, world, port, steps):

@@ -141,3 +141,36 @@ def test_mxfp8_training_linear_matches_quantised_statement(native_lib):
         assert check_status() == 0
     finally:
         F.Fp8Training.configure(None)
+
+
+@pytest.mark.gpu
+def test_quantising_refit_on_one_gpu_matches_copy_then_quantise(native_lib):
+    """The refit pass that quantises on the way (one kernel: bf16 block -> amax -> e4m3 + de-scale + fp8-rounded bf16) against
+    the bf16 re-shard copy followed by the block-128 quantiser."""
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.transformer import build_model
+    from rl_b200.ops import quant as Q
+    from rl_b200.ops.lib import check_status
+    from rl_b200.parallel.tensor import TP
+    from rl_b200.refit.synchronizer import WeightSynchronizer
+
+    mc = ModelConfig(model_type="qwen3", vocab_size=1024, hidden_size=256, intermediate_size=640, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, head_dim=128, qk_norm=True, tie_word_embeddings=False)
+    train = build_model(mc, device="cuda", dtype=torch.bfloat16, seed=3, tp=TP(None, 0, 1))
+    ws = WeightSynchronizer(train, mc, 1)
+    ws.sync_weights()
+    want = {n: Q.quantize_fp8_blockwise(p.data) for n, p in ws.serving_model.named_parameters()
+            if p.dim() == 2 and n.rsplit(".", 1)[-1] in ("qkv_proj", "o_proj", "gate_up_proj", "down_proj")}
+    plain = {n: p.data.clone() for n, p in ws.serving_model.named_parameters()}
+    ws.arena.zero_()
+    ws.sync_weights_fp8()
+    torch.cuda.synchronize()
+    assert check_status() == 0 and len(ws._fp8_fused) == len(want) == 8
+    for n, p in ws.serving_model.named_parameters():
+        if n in want:
+            _, q, sc = p._rlb_q
+            assert torch.equal(q.view(torch.uint8), want[n][0].view(torch.uint8)) and torch.equal(sc, want[n][1]), n
+            assert torch.equal(p.data, Q.dequantize_fp8_blockwise(q, sc)), n      # the bf16 arena holds the fp8-rounded weights
+        else:
+            assert torch.equal(p.data, plain[n]), n                                # norms, embeddings, head: plain copies
+    ws.close()

@@ -129,14 +129,14 @@ LORA = dict(enabled=F(bool), dim=F(int), alpha=F(int, float), dropout=F(float, i
             match_all_linear=F(bool), dropout_position=F(str), lora_A_init=F(str), use_triton=F(bool), rank=F(int),
             lora_A_init_method=F(str), lora_B_init_method=F(str), a2a_experimental=F(bool), lora_dtype=F(str))
 
+FP8 = dict(enabled=F(bool), fp8=F(str, choices=("e4m3", "hybrid")), fp8_recipe=F(str, choices=("mxfp8", "blockwise", "tensorwise", "delayed")),
+           fp8_param=F(bool), force_clear_fp8_caches=F(bool))
+
 DTENSOR = dict(enabled=F(bool), _v2=F(bool), cpu_offload=F(bool), sequence_parallel=F(bool), activation_checkpointing=F(bool),
                tensor_parallel_size=F(int), context_parallel_size=F(int), expert_parallel_size=F(int), custom_parallel_plan=F(str),
                clear_cache_every_n_steps=F(int), lora_cfg=F(dict, sub=LORA), env_vars=F(dict), automodel_kwargs=F(dict),
                data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int), defer_fsdp_grad_sync=F(bool),
                moe_parallelizer=F(dict), fp8_cfg=F(dict, sub=FP8))
-
-FP8 = dict(enabled=F(bool), fp8=F(str, choices=("e4m3", "hybrid")), fp8_recipe=F(str, choices=("mxfp8", "blockwise", "tensorwise", "delayed")),
-           fp8_param=F(bool), force_clear_fp8_caches=F(bool))
 
 MEGATRON = dict(enabled=F(bool), tensor_model_parallel_size=F(int), pipeline_model_parallel_size=F(int), context_parallel_size=F(int),
                 expert_model_parallel_size=F(int), expert_tensor_parallel_size=F(int), sequence_parallel=F(bool),

@@ -551,34 +551,44 @@ class CausalLM(nn.Module):
         """Log-probabilities under the sampler's *processed* distribution (temperature, then top-k / top-p): what the
         importance ratio must use when rollouts were sampled with those filters
         (nemo_rl/algorithms/logits_sampling_utils.py:112-285). The logits are materialised ``chunk_rows`` rows at a time;
-        with tensor parallelism the vocabulary slices of a chunk are gathered first."""
+        with tensor parallelism an all-to-all turns the chunk's vocabulary shards into row shards, so no rank holds
+        ``[T, V]`` (nemo_rl/distributed/model_utils.py:383-510)."""
         from rl_b200.algorithms.sampling_utils import apply_top_k_top_p
 
-        if self.cp is not None or (self.tp.world > 1 and self.tp.sequence_parallel) or self.sharder is not None:
-            raise NotImplementedError("top-k / top-p training log-probabilities need full rows and resident weights on every rank "
-                                      "(no sequence / context parallelism, no fully sharded parameters)")
-        h = self.hidden_states(batch, h_in)
         ids = batch.input_ids.long()
         T = ids.shape[0]
         targets = torch.roll(ids, -1)
-        out = []
-        for r0 in range(0, T, chunk_rows):
-            hc = h[r0 : r0 + chunk_rows]
-            if self.tp.world == 1:
-                z = F.linear(hc, self.output_weight).float()
-            else:
-                from rl_b200.parallel.tensor import gather_cols
+        inv_t = temperature if temperature > 0 else 1.0
 
-                z = gather_cols(column_linear(hc, self.output_weight, None, self.tp), self.tp).float()
-            z = z / (temperature if temperature > 0 else 1.0)
-            z, _ = apply_top_k_top_p(z, top_k, top_p)
-            lp = torch.log_softmax(z, dim=-1).gather(-1, targets[r0 : r0 + chunk_rows, None])[:, 0]
-            out.append(torch.where(torch.isfinite(lp), lp, torch.full_like(lp, -1e4)))   # a token outside the kept set
-        lp_rows = torch.cat(out)
+        def score_rows(hr, tg, w):   # rows with the whole vocabulary on this rank
+            out = []
+            for r0 in range(0, hr.shape[0], chunk_rows):
+                z = F.linear(hr[r0 : r0 + chunk_rows], w).float() / inv_t
+                z, _ = apply_top_k_top_p(z, top_k, top_p)
+                lp = torch.log_softmax(z, dim=-1).gather(-1, tg[r0 : r0 + chunk_rows, None])[:, 0]
+                out.append(torch.where(torch.isfinite(lp), lp, torch.full_like(lp, -1e4)))   # a token outside the kept set
+            return torch.cat(out)
+
+        if self.sharder is not None:      # fully sharded parameters: the head unit is gathered for the duration of the call
+            hh = self.run_layers(self.embed(batch), batch)
+            lp_rows = self.sharder.run("head", lambda x: score_rows(F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), targets, self.output_weight), hh)
+        else:
+            h = self.hidden_states(batch, h_in)
+            if self.cp is not None:       # context parallel: every rank scores its own rows, results return to stream order
+                from rl_b200.parallel.context import gather_to_stream
+
+                lp_rows = gather_to_stream(score_rows(h, targets[self.cp.local_index(T, ids.device)], self.output_weight), self.cp)
+            elif self.tp.world == 1:
+                lp_rows = score_rows(h, targets, self.output_weight)
+            else:                         # vocabulary parallel (with or without sequence parallelism): no [T, V] anywhere
+                from rl_b200.parallel.vocab import vocab_parallel_filtered_logprobs
+
+                lp_rows = vocab_parallel_filtered_logprobs(h, self.output_weight, targets, self.tp, temperature, top_k, top_p, chunk_rows)
+        dev = lp_rows.device
         starts = batch.cu_seqlens[:-1].long()
-        is_start = torch.zeros(T, dtype=torch.bool, device=h.device)
+        is_start = torch.zeros(T, dtype=torch.bool, device=dev)
         is_start[starts[starts < T]] = True
-        logp = torch.zeros(T, dtype=torch.float32, device=h.device)
+        logp = torch.zeros(T, dtype=torch.float32, device=dev)
         logp[1:] = torch.where(~is_start[1:], lp_rows[:-1], torch.zeros_like(lp_rows[:-1]))
         return logp
 

@@ -145,3 +145,77 @@ def vocab_parallel_topk(logits_shard: torch.Tensor, k: int, tp: TP, vocab_start:
 def vocab_parallel_argmax(logits_shard: torch.Tensor, tp: TP, vocab_start: int) -> torch.Tensor:
     """Global argmax token id per row (greedy decoding over a sharded vocabulary)."""
     return vocab_parallel_topk(logits_shard, 1, tp, vocab_start)[1][:, 0]
+
+
+# ------------------------------------------------------------------------- log-probabilities under top-k / top-p
+class _VocabToRows(torch.autograd.Function):
+    """Vocabulary-parallel logits [R, V / tp] (all rows, this rank's columns) -> row-parallel logits [R / tp, V] (this
+    rank's rows, all columns) with one all-to-all; the backward pass is the reverse exchange
+    (the vocab <-> sequence all-to-all of nemo_rl/distributed/model_utils.py:2465-2565)."""
+
+    @staticmethod
+    def forward(ctx, z, tp: TP):
+        R, n = z.shape
+        W = tp.world
+        assert R % W == 0
+        ctx.tp, ctx.shape = tp, (R, n)
+        send = z.reshape(W, R // W, n).contiguous()                  # chunk j: the rows rank j will own
+        recv = torch.empty_like(send)                                # chunk i: my rows, rank i's columns
+        dist.all_to_all_single(recv.view(-1), send.view(-1), group=tp.group)
+        return recv.permute(1, 0, 2).reshape(R // W, W * n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        tp = ctx.tp
+        R, n = ctx.shape
+        W = tp.world
+        send = dy.reshape(R // W, W, n).permute(1, 0, 2).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv.view(-1), send.view(-1), group=tp.group)
+        return recv.reshape(R, n), None
+
+
+def vocab_parallel_filtered_logprobs(h: torch.Tensor, w_shard: torch.Tensor, targets: torch.Tensor, tp: TP, temperature: float,
+                                     top_k, top_p, chunk_rows: int = 2048) -> torch.Tensor:
+    """log p(target) under the sampler's processed distribution (temperature, top-k, then top-p) with a vocabulary-parallel
+    output projection, without any rank ever holding ``[T, V]``: ``chunk_rows`` rows at a time, each rank projects the
+    chunk onto its vocabulary slice, an all-to-all turns the column shards into row shards with the full vocabulary,
+    every rank filters and scores its rows, and the per-row results are gathered. ``h``: all rows (or this rank's rows
+    when ``tp.sequence_parallel``); ``targets`` [T]. Returns [T] fp32, -1e4 where the target is outside the kept set.
+    (DistributedLogprobWithSampling, nemo_rl/distributed/model_utils.py:383-510.)"""
+    from rl_b200.algorithms.sampling_utils import apply_top_k_top_p
+    from rl_b200.parallel.tensor import column_linear, gather_rows
+
+    W = tp.world
+    T = targets.shape[0]
+    rows_tp = TP(tp.group, tp.rank, W)
+    inv_t = temperature if temperature > 0 else 1.0
+
+    def score(z, tg):
+        z, _ = apply_top_k_top_p(z / inv_t, top_k, top_p)
+        lp = torch.log_softmax(z, dim=-1).gather(-1, tg.long()[:, None])[:, 0]
+        return torch.where(torch.isfinite(lp), lp, torch.full_like(lp, -1e4))
+
+    out = []
+    if tp.sequence_parallel:
+        # h holds this rank's rows: the gathering projection returns the chunk's rows rank-major, so the all-to-all hands
+        # every rank exactly its own rows back, now with the whole vocabulary
+        per = h.shape[0]
+        mine = targets[tp.rank * per : (tp.rank + 1) * per]
+        step = max(1, chunk_rows // W)
+        for r0 in range(0, per, step):
+            z = _VocabToRows.apply(column_linear(h[r0 : r0 + step], w_shard, None, tp).float(), tp)
+            out.append(score(z, mine[r0 : r0 + step]))
+        return gather_rows(torch.cat(out), rows_tp)
+    step = max(W, chunk_rows // W * W)
+    for r0 in range(0, T, step):
+        hc, tg = h[r0 : r0 + step], targets[r0 : r0 + step]
+        n = hc.shape[0]
+        pad = (-n) % W
+        if pad:
+            hc = torch.cat([hc, hc.new_zeros((pad, hc.shape[1]))])
+            tg = torch.cat([tg, tg.new_zeros(pad)])
+        z = _VocabToRows.apply(column_linear(hc, w_shard, None, tp).float(), tp)           # [rows / W, V]
+        per = (n + pad) // W
+        out.append(gather_rows(score(z, tg[tp.rank * per : (tp.rank + 1) * per]), rows_tp)[:n])
+    return torch.cat(out)

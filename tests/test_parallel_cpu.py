@@ -271,6 +271,37 @@ def test_context_parallel_worker_matches_single_rank(world):
         assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)
 
 
+def _filtered_worker(rank, world, par):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.models.config import preset
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    w = PolicyWorker(_worker_cfg(**par), model_cfg=mc, init_reference_model=False, seed=4)
+    w.train_top_k, w.train_top_p = 50, 0.9
+    data = _train_data()
+    lp = w.get_logprobs(data)["logprobs"]
+    out = w.train(data, NLLLossFn(), gbs=4, mbs=2)
+    lp2 = w.get_logprobs(data)["logprobs"]
+    return dict(lp=lp.tolist(), lp2=lp2.sum().item(), loss=float(out["loss"][0]), gn=float(out["grad_norm"][0]))
+
+
+@pytest.mark.parametrize("par", [dict(tensor_parallel_size=2), dict(tensor_parallel_size=2, sequence_parallel=True), dict(context_parallel_size=2)])
+def test_filtered_logprobs_under_sharded_layouts_match_single_rank(par):
+    """Training log-probabilities under top-k / top-p with a vocabulary-parallel head (all-to-all to row shards, no [T, V]
+    on any rank), with sequence parallelism and with context parallelism, against one rank holding everything."""
+    from rl_b200.parallel.state import reset_parallel
+
+    reset_parallel()
+    ref = _filtered_worker(0, 1, {})
+    reset_parallel()
+    out = _spawn(_filtered_worker, 2, par)
+    for r, m in out.items():
+        assert torch.allclose(torch.tensor(m["lp"]), torch.tensor(ref["lp"]), atol=2e-4), (r, par)
+        assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4) and m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m["loss"], ref["loss"])
+        assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4)
+
+
 def _moe_cfg():
     from rl_b200.models.config import preset
 

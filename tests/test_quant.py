@@ -132,7 +132,7 @@ def test_mxfp8_training_linear_matches_quantised_statement(native_lib):
     try:
         outs = {}
         for dev in ("cpu", "cuda"):
-            xd, wd = x.to(dev).requires_grad_(), w.to(dev).requires_grad_()
+            xd, wd = x.detach().clone().to(dev).requires_grad_(), w.detach().clone().to(dev).requires_grad_()
             y = F.linear(xd, wd)
             y.backward(dy.to(dev))
             outs[dev] = (y.detach().float().cpu(), xd.grad.float().cpu(), wd.grad.float().cpu())

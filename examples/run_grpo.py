@@ -36,6 +36,13 @@ def main(argv=None):
             from rl_b200.algorithms.async_grpo import async_grpo_train
 
             async_grpo_train(policy, generation, loader, tokenizer, loss_fn, task_to_env, logger, checkpointer, save_state, cfg)
+        elif (cfg.get("data_plane") or {}).get("enabled"):
+            # samples travel through the data plane between rollout and optimizer step (the reference picks its
+            # TransferQueue-mediated trainer by the same key)
+            from rl_b200.algorithms.grpo_sync import grpo_train_sync
+
+            grpo_train_sync(policy, generation, loader, val_loader, tokenizer, loss_fn, task_to_env, val_task_to_env, logger,
+                            checkpointer, save_state, cfg)
         else:
             grpo.grpo_train(policy, generation, loader, val_loader, tokenizer, loss_fn, task_to_env, val_task_to_env, logger,
                             checkpointer, save_state, cfg)

@@ -155,3 +155,55 @@ def test_observed_data_plane_counts_events():
     assert len(dp.get(["a", "b"])) == 2 and dp.delete(["a"]) == 1
     st = dp.stats()
     assert st["put_calls"] == 2 and st["get_items"] == 2 and st["delete_calls"] == 1 and st["resident_samples"] == 1 and st["get_seconds"] >= 0
+
+
+def _sync_cfg(tmp_path, steps, plane=True):
+    cfg = {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=4, max_num_steps=steps, val_period=0, seed=0),
+           "loss_fn": dict(use_importance_sampling_correction=False, reference_policy_kl_penalty=0.01),
+           "policy": dict(precision="float32", train_global_batch_size=16, train_micro_batch_size=8, logprob_batch_size=16,
+                          max_total_sequence_length=48, max_grad_norm=1.0,
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=5e-3, weight_decay=0.0)),
+                          generation=dict(max_new_tokens=8, temperature=1.0, stop_token_ids=[], kv_cache_tokens=4096, block_size=8, max_running=32)),
+           "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    if plane:
+        cfg["data_plane"] = dict(enabled=True, backend="local")
+    return cfg
+
+
+def test_grpo_over_the_data_plane_matches_the_in_memory_trainer(tmp_path):
+    """The data-plane-mediated trainer (rollout actor -> records, driver reads small fields only, policy fetches by key) takes
+    the same optimizer steps as ``grpo_train`` and leaves the plane empty after every step."""
+    from rl_b200.algorithms.grpo_sync import BatchMeta, PlanePolicy, grpo_train_sync
+
+    mc = ModelConfig(vocab_size=32, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    hist = {}
+    for mode in ("plane", "memory"):
+        ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+        policy, gen, loader, _, loss_fn, logger, ck, ss, cfg = grpo.setup(_sync_cfg(tmp_path / mode, 3, mode == "plane"), None, ds, None, env, model_cfg=mc)
+        h = []
+        if mode == "plane":
+            plane = LocalDataPlane()
+            grpo_train_sync(policy, gen, loader, None, None, loss_fn, env, None, logger, ck, ss, cfg, data_plane=plane,
+                            step_callback=lambda s, m: h.append(m["train"]))
+            assert plane.stats()["resident_samples"] == 0 and plane.stats()["puts"] == 3 * 16
+            assert all(x["data_plane_resident_peak"] == 16 for x in h)
+        else:
+            grpo.grpo_train(policy, gen, loader, None, None, loss_fn, env, None, logger, ck, ss, cfg, step_callback=lambda s, m: h.append(m["train"]))
+        hist[mode] = h
+    assert len(hist["plane"]) == len(hist["memory"]) == 3
+    for a, b in zip(hist["plane"], hist["memory"]):
+        assert a["loss"] == pytest.approx(b["loss"], rel=1e-4, abs=1e-6) and a["reward"] == pytest.approx(b["reward"], rel=1e-5)
+        assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=1e-3)
+
+    # the facade's streaming form: a step fed in two pieces equals one call
+    with pytest.raises(ValueError):
+        grpo_train_sync(policy, gen, loader, None, None, loss_fn, env, None, logger, ck, dict(ss), _sync_cfg(tmp_path, 1, plane=False))
+    pol = PlanePolicy(policy, LocalDataPlane())
+    pol.begin_train_step(loss_fn)
+    with pytest.raises(AssertionError):
+        pol.begin_train_step(loss_fn)
+    pol.abort_train_step()
+    m = BatchMeta("p", ["a", "b", "c"], [3, 4, 5], ["g0", "g0", "g1"], {"x"})
+    assert m.select([0, 2]).keys == ["a", "c"] and m.size == 3 and [s.num_tokens for s in m.sample_metas()] == [3, 4, 5]

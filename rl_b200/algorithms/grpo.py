@@ -344,8 +344,10 @@ def validate(policy, generation, val_loader, tokenizer, task_to_env, step: int, 
 
 # ---------------------------------------------------------------------------------------------- the loop
 def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_fn, task_to_env, val_task_to_env, logger,
-               checkpointer, save_state: dict, master_config: dict, step_callback: Optional[Callable[[int, dict], None]] = None) -> dict:
-    """Runs GRPO until ``max_num_steps`` / ``max_num_epochs``. Returns the last step's metrics."""
+               checkpointer, save_state: dict, master_config: dict, step_callback: Optional[Callable[[int, dict], None]] = None,
+               teacher_groups=None) -> dict:
+    """Runs GRPO until ``max_num_steps`` / ``max_num_epochs``. Returns the last step's metrics. ``teacher_groups``:
+    ``(alias -> TeacherGroup, alias -> serving alias)`` for on-policy distillation (built from the config when absent)."""
     rank, world = _world()
     cfg = master_config
     g, pcfg = cfg["grpo"], cfg["policy"]
@@ -361,6 +363,13 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
     total_steps = save_state["total_steps"]
     val_task_to_env = val_task_to_env or task_to_env
     last_metrics: dict = {}
+    # on-policy distillation (grpo.adv_estimator.name: opd): frozen teachers, one per distinct checkpoint
+    opd_groups = teacher_groups
+    opd_metrics: dict = {}
+    if opd_groups is None and (g.get("adv_estimator") or {}).get("name") == "opd":
+        from rl_b200.algorithms import opd as _opd
+
+        opd_groups = _opd.create_teacher_groups(cfg, tokenizer, getattr(policy, "model_cfg", None))
 
     if g["val_at_start"] and step == 0:
         validate(policy, generation, val_dataloader, tokenizer, val_task_to_env, 0, cfg, logger)
@@ -434,10 +443,18 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                 # ---- advantages
                 with timer.time("advantage_calculation"):
                     tm = train_data["token_mask"]
+                    extra = {}
+                    if opd_groups is not None:   # on-policy distillation: every sample is scored by its agent's teacher
+                        from rl_b200.algorithms import opd as _opd
+
+                        with timer.time("teacher_logprob_inference"):
+                            agents = repeated.get("agent_ref") or repeated.get("task_name") or [None] * train_data.size
+                            extra["teacher_logprobs"], opd_metrics = _opd.compute_teacher_logprobs(
+                                train_data, agents, opd_groups[0], opd_groups[1], _opd.opd_cfg(cfg))
                     adv = adv_estimator.compute_advantage(
                         prompt_ids, rewards, tm, valid_mask=torch.ones_like(rewards),
                         reward_components=repeated.get("reward_components"), logprobs_policy=train_data["prev_logprobs"],
-                        logprobs_reference=train_data["reference_policy_logprobs"], dp_group=_dp_group())
+                        logprobs_reference=train_data["reference_policy_logprobs"], dp_group=_dp_group(), **extra)
                     if isinstance(adv, tuple):
                         adv = adv[0]
                     lo, hi = g["advantage_clip_low"], g["advantage_clip_high"]
@@ -471,6 +488,7 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                 "mean_abs_advantage": counts["adv_abs_sum"] / max(1.0, counts["valid_tokens"]),
                 **{k: v for k, v in rollout_metrics.items() if isinstance(v, (int, float))},
                 **mask_metrics,
+                **opd_metrics, **(getattr(adv_estimator, "last_metrics", None) or {}),
             })
             save_state.update(current_step=step, total_steps=total_steps, current_epoch=epoch,
                               consumed_samples=save_state["consumed_samples"] + int(counts["n"]),

@@ -1,5 +1,6 @@
 """PPO, on-policy distillation and off-policy (async) GRPO loops on CPU with tiny models."""
 
+import pytest
 import torch
 
 from rl_b200.algorithms import async_grpo, distillation, grpo, ppo
@@ -124,3 +125,51 @@ def test_async_ppo_trains_on_stale_trajectories(tmp_path):
     ppo.async_ppo_train(policy, value, gen, loader, None, pl, vl, env, logger, ck, ss, cfg, step_callback=lambda s, m: hist.append(m["train"]))
     assert len(hist) == 4 and max(h["trajectory_age"] for h in hist) >= 1 and max(h["trajectory_age"] for h in hist) <= 2
     assert all(torch.isfinite(torch.tensor(h["value_loss"])) for h in hist) and ss["weight_version"] == 4
+
+
+def test_on_policy_distillation_routes_samples_to_teachers(tmp_path):
+    """GRPO with the OPD estimator: two agent aliases share one teacher checkpoint (de-duplicated into one frozen worker), the
+    advantage is teacher - student log-probability, and a student distilled from a teacher moves towards it."""
+    from rl_b200.algorithms import grpo, opd
+    from rl_b200.data.datasets.synthetic import RandomTokenPromptDataset
+    from rl_b200.environments.synthetic import TokenFractionEnv
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.policy.worker import PolicyWorker
+
+    ocfg = dict(teacher_model_by_agent_name={"synthetic": "ckpt-A", "other": "ckpt-A", "third": "ckpt-B"}, default_teacher_alias="synthetic",
+                non_colocated_teachers=dict(enabled=False, default_teacher_cfg=dict(micro_batch_size=4, some_override=1),
+                                            teacher_overrides=dict(third=dict(precision="float32"))))
+    tcs = opd.create_teacher_configs(ocfg)
+    assert [t.alias for t in tcs] == ["synthetic", "third"] and tcs[0].micro_batch_size == 4 and tcs[0].overrides == {"some_override": 1}
+    assert tcs[1].precision == "float32" and opd.alias_to_group_alias(ocfg) == {"synthetic": "synthetic", "other": "synthetic", "third": "third"}
+    assert opd.resolve_teacher_aliases(["other", "nobody"], ocfg["teacher_model_by_agent_name"], "synthetic") == ["other", "synthetic"]
+    with pytest.raises(KeyError):
+        opd.resolve_teacher_aliases(["nobody"], ocfg["teacher_model_by_agent_name"], None)
+    m = opd.teacher_routing_metrics(["synthetic", "other", "third"], ocfg["teacher_model_by_agent_name"])
+    assert m["on_policy_distillation/teacher_alias_unique"] == 3 and m["on_policy_distillation/teacher_model_unique"] == 2
+
+    mc = ModelConfig(vocab_size=32, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    cfg = {"grpo": dict(num_prompts_per_step=4, num_generations_per_prompt=4, max_num_steps=40, val_period=0, seed=0,
+                        adv_estimator=dict(name="opd", opd_coef=1.0)),
+           "on_policy_distillation": dict(teacher_model_by_agent_name={"synthetic": "ckpt-A"}),
+           "loss_fn": dict(reference_policy_kl_penalty=0.0),
+           "policy": dict(precision="float32", train_global_batch_size=16, train_micro_batch_size=8, logprob_batch_size=16,
+                          max_total_sequence_length=48, max_grad_norm=1.0,
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=2e-2, weight_decay=0.0)),
+                          generation=dict(max_new_tokens=8, temperature=1.0, stop_token_ids=[], kv_cache_tokens=4096, block_size=8, max_running=32)),
+           "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    policy, gen, loader, _, loss_fn, logger, ck, ss, cfg = grpo.setup(cfg, None, ds, None, env, model_cfg=mc)
+    teacher = PolicyWorker(cfg["policy"], model_cfg=mc, init_optimizer=False, init_reference_model=False, seed=123)
+    with torch.no_grad():   # a teacher with opinions: sharpen its output distribution
+        teacher.model.output_weight.mul_(12.0)
+    groups = ({"synthetic": opd.TeacherGroup(opd.TeacherConfig("synthetic", "ckpt-A"), cfg["policy"], worker=teacher)}, {"synthetic": "synthetic"})
+    assert all(not p.requires_grad for p in teacher.model.parameters())
+    hist = []
+    grpo.grpo_train(policy, gen, loader, None, None, loss_fn, env, None, logger, ck, ss, cfg, step_callback=lambda s, m: hist.append(m["train"]),
+                    teacher_groups=groups)
+    gaps = [h["on_policy_distillation/teacher_student_logprob_gap_mean"] for h in hist]
+    assert len(gaps) == 40 and gaps[0] < 0 and sum(gaps[-3:]) / 3 > sum(gaps[:3]) / 3 + 0.05, gaps     # the student closes in on the teacher
+    assert hist[0]["on_policy_distillation/teacher_model_unique"] == 1.0

@@ -277,6 +277,99 @@ __global__ void __launch_bounds__(512, 1) p2p_gather_cols_kernel(GatherColsArgs 
   }
 }
 
+// One-shot all-reduce of decode-sized partial sums over peer memory, with the epilogue of a row-parallel projection:
+//   out[M, N]  = bf16( sum over ranks of partial_r[M, N] (fp32, fixed rank order) + residual )
+//   out2[M, N] = out * rsqrt(mean(out^2) + eps) * norm_w          (optional: the RMSNorm that follows in the layer)
+// Every rank copies its fp32 partial into its symmetric stage, the ranks meet at a flag barrier, then every rank reads all
+// stages (plain peer loads) and reduces ALL rows, so every rank ends with identical bf16 results. One CTA owns whole rows
+// in the reduce phase, which lets it compute the row's sum of squares for the fused norm. Stages are double-buffered at
+// fixed offsets by the parity of a device-resident epoch (the launch can be replayed from a CUDA graph); waits are
+// bounded, a rank that gives up sets the status word and leaves its outputs untouched.
+struct AllReduceRowsArgs {
+  const float4* partial;          // [M, N] fp32, this rank's partial sums
+  const uint4* residual;          // [M, N] bf16 or null
+  uint4* out;                     // [M, N] bf16
+  const uint4* norm_w;            // [N] bf16 or null
+  uint4* out2;                    // [M, N] bf16 (with norm_w)
+  float4* stage[MAX_RANKS];       // per rank: two halves of half_f4 float4
+  unsigned int* flags[MAX_RANKS];
+  unsigned int* epoch_ptr;
+  unsigned long long limit_ns;
+  int* abort_word;
+  int* status;
+  long long half_f4;
+  float eps;
+  int M, N, rank, world;
+};
+__global__ void __launch_bounds__(512, 1) p2p_allreduce_rows_kernel(AllReduceRowsArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  __shared__ float red[32];
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(a.epoch_ptr) + 1;
+  const long long n4 = static_cast<long long>(a.M) * a.N / 4;
+  const long long half = (epoch & 1u) ? a.half_f4 : 0;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  float4* mine = a.stage[a.rank] + half;
+  for (long long i = tid; i < n4; i += nthreads) mine[i] = a.partial[i];
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    PeerTable t;
+    for (int r = 0; r < MAX_RANKS; ++r) t.flags[r] = a.flags[r];
+    const bool ok = peer_barrier(t, a.rank, a.world, 0, epoch, a.limit_ns, a.status);
+    if (threadIdx.x == 0) {
+      *a.abort_word = ok ? 0 : 1;
+      *a.epoch_ptr = epoch;   // every CTA read the old value before the grid barrier above
+    }
+    __threadfence();
+  }
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(a.abort_word)) return;
+  const int vecs = a.N / 8;   // 8 columns per thread step
+  for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+    float ssq = 0.f;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      const long long i = static_cast<long long>(row) * vecs + v;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < a.world; ++r) {
+        const float4* src = a.stage[r] + half + 2 * i;
+        const float4 lo = src[0], hi = src[1];
+        acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+        acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+      }
+      if (a.residual) {
+        const uint4 rr = a.residual[i];
+        const float2 r0 = rlb::unpack_bf16x2(rr.x), r1 = rlb::unpack_bf16x2(rr.y), r2 = rlb::unpack_bf16x2(rr.z), r3 = rlb::unpack_bf16x2(rr.w);
+        acc[0] += r0.x; acc[1] += r0.y; acc[2] += r1.x; acc[3] += r1.y; acc[4] += r2.x; acc[5] += r2.y; acc[6] += r3.x; acc[7] += r3.y;
+      }
+      uint4 o;
+      o.x = rlb::pack_bf16x2(acc[0], acc[1]); o.y = rlb::pack_bf16x2(acc[2], acc[3]);
+      o.z = rlb::pack_bf16x2(acc[4], acc[5]); o.w = rlb::pack_bf16x2(acc[6], acc[7]);
+      a.out[i] = o;
+      if (a.norm_w) {   // the norm sees the bf16 residual stream, as the unfused RMSNorm kernel does
+        const float2 q0 = rlb::unpack_bf16x2(o.x), q1 = rlb::unpack_bf16x2(o.y), q2 = rlb::unpack_bf16x2(o.z), q3 = rlb::unpack_bf16x2(o.w);
+        ssq += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
+      }
+    }
+    if (a.norm_w) {
+      const float tot = rlb::block_sum(ssq, red);
+      const float rstd = rsqrtf(tot / static_cast<float>(a.N) + a.eps);
+      for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+        const long long i = static_cast<long long>(row) * vecs + v;
+        const uint4 o = a.out[i];   // written by this thread just above
+        const uint4 w = a.norm_w[v];
+        const float2 q0 = rlb::unpack_bf16x2(o.x), q1 = rlb::unpack_bf16x2(o.y), q2 = rlb::unpack_bf16x2(o.z), q3 = rlb::unpack_bf16x2(o.w);
+        const float2 w0 = rlb::unpack_bf16x2(w.x), w1 = rlb::unpack_bf16x2(w.y), w2 = rlb::unpack_bf16x2(w.z), w3 = rlb::unpack_bf16x2(w.w);
+        uint4 y;
+        y.x = rlb::pack_bf16x2(q0.x * rstd * w0.x, q0.y * rstd * w0.y); y.y = rlb::pack_bf16x2(q1.x * rstd * w1.x, q1.y * rstd * w1.y);
+        y.z = rlb::pack_bf16x2(q2.x * rstd * w2.x, q2.y * rstd * w2.y); y.w = rlb::pack_bf16x2(q3.x * rstd * w3.x, q3.y * rstd * w3.y);
+        a.out2[i] = y;
+      }
+      __syncthreads();   // `red` is reused by the next row
+    }
+  }
+}
+
 // Pull gather for fully sharded parameters: dst[r * n .. (r + 1) * n) = peer r's shard[off .. off + n) for every rank r.
 // An ordinary (non-cooperative) launch of a few CTAs, meant for a side stream: the peers' shards do not change while a
 // forward / backward pass runs, so no flag is needed, and the copy shares the GPU with the GEMMs of the previous unit
@@ -433,6 +526,44 @@ RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void
   const int grid = coop_grid(reinterpret_cast<const void*>(p2p_gather_cols_kernel), 512);
   void* args[] = {&a};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_gather_cols_kernel), dim3(grid),
+                                                      dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
+}
+
+// One-shot all-reduce of fp32 partial sums [M, N] with residual add and optional fused RMSNorm (see
+// p2p_allreduce_rows_kernel). N a multiple of 8; stage_ptrs[r]: rank r's stage of 2 * half_bytes bytes with
+// half_bytes >= M * N * 4 (fixed per stage); flag_ptrs[r]: 8 zero-initialised uint32 words; epoch_ptr: device uint32.
+RLB_API int rlb_p2p_allreduce_rows(const void* partial, const void* residual, void* out, const void* norm_w, void* out2, float eps,
+                                   int M, int N, void* const* stage_ptrs, void* const* flag_ptrs, int rank, int world,
+                                   void* epoch_ptr, double wait_limit_s, int* scratch, int* status, long long half_bytes,
+                                   void* stream) {
+  if (world < 1 || world > MAX_RANKS || M <= 0 || N <= 0 || (N % 8) || (half_bytes % 16) ||
+      half_bytes < static_cast<long long>(M) * N * 4)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual) |
+       reinterpret_cast<uintptr_t>(norm_w) | reinterpret_cast<uintptr_t>(out2)) & 15)
+    return -3;
+  if (norm_w && !out2) return -2;
+  AllReduceRowsArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int r = 0; r < world; ++r) {
+    a.stage[r] = static_cast<float4*>(stage_ptrs[r]);
+    a.flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
+  }
+  a.partial = static_cast<const float4*>(partial);
+  a.residual = static_cast<const uint4*>(residual);
+  a.out = static_cast<uint4*>(out);
+  a.norm_w = static_cast<const uint4*>(norm_w);
+  a.out2 = static_cast<uint4*>(out2);
+  a.epoch_ptr = static_cast<unsigned int*>(epoch_ptr);
+  a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
+  a.abort_word = scratch;
+  a.status = status;
+  a.half_f4 = half_bytes / 16;
+  a.eps = eps;
+  a.M = M; a.N = N; a.rank = rank; a.world = world;
+  const int grid = coop_grid(reinterpret_cast<const void*>(p2p_allreduce_rows_kernel), 512);
+  void* args[] = {&a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_allreduce_rows_kernel), dim3(grid),
                                                       dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
 }
 

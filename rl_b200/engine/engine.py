@@ -597,10 +597,53 @@ class GenerationEngine:
             z.index_fill_(1, self._banned_ids, -1e30)
         return z
 
+    def _can_fuse_decode_tp(self, n: int) -> bool:
+        """Tensor-parallel decode on the weight-streaming GEMM: the row-parallel projections leave fp32 partial sums that a
+        one-shot peer all-reduce kernel sums, adds to the residual stream and normalises for the next projection."""
+        c = self.cfg
+        if not (self.native and self.tpw > 1 and getattr(self.tp, "comm", None) is not None and not self.quantization and not c.is_moe
+                and n <= 256 and os.environ.get("RLB_FUSED_DECODE_TP", "1") != "0"):
+            return False
+        if c.hidden_size % 128 or not len(self.model.layers):
+            return False
+        l0 = self.model.layers[0]
+        f_local = l0.mlp.gate_up_proj.shape[0] // 2
+        return (f_local % 64 == 0 and getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
+                and getattr(l0.self_attn, "o_lora", None) is None)
+
+    @torch.no_grad()
+    def _decode_forward_fused_tp(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
+        """Per layer: qkv (column shard) -> rope + cache write -> paged attention over the local heads -> o_proj partial sums ->
+        all-reduce + residual + post-attention norm (one peer kernel) -> gate_up with SwiGLU -> down partial sums ->
+        all-reduce + residual + next input norm. No NCCL call: the step is captured in a CUDA graph."""
+        m, c, comm = self.model, self.cfg, self.tp.comm
+        eps = c.rms_norm_eps
+        h = F.embedding(ids, m.embed_tokens)
+        L = len(m.layers)
+        x = F.rmsnorm(h, m.layers[0].input_layernorm, eps)
+        for li, layer in enumerate(m.layers):
+            at = layer.self_attn
+            qkv = E.skinny_linear(x, at.qkv_proj, bias=at.qkv_bias)
+            if c.qk_norm:
+                qkv = F.head_rmsnorm(qkv, at.q_norm, 0, at.hq, c.head_dim, eps)
+                qkv = F.head_rmsnorm(qkv, at.k_norm, at.q_local, at.hkv, c.head_dim, eps)
+            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, self.hq, self.hkv, c.head_dim,
+                               num_splits=num_splits, scratch=scratch)
+            part = E.skinny_linear(a, at.o_proj, out_dtype=torch.float32)
+            h, x2 = comm.allreduce_rows(part, h, layer.post_attention_layernorm, eps)
+            act = E.skinny_linear(x2, layer.mlp.gate_up_proj, swiglu=True)
+            part = E.skinny_linear(act, layer.mlp.down_proj, out_dtype=torch.float32)
+            next_w = m.layers[li + 1].input_layernorm if li + 1 < L else m.norm
+            h, x = comm.allreduce_rows(part, h, next_w, eps)
+        return self._output_logits(x, logits_out)
+
     @torch.no_grad()
     def _decode_forward(self, ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out=None):
         if self._can_fuse_decode(ids.shape[0]):
             return self._decode_forward_fused(ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out)
+        if self._can_fuse_decode_tp(ids.shape[0]):
+            return self._decode_forward_fused_tp(ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out)
         m, c = self.model, self.cfg
         h = F.embedding(ids, m.embed_tokens)
         for li, layer in enumerate(m.layers):

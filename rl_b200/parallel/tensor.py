@@ -72,6 +72,8 @@ def _bind():
         lib.rlb_gemm_tp_scatter.argtypes = [_P, _LL, _P, _LL, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _LL, _P, _P, _I, _I, _U, _P, _D, _P, _P]
         lib.rlb_p2p_gather_cols.argtypes = [_P, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _D, _P, _P, _LL, _P]
         lib.rlb_p2p_gather_cols.restype = C.c_int
+        lib.rlb_p2p_allreduce_rows.argtypes = [_P, _P, _P, _P, _P, C.c_float, _I, _I, _P, _P, _I, _I, _P, _D, _P, _P, _LL, _P]
+        lib.rlb_p2p_allreduce_rows.restype = C.c_int
         lib.rlb_gemm_tp_gather.restype = C.c_int
         lib.rlb_gemm_tp_scatter.restype = C.c_int
         _bound = True
@@ -91,11 +93,15 @@ class TPFusedComm:
         self.group = group
         self.wait_limit_s = wait_limit_s
         self.pushers = pushers
-        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256, column-gather flags at 512
+        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256, column-gather flags at 512, all-reduce at 768
         self.rank, self.world = self.ctrl.rank, self.ctrl.world
         self._gflags = (_P * self.world)(*self.ctrl.peer_ptrs)
         self._sflags = (_P * self.world)(*[p + 256 for p in self.ctrl.peer_ptrs])
         self._cflags = (_P * self.world)(*[p + 512 for p in self.ctrl.peer_ptrs])
+        self._rflags = (_P * self.world)(*[p + 768 for p in self.ctrl.peer_ptrs])
+        self.stage_r = None
+        self.epoch_r_dev = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
+        self._r_scratch = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
         self.stage_l = None
         self.epoch_c_dev = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
         self._c_scratch = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
@@ -186,6 +192,30 @@ class TPFusedComm:
             raise RuntimeError(f"rlb_p2p_gather_cols failed with code {rc}")
         return out
 
+    def allreduce_rows(self, partial: torch.Tensor, residual: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                       eps: float = 1e-6, max_rows: int = 256):
+        """Decode-sized all-reduce over peer memory: ``out = bf16(sum over ranks of partial + residual)`` on every rank, plus
+        ``out2 = rmsnorm(out) * norm_w`` when ``norm_w`` is given (the norm that follows a row-parallel projection).
+        ``partial`` [M, N] fp32 (M <= ``max_rows``). One launch, device-resident epoch: capturable in a CUDA graph."""
+        lib = _bind()
+        M, N = partial.shape
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and N % 8 == 0 and M <= max_rows
+        st = self._ensure("stage_r", 2 * max_rows * N * 4)
+        half_bytes = (st.nbytes // 2) // 16 * 16
+        out = torch.empty((M, N), dtype=BF16, device=partial.device)
+        out2 = torch.empty((M, N), dtype=BF16, device=partial.device) if norm_w is not None else None
+        if residual is not None and not residual.is_contiguous():
+            residual = residual.contiguous()
+        rc = lib.rlb_p2p_allreduce_rows(partial.data_ptr(), residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                        norm_w.data_ptr() if norm_w is not None else None, out2.data_ptr() if out2 is not None else None,
+                                        float(eps), M, N, st.table, self._rflags, self.rank, self.world, self.epoch_r_dev.data_ptr(),
+                                        float(self.wait_limit_s), self._r_scratch.data_ptr(), _L.status_word(partial.device).data_ptr(),
+                                        half_bytes, torch.cuda.current_stream().cuda_stream)
+        _L.Counters.launches += 1
+        if rc:
+            raise RuntimeError(f"rlb_p2p_allreduce_rows failed with code {rc}")
+        return out, out2
+
     @staticmethod
     def phase_times_us() -> list[float]:
         """Durations (us) of the phases of the last ``scatter_gemm`` launch on this GPU, measured by CTA 0:
@@ -200,7 +230,7 @@ class TPFusedComm:
         return [(buf[i + 1] - buf[i]) / 1e3 for i in range(4)]
 
     def close(self):
-        for b in (self.stage_a, self.stage_c, self.stage_l, self.ctrl):
+        for b in (self.stage_a, self.stage_c, self.stage_l, self.stage_r, self.ctrl):
             if b is not None:
                 b.close()
 

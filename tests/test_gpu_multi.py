@@ -146,6 +146,30 @@ def _tp_kernel_worker(rank, world, port):
         torch.cuda.synchronize()
         assert check_status() == 0
         assert torch.equal(full, torch.cat(parts, dim=1)), ("gather_cols", it)
+    # one-shot all-reduce of decode-sized fp32 partial sums with residual add and fused RMSNorm; changing row counts
+    for it, (rows, n, with_norm) in enumerate([(48, 1024, True), (7, 1024, True), (256, 5120, True), (64, 1024, False), (64, 1024, True)]):
+        part = torch.randn(rows, n, generator=g, device=dev) + 0.1 * rank
+        res = torch.randn(rows, n, generator=g, device=dev).to(torch.bfloat16)
+        dist.broadcast(res, src=0)
+        wn = (1.0 + 0.1 * torch.randn(n, generator=g, device=dev)).to(torch.bfloat16)
+        dist.broadcast(wn, src=0)
+        out, out2 = comm.allreduce_rows(part, res, wn if with_norm else None, 1e-6)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        torch.cuda.synchronize()
+        assert check_status() == 0
+        tot = res.float()
+        acc = torch.zeros_like(part)
+        for q in parts:                      # the kernel sums the ranks in this order, in fp32
+            acc = acc + q
+        want = (acc + tot).to(torch.bfloat16)
+        assert torch.equal(out, want), ("allreduce_rows", it, (out.float() - want.float()).abs().max().item())
+        if with_norm:
+            wf = want.float()
+            ref2 = (wf * torch.rsqrt(wf.pow(2).mean(-1, keepdim=True) + 1e-6) * wn.float())
+            assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item(), ("allreduce_rows norm", it)
+        else:
+            assert out2 is None
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
@@ -155,6 +179,63 @@ def _tp_kernel_worker(rank, world, port):
 def test_fused_tensor_parallel_gemms(native_lib, world):
     _need(world)
     mp.spawn(_tp_kernel_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+def _tp_decode_worker(rank, world, port):
+    """Tensor-parallel generation: the weight-streaming decode step with one-shot peer all-reduces against the layer-by-layer
+    step (tile GEMM + all-reduce kernel); both captured in CUDA graphs, greedy."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.ops.lib import check_status
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = ModelConfig(model_type="qwen3", vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                     num_attention_heads=8, num_key_value_heads=4, head_dim=128, qk_norm=True, tie_word_embeddings=False)
+    p = PolicyWorker(dict(precision="bfloat16", train_global_batch_size=4, train_micro_batch_size=2, max_total_sequence_length=256,
+                          parallel=dict(tensor_parallel_size=world, sequence_parallel=True),
+                          generation=dict(max_new_tokens=40, temperature=1.0, stop_token_ids=[], kv_cache_tokens=8192, block_size=16, max_running=16),
+                          optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3))),
+                     model_cfg=mc, device=f"cuda:{rank}", init_reference_model=False, init_optimizer=False, seed=3)
+    ids = torch.randint(1, 4096, (6, 24), generator=torch.Generator().manual_seed(10))
+    data = BatchedDataDict(input_ids=ids, input_lengths=torch.full((6,), 24))
+    gen = p.build_generation()
+    gen.prepare_for_generation()
+    eng = gen.engine
+    assert eng._can_fuse_decode_tp(8)
+    fast = gen.generate(data, greedy=True)
+    n_graphs = len(eng._graphs)
+    os.environ["RLB_FUSED_DECODE_TP"] = "0"
+    eng._graphs.clear()
+    slow = gen.generate(data, greedy=True)
+    os.environ["RLB_FUSED_DECODE_TP"] = "1"
+    gen.finish_generation()
+    torch.cuda.synchronize()
+    assert check_status() == 0 and n_graphs >= 1
+    a, b, la, lb = fast["output_ids"], slow["output_ids"], fast["logprobs"], slow["logprobs"]
+    same, prefix = 0, []
+    for x, y, u, v in zip(a, b, la, lb):
+        neq = (x != y).nonzero()
+        t = int(neq[0]) if neq.numel() else x.numel()
+        same += int(t == x.numel())
+        prefix.append((t - 24) / (x.numel() - 24))
+        if t > 24:
+            assert (u[24:t] - v[24:t]).abs().max().item() < 0.08, (rank, t)
+    assert same * 2 >= 6 and sum(prefix) / 6 > 0.6, (rank, same, prefix)
+    # every tensor-parallel rank produced the same tokens without exchanging them
+    other = a.clone().cuda()
+    dist.broadcast(other, src=0)
+    assert torch.equal(other.cpu(), a)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_decode_with_one_shot_allreduce(native_lib, world):
+    _need(world)
+    mp.spawn(_tp_decode_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 def _tp_train_worker(rank, world, port):

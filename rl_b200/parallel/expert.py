@@ -178,9 +178,14 @@ class _DispatchPlan:
         self.n = n
         self.dst_rank = (e_of // El).to(torch.int32)
         self.dst_row = (my_off[e_of] + torch.arange(n, device=dev) - start[e_of]).to(torch.int32)
-        # my own receive layout
-        self.mpad = comm.cap_rows
+        # my own receive layout. The receive buffer is sized for the worst case (every copy of every rank lands here), but
+        # everything downstream (masking, grouped GEMMs, SwiGLU, the return trip) only has to cover the rows that did
+        # arrive: one small host read per call buys back passes over gigabytes of unused rows.
         mine_total, mine_pad, mine_row0 = total[ep.rank], padded[ep.rank], row0[ep.rank]
+        need = int(mine_pad.sum().item())
+        if need > comm.cap_rows:
+            raise RuntimeError(f"expert-parallel receive buffer too small: {need} rows arrive, {comm.cap_rows} fit")
+        self.mpad = max(128, need)
         self.row0 = mine_row0.to(torch.int32)
         self.rows = mine_pad.to(torch.int32)
         ends = torch.cumsum(mine_pad, 0)

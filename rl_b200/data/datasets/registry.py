@@ -40,6 +40,20 @@ HF_SETS: dict[str, tuple] = {
     "oasst": ("OpenAssistant/oasst1", None, "train", "validation", {}, "sft_processor"),
     "HelpSteer3": ("nvidia/HelpSteer3", "preference", "train", "validation", {}, "preference_processor"),
     "Tulu3Preference": ("allenai/llama-3.1-tulu-3-8b-preference-mixture", None, "train", None, {}, "preference_processor"),
+    "OpenR1-Math-220k": ("open-r1/OpenR1-Math-220k", "default", "train", None, {"problem": "problem", "answer": "expected_answer"}, "math_data_processor"),
+    "Nemotron-Cascade-2-SFT-math": ("nvidia/Nemotron-Cascade-2-SFT-Data", "math", "train", None, {}, "sft_processor"),
+    "geometry3k": ("hiyouga/geometry3k", None, "train", "validation", {"problem": "problem", "answer": "expected_answer"}, "vlm_processor"),
+    "clevr-cogent": ("MMInstruction/Clevr_CoGenT_TrainA_R1", None, "train", None, {"problem": "problem", "solution": "expected_answer"}, "vlm_processor"),
+    "refcoco": ("jxu124/refcoco", None, "train", "validation", {}, "vlm_processor"),
+    "mmpr-tiny": ("OpenGVLab/MMPR-Tiny", None, "train", None, {}, "vlm_processor"),
+    "avqa": ("gijs/avqa-processed", None, "train", "validation", {"question": "problem", "answer": "expected_answer"}, "multichoice_qa_processor"),
+    "MMAU": ("TwinkStart/MMAU", None, "test", None, {"question": "problem", "answer": "expected_answer", "choices": "options"}, "multichoice_qa_processor"),
+    "intent": (None, None, "train", "validation", {"text": "problem", "label": "expected_answer"}, "math_data_processor"),
+    "general_conversations": (None, None, "train", "validation", {}, "sft_processor"),
+    "BinaryPreferenceDataset": (None, None, "train", "validation", {}, "preference_processor"),
+    "arrow_text": (None, None, "train", None, {}, "sft_processor"),
+    "local_math": (None, None, "train", None, {}, "math_data_processor"),
+    "nemogym": (None, None, "train", "validation", {}, "nemogym_processor"),
 }
 
 
@@ -79,6 +93,38 @@ class JsonlRecords:
 
     def __getitem__(self, i):
         return self.records[i]
+
+
+class ArrowRecords:
+    """Rows of a local Arrow IPC / Parquet file (the arrow_text data sets of the reference,
+    nemo_rl/data/datasets/response_datasets/arrow_text_dataset.py)."""
+
+    def __init__(self, path: str, renames: Optional[dict] = None, max_samples: Optional[int] = None):
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+
+        if str(path).endswith(".parquet"):
+            table = pq.read_table(path)
+        else:
+            with pa.memory_map(path, "r") as src:
+                try:
+                    table = pa.ipc.open_file(src).read_all()
+                except pa.ArrowInvalid:
+                    table = pa.ipc.open_stream(src).read_all()
+        if max_samples:
+            table = table.slice(0, max_samples)
+        self.rows = table.to_pylist()
+        self.renames = renames or {}
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        r = dict(self.rows[i])
+        for a, b in self.renames.items():
+            if a in r and b not in r:
+                r[b] = r[a]
+        return r
 
 
 class HFRecords:
@@ -146,6 +192,17 @@ def load_raw_dataset(dcfg: dict, split: str = "train"):
     if name == "arithmetic":
         n = dcfg.get("num_samples", 1024) if split == "train" else dcfg.get("num_val_samples", 64)
         return ArithmeticDataset(n, dcfg.get("max_operand", 99), dcfg.get("ops", "+-*"), seed=dcfg.get("seed", 0) + (0 if split == "train" else 1)), "math_data_processor"
+    if name in ("intent", "general_conversations", "BinaryPreferenceDataset", "arrow_text", "local_math", "nemogym") and dcfg.get("data_path"):
+        # sets that live in local files (jsonl / json / arrow / parquet): the registry row supplies renames and the processor
+        _, _, _, _, renames, proc = HF_SETS[name]
+        path = dcfg["data_path"] if split == "train" else dcfg.get("val_data_path")
+        if path is None:
+            return None, None
+        renames = dict(renames, **{dcfg[k]: v for k, v in (("input_key", "problem"), ("output_key", "expected_answer"),
+                                                           ("problem_key", "problem"), ("solution_key", "expected_answer")) if dcfg.get(k)})
+        if str(path).endswith((".arrow", ".parquet")):
+            return ArrowRecords(path, renames, dcfg.get("max_samples")), proc
+        return JsonlRecords(path, renames), proc
     if name in ("jsonl", "json", "ResponseDataset", "PreferenceDataset", "openai_format"):
         path = dcfg["data_path"] if split == "train" else dcfg.get("val_data_path")
         if path is None:

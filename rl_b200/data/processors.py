@@ -128,6 +128,28 @@ def token_prompt_processor(rec: dict, spec: TaskDataSpec, tokenizer, max_seq_len
                    rec.get("task_name", spec.task_name or "synthetic"))
 
 
+def nemogym_processor(rec: dict, spec: TaskDataSpec, tokenizer, max_seq_length: Optional[int], idx: int) -> DatumSpec:
+    """Records of a gym-style resource server (nemo_rl/data/datasets/response_datasets/nemogym_dataset.py): the prompt is
+    ``responses_create_params.input`` (or ``messages``), the whole record travels to the environment as ``extra_env_info``
+    and the sample is routed by the agent that owns it (``agent_ref.name``)."""
+    params = rec.get("responses_create_params") or {}
+    msgs = params.get("input") or rec.get("messages") or [{"role": "user", "content": str(rec.get("question", rec.get("problem", "")))}]
+    if isinstance(msgs, str):
+        msgs = [{"role": "user", "content": msgs}]
+    msgs = [{"role": m.get("role", "user"), "content": m.get("content", "")} for m in msgs]
+    agent = (rec.get("agent_ref") or {}).get("name") or rec.get("task_name") or spec.task_name or "nemo_gym"
+    out = _finish(_chat(msgs, tokenizer), dict(rec), max_seq_length, idx, agent)
+    out["agent_ref"] = agent
+    return out
+
+
+def vlm_processor(rec: dict, spec: TaskDataSpec, tokenizer, max_seq_length: Optional[int], idx: int) -> DatumSpec:
+    """Image sets need the model's patch size and image token: they are built by
+    :func:`rl_b200.data.datasets.vlm.setup_vlm_data` (``examples/run_vlm_grpo.py`` / ``run_vlm_sft.py``), not by name."""
+    raise RuntimeError("vision-language records are processed by rl_b200.data.datasets.vlm.make_vlm_processor (it needs the model's "
+                       "patch size and image token id); use setup_vlm_data / the run_vlm_* entry points")
+
+
 PROCESSOR_REGISTRY: dict[str, Callable[..., Any]] = {
     "default": math_hf_data_processor,
     "math_data_processor": math_data_processor,
@@ -137,6 +159,8 @@ PROCESSOR_REGISTRY: dict[str, Callable[..., Any]] = {
     "sft_processor": sft_processor,
     "preference_processor": preference_processor,
     "token_prompt_processor": token_prompt_processor,
+    "nemogym_processor": nemogym_processor,
+    "vlm_processor": vlm_processor,
 }
 
 

@@ -88,3 +88,30 @@ def test_from_batches_pads_and_repeat_interleave():
     assert m["x"].shape == (3, 5) and m["x"][0, 4] == -1 and m["l"] == [1, 2, 3]
     r = m.repeat_interleave(2)
     assert r.size == 6 and r["l"] == [1, 1, 2, 2, 3, 3]
+
+
+def test_local_dataset_rows_of_the_registry(tmp_path):
+    """Sets that live in local files: jsonl with key renames, Arrow / Parquet text corpora, gym-style records."""
+    import json
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from rl_b200.data.datasets.registry import HF_SETS, load_raw_dataset
+    from rl_b200.data.processors import get_processor
+
+    p = tmp_path / "intent.jsonl"
+    p.write_text("\n".join(json.dumps(dict(text=f"q{i}", label=str(i))) for i in range(3)))
+    recs, proc = load_raw_dataset(dict(dataset_name="intent", data_path=str(p)))
+    assert len(recs) == 3 and recs[1]["problem"] == "q1" and recs[1]["expected_answer"] == "1" and proc == "math_data_processor"
+    table = pa.table({"messages": [[{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]] * 4})
+    pq.write_table(table, tmp_path / "c.parquet")
+    with pa.OSFile(str(tmp_path / "c.arrow"), "wb") as f, pa.ipc.new_file(f, table.schema) as w:
+        w.write_table(table)
+    for name in ("c.parquet", "c.arrow"):
+        recs, proc = load_raw_dataset(dict(dataset_name="arrow_text", data_path=str(tmp_path / name), max_samples=3))
+        assert len(recs) == 3 and recs[0]["messages"][1]["content"] == "yo" and proc == "sft_processor"
+    assert load_raw_dataset(dict(dataset_name="local_math", data_path=str(p), problem_key="text", solution_key="label"))[0][2]["expected_answer"] == "2"
+    for name, row in HF_SETS.items():
+        get_processor(row[5])     # every row names a registered processor
+    assert {"OpenR1-Math-220k", "geometry3k", "refcoco", "avqa", "MMAU", "nemogym", "BinaryPreferenceDataset"} <= set(HF_SETS)

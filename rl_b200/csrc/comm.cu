@@ -280,53 +280,62 @@ __global__ void __launch_bounds__(512, 1) p2p_gather_cols_kernel(GatherColsArgs 
 // One-shot all-reduce of decode-sized partial sums over peer memory, with the epilogue of a row-parallel projection:
 //   out[M, N]  = bf16( sum over ranks of partial_r[M, N] (fp32, fixed rank order) + residual )
 //   out2[M, N] = out * rsqrt(mean(out^2) + eps) * norm_w          (optional: the RMSNorm that follows in the layer)
-// Every rank copies its fp32 partial into its symmetric stage, the ranks meet at a flag barrier, then every rank reads all
-// stages (plain peer loads) and reduces ALL rows, so every rank ends with identical bf16 results. One CTA owns whole rows
-// in the reduce phase, which lets it compute the row's sum of squares for the fused norm. Stages are double-buffered at
-// fixed offsets by the parity of a device-resident epoch (the launch can be replayed from a CUDA graph); waits are
-// bounded, a rank that gives up sets the status word and leaves its outputs untouched.
+// One CTA per row and no grid-wide step: CTA r copies row r of this rank's partial sums into its symmetric stage, tells
+// every peer "row r of epoch e is there" (one release store per peer), waits for the same word from every peer, then
+// reduces row r from all stages with plain peer loads. The CTAs of one GPU never wait for each other, only for the same
+// row's CTA on the other GPUs, which starts whether or not this GPU is ahead, so an ordinary (non-cooperative) launch
+// is enough and the latency is one NVLink round trip instead of two grid barriers and a cross-GPU barrier.
+// Stage and flag slots are double-buffered by the parity of a device-resident epoch: a peer signals epoch e + 1 only
+// after its epoch-e kernel has finished reading, so the slots of epoch e are free again at e + 2. The last CTA to finish
+// advances the epoch (every CTA read it on entry), so the launch replays from a CUDA graph. Waits are bounded; a CTA that
+// gives up sets the status word and leaves its row's outputs untouched.
+constexpr int AR_MAX_ROWS = 256;
 struct AllReduceRowsArgs {
   const float4* partial;          // [M, N] fp32, this rank's partial sums
   const uint4* residual;          // [M, N] bf16 or null
   uint4* out;                     // [M, N] bf16
   const uint4* norm_w;            // [N] bf16 or null
   uint4* out2;                    // [M, N] bf16 (with norm_w)
-  float4* stage[MAX_RANKS];       // per rank: two halves of half_f4 float4
-  unsigned int* flags[MAX_RANKS];
+  float4* stage[MAX_RANKS];       // per rank: two halves of half_f4 float4, rows at a pitch of N floats
+  unsigned int* flags[MAX_RANKS]; // per rank: [2][AR_MAX_ROWS][MAX_RANKS] epoch words
   unsigned int* epoch_ptr;
+  unsigned int* done_counter;     // device word, zero between launches
   unsigned long long limit_ns;
-  int* abort_word;
   int* status;
   long long half_f4;
   float eps;
   int M, N, rank, world;
 };
-__global__ void __launch_bounds__(512, 1) p2p_allreduce_rows_kernel(AllReduceRowsArgs a) {
-  cg::grid_group grid = cg::this_grid();
+__global__ void __launch_bounds__(256) p2p_allreduce_rows_kernel(AllReduceRowsArgs a) {
   __shared__ float red[32];
+  __shared__ int s_ok;
+  const int row = blockIdx.x;
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(a.epoch_ptr) + 1;
-  const long long n4 = static_cast<long long>(a.M) * a.N / 4;
-  const long long half = (epoch & 1u) ? a.half_f4 : 0;
-  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
-  float4* mine = a.stage[a.rank] + half;
-  for (long long i = tid; i < n4; i += nthreads) mine[i] = a.partial[i];
+  const unsigned int parity = epoch & 1u;
+  const long long half = parity ? a.half_f4 : 0;
+  const int f4_per_row = a.N / 4;
+  float4* mine = a.stage[a.rank] + half + static_cast<long long>(row) * f4_per_row;
+  const float4* src_row = a.partial + static_cast<long long>(row) * f4_per_row;
+  for (int i = threadIdx.x; i < f4_per_row; i += blockDim.x) mine[i] = src_row[i];
+  if (threadIdx.x == 0) s_ok = 1;
   __threadfence_system();
-  grid.sync();
-  if (blockIdx.x == 0) {
-    PeerTable t;
-    for (int r = 0; r < MAX_RANKS; ++r) t.flags[r] = a.flags[r];
-    const bool ok = peer_barrier(t, a.rank, a.world, 0, epoch, a.limit_ns, a.status);
-    if (threadIdx.x == 0) {
-      *a.abort_word = ok ? 0 : 1;
-      *a.epoch_ptr = epoch;   // every CTA read the old value before the grid barrier above
+  __syncthreads();
+  const long long slot = (static_cast<long long>(parity) * AR_MAX_ROWS + row) * MAX_RANKS;
+  if (threadIdx.x < a.world) {
+    st_release_sys(a.flags[threadIdx.x] + slot + a.rank, epoch);
+    const unsigned int* wait_on = a.flags[a.rank] + slot + threadIdx.x;
+    const unsigned long long t0 = globaltimer_ns();
+    while (static_cast<int>(ld_acquire_sys(wait_on) - epoch) < 0) {
+      if (globaltimer_ns() - t0 > a.limit_ns) {
+        if (a.status) atomicCAS(a.status, 0, RLB_ERR_WAIT_PEER);
+        s_ok = 0;
+        break;
+      }
     }
-    __threadfence();
   }
-  grid.sync();
-  if (*reinterpret_cast<volatile int*>(a.abort_word)) return;
-  const int vecs = a.N / 8;   // 8 columns per thread step
-  for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+  __syncthreads();
+  if (s_ok) {
+    const int vecs = a.N / 8;   // 8 columns per thread step
     float ssq = 0.f;
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       const long long i = static_cast<long long>(row) * vecs + v;
@@ -365,7 +374,16 @@ __global__ void __launch_bounds__(512, 1) p2p_allreduce_rows_kernel(AllReduceRow
         y.z = rlb::pack_bf16x2(q2.x * rstd * w2.x, q2.y * rstd * w2.y); y.w = rlb::pack_bf16x2(q3.x * rstd * w3.x, q3.y * rstd * w3.y);
         a.out2[i] = y;
       }
-      __syncthreads();   // `red` is reused by the next row
+    }
+  }
+  // the last CTA to finish publishes the new epoch: every CTA of this launch read the old one on entry
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.done_counter, 1u) + 1u == gridDim.x) {
+      *a.done_counter = 0;
+      *a.epoch_ptr = epoch;
+      __threadfence();
     }
   }
 }
@@ -530,13 +548,15 @@ RLB_API int rlb_p2p_gather_cols(const void* local, void* const* stage_ptrs, void
 }
 
 // One-shot all-reduce of fp32 partial sums [M, N] with residual add and optional fused RMSNorm (see
-// p2p_allreduce_rows_kernel). N a multiple of 8; stage_ptrs[r]: rank r's stage of 2 * half_bytes bytes with
-// half_bytes >= M * N * 4 (fixed per stage); flag_ptrs[r]: 8 zero-initialised uint32 words; epoch_ptr: device uint32.
+// p2p_allreduce_rows_kernel). M <= 256, N a multiple of 8; stage_ptrs[r]: rank r's stage of 2 * half_bytes bytes with
+// half_bytes >= M * N * 4 (fixed per stage); flag_ptrs[r]: rlb_p2p_allreduce_flag_bytes() zero-initialised bytes of
+// symmetric memory; epoch_ptr: device uint32 (starts at 0); scratch: one zero-initialised device word.
+RLB_API int rlb_p2p_allreduce_flag_bytes() { return 2 * AR_MAX_ROWS * MAX_RANKS * static_cast<int>(sizeof(unsigned int)); }
 RLB_API int rlb_p2p_allreduce_rows(const void* partial, const void* residual, void* out, const void* norm_w, void* out2, float eps,
                                    int M, int N, void* const* stage_ptrs, void* const* flag_ptrs, int rank, int world,
                                    void* epoch_ptr, double wait_limit_s, int* scratch, int* status, long long half_bytes,
                                    void* stream) {
-  if (world < 1 || world > MAX_RANKS || M <= 0 || N <= 0 || (N % 8) || (half_bytes % 16) ||
+  if (world < 1 || world > MAX_RANKS || M <= 0 || M > AR_MAX_ROWS || N <= 0 || (N % 8) || (half_bytes % 16) ||
       half_bytes < static_cast<long long>(M) * N * 4)
     return -2;
   if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual) |
@@ -555,16 +575,14 @@ RLB_API int rlb_p2p_allreduce_rows(const void* partial, const void* residual, vo
   a.norm_w = static_cast<const uint4*>(norm_w);
   a.out2 = static_cast<uint4*>(out2);
   a.epoch_ptr = static_cast<unsigned int*>(epoch_ptr);
+  a.done_counter = reinterpret_cast<unsigned int*>(scratch);
   a.limit_ns = static_cast<unsigned long long>(wait_limit_s * 1e9);
-  a.abort_word = scratch;
   a.status = status;
   a.half_f4 = half_bytes / 16;
   a.eps = eps;
   a.M = M; a.N = N; a.rank = rank; a.world = world;
-  const int grid = coop_grid(reinterpret_cast<const void*>(p2p_allreduce_rows_kernel), 512);
-  void* args[] = {&a};
-  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(p2p_allreduce_rows_kernel), dim3(grid),
-                                                      dim3(512), args, 0, static_cast<cudaStream_t>(stream)));
+  p2p_allreduce_rows_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // dst[r * bytes_per_rank ...] = (shard_ptrs[r] + src_offset_bytes)[0 .. bytes_per_rank) for r < world, with `ctas` CTAs

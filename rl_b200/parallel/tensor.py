@@ -93,12 +93,13 @@ class TPFusedComm:
         self.group = group
         self.wait_limit_s = wait_limit_s
         self.pushers = pushers
-        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256, column-gather flags at 512, all-reduce at 768
+        self.ctrl = SymmetricBuffer(1024, group)  # gather flags at 0, scatter flags at 256, column-gather flags at 512
         self.rank, self.world = self.ctrl.rank, self.ctrl.world
         self._gflags = (_P * self.world)(*self.ctrl.peer_ptrs)
         self._sflags = (_P * self.world)(*[p + 256 for p in self.ctrl.peer_ptrs])
         self._cflags = (_P * self.world)(*[p + 512 for p in self.ctrl.peer_ptrs])
-        self._rflags = (_P * self.world)(*[p + 768 for p in self.ctrl.peer_ptrs])
+        self._rflag_buf = None      # per-row flag words of the one-shot all-reduce (allocated at first use)
+        self._rflags = None
         self.stage_r = None
         self.epoch_r_dev = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
         self._r_scratch = torch.zeros(1, dtype=torch.int32, device=self.ctrl.device)
@@ -202,6 +203,10 @@ class TPFusedComm:
         assert partial.dtype == torch.float32 and partial.is_contiguous() and N % 8 == 0 and M <= max_rows
         st = self._ensure("stage_r", 2 * max_rows * N * 4)
         half_bytes = (st.nbytes // 2) // 16 * 16
+        if self._rflag_buf is None:
+            lib.rlb_p2p_allreduce_flag_bytes.restype = C.c_int
+            self._rflag_buf = self._SB(int(lib.rlb_p2p_allreduce_flag_bytes()), self.group)
+            self._rflags = (_P * self.world)(*self._rflag_buf.peer_ptrs)
         out = torch.empty((M, N), dtype=BF16, device=partial.device)
         out2 = torch.empty((M, N), dtype=BF16, device=partial.device) if norm_w is not None else None
         if residual is not None and not residual.is_contiguous():
@@ -230,7 +235,7 @@ class TPFusedComm:
         return [(buf[i + 1] - buf[i]) / 1e3 for i in range(4)]
 
     def close(self):
-        for b in (self.stage_a, self.stage_c, self.stage_l, self.stage_r, self.ctrl):
+        for b in (self.stage_a, self.stage_c, self.stage_l, self.stage_r, self._rflag_buf, self.ctrl):
             if b is not None:
                 b.close()
 

@@ -15,6 +15,8 @@ _REGISTRY: dict[str, str] = {
     "code_jaccard": "rl_b200.environments.code_environment:CodeJaccardEnvironment",
     "reward_model": "rl_b200.environments.reward_model_environment:RewardModelEnvironment",
     "dapo": "rl_b200.environments.math_environment:MathEnvironment",
+    "math_multi_reward": "rl_b200.environments.math_environment:MathMultiRewardEnvironment",
+    "multichoice": "rl_b200.environments.math_environment:MathEnvironment",
     "vlm": "rl_b200.environments.vlm_environment:VLMEnvironment",
     "tool": "rl_b200.environments.tool_environment:ToolEnvironment",
     "retriever": "rl_b200.environments.tool_environment:ToolEnvironment",

@@ -97,3 +97,38 @@ def test_tool_environment_runs_calls_and_scores_final_answers():
     logs[3] += [out.observations[3], {"role": "assistant", "content": "<tool_call>{}</tool_call>"}]
     out2 = env.step([logs[0], logs[3]], [out.metadata[0], dict(out.metadata[3], tool_calls=2)])
     assert out2.terminateds.tolist() == [True, True] and out2.rewards.tolist() == [1.0, 0.0]
+
+
+def test_math_verifier_types_and_structured_answers():
+    """Graders beyond the scalar case: tuples / sets / intervals, mixed numbers, scientific notation; the DAPO string rule;
+    English and multilingual multiple choice; the multi-reward environment; a verification that runs out of time scores 0."""
+    from rl_b200.environments import math_environment as M
+    from rl_b200.environments.registry import create_env
+
+    ok = M.answers_match_structured
+    assert ok("(1, \\frac{1}{2})", "(1,0.5)") and ok("\\{3,1\\}", "{1,3}") and not ok("[1,2)", "(1,2)") and ok("[1,2)", "[1, 2)")
+    assert ok("1 1/2", "3/2") and ok("3 \\times 10^{4}", "30000") and ok("3, 5", "3,5") and not ok("3, 5", "3, 6") and not ok("(1,2,3)", "(1,2)")
+    assert M.dapo_math_verify("so the answer is \\boxed{1,000}", "1000") == (1.0, "1,000")
+    assert M.dapo_math_verify("\\boxed{0.50}", "0.5")[0] == 0.0                       # no numeric leniency under this rule
+    assert M.dapo_math_verify("\\boxed{7}" + " " * 400, "7") == (0.0, None)            # only the tail of the response counts
+    assert M.extract_multichoice("reasoning... **Answer: (C)**") == "C" and M.extract_multichoice("答案：B", True) == "B"
+    assert M.extract_multichoice("الإجابة: ب", True) == "B" and M.extract_multichoice("答案：B", False) is None
+
+    def run(env, texts, truths):
+        return env.step([[{"role": "assistant", "content": t}] for t in texts], [{"ground_truth": g} for g in truths])
+
+    env = create_env("math", dict(math_verify_impl="dapo_math_verify"))
+    assert run(env, ["\\boxed{12}", "\\boxed{13}"], ["12", "12"]).rewards.tolist() == [1.0, 0.0]
+    mc = create_env("multichoice", dict(verifier_type="english_multichoice"))
+    r = run(mc, ["Answer: b", "I think Answer: D", "nothing"], ["B", "A", "C"])
+    assert r.rewards.tolist() == [1.0, 0.0, 0.0] and r.answers == ["B", "D", None]
+    ml = create_env("multichoice", dict(verifier_type="multilingual_multichoice"))
+    assert run(ml, ["정답: C", "Respuesta: A"], ["C", "B"]).rewards.tolist() == [1.0, 0.0]
+    multi = create_env("math_multi_reward")
+    r = run(multi, ["<think>x</think>\n<answer>42</answer>", "<answer>4.5</answer> trailing"], ["42", "4.5"])
+    assert r.rewards.tolist() == [[1.0, 1.0, 1.0], [1.0, 0.0, 0.0]] and multi.REWARD_NAMES[0] == "reward/correctness"
+    with pytest.raises(ValueError):
+        create_env("math", dict(math_verify_impl="nope"))
+    import time
+
+    assert M._with_time_limit(lambda: time.sleep(2) or True, 0.05, False) is False

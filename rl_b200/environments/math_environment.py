@@ -195,15 +195,20 @@ _HF_VERIFY = None
 
 
 def _hf_math_verify():
-    """``math_verify.math_metric`` configured like the reference's worker, or False when the package is not installed."""
+    """``(parse, verify, gold config, prediction config)`` of the ``math_verify`` package set up like the reference's worker
+    (gold: LaTeX; prediction: expression or LaTeX), or False when the package is not installed. Its own time limits use
+    signals, which only work on a process's main thread; they are switched off and the caller's limit applies instead."""
     global _HF_VERIFY
     if _HF_VERIFY is None:
         try:
-            from math_verify.metric import math_metric
+            import logging
+
+            from math_verify import parse, verify
             from math_verify.parser import ExprExtractionConfig, LatexExtractionConfig
 
-            _HF_VERIFY = math_metric(gold_extraction_target=(LatexExtractionConfig(),),
-                                     pred_extraction_target=(ExprExtractionConfig(), LatexExtractionConfig()))
+            for name in ("math_verify", "math_verify.parser", "math_verify.grader", "math_verify.utils"):
+                logging.getLogger(name).setLevel(logging.CRITICAL)
+            _HF_VERIFY = (parse, verify, (LatexExtractionConfig(),), (ExprExtractionConfig(), LatexExtractionConfig()))
         except Exception:
             _HF_VERIFY = False
     return _HF_VERIFY
@@ -275,9 +280,13 @@ class MathEnvironment:
             return dapo_math_verify(response, truth)
         hf = _hf_math_verify()
         if hf:
+            parse, verify, gold_cfg, pred_cfg = hf
+
             def run():
-                score, extracted = hf([f"\\boxed{{{truth}}}"], [response])
-                return float(score), (str(extracted[1][0]) if extracted and extracted[1] else None)
+                gold = parse("\\boxed{" + str(truth) + "}", extraction_config=gold_cfg, parsing_timeout=None)
+                pred = parse(response, extraction_config=pred_cfg, parsing_timeout=None)
+                shown = str(pred[-1]) if pred else None
+                return (1.0 if (gold and pred and verify(gold, pred, timeout_seconds=None)) else 0.0), shown
 
             return _with_time_limit(run, self.time_limit_s, (0.0, None))
         pred = extract_answer(response)

@@ -1,5 +1,6 @@
 """Environments: math verification, code execution, sliding puzzle, synthetic token rewards."""
 
+import pytest
 import torch
 
 from rl_b200.environments.code_environment import CodeEnvironment, CodeJaccardEnvironment, extract_code

@@ -30,9 +30,19 @@ using namespace rlb;
 
 constexpr int BQ = 128;   // query rows per CTA
 constexpr int BKV = 64;   // keys per pipeline stage
-constexpr int HD = 128;   // head dimension
+#ifndef RLB_HD
+#define RLB_HD 128        // head dimension of this translation unit; flash_attention_d64.cu includes this file with 64
+#endif
+#ifndef RLB_NAME
+#define RLB_NAME(x) x     // exported names get a suffix in the other instantiations (rlb_flash_attn_fwd_d64, ...)
+#endif
+constexpr int HD = RLB_HD;
+static_assert(HD == 64 || HD == 128, "head dimension: 64 or 128");
+constexpr int ATOMS = HD / 64;            // [rows x 64] swizzle atoms per operand tile along the head dimension
 constexpr int KV_STAGES = 2;
-constexpr int Q_BYTES = BQ * HD * 2;         // 32 KB: two [128 x 64] swizzle atoms
+constexpr int Q_BYTES = BQ * HD * 2;         // 32 KB at HD 128: two [128 x 64] swizzle atoms
+constexpr int Q_ATOM = BQ * 64 * 2;
+constexpr int KV_ATOM = BKV * 64 * 2;
 constexpr int K_BYTES = BKV * HD * 2;        // 16 KB: two [64 x 64] atoms
 constexpr int V_BYTES = BKV * HD * 2;        // 16 KB: two boxes of 64 head-dim columns
 constexpr int P_BYTES = BQ * BKV * 2;        // 16 KB: one [128 x 64] atom
@@ -167,19 +177,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       prefetch_tmap(&tmap_q);
       prefetch_tmap(&tmap_kv);
       mbar_arrive_expect_tx(smem_u32(q_full), Q_BYTES);
-      tma_load_2d(smem_u32(q_s), &tmap_q, smem_u32(q_full), q_col, seq_start + q0);
-      tma_load_2d(smem_u32(q_s + Q_BYTES / 2), &tmap_q, smem_u32(q_full), q_col + 64, seq_start + q0);
+#pragma unroll
+      for (int a = 0; a < ATOMS; ++a)
+        tma_load_2d(smem_u32(q_s + a * Q_ATOM), &tmap_q, smem_u32(q_full), q_col + a * 64, seq_start + q0);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, abort_flag, p.status, RLB_ERR_WAIT_EMPTY)) break;
         const int row = seq_start + j * BKV;
         mbar_arrive_expect_tx(smem_u32(&k_full[st]), K_BYTES);
-        tma_load_2d(smem_u32(k_s + st * K_BYTES), &tmap_kv, smem_u32(&k_full[st]), k_col, row);
-        tma_load_2d(smem_u32(k_s + st * K_BYTES + K_BYTES / 2), &tmap_kv, smem_u32(&k_full[st]), k_col + 64, row);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_2d(smem_u32(k_s + st * K_BYTES + a * KV_ATOM), &tmap_kv, smem_u32(&k_full[st]), k_col + a * 64, row);
         mbar_arrive_expect_tx(smem_u32(&v_full[st]), V_BYTES);
-        tma_load_2d(smem_u32(v_s + st * V_BYTES), &tmap_kv, smem_u32(&v_full[st]), v_col, row);
-        tma_load_2d(smem_u32(v_s + st * V_BYTES + V_BYTES / 2), &tmap_kv, smem_u32(&v_full[st]), v_col + 64, row);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_2d(smem_u32(v_s + st * V_BYTES + a * KV_ATOM), &tmap_kv, smem_u32(&v_full[st]), v_col + a * 64, row);
       }
     }
   } else if (warp == 1) {
@@ -195,8 +208,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // S = Q K^T over the head dimension: 8 steps of 16, two swizzle atoms of 64
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t qa = smem_u32(q_s) + (kk / 4) * (Q_BYTES / 2) + (kk % 4) * 32;
-          const uint32_t ka = smem_u32(k_s + st * K_BYTES) + (kk / 4) * (K_BYTES / 2) + (kk % 4) * 32;
+          const uint32_t qa = smem_u32(q_s) + (kk / 4) * Q_ATOM + (kk % 4) * 32;
+          const uint32_t ka = smem_u32(k_s + st * K_BYTES) + (kk / 4) * KV_ATOM + (kk % 4) * 32;
           umma_f16(tmem_s, make_smem_desc_sw128(qa, 16, 1024), make_smem_desc_sw128(ka, 16, 1024), idesc_s,
                    kk != 0 ? 1u : 0u);
         }
@@ -209,7 +222,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int kk = 0; kk < BKV / 16; ++kk) {
           const uint32_t pa = smem_u32(p_s) + kk * 32;
           const uint32_t va = smem_u32(v_s + st * V_BYTES) + kk * (16 * 128);
-          umma_f16(tmem_o, make_smem_desc_sw128(pa, 16, 1024), make_smem_desc_sw128(va, V_BYTES / 2, 1024), idesc_o,
+          umma_f16(tmem_o, make_smem_desc_sw128(pa, 16, 1024), make_smem_desc_sw128(va, KV_ATOM, 1024), idesc_o,
                    (j | kk) != 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&kv_empty[st]));
@@ -342,11 +355,15 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const 
   const int lane = threadIdx.x & 31;
   if (wid >= static_cast<long long>(T) * Hq) return;
   const int t = static_cast<int>(wid / Hq), h = static_cast<int>(wid % Hq);
-  const __nv_bfloat16* a = dout + t * do_stride + h * HD + lane * 4;
-  const __nv_bfloat16* b = out + t * o_stride + h * HD + lane * 4;
-  const uint2 av = *reinterpret_cast<const uint2*>(a), bv = *reinterpret_cast<const uint2*>(b);
-  const float2 a0 = unpack_bf16x2(av.x), a1 = unpack_bf16x2(av.y), b0 = unpack_bf16x2(bv.x), b1 = unpack_bf16x2(bv.y);
-  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  constexpr int PER = HD / 32;   // elements per lane: 4 or 2
+  const __nv_bfloat16* a = dout + t * do_stride + h * HD + lane * PER;
+  const __nv_bfloat16* b = out + t * o_stride + h * HD + lane * PER;
+  float s = 0.f;
+#pragma unroll
+  for (int q = 0; q < PER / 2; ++q) {
+    const float2 x = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a)[q]), y = unpack_bf16x2(reinterpret_cast<const uint32_t*>(b)[q]);
+    s += x.x * y.x + x.y * y.y;
+  }
   s = warp_sum(s);
   if (lane == 0) delta[static_cast<long long>(h) * T + t] = s;
 }
@@ -358,7 +375,7 @@ int g_fwd_configured = 0;
 // qkv: [T, (Hq+2Hkv)*128] bf16 with row stride `qkv_stride` (elements); out: [T, Hq*128]; lse: [Hq, T] or null.
 // cu_seqlens: device int32 [num_seqs + 1]. max_tiles: an upper bound on the number of 128-row query tiles
 // (ceil(T / 128) + num_seqs is always enough).
-RLB_API int rlb_flash_attn_fwd(const void* qkv, long long qkv_stride, const int* cu_seqlens, int num_seqs, int T,
+RLB_API int RLB_NAME(rlb_flash_attn_fwd)(const void* qkv, long long qkv_stride, const int* cu_seqlens, int num_seqs, int T,
                                int Hq, int Hkv, int D, float scale, void* out, long long out_stride, float* lse,
                                int max_tiles, int* status, void* stream) {
   if (T <= 0 || num_seqs <= 0) return 0;
@@ -392,7 +409,7 @@ RLB_API int rlb_flash_attn_fwd(const void* qkv, long long qkv_stride, const int*
   return static_cast<int>(cudaGetLastError());
 }
 
-RLB_API int rlb_attn_delta(const void* dout, const void* out, float* delta, int T, int Hq, long long do_stride,
+RLB_API int RLB_NAME(rlb_attn_delta)(const void* dout, const void* out, float* delta, int T, int Hq, long long do_stride,
                            long long o_stride, void* stream) {
   if (T <= 0) return 0;
   const long long warps = static_cast<long long>(T) * Hq;

@@ -17,7 +17,15 @@
 namespace {
 using namespace rlb;
 
-constexpr int HD = 128;
+#ifndef RLB_HD
+#define RLB_HD 128        // head dimension of this translation unit; flash_attention_bwd_d64.cu includes this file with 64
+#endif
+#ifndef RLB_NAME
+#define RLB_NAME(x) x
+#endif
+constexpr int HD = RLB_HD;
+static_assert(HD == 64 || HD == 128, "head dimension: 64 or 128");
+constexpr int ATOMS = HD / 64;   // [rows x 64] swizzle atoms per operand tile along the head dimension
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int BWD_THREADS = 192;
 
@@ -62,6 +70,7 @@ struct BwdParams {
 constexpr int DQ_BQ = 128, DQ_BKV = 64;
 constexpr int DQ_Q_BYTES = DQ_BQ * HD * 2;     // 32 KB
 constexpr int DQ_KV_BYTES = DQ_BKV * HD * 2;   // 16 KB
+constexpr int DQ_Q_ATOM = DQ_BQ * 128, DQ_KV_ATOM = DQ_BKV * 128;   // bytes of one [rows x 64] bf16 atom
 constexpr int DQ_DS_BYTES = DQ_BQ * DQ_BKV * 2;  // 16 KB
 constexpr int DQ_SMEM = 2 * DQ_Q_BYTES + 4 * DQ_KV_BYTES + DQ_DS_BYTES + 256;
 
@@ -125,9 +134,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (warp == 0) {
     if (lane == 0) {
       mbar_arrive_expect_tx(smem_u32(q_full), 2 * DQ_Q_BYTES);
-      for (int a = 0; a < 2; ++a) {
-        tma_load_2d(smem_u32(q_s + a * (DQ_Q_BYTES / 2)), &tmap_q, smem_u32(q_full), q_col + a * 64, seq_start + q0);
-        tma_load_2d(smem_u32(do_s + a * (DQ_Q_BYTES / 2)), &tmap_do, smem_u32(q_full), head * HD + a * 64, seq_start + q0);
+      for (int a = 0; a < ATOMS; ++a) {
+        tma_load_2d(smem_u32(q_s + a * DQ_Q_ATOM), &tmap_q, smem_u32(q_full), q_col + a * 64, seq_start + q0);
+        tma_load_2d(smem_u32(do_s + a * DQ_Q_ATOM), &tmap_do, smem_u32(q_full), head * HD + a * 64, seq_start + q0);
       }
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
@@ -135,9 +144,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!mbar_wait(smem_u32(&kv_empty[st]), ph ^ 1, abort_flag, p.status, RLB_ERR_WAIT_EMPTY)) break;
         const int row = seq_start + j * DQ_BKV;
         mbar_arrive_expect_tx(smem_u32(&kv_full[st]), 2 * DQ_KV_BYTES);
-        for (int a = 0; a < 2; ++a) {
-          tma_load_2d(smem_u32(k_s + st * DQ_KV_BYTES + a * (DQ_KV_BYTES / 2)), &tmap_kv, smem_u32(&kv_full[st]), k_col + a * 64, row);
-          tma_load_2d(smem_u32(v_s + st * DQ_KV_BYTES + a * (DQ_KV_BYTES / 2)), &tmap_kv, smem_u32(&kv_full[st]), v_col + a * 64, row);
+        for (int a = 0; a < ATOMS; ++a) {
+          tma_load_2d(smem_u32(k_s + st * DQ_KV_BYTES + a * DQ_KV_ATOM), &tmap_kv, smem_u32(&kv_full[st]), k_col + a * 64, row);
+          tma_load_2d(smem_u32(v_s + st * DQ_KV_BYTES + a * DQ_KV_ATOM), &tmap_kv, smem_u32(&kv_full[st]), v_col + a * 64, row);
         }
       }
     }
@@ -153,15 +162,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off_a = (kk / 4) * (DQ_Q_BYTES / 2) + (kk % 4) * 32;
-          const uint32_t off_b = (kk / 4) * (DQ_KV_BYTES / 2) + (kk % 4) * 32;
+          const uint32_t off_a = (kk / 4) * DQ_Q_ATOM + (kk % 4) * 32;
+          const uint32_t off_b = (kk / 4) * DQ_KV_ATOM + (kk % 4) * 32;
           umma_f16(tmem_s, make_smem_desc_sw128(smem_u32(q_s) + off_a, 16, 1024),
                    make_smem_desc_sw128(smem_u32(k_s + st * DQ_KV_BYTES) + off_b, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off_a = (kk / 4) * (DQ_Q_BYTES / 2) + (kk % 4) * 32;
-          const uint32_t off_b = (kk / 4) * (DQ_KV_BYTES / 2) + (kk % 4) * 32;
+          const uint32_t off_a = (kk / 4) * DQ_Q_ATOM + (kk % 4) * 32;
+          const uint32_t off_b = (kk / 4) * DQ_KV_ATOM + (kk % 4) * 32;
           umma_f16(tmem_dp, make_smem_desc_sw128(smem_u32(do_s) + off_a, 16, 1024),
                    make_smem_desc_sw128(smem_u32(v_s + st * DQ_KV_BYTES) + off_b, 16, 1024), idesc_s, kk != 0);
         }
@@ -171,7 +180,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
         for (int kk = 0; kk < DQ_BKV / 16; ++kk) {
           umma_f16(tmem_dq, make_smem_desc_sw128(smem_u32(ds_s) + kk * 32, 16, 1024),
-                   make_smem_desc_sw128(smem_u32(k_s + st * DQ_KV_BYTES) + kk * 2048, DQ_KV_BYTES / 2, 1024), idesc_dq,
+                   make_smem_desc_sw128(smem_u32(k_s + st * DQ_KV_BYTES) + kk * 2048, DQ_KV_ATOM, 1024), idesc_dq,
                    (j | kk) != 0);
         }
         umma_commit(smem_u32(&kv_empty[st]));
@@ -261,6 +270,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 constexpr int KV_BKV = 128, KV_BQ = 64;
 constexpr int KV_K_BYTES = KV_BKV * HD * 2;      // 32 KB (two [128 x 64] atoms)
 constexpr int KV_Q_BYTES = KV_BQ * HD * 2;       // 16 KB (two [64 x 64] atoms)
+constexpr int KV_K_ATOM = KV_BKV * 128, KV_Q_ATOM = KV_BQ * 128;
 constexpr int KV_P_BYTES = KV_BKV * KV_BQ * 2;   // 16 KB (one [128 x 64] atom)
 constexpr int KV_STAT_BYTES = 2 * 2 * KV_BQ * 4; // lse2 / delta of the 64 query rows, double buffered
 constexpr int KV_SMEM = 2 * KV_K_BYTES + 4 * KV_Q_BYTES + 2 * KV_P_BYTES + KV_STAT_BYTES + 256;
@@ -329,9 +339,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_kv128, const __gri
   if (warp == 0) {
     if (lane == 0) {
       mbar_arrive_expect_tx(smem_u32(kv_full), 2 * KV_K_BYTES);
-      for (int a = 0; a < 2; ++a) {
-        tma_load_2d(smem_u32(k_s + a * (KV_K_BYTES / 2)), &tmap_kv128, smem_u32(kv_full), k_col + a * 64, seq_start + kv0);
-        tma_load_2d(smem_u32(v_s + a * (KV_K_BYTES / 2)), &tmap_kv128, smem_u32(kv_full), v_col + a * 64, seq_start + kv0);
+      for (int a = 0; a < ATOMS; ++a) {
+        tma_load_2d(smem_u32(k_s + a * KV_K_ATOM), &tmap_kv128, smem_u32(kv_full), k_col + a * 64, seq_start + kv0);
+        tma_load_2d(smem_u32(v_s + a * KV_K_ATOM), &tmap_kv128, smem_u32(kv_full), v_col + a * 64, seq_start + kv0);
       }
       for (int it = 0; it < n_iter; ++it) {
         const int st = it & 1;
@@ -341,9 +351,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_kv128, const __gri
         const int head = kv_head * G + g;
         const int row = seq_start + qt * KV_BQ;
         mbar_arrive_expect_tx(smem_u32(&qdo_full[st]), 2 * KV_Q_BYTES);
-        for (int a = 0; a < 2; ++a) {
-          tma_load_2d(smem_u32(q_s + st * KV_Q_BYTES + a * (KV_Q_BYTES / 2)), &tmap_q64, smem_u32(&qdo_full[st]), head * HD + a * 64, row);
-          tma_load_2d(smem_u32(do_s + st * KV_Q_BYTES + a * (KV_Q_BYTES / 2)), &tmap_do64, smem_u32(&qdo_full[st]), head * HD + a * 64, row);
+        for (int a = 0; a < ATOMS; ++a) {
+          tma_load_2d(smem_u32(q_s + st * KV_Q_BYTES + a * KV_Q_ATOM), &tmap_q64, smem_u32(&qdo_full[st]), head * HD + a * 64, row);
+          tma_load_2d(smem_u32(do_s + st * KV_Q_BYTES + a * KV_Q_ATOM), &tmap_do64, smem_u32(&qdo_full[st]), head * HD + a * 64, row);
         }
       }
     }
@@ -359,15 +369,15 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_kv128, const __gri
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off_a = (kk / 4) * (KV_K_BYTES / 2) + (kk % 4) * 32;
-          const uint32_t off_b = (kk / 4) * (KV_Q_BYTES / 2) + (kk % 4) * 32;
+          const uint32_t off_a = (kk / 4) * KV_K_ATOM + (kk % 4) * 32;
+          const uint32_t off_b = (kk / 4) * KV_Q_ATOM + (kk % 4) * 32;
           umma_f16(tmem_st, make_smem_desc_sw128(smem_u32(k_s) + off_a, 16, 1024),
                    make_smem_desc_sw128(smem_u32(q_s + st * KV_Q_BYTES) + off_b, 16, 1024), idesc_st, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off_a = (kk / 4) * (KV_K_BYTES / 2) + (kk % 4) * 32;
-          const uint32_t off_b = (kk / 4) * (KV_Q_BYTES / 2) + (kk % 4) * 32;
+          const uint32_t off_a = (kk / 4) * KV_K_ATOM + (kk % 4) * 32;
+          const uint32_t off_b = (kk / 4) * KV_Q_ATOM + (kk % 4) * 32;
           umma_f16(tmem_dpt, make_smem_desc_sw128(smem_u32(v_s) + off_a, 16, 1024),
                    make_smem_desc_sw128(smem_u32(do_s + st * KV_Q_BYTES) + off_b, 16, 1024), idesc_st, kk != 0);
         }
@@ -378,13 +388,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_kv128, const __gri
         for (int kk = 0; kk < KV_BQ / 16; ++kk) {
           // the query tile read as an MN-major operand: 16 query rows per step, 64-column groups 8 KB apart
           umma_f16(tmem_dv, make_smem_desc_sw128(smem_u32(pt_s) + kk * 32, 16, 1024),
-                   make_smem_desc_sw128(smem_u32(do_s + st * KV_Q_BYTES) + kk * 2048, KV_Q_BYTES / 2, 1024), idesc_acc,
+                   make_smem_desc_sw128(smem_u32(do_s + st * KV_Q_BYTES) + kk * 2048, KV_Q_ATOM, 1024), idesc_acc,
                    (it | kk) != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < KV_BQ / 16; ++kk) {
           umma_f16(tmem_dk, make_smem_desc_sw128(smem_u32(dst_s) + kk * 32, 16, 1024),
-                   make_smem_desc_sw128(smem_u32(q_s + st * KV_Q_BYTES) + kk * 2048, KV_Q_BYTES / 2, 1024), idesc_acc,
+                   make_smem_desc_sw128(smem_u32(q_s + st * KV_Q_BYTES) + kk * 2048, KV_Q_ATOM, 1024), idesc_acc,
                    (it | kk) != 0);
         }
         umma_commit(smem_u32(&qdo_empty[st]));
@@ -499,7 +509,7 @@ int g_bwd_configured = 0;
 // dqkv[T, (Hq+2Hkv)*128] = gradient of the packed causal attention w.r.t. the fused [q | k | v] buffer.
 // lse and delta are [Hq, T] fp32 (lse from the forward pass, delta from rlb_attn_delta).
 // max_q_tiles / max_kv_tiles: upper bounds on the number of 128-row tiles (ceil(T/128) + num_seqs is enough for both).
-RLB_API int rlb_flash_attn_bwd(const void* qkv, long long qkv_stride, const void* dout, long long do_stride,
+RLB_API int RLB_NAME(rlb_flash_attn_bwd)(const void* qkv, long long qkv_stride, const void* dout, long long do_stride,
                                const float* lse, const float* delta, const int* cu_seqlens, int num_seqs, int T, int Hq,
                                int Hkv, int D, float scale, void* dqkv, long long dqkv_stride, int max_q_tiles,
                                int max_kv_tiles, int* status, void* stream) {

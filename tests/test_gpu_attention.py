@@ -8,22 +8,22 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _case(lens, Hq, Hkv, seed=0):
+def _case(lens, Hq, Hkv, seed=0, D=128):
     torch.manual_seed(seed)
-    D = 128
     T = sum(lens)
     qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda") * 0.7).to(torch.bfloat16)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
     return qkv, cu, D
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("lens,Hq,Hkv", [([128], 2, 2), ([64], 4, 1), ([200, 57, 1, 333], 8, 2), ([1280] * 3, 32, 8), ([4096], 4, 4)])
-def test_flash_fwd(native_lib, lens, Hq, Hkv):
+def test_flash_fwd(native_lib, lens, Hq, Hkv, D):
     from rl_b200.ops import attention as A
     from rl_b200.ops import functional as F
     from rl_b200.ops.lib import check_status
 
-    qkv, cu, D = _case(lens, Hq, Hkv)
+    qkv, cu, D = _case(lens, Hq, Hkv, D=D)
     out, lse = A.flash_fwd(qkv, cu, Hq, Hkv, D, 1.0 / math.sqrt(D))
     torch.cuda.synchronize()
     assert check_status() == 0
@@ -39,12 +39,13 @@ def test_flash_fwd(native_lib, lens, Hq, Hkv):
     assert (torch.logsumexp(s, -1) - lse[0, :n]).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("lens,Hq,Hkv", [([128], 2, 2), ([200, 57, 1, 333], 8, 2), ([1280, 700], 8, 2)])
-def test_flash_autograd(native_lib, lens, Hq, Hkv):
+def test_flash_autograd(native_lib, lens, Hq, Hkv, D):
     from rl_b200.ops import functional as F
     from rl_b200.ops.lib import check_status
 
-    qkv, cu, D = _case(lens, Hq, Hkv, seed=1)
+    qkv, cu, D = _case(lens, Hq, Hkv, seed=1, D=D)
     x = qkv.clone().requires_grad_()
     y = F.attention_varlen(x, cu, max(lens), Hq, Hkv, D)
     g = torch.randn_like(y)

@@ -98,9 +98,10 @@ class ShardedAdamW:
             return g
         mine = g[self.lo : self.hi]
         if g.is_cuda:
-            out = torch.empty_like(mine)
-            dist.reduce_scatter_tensor(out, g, op=dist.ReduceOp.SUM, group=self.group)
-            return out
+            # in place: NCCL reduces into this rank's own slice of the buffer (recvbuff == sendbuff + rank * count), so no
+            # shard-sized temporary is needed (16 GB for a 32B model at TP4 x DP2)
+            dist.reduce_scatter_tensor(mine, g, op=dist.ReduceOp.SUM, group=self.group)
+            return mine
         dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce-scatter
         return mine
 
@@ -110,7 +111,7 @@ class ShardedAdamW:
         flat = self.flat.flat
         mine = flat[self.lo : self.hi]
         if flat.is_cuda:
-            dist.all_gather_into_tensor(flat, mine.clone(), group=self.group)
+            dist.all_gather_into_tensor(flat, mine, group=self.group)   # in place: this rank's slice is already where it belongs
         else:
             parts = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(parts, mine.contiguous(), group=self.group)

@@ -207,3 +207,26 @@ def test_grpo_over_the_data_plane_matches_the_in_memory_trainer(tmp_path):
     pol.abort_train_step()
     m = BatchMeta("p", ["a", "b", "c"], [3, 4, 5], ["g0", "g0", "g1"], {"x"})
     assert m.select([0, 2]).keys == ["a", "c"] and m.size == 3 and [s.num_tokens for s in m.sample_metas()] == [3, 4, 5]
+
+
+def test_prompt_group_record_to_rows_in_the_plane():
+    from rl_b200.experience.payload import Completion, PromptGroupRecord, pack_payload, record_to_train_batch
+
+    prompt = [{"role": "user", "content": "q", "token_ids": torch.tensor([5, 6, 7])}]
+
+    def completion(gen, reward):
+        return Completion([dict(prompt[0]), {"role": "assistant", "content": "a", "token_ids": torch.tensor(gen),
+                                             "generation_logprobs": torch.full((len(gen),), -0.5)}], reward)
+
+    rec = PromptGroupRecord(prompt, [completion([1, 2], 1.0), completion([3, 4, 8, 9], 0.0)], prompt_idx=3)
+    td = record_to_train_batch(rec)
+    assert td["input_ids"].tolist() == [[5, 6, 7, 1, 2, 0, 0], [5, 6, 7, 3, 4, 8, 9]] and td["input_lengths"].tolist() == [5, 7]
+    assert td["token_mask"].tolist() == [[0, 0, 0, 1, 1, 0, 0], [0, 0, 0, 1, 1, 1, 1]] and td["total_reward"].tolist() == [1.0, 0.0]
+    assert td["prompt_ids_for_adv"].tolist() == [[5, 6, 7], [5, 6, 7]] and td["generation_logprobs"][0, 3].item() == -0.5
+    keys, recs, metas = pack_payload(td, weight_version=4, group_id="s7_p3")
+    assert keys == ["s7_p3_g0", "s7_p3_g1"] and recs[0]["input_ids"].tolist() == [5, 6, 7, 1, 2] and recs[1]["token_mask"].numel() == 7
+    assert [m.weight_version for m in metas] == [4, 4] and metas[0].num_tokens == 5 and metas[1].group == "s7_p3"
+    plane = LocalDataPlane()
+    plane.put_batch(keys, recs, metas)
+    back = records_to_batch(plane.get(keys, ("input_ids", "input_lengths")))
+    assert torch.equal(back["input_ids"], td["input_ids"])

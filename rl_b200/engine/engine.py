@@ -481,9 +481,19 @@ class GenerationEngine:
 
     # ------------------------------------------------------------------ model forward (inference)
     def _layer_tail(self, layer, h, a):
-        eps = self.cfg.rms_norm_eps
-        h = layer.self_attn.project_out(a, h)  # tp > 1: GEMM + all-reduce (+ residual) in one kernel; adds LoRA deltas
-        return layer.mlp(F.rmsnorm(h, layer.post_attention_layernorm, eps), h)
+        # o_proj (tp > 1: GEMM + all-reduce (+ residual) in one kernel; adds LoRA deltas), norms and MLP in the family's order
+        return layer.tail(h, a)
+
+    def _embed(self, ids):
+        m = self.model
+        h = F.embedding(ids, m.embed_tokens)
+        s = self.cfg.embed_scale
+        return h if s == 1.0 else h * torch.tensor(s, dtype=h.dtype, device=h.device)
+
+    def _freq(self, layer):
+        """RoPE frequencies of a layer (sliding-window layers may rotate with their own base)."""
+        m = self.model
+        return m.inv_freq_local if (layer.window and m.inv_freq_local is not None) else m.inv_freq
 
     def _output_logits(self, h, out=None):
         """[n, V] logits: the local vocabulary slice is projected here and the slices are gathered over the tp group."""
@@ -535,14 +545,14 @@ class GenerationEngine:
     @torch.no_grad()
     def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor) -> torch.Tensor:
         m, c = self.model, self.cfg
-        h = F.embedding(batch.input_ids, m.embed_tokens)
+        h = self._embed(batch.input_ids)
         if hasattr(m, "merge_vision"):
             h = m.merge_vision(h, batch.input_ids, getattr(batch, "mm", None))
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq, apply_rope=False)
-            qkv = E.rope_kv_cache_write(qkv, batch.positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
-            a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, self.hq, self.hkv, c.head_dim)
+            qkv = E.rope_kv_cache_write(qkv, batch.positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            a = F.attention_varlen(qkv, batch.cu_seqlens, batch.max_seqlen, self.hq, self.hkv, c.head_dim, scale=c.attn_scale, window=layer.window)
             h = self._layer_tail(layer, h, a)
         hl = E.gather_rows(h, last_idx.to(torch.int32))
         hl = F.rmsnorm(hl, m.norm, c.rms_norm_eps)
@@ -557,6 +567,8 @@ class GenerationEngine:
             return False
         if c.hidden_size % 128 or c.intermediate_size % 64 or not len(self.model.layers):
             return False
+        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None:
+            return False   # the fused step hard-wires the Llama / Qwen block structure
         l0 = self.model.layers[0]
         return getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
 
@@ -606,6 +618,8 @@ class GenerationEngine:
             return False
         if c.hidden_size % 128 or not len(self.model.layers):
             return False
+        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None:
+            return False
         l0 = self.model.layers[0]
         f_local = l0.mlp.gate_up_proj.shape[0] // 2
         return (f_local % 64 == 0 and getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
@@ -645,13 +659,13 @@ class GenerationEngine:
         if self._can_fuse_decode_tp(ids.shape[0]):
             return self._decode_forward_fused_tp(ids, positions, slots, block_table, seq_lens, num_splits, scratch, logits_out)
         m, c = self.model, self.cfg
-        h = F.embedding(ids, m.embed_tokens)
+        h = self._embed(ids)
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
-            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
+            qkv = E.rope_kv_cache_write(qkv, positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
             a = E.paged_decode(qkv, self.k_cache[li], self.v_cache[li], block_table, seq_lens, self.hq,
-                               self.hkv, c.head_dim, num_splits=num_splits, scratch=scratch)
+                               self.hkv, c.head_dim, scale=c.attn_scale, window=layer.window, num_splits=num_splits, scratch=scratch)
             h = self._layer_tail(layer, h, a)
         h = F.rmsnorm(h, m.norm, c.rms_norm_eps)
         return self._output_logits(h, logits_out)
@@ -872,20 +886,20 @@ class GenerationEngine:
             pre_rows = torch.cat(pre_idx).to(dev)
             pre_blk, pre_off = ps // self.block_size, ps % self.block_size
         total, W = row, (hq + 2 * hkv) * D
-        h = F.embedding(ids, m.embed_tokens)
+        h = self._embed(ids)
         for li, layer in enumerate(m.layers):
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
-            qkv = E.rope_kv_cache_write(qkv, positions, m.inv_freq, slots, self.k_cache[li], self.v_cache[li], hq, hkv, D)
+            qkv = E.rope_kv_cache_write(qkv, positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], hq, hkv, D)
             if pre_slots:
                 # rows of the cached prefix carry keys / values from the cache pages (already rotated) and a zero query
                 full = torch.zeros((total, W), dtype=qkv.dtype, device=dev)
                 full[new_rows] = qkv
                 full[pre_rows, hq * D : (hq + hkv) * D] = self.k_cache[li][pre_blk, :, pre_off, :].reshape(-1, hkv * D)
                 full[pre_rows, (hq + hkv) * D :] = self.v_cache[li][pre_blk, :, pre_off, :].reshape(-1, hkv * D)
-                a = F.attention_varlen(full, cu, max(full_lens), hq, hkv, D)[new_rows]
+                a = F.attention_varlen(full, cu, max(full_lens), hq, hkv, D, scale=c.attn_scale, window=layer.window)[new_rows]
             else:
-                a = F.attention_varlen(qkv, cu, max(full_lens), hq, hkv, D)
+                a = F.attention_varlen(qkv, cu, max(full_lens), hq, hkv, D, scale=c.attn_scale, window=layer.window)
             h = self._layer_tail(layer, h, a)
         hl = E.gather_rows(h, torch.tensor(last, dtype=torch.int32, device=dev))
         return self._output_logits(F.rmsnorm(hl, m.norm, c.rms_norm_eps))

@@ -1,7 +1,8 @@
 """Architecture description for the decoder-only model families the framework trains and serves.
 
-One dataclass covers Llama (2/3/3.1/3.2), Mistral, Qwen2/2.5, Qwen3 and Qwen3-MoE; the differences are switches
-(QKV bias, per-head q/k RMSNorm, tied embeddings, RoPE scaling, mixture-of-experts FFN). ``from_hf_dict`` reads a
+One dataclass covers Llama (2/3/3.1/3.2), Mistral, Qwen2/2.5, Qwen3, Qwen3-MoE and Gemma 3 (text); the differences are switches
+(QKV bias, per-head q/k RMSNorm, tied embeddings, RoPE scaling, mixture-of-experts FFN; for Gemma 3: tanh-GELU gate, norms
+before and after each block, scaled embeddings, sliding-window layers with their own RoPE base, a fixed attention scale). ``from_hf_dict`` reads a
 HuggingFace ``config.json`` dictionary; ``PRESETS`` names the architectures used by the benchmark configs.
 """
 
@@ -46,6 +47,19 @@ class ModelConfig:
     value_head: bool = False           # critic / reward model: scalar head instead of the vocabulary projection
     vision: Optional[dict] = None      # vision tower settings (models/vision.py); None: text-only model
     image_token_id: Optional[int] = None
+    # Gemma 3 (nemo_rl/models/dtensor/parallelize.py:170-217 is the reference's parallel plan for this family)
+    hidden_act: str = "silu"           # gate activation of the MLP: silu | gelu_pytorch_tanh
+    sandwich_norm: bool = False        # RMSNorm before AND after attention / MLP (the post norms act on the block output)
+    embed_scale: float = 1.0           # embeddings are multiplied by this (sqrt(hidden_size))
+    norm_offset: float = 0.0           # checkpoints store RMSNorm weights as w - offset (Gemma: 1); buffers here hold w
+    sliding_window: int = 0            # > 0: layers listed as "sliding_attention" see only the last `sliding_window` keys
+    layer_types: Optional[list] = None  # per layer: "full_attention" | "sliding_attention"
+    rope_local_theta: float = 0.0      # RoPE base of the sliding-window layers (0: same as rope_theta, scaling included)
+    attn_scale: Optional[float] = None  # softmax scale when it is not head_dim ** -0.5 (query_pre_attn_scalar ** -0.5)
+    final_logit_softcap: float = 0.0   # logits <- cap * tanh(logits / cap) (Gemma 2; 0: off)
+
+    def layer_is_sliding(self, i: int) -> bool:
+        return bool(self.sliding_window) and self.layer_types is not None and self.layer_types[i] == "sliding_attention"
 
     @property
     def q_size(self) -> int:
@@ -76,10 +90,17 @@ class ModelConfig:
 
     def to_hf_dict(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
-                "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+                "gemma3_text": "Gemma3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         d = asdict(self)
         d.pop("value_head")
         d.pop("qk_norm")
+        gem = {k: d.pop(k) for k in ("hidden_act", "sandwich_norm", "embed_scale", "norm_offset", "sliding_window", "layer_types",
+                                     "rope_local_theta", "attn_scale", "final_logit_softcap")}
+        if self.model_type == "gemma3_text":
+            d.update(hidden_activation=gem["hidden_act"], sliding_window=gem["sliding_window"], layer_types=gem["layer_types"],
+                     rope_local_base_freq=gem["rope_local_theta"], query_pre_attn_scalar=round(gem["attn_scale"] ** -2) if gem["attn_scale"] else self.head_dim,
+                     final_logit_softcapping=gem["final_logit_softcap"] or None)
         d["architectures"] = [arch]
         if self.vision is None:
             d.pop("vision")
@@ -92,6 +113,9 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, hf: dict, **overrides) -> "ModelConfig":
         mt = hf.get("model_type", "llama")
+        if mt == "gemma3" and "text_config" in hf:      # the multimodal wrapper: the language model's settings are nested
+            hf = dict(hf["text_config"], model_type="gemma3_text")
+            mt = "gemma3_text"
         n_heads = hf["num_attention_heads"]
         cfg = cls(
             model_type=mt,
@@ -108,7 +132,7 @@ class ModelConfig:
             max_position_embeddings=hf.get("max_position_embeddings", 131072),
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", False)),
             attention_bias=bool(hf.get("attention_bias", mt == "qwen2")),
-            qk_norm=mt in ("qwen3", "qwen3_moe"),
+            qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"),
             num_experts=hf.get("num_experts", 0) if mt.endswith("_moe") else 0,
             num_experts_per_tok=hf.get("num_experts_per_tok", 0),
             moe_intermediate_size=hf.get("moe_intermediate_size", 0),
@@ -121,6 +145,25 @@ class ModelConfig:
             vision=hf.get("vision"),
             image_token_id=hf.get("image_token_id"),
         )
+        if mt == "gemma3_text":
+            L = cfg.num_hidden_layers
+            pattern = int(hf.get("sliding_window_pattern", 6) or 6)
+            cfg.hidden_act = hf.get("hidden_activation", "gelu_pytorch_tanh")
+            cfg.sandwich_norm, cfg.norm_offset = True, 1.0
+            cfg.embed_scale = float(cfg.hidden_size) ** 0.5
+            cfg.sliding_window = int(hf.get("sliding_window") or 0)
+            cfg.layer_types = list(hf.get("layer_types") or ["sliding_attention" if (i + 1) % pattern else "full_attention" for i in range(L)])
+            cfg.rope_local_theta = float(hf.get("rope_local_base_freq", 10000.0))
+            cfg.attn_scale = float(hf.get("query_pre_attn_scalar", cfg.head_dim)) ** -0.5
+            cfg.final_logit_softcap = float(hf.get("final_logit_softcapping") or 0.0)
+            cfg.tie_word_embeddings = bool(hf.get("tie_word_embeddings", True))
+            cfg.rms_norm_eps = hf.get("rms_norm_eps", 1e-6)
+            rp = hf.get("rope_parameters")    # newer configs nest the RoPE settings per layer type
+            if isinstance(rp, dict) and "full_attention" in rp:
+                full, loc = rp["full_attention"], rp.get("sliding_attention", {})
+                cfg.rope_theta = float(full.get("rope_theta", cfg.rope_theta))
+                cfg.rope_scaling = {k: v for k, v in full.items() if k != "rope_theta"} if full.get("rope_type", "default") != "default" else None
+                cfg.rope_local_theta = float(loc.get("rope_theta", cfg.rope_local_theta))
         for k, v in overrides.items():
             setattr(cfg, k, v)
         return cfg
@@ -192,6 +235,12 @@ PRESETS: dict[str, dict] = {
                          num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
                          rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=True, tie_word_embeddings=True),
     # the CPU/gloo oracle model: 4 layers, d 256, 4 heads, SwiGLU 688, vocab 2048
+    # Gemma-3-1B (text): 26 layers, d 1152, 4 q / 1 kv heads of 256, GeGLU 6912, five sliding-window (512) layers per global one
+    "gemma3-1b": dict(model_type="gemma3_text", vocab_size=262144, hidden_size=1152, intermediate_size=6912, num_hidden_layers=26,
+                      num_attention_heads=4, num_key_value_heads=1, head_dim=256, rms_norm_eps=1e-6, rope_theta=1000000.0,
+                      tie_word_embeddings=True, qk_norm=True, hidden_act="gelu_pytorch_tanh", sandwich_norm=True, embed_scale=1152 ** 0.5,
+                      norm_offset=1.0, sliding_window=512, rope_local_theta=10000.0, attn_scale=256 ** -0.5,
+                      layer_types=["full_attention" if (i + 1) % 6 == 0 else "sliding_attention" for i in range(26)]),
     "tiny-llama-oracle": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
                               num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
                               rms_norm_eps=1e-5, rope_theta=10000.0),

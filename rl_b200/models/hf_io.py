@@ -39,6 +39,7 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         elif not tied:
             vl = cfg.vocab_size // tp_size
             rows.append(("lm_head.weight", "lm_head", None, None, (0, tp_rank * vl, vl) if tp_size > 1 else None))
+    # (Gemma's two extra norms per layer are added with the other layer tensors below)
     if cfg.vision is not None and first_stage:   # vision tower: replicated, stored under its own names
         from .vision import vision_config
 
@@ -70,6 +71,9 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         if cfg.qk_norm:
             rows += [(f"{hp}.self_attn.q_norm.weight", f"{lp}.self_attn.q_norm", None, None, None),
                      (f"{hp}.self_attn.k_norm.weight", f"{lp}.self_attn.k_norm", None, None, None)]
+        if cfg.sandwich_norm:
+            rows += [(f"{hp}.pre_feedforward_layernorm.weight", f"{lp}.pre_feedforward_layernorm", None, None, None),
+                     (f"{hp}.post_feedforward_layernorm.weight", f"{lp}.post_feedforward_layernorm", None, None, None)]
         if cfg.is_moe:
             f = cfg.moe_intermediate_size
             rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None, None))
@@ -127,8 +131,11 @@ def iter_hf_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
     from rl_b200.parallel.tensor import all_gather_rows
 
     tp = model.tp
+    off = float(getattr(model.cfg, "norm_offset", 0.0) or 0.0)
     for hf, t, hs in iter_hf_shards(model):
-        if hs is None or tp.world == 1:
+        if off and _is_norm_weight(hf):
+            yield hf, (t.detach().float() - off).to(t.dtype)    # checkpoints of this family store w - offset
+        elif hs is None or tp.world == 1:
             yield hf, t
         elif hs[0] == 0:
             yield hf, all_gather_rows(t.detach(), tp.group, tp.world)
@@ -136,11 +143,17 @@ def iter_hf_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
             yield hf, all_gather_rows(t.detach().t().contiguous(), tp.group, tp.world).t().contiguous()
 
 
+def _is_norm_weight(hf_name: str) -> bool:
+    return hf_name.endswith("norm.weight") or hf_name.endswith("layernorm.weight")
+
+
 @torch.no_grad()
 def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]], strict: bool = True) -> list[str]:
     """Copies HF-named tensors (as returned by ``get(name)``) into the fused (and possibly sharded) parameters.
-    Returns missing names."""
+    Returns missing names. Families whose checkpoints store RMSNorm weights as ``w - 1`` (Gemma) get the offset added
+    here and removed by :func:`iter_hf_tensors`, so the buffers always hold the multiplier itself."""
     missing = []
+    off = float(getattr(model.cfg, "norm_offset", 0.0) or 0.0)
     for hf, dst, hs in iter_hf_shards(model):
         src = get(hf)
         if src is None:
@@ -150,6 +163,8 @@ def load_hf_tensors(model: CausalLM, get: Callable[[str], Optional[torch.Tensor]
             src = src.narrow(hs[0], hs[1], hs[2])
         if tuple(src.shape) != tuple(dst.shape):
             raise ValueError(f"{hf}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
+        if off and _is_norm_weight(hf):
+            src = src.float() + off
         dst.copy_(src.to(dst.dtype))
     if strict and missing:
         raise KeyError(f"{len(missing)} tensors missing from checkpoint, first: {missing[:5]}")

@@ -182,9 +182,10 @@ class Attention(nn.Module):
             return qkv
         return F.rope(qkv, positions, inv_freq, self.hq + self.hkv, c.head_dim)
 
-    def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen):
+    def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen, window: int = 0):
         c = self.cfg
         if self.cp is not None:
+            assert not window and c.attn_scale is None, "context parallelism: no sliding windows / custom attention scale"
             from rl_b200.parallel.context import cp_attention_varlen
 
             T = positions.numel()
@@ -192,7 +193,7 @@ class Attention(nn.Module):
             a = cp_attention_varlen(qkv, cu_seqlens, self.cp, self.hq, self.hkv, c.head_dim, total_rows=T)
             return F.linear(a, self.o_proj, None, residual)
         qkv = self.project_qkv(x, positions, inv_freq)
-        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim)
+        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, c.head_dim, scale=c.attn_scale, window=window)
         return self.project_out(a, residual)
 
     def project_out(self, a, residual):
@@ -214,6 +215,7 @@ class DenseMLP(nn.Module):
         d, f = cfg.hidden_size, cfg.intermediate_size // self.tp.world
         self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
+        self.act = cfg.hidden_act
         self.gate_up_lora = self.down_lora = None
         if lora:
             assert self.tp.world == 1, "LoRA adapters are not tensor parallel"
@@ -226,7 +228,7 @@ class DenseMLP(nn.Module):
             dl = self.gate_up_lora.delta(x)
             if dl is not None:
                 h = h + dl
-        a = F.swiglu(h)
+        a = F.gated_act(h, self.act)
         y = row_linear(a, self.down_proj, residual, self.tp)
         if self.down_lora is not None:
             dl = self.down_lora.delta(a)
@@ -236,10 +238,16 @@ class DenseMLP(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None, lora: Optional[dict] = None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None, lora: Optional[dict] = None,
+                 layer_idx: int = 0):
         super().__init__()
         self.cfg = cfg
         d = cfg.hidden_size
+        self.layer_idx = layer_idx
+        self.window = cfg.sliding_window if cfg.layer_is_sliding(layer_idx) else 0
+        if cfg.sandwich_norm:   # Gemma: the block outputs are normalised too, before they join the residual stream
+            self.pre_feedforward_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+            self.post_feedforward_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         self.self_attn = Attention(cfg, dtype, device, tp, cp, lora)
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
@@ -252,10 +260,30 @@ class DecoderLayer(nn.Module):
             self.mlp = DenseMLP(cfg, dtype, device, tp, lora)
 
     def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
+        """``inv_freq``: the model's RoPE frequencies, or a pair (global, local) when sliding-window layers rotate with
+        their own base."""
         eps = self.cfg.rms_norm_eps
-        h = self.self_attn(F.rmsnorm(h, self.input_layernorm, eps), h, positions, inv_freq, cu_seqlens, max_seqlen)
+        if isinstance(inv_freq, tuple):
+            inv_freq = inv_freq[1] if self.window else inv_freq[0]
+        if self.cfg.sandwich_norm:
+            a = self.self_attn(F.rmsnorm(h, self.input_layernorm, eps), None, positions, inv_freq, cu_seqlens, max_seqlen, self.window)
+            h = h + F.rmsnorm(a, self.post_attention_layernorm, eps)
+            m = self.mlp(F.rmsnorm(h, self.pre_feedforward_layernorm, eps), None)
+            return h + F.rmsnorm(m, self.post_feedforward_layernorm, eps)
+        h = self.self_attn(F.rmsnorm(h, self.input_layernorm, eps), h, positions, inv_freq, cu_seqlens, max_seqlen, self.window)
         h = self.mlp(F.rmsnorm(h, self.post_attention_layernorm, eps), h)
         return h
+
+    def tail(self, h, a):
+        """From the attention output ``a`` (before o_proj) to the layer's output; used by the generation engine, whose
+        attention runs over its paged cache."""
+        eps = self.cfg.rms_norm_eps
+        if self.cfg.sandwich_norm:
+            h = h + F.rmsnorm(self.self_attn.project_out(a, None), self.post_attention_layernorm, eps)
+            m = self.mlp(F.rmsnorm(h, self.pre_feedforward_layernorm, eps), None)
+            return h + F.rmsnorm(m, self.post_feedforward_layernorm, eps)
+        h = self.self_attn.project_out(a, h)
+        return self.mlp(F.rmsnorm(h, self.post_attention_layernorm, eps), h)
 
 
 @dataclass
@@ -343,7 +371,8 @@ class CausalLM(nn.Module):
             self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
         else:
             self.embed_tokens = None
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg) for _ in range(n_local)])
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg, layer_idx=self.layer_offset + i)
+                                     for i in range(n_local)])
         self.lm_head = None
         if self.last_stage:
             self.norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
@@ -354,6 +383,15 @@ class CausalLM(nn.Module):
         else:
             self.norm = None
         self.register_buffer("inv_freq", rope_inv_freq(cfg, device), persistent=False)
+        if cfg.rope_local_theta:   # sliding-window layers rotate with their own base and no long-context scaling
+            from dataclasses import replace
+
+            self.register_buffer("inv_freq_local", rope_inv_freq(replace(cfg, rope_theta=cfg.rope_local_theta, rope_scaling=None), device),
+                                 persistent=False)
+        else:
+            self.inv_freq_local = None
+        if cfg.final_logit_softcap:
+            raise NotImplementedError("final logit soft-capping (Gemma 2) is not supported by the fused log-probability paths")
         self.activation_checkpointing = activation_checkpointing
         if init:
             self.reset_parameters(seed)
@@ -455,7 +493,16 @@ class CausalLM(nn.Module):
         return self.embed_tokens[self.vocab_start : self.vocab_start + self.vocab_local]
 
     # ------------------------------------------------------------------ forward
+    def rope_freqs(self):
+        """What the layers take as ``inv_freq``: one tensor, or (global, local) when sliding-window layers have their own."""
+        return self.inv_freq if self.inv_freq_local is None else (self.inv_freq, self.inv_freq_local)
+
     def embed(self, batch: PackedBatch) -> torch.Tensor:
+        h = self._embed(batch)
+        s = self.cfg.embed_scale
+        return h if s == 1.0 else h * torch.tensor(s, dtype=h.dtype, device=h.device)   # the scale is rounded to the model dtype first
+
+    def _embed(self, batch: PackedBatch) -> torch.Tensor:
         if self.sharder is not None:
             return self.sharder.run("embed", lambda: F.embedding(batch.input_ids, self.embed_tokens))
         if self.tp.world > 1 and self.tp.sequence_parallel:
@@ -469,7 +516,7 @@ class CausalLM(nn.Module):
         return F.embedding(batch.input_ids, self.embed_tokens)
 
     def run_layers(self, h: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
-        inv_freq = self.inv_freq
+        inv_freq = self.rope_freqs()
         if self.sharder is not None:
             for i, layer in enumerate(self.layers):
                 h = self.sharder.run(f"layer{i}", lambda x, L=layer: L(x, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen), h)

@@ -71,7 +71,7 @@ def choose_splits(B: int, Hkv: int, max_len: int, block_size: int, sm_count: int
     return int(max(1, min(want, max(1, max_len // max(block_size, 128)), 32)))
 
 
-def _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out, rows_per_chunk: int = 64):
+def _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out, rows_per_chunk: int = 64, window: int = 0):
     """Decode attention for head dimensions the native kernels do not cover (they are built for 128): the paged keys and
     values of a chunk of sequences are gathered through the block table and attended with batched matmuls. No host
     synchronisation and static shapes, so it can be captured in a CUDA graph like the native path."""
@@ -87,6 +87,8 @@ def _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D,
         qb = (q[r0:r1, : Hq * D].reshape(r1 - r0, Hkv, g, D).float() * scale).to(k.dtype)
         s_ = torch.matmul(qb, k.transpose(2, 3)).float()
         live = ar[None, :] < seq_lens[r0:r1, None]
+        if window:
+            live = live & (ar[None, :] >= seq_lens[r0:r1, None] - window)
         s_ = s_.masked_fill(~live[:, None, None, :], float("-inf"))
         p = torch.nan_to_num(torch.softmax(s_, dim=-1), nan=0.0)   # rows without context (padding rows) give zeros
         out[r0:r1] = torch.matmul(p.to(v.dtype), v).reshape(r1 - r0, Hq * D).to(out.dtype)
@@ -96,8 +98,9 @@ def _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D,
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                  seq_lens: torch.Tensor, Hq: int, Hkv: int, D: int, *, scale: Optional[float] = None,
                  num_splits: int = 1, scratch: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention of one query token per sequence against its paged KV. ``q`` [B, Hq*D] (rows may be strided)."""
+                 out: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
+    """Attention of one query token per sequence against its paged KV. ``q`` [B, Hq*D] (rows may be strided). ``window`` > 0:
+    only the last ``window`` cached tokens are visible (sliding-window layers; served by the gather path)."""
     B = q.shape[0]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     block_size = k_cache.shape[2]
@@ -112,14 +115,15 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                 continue
             nb = (n + block_size - 1) // block_size
             blocks = block_table[b, :nb].long()
-            k = k_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, :n].float()
-            v = v_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, :n].float()
+            lo = max(0, n - window) if window else 0
+            k = k_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, lo:n].float()
+            v = v_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nb * block_size, D)[:, lo:n].float()
             qb = q[b, : Hq * D].reshape(Hkv, g, D).float() * scale
             p = torch.softmax(qb @ k.transpose(1, 2), dim=-1)
             out[b] = (p @ v).reshape(Hq * D).to(out.dtype)
         return out
-    if D != 128:
-        return _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out)
+    if D != 128 or window:
+        return _paged_decode_gather(q, k_cache, v_cache, block_table, seq_lens, Hq, Hkv, D, scale, out, window=window)
     po = pml = None
     if num_splits > 1:
         if scratch is None:

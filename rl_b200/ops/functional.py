@@ -445,6 +445,18 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(gate_up.contiguous())
 
 
+def gated_act(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(gate) * up for a fused [..., 2F] projection: ``silu`` (SwiGLU, native kernel) or ``gelu_pytorch_tanh`` (GeGLU)."""
+    if act == "silu":
+        return swiglu(gate_up)
+    g, u = gate_up.chunk(2, dim=-1)
+    if act in ("gelu_pytorch_tanh", "gelu_tanh"):
+        return (tF.gelu(g.float(), approximate="tanh") * u.float()).to(gate_up.dtype)
+    if act == "gelu":
+        return (tF.gelu(g.float()) * u.float()).to(gate_up.dtype)
+    raise ValueError(f"unknown gate activation '{act}'")
+
+
 # --------------------------------------------------------------------------------------- embedding
 class _Embedding(torch.autograd.Function):
     @staticmethod
@@ -480,7 +492,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------------------- attention (varlen, causal, GQA)
-def _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale):
+def _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale, window: int = 0):
+    """``window`` > 0: a query sees only the last ``window`` keys up to and including itself (sliding-window layers)."""
     T = qkv.shape[0]
     q = qkv[:, : Hq * D].reshape(T, Hq, D)
     k = qkv[:, Hq * D : (Hq + Hkv) * D].reshape(T, Hkv, D)
@@ -494,7 +507,13 @@ def _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale):
         qs = q[s:e].transpose(0, 1).unsqueeze(0)
         ks = k[s:e].transpose(0, 1).unsqueeze(0)
         vs = v[s:e].transpose(0, 1).unsqueeze(0)
-        o = tF.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale, enable_gqa=g > 1)
+        n = e - s
+        if window and n > window:
+            i = torch.arange(n, device=qkv.device)
+            band = (i[None, :] <= i[:, None]) & (i[None, :] > i[:, None] - window)
+            o = tF.scaled_dot_product_attention(qs, ks, vs, attn_mask=band, scale=scale, enable_gqa=g > 1)
+        else:
+            o = tF.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale, enable_gqa=g > 1)
         out[s:e] = o[0].transpose(0, 1)
     return out.reshape(T, Hq * D)
 
@@ -509,13 +528,14 @@ def set_attention_impl(fn) -> None:
 
 
 def attention_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, Hq: int, Hkv: int, D: int,
-                     scale: Optional[float] = None) -> torch.Tensor:
+                     scale: Optional[float] = None, window: int = 0) -> torch.Tensor:
     """Causal self-attention over packed sequences. ``qkv`` is the fused projection output [T, (Hq+2Hkv)*D] (after
-    RoPE); ``cu_seqlens`` [B+1] int32 are the packed sequence boundaries. Returns [T, Hq*D]."""
+    RoPE); ``cu_seqlens`` [B+1] int32 are the packed sequence boundaries. Returns [T, Hq*D]. ``window`` > 0 restricts every
+    query to its last ``window`` keys (the native kernels have no window: sequences longer than it take the PyTorch path)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if use_native(qkv) and _attn_impl is not None:
+    if use_native(qkv) and _attn_impl is not None and not (window and max_seqlen > window):
         return _attn_impl(qkv, cu_seqlens, max_seqlen, Hq, Hkv, D, scale)
-    return _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale)
+    return _attention_ref(qkv, cu_seqlens, Hq, Hkv, D, scale, window)
 
 
 # --------------------------------------------------------------------------------------- fused lm_head -> logprob / entropy

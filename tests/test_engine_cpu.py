@@ -142,3 +142,30 @@ def test_native_scheduler_lookahead_reserves_blocks_for_a_window():
     t.commit(pf, [0, 0], first=True)
     t.schedule()
     assert t.window == 1
+
+
+def test_engine_serves_gemma_style_layers():
+    """Sliding-window layers (context longer than the window), their own RoPE base, norms after the blocks, GeGLU, scaled
+    embeddings and a fixed attention scale: the engine's prefill, chunked / cached-prefix prefill and paged decode give the
+    log-probabilities of the training model."""
+    from rl_b200.models.config import preset
+
+    torch.manual_seed(0)
+    mc = preset("gemma3-1b", torch_dtype="float32", vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=3,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=8, sliding_window=6, attn_scale=0.3, embed_scale=32 ** 0.5,
+                layer_types=["sliding_attention", "full_attention", "sliding_attention"])
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    for kw in (dict(), dict(max_prefill_tokens=8, enable_prefix_caching=True)):
+        eng = GenerationEngine(model, block_size=4, num_blocks=64, max_running=8, max_model_len=64, use_cuda_graphs=False, **kw)
+        prompts = [[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11], [9, 8, 7], [11] * 9]
+        recs = eng.generate(prompts, SamplingParams(max_new_tokens=10, stop_token_ids=[], seed=3, temperature=0.8))
+        for r in recs:
+            seq = torch.tensor([r.prompt + r.out_tokens])
+            b = PackedBatch.from_padded(seq, torch.tensor([seq.shape[1]]))
+            lp, _ = model.next_token_logprobs(b, temperature=0.8)
+            got = torch.tensor(r.out_logprobs)
+            assert torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (kw, lp[len(r.prompt):], got)

@@ -280,6 +280,11 @@ def main() -> int:
         res = policy.train(train_data, loss_fn, gbs=cfg["policy"]["train_global_batch_size"], mbs=4)
         ev[4].record()
         torch.cuda.synchronize()
+        if rank == 0:   # progress on stderr: a run that is cut short still leaves the phases of the steps it finished
+            print("[bench] step done (%s): " % ("timed" if timed else "warm-up") +
+                  ", ".join("%s %.0f ms" % (n, ev[a].elapsed_time(ev[b])) for n, a, b in
+                            (("refit", 0, 1), ("generation", 1, 2), ("logprobs", 2, 3), ("training", 3, 4))) +
+                  ", tokens %d, status %d" % (int(train_data["input_lengths"].sum()), L.check_status()), file=sys.stderr, flush=True)
         if timed:
             for name, a, b in (("refit", 0, 1), ("generation", 1, 2), ("logprobs", 2, 3), ("training", 3, 4)):
                 phase_ms[name] += ev[a].elapsed_time(ev[b])

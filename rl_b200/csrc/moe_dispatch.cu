@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) push_rows_kernel(const unsigned char* __r
                                                         const int* __restrict__ src_row, const int* __restrict__ dst_rank,
                                                         const int* __restrict__ dst_row, int n, int row_bytes, PeerBufs pb,
                                                         int rank, int world, int record_meta, int stage, unsigned int epoch,
-                                                        unsigned long long limit_ns, int* status) {
+                                                        unsigned long long limit_ns, int* status, long long dst_capacity) {
   const int warps_per_cta = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = row_bytes / 16;
@@ -70,6 +70,10 @@ __global__ void __launch_bounds__(256) push_rows_kernel(const unsigned char* __r
     const int r = dst_rank[i];
     if (r < 0) continue;
     const long long drow = dst_row[i];
+    if (r >= world || drow < 0 || drow >= dst_capacity) {   // a store outside the peer's buffer is recorded and skipped
+      if (lane == 0 && status) atomicCAS(status, 0, RLB_ERR_BOUNDS);
+      continue;
+    }
     const uint4* s = reinterpret_cast<const uint4*>(src_base + static_cast<long long>(src_row ? src_row[i] : i) * src_pitch);
     uint4* d = reinterpret_cast<uint4*>(pb.rows[r] + drow * row_bytes);
     for (int v0 = lane; v0 < vecs; v0 += 128) {  // four vectors in flight per lane
@@ -92,13 +96,17 @@ __global__ void __launch_bounds__(256) return_rows_kernel(const unsigned char* _
                                                           const int2* __restrict__ meta, const int* __restrict__ valid, int n,
                                                           int row_bytes, PeerBufs pb,
                                                           int rank, int world, int stage, unsigned int epoch,
-                                                          unsigned long long limit_ns, int* status) {
+                                                          unsigned long long limit_ns, int* status, long long dst_capacity) {
   const int warps_per_cta = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int vecs = row_bytes / 16;
   for (int j = blockIdx.x * warps_per_cta + warp; j < n; j += gridDim.x * warps_per_cta) {
     if (!valid[j]) continue;
     const int2 m = meta[j];
+    if (m.x < 0 || m.x >= world || m.y < 0 || m.y >= dst_capacity) {   // a stale or corrupt return address: recorded, skipped
+      if (lane == 0 && status) atomicCAS(status, 0, RLB_ERR_BOUNDS);
+      continue;
+    }
     const uint4* s = reinterpret_cast<const uint4*>(src_base + static_cast<long long>(j) * src_pitch);
     uint4* d = reinterpret_cast<uint4*>(pb.rows[m.x] + static_cast<long long>(m.y) * row_bytes);
     for (int v0 = lane; v0 < vecs; v0 += 128) {
@@ -138,12 +146,13 @@ void fill(PeerBufs& pb, void* const* row_ptrs, void* const* meta_ptrs, void* con
 RLB_API int rlb_moe_push_rows(const void* src, long long src_pitch_bytes, const int* src_row, const int* dst_rank,
                               const int* dst_row, int n, int row_bytes, void* const* row_ptrs, void* const* meta_ptrs,
                               void* const* flag_ptrs, int rank, int world, int stage, unsigned int epoch, double wait_limit_s,
-                              int* status, void* stream) {
+                              int* status, long long dst_capacity_rows, void* stream) {
   if (world < 1 || world > MAX_EP || (row_bytes % 16) || (src_pitch_bytes % 16) || stage < 0 || stage > 1) return -2;
   PeerBufs pb;
   fill(pb, row_ptrs, meta_ptrs, flag_ptrs, world);
   const int grid = grid_for(n);
-  void* args[] = {&src, &src_pitch_bytes, &src_row, &dst_rank, &dst_row, &n, &row_bytes, &pb, &rank, &world, nullptr, &stage, &epoch, nullptr, &status};
+  void* args[] = {&src, &src_pitch_bytes, &src_row, &dst_rank, &dst_row, &n, &row_bytes, &pb, &rank, &world, nullptr, &stage, &epoch, nullptr, &status,
+                  &dst_capacity_rows};
   int record = meta_ptrs != nullptr;
   unsigned long long limit = static_cast<unsigned long long>(wait_limit_s * 1e9);
   args[10] = &record;
@@ -155,13 +164,13 @@ RLB_API int rlb_moe_push_rows(const void* src, long long src_pitch_bytes, const 
 // Returns row j of `src` (j < n) to rank meta[j].x, row meta[j].y of that rank's buffer, then barriers like above.
 RLB_API int rlb_moe_return_rows(const void* src, long long src_pitch_bytes, const void* meta, const int* valid, int n, int row_bytes,
                                 void* const* row_ptrs, void* const* flag_ptrs, int rank, int world, int stage, unsigned int epoch,
-                                double wait_limit_s, int* status, void* stream) {
+                                double wait_limit_s, int* status, long long dst_capacity_rows, void* stream) {
   if (world < 1 || world > MAX_EP || (row_bytes % 16) || (src_pitch_bytes % 16) || stage < 0 || stage > 1) return -2;
   PeerBufs pb;
   fill(pb, row_ptrs, nullptr, flag_ptrs, world);
   const int grid = grid_for(n);
   unsigned long long limit = static_cast<unsigned long long>(wait_limit_s * 1e9);
-  void* args[] = {&src, &src_pitch_bytes, &meta, &valid, &n, &row_bytes, &pb, &rank, &world, &stage, &epoch, &limit, &status};
+  void* args[] = {&src, &src_pitch_bytes, &meta, &valid, &n, &row_bytes, &pb, &rank, &world, &stage, &epoch, &limit, &status, &dst_capacity_rows};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(return_rows_kernel), dim3(grid), dim3(256), args, 0,
                                                       static_cast<cudaStream_t>(stream)));
 }

@@ -113,8 +113,8 @@ class EPFusedComm:
         self.epoch = [0, 0]
         lib = _L.lib()
         P, I, LL, U, D = C.c_void_p, C.c_int, C.c_longlong, C.c_uint, C.c_double
-        lib.rlb_moe_push_rows.argtypes = [P, LL, P, P, P, I, I, P, P, P, I, I, I, U, D, P, P]
-        lib.rlb_moe_return_rows.argtypes = [P, LL, P, P, I, I, P, P, I, I, I, U, D, P, P]
+        lib.rlb_moe_push_rows.argtypes = [P, LL, P, P, P, I, I, P, P, P, I, I, I, U, D, P, LL, P]
+        lib.rlb_moe_return_rows.argtypes = [P, LL, P, P, I, I, P, P, I, I, I, U, D, P, LL, P]
         lib.rlb_moe_push_rows.restype = lib.rlb_moe_return_rows.restype = C.c_int
         self._lib, self._L = lib, _L
 
@@ -135,7 +135,7 @@ class EPFusedComm:
         rc = self._lib.rlb_moe_push_rows(src.data_ptr(), src.stride(0) * src.element_size(), None, dst_rank.data_ptr(), dst_row.data_ptr(),
                                          n, d * src.element_size(), self.recv.table, self.meta.table if record_meta else None,
                                          self.ctrl.table, self.rank, self.world, 0, self.epoch[0], float(self.wait_limit_s),
-                                         self._L.status_word(src.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                                         self._L.status_word(src.device).data_ptr(), self.cap_rows, torch.cuda.current_stream().cuda_stream)
         self._L.Counters.launches += 1
         if rc:
             raise RuntimeError(f"rlb_moe_push_rows failed with code {rc}")
@@ -147,7 +147,7 @@ class EPFusedComm:
         rc = self._lib.rlb_moe_return_rows(src.data_ptr(), src.stride(0) * src.element_size(), meta.data_ptr(), valid.data_ptr(), n,
                                            d * src.element_size(), self.ret.table, self.ctrl.table, self.rank, self.world, 1,
                                            self.epoch[1], float(self.wait_limit_s), self._L.status_word(src.device).data_ptr(),
-                                           torch.cuda.current_stream().cuda_stream)
+                                           self.max_copies, torch.cuda.current_stream().cuda_stream)
         self._L.Counters.launches += 1
         if rc:
             raise RuntimeError(f"rlb_moe_return_rows failed with code {rc}")

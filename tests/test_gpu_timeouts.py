@@ -103,7 +103,7 @@ def test_moe_dispatch_times_out_cleanly(native_lib):
     from rl_b200.ops.lib import check_status, lib as get_lib, status_word
 
     lib = get_lib()
-    lib.rlb_moe_push_rows.argtypes = [P, LL, P, P, P, I, I, P, P, P, I, I, I, U, D, P, P]
+    lib.rlb_moe_push_rows.argtypes = [P, LL, P, P, P, I, I, P, P, P, I, I, I, U, D, P, LL, P]
     lib.rlb_moe_push_rows.restype = C.c_int
     check_status()
     n, d, world = 64, 256, 2
@@ -114,7 +114,7 @@ def test_moe_dispatch_times_out_cleanly(native_lib):
     metas = [torch.zeros(n, 2, dtype=torch.int32, device="cuda") for _ in range(world)]
     flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
     rc = lib.rlb_moe_push_rows(src.data_ptr(), d * 2, None, dst_rank.data_ptr(), dst_row.data_ptr(), n, d * 2, _table(*bufs),
-                               _table(*metas), _table(*flags), 0, world, 0, 1, WAIT_S, status_word().data_ptr(),
+                               _table(*metas), _table(*flags), 0, world, 0, 1, WAIT_S, status_word().data_ptr(), n,
                                torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     t0 = time.perf_counter()
@@ -122,6 +122,19 @@ def test_moe_dispatch_times_out_cleanly(native_lib):
     assert time.perf_counter() - t0 < 1.0
     assert check_status() == 7                        # the closing barrier gave up on the silent peer
     assert torch.equal(bufs[0], src) and torch.all(bufs[1] == 0)   # local rows landed; the "peer" got nothing
+    _plain_gemm_ok()
+    # a destination row beyond the receiver's buffer is recorded and skipped, never stored (world 1: no peer to wait for)
+    bad_row = dst_row.clone()
+    bad_row[5] = n + 3
+    one = [torch.zeros(n, d, device="cuda", dtype=torch.bfloat16)]
+    rc = lib.rlb_moe_push_rows(src.data_ptr(), d * 2, None, dst_rank.data_ptr(), bad_row.data_ptr(), n, d * 2, _table(*one),
+                               _table(metas[0]), _table(flags[0]), 0, 1, 0, 2, WAIT_S, status_word().data_ptr(), n,
+                               torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and check_status() == 8            # RLB_ERR_BOUNDS
+    keep = torch.ones(n, dtype=torch.bool, device="cuda")
+    keep[5] = False
+    assert torch.equal(one[0][keep], src[keep]) and torch.all(one[0][5] == 0)
     _plain_gemm_ok()
 
 

@@ -493,6 +493,10 @@ class GenerationEngine:
     def _freq(self, layer):
         """RoPE frequencies of a layer (sliding-window layers may rotate with their own base)."""
         m = self.model
+        if self.cfg.is_mla:   # latent attention rotates its decoupled rotary part itself: the cache write rotates by zero
+            if getattr(self, "_zero_freq", None) is None:
+                self._zero_freq = torch.zeros(self.cfg.head_dim // 2, dtype=torch.float32, device=self.device)
+            return self._zero_freq
         return m.inv_freq_local if (layer.window and m.inv_freq_local is not None) else m.inv_freq
 
     def _output_logits(self, h, out=None):
@@ -567,7 +571,7 @@ class GenerationEngine:
             return False
         if c.hidden_size % 128 or c.intermediate_size % 64 or not len(self.model.layers):
             return False
-        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None:
+        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None or c.is_mla:
             return False   # the fused step hard-wires the Llama / Qwen block structure
         l0 = self.model.layers[0]
         return getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
@@ -618,7 +622,7 @@ class GenerationEngine:
             return False
         if c.hidden_size % 128 or not len(self.model.layers):
             return False
-        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None:
+        if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None or c.is_mla:
             return False
         l0 = self.model.layers[0]
         f_local = l0.mlp.gate_up_proj.shape[0] // 2

@@ -58,6 +58,27 @@ class ModelConfig:
     attn_scale: Optional[float] = None  # softmax scale when it is not head_dim ** -0.5 (query_pre_attn_scalar ** -0.5)
     final_logit_softcap: float = 0.0   # logits <- cap * tanh(logits / cap) (Gemma 2; 0: off)
 
+    # DeepSeek-V3: multi-head latent attention and its mixture of experts
+    kv_lora_rank: int = 0              # > 0: attention is MLA (keys / values decompressed from a latent of this width)
+    q_lora_rank: Optional[int] = None  # low-rank query projection (None: a plain q_proj)
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    rope_interleave: bool = True       # checkpoints store the rotary dimensions interleaved (pairs), not split in halves
+    n_shared_experts: int = 0          # dense experts every token passes through, added to the routed output
+    first_k_dense_replace: int = 0     # the first k layers keep a dense MLP
+    scoring_func: str = "softmax"      # router scores: softmax | sigmoid (with a per-expert selection bias)
+    n_group: int = 1                   # experts are split in groups; only `topk_group` groups stay eligible per token
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_k_dense_replace
+
     def layer_is_sliding(self, i: int) -> bool:
         return bool(self.sliding_window) and self.layer_types is not None and self.layer_types[i] == "sliding_attention"
 
@@ -91,7 +112,7 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
                 "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
-                "gemma3_text": "Gemma3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "gemma3_text": "Gemma3ForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         d = asdict(self)
         d.pop("value_head")
         d.pop("qk_norm")
@@ -105,9 +126,15 @@ class ModelConfig:
         if self.vision is None:
             d.pop("vision")
             d.pop("image_token_id")
+        ds = {k: d.pop(k) for k in ("kv_lora_rank", "q_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim", "rope_interleave",
+                                    "n_shared_experts", "first_k_dense_replace", "scoring_func", "n_group", "topk_group", "routed_scaling_factor")}
+        if self.model_type == "deepseek_v3":
+            d.update(ds, n_routed_experts=self.num_experts)
+            d.pop("num_experts")
+            d.pop("head_dim")
         if not self.is_moe:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob", "router_aux_loss_coef"):
-                d.pop(k)
+                d.pop(k, None)
         return d
 
     @classmethod
@@ -133,7 +160,7 @@ class ModelConfig:
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", False)),
             attention_bias=bool(hf.get("attention_bias", mt == "qwen2")),
             qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"),
-            num_experts=hf.get("num_experts", 0) if mt.endswith("_moe") else 0,
+            num_experts=(hf.get("num_experts", 0) if mt.endswith("_moe") else (hf.get("n_routed_experts") or 0) if mt == "deepseek_v3" else 0),
             num_experts_per_tok=hf.get("num_experts_per_tok", 0),
             moe_intermediate_size=hf.get("moe_intermediate_size", 0),
             norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
@@ -145,6 +172,25 @@ class ModelConfig:
             vision=hf.get("vision"),
             image_token_id=hf.get("image_token_id"),
         )
+        if mt == "deepseek_v3":
+            for k in ("kv_lora_rank", "q_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim", "n_shared_experts",
+                      "first_k_dense_replace", "n_group", "topk_group", "routed_scaling_factor"):
+                if hf.get(k) is not None or k == "q_lora_rank":
+                    setattr(cfg, k, hf.get(k))
+            cfg.rope_interleave = bool(hf.get("rope_interleave", True))
+            cfg.scoring_func = hf.get("scoring_func", "sigmoid")
+            cfg.num_key_value_heads = cfg.num_attention_heads       # after decompression every head has its own keys and values
+            cfg.head_dim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim   # what the attention kernels and the KV cache see (V is padded to it)
+            rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+            if isinstance(rp, dict) and rp.get("rope_type", rp.get("type", "default")) != "default":
+                cfg.rope_scaling = {k: v for k, v in rp.items() if k != "rope_theta"}
+                cfg.rope_theta = float(rp.get("rope_theta", cfg.rope_theta))
+                m_all = float(rp.get("mscale_all_dim", 0) or 0)
+                if m_all and float(rp["factor"]) > 1:      # the long-context recipe also sharpens the soft-max
+                    ms = 0.1 * m_all * math.log(float(rp["factor"])) + 1.0
+                    cfg.attn_scale = cfg.head_dim ** -0.5 * ms * ms
+            elif isinstance(rp, dict) and rp.get("rope_theta"):
+                cfg.rope_theta = float(rp["rope_theta"])
         if mt == "gemma3_text":
             L = cfg.num_hidden_layers
             pattern = int(hf.get("sliding_window_pattern", 6) or 6)
@@ -181,7 +227,7 @@ class ModelConfig:
 
 def rope_inv_freq(cfg: ModelConfig, device=None) -> torch.Tensor:
     """Inverse frequencies [head_dim/2] including the ``llama3`` / ``linear`` / ``yarn`` scaling rules."""
-    D = cfg.head_dim
+    D = cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim     # MLA rotates only the decoupled rotary part of each head
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
     rs = cfg.rope_scaling or {}
     kind = rs.get("rope_type", rs.get("type", "default"))

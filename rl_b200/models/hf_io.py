@@ -57,26 +57,48 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         rows += [
             (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None, None),
             (f"{hp}.post_attention_layernorm.weight", f"{lp}.post_attention_layernorm", None, None, None),
-            (f"{hp}.self_attn.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, q), None, sl(0, q)),
-            (f"{hp}.self_attn.k_proj.weight", f"{lp}.self_attn.qkv_proj", (q, q + kv), None, sl(0, kv)),
-            (f"{hp}.self_attn.v_proj.weight", f"{lp}.self_attn.qkv_proj", (q + kv, q + 2 * kv), None, sl(0, kv)),
-            (f"{hp}.self_attn.o_proj.weight", f"{lp}.self_attn.o_proj", None, None, sl(1, q)),
         ]
+        if cfg.is_mla:   # latent attention (not tensor parallel): its projections keep their own names
+            sa = f"{hp}.self_attn"
+            if cfg.q_lora_rank:
+                rows += [(f"{sa}.q_a_proj.weight", f"{lp}.self_attn.q_a_proj", None, None, None),
+                         (f"{sa}.q_a_layernorm.weight", f"{lp}.self_attn.q_a_layernorm", None, None, None),
+                         (f"{sa}.q_b_proj.weight", f"{lp}.self_attn.q_b_proj", None, None, None)]
+            else:
+                rows.append((f"{sa}.q_proj.weight", f"{lp}.self_attn.q_proj", None, None, None))
+            rows += [(f"{sa}.kv_a_proj_with_mqa.weight", f"{lp}.self_attn.kv_a_proj", None, None, None),
+                     (f"{sa}.kv_a_layernorm.weight", f"{lp}.self_attn.kv_a_layernorm", None, None, None),
+                     (f"{sa}.kv_b_proj.weight", f"{lp}.self_attn.kv_b_proj", None, None, None),
+                     (f"{sa}.o_proj.weight", f"{lp}.self_attn.o_proj", None, None, None)]
+        else:
+            rows += [
+                (f"{hp}.self_attn.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, q), None, sl(0, q)),
+                (f"{hp}.self_attn.k_proj.weight", f"{lp}.self_attn.qkv_proj", (q, q + kv), None, sl(0, kv)),
+                (f"{hp}.self_attn.v_proj.weight", f"{lp}.self_attn.qkv_proj", (q + kv, q + 2 * kv), None, sl(0, kv)),
+                (f"{hp}.self_attn.o_proj.weight", f"{lp}.self_attn.o_proj", None, None, sl(1, q)),
+            ]
         if cfg.attention_bias:
             rows += [
                 (f"{hp}.self_attn.q_proj.bias", f"{lp}.self_attn.qkv_bias", (0, q), None, sl(0, q)),
                 (f"{hp}.self_attn.k_proj.bias", f"{lp}.self_attn.qkv_bias", (q, q + kv), None, sl(0, kv)),
                 (f"{hp}.self_attn.v_proj.bias", f"{lp}.self_attn.qkv_bias", (q + kv, q + 2 * kv), None, sl(0, kv)),
             ]
-        if cfg.qk_norm:
+        if cfg.qk_norm and not cfg.is_mla:
             rows += [(f"{hp}.self_attn.q_norm.weight", f"{lp}.self_attn.q_norm", None, None, None),
                      (f"{hp}.self_attn.k_norm.weight", f"{lp}.self_attn.k_norm", None, None, None)]
         if cfg.sandwich_norm:
             rows += [(f"{hp}.pre_feedforward_layernorm.weight", f"{lp}.pre_feedforward_layernorm", None, None, None),
                      (f"{hp}.post_feedforward_layernorm.weight", f"{lp}.post_feedforward_layernorm", None, None, None)]
-        if cfg.is_moe:
+        if cfg.layer_is_moe(layer_offset + j):
             f = cfg.moe_intermediate_size
             rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None, None))
+            if cfg.scoring_func == "sigmoid":
+                rows.append((f"{hp}.mlp.gate.e_score_correction_bias", f"{lp}.mlp.e_score_correction_bias", None, None, None))
+            if cfg.n_shared_experts:
+                fs = f * cfg.n_shared_experts
+                rows += [(f"{hp}.mlp.shared_experts.gate_proj.weight", f"{lp}.mlp.shared_experts.gate_up_proj", (0, fs), None, None),
+                         (f"{hp}.mlp.shared_experts.up_proj.weight", f"{lp}.mlp.shared_experts.gate_up_proj", (fs, 2 * fs), None, None),
+                         (f"{hp}.mlp.shared_experts.down_proj.weight", f"{lp}.mlp.shared_experts.down_proj", None, None, None)]
             for e in range(cfg.num_experts):
                 rows += [
                     (f"{hp}.mlp.experts.{e}.gate_proj.weight", f"{lp}.mlp.gate_up_proj", (0, f), e, None),
@@ -94,7 +116,9 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
 
 
 def _local(model: CausalLM) -> dict[str, torch.Tensor]:
-    return dict(model.named_parameters())
+    out = dict(model.named_parameters())
+    out.update({n: b for n, b in model.named_buffers() if n.endswith("e_score_correction_bias")})   # stored in checkpoints, not trained
+    return out
 
 
 def _model_map(model: CausalLM):

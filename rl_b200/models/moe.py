@@ -1,4 +1,5 @@
-"""Mixture-of-experts feed-forward block (Qwen3-MoE style: softmax router, top-k, optional renormalisation).
+"""Mixture-of-experts feed-forward block: Qwen3-MoE style (softmax router, top-k, optional renormalisation) and DeepSeek-V3
+style (sigmoid scores, a per-expert selection bias, group-limited top-k, a scaling factor, shared experts).
 
 Tokens are sorted by expert once, each expert's SwiGLU MLP runs over its contiguous slice, and the weighted
 outputs are scattered back. With expert parallelism (``ep_group``) the sorted slices are exchanged with an
@@ -33,11 +34,45 @@ class MoEMLP(nn.Module):
         self.router = nn.Parameter(torch.empty(E, d, dtype=dtype, device=device))
         self.gate_up_proj = nn.Parameter(torch.empty(self.local_experts, 2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(self.local_experts, d, f, dtype=dtype, device=device))
+        if cfg.scoring_func == "sigmoid":
+            # selection bias of the auxiliary-loss-free load balancing: shifts which experts are chosen, never the weights;
+            # not trained by gradient (a buffer, stored in checkpoints as mlp.gate.e_score_correction_bias)
+            self.register_buffer("e_score_correction_bias", torch.zeros(E, dtype=torch.float32, device=device))
+        self.shared_experts = None
+        if cfg.n_shared_experts:
+            from .transformer import DenseMLP
+
+            self.shared_experts = DenseMLP(cfg, dtype, device, intermediate_size=cfg.moe_intermediate_size * cfg.n_shared_experts)
         self.last_routing: Optional[torch.Tensor] = None  # top-k expert ids of the last forward (router replay / traces)
         self.forced_routing: Optional[torch.Tensor] = None  # when set, replaces the router's choice (router replay)
 
+    def _route_sigmoid(self, x: torch.Tensor):
+        """DeepSeek-V3 routing: sigmoid scores; experts are chosen by score + bias among the ``topk_group`` best groups (a
+        group's rank is the sum of its two best biased scores); the weights are the unbiased scores, renormalised and scaled."""
+        c = self.cfg
+        E, k = c.num_experts, c.num_experts_per_tok
+        scores = torch.sigmoid(x.float() @ self.router.float().t())
+        if self.forced_routing is not None:
+            idx = self.forced_routing
+        else:
+            choice = scores + self.e_score_correction_bias
+            if c.n_group > 1:
+                g = choice.view(-1, c.n_group, E // c.n_group)
+                gs = g.topk(2, dim=-1)[0].sum(-1)
+                keep = torch.zeros_like(gs).scatter_(1, gs.topk(c.topk_group, dim=-1, sorted=False)[1], 1.0)
+                choice = choice.masked_fill(~keep.bool().unsqueeze(-1).expand_as(g).reshape(-1, E), 0.0)
+            idx = choice.topk(k, dim=-1, sorted=False)[1]
+        w = scores.gather(1, idx)
+        if c.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w * c.routed_scaling_factor
+        self.last_routing = idx.detach()
+        return w, idx, scores
+
     def route(self, x: torch.Tensor):
         c = self.cfg
+        if c.scoring_func == "sigmoid":
+            return self._route_sigmoid(x)
         logits = F.linear(x, self.router).float()
         probs = torch.softmax(logits, dim=-1)
         if self.forced_routing is not None:
@@ -70,6 +105,8 @@ class MoEMLP(nn.Module):
         c = self.cfg
         if torch.is_grad_enabled() or self.forced_routing is not None or not _L.available():
             return None
+        if c.scoring_func != "softmax" or self.shared_experts is not None:
+            return None   # the routing kernel implements the soft-max router; other routers take the general path
         W = self.ep_size
         lock = int(getattr(self.ep, "lockstep_tokens", 0) or 0)
         if W > 1 and (lock <= 0 or self.ep.comm is None):
@@ -121,4 +158,6 @@ class MoEMLP(nn.Module):
         wy = ys * w.reshape(-1)[order].unsqueeze(-1).to(ys.dtype)
         out = torch.zeros_like(x) if residual is None else residual.clone()
         out = out.index_add(0, tok, wy)
+        if self.shared_experts is not None:
+            out = self.shared_experts(x, out)
         return out

@@ -205,14 +205,95 @@ class Attention(nn.Module):
         return y
 
 
+def _rope_interleaved(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, interleave: bool) -> torch.Tensor:
+    """Rotary embedding of ``x`` [T, H, R]. ``interleave``: the R dimensions are stored as (even, odd) pairs and are first
+    regrouped into halves (DeepSeek checkpoints); the rotation itself is the half-split form."""
+    T, H, R = x.shape
+    if interleave:
+        x = x.reshape(T, H, R // 2, 2).transpose(2, 3).reshape(T, H, R)
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]            # [T, R / 2]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x1, x2 = x[..., : R // 2].float(), x[..., R // 2 :].float()
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class MLAAttention(nn.Module):
+    """Multi-head latent attention (DeepSeek-V2 / V3): queries go through a low-rank bottleneck, keys and values are
+    decompressed per head from one shared latent of width ``kv_lora_rank``, and positions enter through a small decoupled
+    rotary part (``qk_rope_head_dim`` dimensions, one rotary key shared by all heads).
+
+    For the attention kernels and the generation engine's paged cache the result is laid out like ordinary attention with
+    ``H`` query and ``H`` key / value heads of ``qk_nope_head_dim + qk_rope_head_dim`` dimensions; values are zero-padded to
+    that width and the padding is dropped before ``o_proj``. (The engine therefore caches decompressed keys and values, not
+    the latent: simple, at the cost of the memory MLA was designed to save.) Not tensor parallel."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, cp=None, lora: Optional[dict] = None):
+        super().__init__()
+        self.cfg, self.tp = cfg, tp or TP()
+        assert self.tp.world == 1 and (cp is None or cp.world == 1) and not lora, "MLA: no tensor / context parallelism, no LoRA"
+        self.cp = None
+        self.qkv_lora = self.o_lora = None
+        d, H = cfg.hidden_size, cfg.num_attention_heads
+        self.hq = self.hkv = H
+        self.nope, self.rope, self.vd = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        self.dq = self.nope + self.rope
+        assert cfg.head_dim == self.dq and self.vd <= self.dq
+        self.q_local = self.kv_local = H * self.dq
+        P = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))   # noqa: E731
+        if cfg.q_lora_rank:
+            self.q_a_proj, self.q_b_proj = P(cfg.q_lora_rank, d), P(H * self.dq, cfg.q_lora_rank)
+            self.q_a_layernorm = nn.Parameter(torch.ones(cfg.q_lora_rank, dtype=dtype, device=device))
+        else:
+            self.q_proj = P(H * self.dq, d)
+        self.kv_a_proj = P(cfg.kv_lora_rank + self.rope, d)
+        self.kv_a_layernorm = nn.Parameter(torch.ones(cfg.kv_lora_rank, dtype=dtype, device=device))
+        self.kv_b_proj = P(H * (self.nope + self.vd), cfg.kv_lora_rank)
+        self.o_proj = P(d, H * self.vd)
+        self.qkv_bias = None
+
+    def project_qkv(self, x, positions, inv_freq, apply_rope: bool = True):
+        """x [T, d] -> fused [T, 3 * H * dq] = [q | k | v (zero-padded)], already rotated (the rotary part is rotated here
+        whatever ``apply_rope`` says: callers that rotate themselves are handed zero frequencies for these layers)."""
+        c = self.cfg
+        T, H = x.shape[0], self.hq
+        eps = c.rms_norm_eps
+        if c.q_lora_rank:
+            q = F.linear(F.rmsnorm(F.linear(x, self.q_a_proj), self.q_a_layernorm, eps), self.q_b_proj)
+        else:
+            q = F.linear(x, self.q_proj)
+        q = q.reshape(T, H, self.dq)
+        ckv = F.linear(x, self.kv_a_proj)
+        lat, k_rot = ckv[:, : c.kv_lora_rank], ckv[:, c.kv_lora_rank :]
+        kv = F.linear(F.rmsnorm(lat.contiguous(), self.kv_a_layernorm, eps), self.kv_b_proj).reshape(T, H, self.nope + self.vd)
+        q_rot = _rope_interleaved(q[..., self.nope :], positions, inv_freq, c.rope_interleave)
+        k_rot = _rope_interleaved(k_rot.reshape(T, 1, self.rope), positions, inv_freq, c.rope_interleave).expand(T, H, self.rope)
+        qf = torch.cat([q[..., : self.nope], q_rot], dim=-1)
+        kf = torch.cat([kv[..., : self.nope], k_rot], dim=-1)
+        vf = torch.nn.functional.pad(kv[..., self.nope :], (0, self.dq - self.vd))
+        return torch.cat([qf.reshape(T, -1), kf.reshape(T, -1), vf.reshape(T, -1)], dim=1)
+
+    def forward(self, x, residual, positions, inv_freq, cu_seqlens, max_seqlen, window: int = 0):
+        c = self.cfg
+        qkv = self.project_qkv(x, positions, inv_freq)
+        a = F.attention_varlen(qkv, cu_seqlens, max_seqlen, self.hq, self.hkv, self.dq, scale=c.attn_scale, window=window)
+        return self.project_out(a, residual)
+
+    def project_out(self, a, residual):
+        T = a.shape[0]
+        a = a.reshape(T, self.hq, self.dq)[..., : self.vd].reshape(T, self.hq * self.vd)
+        return F.linear(a.contiguous(), self.o_proj, None, residual)
+
+
 class DenseMLP(nn.Module):
     """SwiGLU MLP; ``gate_up_proj`` rows are [local gate | local up] (column-parallel), ``down_proj`` row-parallel."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, lora: Optional[dict] = None):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, lora: Optional[dict] = None,
+                 intermediate_size: Optional[int] = None):
         super().__init__()
         self.tp = tp or TP()
-        assert cfg.intermediate_size % self.tp.world == 0
-        d, f = cfg.hidden_size, cfg.intermediate_size // self.tp.world
+        inter = intermediate_size or cfg.intermediate_size
+        assert inter % self.tp.world == 0
+        d, f = cfg.hidden_size, inter // self.tp.world
         self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
         self.act = cfg.hidden_act
@@ -249,9 +330,9 @@ class DecoderLayer(nn.Module):
             self.pre_feedforward_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
             self.post_feedforward_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device, tp, cp, lora)
+        self.self_attn = (MLAAttention if cfg.is_mla else Attention)(cfg, dtype, device, tp, cp, lora)
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
-        if cfg.is_moe:
+        if cfg.layer_is_moe(layer_idx):
             from .moe import MoEMLP
 
             assert tp is None or tp.world == 1, "MoE layers shard experts (ep), not tensors"
@@ -432,6 +513,9 @@ class CausalLM(nn.Module):
                 mod.reset(g)
         for hf, dst, hs in iter_hf_shards(self):
             if hf.endswith("norm.weight") or hf.endswith("layernorm.weight") or hf.endswith(".bias"):
+                continue
+            if hf.endswith("e_score_correction_bias"):
+                dst.zero_()
                 continue
             g = torch.Generator(device=dst.device)
             g.manual_seed((seed * 1000003 + zlib.crc32(hf.encode())) & 0x7FFFFFFFFFFFFFFF)

@@ -169,3 +169,30 @@ def test_engine_serves_gemma_style_layers():
             lp, _ = model.next_token_logprobs(b, temperature=0.8)
             got = torch.tensor(r.out_logprobs)
             assert torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (kw, lp[len(r.prompt):], got)
+
+
+def test_engine_serves_latent_attention_and_deepseek_experts():
+    """DeepSeek-V3 layers through the engine: latent attention (keys / values cached decompressed, values padded to the key
+    width, the rotary part rotated by the layer itself) and the sigmoid / grouped router with a shared expert."""
+    torch.manual_seed(0)
+    mc = ModelConfig(model_type="deepseek_v3", vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                     num_key_value_heads=4, head_dim=12, kv_lora_rank=8, q_lora_rank=12, qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=6,
+                     num_experts=8, num_experts_per_tok=2, moe_intermediate_size=16, n_shared_experts=1, first_k_dense_replace=1,
+                     scoring_func="sigmoid", n_group=2, topk_group=1, routed_scaling_factor=1.5, torch_dtype="float32")
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.mul_(4.0)
+        for n, b in model.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(torch.randn_like(b) * 0.2)
+    eng = GenerationEngine(model, block_size=4, num_blocks=64, max_running=8, max_model_len=64, use_cuda_graphs=False)
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9, 8, 7], [11] * 9]
+    recs = eng.generate(prompts, SamplingParams(max_new_tokens=8, stop_token_ids=[], seed=3, temperature=0.8))
+    for r in recs:
+        seq = torch.tensor([r.prompt + r.out_tokens])
+        b = PackedBatch.from_padded(seq, torch.tensor([seq.shape[1]]))
+        lp, _ = model.next_token_logprobs(b, temperature=0.8)
+        got = torch.tensor(r.out_logprobs)
+        assert torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (lp[len(r.prompt):], got)

@@ -51,3 +51,71 @@ def test_gemma3_matches_huggingface():
     lp, _ = m.next_token_logprobs(batch)
     lp.sum().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in m.named_parameters())
+
+
+def _deepseek_get(sd):
+    """HF keeps the experts stacked (``experts.gate_up_proj`` [E, 2f, d]); checkpoints and this repo name them per expert."""
+    import re
+
+    def get(name):
+        m = re.match(r"(.*\.mlp\.experts)\.(\d+)\.(gate|up|down)_proj\.weight", name)
+        if not m:
+            return sd.get(name)
+        base, e, which = m.group(1), int(m.group(2)), m.group(3)
+        if which == "down":
+            return sd[base + ".down_proj"][e]
+        gu = sd[base + ".gate_up_proj"][e]
+        f = gu.shape[0] // 2
+        return gu[:f] if which == "gate" else gu[f:]
+
+    return get
+
+
+@pytest.mark.parametrize("q_lora,yarn", [(24, False), (None, True)])
+def test_deepseek_v3_matches_huggingface(q_lora, yarn):
+    """DeepSeek-V3: latent attention with the decoupled, interleaved rotary part, a dense first layer, then experts chosen by
+    sigmoid score + bias inside the best groups, weighted by the renormalised, scaled scores, plus a shared expert."""
+    transformers = pytest.importorskip("transformers")
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+    from rl_b200.models.transformer import PackedBatch, build_model
+
+    rope = dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=64, beta_fast=32, beta_slow=1, mscale=1.0, mscale_all_dim=1.0,
+                rope_theta=10000.0) if yarn else None
+    hf_cfg = transformers.DeepseekV3Config(vocab_size=512, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+                                           num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=3, n_group=4,
+                                           topk_group=2, first_k_dense_replace=1, kv_lora_rank=16, q_lora_rank=q_lora, qk_nope_head_dim=16,
+                                           qk_rope_head_dim=8, v_head_dim=12, routed_scaling_factor=2.5, max_position_embeddings=256,
+                                           rope_parameters=rope, attn_implementation="eager")
+    torch.manual_seed(0)
+    hf = transformers.DeepseekV3ForCausalLM(hf_cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.2)
+            elif p.dim() >= 2:
+                p.normal_(0, 0.08)
+        for n, b in hf.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(torch.randn_like(b) * 0.3)
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict(), torch_dtype="float32")
+    assert cfg.is_mla and cfg.head_dim == 24 and cfg.num_experts == 8 and cfg.scoring_func == "sigmoid" and not cfg.layer_is_moe(0) and cfg.layer_is_moe(1)
+    m = build_model(cfg, dtype=torch.float32, init=False)
+    sd = _hf_state(hf)
+    sd.update({n: b.detach().clone() for n, b in hf.named_buffers() if n.endswith("e_score_correction_bias")})
+    assert not load_hf_tensors(m, _deepseek_get(sd))
+    ids = torch.randint(0, 512, (2, 100 if yarn else 30))
+    S = ids.shape[1]
+    lens = torch.tensor([S, S - 11])
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=(torch.arange(S)[None] < lens[:, None]).long()).logits
+        batch = PackedBatch.from_padded(ids, lens)
+        z = batch.unpack(m.logits(batch), S)
+    for b, n in enumerate(lens.tolist()):
+        assert (z[b, :n] - ref[b, :n]).abs().max().item() < 3e-4, (b, (z[b, :n] - ref[b, :n]).abs().max().item())
+    out = dict(iter_hf_tensors(m))
+    get = _deepseek_get(sd)
+    assert all(torch.equal(t, get(k)) for k, t in out.items())
+    lp, _ = m.next_token_logprobs(batch)
+    lp.sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in m.named_parameters())

@@ -40,8 +40,9 @@ CONFIGS = {
     "llama8b-dp": dict(model="llama3.1-8b", tp=1, ep=1, gen_tp=0, prompts_per_gpu=8, generations=8, prompt_len=256, max_new_tokens=1024,
                        train_mb_tokens=5120, logprob_mb_tokens=20480, act_ckpt="off"),
     # Qwen3-32B: TP4 x DP2 training with sequence parallelism, generation TP2 x 4 engines, fused vocabulary-parallel lm_head
+    # (4096-token training micro-batches: with 8192 the second step ran out of memory next to the 33 GB serving arena)
     "qwen3-32b-tp4dp2": dict(model="qwen3-32b", tp=4, ep=1, gen_tp=2, prompts_per_gpu=2, generations=8, prompt_len=512, max_new_tokens=3584,
-                             train_mb_tokens=8192, logprob_mb_tokens=16384, act_ckpt="on"),
+                             train_mb_tokens=4096, logprob_mb_tokens=8192, act_ckpt="on"),
     # Qwen3-30B-A3B: expert parallel over all GPUs, dense parts data parallel
     "qwen3-30b-a3b-ep8": dict(model="qwen3-30b-a3b", tp=1, ep=0, gen_tp=0, prompts_per_gpu=4, generations=8, prompt_len=512, max_new_tokens=2048,
                               train_mb_tokens=8192, logprob_mb_tokens=16384, act_ckpt="on"),

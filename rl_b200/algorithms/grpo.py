@@ -363,6 +363,16 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
     total_steps = save_state["total_steps"]
     val_task_to_env = val_task_to_env or task_to_env
     last_metrics: dict = {}
+    # rollouts owned by a gym (env.should_use_nemo_gym): rows go to the agent server named by env.nemo_gym.url, which calls the
+    # policy server at env.nemo_gym.policy_base_url (engine/http_server.py)
+    gym_client = None
+    env_cfg = cfg.get("env") or {}
+    if env_cfg.get("should_use_nemo_gym"):
+        from rl_b200.experience.gym_rollouts import GymClient
+
+        gcfg = env_cfg.get("nemo_gym") or {}
+        gym_client = task_to_env.get("nemo_gym_client") if isinstance(task_to_env, dict) and "nemo_gym_client" in task_to_env else GymClient(
+            gcfg["url"], gcfg["policy_base_url"], float(gcfg.get("timeout_s", 1800.0)), int(gcfg.get("max_retries", 2)))
     # on-policy distillation (grpo.adv_estimator.name: opd): frozen teachers, one per distinct checkpoint
     opd_groups = teacher_groups
     opd_metrics: dict = {}
@@ -395,9 +405,20 @@ def grpo_train(policy, generation, dataloader, val_dataloader, tokenizer, loss_f
                 with timer.time("prepare_for_generation/total"):
                     refit_policy_generation(policy, generation, timer)
                 with timer.time("generation"):
-                    repeated, rollout_metrics = run_multi_turn_rollout(
-                        generation, repeated, tokenizer, task_to_env, pcfg["max_total_sequence_length"], g["max_rollout_turns"],
-                        greedy=False, pad_token_id=pad)
+                    if gym_client is not None:
+                        # the gym owns the episodes (turns, tools, verification) and calls the policy's HTTP endpoint
+                        from rl_b200.experience.gym_rollouts import run_gym_rollout_sync
+
+                        repeated, rollout_metrics = run_gym_rollout_sync(
+                            repeated, gym_client, tokenizer, n_gen, max_seq_len=pcfg["max_total_sequence_length"],
+                            reward_penalty_config=cfg.get("reward_penalties"), sampling=dict(temperature=(pcfg.get("generation") or {}).get("temperature", 1.0)))
+                        rollout_metrics = {k: v for k, v in rollout_metrics.items() if isinstance(v, (int, float))}
+                        repeated["generation_lengths"] = torch.tensor([sum(int(m["token_ids"].numel()) for m in log if m["role"] == "assistant")
+                                                                       for log in repeated["message_log"]])
+                    else:
+                        repeated, rollout_metrics = run_multi_turn_rollout(
+                            generation, repeated, tokenizer, task_to_env, pcfg["max_total_sequence_length"], g["max_rollout_turns"],
+                            greedy=False, pad_token_id=pad)
                     generation.finish_generation()
                 # ---- rewards
                 with timer.time("reward_calculation"):

@@ -117,7 +117,8 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
 
 def _local(model: CausalLM) -> dict[str, torch.Tensor]:
     out = dict(model.named_parameters())
-    out.update({n: b for n, b in model.named_buffers() if n.endswith("e_score_correction_bias")})   # stored in checkpoints, not trained
+    if hasattr(model, "named_buffers"):   # (views that stand in for a model, e.g. its gradients, have parameters only)
+        out.update({n: b for n, b in model.named_buffers() if n.endswith("e_score_correction_bias")})   # stored in checkpoints, not trained
     return out
 
 

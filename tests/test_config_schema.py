@@ -72,9 +72,12 @@ def test_every_shipped_recipe_validates():
         validate_master_config(cfg, infer_algorithm(cfg), quiet=True)
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/examples/configs"), reason="reference checkout not present")
+_REF_CONFIGS = os.environ.get("RLB_REFERENCE_CONFIGS", "")   # a directory of recipes written for the reference implementation
+
+
+@pytest.mark.skipif(not os.path.isdir(_REF_CONFIGS), reason="set RLB_REFERENCE_CONFIGS to a directory of reference recipes")
 def test_reference_recipes_validate_without_errors():
-    paths = sorted(glob.glob("/root/reference/examples/configs/*.yaml"))
+    paths = sorted(glob.glob(os.path.join(_REF_CONFIGS, "*.yaml")))
     for p in paths:
         cfg = load_config(p, [])
         validate_master_config(cfg, infer_algorithm(cfg), quiet=True)

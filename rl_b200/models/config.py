@@ -168,7 +168,7 @@ class ModelConfig:
             bos_token_id=hf.get("bos_token_id"),
             eos_token_id=hf.get("eos_token_id"),
             pad_token_id=hf.get("pad_token_id"),
-            torch_dtype=str(hf.get("torch_dtype", hf.get("dtype", "bfloat16"))),
+            torch_dtype=str(hf.get("torch_dtype") or hf.get("dtype") or "bfloat16").replace("torch.", ""),
             vision=hf.get("vision"),
             image_token_id=hf.get("image_token_id"),
         )

@@ -119,3 +119,31 @@ def test_deepseek_v3_matches_huggingface(q_lora, yarn):
     lp, _ = m.next_token_logprobs(batch)
     lp.sum().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in m.named_parameters())
+
+
+@pytest.mark.parametrize("family", ["gemma3", "deepseek_v3"])
+def test_saved_checkpoints_load_in_huggingface(tmp_path, family):
+    """The way out: a checkpoint written by ``save_pretrained`` is read by ``AutoModelForCausalLM.from_pretrained`` (config and
+    tensor names included) and produces the same logits."""
+    transformers = pytest.importorskip("transformers")
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import save_pretrained
+    from rl_b200.models.transformer import PackedBatch, build_model
+
+    if family == "gemma3":
+        hc = transformers.Gemma3TextConfig(vocab_size=512, hidden_size=64, intermediate_size=160, num_hidden_layers=6, num_attention_heads=4,
+                                           num_key_value_heads=2, head_dim=32, sliding_window=8, query_pre_attn_scalar=24, max_position_embeddings=256)
+    else:
+        hc = transformers.DeepseekV3Config(vocab_size=512, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+                                           num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,
+                                           num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, kv_lora_rank=16, q_lora_rank=24,
+                                           qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, max_position_embeddings=256)
+    cfg = ModelConfig.from_hf_dict(hc.to_dict(), torch_dtype="float32")
+    m = build_model(cfg, dtype=torch.float32, seed=3)
+    save_pretrained(m, str(tmp_path))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32, attn_implementation="eager").eval()
+    ids = torch.randint(0, 512, (1, 24))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits[0]
+        z = m.logits(PackedBatch.from_padded(ids, torch.tensor([24])))
+    assert (z - ref).abs().max().item() < 1e-5

@@ -160,7 +160,8 @@ class ModelConfig:
             tie_word_embeddings=bool(hf.get("tie_word_embeddings", False)),
             attention_bias=bool(hf.get("attention_bias", mt == "qwen2")),
             qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"),
-            num_experts=(hf.get("num_experts", 0) if mt.endswith("_moe") else (hf.get("n_routed_experts") or 0) if mt == "deepseek_v3" else 0),
+            num_experts=((hf.get("num_experts") or hf.get("num_local_experts") or 0) if mt.endswith("_moe")     # (newer HF configs: num_local_experts)
+                         else (hf.get("n_routed_experts") or 0) if mt == "deepseek_v3" else 0),
             num_experts_per_tok=hf.get("num_experts_per_tok", 0),
             moe_intermediate_size=hf.get("moe_intermediate_size", 0),
             norm_topk_prob=bool(hf.get("norm_topk_prob", True)),

@@ -147,3 +147,54 @@ def test_saved_checkpoints_load_in_huggingface(tmp_path, family):
         ref = hf(input_ids=ids).logits[0]
         z = m.logits(PackedBatch.from_padded(ids, torch.tensor([24])))
     assert (z - ref).abs().max().item() < 1e-5
+
+
+def _family_config(transformers, family):
+    common = dict(vocab_size=512, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                  max_position_embeddings=512, attn_implementation="eager")
+    if family == "llama":
+        return transformers.LlamaConfig(**common, rope_parameters=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                                                      original_max_position_embeddings=64, rope_theta=500000.0))
+    if family == "mistral":
+        return transformers.MistralConfig(**common, sliding_window=None)
+    if family == "qwen2":
+        return transformers.Qwen2Config(**common, tie_word_embeddings=True)
+    if family == "qwen3":
+        return transformers.Qwen3Config(**common, head_dim=32)
+    if family == "qwen3_moe":
+        return transformers.Qwen3MoeConfig(**common, head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=48, norm_topk_prob=True,
+                                           decoder_sparse_step=1, mlp_only_layers=[])
+    raise KeyError(family)
+
+
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "qwen3_moe"])
+def test_dense_and_moe_families_match_huggingface(tmp_path, family):
+    """Same check for the families the benchmarks use: our checkpoint, HuggingFace's model class, equal logits on a sequence
+    long enough to reach the scaled part of the RoPE spectrum."""
+    transformers = pytest.importorskip("transformers")
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import save_pretrained
+    from rl_b200.models.transformer import PackedBatch, build_model
+
+    hc = _family_config(transformers, family)
+    d = hc.to_dict()
+    if "rope_parameters" in d and isinstance(d["rope_parameters"], dict):     # newer configs nest what older ones spell rope_theta / rope_scaling
+        rp = dict(d["rope_parameters"])
+        d.setdefault("rope_theta", rp.pop("rope_theta", 10000.0))
+        d["rope_theta"] = rp.pop("rope_theta", d["rope_theta"]) if "rope_theta" in rp else d["rope_theta"]
+        d["rope_scaling"] = rp if rp.get("rope_type", "default") != "default" else None
+    cfg = ModelConfig.from_hf_dict(d, torch_dtype="float32")
+    m = build_model(cfg, dtype=torch.float32, seed=5)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+            elif n.endswith("bias"):
+                p.normal_(0, 0.1)
+    save_pretrained(m, str(tmp_path))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32, attn_implementation="eager").eval()
+    ids = torch.randint(0, 512, (1, 200))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits[0]
+        z = m.logits(PackedBatch.from_padded(ids, torch.tensor([200])))
+    assert (z - ref).abs().max().item() < 2e-4, (family, (z - ref).abs().max().item())

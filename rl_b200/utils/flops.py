@@ -208,8 +208,30 @@ def bert_flops(hf, seq: int) -> float:
     return L * layer + head_flops(seq, d, _g(hf, "vocab_size"))
 
 
+def gemma3_flops(hf, seq: int) -> float:
+    """Gemma 3: gated MLP everywhere; sliding-window layers attend to at most ``sliding_window`` keys per query, the
+    global layers (every ``sliding_window_pattern``-th, or as listed in ``layer_types``) to the whole causal prefix."""
+    d, L = _g(hf, "hidden_size"), _g(hf, "num_hidden_layers")
+    nh = _g(hf, "num_attention_heads")
+    nkv = _g(hf, "num_key_value_heads") or nh
+    hd = _g(hf, "head_dim") or d // nh
+    win = _g(hf, "sliding_window") or 0
+    types = _g(hf, "layer_types")
+    pattern = _g(hf, "sliding_window_pattern") or 6
+    total = 0.0
+    for i in range(L):
+        sliding = (types[i] == "sliding_attention") if types else bool(win) and (i + 1) % pattern != 0
+        a = attention_flops(seq, d, nh, nkv, hd)
+        if sliding and win and seq > win:   # the core products see a band of width `win` instead of the causal triangle
+            q = nh * hd
+            a += 2 * 2 * seq * q * (win - (win * win) / (2.0 * seq)) - 2 * 2 * seq * seq * q * 0.5
+        total += a + mlp_flops(seq, d, _g(hf, "intermediate_size"), True)
+    return total + head_flops(seq, d, _g(hf, "vocab_size"))
+
+
 FAMILY_FLOPS = {
-    "llama": llama_flops, "mistral": mistral_flops, "qwen2": qwen2_flops, "qwen3": qwen3_flops, "gemma3": llama_flops,
+    "llama": llama_flops, "mistral": mistral_flops, "qwen2": qwen2_flops, "qwen3": qwen3_flops, "gemma3": gemma3_flops,
+    "gemma3_text": gemma3_flops,
     "gpt2": gpt_flops, "gpt3": gpt_flops, "nemotron": nemotron_flops, "mixtral": mixtral_flops, "qwen3_moe": qwen3_moe_flops,
     "qwen2_moe": moe_decoder_flops, "deepseek_v3": deepseek_v3_flops, "deepseek_v2": deepseek_v3_flops, "nemotron_h": nemotron_h_flops,
     "bert": bert_flops,

@@ -47,6 +47,7 @@ def main():
     ap.add_argument("--serve-tp", default="1,2")
     ap.add_argument("--twin", action="store_true", help="also time the collective twin (all-gather + slice)")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--fp8", action="store_true", help="time the quantising refit (block-128 FP8 written on the way) as well")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -68,6 +69,8 @@ def main():
                    nvlink_bytes_sent=sent, nvlink_bytes_received=recv, write_gbs=local_bytes / ms / 1e6)
         if a.twin:
             row["twin_ms"] = _time(ws.twin_sync, iters=2, warmup=1)
+        if a.fp8:
+            row["fp8_sync_ms"] = _time(ws.sync_weights_fp8, iters=3, warmup=1)
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)

@@ -88,38 +88,29 @@ struct RefitQWork {
   int pad;
 };
 
-// 256 threads per CTA; the 128 x 128 bf16 block is staged in shared memory (32 KB) between the amax pass and the
-// conversion pass instead of in registers: about 40 registers per thread, so several CTAs are resident per SM and their
-// loads overlap (the register-staged form ran at 25 % occupancy and 41 % of the DRAM rate). Thread t owns row (t / 2) and
-// 64 columns of the block in both passes, so it re-reads only what it wrote itself and the block needs one barrier (the
-// amax reduction). Pieces are whole blocks (checked by the host).
-__global__ void __launch_bounds__(256, 4) refit_quant_kernel(const RefitQDesc* __restrict__ descs,
-                                                             const RefitQWork* __restrict__ work, int num_work) {
+// 256 threads; thread t owns row (t / 2) and 64 columns of the block. Pieces are whole blocks (checked by the host).
+__global__ void __launch_bounds__(256) refit_quant_kernel(const RefitQDesc* __restrict__ descs,
+                                                          const RefitQWork* __restrict__ work, int num_work) {
   __shared__ float red[32];
-  __shared__ uint4 tile[128 * 16];   // [row][16 vectors of 8 bf16]
   using namespace rlb;
   const int lr = threadIdx.x >> 1, lc = (threadIdx.x & 1) * 64;
-  uint4* mine = tile + lr * 16 + (threadIdx.x & 1) * 8;
-  // slot q of this thread sits at q ^ sw: the eight threads of a shared-memory phase (four rows x two halves) then hit eight
-  // different 16-byte bank groups instead of one
-  const int sw = (lr & 7) ^ ((threadIdx.x & 1) * 4);
   for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
     const RefitQWork wk = work[w];
     const RefitQDesc d = descs[wk.desc];
     for (int b = wk.first_block; b < wk.first_block + wk.num_blocks; ++b) {
       const int br = b / d.block_cols, bc = b - br * d.block_cols;
       const long long r = br * 128LL + lr, c0 = bc * 128LL + lc;
-      const uint4* sp = reinterpret_cast<const uint4*>(d.src + r * d.src_pitch + c0);
+      const __nv_bfloat16* sp = d.src + r * d.src_pitch + c0;
+      float v[64];
       float amax = 0.f;
-      uint4 x[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) x[q] = sp[q];      // eight independent 16-byte loads in flight
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        mine[q ^ sw] = x[q];
-        const float2 a0 = unpack_bf16x2(x[q].x), a1 = unpack_bf16x2(x[q].y), a2 = unpack_bf16x2(x[q].z), a3 = unpack_bf16x2(x[q].w);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a0.x), fabsf(a0.y)), fmaxf(fabsf(a1.x), fabsf(a1.y))));
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a2.x), fabsf(a2.y)), fmaxf(fabsf(a3.x), fabsf(a3.y))));
+        const uint4 x = *reinterpret_cast<const uint4*>(sp + q * 8);
+        const float2 a0 = unpack_bf16x2(x.x), a1 = unpack_bf16x2(x.y), a2 = unpack_bf16x2(x.z), a3 = unpack_bf16x2(x.w);
+        v[q * 8 + 0] = a0.x; v[q * 8 + 1] = a0.y; v[q * 8 + 2] = a1.x; v[q * 8 + 3] = a1.y;
+        v[q * 8 + 4] = a2.x; v[q * 8 + 5] = a2.y; v[q * 8 + 6] = a3.x; v[q * 8 + 7] = a3.y;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[q * 8 + k]));
       }
       amax = block_max(amax, red);
       const float scale = (amax == 0.f || isinf(amax)) ? 1.f : 448.f / amax;
@@ -131,13 +122,9 @@ __global__ void __launch_bounds__(256, 4) refit_quant_kernel(const RefitQDesc* _
       for (int q = 0; q < 4; ++q) {
         unsigned char bytes[16];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint4 v = mine[(q * 2 + h) ^ sw];
-          const float2 a0 = unpack_bf16x2(v.x), a1 = unpack_bf16x2(v.y), a2 = unpack_bf16x2(v.z), a3 = unpack_bf16x2(v.w);
-          const float f[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            bytes[h * 8 + k] = __nv_cvt_float_to_fp8(fminf(fmaxf(f[k] * scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+        for (int k = 0; k < 16; ++k) {
+          const float y = fminf(fmaxf(v[q * 16 + k] * scale, -448.f), 448.f);
+          bytes[k] = __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
         }
         *reinterpret_cast<uint4*>(qp + q * 16) = *reinterpret_cast<const uint4*>(bytes);
         if (wp) {
@@ -151,7 +138,6 @@ __global__ void __launch_bounds__(256, 4) refit_quant_kernel(const RefitQDesc* _
           reinterpret_cast<uint4*>(wp + q * 16)[1] = reinterpret_cast<const uint4*>(o)[1];
         }
       }
-      __syncthreads();   // `red` and the tile are reused by the next block
     }
   }
 }
@@ -167,7 +153,7 @@ RLB_API int rlb_refit_quant(const void* descs, const void* work, int num_work, i
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int grid = sms * 6;
+  int grid = sms * 4;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > num_work) grid = num_work;
   refit_quant_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const RefitQDesc*>(descs),

@@ -122,3 +122,50 @@ def test_object_store_manifest(tmp_path):
         store.get(stats["manifest"])
     with pytest.raises(ValueError):
         store.put("../escape", b"x")
+
+
+def test_weight_synchronizer_factory_and_sparse_sender(tmp_path):
+    """The factory names every way of moving weights; the sparse sender streams successive refits as deltas against what the
+    receiver holds (the second refit sends only what the optimizer step changed)."""
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import iter_hf_tensors
+    from rl_b200.models.transformer import build_model
+    from rl_b200.refit.factory import ColocatedHandoff, SparseDeltaSynchronizer, create_weight_synchronizer
+
+    mc = ModelConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=8, torch_dtype="bfloat16")
+    train = build_model(mc, dtype=torch.bfloat16, seed=1)
+    h = create_weight_synchronizer("colocated", train)
+    assert isinstance(h, ColocatedHandoff) and h.serving_model is train and h.sync_weights() is None
+    with pytest.raises(ValueError):
+        create_weight_synchronizer("carrier_pigeon", train)
+    receiver = {n: t.detach().clone() for n, t in iter_hf_tensors(train)}
+    store = ST.FileObjectStore(str(tmp_path / "bucket"))
+    sync = create_weight_synchronizer("sparse_object_store", train, store_dir=str(tmp_path / "bucket"), bucket_bytes=4096)
+    assert isinstance(sync, SparseDeltaSynchronizer)
+    s0 = sync.sync_weights()                       # nothing changed since the baseline: all-zero deltas
+    assert s0["unchanged_tensors"] == s0["tensors"] and ST.apply_manifest(receiver, store, s0["manifest"]) == s0["payloads"]
+    with torch.no_grad():
+        for n, p in train.named_parameters():
+            if n.endswith("down_proj"):
+                p.add_(0.01)
+    s1 = sync.sync_weights()
+    assert 0 < s1["tensors"] - s1["unchanged_tensors"] <= 2 and s1["manifest"] != s0["manifest"]
+    ST.apply_manifest(receiver, store, s1["manifest"])
+    for n, t in iter_hf_tensors(train):
+        assert torch.equal(receiver[n], t.detach()), n
+
+
+def test_value_model_facade():
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.policy.value import ValueModel
+
+    mc = ModelConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=8, torch_dtype="float32")
+    vm = ValueModel(dict(precision="float32", train_global_batch_size=2, train_micro_batch_size=2, max_total_sequence_length=32,
+                         optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3))), model_cfg=mc)
+    data = BatchedDataDict(input_ids=torch.randint(0, 64, (2, 9)), input_lengths=torch.tensor([9, 5]))
+    out = vm.get_values(data)
+    assert out["values"].shape == (2, 9) and out["scores"].shape == (2,)
+    assert not hasattr(vm, "generate") and not hasattr(vm, "get_logprobs")

@@ -130,3 +130,37 @@ def test_reward_shaping_and_scaling():
     assert apply_reward_shaping(b2, dict(enabled=True, stop_properly_penalty_coef=0.0))["total_reward"].tolist() == [0.0, 2.0]
     b3 = BatchedDataDict(total_reward=torch.tensor([-1.0, 0.5, 3.0]))
     assert scale_rewards(b3, dict(enabled=True, source_min=0, source_max=1, target_min=-1, target_max=1))["total_reward"].tolist() == pytest.approx([-1.0, 0.0, 1.0])
+
+
+def test_per_sequence_wrapper_equals_the_batched_loss_and_draft_wrapper_adds_up():
+    from rl_b200.algorithms.loss.loss_functions import ClippedPGLossFn, DraftCrossEntropyLossFn
+    from rl_b200.algorithms.loss.wrapper import DraftLossWrapper, PerSequenceLossWrapper, merge_metrics
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+    torch.manual_seed(0)
+    B, S, V = 3, 10, 7
+    lens = torch.tensor([10, 6, 8])
+    tm = (torch.arange(S)[None] < lens[:, None]).float()
+    tm[:, :2] = 0
+    data = BatchedDataDict(input_ids=torch.randint(0, V, (B, S)), input_lengths=lens, token_mask=tm, sample_mask=torch.tensor([1.0, 1.0, 0.5]),
+                           advantages=torch.randn(B, S), prev_logprobs=-torch.rand(B, S), generation_logprobs=-torch.rand(B, S),
+                           reference_policy_logprobs=-torch.rand(B, S))
+    lp = (-torch.rand(B, S - 1)).requires_grad_()
+    fn = ClippedPGLossFn(dict(reference_policy_kl_penalty=0.05))
+    toks = (tm[:, 1:] * data["sample_mask"][:, None]).sum()
+    seqs = data["sample_mask"].sum()
+    kw = dict(data=data, global_valid_seqs=seqs, global_valid_toks=toks)
+    full, m_full = fn(next_token_logprobs=lp, **kw)
+    per, m_per = PerSequenceLossWrapper(fn)(next_token_logprobs=lp, **kw)
+    assert torch.allclose(full, per, atol=1e-6) and m_per["num_valid_samples"] == pytest.approx(m_full["num_valid_samples"])
+    g1 = torch.autograd.grad(full, lp, retain_graph=True)[0]
+    g2 = torch.autograd.grad(per, lp)[0]
+    assert torch.allclose(g1, g2, atol=1e-6)
+    assert merge_metrics({"probs_ratio_min": 0.5, "x": 1}, {"probs_ratio_min": 0.2, "probs_ratio_max": float("inf"), "x": 2}) == {"probs_ratio_min": 0.2, "x": 3}
+    draft = torch.randn(B, S - 1, V, requires_grad=True)
+    target = torch.randn(B, S - 1, V)
+    w = DraftLossWrapper(fn, draft_weight=0.5)
+    both, m = w(draft_logits=draft, target_logits=target, next_token_logprobs=lp.detach().requires_grad_(), **kw)
+    d_only, dm = DraftCrossEntropyLossFn()(draft, target, data, seqs, toks)
+    assert torch.allclose(both, full.detach() + 0.5 * d_only, atol=1e-6) and m["draft_accuracy"] == dm["draft_accuracy"] and m["policy_loss"] == m_full["loss"]
+    assert w(next_token_logprobs=lp, **kw)[0].item() == pytest.approx(full.item())      # no draft head: the policy loss alone

@@ -11,12 +11,28 @@ from rl_b200.distributed.launch import init_distributed
 from rl_b200.utils.config import load_config, parse_args_and_overrides
 
 
+def apply_env_vars(cfg: dict) -> dict:
+    """Recipe ``env_vars`` override the shell; the policy's own blocks (``policy.env_vars``, ``policy.dtensor_cfg.env_vars``,
+    ``policy.megatron_cfg.env_vars``, ``policy.generation.*_cfg.env_vars``) override the recipe's top level, in that order
+    (the reference's precedence: docs/design-docs/env-vars.md:5-31). Returns what was set."""
+    pol = cfg.get("policy") or {}
+    gen = pol.get("generation") or {}
+    layers = [cfg.get("env_vars"), pol.get("env_vars"), (pol.get("dtensor_cfg") or {}).get("env_vars"),
+              (pol.get("megatron_cfg") or {}).get("env_vars"), (gen.get("native_cfg") or {}).get("env_vars"),
+              (gen.get("vllm_cfg") or {}).get("env_vars")]
+    applied = {}
+    for layer in layers:
+        for k, v in (layer or {}).items():
+            os.environ[str(k)] = str(v)
+            applied[str(k)] = str(v)
+    return applied
+
+
 def bootstrap(default_config: str, argv: Optional[list[str]] = None, backend: Optional[str] = None):
     """Returns (cfg, rank, world, device, tokenizer)."""
     path, overrides = parse_args_and_overrides(argv)
     cfg = load_config(path or default_config, overrides)
-    for k, v in (cfg.get("env_vars") or {}).items():  # YAML env_vars override the shell (docs/design-docs/env-vars.md:5-31)
-        os.environ[str(k)] = str(v)
+    apply_env_vars(cfg)
     validate_recipe(cfg, quiet=int(os.environ.get("RANK", "0")) != 0)
     from rl_b200.distributed import roles
 

@@ -50,3 +50,20 @@ def test_circular_defaults(tmp_path):
     _write(tmp_path / "b.yaml", {"defaults": "a.yaml"})
     with pytest.raises(ConfigError):
         load_config(tmp_path / "a.yaml")
+
+
+def test_env_vars_precedence(monkeypatch):
+    import os
+
+    from rl_b200.utils.cli import apply_env_vars
+
+    monkeypatch.setenv("RLB_TEST_A", "shell")
+    monkeypatch.setenv("RLB_TEST_B", "shell")
+    monkeypatch.setenv("RLB_TEST_C", "shell")
+    cfg = dict(env_vars=dict(RLB_TEST_A="recipe", RLB_TEST_B="recipe"),
+               policy=dict(dtensor_cfg=dict(env_vars=dict(RLB_TEST_B="worker")), generation=dict(vllm_cfg=dict(env_vars=dict(RLB_TEST_D=1)))))
+    applied = apply_env_vars(cfg)
+    assert os.environ["RLB_TEST_A"] == "recipe" and os.environ["RLB_TEST_B"] == "worker" and os.environ["RLB_TEST_C"] == "shell"
+    assert os.environ["RLB_TEST_D"] == "1" and applied["RLB_TEST_B"] == "worker"
+    for k in ("RLB_TEST_D",):
+        monkeypatch.delenv(k, raising=False)

@@ -158,3 +158,32 @@ def test_model_diagnostics(tmp_path, capsys):
     assert md.main(["embeddings", "--path", str(tmp_path)]) == 1
     out = capsys.readouterr().out
     assert '"zero_rows": [5]' in out and '"check": "max-len"' in out
+
+
+def test_perf_numbers_from_a_metrics_log(tmp_path):
+    import json
+
+    from rl_b200.tools import perf_numbers as P
+
+    with open(tmp_path / "metrics.jsonl", "w") as f:
+        for step in range(1, 11):
+            f.write(json.dumps({"step": step, "timing/train/total_step_time": 10.0 + step, "train/loss": 0.1}) + "\n")
+            f.write(json.dumps({"step": step, "performance/tokens_per_sec_per_gpu": 1000.0 * step, "note": "text"}) + "\n")
+    m = P.read_metrics(str(tmp_path))
+    assert sorted(m) == list(range(1, 11)) and m[3]["performance/tokens_per_sec_per_gpu"] == 3000.0 and "note" not in m[3]
+    assert list(P.window(6, 5)) == [4, 5, 6, 7, 8] and list(P.window(6, 4)) == [4, 5, 6, 7]
+    s = P.summarize(m, at_step=6, average_steps=5)
+    assert s["steps"] == [4, 5, 6, 7, 8] and s["averages"]["timing/train/total_step_time"] == 16.0
+    assert s["averages"]["performance/tokens_per_sec_per_gpu"] == 6000.0 and "timing/train/generation" not in s["averages"]
+    with pytest.raises(ValueError):
+        P.summarize(m, at_step=50)
+    assert P.main([str(tmp_path), "--at-step", "3", "--average-steps", "2", "--json"]) == 0
+
+
+def test_model_diagnostics_sub_commands_on_cpu():
+    from rl_b200.tools import model_diagnostics as D
+
+    assert D.precision("tiny-llama-oracle", "cpu", new_tokens=16)["ok"]
+    r = D.prefix_caching("tiny-llama-oracle", "cpu")
+    assert r["ok"] and r["cached_prefix_tokens"] > 0
+    assert D.routed_experts("cpu")["ok"]

@@ -72,11 +72,47 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
 
+    # Nemotron-H (hybrid Mamba-2 / attention / MLP / MoE; nemo_rl/models/dtensor/parallelize.py:465 is the reference's plan
+    # for this family): every layer is ONE mixer behind one RMSNorm, named by ``layers_block_type``
+    layers_block_type: Optional[list] = None   # per layer: "mamba" | "attention" | "mlp" | "moe"
+    use_rope: bool = True              # False: attention has no positional rotation (the state-space layers carry order)
+    mlp_gated: bool = True             # False: down(act(up(x))) instead of down(act(gate(x)) * up(x))
+    mlp_bias: bool = False
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    ssm_state_size: int = 0
+    mamba_n_groups: int = 1
+    mamba_d_conv: int = 4
+    mamba_chunk_size: int = 128
+    mamba_conv_bias: bool = True
+    mamba_proj_bias: bool = False
+    mamba_dt_limit: Optional[list] = None      # [lo, hi] clamp of the step size after softplus
+    moe_latent_size: Optional[int] = None      # routed experts work in a narrower space between two shared projections
+    moe_shared_expert_intermediate_size: int = 0
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.layers_block_type is not None
+
+    def block_type(self, i: int) -> str:
+        """"mamba" | "attention" | "mlp" | "moe" for hybrid models, "decoder" (attention + MLP in one layer) otherwise."""
+        return self.layers_block_type[i] if self.layers_block_type is not None else "decoder"
+
+    @property
+    def mamba_inner(self) -> int:
+        return self.mamba_num_heads * self.mamba_head_dim
+
+    @property
+    def mamba_conv_dim(self) -> int:
+        return self.mamba_inner + 2 * self.mamba_n_groups * self.ssm_state_size
+
     @property
     def is_mla(self) -> bool:
         return self.kv_lora_rank > 0
 
     def layer_is_moe(self, i: int) -> bool:
+        if self.layers_block_type is not None:
+            return self.layers_block_type[i] == "moe"
         return self.is_moe and i >= self.first_k_dense_replace
 
     def layer_is_sliding(self, i: int) -> bool:
@@ -112,8 +148,22 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         arch = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
                 "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
-                "gemma3_text": "Gemma3ForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
+                "gemma3_text": "Gemma3ForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
+                "nemotron_h": "NemotronHForCausalLM"}.get(self.model_type, "LlamaForCausalLM")
         d = asdict(self)
+        nh = {k: d.pop(k) for k in ("layers_block_type", "use_rope", "mlp_gated", "mlp_bias", "mamba_num_heads", "mamba_head_dim", "ssm_state_size",
+                                    "mamba_n_groups", "mamba_d_conv", "mamba_chunk_size", "mamba_conv_bias", "mamba_proj_bias", "mamba_dt_limit",
+                                    "moe_latent_size", "moe_shared_expert_intermediate_size")}
+        if self.model_type == "nemotron_h":
+            pat = "".join({"mamba": "M", "attention": "*", "mlp": "-", "moe": "E"}[t] for t in nh["layers_block_type"])
+            d.update(hybrid_override_pattern=pat, layers_block_type=nh["layers_block_type"], mamba_num_heads=nh["mamba_num_heads"],
+                     mamba_head_dim=nh["mamba_head_dim"], ssm_state_size=nh["ssm_state_size"], n_groups=nh["mamba_n_groups"],
+                     conv_kernel=nh["mamba_d_conv"], chunk_size=nh["mamba_chunk_size"], use_conv_bias=nh["mamba_conv_bias"],
+                     use_bias=nh["mamba_proj_bias"], mlp_bias=nh["mlp_bias"], mlp_hidden_act=d["hidden_act"], layer_norm_epsilon=d["rms_norm_eps"],
+                     time_step_limit=nh["mamba_dt_limit"] or [0.0, float("inf")], moe_latent_size=nh["moe_latent_size"],
+                     moe_shared_expert_intermediate_size=nh["moe_shared_expert_intermediate_size"], n_routed_experts=self.num_experts,
+                     n_shared_experts=self.n_shared_experts, n_group=self.n_group, topk_group=self.topk_group,
+                     routed_scaling_factor=self.routed_scaling_factor)
         d.pop("value_head")
         d.pop("qk_norm")
         gem = {k: d.pop(k) for k in ("hidden_act", "sandwich_norm", "embed_scale", "norm_offset", "sliding_window", "layer_types",
@@ -128,6 +178,8 @@ class ModelConfig:
             d.pop("image_token_id")
         ds = {k: d.pop(k) for k in ("kv_lora_rank", "q_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim", "rope_interleave",
                                     "n_shared_experts", "first_k_dense_replace", "scoring_func", "n_group", "topk_group", "routed_scaling_factor")}
+        if self.model_type == "nemotron_h":
+            d.update({k: ds[k] for k in ("n_shared_experts", "n_group", "topk_group", "routed_scaling_factor")})
         if self.model_type == "deepseek_v3":
             d.update(ds, n_routed_experts=self.num_experts)
             d.pop("num_experts")
@@ -144,6 +196,14 @@ class ModelConfig:
             hf = dict(hf["text_config"], model_type="gemma3_text")
             mt = "gemma3_text"
         n_heads = hf["num_attention_heads"]
+        if mt == "nemotron_h":
+            hf = dict(hf)
+            types = hf.get("layers_block_type")
+            if types is None:    # older configs: one character per layer (M mamba, * attention, - MLP, E mixture of experts)
+                types = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[ch] for ch in hf["hybrid_override_pattern"]]
+            hf["layers_block_type"] = list(types)
+            hf["num_hidden_layers"] = len(types)
+            hf.setdefault("rms_norm_eps", hf.get("layer_norm_epsilon", 1e-5))
         cfg = cls(
             model_type=mt,
             vocab_size=hf["vocab_size"],
@@ -161,7 +221,8 @@ class ModelConfig:
             attention_bias=bool(hf.get("attention_bias", mt == "qwen2")),
             qk_norm=mt in ("qwen3", "qwen3_moe", "gemma3_text"),
             num_experts=((hf.get("num_experts") or hf.get("num_local_experts") or 0) if mt.endswith("_moe")     # (newer HF configs: num_local_experts)
-                         else (hf.get("n_routed_experts") or 0) if mt == "deepseek_v3" else 0),
+                         else (hf.get("n_routed_experts") or 0) if mt == "deepseek_v3"
+                         else (hf.get("n_routed_experts") or 0) if (mt == "nemotron_h" and "moe" in hf["layers_block_type"]) else 0),
             num_experts_per_tok=hf.get("num_experts_per_tok", 0),
             moe_intermediate_size=hf.get("moe_intermediate_size", 0),
             norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
@@ -192,6 +253,26 @@ class ModelConfig:
                     cfg.attn_scale = cfg.head_dim ** -0.5 * ms * ms
             elif isinstance(rp, dict) and rp.get("rope_theta"):
                 cfg.rope_theta = float(rp["rope_theta"])
+        if mt == "nemotron_h":
+            cfg.layers_block_type = hf["layers_block_type"]
+            cfg.use_rope, cfg.mlp_gated = False, False
+            cfg.hidden_act = hf.get("mlp_hidden_act", "relu2")
+            cfg.mlp_bias = bool(hf.get("mlp_bias", False))
+            cfg.mamba_num_heads, cfg.mamba_head_dim = hf["mamba_num_heads"], hf["mamba_head_dim"]
+            cfg.ssm_state_size = hf.get("ssm_state_size", 128)
+            cfg.mamba_n_groups = hf.get("mamba_n_groups", hf.get("n_groups", 8))
+            cfg.mamba_d_conv = hf.get("mamba_d_conv", hf.get("conv_kernel", 4))
+            cfg.mamba_chunk_size = hf.get("mamba_chunk_size", hf.get("chunk_size", 128))
+            cfg.mamba_conv_bias = bool(hf.get("mamba_conv_bias", hf.get("use_conv_bias", True)))
+            cfg.mamba_proj_bias = bool(hf.get("mamba_proj_bias", hf.get("use_bias", False)))
+            lim = hf.get("mamba_dt_limit", hf.get("time_step_limit"))
+            cfg.mamba_dt_limit = [float(lim[0]), float(lim[1])] if lim is not None else None
+            if cfg.is_moe:
+                for k in ("n_shared_experts", "n_group", "topk_group", "routed_scaling_factor", "moe_latent_size"):
+                    if hf.get(k) is not None:
+                        setattr(cfg, k, hf[k])
+                cfg.scoring_func = "sigmoid"
+                cfg.moe_shared_expert_intermediate_size = hf.get("moe_shared_expert_intermediate_size", 0) or 0
         if mt == "gemma3_text":
             L = cfg.num_hidden_layers
             pattern = int(hf.get("sliding_window_pattern", 6) or 6)
@@ -229,6 +310,9 @@ class ModelConfig:
 def rope_inv_freq(cfg: ModelConfig, device=None) -> torch.Tensor:
     """Inverse frequencies [head_dim/2] including the ``llama3`` / ``linear`` / ``yarn`` scaling rules."""
     D = cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim     # MLA rotates only the decoupled rotary part of each head
+    if not cfg.use_rope:   # a rotation by angle zero: the attention code paths stay the same
+        z = torch.zeros(D // 2, dtype=torch.float32)
+        return z.to(device) if device is not None else z
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
     rs = cfg.rope_scaling or {}
     kind = rs.get("rope_type", rs.get("type", "default"))

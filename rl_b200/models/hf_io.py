@@ -30,10 +30,11 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
     n_layers = cfg.num_hidden_layers - layer_offset if num_local_layers is None else num_local_layers
     tied = cfg.tie_word_embeddings and not cfg.value_head
     rows = []
+    hybrid = cfg.is_hybrid     # Nemotron-H names: model.embeddings, model.norm_f, layers.N.norm + layers.N.mixer.*
     if first_stage or (last_stage and tied):
-        rows.append(("model.embed_tokens.weight", "embed_tokens", None, None, None))
+        rows.append(("model.embeddings.weight" if hybrid else "model.embed_tokens.weight", "embed_tokens", None, None, None))
     if last_stage:
-        rows.append(("model.norm.weight", "norm", None, None, None))
+        rows.append(("model.norm_f.weight" if hybrid else "model.norm.weight", "norm", None, None, None))
         if cfg.value_head:
             rows.append(("score.weight", "score", (0, 1), None, None))
         elif not tied:
@@ -52,7 +53,46 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
     def sl(dim, n):  # this rank's slice of a dimension of (global) length n * tp_size
         return (dim, tp_rank * n, n) if tp_size > 1 else None
 
-    for j in range(n_layers):
+    for j in range(n_layers if hybrid else 0):
+        hp, lp = f"model.layers.{layer_offset + j}", f"layers.{j}"
+        mx, kind = f"{hp}.mixer", cfg.block_type(layer_offset + j)
+        rows.append((f"{hp}.norm.weight", f"{lp}.norm", None, None, None))
+        if kind == "mamba":
+            rows += [(f"{mx}.in_proj.weight", f"{lp}.mamba.in_proj", None, None, None),
+                     (f"{mx}.conv1d.weight", f"{lp}.mamba.conv_weight", None, None, None),
+                     (f"{mx}.dt_bias", f"{lp}.mamba.dt_bias", None, None, None),
+                     (f"{mx}.A_log", f"{lp}.mamba.A_log", None, None, None),
+                     (f"{mx}.D", f"{lp}.mamba.D", None, None, None),
+                     (f"{mx}.norm.weight", f"{lp}.mamba.norm", None, None, None),
+                     (f"{mx}.out_proj.weight", f"{lp}.mamba.out_proj", None, None, None)]
+            if cfg.mamba_conv_bias:
+                rows.append((f"{mx}.conv1d.bias", f"{lp}.mamba.conv_bias", None, None, None))
+            if cfg.mamba_proj_bias:
+                rows += [(f"{mx}.in_proj.bias", f"{lp}.mamba.in_proj_bias", None, None, None),
+                         (f"{mx}.out_proj.bias", f"{lp}.mamba.out_proj_bias", None, None, None)]
+        elif kind == "attention":   # replicated over a tensor-parallel group
+            qf, kvf = cfg.q_size, cfg.kv_size
+            rows += [(f"{mx}.q_proj.weight", f"{lp}.self_attn.qkv_proj", (0, qf), None, None),
+                     (f"{mx}.k_proj.weight", f"{lp}.self_attn.qkv_proj", (qf, qf + kvf), None, None),
+                     (f"{mx}.v_proj.weight", f"{lp}.self_attn.qkv_proj", (qf + kvf, qf + 2 * kvf), None, None),
+                     (f"{mx}.o_proj.weight", f"{lp}.self_attn.o_proj", None, None, None)]
+        elif kind == "mlp":
+            f = cfg.intermediate_size // tp_size
+            rows += [(f"{mx}.up_proj.weight", f"{lp}.mlp.up_proj", None, None, sl(0, f)),
+                     (f"{mx}.down_proj.weight", f"{lp}.mlp.down_proj", None, None, sl(1, f))]
+        else:
+            rows += [(f"{mx}.gate.weight", f"{lp}.mlp.router", None, None, None),
+                     (f"{mx}.gate.e_score_correction_bias", f"{lp}.mlp.e_score_correction_bias", None, None, None)]
+            if cfg.moe_latent_size:
+                rows += [(f"{mx}.fc1_latent_proj.weight", f"{lp}.mlp.fc1_latent_proj", None, None, None),
+                         (f"{mx}.fc2_latent_proj.weight", f"{lp}.mlp.fc2_latent_proj", None, None, None)]
+            if cfg.n_shared_experts:
+                rows += [(f"{mx}.shared_experts.up_proj.weight", f"{lp}.mlp.shared_experts.up_proj", None, None, None),
+                         (f"{mx}.shared_experts.down_proj.weight", f"{lp}.mlp.shared_experts.down_proj", None, None, None)]
+            for e in range(cfg.num_experts):
+                rows += [(f"{mx}.experts.{e}.up_proj.weight", f"{lp}.mlp.up_proj", None, e, None),
+                         (f"{mx}.experts.{e}.down_proj.weight", f"{lp}.mlp.down_proj", None, e, None)]
+    for j in range(0 if hybrid else n_layers):
         hp, lp = f"model.layers.{layer_offset + j}", f"layers.{j}"
         rows += [
             (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None, None),

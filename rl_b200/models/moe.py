@@ -32,8 +32,18 @@ class MoEMLP(nn.Module):
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.local_experts = E // ep_size
         self.router = nn.Parameter(torch.empty(E, d, dtype=dtype, device=device))
-        self.gate_up_proj = nn.Parameter(torch.empty(self.local_experts, 2 * f, d, dtype=dtype, device=device))
-        self.down_proj = nn.Parameter(torch.empty(self.local_experts, d, f, dtype=dtype, device=device))
+        self.gated = cfg.mlp_gated
+        # Nemotron-H: the routed experts may work in a narrower ("latent") space between two shared projections
+        din = cfg.moe_latent_size or d
+        self.fc1_latent_proj = self.fc2_latent_proj = None
+        if cfg.moe_latent_size:
+            self.fc1_latent_proj = nn.Parameter(torch.empty(din, d, dtype=dtype, device=device))
+            self.fc2_latent_proj = nn.Parameter(torch.empty(d, din, dtype=dtype, device=device))
+        if self.gated:
+            self.gate_up_proj = nn.Parameter(torch.empty(self.local_experts, 2 * f, din, dtype=dtype, device=device))
+        else:   # down(act(up(x))) experts
+            self.up_proj = nn.Parameter(torch.empty(self.local_experts, f, din, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(self.local_experts, din, f, dtype=dtype, device=device))
         if cfg.scoring_func == "sigmoid":
             # selection bias of the auxiliary-loss-free load balancing: shifts which experts are chosen, never the weights;
             # not trained by gradient (a buffer, stored in checkpoints as mlp.gate.e_score_correction_bias)
@@ -42,7 +52,8 @@ class MoEMLP(nn.Module):
         if cfg.n_shared_experts:
             from .transformer import DenseMLP
 
-            self.shared_experts = DenseMLP(cfg, dtype, device, intermediate_size=cfg.moe_intermediate_size * cfg.n_shared_experts)
+            self.shared_experts = DenseMLP(cfg, dtype, device, intermediate_size=cfg.moe_shared_expert_intermediate_size
+                                           or cfg.moe_intermediate_size * cfg.n_shared_experts)
         self.last_routing: Optional[torch.Tensor] = None  # top-k expert ids of the last forward (router replay / traces)
         self.forced_routing: Optional[torch.Tensor] = None  # when set, replaces the router's choice (router replay)
 
@@ -90,6 +101,16 @@ class MoEMLP(nn.Module):
         over all local experts (see :mod:`rl_b200.ops.moe_ops`)."""
         from rl_b200.ops.moe_ops import grouped_expert_mlp
 
+        if not self.gated:
+            # non-gated experts: one pair of products per expert over its slice (the split sizes are read on the host)
+            cl = counts.tolist() if isinstance(counts, torch.Tensor) else list(counts)
+            outs, s0 = [], 0
+            for e, n in enumerate(cl):
+                if n:
+                    h = F.plain_act(torch.nn.functional.linear(xs[s0 : s0 + n], self.up_proj[e]), self.cfg.hidden_act)
+                    outs.append(torch.nn.functional.linear(h, self.down_proj[e]))
+                s0 += n
+            return torch.cat(outs) if outs else xs.new_zeros((0, self.down_proj.shape[1]))
         if not isinstance(counts, torch.Tensor):
             counts = torch.tensor(counts, dtype=torch.int64, device=xs.device)
         return grouped_expert_mlp(xs, counts, self.gate_up_proj, self.down_proj)
@@ -105,7 +126,7 @@ class MoEMLP(nn.Module):
         c = self.cfg
         if torch.is_grad_enabled() or self.forced_routing is not None or not _L.available():
             return None
-        if c.scoring_func != "softmax" or self.shared_experts is not None:
+        if c.scoring_func != "softmax" or self.shared_experts is not None or not self.gated or self.fc1_latent_proj is not None:
             return None   # the routing kernel implements the soft-max router; other routers take the general path
         W = self.ep_size
         lock = int(getattr(self.ep, "lockstep_tokens", 0) or 0)
@@ -143,12 +164,15 @@ class MoEMLP(nn.Module):
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = order // k
+        x_in = x
+        if self.fc1_latent_proj is not None:
+            x = torch.nn.functional.linear(x, self.fc1_latent_proj)
         xs = x[tok]
         counts = torch.zeros(E, dtype=torch.int64, device=x.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
         if self.ep_size > 1:
             from rl_b200.parallel.expert import all_to_all_tokens, fused_dispatch_experts_combine
 
-            if self.ep.comm is not None and xs.is_cuda and xs.dtype == torch.bfloat16 and xs.shape[0] <= self.ep.comm.max_copies:
+            if self.gated and self.ep.comm is not None and xs.is_cuda and xs.dtype == torch.bfloat16 and xs.shape[0] <= self.ep.comm.max_copies:
                 # dispatch, grouped expert MLP and combine over peer memory: no host-side split sizes, no NCCL all-to-all
                 ys = fused_dispatch_experts_combine(xs, counts, self.ep, self.local_experts, self.gate_up_proj, self.down_proj)
             else:
@@ -156,8 +180,13 @@ class MoEMLP(nn.Module):
         else:
             ys = self._experts(xs, counts)
         wy = ys * w.reshape(-1)[order].unsqueeze(-1).to(ys.dtype)
-        out = torch.zeros_like(x) if residual is None else residual.clone()
-        out = out.index_add(0, tok, wy)
+        if self.fc2_latent_proj is not None:   # sum in the latent space, one projection back for all experts
+            lat = torch.zeros_like(x).index_add(0, tok, wy)
+            out = torch.nn.functional.linear(lat, self.fc2_latent_proj)
+            out = out if residual is None else out + residual
+        else:
+            out = torch.zeros_like(x) if residual is None else residual.clone()
+            out = out.index_add(0, tok, wy)
         if self.shared_experts is not None:
-            out = self.shared_experts(x, out)
+            out = self.shared_experts(x_in, out)
         return out

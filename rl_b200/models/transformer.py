@@ -294,16 +294,26 @@ class DenseMLP(nn.Module):
         inter = intermediate_size or cfg.intermediate_size
         assert inter % self.tp.world == 0
         d, f = cfg.hidden_size, inter // self.tp.world
-        self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
+        self.gated = cfg.mlp_gated
+        if cfg.mlp_bias:
+            raise NotImplementedError("MLP biases are not supported")
+        if self.gated:
+            self.gate_up_proj = nn.Parameter(torch.empty(2 * f, d, dtype=dtype, device=device))
+        else:   # down(act(up(x))): Nemotron-H
+            self.up_proj = nn.Parameter(torch.empty(f, d, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(d, f, dtype=dtype, device=device))
         self.act = cfg.hidden_act
         self.gate_up_lora = self.down_lora = None
+        if lora and not self.gated:
+            raise NotImplementedError("LoRA adapters on the non-gated MLP")
         if lora:
             assert self.tp.world == 1, "LoRA adapters are not tensor parallel"
             self.gate_up_lora = LoRA([("gate_proj", f), ("up_proj", f)], d, lora, dtype, device)
             self.down_lora = LoRA([("down_proj", d)], f, lora, dtype, device)
 
     def forward(self, x, residual):
+        if not self.gated:
+            return row_linear(F.plain_act(column_linear(x, self.up_proj, None, self.tp), self.act), self.down_proj, residual, self.tp)
         h = column_linear(x, self.gate_up_proj, None, self.tp)
         if self.gate_up_lora is not None:
             dl = self.gate_up_lora.delta(x)
@@ -365,6 +375,45 @@ class DecoderLayer(nn.Module):
             return h + F.rmsnorm(m, self.post_feedforward_layernorm, eps)
         h = self.self_attn.project_out(a, h)
         return self.mlp(F.rmsnorm(h, self.post_attention_layernorm, eps), h)
+
+
+class HybridBlock(nn.Module):
+    """One layer of a hybrid model (Nemotron-H): RMSNorm, then ONE mixer -- a Mamba-2 state-space mixer, attention
+    (no positional rotation), a plain MLP or a mixture of experts -- added to the residual stream. Only the MLP mixers are
+    tensor parallel (the plan of nemo_rl/models/dtensor/parallelize.py:465); the others are replicated over the group."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, tp: Optional[TP] = None, ep=None, cp=None, lora: Optional[dict] = None,
+                 layer_idx: int = 0):
+        super().__init__()
+        self.cfg, self.layer_idx, self.window = cfg, layer_idx, 0
+        self.kind = cfg.block_type(layer_idx)
+        assert cp is None or cp.world == 1, "context parallelism is not available for hybrid state-space models"
+        assert not lora, "LoRA adapters are not available for hybrid state-space models"
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+        # the mixer sits under the name its kind has in the other families (checkpoints call all of them "mixer")
+        self.mamba = self.self_attn = self.mlp = None
+        if self.kind == "mamba":
+            from .mamba import Mamba2Mixer
+
+            self.mamba = Mamba2Mixer(cfg, dtype, device)
+        elif self.kind == "attention":
+            self.self_attn = Attention(cfg, dtype, device, None, None, None)
+        elif self.kind == "mlp":
+            self.mlp = DenseMLP(cfg, dtype, device, tp)
+        elif self.kind == "moe":
+            from .moe import MoEMLP
+
+            self.mlp = MoEMLP(cfg, dtype, device, ep=ep)
+        else:
+            raise ValueError(f"unknown block type {self.kind!r}")
+
+    def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
+        x = F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+        if self.kind == "mamba":
+            return h + self.mamba(x, cu_seqlens, max_seqlen)
+        if self.kind == "attention":
+            return self.self_attn(x, h, positions, inv_freq, cu_seqlens, max_seqlen, 0)
+        return self.mlp(x, h)
 
 
 @dataclass
@@ -452,7 +501,10 @@ class CausalLM(nn.Module):
             self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, d, dtype=dtype, device=device))
         else:
             self.embed_tokens = None
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg, layer_idx=self.layer_offset + i)
+        block = HybridBlock if cfg.is_hybrid else DecoderLayer
+        if cfg.is_hybrid and self.tp.sequence_parallel:
+            raise NotImplementedError("sequence parallelism is not available for hybrid state-space models")
+        self.layers = nn.ModuleList([block(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg, layer_idx=self.layer_offset + i)
                                      for i in range(n_local)])
         self.lm_head = None
         if self.last_stage:
@@ -482,13 +534,20 @@ class CausalLM(nn.Module):
         self.sharder = None
 
     # ------------------------------------------------------------------ parameters
-    _TP_SHARDED = ("qkv_proj", "qkv_bias", "o_proj", "gate_up_proj", "down_proj", "lm_head")
+    _TP_SHARDED = ("qkv_proj", "qkv_bias", "o_proj", "gate_up_proj", "up_proj", "down_proj", "lm_head")
 
     def is_tp_sharded(self, name: str) -> bool:
         """Whether parameter ``name`` holds a tensor-parallel shard (False: replicated over the tp group)."""
         if self.tp.world == 1:
             return False
         leaf = name.rsplit(".", 1)[-1]
+        if self.cfg.is_hybrid:   # only the plain MLP blocks and the output head are sharded
+            if leaf == "lm_head":
+                return True
+            if leaf not in ("up_proj", "down_proj") or ".mlp." not in name or "shared_experts" in name:
+                return False
+            li = int(name.split(".")[1]) + self.layer_offset
+            return self.cfg.block_type(li) == "mlp"
         return leaf in self._TP_SHARDED and ".mlp.router" not in name and not (self.cfg.is_moe and ".mlp." in name)
 
     @torch.no_grad()
@@ -511,8 +570,15 @@ class CausalLM(nn.Module):
                 g = torch.Generator(device=mod.lora_A.device)
                 g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
                 mod.reset(g)
+        for mname, mod in self.named_modules():
+            if hasattr(mod, "reset_special"):   # state-space mixers: decay rates, step sizes, skip weights
+                g = torch.Generator(device=mod.dt_bias.device)
+                g.manual_seed((seed * 1000003 + zlib.crc32(mname.encode())) & 0x7FFFFFFFFFFFFFFF)
+                mod.reset_special(g)
         for hf, dst, hs in iter_hf_shards(self):
-            if hf.endswith("norm.weight") or hf.endswith("layernorm.weight") or hf.endswith(".bias"):
+            if hf.endswith("norm.weight") or hf.endswith("layernorm.weight") or hf.endswith("norm_f.weight") or hf.endswith(".bias"):
+                continue
+            if hf.endswith(".A_log") or hf.endswith(".D") or hf.endswith(".dt_bias"):
                 continue
             if hf.endswith("e_score_correction_bias"):
                 dst.zero_()
@@ -526,6 +592,8 @@ class CausalLM(nn.Module):
             # rows are generated in order in bounded fp32 chunks; only this rank's slice is kept
             step = max(1, (1 << 26) // max(1, cols))
             d2 = dst.view(dst.shape[0], -1)
+            cols = d2.shape[1] if hs is None else cols      # (3-D tensors such as the depth-wise conv: all trailing dimensions)
+            c1 = cols if hs is None else c1
             for s0 in range(0, r1, step):
                 e0 = min(rows, s0 + step)
                 blk = torch.randn((e0 - s0, cols), generator=g, device=dst.device, dtype=torch.float32) * std
@@ -566,6 +634,17 @@ class CausalLM(nn.Module):
     def is_expert_param(name: str) -> bool:
         """Expert-parallel parameters (stacked expert weights); the router is replicated like any dense parameter."""
         return name.endswith(".mlp.gate_up_proj") or name.endswith(".mlp.down_proj")
+
+    def expert_param_names(self) -> set:
+        """Names of the expert-parallel parameters of THIS model: the stacked weights of its mixture-of-experts blocks
+        (a dense MLP of the same model, e.g. DeepSeek's first layers or a hybrid model's MLP blocks, is not among them)."""
+        from .moe import MoEMLP
+
+        out = set()
+        for mname, mod in self.named_modules():
+            if isinstance(mod, MoEMLP):
+                out.update(f"{mname}.{leaf}" for leaf in ("gate_up_proj", "up_proj", "down_proj") if getattr(mod, leaf, None) is not None)
+        return out
 
     @property
     def output_weight(self) -> torch.Tensor:

@@ -457,6 +457,19 @@ def gated_act(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
     raise ValueError(f"unknown gate activation '{act}'")
 
 
+def plain_act(x: torch.Tensor, act: str = "relu2") -> torch.Tensor:
+    """Activation of a non-gated MLP: ``relu2`` (squared ReLU, Nemotron-H), ``silu``, ``gelu``, ``relu``."""
+    if act == "relu2":
+        return torch.relu(x).square()
+    if act == "silu":
+        return tF.silu(x)
+    if act == "relu":
+        return torch.relu(x)
+    if act in ("gelu", "gelu_pytorch_tanh", "gelu_tanh"):
+        return tF.gelu(x, approximate="none" if act == "gelu" else "tanh")
+    raise ValueError(f"unknown activation '{act}'")
+
+
 # --------------------------------------------------------------------------------------- embedding
 class _Embedding(torch.autograd.Function):
     @staticmethod

@@ -206,7 +206,8 @@ class PolicyWorker:
             except Exception as e:
                 print(f"[policy] fused expert-parallel dispatch unavailable ({type(e).__name__}: {e}); using NCCL all-to-all")
         self.ep.comm = st.ep_comm
-        dense = (lambda n: not CausalLM.is_expert_param(n)) if split_experts else None
+        expert_names = self.model.expert_param_names() if split_experts else set()
+        dense = (lambda n: n not in expert_names) if split_experts else None
         self.flat_base = None
         if self.lora_cfg is not None:
             # LoRA: the base weights are frozen (no gradient buffer, no optimizer state, and they double as the reference
@@ -223,7 +224,7 @@ class PolicyWorker:
         e_group, e_world = None, 1
         if split_experts:
             e_group, e_world = st.extras.get("expert_dp_group"), int(st.extras.get("expert_dp_size", 1))
-            self.flat_e = self.model.flatten_parameters(align=256 * max(1, e_world), include=CausalLM.is_expert_param)
+            self.flat_e = self.model.flatten_parameters(align=256 * max(1, e_world), include=expert_names.__contains__)
         self.ref_flat: Optional[torch.Tensor] = None
         self.ref_flat_e: Optional[torch.Tensor] = None
         self._has_reference = bool(init_reference_model)

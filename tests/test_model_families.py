@@ -198,3 +198,105 @@ def test_dense_and_moe_families_match_huggingface(tmp_path, family):
         ref = hf(input_ids=ids).logits[0]
         z = m.logits(PackedBatch.from_padded(ids, torch.tensor([200])))
     assert (z - ref).abs().max().item() < 2e-4, (family, (z - ref).abs().max().item())
+
+
+def _nemotron_get(sd):
+    """HF keeps the experts stacked (``experts.up_proj`` [E, f, d]); checkpoints and this repo name them per expert."""
+    import re
+
+    def get(name):
+        m = re.match(r"(.*\.mixer\.experts)\.(\d+)\.(up|down)_proj\.weight", name)
+        return sd[f"{m.group(1)}.{m.group(3)}_proj"][int(m.group(2))] if m else sd.get(name)
+
+    return get
+
+
+@pytest.mark.parametrize("latent", [None, 24])
+def test_nemotron_h_matches_huggingface(latent):
+    """Nemotron-H: Mamba-2 mixers (chunked scan, depth-wise conv, grouped gated norm), attention without rotation, experts
+    without a gate (squared ReLU) behind a sigmoid group-limited router, optionally in a latent space, plus a shared expert."""
+    transformers = pytest.importorskip("transformers")
+    if not hasattr(transformers, "NemotronHForCausalLM"):
+        pytest.skip("this transformers build has no NemotronH")
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+    from rl_b200.models.transformer import PackedBatch, build_model
+
+    hf_cfg = transformers.NemotronHConfig(
+        vocab_size=256, hidden_size=64, layers_block_type=["mamba", "moe", "attention", "mamba", "moe"], num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, mamba_num_heads=8, mamba_head_dim=16, ssm_state_size=16, n_groups=2, chunk_size=8,
+        n_routed_experts=4, moe_intermediate_size=32, moe_shared_expert_intermediate_size=48, num_experts_per_tok=2,
+        moe_latent_size=latent, attn_implementation="eager", n_group=2, topk_group=1, routed_scaling_factor=1.5)
+    torch.manual_seed(0)
+    hf = transformers.NemotronHForCausalLM(hf_cfg).eval().float()
+    for mod in hf.modules():      # the library's pure-PyTorch path clamps the step size at time_step_min; its kernels do not
+        if hasattr(mod, "time_step_min"):
+            mod.time_step_min = 0.0
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or n.endswith(".D"):
+                p.copy_(1 + torch.randn_like(p) * 0.2)
+            if "experts" in n or "gate.weight" in n:
+                p.copy_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if "e_score" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict(), torch_dtype="float32")
+    assert cfg.is_hybrid and cfg.layers_block_type[0] == "mamba" and not cfg.use_rope and not cfg.mlp_gated and cfg.num_experts == 4
+    assert ModelConfig.from_hf_dict(cfg.to_hf_dict()) == cfg
+    m = build_model(cfg, dtype=torch.float32, init=False)
+    sd = _hf_state(hf)
+    assert not load_hf_tensors(m, _nemotron_get(sd))
+    ids = torch.randint(0, 256, (2, 37))
+    lens = torch.tensor([37, 21])       # several chunks of 8, one ragged
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=(torch.arange(37)[None] < lens[:, None]).long()).logits
+        batch = PackedBatch.from_padded(ids, lens)
+        z = batch.unpack(m.logits(batch), 37)
+    for b, n in enumerate(lens.tolist()):
+        assert (z[b, :n] - ref[b, :n]).abs().max().item() < 2e-4, (b, (z[b, :n] - ref[b, :n]).abs().max().item())
+    out = dict(iter_hf_tensors(m))
+    get = _nemotron_get(sd)
+    for k, v in out.items():
+        assert torch.allclose(v, get(k), atol=1e-6), k
+    lp, _ = m.next_token_logprobs(batch)
+    lp.sum().backward()
+    skip = ("e_score",)
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in m.named_parameters() if not any(s in n for s in skip))
+
+
+def test_mamba_mixer_continues_from_its_state():
+    """A sequence evaluated in two pieces, and then token by token, gives what one pass gives: the states handed on (last conv
+    inputs, state-space state) carry everything the rest of the sequence needs."""
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.mamba import Mamba2Mixer
+
+    cfg = ModelConfig(model_type="nemotron_h", hidden_size=32, layers_block_type=["mamba"], num_hidden_layers=1, mamba_num_heads=4,
+                      mamba_head_dim=8, ssm_state_size=8, mamba_n_groups=2, mamba_chunk_size=4, use_rope=False, mlp_gated=False)
+    torch.manual_seed(1)
+    mx = Mamba2Mixer(cfg, torch.float32, "cpu")
+    with torch.no_grad():
+        for p in mx.parameters():
+            p.copy_(torch.randn_like(p) * 0.3)
+        mx.reset_special(torch.Generator().manual_seed(0))
+    lens = [11, 6]
+    u = torch.randn(sum(lens), 32)
+    cu = torch.tensor([0, 11, 17], dtype=torch.int32)
+    with torch.no_grad():
+        full, (conv, ssm) = mx(u, cu, 11, return_state=True)
+        # first 7 / 4 tokens, then the rest from the returned state
+        a = torch.cat([u[0:7], u[11:15]])
+        b = torch.cat([u[7:11], u[15:17]])
+        ya, st = mx(a, torch.tensor([0, 7, 11], dtype=torch.int32), 7, return_state=True)
+        yb, (conv2, ssm2) = mx(b, torch.tensor([0, 4, 6], dtype=torch.int32), 4, state=st, return_state=True)
+        assert torch.allclose(torch.cat([ya[:7], yb[:4], ya[7:], yb[4:]]), full, atol=1e-5)
+        assert torch.allclose(conv2, conv, atol=1e-6) and torch.allclose(ssm2, ssm, atol=1e-5)
+        # token by token from the state after the first piece
+        cs, ss = st
+        outs = []
+        for t in range(4):
+            row = torch.stack([u[7 + t], u[15 + min(t, 1)]])
+            y, cs, ss = mx.step(row, cs, ss)
+            outs.append(y)
+        assert torch.allclose(torch.stack([o[0] for o in outs]), full[7:11], atol=1e-5)
+        assert torch.allclose(outs[0][1], full[15], atol=1e-5) and torch.allclose(outs[1][1], full[16], atol=1e-5)

@@ -386,7 +386,23 @@ class GenerationEngine:
         # scheduler on the same requests and samples the same tokens (rank 0's sample is broadcast each step)
         self.tp = getattr(model, "tp", None)
         self.tpw = self.tp.world if self.tp is not None else 1
-        attn0 = model.layers[0].self_attn if len(model.layers) else None
+        # hybrid state-space models (Nemotron-H): only the attention blocks have key / value pages; every running sequence
+        # also owns one row of each Mamba block's state pools (the last conv inputs and the state-space state), see
+        # ``_hybrid_block``. Prefixes are not shared between sequences (pages carry no state) and decode runs eagerly.
+        self.hybrid = bool(self.cfg.is_hybrid)
+        self._attn_layers = [i for i, l in enumerate(model.layers) if l.self_attn is not None]
+        if self.hybrid:
+            ep_h = getattr(model, "ep", None)
+            if self.tpw > 1 or (ep_h is not None and ep_h.world > 1):
+                raise NotImplementedError("the generation engine serves hybrid state-space models on one GPU per replica")
+            if self.quantization:
+                raise NotImplementedError("quantised rollout is not available for hybrid state-space models")
+        self.mamba_conv: Optional[list] = None
+        self.mamba_ssm: Optional[list] = None
+        self._state_row: dict[int, int] = {}
+        self._free_rows: list[int] = []
+        self._decode_rows: Optional[torch.Tensor] = None
+        attn0 = model.layers[self._attn_layers[0]].self_attn if self._attn_layers else None
         self.hq = attn0.hq if attn0 is not None else self.cfg.num_attention_heads
         self.hkv = attn0.hkv if attn0 is not None else self.cfg.num_key_value_heads
         # tensor-parallel decode is captured too when the fused GEMM + all-reduce kernel (device-resident epoch) carries the
@@ -395,7 +411,8 @@ class GenerationEngine:
         # host visit, on one GPU or, with the peer-memory expert-parallel communicator, across the expert group
         ep0 = getattr(model, "ep", None)
         moe_ok = (not self.cfg.is_moe) or ep0 is None or ep0.world == 1 or getattr(ep0, "comm", None) is not None
-        self.use_graphs = use_cuda_graphs and self.native and moe_ok and (self.tpw == 1 or getattr(self.tp, "comm", None) is not None)
+        self.use_graphs = use_cuda_graphs and self.native and moe_ok and (self.tpw == 1 or getattr(self.tp, "comm", None) is not None) \
+            and not self.hybrid
         self.logits_dtype = torch.float32 if logits_fp32 else model.dtype
         c = self.cfg
         if num_blocks is None:
@@ -403,7 +420,7 @@ class GenerationEngine:
                 num_blocks = (kv_cache_tokens + block_size - 1) // block_size + max_running
             elif self.device.type == "cuda":
                 free, _ = torch.cuda.mem_get_info(self.device)
-                per_block = 2 * len(model.layers) * self.hkv * block_size * c.head_dim * 2
+                per_block = 2 * max(1, len(self._attn_layers)) * self.hkv * block_size * c.head_dim * 2
                 num_blocks = max(16, int(free * gpu_memory_utilization) // per_block)
             else:
                 num_blocks = 256
@@ -421,7 +438,7 @@ class GenerationEngine:
         # Prefix cache: full prompt blocks stay addressable by the hash of the token prefix they end, across requests and
         # generate calls (until the weights change: ``sleep`` resets it). A later prompt with the same prefix, e.g. the next
         # turn of a multi-turn rollout, prefills only its new tokens.
-        self.prefix_caching = bool(enable_prefix_caching) and isinstance(self.sched, _NativeScheduler)
+        self.prefix_caching = bool(enable_prefix_caching) and isinstance(self.sched, _NativeScheduler) and not self.hybrid
         self._graphs: dict[int, tuple] = {}
         self._agreed_bucket = 0
         self._static: Optional[dict] = None
@@ -461,23 +478,70 @@ class GenerationEngine:
         c = self.cfg
         shape = (self.num_blocks, self.hkv, self.block_size, c.head_dim)
         dt = self.model.dtype
-        self.k_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(len(self.model.layers))]
-        self.v_cache = [torch.zeros(shape, dtype=dt, device=self.device) for _ in range(len(self.model.layers))]
+        attn = set(self._attn_layers)
+        self.k_cache = [torch.zeros(shape, dtype=dt, device=self.device) if i in attn else None for i in range(len(self.model.layers))]
+        self.v_cache = [torch.zeros(shape, dtype=dt, device=self.device) if i in attn else None for i in range(len(self.model.layers))]
+        if self.hybrid:   # row 0 is scratch (padding rows of a decode batch write there)
+            R = self.max_running + 1
+            self.mamba_conv = [torch.zeros((R, c.mamba_conv_dim, c.mamba_d_conv - 1), dtype=dt, device=self.device) if l.kind == "mamba" else None
+                               for l in self.model.layers]
+            self.mamba_ssm = [torch.zeros((R, c.mamba_num_heads, c.mamba_head_dim, c.ssm_state_size), dtype=torch.float32, device=self.device)
+                              if l.kind == "mamba" else None for l in self.model.layers]
+            self._state_row, self._free_rows = {}, list(range(R - 1, 0, -1))
 
     def sleep(self, free_kv_cache: bool = True) -> None:
         """Ends a generation phase: drops all requests; optionally returns the KV cache memory (captured graphs are
         tied to the cache addresses and are dropped with it)."""
         self.sched.reset()
+        if self.hybrid:
+            self._state_row, self._free_rows = {}, list(range(self.max_running, 0, -1))
         if free_kv_cache:
             self._graphs.clear()
             self._static = None
             self.k_cache = self.v_cache = None
+            self.mamba_conv = self.mamba_ssm = None
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
 
     def kv_cache_bytes(self) -> int:
         c = self.cfg
-        return 2 * len(self.model.layers) * self.num_blocks * self.hkv * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
+        return 2 * len(self._attn_layers) * self.num_blocks * self.hkv * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
+
+    # ------------------------------------------------------------------ hybrid state-space models
+    def _claim_state_rows(self, live) -> None:
+        """Keeps one state row per sequence that is scheduled this iteration and returns the rows of sequences that are not
+        (finished, or preempted: a preempted sequence is prefilled again from its first token, which rebuilds its state)."""
+        for sid in [s for s in self._state_row if s not in live]:
+            self._free_rows.append(self._state_row.pop(sid))
+        for sid in live:
+            if sid not in self._state_row:
+                if not self._free_rows:
+                    raise RuntimeError("no free state row: more sequences scheduled than max_running")
+                self._state_row[sid] = self._free_rows.pop()
+
+    def _hybrid_block(self, li: int, layer, h, seq=None):
+        """A block of a hybrid model that is not attention. ``seq`` = (cu_seqlens, max_len, state rows [sequences]) for whole
+        (pieces of) sequences, whose Mamba states start from and are left in the pools; None: one token per sequence of the
+        decode batch (``self._decode_rows``)."""
+        x = F.rmsnorm(h, layer.norm, self.cfg.rms_norm_eps)
+        if layer.kind != "mamba":
+            return layer.mlp(x, h)
+        conv, ssm = self.mamba_conv[li], self.mamba_ssm[li]
+        if seq is None:
+            rows = self._decode_rows
+            y, c1, s1 = layer.mamba.step(x, conv[rows], ssm[rows])
+        else:
+            cu, max_len, rows = seq
+            y, (c1, s1) = layer.mamba(x, cu, max_len, state=(conv[rows], ssm[rows]), return_state=True)
+        conv.index_copy_(0, rows, c1.to(conv.dtype))
+        ssm.index_copy_(0, rows, s1)
+        return h + y
+
+    def _zero_state_rows(self, rows: torch.Tensor) -> None:
+        for cbuf, sbuf in zip(self.mamba_conv, self.mamba_ssm):
+            if cbuf is not None:
+                cbuf.index_fill_(0, rows, 0)
+                sbuf.index_fill_(0, rows, 0)
 
     # ------------------------------------------------------------------ model forward (inference)
     def _layer_tail(self, layer, h, a):
@@ -547,12 +611,15 @@ class GenerationEngine:
         return tok, lp
 
     @torch.no_grad()
-    def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor) -> torch.Tensor:
+    def _prefill_forward(self, batch: PackedBatch, slots: torch.Tensor, last_idx: torch.Tensor, state_rows=None) -> torch.Tensor:
         m, c = self.model, self.cfg
         h = self._embed(batch.input_ids)
         if hasattr(m, "merge_vision"):
             h = m.merge_vision(h, batch.input_ids, getattr(batch, "mm", None))
         for li, layer in enumerate(m.layers):
+            if self.hybrid and layer.kind != "attention":
+                h = self._hybrid_block(li, layer, h, (batch.cu_seqlens, batch.max_seqlen, state_rows))
+                continue
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, batch.positions, m.inv_freq, apply_rope=False)
             qkv = E.rope_kv_cache_write(qkv, batch.positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
@@ -566,7 +633,7 @@ class GenerationEngine:
         """The decode step with RMSNorm and SwiGLU folded into the projections' epilogues (7 kernels per layer instead of
         10) covers dense bf16 layers on one GPU; everything else takes the layer-by-layer path below."""
         c = self.cfg
-        if not (self.native and self.tpw == 1 and not self.quantization and not c.is_moe and n <= 256
+        if not (self.native and self.tpw == 1 and not self.quantization and not c.is_moe and not self.hybrid and n <= 256
                 and os.environ.get("RLB_FUSED_DECODE", "1") != "0"):
             return False
         if c.hidden_size % 128 or c.intermediate_size % 64 or not len(self.model.layers):
@@ -665,6 +732,9 @@ class GenerationEngine:
         m, c = self.model, self.cfg
         h = self._embed(ids)
         for li, layer in enumerate(m.layers):
+            if self.hybrid and layer.kind != "attention":
+                h = self._hybrid_block(li, layer, h)
+                continue
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
             qkv = E.rope_kv_cache_write(qkv, positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], self.hq, self.hkv, c.head_dim)
@@ -685,7 +755,8 @@ class GenerationEngine:
             dev = self.device
             fields = [("slots", torch.int64, (B,)), ("keys", torch.int64, (B,)), ("ids", torch.int32, (B,)), ("positions", torch.int32, (B,)),
                       ("seq_lens", torch.int32, (B,)), ("active", torch.int32, (B,)), ("remaining", torch.int32, (B,)),
-                      ("win_step", torch.int32, (4,)), ("stop_ids", torch.int32, (self.MAX_STOP_IDS,)), ("block_table", torch.int32, (B, MB))]
+                      ("win_step", torch.int32, (4,)), ("stop_ids", torch.int32, (self.MAX_STOP_IDS,)), ("state_rows", torch.int64, (B,)),
+                      ("block_table", torch.int32, (B, MB))]
             offs, total = {}, 0
             for name, dt, shape in fields:
                 n = 1
@@ -723,6 +794,7 @@ class GenerationEngine:
         return n
 
     def _decode_body(self, st, B, sp: SamplingParams, num_splits, scratch):
+        self._decode_rows = st["state_rows"][:B]
         logits = self._decode_forward(st["ids"][:B], st["positions"][:B], st["slots"][:B], st["block_table"][:B],
                                       st["seq_lens"][:B], num_splits, scratch)
         E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy, seed=self.BASE_SEED,
@@ -739,6 +811,7 @@ class GenerationEngine:
         c = self.cfg
         num_splits = E.choose_splits(B, self.hkv, max(self.max_model_len // 2, 1), self.block_size, self._sm_count) if self.native else 1
         if not self.native:
+            self._decode_rows = st["state_rows"][:n]
             logits = self._decode_forward(st["ids"][:n].long(), st["positions"][:n], st["slots"][:n], st["block_table"][:n],
                                           st["seq_lens"][:n], 1, None)
             tok, lp = E.sample(logits, temperature=sp.temperature, top_k=sp.top_k or 0, top_p=sp.top_p, greedy=sp.greedy,
@@ -827,7 +900,11 @@ class GenerationEngine:
         mms = [reqs[sid].mm for sid, _, _ in items if getattr(reqs[sid], "mm", None) is not None]
         if mms:
             batch.mm = dict(patches=_L.to_device(torch.cat([m[0] for m in mms]), dev), sizes=[int(x) for m in mms for x in m[1]])
-        logits = self._prefill_forward(batch, torch.cat(slots).to(dev), (cu[1:] - 1).to(dev))
+        rows = None
+        if self.hybrid:   # whole prompts: the states start from zero
+            rows = torch.tensor([self._state_row[sid] for sid, _, _ in items], dtype=torch.int64, device=dev)
+            self._zero_state_rows(rows)
+        logits = self._prefill_forward(batch, torch.cat(slots).to(dev), (cu[1:] - 1).to(dev), rows)
         self.stats["prefill_tokens"] += len(toks)
         return {sid: logits[j] for j, (sid, _, _) in enumerate(items)}
 
@@ -891,7 +968,19 @@ class GenerationEngine:
             pre_blk, pre_off = ps // self.block_size, ps % self.block_size
         total, W = row, (hq + 2 * hkv) * D
         h = self._embed(ids)
+        if self.hybrid:   # the new tokens as sequences of their own; a piece that starts a prompt starts from zero states
+            news = [n for _, _, _, n in round_items]
+            cu_new = torch.zeros(len(news) + 1, dtype=torch.int32)
+            cu_new[1:] = torch.tensor(news, dtype=torch.int64).cumsum(0)
+            cu_new = cu_new.to(dev)
+            st_rows = torch.tensor([self._state_row[sid] for sid, _, _, _ in round_items], dtype=torch.int64, device=dev)
+            fresh = [self._state_row[sid] for sid, _, p, _ in round_items if p == 0]
+            if fresh:
+                self._zero_state_rows(torch.tensor(fresh, dtype=torch.int64, device=dev))
         for li, layer in enumerate(m.layers):
+            if self.hybrid and layer.kind != "attention":
+                h = self._hybrid_block(li, layer, h, (cu_new, max(news), st_rows))
+                continue
             x = F.rmsnorm(h, layer.input_layernorm, c.rms_norm_eps)
             qkv = layer.self_attn.project_qkv(x, positions, m.inv_freq, apply_rope=False)
             qkv = E.rope_kv_cache_write(qkv, positions, self._freq(layer), slots, self.k_cache[li], self.v_cache[li], hq, hkv, D)
@@ -938,6 +1027,10 @@ class GenerationEngine:
             ids_np[j] = r.out_tokens[-1]
             keys_np[j] = self._row_key(r, sp)
             rem_np[j] = r.max_new - len(r.out_tokens)
+        if self.hybrid:
+            hb["state_rows"].zero_()    # padding rows use the scratch row
+            for j, sid in enumerate(decode):
+                hb["state_rows"][j] = self._state_row[sid]
         hb["active"][:n] = 1
         hb["win_step"][0] = 0
         B = self._bucket(max(n, 1))
@@ -1025,7 +1118,7 @@ class GenerationEngine:
             mm = mm_inputs[i] if mm_inputs is not None else None
             if mm is not None and mm[0] is None:
                 mm = None
-            if share_prefixes:
+            if share_prefixes and not self.hybrid:   # (pages of a shared prompt carry no state-space state)
                 key = tuple(p)
                 if mm is not None:   # equal prompts share their prefix only if they show the same images
                     from rl_b200.data.multimodal_utils import content_key
@@ -1069,6 +1162,8 @@ class GenerationEngine:
                                       sum(1 for r in reqs.values() if not r.finished)))
             if not idle and not prefill and not shared and not decode:
                 raise RuntimeError("scheduler made no progress (KV cache too small for a single request)")
+            if self.hybrid:
+                self._claim_state_rows(set(prefill) | set(decode))
             agreed_steps = None
             if lock:
                 # one exchange per iteration: does anyone still work, decode, prefill; the largest decode batch (every rank
@@ -1109,6 +1204,8 @@ class GenerationEngine:
                     r = reqs[sid]
                     ids_np[j] = r.out_tokens[-1]
                     keys_np[j] = self._row_key(r, sp)
+                    if self.hybrid:
+                        hb["state_rows"][j] = self._state_row[sid]
                 st["blob"].copy_(st["host_blob"], non_blocking=True)
                 self._step_counter += 1
                 tok, lp = self._run_decode(n, sp, max_ctx)
@@ -1148,7 +1245,7 @@ class GenerationEngine:
                 if copies:
                     src = torch.tensor([a for a, _ in copies], dtype=torch.int32, device=dev)
                     dst = torch.tensor([b for _, b in copies], dtype=torch.int32, device=dev)
-                    for li in range(len(self.model.layers)):
+                    for li in self._attn_layers:
                         E.block_copy(self.k_cache[li], self.v_cache[li], src, dst)
                 new = list(prefill) + list(shared)
                 rows = torch.stack([last_logits[sid] if sid in last_logits else last_logits[reqs[sid].share_with] for sid in new])

@@ -136,6 +136,15 @@ class ModelConfig:
 
     def num_parameters(self) -> int:
         d, L = self.hidden_size, self.num_hidden_layers
+        if self.layers_block_type is not None:
+            I, C, H = self.mamba_inner, self.mamba_conv_dim, self.mamba_num_heads
+            din = self.moe_latent_size or d
+            per = {"mamba": (I + C + H) * d + C * (self.mamba_d_conv + 1) + 3 * H + I + d * I,
+                   "attention": d * self.qkv_size + self.q_size * d,
+                   "mlp": 2 * d * self.intermediate_size,
+                   "moe": self.num_experts * (2 * din * self.moe_intermediate_size + d) + 2 * d * self.moe_shared_expert_intermediate_size
+                          + (2 * d * din if self.moe_latent_size else 0)}
+            return sum(per[t] + d for t in self.layers_block_type) + self.vocab_size * d * (1 if self.tie_word_embeddings else 2) + d
         attn = d * self.qkv_size + self.q_size * d + (self.qkv_size if self.attention_bias else 0)
         if self.is_moe:
             ffn = self.num_experts * 3 * d * self.moe_intermediate_size + self.num_experts * d
@@ -375,6 +384,29 @@ PRESETS: dict[str, dict] = {
     "tiny-llama-oracle": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
                               num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
                               rms_norm_eps=1e-5, rope_theta=10000.0),
+    # tiny hybrid model for offline recipes and tests: Mamba-2, MLP, attention and expert blocks
+    "tiny-nemotron-h": dict(model_type="nemotron_h", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=6,
+                            layers_block_type=["mamba", "mlp", "mamba", "attention", "mamba", "moe"], num_attention_heads=4,
+                            num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-5, use_rope=False, mlp_gated=False, hidden_act="relu2",
+                            mamba_num_heads=8, mamba_head_dim=64, ssm_state_size=32, mamba_n_groups=2, mamba_chunk_size=64,
+                            num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1,
+                            moe_shared_expert_intermediate_size=256, scoring_func="sigmoid"),
+    # Nemotron-Nano-12B-v2-shaped (Mamba-2 / MLP blocks with six attention blocks; the reference's grpo-nano-v2-12b recipes)
+    "nemotron-nano-12b-v2": dict(model_type="nemotron_h", vocab_size=131072, hidden_size=5120, intermediate_size=20480, num_hidden_layers=62,
+                                 layers_block_type=[{"M": "mamba", "-": "mlp", "*": "attention"}[ch] for ch in
+                                                    "M-M-M-M*-M-M-M-M*-M-M-M-M*-M-M-M-M*-M-M-M-M*-M-M-M-M*-M-M-M-M-"],
+                                 num_attention_heads=40, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5, use_rope=False,
+                                 mlp_gated=False, hidden_act="relu2", mamba_num_heads=128, mamba_head_dim=80, ssm_state_size=128,
+                                 mamba_n_groups=8, mamba_chunk_size=128),
+    # Nemotron-3-Nano-30B-A3B-shaped (Mamba-2 / expert blocks with six attention blocks; the reference's grpo-nanov3 recipes)
+    "nemotron-nano-30b-a3b-v3": dict(model_type="nemotron_h", vocab_size=131072, hidden_size=2688, intermediate_size=1856, num_hidden_layers=52,
+                                     layers_block_type=[{"M": "mamba", "E": "moe", "*": "attention"}[ch] for ch in
+                                                        "MEMEM*EMEMEM*EMEMEM*EMEMEM*EMEMEM*EMEMEMEM*EMEMEMEME"],
+                                     num_attention_heads=32, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-5, use_rope=False,
+                                     mlp_gated=False, hidden_act="relu2", mamba_num_heads=64, mamba_head_dim=64, ssm_state_size=128,
+                                     mamba_n_groups=8, mamba_chunk_size=128, num_experts=128, num_experts_per_tok=6,
+                                     moe_intermediate_size=1856, n_shared_experts=1, moe_shared_expert_intermediate_size=3712,
+                                     scoring_func="sigmoid", routed_scaling_factor=2.5),
     # tiny vision-language model for offline recipes and tests: the oracle language model behind a 2-layer ViT
     "tiny-vlm": dict(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=688,
                      num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=4, head_dim=64,

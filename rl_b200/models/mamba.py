@@ -16,8 +16,8 @@ right-padded [sequences, max_len] grid for the scan (padding has ``dt = 0``: the
 back. The states a sequence ends in (the last ``d_conv - 1`` conv inputs and ``S``) can be returned and passed in again, which
 is how the generation engine continues a prompt chunk by chunk and then token by token.
 
-The products here are PyTorch statements in fp32 (matrix products on the tensor cores through the framework's library
-GEMMs); the reference reaches the same math through the ``mamba_ssm`` package
+The two projections run on the framework's GEMM kernels; the scan's products are PyTorch statements in fp32 (a native
+chunked-scan kernel is not written); the reference reaches the same math through the ``mamba_ssm`` package
 (nemo_rl/models/dtensor/parallelize.py:465 parallelises the HuggingFace NemotronH blocks, whose mixer this module restates).
 """
 
@@ -28,6 +28,8 @@ from typing import Optional
 import torch
 import torch.nn as nn
 import torch.nn.functional as TF
+
+from rl_b200.ops import functional as F
 
 from .config import ModelConfig
 
@@ -113,6 +115,13 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, groups: 
     return (w.float() * g.view_as(h)).to(z.dtype)
 
 
+def _proj(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> torch.Tensor:
+    """The two large projections run on the framework's GEMM (16-byte aligned rows); anything else on the library's."""
+    if b is None and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and x.dim() == 2:
+        return F.linear(x.contiguous(), w)
+    return TF.linear(x, w, b)
+
+
 class Mamba2Mixer(nn.Module):
     """Parameters in the HuggingFace layout: ``in_proj`` rows are [gate | x | B | C | dt]."""
 
@@ -137,7 +146,7 @@ class Mamba2Mixer(nn.Module):
     # ------------------------------------------------------------------ pieces shared by the sequence and the step form
     def _project(self, u: torch.Tensor):
         c = self.cfg
-        p = TF.linear(u, self.in_proj, self.in_proj_bias)
+        p = _proj(u, self.in_proj, self.in_proj_bias)
         return torch.split(p, [c.mamba_inner, c.mamba_conv_dim, c.mamba_num_heads], dim=-1)
 
     def _dt(self, dt: torch.Tensor) -> torch.Tensor:
@@ -151,7 +160,7 @@ class Mamba2Mixer(nn.Module):
         c = self.cfg
         y = y + self.D.float()[:, None] * x
         y = gated_group_norm(y.reshape(*y.shape[:-2], c.mamba_inner), z, self.norm, c.mamba_n_groups, c.rms_norm_eps)
-        return TF.linear(y, self.out_proj, self.out_proj_bias)
+        return _proj(y, self.out_proj, self.out_proj_bias)
 
     # ------------------------------------------------------------------ whole sequences (training, prefill)
     def forward(self, u: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, state: Optional[tuple] = None,

@@ -407,6 +407,14 @@ class HybridBlock(nn.Module):
         else:
             raise ValueError(f"unknown block type {self.kind!r}")
 
+    @property
+    def input_layernorm(self):   # the generation engine's attention path reads the pre-mixer norm under this name
+        return self.norm
+
+    def tail(self, h, a):
+        """Attention blocks only: from the attention output (before o_proj) to the block's output."""
+        return self.self_attn.project_out(a, h)
+
     def forward(self, h, positions, inv_freq, cu_seqlens, max_seqlen):
         x = F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
         if self.kind == "mamba":

@@ -420,7 +420,8 @@ class PolicyWorker:
         from rl_b200.refit.synchronizer import WeightSynchronizer
 
         st = self.pstate
-        assert st.pp * st.cp * st.ep == 1 and not self.model_cfg.is_moe, "re-sharding refit covers dense tensor/data-parallel layouts"
+        assert st.pp * st.cp * st.ep == 1 and not self.model_cfg.is_moe and not self.model_cfg.is_hybrid, \
+            "re-sharding refit covers dense tensor/data-parallel layouts of the attention + MLP families"
         world = dist.get_world_size() if dist.is_initialized() else 1
         assert world % gen_tp == 0, "generation tensor-parallel size must divide the world size"
         serve_group, comm = None, None

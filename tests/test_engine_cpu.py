@@ -196,3 +196,37 @@ def test_engine_serves_latent_attention_and_deepseek_experts():
         lp, _ = model.next_token_logprobs(b, temperature=0.8)
         got = torch.tensor(r.out_logprobs)
         assert torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (lp[len(r.prompt):], got)
+
+
+def test_engine_serves_hybrid_state_space_models():
+    """Nemotron-H blocks through the engine: Mamba-2 states kept per running sequence (prefill leaves them, every decode step
+    advances them, a prompt longer than the prefill budget continues from them chunk by chunk, a preempted sequence rebuilds
+    them), attention blocks on the paged cache without rotation, plain MLP and expert blocks."""
+    torch.manual_seed(0)
+    mc = ModelConfig(model_type="nemotron_h", vocab_size=97, hidden_size=32, intermediate_size=64,
+                     layers_block_type=["mamba", "mlp", "attention", "mamba", "moe"], num_hidden_layers=5, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, mamba_num_heads=4, mamba_head_dim=8, ssm_state_size=8, mamba_n_groups=2,
+                     mamba_chunk_size=4, use_rope=False, mlp_gated=False, hidden_act="relu2", num_experts=4, num_experts_per_tok=2,
+                     moe_intermediate_size=16, n_shared_experts=1, moe_shared_expert_intermediate_size=24, scoring_func="sigmoid",
+                     torch_dtype="float32")
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2 and "conv" not in n:
+                p.mul_(3.0)
+    prompts = [[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11], [9, 8, 7], [11] * 9, [5, 4, 3, 2, 1, 2, 3, 4, 5, 6, 7, 8, 9]]
+    # whole prompts; prompts cut into pieces of 5 tokens; a cache so small that sequences are preempted and come back
+    for kw in (dict(num_blocks=64), dict(num_blocks=64, max_prefill_tokens=5), dict(num_blocks=14, max_running=4)):
+        eng = GenerationEngine(model, block_size=4, max_model_len=64, use_cuda_graphs=False, **{"max_running": 8, **kw})
+        assert not eng.prefix_caching and eng.hybrid
+        recs = eng.generate(prompts, SamplingParams(max_new_tokens=10, stop_token_ids=[], seed=3, temperature=0.8))
+        for r in recs:
+            seq = torch.tensor([r.prompt + r.out_tokens])
+            b = PackedBatch.from_padded(seq, torch.tensor([seq.shape[1]]))
+            lp, _ = model.next_token_logprobs(b, temperature=0.8)
+            got = torch.tensor(r.out_logprobs)
+            assert len(r.out_tokens) == 10 and torch.allclose(lp[len(r.prompt):], got, atol=1e-4), (kw, lp[len(r.prompt):], got)
+        if kw.get("num_blocks") == 14:
+            assert eng.sched.num_preemptions > 0
+        eng.sleep()
+        assert eng.mamba_ssm is None

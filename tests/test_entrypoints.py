@@ -93,6 +93,20 @@ def test_run_grpo_offline_recipe(capsys):
     assert "[grpo] step 2:" in out
 
 
+def test_run_grpo_with_a_hybrid_state_space_model(capsys, tmp_path):
+    """The whole loop (engine with per-sequence Mamba states, log-probabilities, training, checkpoint) on the Nemotron-H blocks."""
+    from examples import run_grpo
+
+    run_grpo.main(["--config", f"{ROOT}/examples/configs/grpo_arithmetic_offline.yaml", "grpo.max_num_steps=2", "policy.model_name=tiny-nemotron-h",
+                   f"logger.log_dir={tmp_path}/logs", f"checkpointing.checkpoint_dir={tmp_path}/ckpt"])
+    out = capsys.readouterr().out
+    assert "[grpo] step 2:" in out
+    import re
+
+    err = [float(x) for x in re.findall(r"mult_prob_err=([0-9.]+)", out)]
+    assert err and all(e < 1.05 for e in err)      # engine and trainer agree on the sampled tokens' probabilities
+
+
 def test_run_sft_dpo_rm_eval(capsys):
     from examples import run_dpo, run_eval, run_rm, run_sft
 

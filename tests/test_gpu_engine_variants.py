@@ -119,3 +119,16 @@ def test_fused_rope_kv_write_matches_fp32_reference(D, Hq, Hkv, bs):
     assert torch.equal(kc[blk, :, off], out.view(T, -1, D)[ok][:, Hq : Hq + Hkv])
     assert torch.equal(vc[blk, :, off], qkv.view(T, -1, D)[ok][:, Hq + Hkv :])
     assert int((kc.abs().sum((1, 3)) > 0).sum()) == int(ok.sum())             # nothing else was touched
+
+
+def test_engine_serves_hybrid_state_space_model_on_gpu():
+    """Nemotron-H blocks on the GPU: Mamba-2 states per running sequence through prefill and windowed decode, attention
+    blocks on the paged cache, MLP and expert blocks; the engine's log-probabilities agree with the trainer's."""
+    from rl_b200.models.config import preset
+    from rl_b200.ops.lib import check_status
+
+    mc = preset("tiny-nemotron-h", vocab_size=4096, hidden_size=512, intermediate_size=1024, head_dim=128, num_attention_heads=4,
+                num_key_value_heads=2)
+    err, out, gen = _gen_and_score(mc, dict(use_cuda_graphs=True))
+    assert check_status() == 0 and (out["generation_lengths"] == 12).all()
+    assert err.mean().item() < 0.03 and err.max().item() < 0.5

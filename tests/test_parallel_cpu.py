@@ -49,11 +49,11 @@ def _entry(fn, rank, world, port, q, args):
         dist.destroy_process_group()
 
 
-def _full_model(seed=3, **over):
+def _full_model(seed=3, name="tiny-llama-oracle", **over):
     from rl_b200.models.config import preset
     from rl_b200.models.transformer import build_model
 
-    cfg = preset("tiny-llama-oracle", **over)
+    cfg = preset(name, **over)
     return cfg, build_model(cfg, dtype=torch.float32, seed=seed)
 
 
@@ -66,14 +66,14 @@ def _batch(cfg, T_seqs=(9, 14, 5)):
     return PackedBatch.from_padded(ids, torch.tensor(T_seqs))
 
 
-def _tp_worker(rank, world, sp, tied):
+def _tp_worker(rank, world, sp, tied, name="tiny-llama-oracle"):
     from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
     from rl_b200.models.transformer import build_model
     from rl_b200.parallel.state import init_parallel
     from rl_b200.parallel.tensor import TP
 
     st = init_parallel(tp=world, sequence_parallel=sp)
-    cfg, full = _full_model(tie_word_embeddings=tied)
+    cfg, full = _full_model(name=name, tie_word_embeddings=tied)
     sd = dict(iter_hf_tensors(full))
     tp = TP.from_state(st)
     model = build_model(cfg, dtype=torch.float32, seed=99, tp=tp)
@@ -112,10 +112,22 @@ class _GradView:
         for n, p in self._m.named_parameters():
             yield n, (p.grad if p.grad is not None else torch.zeros_like(p))
 
+    def named_buffers(self):
+        for n, b in self._m.named_buffers():
+            yield n, torch.zeros_like(b)
+
 
 @pytest.mark.parametrize("sp,tied", [(True, False), (False, False), (True, True)])
 def test_tensor_parallel_matches_single_rank(sp, tied):
     out = _spawn(_tp_worker, 2, sp, tied)
+    for r, m in out.items():
+        assert m["lp"] < 2e-4 and m["ent"] < 2e-4 and m["grad"] < 2e-3 and m["w"] == 0.0 and m["logits"] < 2e-4, (r, m)
+
+
+def test_tensor_parallel_hybrid_model_matches_single_rank():
+    """Nemotron-H under tensor parallelism: the plain MLP blocks and the output head are sharded, the Mamba, attention and
+    expert blocks are replicated."""
+    out = _spawn(_tp_worker, 2, False, False, "tiny-nemotron-h")
     for r, m in out.items():
         assert m["lp"] < 2e-4 and m["ent"] < 2e-4 and m["grad"] < 2e-3 and m["w"] == 0.0 and m["logits"] < 2e-4, (r, m)
 

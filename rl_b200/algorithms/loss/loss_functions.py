@@ -479,8 +479,10 @@ class DraftCrossEntropyLossFn:
     loss_type = LossType.TOKEN_LEVEL
     input_type = LossInputType.DRAFT
 
-    def __call__(self, draft_logits, target_logits, data, global_valid_seqs, global_valid_toks):
-        token_mask = data["token_mask"][:, 1:].to(torch.float32)
+    def __call__(self, draft_logits, target_logits, data, global_valid_seqs, global_valid_toks, token_mask=None):
+        """``token_mask`` [B, S - 1]: which predictions count, when they are not the plain next-token ones (a draft that reads
+        the following token's embedding predicts one position further, so its mask is shifted once more)."""
+        token_mask = (data["token_mask"][:, 1:] if token_mask is None else token_mask).to(torch.float32)
         sample_mask = data["sample_mask"].to(torch.float32)
         mask = token_mask * sample_mask.unsqueeze(-1)
         tgt = torch.softmax(target_logits.float().detach(), dim=-1)

@@ -83,11 +83,12 @@ class DraftLossWrapper:
         self.needs_draft_logits = True
 
     def __call__(self, data=None, global_valid_seqs=None, global_valid_toks=None, draft_logits: Optional[torch.Tensor] = None,
-                 target_logits: Optional[torch.Tensor] = None, **loss_input):
+                 target_logits: Optional[torch.Tensor] = None, draft_token_mask: Optional[torch.Tensor] = None, **loss_input):
         loss, metrics = self.policy_loss_fn(data=data, global_valid_seqs=global_valid_seqs, global_valid_toks=global_valid_toks, **loss_input)
         if draft_logits is None:
             return loss, metrics
-        d_loss, d_metrics = self.draft_loss_fn(draft_logits, target_logits, data, global_valid_seqs, global_valid_toks)
+        d_loss, d_metrics = self.draft_loss_fn(draft_logits, target_logits, data, global_valid_seqs, global_valid_toks,
+                                               **({"token_mask": draft_token_mask} if draft_token_mask is not None else {}))
         metrics = dict(metrics)
         metrics.update({("draft_" + k if not k.startswith("draft") else k): v for k, v in d_metrics.items() if k != "num_valid_samples"})
         metrics["policy_loss"] = metrics.get("loss")

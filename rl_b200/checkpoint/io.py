@@ -94,17 +94,26 @@ def load_weights(worker, path: str) -> None:
         reader = _SafetensorsDir(path)
         by_param = {}
         for hf, loc, rows, e, hs in _model_map(worker.model):
-            by_param.setdefault(loc, []).append((hf, rows))
+            by_param.setdefault(loc, []).append((hf, rows, e))
 
-        def get(name):   # full local parameter assembled from its HF pieces
+        def rows_of(parts):   # one (expert's) matrix from its HF pieces, in row order
+            if len(parts) == 1 and parts[0][1] is None:
+                return reader.get(parts[0][0])
+            return torch.cat([reader.get(hf) for hf, _, _ in sorted(parts, key=lambda x: x[1][0])], dim=0)
+
+        def get(name):   # full local parameter assembled from its HF pieces (stacked experts: one matrix per expert)
             parts = by_param.get(name)
             if not parts:
                 return None
-            if len(parts) == 1 and parts[0][1] is None:
-                return reader.get(parts[0][0])
-            return torch.cat([reader.get(hf) for hf, _ in sorted(parts, key=lambda x: x[1][0])], dim=0)
+            if parts[0][2] is None:
+                return rows_of(parts)
+            experts = sorted({e for _, _, e in parts})
+            return torch.stack([rows_of([p for p in parts if p[2] == e]) for e in experts])
 
         worker.sharder.load_full_params(get)
+        for bname, b in worker.model.named_buffers():      # stored buffers (router selection biases) are not sharded
+            if bname in by_param:
+                b.copy_(reader.get(by_param[bname][0][0]).to(b.dtype))
         return
     from rl_b200.checkpoint.dcp_state import is_per_parameter_checkpoint
 

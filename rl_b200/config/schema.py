@@ -190,11 +190,15 @@ GENERATION = dict(backend=F(str, choices=("native", "vllm", "sglang", "megatron"
                   port_range_low=F(int), port_range_high=F(int), val_temperature=F(float, int), val_top_p=F(float, int), val_top_k=F(int),
                   refit_transport=F(str), real_quant_export_cpu_offload=F(bool), refit_cfg=F(dict))
 
+# draft head trained beside the policy (nemo_rl/models/policy/__init__.py:497 DraftConfig)
+DRAFT = dict(enabled=F(bool, nullable=False), model_name=F(str), loss_weight=F(float, int), num_layers=F(int), aux_layer_indices=F(list),
+             draft_vocab_size=F(int))
+
 POLICY = dict(
     model_name=F(str), tokenizer=F(dict, sub=TOKENIZER), train_global_batch_size=F(int, required=True, nullable=False),
     train_micro_batch_size=F(int, required=True, nullable=False), logprob_batch_size=F(int), logprob_chunk_size=F(int),
     generation=F(dict, sub=GENERATION), generation_batch_size=F(int), precision=F(str, choices=("bfloat16", "float32", "float16", "bf16", "fp32")),
-    reward_model_cfg=F(dict), dtensor_cfg=F(dict, sub=DTENSOR), megatron_cfg=F(dict, sub=MEGATRON), draft=OPAQUE,
+    reward_model_cfg=F(dict), dtensor_cfg=F(dict, sub=DTENSOR), megatron_cfg=F(dict, sub=MEGATRON), draft=F(dict, sub=DRAFT),
     pretrained_checkpoint=F(dict), router_replay=F(dict, sub=dict(enabled=F(bool))), hf_config_overrides=F(dict),
     dynamic_batching=F(dict, sub=DYNAMIC_BATCHING), sequence_packing=F(dict, sub=PACKING), make_sequence_length_divisible_by=F(int),
     max_total_sequence_length=F(int, required=True, nullable=False), max_grad_norm=F(float, int), refit_buffer_size_gb=F(float, int),

@@ -540,6 +540,10 @@ class CausalLM(nn.Module):
         # fully sharded parameters (rl_b200/parallel/fsdp.py): when set, every unit of the model (embedding, each layer,
         # the head) runs through ``sharder.run`` which gathers its parameters for the duration of the call
         self.sharder = None
+        # draft-head training (rl_b200/models/draft.py): when set, the outputs of these layers (global indices), the token
+        # embeddings ("embeds") and the normed final hidden states ("final") of the last forward are kept in ``captured``
+        self.capture_layers: Optional[tuple] = None
+        self.captured: dict = {}
 
     # ------------------------------------------------------------------ parameters
     _TP_SHARDED = ("qkv_proj", "qkv_bias", "o_proj", "gate_up_proj", "up_proj", "down_proj", "lm_head")
@@ -692,11 +696,16 @@ class CausalLM(nn.Module):
             for i, layer in enumerate(self.layers):
                 h = self.sharder.run(f"layer{i}", lambda x, L=layer: L(x, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen), h)
             return h
-        for layer in self.layers:
+        cap = self.capture_layers
+        if cap is not None:
+            self.captured = {"embeds": h}
+        for i, layer in enumerate(self.layers):
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = ckpt.checkpoint(layer, h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen, use_reentrant=False)
             else:
                 h = layer(h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen)
+            if cap is not None and (self.layer_offset + i) in cap:
+                self.captured[self.layer_offset + i] = h
         return h
 
     def hidden_states(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -706,7 +715,10 @@ class CausalLM(nn.Module):
         h = self.run_layers(h, batch)
         if self.sharder is not None:
             return self.sharder.run("head", lambda x: F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), h)
-        return F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.last_stage else h
+        out = F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.last_stage else h
+        if self.capture_layers is not None and self.last_stage:
+            self.captured["final"] = out
+        return out
 
     def logits(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """[T, V] logits in fp32 (small models, tests and the distillation / top-k paths)."""

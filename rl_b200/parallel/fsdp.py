@@ -72,7 +72,8 @@ class ParamSharder:
         cfg = model.cfg
         if cfg.tie_word_embeddings and not cfg.value_head:
             raise NotImplementedError("fully sharded parameters with tied embeddings: untie the output head")
-        if cfg.is_moe or model.tp.world > 1 or model.pp_size > 1:
+        ep = getattr(model, "ep", None)
+        if (cfg.is_moe and ep is not None and ep.world > 1) or model.tp.world > 1 or model.pp_size > 1:
             raise NotImplementedError("fully sharded parameters cover dense data-parallel models (no tp / pp / ep)")
         self.model, self.group = model, group
         on = dist.is_available() and dist.is_initialized() and group != "self"
@@ -433,15 +434,21 @@ def iter_hf_tensors_sharded(model, sharder: ParamSharder):
 
     rows_of = {}
     for hf, loc, rows, e, hs in _model_map(model):
-        rows_of.setdefault(loc, []).append((hf, rows))
+        rows_of.setdefault(loc, []).append((hf, rows, e))
     for ui, u in enumerate(sharder.units):
         sharder.acquire(ui)
         try:
             for name, p in u.params:
-                for hf, rows in rows_of.get(name, []):
-                    yield hf, (p.data if rows is None else p.data[rows[0] : rows[1]])
+                for hf, rows, e in rows_of.pop(name, []):
+                    t = p.data if e is None else p.data[e]      # (stacked experts: one HF tensor per expert)
+                    yield hf, (t if rows is None else t[rows[0] : rows[1]])
         finally:
             sharder.release(ui)
+    buffers = dict(model.named_buffers())
+    for name, items in rows_of.items():      # stored buffers (router selection biases) are replicated, not sharded
+        if name in buffers:
+            for hf, rows, e in items:
+                yield hf, buffers[name]
 
 
 class ShardedServingSync:

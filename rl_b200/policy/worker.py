@@ -264,6 +264,73 @@ class PolicyWorker:
             self.train_top_k = int(gen_cfg["top_k"]) if gen_cfg.get("top_k") else None
             self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
         self.timers: dict[str, float] = {}
+        self.draft = self.draft_opt = None
+        self.draft_loss_weight = 1.0
+        dcfg = cfg.get("draft") or {}
+        if dcfg.get("enabled"):
+            self._init_draft(dcfg, dtype, init_optimizer)
+
+    # ------------------------------------------------------------------ draft head (speculative decoding)
+    def _init_draft(self, dcfg: dict, dtype, init_optimizer: bool) -> None:
+        """``policy.draft``: an EAGLE-3 style head trained beside the policy on the policy's own hidden states
+        (``enabled``, ``model_name`` a directory to start from, ``loss_weight``, ``num_layers``, ``aux_layer_indices``,
+        ``draft_vocab_size``). Role of nemo_rl/models/megatron/draft/utils.py::build_draft_model."""
+        from rl_b200.models.draft import EagleDraft
+
+        st = self.pstate
+        if st.tp * st.pp * st.cp > 1 or getattr(self, "sharder", None) is not None:
+            raise NotImplementedError("draft-head training runs on data-parallel layouts with resident parameters")
+        self.draft = EagleDraft(self.model_cfg, dcfg.get("aux_layer_indices"), int(dcfg.get("num_layers") or 1), dcfg.get("draft_vocab_size"),
+                                dtype=dtype, device=self.device)
+        if dcfg.get("model_name"):
+            self.draft.load_pretrained(str(dcfg["model_name"]))
+        else:
+            self.draft.init_head_from_policy(self.model.output_weight)
+        self.draft_loss_weight = float(dcfg.get("loss_weight", 1.0))
+        self.model.capture_layers = self.draft.aux_layers
+        if init_optimizer:
+            kw = dict((self.cfg.get("optimizer") or {}).get("kwargs") or {})
+            self.draft_opt = torch.optim.AdamW(self.draft.parameters(), lr=float(kw.get("lr", 1e-5)), betas=tuple(kw.get("betas", (0.9, 0.999))),
+                                               eps=float(kw.get("eps", 1e-8)), weight_decay=float(kw.get("weight_decay", 0.0)))
+
+    def wrap_loss_with_draft(self, loss_fn):
+        """The loss to hand to :meth:`train` when the draft head is trained along: policy loss + weight * draft loss."""
+        if self.draft is None:
+            return loss_fn
+        from rl_b200.algorithms.loss.wrapper import DraftLossWrapper
+
+        return DraftLossWrapper(loss_fn, draft_weight=self.draft_loss_weight)
+
+    def _draft_inputs(self, batch: PackedBatch, S: int, mb: BatchedDataDict) -> dict:
+        """Draft logits, their targets and mask for one micro-batch, from what the policy's forward left in ``captured``:
+        position t reads the chosen hidden states at t and the embedding of token t + 1, and is scored against the policy's
+        (detached, temperature-scaled) distribution at t + 1, i.e. over token t + 2."""
+        from rl_b200.ops import functional as F
+
+        cap = self.model.captured
+        aux = torch.cat([cap[i].detach() for i in self.draft.aux_layers], dim=-1)
+        nxt = torch.roll(cap["embeds"].detach(), -1, 0)        # (the last row of a sequence reads its neighbour's: masked below)
+        d_logits = self.draft(aux, nxt, batch.positions, self.model.rope_freqs(), batch.cu_seqlens, batch.max_seqlen)
+        with torch.no_grad():
+            t_logits = F.linear(cap["final"].detach(), self.model.output_weight).float() / self.temperature
+            t_logits = torch.roll(t_logits, -1, 0)
+            if self.draft.draft_vocab != self.model_cfg.vocab_size:
+                t_logits = t_logits.index_select(1, self.draft.target_ids())
+        tm = mb["token_mask"].float()
+        mask = torch.zeros_like(tm[:, 1:])
+        mask[:, : max(0, tm.shape[1] - 2)] = tm[:, 2:]
+        return dict(draft_logits=batch.unpack(d_logits, S)[:, :-1], target_logits=batch.unpack(t_logits, S)[:, :-1], draft_token_mask=mask)
+
+    def _draft_step(self, max_norm: Optional[float]) -> float:
+        params = [p for p in self.draft.parameters() if p.grad is not None]
+        if self.world > 1:
+            for p in params:
+                dist.all_reduce(p.grad, group=self.dp_group)
+        gn = torch.nn.utils.clip_grad_norm_(params, max_norm if max_norm else float("inf"))
+        self.draft_opt.param_groups[0]["lr"] = self.optimizer.lr      # the draft follows the policy's schedule
+        self.draft_opt.step()
+        self.draft_opt.zero_grad(set_to_none=True)
+        return float(gn)
 
     # ------------------------------------------------------------------ fully sharded parameters (ZeRO-3)
     def _init_fully_sharded(self, cfg, st, dp_group, dtype, init_optimizer: bool, init_reference_model: bool) -> None:
@@ -665,6 +732,9 @@ class PolicyWorker:
         """Runs optimizer steps over this rank's shard of ``data`` (``gbs`` counts samples over all ranks; each rank
         holds ``gbs / dp`` samples of every global batch). Returns loss / grad-norm / per-micro-batch metrics."""
         assert self.optimizer is not None or eval_mode
+        if self.draft is not None and not getattr(loss_fn, "needs_draft_logits", False) \
+                and getattr(loss_fn, "input_type", LossInputType.LOGPROB) == LossInputType.LOGPROB:
+            loss_fn = self.wrap_loss_with_draft(loss_fn)      # every algorithm trains the draft head along with the policy
         gbs = gbs or self.cfg["train_global_batch_size"]
         mbs = mbs or self.cfg["train_micro_batch_size"]
         cpw = self.cp.world  # context-parallel ranks of one replica see the same samples
@@ -705,6 +775,8 @@ class PolicyWorker:
                 total_tokens += int(batch.input_ids.numel())
                 with torch.set_grad_enabled(not eval_mode):
                     inputs = self._loss_inputs(loss_fn, batch, S, mb_dev)
+                    if self.draft is not None and getattr(loss_fn, "needs_draft_logits", False):
+                        inputs.update(self._draft_inputs(batch, S, mb_dev))
                     loss, metrics = loss_fn(data=mb_dev, global_valid_seqs=global_valid_seqs,
                                             global_valid_toks=global_valid_toks, **inputs)
                     if not eval_mode:
@@ -725,6 +797,10 @@ class PolicyWorker:
                     self.optimizer_e.lr = self.optimizer.lr
                     self.optimizer_e.apply(total.clone())
                 grad_norms.append(gn)
+                if self.draft_opt is not None and any(p.grad is not None for p in self.draft.parameters()):
+                    draft_gn = self._draft_step(self.cfg.get("max_grad_norm"))
+                    if all_mb_metrics:
+                        all_mb_metrics[-1]["draft_grad_norm"] = draft_gn
                 if getattr(self, "fp8_training", False):
                     _Fn_fp8.weights_changed()   # cached MXFP8 copies of the weights are stale now
             if self.world > 1:
@@ -816,6 +892,8 @@ class PolicyWorker:
             save_optimizer_shard(self, optimizer_path, model_save_format)
         if tokenizer_path and self.tokenizer is not None and self.rank == 0:
             self.tokenizer.save_pretrained(tokenizer_path)
+        if self.draft is not None and self.rank == 0:      # the draft head, in the EAGLE-3 checkpoint layout, beside the weights
+            self.draft.save_pretrained(os.path.join(os.path.dirname(os.path.abspath(weights_path)), "draft"))
         if self.world > 1:
             dist.barrier(group=self.dp_group)
 
@@ -825,6 +903,9 @@ class PolicyWorker:
         load_weights(self, weights_path)
         if optimizer_path and self.optimizer is not None and os.path.exists(optimizer_path):
             load_optimizer_shard(self, optimizer_path)
+        dpath = os.path.join(os.path.dirname(os.path.abspath(weights_path)), "draft")
+        if self.draft is not None and os.path.exists(os.path.join(dpath, "model.safetensors")):
+            self.draft.load_pretrained(dpath)
 
     def shutdown(self) -> bool:
         if self.generation is not None:

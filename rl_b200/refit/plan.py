@@ -17,6 +17,7 @@ The reference's counterparts are the CUDA-IPC / NCCL refit paths and the ``nccl_
 
 from __future__ import annotations
 
+import torch
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -64,30 +65,25 @@ class RefitPlan:
 
 
 def _param_shapes(cfg: ModelConfig, tp: int) -> dict[str, tuple[int, int]]:
-    """(rows, cols) of every local parameter of a tensor-parallel shard (1-D parameters have cols = 1... stored as (n, 1))."""
-    d, hd = cfg.hidden_size, cfg.head_dim
-    q, kv = cfg.q_size // tp, cfg.kv_size // tp
-    shapes = {"embed_tokens": (cfg.vocab_size, d), "norm": (d, 1)}
-    if cfg.value_head:
-        shapes["score"] = (8, d)
-    elif not cfg.tie_word_embeddings:
-        shapes["lm_head"] = (cfg.vocab_size // tp, d)
-    for i in range(cfg.num_hidden_layers):
-        lp = f"layers.{i}"
-        shapes[f"{lp}.input_layernorm"] = (d, 1)
-        shapes[f"{lp}.post_attention_layernorm"] = (d, 1)
-        shapes[f"{lp}.self_attn.qkv_proj"] = (q + 2 * kv, d)
-        shapes[f"{lp}.self_attn.o_proj"] = (d, q)
-        if cfg.attention_bias:
-            shapes[f"{lp}.self_attn.qkv_bias"] = (q + 2 * kv, 1)
-        if cfg.qk_norm:
-            shapes[f"{lp}.self_attn.q_norm"] = (hd, 1)
-            shapes[f"{lp}.self_attn.k_norm"] = (hd, 1)
-        if not cfg.is_moe:
-            f = cfg.intermediate_size // tp
-            shapes[f"{lp}.mlp.gate_up_proj"] = (2 * f, d)
-            shapes[f"{lp}.mlp.down_proj"] = (d, f)
-    return shapes
+    """(rows, cols) of every local parameter of a tensor-parallel shard, in the model's own parameter order: matrices as
+    (product of the leading dimensions, last dimension), vectors as (n, 1). Read off a model built without storage, so every
+    family (extra norms, latent attention, hybrid state-space blocks, stacked experts) is covered by construction."""
+    from rl_b200.models.transformer import CausalLM
+    from rl_b200.parallel.tensor import TP
+
+    key = (repr(cfg), tp)
+    hit = _SHAPE_CACHE.get(key)
+    if hit is None:
+        model = CausalLM(cfg, dtype=torch.bfloat16, device="meta", init=False, tp=TP(None, 0, tp))
+        hit = {}
+        for n, p in model.named_parameters():
+            shp = tuple(p.shape)
+            hit[n] = (shp[0], 1) if len(shp) == 1 else (int(torch.Size(shp[:-1]).numel()), shp[-1])
+        _SHAPE_CACHE[key] = hit
+    return dict(hit)
+
+
+_SHAPE_CACHE: dict = {}
 
 
 def serving_param_layout(cfg: ModelConfig, tp: int, align_elems: int = 8) -> tuple[dict[str, tuple[int, tuple[int, int]]], int]:

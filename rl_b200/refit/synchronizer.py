@@ -40,9 +40,17 @@ def build_serving_model(cfg: ModelConfig, tp_serve: int, rank: int, arena: torch
         for part in path:
             mod = getattr(mod, part) if not part.isdigit() else mod[int(part)]
         setattr(mod, leaf, torch.nn.Parameter(view, requires_grad=False))
+    from dataclasses import replace
+
     from rl_b200.models.config import rope_inv_freq
 
     model.inv_freq = rope_inv_freq(cfg, arena.device)
+    if getattr(model, "inv_freq_local", None) is not None:
+        model.inv_freq_local = rope_inv_freq(replace(cfg, rope_theta=cfg.rope_local_theta, rope_scaling=None), arena.device)
+    for mod in model.modules():     # stored buffers (router selection biases): real storage, filled by the weight sync
+        for bname, b in list(mod.named_buffers(recurse=False)):
+            if b.is_meta:
+                setattr(mod, bname, torch.zeros(b.shape, dtype=b.dtype, device=arena.device))
     return model
 
 

@@ -32,12 +32,12 @@ def _data(world, rank, n=8, S=20):
     return BatchedDataDict(input_ids=ids[sl], input_lengths=lens[sl], token_mask=torch.ones(per, S), sample_mask=torch.ones(per))
 
 
-def _run(rank, world, full, tmp):
+def _run(rank, world, full, tmp, name="tiny-llama-oracle"):
     from rl_b200.algorithms.loss.loss_functions import NLLLossFn
     from rl_b200.models.config import preset
     from rl_b200.policy.worker import PolicyWorker
 
-    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    mc = preset(name, torch_dtype="float32")
     w = PolicyWorker(_cfg(full), model_cfg=mc, device="cpu", init_reference_model=True, seed=5)
     assert (w.sharder is not None) == full
     data = _data(world, rank)
@@ -74,18 +74,19 @@ def _run(rank, world, full, tmp):
     return {k: (v.tolist() if isinstance(v, torch.Tensor) else v) for k, v in out.items()}
 
 
-@pytest.mark.parametrize("world", [1, 2])
-def test_fully_sharded_matches_resident_parameters(tmp_path, world):
+@pytest.mark.parametrize("world,name", [(1, "tiny-llama-oracle"), (2, "tiny-llama-oracle"), (2, "tiny-nemotron-h")])
+def test_fully_sharded_matches_resident_parameters(tmp_path, world, name):
+    """(the hybrid model adds Mamba-2 blocks, stacked experts without expert parallelism and a stored router buffer)"""
     if world == 1:
         from rl_b200.parallel.state import reset_parallel
 
         reset_parallel()
-        res = {0: _run(0, 1, False, str(tmp_path))}
+        res = {0: _run(0, 1, False, str(tmp_path), name)}
         reset_parallel()
-        full = {0: _run(0, 1, True, str(tmp_path))}
+        full = {0: _run(0, 1, True, str(tmp_path), name)}
     else:
-        res = _spawn(_run, world, False, str(tmp_path))
-        full = _spawn(_run, world, True, str(tmp_path))
+        res = _spawn(_run, world, False, str(tmp_path), name)
+        full = _spawn(_run, world, True, str(tmp_path), name)
     for r in range(world):
         a = {k: (torch.tensor(v) if k.startswith(("lp", "ref")) else v) for k, v in res[r].items()}
         b = {k: (torch.tensor(v) if k.startswith(("lp", "ref")) else v) for k, v in full[r].items()}

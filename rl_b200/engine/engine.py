@@ -641,6 +641,8 @@ class GenerationEngine:
         if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None or c.is_mla:
             return False   # the fused step hard-wires the Llama / Qwen block structure
         l0 = self.model.layers[0]
+        if any(getattr(p, "_rlb_qat", None) is not None for p in l0.parameters()):
+            return False   # quantisation-aware training: the projections go through the quantise-dequantise operators
         return getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
 
     @torch.no_grad()
@@ -692,6 +694,8 @@ class GenerationEngine:
         if c.sandwich_norm or c.hidden_act != "silu" or c.embed_scale != 1.0 or c.sliding_window or c.attn_scale is not None or c.is_mla:
             return False
         l0 = self.model.layers[0]
+        if any(getattr(p, "_rlb_qat", None) is not None for p in l0.parameters()):
+            return False
         f_local = l0.mlp.gate_up_proj.shape[0] // 2
         return (f_local % 64 == 0 and getattr(l0.self_attn, "qkv_lora", None) is None and getattr(l0.mlp, "gate_up_lora", None) is None
                 and getattr(l0.self_attn, "o_lora", None) is None)

@@ -105,10 +105,22 @@ class MoEMLP(nn.Module):
             # non-gated experts: one pair of products per expert over its slice (the split sizes are read on the host)
             cl = counts.tolist() if isinstance(counts, torch.Tensor) else list(counts)
             outs, s0 = [], 0
+            up, down = self.up_proj, self.down_proj
+            q_up, q_down = getattr(up, "_rlb_qat", None), getattr(down, "_rlb_qat", None)
+            if q_up is not None or q_down is not None:     # quantisation-aware training (rl_b200/policy/qat.py)
+                from rl_b200.policy.qat import QatState
+
+                if QatState.enabled:
+                    if q_up is not None:
+                        xs, up = q_up.q_input(xs), q_up.q_weight(up)
+                    if q_down is not None:
+                        down = q_down.q_weight(down)
+                else:
+                    q_down = None
             for e, n in enumerate(cl):
                 if n:
-                    h = F.plain_act(torch.nn.functional.linear(xs[s0 : s0 + n], self.up_proj[e]), self.cfg.hidden_act)
-                    outs.append(torch.nn.functional.linear(h, self.down_proj[e]))
+                    h = F.plain_act(torch.nn.functional.linear(xs[s0 : s0 + n], up[e]), self.cfg.hidden_act)
+                    outs.append(torch.nn.functional.linear(h if q_down is None else q_down.q_input(h), down[e]))
                 s0 += n
             return torch.cat(outs) if outs else xs.new_zeros((0, self.down_proj.shape[1]))
         if not isinstance(counts, torch.Tensor):
@@ -126,7 +138,8 @@ class MoEMLP(nn.Module):
         c = self.cfg
         if torch.is_grad_enabled() or self.forced_routing is not None or not _L.available():
             return None
-        if c.scoring_func != "softmax" or self.shared_experts is not None or not self.gated or self.fc1_latent_proj is not None:
+        if c.scoring_func != "softmax" or self.shared_experts is not None or not self.gated or self.fc1_latent_proj is not None \
+                or getattr(self.down_proj, "_rlb_qat", None) is not None or getattr(self.gate_up_proj, "_rlb_qat", None) is not None:
             return None   # the routing kernel implements the soft-max router; other routers take the general path
         W = self.ep_size
         lock = int(getattr(self.ep, "lockstep_tokens", 0) or 0)
@@ -172,7 +185,8 @@ class MoEMLP(nn.Module):
         if self.ep_size > 1:
             from rl_b200.parallel.expert import all_to_all_tokens, fused_dispatch_experts_combine
 
-            if self.gated and self.ep.comm is not None and xs.is_cuda and xs.dtype == torch.bfloat16 and xs.shape[0] <= self.ep.comm.max_copies:
+            if self.gated and getattr(self.down_proj, "_rlb_qat", None) is None and getattr(self.gate_up_proj, "_rlb_qat", None) is None \
+                    and self.ep.comm is not None and xs.is_cuda and xs.dtype == torch.bfloat16 and xs.shape[0] <= self.ep.comm.max_copies:
                 # dispatch, grouped expert MLP and combine over peer memory: no host-side split sizes, no NCCL all-to-all
                 ys = fused_dispatch_experts_combine(xs, counts, self.ep, self.local_experts, self.gate_up_proj, self.down_proj)
             else:

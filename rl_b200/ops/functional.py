@@ -246,6 +246,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
     ``residual`` (same shape as y) is added inside the GEMM epilogue, which saves one read-modify-write pass over
     the residual stream per projection."""
+    qat = getattr(w, "_rlb_qat", None)
+    if qat is not None:      # quantisation-aware training: quantise-dequantise the operands, then the usual product
+        from rl_b200.policy.qat import QatState
+
+        if QatState.enabled:
+            x, w = qat.q_input(x), qat.q_weight(w)
     qz = getattr(w, "_rlb_q", None)
     if qz is not None and not torch.is_grad_enabled():
         from rl_b200.engine import quantized as _qz   # low-precision rollout: only inside the engine's generation phase

@@ -82,24 +82,38 @@ def grouped_linear(x_padded: torch.Tensor, w: torch.Tensor, lay: ExpertLayout) -
 
 def grouped_expert_mlp(xs: torch.Tensor, counts: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
     """``xs`` [n, d] sorted by (local) expert, ``counts`` [E] rows per expert (device tensor), ``gate_up`` [E, 2f, d],
-    ``down`` [E, d, f]. Returns the experts' outputs [n, d] in the order of ``xs``."""
+    ``down`` [E, d, f]. Returns the experts' outputs [n, d] in the order of ``xs``. Parameters that carry quantisation-aware
+    training quantizers (``rl_b200/policy/qat.py``) have them applied to their weights and to the rows entering them."""
     n, d = xs.shape
     E = gate_up.shape[0]
     if n == 0:
         return xs.new_zeros((0, d))
+    q_up, q_down = getattr(gate_up, "_rlb_qat", None), getattr(down, "_rlb_qat", None)
+    if q_up is not None or q_down is not None:
+        from rl_b200.policy.qat import QatState
+
+        if not QatState.enabled:
+            q_up = q_down = None
+    if q_up is not None:
+        xs, gate_up = q_up.q_input(xs), q_up.q_weight(gate_up)
+    if q_down is not None:
+        down = q_down.q_weight(down)
     native = use_native(xs) and xs.dtype == BF16 and d % 64 == 0 and down.shape[2] % 64 == 0
     if not native:
         outs, s = [], 0
         for e, c in enumerate(counts.tolist()):
             if c:
                 xe = xs[s : s + c]
-                outs.append(F.linear(F.swiglu(F.linear(xe, gate_up[e])), down[e]))
+                a = F.swiglu(F.linear(xe, gate_up[e]))
+                outs.append(F.linear(a if q_down is None else q_down.q_input(a), down[e]))
                 s += c
         return torch.cat(outs, 0) if outs else xs.new_zeros((0, d))
     lay = ExpertLayout(counts, n)
     xp = torch.zeros((lay.mpad, d), dtype=xs.dtype, device=xs.device).index_copy(0, lay.dest, xs)
     h = grouped_linear(xp, gate_up, lay)
     a = F.swiglu(h)
+    if q_down is not None:
+        a = q_down.q_input(a)
     y = grouped_linear(a, down, lay)
     return y.index_select(0, lay.dest)
 

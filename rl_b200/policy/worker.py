@@ -264,11 +264,82 @@ class PolicyWorker:
             self.train_top_k = int(gen_cfg["top_k"]) if gen_cfg.get("top_k") else None
             self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
         self.timers: dict[str, float] = {}
+        self.quantizers: dict = {}
+        if cfg.get("quant_cfg"):
+            self._init_quantization(cfg)
         self.draft = self.draft_opt = None
         self.draft_loss_weight = 1.0
         dcfg = cfg.get("draft") or {}
         if dcfg.get("enabled"):
             self._init_draft(dcfg, dtype, init_optimizer)
+
+    # ------------------------------------------------------------------ quantisation-aware training
+    def _init_quantization(self, cfg: dict) -> None:
+        """``policy.quant_cfg`` (a built-in recipe name or a YAML recipe, see rl_b200/policy/qat.py): the chosen linear layers
+        run through quantise-dequantise operators in training, scoring and generation. ``quant_calib_size`` > 0 calibrates the
+        input ranges at start-up on ``quant_calib_data`` (a text / jsonl file; absent: random tokens) in batches of
+        ``quant_batch_size`` sequences of ``quant_sequence_length`` tokens; without calibration input ranges are dynamic."""
+        from rl_b200.policy import qat
+
+        st = self.pstate
+        if st.tp * st.pp * st.cp > 1 or getattr(self, "sharder", None) is not None:
+            raise NotImplementedError("quantisation-aware training runs on data- / expert-parallel layouts with resident parameters")
+        self.quant_recipe = qat.resolve_quant_cfg(str(cfg["quant_cfg"]))
+        self.quantizers = qat.attach(self.model, self.quant_recipe)
+        if not self.quantizers:
+            raise ValueError(f"quant_cfg '{cfg['quant_cfg']}' enables no quantizer of this model")
+        if int(cfg.get("quant_calib_size") or 0) > 0:
+            self.calibrate_quantizers(None, int(cfg["quant_calib_size"]), int(cfg.get("quant_batch_size") or 8),
+                                      int(cfg.get("quant_sequence_length") or min(512, cfg["max_total_sequence_length"])), cfg.get("quant_calib_data"))
+
+    def calibrate_quantizers(self, data: Optional[BatchedDataDict] = None, num_samples: int = 64, batch_size: int = 8, seq_len: int = 512,
+                             calib_file: Optional[str] = None) -> int:
+        """Freezes the input quantizers' ranges from forward passes over ``data`` (or the file's texts, or random tokens)."""
+        from rl_b200.policy import qat
+
+        if data is None:
+            V = self.model_cfg.vocab_size
+            if calib_file and os.path.exists(calib_file) and self.tokenizer is not None:
+                import json as _json
+
+                rows = []
+                with open(calib_file) as f:
+                    for line in f:
+                        line = line.strip()
+                        if line:
+                            try:
+                                obj = _json.loads(line)
+                                line = obj.get("text") or obj.get("article") or obj.get("prompt") or str(obj)
+                            except ValueError:
+                                pass
+                            rows.append(self.tokenizer.encode(line)[:seq_len])
+                        if len(rows) >= num_samples:
+                            break
+                lens = torch.tensor([max(1, len(r)) for r in rows])
+                ids = torch.zeros((len(rows), int(lens.max())), dtype=torch.long)
+                for i, r in enumerate(rows):
+                    ids[i, : len(r)] = torch.tensor(r, dtype=torch.long)
+            else:
+                g = torch.Generator().manual_seed(1234 + self.rank)
+                ids = torch.randint(0, V, (num_samples, seq_len), generator=g)
+                lens = torch.full((num_samples,), seq_len)
+            data = BatchedDataDict(input_ids=ids, input_lengths=lens)
+        self.model.eval()
+
+        def passes():
+            for s0 in range(0, data.size, batch_size):
+                mb = data.slice(s0, min(data.size, s0 + batch_size))
+                yield lambda mb=mb: self._policy_logprobs(self._pack(mb)[0])
+
+        n = qat.calibrate(self.quantizers, passes(), self.dp_group if self.world > 1 else None)
+        self._weights_changed()
+        return n
+
+    def export_quantized(self, path: str) -> dict:
+        """The deployment checkpoint of the quantised policy (packed 4-bit tensors, scales, ``hf_quant_config.json``)."""
+        from rl_b200.policy import qat
+
+        return qat.export_quantized(self.model, self.quantizers, path) if self.rank == 0 else {}
 
     # ------------------------------------------------------------------ draft head (speculative decoding)
     def _init_draft(self, dcfg: dict, dtype, init_optimizer: bool) -> None:
@@ -558,11 +629,20 @@ class PolicyWorker:
             for fl, ref in pairs:
                 for p, o, n in zip(fl.params, fl.offsets, fl.numels):
                     p.data = ref[o : o + n].view(p.shape)
+            self._weights_changed()
             yield
         finally:
             for fl, _ in pairs:
                 for p, o, n in zip(fl.params, fl.offsets, fl.numels):
                     p.data = fl.flat[o : o + n].view(p.shape)
+            self._weights_changed()
+
+    def _weights_changed(self) -> None:
+        """Derived copies of the weights (quantised forms) are stale."""
+        if getattr(self, "quantizers", None):
+            from rl_b200.policy.qat import QatState
+
+            QatState.weights_changed()
 
     # ------------------------------------------------------------------ micro-batching
     def _microbatches(self, data: BatchedDataDict, mbs: int, token_budget: Optional[int]):
@@ -801,6 +881,7 @@ class PolicyWorker:
                     draft_gn = self._draft_step(self.cfg.get("max_grad_norm"))
                     if all_mb_metrics:
                         all_mb_metrics[-1]["draft_grad_norm"] = draft_gn
+                self._weights_changed()
                 if getattr(self, "fp8_training", False):
                     _Fn_fp8.weights_changed()   # cached MXFP8 copies of the weights are stale now
             if self.world > 1:
@@ -892,6 +973,10 @@ class PolicyWorker:
             save_optimizer_shard(self, optimizer_path, model_save_format)
         if tokenizer_path and self.tokenizer is not None and self.rank == 0:
             self.tokenizer.save_pretrained(tokenizer_path)
+        if self.quantizers and self.rank == 0:      # calibrated input ranges travel with the weights
+            from rl_b200.policy import qat
+
+            torch.save(qat.state_dict(self.quantizers), os.path.join(os.path.dirname(os.path.abspath(weights_path)), "quantizers.pt"))
         if self.draft is not None and self.rank == 0:      # the draft head, in the EAGLE-3 checkpoint layout, beside the weights
             self.draft.save_pretrained(os.path.join(os.path.dirname(os.path.abspath(weights_path)), "draft"))
         if self.world > 1:
@@ -903,6 +988,15 @@ class PolicyWorker:
         load_weights(self, weights_path)
         if optimizer_path and self.optimizer is not None and os.path.exists(optimizer_path):
             load_optimizer_shard(self, optimizer_path)
+        self._weights_changed()
+        qpath = os.path.join(os.path.dirname(os.path.abspath(weights_path)), "quantizers.pt")
+        if self.quantizers and os.path.exists(qpath):
+            from rl_b200.policy import qat
+
+            qat.load_state_dict(self.quantizers, torch.load(qpath))
+            for q in self.quantizers.values():
+                if q.input_amax is not None:
+                    q.input_amax = q.input_amax.to(self.device)
         dpath = os.path.join(os.path.dirname(os.path.abspath(weights_path)), "draft")
         if self.draft is not None and os.path.exists(os.path.join(dpath, "model.safetensors")):
             self.draft.load_pretrained(dpath)

@@ -177,3 +177,30 @@ def test_native_nvfp4_kernels_match_the_pytorch_statement(dtype, monkeypatch):
     assert torch.equal(packed, rp) and torch.equal(sb.view(torch.uint8), rsb.view(torch.uint8)) and float(s2) == float(rs2)
     assert torch.equal(N.dequantize_nvfp4(packed, sb, s2, dtype), got[0])
     assert L.check_status() == 0
+
+
+def test_export_script_from_a_checkpoint(tmp_path):
+    import sys
+
+    from rl_b200.models.hf_io import save_pretrained
+    from rl_b200.models.transformer import build_model
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    from examples.converters import export_quantized_to_hf as ex
+
+    m = build_model(preset("tiny-llama-oracle", torch_dtype="float32"), dtype=torch.float32, seed=2)
+    save_pretrained(m, str(tmp_path / "w"))
+    meta = ex.main(["--ckpt", str(tmp_path / "w"), "--quant-cfg", f"{root}/examples/configs/quant/nvfp4_a16_mlp_only.yaml", "--out", str(tmp_path / "q"),
+                    "--device", "cpu"])
+    assert meta["quantization"]["quant_algo"] == "W4A16_NVFP4"
+    from safetensors.torch import load_file
+
+    from rl_b200.ops.nvfp4 import dequantize_nvfp4, fake_quant
+
+    sd = load_file(str(tmp_path / "q" / "model.safetensors"))
+    w = dict(m.named_parameters())["layers.1.mlp.down_proj"].detach()
+    got = dequantize_nvfp4(sd["model.layers.1.mlp.down_proj.weight"], sd["model.layers.1.mlp.down_proj.weight_scale"],
+                           sd["model.layers.1.mlp.down_proj.weight_scale_2"])
+    assert torch.equal(got, fake_quant(w)) and "model.layers.1.mlp.down_proj.input_scale" not in sd
+    assert sd["model.layers.1.self_attn.q_proj.weight"].dtype == torch.float32

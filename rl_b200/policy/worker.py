@@ -972,7 +972,15 @@ class PolicyWorker:
         if optimizer_path and self.optimizer is not None:
             save_optimizer_shard(self, optimizer_path, model_save_format)
         if tokenizer_path and self.tokenizer is not None and self.rank == 0:
-            self.tokenizer.save_pretrained(tokenizer_path)
+            if hasattr(self.tokenizer, "save_pretrained"):
+                self.tokenizer.save_pretrained(tokenizer_path)
+            else:      # the built-in byte-level tokenizers have no files: record which one it was
+                import json as _json
+
+                os.makedirs(tokenizer_path, exist_ok=True)
+                with open(os.path.join(tokenizer_path, "tokenizer_config.json"), "w") as f:
+                    _json.dump({"tokenizer_class": type(self.tokenizer).__name__, "name": getattr(self.tokenizer, "name_or_path", None),
+                                "vocab_size": len(self.tokenizer)}, f)
         if self.quantizers and self.rank == 0:      # calibrated input ranges travel with the weights
             from rl_b200.policy import qat
 

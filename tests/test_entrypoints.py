@@ -108,6 +108,18 @@ def test_run_grpo_with_a_hybrid_state_space_model(capsys, tmp_path):
     assert err and all(e < 1.05 for e in err)      # engine and trainer agree on the sampled tokens' probabilities
 
 
+def test_run_grpo_from_a_single_controller_over_worker_processes(capfd, tmp_path):
+    """One controller process, two policy workers behind the worker-group facade, the ordinary GRPO loop on top."""
+    from examples import run_grpo_controller
+
+    run_grpo_controller.main(["--config", f"{ROOT}/examples/configs/grpo_arithmetic_offline.yaml", "grpo.max_num_steps=2", "cluster.gpus_per_node=2",
+                              "+cluster.backend=gloo", f"logger.log_dir={tmp_path}/logs", f"checkpointing.checkpoint_dir={tmp_path}/ckpt",
+                              "checkpointing.save_period=2", "checkpointing.enabled=true"])
+    out = capfd.readouterr().out
+    assert "[grpo] step 2:" in out
+    assert os.path.exists(f"{tmp_path}/ckpt/step_2/policy/weights/config.json")
+
+
 def test_run_sft_dpo_rm_eval(capsys):
     from examples import run_dpo, run_eval, run_rm, run_sft
 

@@ -123,7 +123,7 @@ TOKENIZER = dict(use_fastokens=F(bool), name=F(str), chat_template=F(str), chat_
 
 PARALLEL = dict(tensor_parallel_size=F(int, nullable=False), pipeline_parallel_size=F(int), context_parallel_size=F(int),
                 expert_parallel_size=F(int), sequence_parallel=F(bool), virtual_pipeline_stages=F(int),
-                data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int))
+                data_parallel_replicate_size=F(int), data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int))
 
 LORA = dict(enabled=F(bool), dim=F(int), alpha=F(int, float), dropout=F(float, int), target_modules=F(list), exclude_modules=F(list),
             match_all_linear=F(bool), dropout_position=F(str), lora_A_init=F(str), use_triton=F(bool), rank=F(int),
@@ -135,7 +135,7 @@ FP8 = dict(enabled=F(bool), fp8=F(str, choices=("e4m3", "hybrid")), fp8_recipe=F
 DTENSOR = dict(enabled=F(bool), _v2=F(bool), cpu_offload=F(bool), sequence_parallel=F(bool), activation_checkpointing=F(bool),
                tensor_parallel_size=F(int), context_parallel_size=F(int), expert_parallel_size=F(int), custom_parallel_plan=F(str),
                clear_cache_every_n_steps=F(int), lora_cfg=F(dict, sub=LORA), env_vars=F(dict), automodel_kwargs=F(dict),
-               data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int), defer_fsdp_grad_sync=F(bool),
+               data_parallel_sharding=F(str, choices=("optimizer", "full")), hsdp_replicas=F(int), dp_replicate_size=F(int), defer_fsdp_grad_sync=F(bool),
                moe_parallelizer=F(dict), fp8_cfg=F(dict, sub=FP8))
 
 MEGATRON = dict(enabled=F(bool), tensor_model_parallel_size=F(int), pipeline_model_parallel_size=F(int), context_parallel_size=F(int),

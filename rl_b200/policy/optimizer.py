@@ -36,11 +36,16 @@ def _world(group) -> tuple[int, int]:
 class ShardedAdamW:
     def __init__(self, flat: FlatParams, *, lr: float = 1e-5, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, group=None,
-                 master_format: str = "split16", fused_comm: Optional[Any] = None):
+                 master_format: str = "split16", fused_comm: Optional[Any] = None, replicate_group=None):
         """``master_format``: ``split16`` keeps bf16 + 16 low bits (exact fp32 master at 4 B/param), ``fp32`` keeps a
-        separate fp32 master shard (CPU / fp32 models use this)."""
+        separate fp32 master shard (CPU / fp32 models use this). ``replicate_group`` (hybrid sharding): ``group`` is then one
+        SHARD group (e.g. the GPUs of a node) over which the optimizer state is cut, and ``replicate_group`` holds the ranks
+        of the other shard groups that own the same slice: gradients are reduce-scattered inside the shard group and the
+        slices all-reduced across it, so only one slice per rank crosses the slower links between shard groups."""
         self.flat = flat
         self.group = group
+        self.replicate_group = replicate_group
+        self.replicas_of_shard = dist.get_world_size(replicate_group) if replicate_group is not None else 1
         self.rank, self.world = _world(group)
         assert flat.padded % self.world == 0, "flat parameter buffer must split evenly over optimizer shards"
         self.shard_numel = flat.padded // self.world
@@ -95,14 +100,18 @@ class ShardedAdamW:
     def _reduce_scatter(self) -> torch.Tensor:
         g = self.flat.grad
         if self.world == 1:
+            if self.replicas_of_shard > 1:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.replicate_group)
             return g
         mine = g[self.lo : self.hi]
         if g.is_cuda:
             # in place: NCCL reduces into this rank's own slice of the buffer (recvbuff == sendbuff + rank * count), so no
             # shard-sized temporary is needed (16 GB for a 32B model at TP4 x DP2)
             dist.reduce_scatter_tensor(mine, g, op=dist.ReduceOp.SUM, group=self.group)
-            return mine
-        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce-scatter
+        else:
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)  # gloo has no reduce-scatter
+        if self.replicas_of_shard > 1:      # hybrid sharding: the same slice of every shard group
+            dist.all_reduce(mine, op=dist.ReduceOp.SUM, group=self.replicate_group)
         return mine
 
     def _all_gather(self) -> None:
@@ -206,7 +215,7 @@ class ShardedAdamW:
 
 
 # ---------------------------------------------------------------------- config glue
-def build_optimizer(flat: FlatParams, policy_cfg: dict, group=None, fused_comm=None) -> ShardedAdamW:
+def build_optimizer(flat: FlatParams, policy_cfg: dict, group=None, fused_comm=None, replicate_group=None) -> ShardedAdamW:
     """Reads ``policy.optimizer = {name: <dotted class path>, kwargs: {...}}``. Adam / AdamW (any module path) map to
     the sharded fused implementation."""
     ocfg = policy_cfg.get("optimizer") or {}
@@ -219,7 +228,7 @@ def build_optimizer(flat: FlatParams, policy_cfg: dict, group=None, fused_comm=N
     return ShardedAdamW(flat, lr=float(kw.get("lr", 1e-5)), betas=tuple(kw.get("betas", (0.9, 0.999))),
                         eps=float(kw.get("eps", 1e-8)), weight_decay=float(wd),
                         max_grad_norm=policy_cfg.get("max_grad_norm"), group=group, fused_comm=fused_comm,
-                        master_format=policy_cfg.get("master_weight_format", "split16"))
+                        master_format=policy_cfg.get("master_weight_format", "split16"), replicate_group=replicate_group)
 
 
 class LRSchedule:

@@ -161,9 +161,30 @@ class PolicyWorker:
         else:
             self.model = build_model(model_cfg, device=self.device, dtype=dtype, seed=seed, activation_checkpointing=act_ckpt,
                                      lora=self.lora_cfg, **mp)
+        # Hybrid sharding (HSDP; ``dtensor_cfg.dp_replicate_size`` / ``parallel.data_parallel_replicate_size`` = R): the
+        # data-parallel ranks form R shard groups of dp / R consecutive ranks (a node each); optimizer state is cut inside a
+        # shard group and gradient slices are all-reduced across the groups (nemo_rl/models/automodel/setup.py:464-509).
+        par_h, dt_h = cfg.get("parallel") or {}, cfg.get("dtensor_cfg") or {}
+        rep = int(par_h.get("data_parallel_replicate_size") or par_h.get("hsdp_replicas") or dt_h.get("dp_replicate_size") or dt_h.get("hsdp_replicas") or 1)
+        self.shard_group, self.replicate_group = dp_group, None
+        if rep > 1 and self.world > 1:
+            if st.tp * st.pp * st.cp * st.ep > 1:
+                raise NotImplementedError("hybrid sharding is available for plain data-parallel layouts")
+            if self.world % rep:
+                raise ValueError(f"dp_replicate_size {rep} must divide the data-parallel size {self.world}")
+            ranks = dist.get_process_group_ranks(dp_group) if dp_group is not None else list(range(dist.get_world_size()))
+            S = self.world // rep
+            for r0 in range(0, self.world, S):          # collective: every rank creates every group, in the same order
+                grp = dist.new_group(ranks=ranks[r0 : r0 + S]) if S > 1 else "self"
+                if r0 <= self.rank < r0 + S:
+                    self.shard_group = grp
+            for j in range(S):
+                grp = dist.new_group(ranks=ranks[j::S])
+                if self.rank % S == j:
+                    self.replicate_group = grp
         # On several GPUs of one node the flat parameter / gradient buffers live in peer-mapped memory so that the
         # optimizer step can run as one fused kernel over NVLink (rl_b200/csrc/comm.cu); NCCL is the fallback.
-        model_parallel = st.tp * st.pp * st.cp * st.ep > 1
+        model_parallel = st.tp * st.pp * st.cp * st.ep > 1 or self.replicate_group is not None
         if fused_comm is None and self.world > 1 and self.device.type == "cuda" and cfg.get("fused_optimizer", True) \
                 and dtype == torch.bfloat16 and init_optimizer and not model_parallel and self.lora_cfg is None:
             try:
@@ -239,8 +260,9 @@ class PolicyWorker:
         if init_optimizer:
             gdt = _precision(cfg.get("grad_dtype", "float32")) if dtype == torch.bfloat16 else torch.float32
             self.flat.attach_grad_buffer(gdt, allocator=fused_comm.alloc_grads if (fused_comm is not None and gdt == torch.float32) else None)
-            self.optimizer = build_optimizer(self.flat, cfg, group=dp_group if self.world > 1 or st.world == 1 else "self",
-                                             fused_comm=fused_comm)
+            self.optimizer = build_optimizer(self.flat, cfg, group=(self.shard_group if self.replicate_group is not None else dp_group)
+                                             if self.world > 1 or st.world == 1 else "self", fused_comm=fused_comm,
+                                             replicate_group=self.replicate_group)
             if self.flat_e is not None:
                 self.flat_e.attach_grad_buffer(gdt)
                 self.optimizer_e = build_optimizer(self.flat_e, cfg, group=e_group if (e_world > 1 and e_group != "self") else "self")

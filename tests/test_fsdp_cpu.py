@@ -98,3 +98,31 @@ def test_fully_sharded_matches_resident_parameters(tmp_path, world, name):
         assert not torch.allclose(a["lp0"], a["lp2"], atol=1e-4)
         assert a["gen"] == b["gen"]                                     # the engine serves the trained weights
         assert torch.allclose(b["lp_reload"], b["lp2"], atol=1e-6)      # HF save -> load into a fresh sharded worker
+
+
+def _hsdp_run(rank, world, rep):
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+    from rl_b200.models.config import preset
+    from rl_b200.policy.worker import PolicyWorker
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    cfg = _cfg(False)
+    cfg["parallel"] = dict(data_parallel_replicate_size=rep)
+    w = PolicyWorker(cfg, model_cfg=mc, device="cpu", init_reference_model=False, seed=5)
+    data = _data(world, rank)
+    res = [w.train(data, NLLLossFn(), gbs=8, mbs=2) for _ in range(2)]
+    shard = w.optimizer.shard_numel * (world if rep == 1 else world // rep)
+    return dict(loss=[float(r["loss"][0]) for r in res], gn=[float(r["grad_norm"][0]) for r in res], lp=w.get_logprobs(data)["logprobs"].tolist(),
+                opt_world=w.optimizer.world, replicas=w.optimizer.replicas_of_shard, covered=shard == w.flat.padded)
+
+
+@pytest.mark.parametrize("rep", [2, 4])
+def test_hybrid_sharding_matches_fully_sharded_optimizer_state(rep):
+    """Optimizer state cut inside shard groups of dp / R ranks and replicated over R groups (R = 4: plain replication) takes
+    the steps that sharding over all ranks takes."""
+    base = _spawn(_hsdp_run, 4, 1)
+    hs = _spawn(_hsdp_run, 4, rep)
+    for r in range(4):
+        assert hs[r]["opt_world"] == 4 // rep and hs[r]["replicas"] == rep and hs[r]["covered"] and base[r]["opt_world"] == 4
+        assert hs[r]["loss"] == pytest.approx(base[r]["loss"], rel=1e-5) and hs[r]["gn"] == pytest.approx(base[r]["gn"], rel=1e-4)
+        assert torch.allclose(torch.tensor(hs[r]["lp"]), torch.tensor(base[r]["lp"]), atol=2e-5)

@@ -115,3 +115,77 @@ def test_local_dataset_rows_of_the_registry(tmp_path):
     for name, row in HF_SETS.items():
         get_processor(row[5])     # every row names a registered processor
     assert {"OpenR1-Math-220k", "geometry3k", "refcoco", "avqa", "MMAU", "nemogym", "BinaryPreferenceDataset"} <= set(HF_SETS)
+
+
+def test_message_log_decompose_and_reconstruct_round_trip():
+    from rl_b200.data.llm_message_utils import (attach_message_log_view, batched_message_log_to_flat_message, decompose_message_log,
+                                                get_first_index_that_differs, message_log_shape, pad_tensor, remap_dataset_keys,
+                                                validate_tensor_consistency)
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+    logs = [[{"role": "user", "content": "hi", "token_ids": torch.tensor([1, 2, 3])},
+             {"role": "assistant", "content": "yo", "token_ids": torch.tensor([4, 5]), "generation_logprobs": torch.tensor([-0.1, -0.2])},
+             {"role": "environment", "content": "ok", "token_ids": torch.tensor([6])},
+             {"role": "assistant", "content": "bye", "token_ids": torch.tensor([7, 8, 9]), "generation_logprobs": torch.tensor([-0.3, -0.4, -0.5])}],
+            [{"role": "system", "content": "no tokens"},
+             {"role": "user", "content": "q", "token_ids": torch.tensor([10])},
+             {"role": "assistant", "content": "a", "token_ids": torch.tensor([11, 12]), "generation_logprobs": torch.tensor([-1.0, -2.0])}]]
+    assert message_log_shape(logs[0])[1] == {"token_ids": torch.Size([2]), "generation_logprobs": torch.Size([2])}
+    d = decompose_message_log(logs)
+    assert d["turn_lengths"].tolist() == [[3, 2, 1, 3], [0, 1, 2, 0]] and d["response_token_lengths"].tolist() == [2, 2]
+    assert d["turn_roles"][1] == ["system", "user", "assistant"]
+    for log in logs:
+        for m in log:
+            if "token_ids" in m and "generation_logprobs" not in m:
+                m["generation_logprobs"] = torch.zeros(m["token_ids"].numel())
+    flat, lens = batched_message_log_to_flat_message([[m for m in log if "token_ids" in m] for log in logs], {"token_ids": 0})
+    batch = BatchedDataDict(input_ids=flat["token_ids"], generation_logprobs=flat["generation_logprobs"], **{k: d[k] for k in
+                                                                                                           ("turn_lengths", "turn_roles", "turn_contents")})
+    attach_message_log_view(batch)
+    back = batch["message_log"]
+    assert [m["role"] for m in back[1]] == ["system", "user", "assistant"] and "token_ids" not in back[1][0]
+    assert back[0][3]["token_ids"].tolist() == [7, 8, 9] and back[0][3]["generation_logprobs"].tolist() == pytest.approx([-0.3, -0.4, -0.5])
+    assert "generation_logprobs" not in back[0][2]
+    assert back[0][1]["token_ids"].data_ptr() == batch["input_ids"][0, 3:].data_ptr()       # a view, not a copy
+    assert get_first_index_that_differs("abcX", "abcY") == 3 and get_first_index_that_differs("ab", "abc") == 2
+    assert pad_tensor(torch.tensor([1, 2]), 4, "left", 9).tolist() == [9, 9, 1, 2] and pad_tensor(torch.tensor([1, 2]), 1).tolist() == [1, 2]
+    with pytest.raises(ValueError):
+        validate_tensor_consistency([torch.zeros(2, dtype=torch.long), torch.zeros(2)])
+    assert remap_dataset_keys([{"q": 1, "a": 2, "z": 3}], {"q": "input", "a": "output"}) == [{"z": 3, "input": 1, "output": 2}]
+
+
+def test_formatted_message_log_applies_task_prompts_and_generation_headers():
+    from rl_b200.data.interfaces import TaskDataSpec
+    from rl_b200.data.llm_message_utils import get_formatted_message_log
+    from rl_b200.data.tokenizers import ByteTokenizer
+
+    tok = ByteTokenizer()
+    spec = TaskDataSpec(task_name="t", prompt="Solve: {}", system_prompt="Be brief.")
+    log = get_formatted_message_log([{"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"}, {"role": "user", "content": "3+3?"}],
+                                    tok, spec, add_eos_token=False, add_generation_prompt=True)
+    text = "".join(tok.decode(m["token_ids"]) for m in log)
+    assert [m["role"] for m in log] == ["system", "user", "assistant", "user"]
+    assert text == "<bos><|system|>Be brief.<|end|><|user|>Solve: 2+2?<|end|><|assistant|>4<|end|><|user|>3+3?<|end|><|assistant|>"
+    # the assistant header rendered after the first user message belongs to that message; the assistant turn owns only its text
+    assert tok.decode(log[1]["token_ids"]).endswith("<|assistant|>") and tok.decode(log[2]["token_ids"]) == "4<|end|>"
+    # multimodal content: text parts are replaced by the rendered chunk, other parts stay
+    mm = get_formatted_message_log([{"role": "user", "content": [{"type": "text", "text": "what is this?"}, {"type": "image", "image": "x.png"}]}],
+                                   _ListContentTokenizer(), None)
+    assert mm[0]["content"][1] == {"type": "image", "image": "x.png"} and "what is this?" in mm[0]["content"][0]["text"]
+
+
+class _ListContentTokenizer:
+    """A byte tokenizer whose template accepts typed content lists (what multimodal processors do)."""
+
+    def __init__(self):
+        from rl_b200.data.tokenizers import ByteTokenizer
+
+        self.t = ByteTokenizer()
+        self.bos_token, self.eos_token = self.t.bos_token, self.t.eos_token
+
+    def apply_chat_template(self, msgs, **kw):
+        flat = [dict(m, content="".join(p.get("text", "<image>") for p in m["content"]) if isinstance(m["content"], list) else m["content"]) for m in msgs]
+        return self.t.apply_chat_template(flat, **kw)
+
+    def __call__(self, *a, **k):
+        return self.t(*a, **k)

@@ -100,6 +100,9 @@ class PolicyWorker:
         cfg = dict(POLICY_DEFAULTS)
         cfg.update(policy_cfg or {})
         self.cfg = cfg
+        self.draft = self.draft_opt = None          # policy.draft / policy.quant_cfg: set up at the end of construction
+        self.draft_loss_weight = 1.0
+        self.quantizers: dict = {}
         st = ensure_parallel(cfg)
         self.pstate = st
         if st.world > 1 and st.tp * st.pp * st.cp > 1 and dp_group is None:
@@ -208,6 +211,8 @@ class PolicyWorker:
         par_cfg = cfg.get("parallel") or {}
         self.full_sharding = (par_cfg.get("data_parallel_sharding") or dtc.get("data_parallel_sharding") or "optimizer") == "full"
         if self.full_sharding:
+            if cfg.get("quant_cfg") or (cfg.get("draft") or {}).get("enabled"):
+                raise NotImplementedError("quantisation-aware training and draft heads need resident parameters (data_parallel_sharding: optimizer)")
             return self._init_fully_sharded(cfg, st, dp_group, dtype, init_optimizer, init_reference_model)
         self.sharder = None
         self.fused_comm = fused_comm
@@ -286,11 +291,8 @@ class PolicyWorker:
             self.train_top_k = int(gen_cfg["top_k"]) if gen_cfg.get("top_k") else None
             self.train_top_p = float(gen_cfg.get("top_p") or 1.0)
         self.timers: dict[str, float] = {}
-        self.quantizers: dict = {}
         if cfg.get("quant_cfg"):
             self._init_quantization(cfg)
-        self.draft = self.draft_opt = None
-        self.draft_loss_weight = 1.0
         dcfg = cfg.get("draft") or {}
         if dcfg.get("enabled"):
             self._init_draft(dcfg, dtype, init_optimizer)

@@ -243,10 +243,19 @@ def build_train_data(batch: BatchedDataDict, pad_token_id: int, make_divisible_b
                 m["token_loss_mask"] = torch.zeros(n, dtype=torch.long)
                 m["generation_logprobs"] = torch.zeros(n, dtype=torch.float32)
     flat, lengths = batched_message_log_to_flat_message(batch["message_log"], {"token_ids": pad_token_id}, make_divisible_by)
+    extra = {}
+    traces = batch.get("routed_experts")
+    if traces is not None and len(traces) and all(t is not None for t in traces):
+        # the engine's routing decisions per position (rollout routing replay): aligned with input_ids, -1 where unknown
+        S = flat["token_ids"].shape[1]
+        re = torch.full((len(traces), S) + tuple(traces[0].shape[1:]), -1, dtype=torch.int16)
+        for i, t in enumerate(traces):
+            re[i, : min(S, t.shape[0])] = t[:S]
+        extra["routed_experts"] = re
     return BatchedDataDict(
         input_ids=flat["token_ids"], input_lengths=lengths, token_mask=flat["token_loss_mask"].float(),
         sample_mask=batch["loss_multiplier"].float().clone(), generation_logprobs=flat["generation_logprobs"].float(),
-        **multimodal_fields(flat),
+        **multimodal_fields(flat), **extra,
     )
 
 

@@ -349,6 +349,7 @@ class _Request:
     share_with: int = -1
     uid: int = 0  # keys the request's random stream: same uid and seed -> same draws on any rank / batch
     mm: object = None  # (image patch rows, patches per image) of a vision-language prompt
+    routed_experts: object = None  # [prompt + generated tokens, MoE layers, top-k] int16 expert ids (-1: position never ran)
 
 
 class GenerationEngine:
@@ -397,6 +398,11 @@ class GenerationEngine:
                 raise NotImplementedError("the generation engine serves hybrid state-space models on one GPU per replica")
             if self.quantization:
                 raise NotImplementedError("quantised rollout is not available for hybrid state-space models")
+        # rollout routing replay: when switched on (``record_routing``), every MoE layer reports the experts it chose and the
+        # engine files them by request and position; decode then runs eagerly with a host visit per step
+        self.record_routing = False
+        self._r3_meta = None
+        self._r3_buf: list = []
         self.mamba_conv: Optional[list] = None
         self.mamba_ssm: Optional[list] = None
         self._state_row: dict[int, int] = {}
@@ -507,6 +513,47 @@ class GenerationEngine:
         c = self.cfg
         return 2 * len(self._attn_layers) * self.num_blocks * self.hkv * self.block_size * c.head_dim * self.model.dtype.itemsize if hasattr(self.model.dtype, "itemsize") else 0
 
+    # ------------------------------------------------------------------ routed-expert recording (rollout routing replay)
+    def set_record_routing(self, on: bool) -> None:
+        moe = [l.mlp for l in self.model.layers if getattr(l, "mlp", None) is not None and hasattr(l.mlp, "routing_sink")]
+        self.record_routing = bool(on) and bool(moe)
+        for j, m in enumerate(moe):
+            m._r3_layer = j
+            m.routing_sink = self._r3_sink if self.record_routing else None
+        self._r3_layers = len(moe)
+
+    def _r3_sink(self, moe, idx) -> None:
+        meta = self._r3_meta
+        if meta is None:
+            return
+        n = meta[0].numel()
+        self._r3_buf.append((moe._r3_layer, meta[0], meta[1], idx[:n].to(torch.int16)))
+
+    def _r3_rows(self, sids, positions) -> None:
+        """Declares which (request, position) every row of the next forward pass is."""
+        if self.record_routing:
+            self._r3_meta = (torch.as_tensor(sids, dtype=torch.int64), torch.as_tensor(positions, dtype=torch.int64).cpu())
+
+    def _r3_assemble(self, reqs: dict) -> None:
+        buf, self._r3_buf, self._r3_meta = self._r3_buf, [], None
+        if not buf:
+            return
+        k = buf[0][3].shape[1]
+        start, total = {}, 0
+        for sid, r in reqs.items():
+            start[sid] = total
+            total += len(r.prompt) + len(r.out_tokens)
+        big = torch.full((total, self._r3_layers, k), -1, dtype=torch.int16)
+        base = torch.zeros(max(reqs) + 1, dtype=torch.int64)
+        size = torch.zeros(max(reqs) + 1, dtype=torch.int64)
+        for sid, r in reqs.items():
+            base[sid], size[sid] = start[sid], len(r.prompt) + len(r.out_tokens)
+        for layer, sids, pos, idx in buf:      # in issue order: a re-prefilled (preempted) sequence overwrites its rows
+            ok = pos < size[sids]
+            big[(base[sids] + pos)[ok], layer] = idx.cpu()[ok]
+        for sid, r in reqs.items():
+            r.routed_experts = big[start[sid] : start[sid] + len(r.prompt) + len(r.out_tokens)]
+
     # ------------------------------------------------------------------ hybrid state-space models
     def _claim_state_rows(self, live) -> None:
         """Keeps one state row per sequence that is scheduled this iteration and returns the rows of sequences that are not
@@ -584,6 +631,7 @@ class GenerationEngine:
 
     @torch.no_grad()
     def _dummy_forward(self, decode: bool) -> None:
+        self._r3_meta = None
         """One forward pass over a single padding token (slot -1: nothing is written to the KV cache)."""
         dev = self.device
         idt = torch.int32 if self.native else torch.int64
@@ -825,7 +873,7 @@ class GenerationEngine:
         # the per-call seed is not part of the key: it reaches the sampler through the row keys (device memory), so one
         # captured graph serves every generate call with the same sampling parameters
         key = (B, num_splits, sp.temperature, sp.top_k or 0, sp.top_p, sp.greedy, self._n_stop)
-        use_graphs = self.use_graphs
+        use_graphs = self.use_graphs and not self.record_routing
         ep = getattr(self.model, "ep", None)
         if c.is_moe:
             # the few-token MoE layer needs every expert-parallel rank to run the same batch size (the generate loop agreed
@@ -904,6 +952,7 @@ class GenerationEngine:
         mms = [reqs[sid].mm for sid, _, _ in items if getattr(reqs[sid], "mm", None) is not None]
         if mms:
             batch.mm = dict(patches=_L.to_device(torch.cat([m[0] for m in mms]), dev), sizes=[int(x) for m in mms for x in m[1]])
+        self._r3_rows([sid for (sid, _, _), L in zip(items, lens) for _ in range(L)], pos)
         rows = None
         if self.hybrid:   # whole prompts: the states start from zero
             rows = torch.tensor([self._state_row[sid] for sid, _, _ in items], dtype=torch.int64, device=dev)
@@ -960,6 +1009,7 @@ class GenerationEngine:
             full_lens.append(p + n)
             last.append(len(toks) - 1)
         ids = _L.to_device(torch.tensor(toks, dtype=idt), dev)
+        self._r3_rows([sid for sid, _, _, n in round_items for _ in range(n)], torch.cat(pos))
         positions = torch.cat(pos).to(dev)
         slots = torch.cat(new_slots).to(dev)
         new_rows = torch.cat(new_idx).to(dev)
@@ -1045,6 +1095,9 @@ class GenerationEngine:
             hb["block_table"][n:B] = 0
         if steps is None:
             steps = self._window_steps(decode, reqs)
+        if self.record_routing:
+            steps = 1
+            self._r3_rows(list(decode), hb["positions"][:n].clone()) if n else self._r3_rows([], [])
         st["blob"].copy_(st["host_blob"], non_blocking=True)   # all inputs of the window in one upload
         _L.Counters.h2d_bytes += st["host_blob"].numel()
         self._step_counter += steps
@@ -1122,7 +1175,7 @@ class GenerationEngine:
             mm = mm_inputs[i] if mm_inputs is not None else None
             if mm is not None and mm[0] is None:
                 mm = None
-            if share_prefixes and not self.hybrid:   # (pages of a shared prompt carry no state-space state)
+            if share_prefixes and not self.hybrid and not self.record_routing:   # (shared pages carry no state / no routing record)
                 key = tuple(p)
                 if mm is not None:   # equal prompts share their prefix only if they show the same images
                     from rl_b200.data.multimodal_utils import content_key
@@ -1136,7 +1189,7 @@ class GenerationEngine:
             reqs[i].mm = mm
             if self.sched.add(i, len(p), mx, share) != 0:
                 raise ValueError(f"request {i} (prompt {len(p)} + {mx} new tokens) can never fit the KV cache")
-            if self.prefix_caching and mm is None:
+            if self.prefix_caching and mm is None and not self.record_routing:
                 self.sched.set_hashes(i, self._block_hashes(p))
         dev = self.device
         st = self._static_buffers()
@@ -1212,6 +1265,7 @@ class GenerationEngine:
                         hb["state_rows"][j] = self._state_row[sid]
                 st["blob"].copy_(st["host_blob"], non_blocking=True)
                 self._step_counter += 1
+                self._r3_rows(list(decode), hb["positions"][:n].clone())
                 tok, lp = self._run_decode(n, sp, max_ctx)
                 tok_h, lp_h = _L.to_host(tok).tolist(), _L.to_host(lp).tolist()
                 fin = [1 if t in stop else 0 for t in tok_h]
@@ -1233,7 +1287,7 @@ class GenerationEngine:
                     items = []
                     for sid in prefill:
                         r = reqs[sid]
-                        cached = self.sched.cached_prefix(sid) if self.prefix_caching else 0
+                        cached = self.sched.cached_prefix(sid) if (self.prefix_caching and not self.record_routing) else 0
                         items.append((sid, r.prompt + r.out_tokens, cached))
                     has_mm = any(getattr(reqs[sid], "mm", None) is not None for sid in prefill)
                     cap = max(1, self.max_prefill_tokens)
@@ -1277,4 +1331,6 @@ class GenerationEngine:
                 self.stats["prefill_s"] += time.perf_counter() - t0
         if self.native:   # every token download above synchronised the stream
             _L.raise_on_status("GenerationEngine.generate", self.device)
+        if self.record_routing:
+            self._r3_assemble(reqs)
         return [reqs[i] for i in range(len(prompts))]

@@ -176,8 +176,16 @@ class NativeGeneration:
             out_ids[i, P : P + G] = torch.tensor(r.out_tokens, dtype=torch.long)
             logprobs[i, P : P + G] = torch.tensor(r.out_logprobs, dtype=torch.float32)
             gen_lens[i], tot_lens[i], trunc[i] = G, P + G, r.truncated
-        return BatchedDataDict({"output_ids": out_ids, "generation_lengths": gen_lens,
-                                "unpadded_sequence_lengths": tot_lens, "logprobs": logprobs, "truncated": trunc})
+        out = BatchedDataDict({"output_ids": out_ids, "generation_lengths": gen_lens,
+                               "unpadded_sequence_lengths": tot_lens, "logprobs": logprobs, "truncated": trunc})
+        traces = [getattr(r, "routed_experts", None) for r in recs]
+        if traces and all(t is not None for t in traces):
+            # rollout routing replay: expert ids per position and MoE layer, -1 where a position was never run (the last token)
+            re = torch.full((B, out_len) + tuple(traces[0].shape[1:]), -1, dtype=torch.int16)
+            for i, t in enumerate(traces):
+                re[i, : t.shape[0]] = t
+            out["routed_experts"] = re
+        return out
 
     def _apply_stop_strings(self, recs, stop_strings) -> None:
         """Cuts each response at the first token whose decoded prefix contains a stop string."""

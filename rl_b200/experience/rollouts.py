@@ -87,6 +87,7 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
     answers: list[Any] = [None] * n
     stop_strings = batch.get("stop_strings")
     gen_metrics_acc: dict[str, float] = {"total_generated_tokens": 0}
+    routed = None
     for turn in range(max_rollout_turns):
         if not active:
             break
@@ -96,6 +97,11 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
         ss = [stop_strings[i] for i in active] if stop_strings is not None else None
         sub, generated, gm, out = generate_responses(generation, flat["token_ids"], lens, sub, tokenizer, greedy, ss, multimodal_fields(flat))
         gen_metrics_acc["total_generated_tokens"] += gm["total_generated_tokens"]
+        if "routed_experts" in out:   # the latest call's record covers the whole sequence so far (earlier turns are its prompt)
+            if routed is None:
+                routed = [None] * n
+            for j, i in enumerate(active):
+                routed[i] = out["routed_experts"][j, : int(out["unpadded_sequence_lengths"][j])].clone()
         for j, i in enumerate(active):
             gen_tokens[i] += generated[j].numel()
             turns[i] += 1
@@ -133,6 +139,8 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
     batch["generation_lengths"] = gen_tokens
     if reward_components is not None:
         batch["reward_components"] = reward_components
+    if routed is not None:
+        batch["routed_experts"] = routed
     batch["length"] = torch.tensor([sum(int(m["token_ids"].numel()) for m in log) for log in batch["message_log"]], dtype=torch.long)
     metrics = {
         "total_turns": int(turns.sum()),

@@ -55,7 +55,8 @@ class MoEMLP(nn.Module):
             self.shared_experts = DenseMLP(cfg, dtype, device, intermediate_size=cfg.moe_shared_expert_intermediate_size
                                            or cfg.moe_intermediate_size * cfg.n_shared_experts)
         self.last_routing: Optional[torch.Tensor] = None  # top-k expert ids of the last forward (router replay / traces)
-        self.forced_routing: Optional[torch.Tensor] = None  # when set, replaces the router's choice (router replay)
+        self.forced_routing: Optional[torch.Tensor] = None  # when set, replaces the router's choice (router replay); rows of -1 keep it
+        self.routing_sink = None   # optional callable(layer, idx [T, k]) told every routing decision (the engine records them)
 
     def _route_sigmoid(self, x: torch.Tensor):
         """DeepSeek-V3 routing: sigmoid scores; experts are chosen by score + bias among the ``topk_group`` best groups (a
@@ -63,8 +64,9 @@ class MoEMLP(nn.Module):
         c = self.cfg
         E, k = c.num_experts, c.num_experts_per_tok
         scores = torch.sigmoid(x.float() @ self.router.float().t())
-        if self.forced_routing is not None:
-            idx = self.forced_routing
+        forced = self._forced_rows(x.shape[0])
+        if forced is not None and bool((forced >= 0).all()):
+            idx = forced
         else:
             choice = scores + self.e_score_correction_bias
             if c.n_group > 1:
@@ -73,12 +75,25 @@ class MoEMLP(nn.Module):
                 keep = torch.zeros_like(gs).scatter_(1, gs.topk(c.topk_group, dim=-1, sorted=False)[1], 1.0)
                 choice = choice.masked_fill(~keep.bool().unsqueeze(-1).expand_as(g).reshape(-1, E), 0.0)
             idx = choice.topk(k, dim=-1, sorted=False)[1]
+            if forced is not None:
+                idx = torch.where((forced >= 0).all(-1, keepdim=True), forced.clamp(min=0), idx)
         w = scores.gather(1, idx)
         if c.norm_topk_prob:
             w = w / (w.sum(-1, keepdim=True) + 1e-20)
         w = w * c.routed_scaling_factor
         self.last_routing = idx.detach()
+        if self.routing_sink is not None:
+            self.routing_sink(self, self.last_routing)
         return w, idx, scores
+
+    def _forced_rows(self, T: int) -> Optional[torch.Tensor]:
+        """The replayed expert ids for the T rows of this call (rows the trace does not cover are -1: the router decides)."""
+        f = self.forced_routing
+        if f is None:
+            return None
+        if f.shape[0] < T:
+            f = torch.cat([f, f.new_full((T - f.shape[0], f.shape[1]), -1)])
+        return f[:T]
 
     def route(self, x: torch.Tensor):
         c = self.cfg
@@ -86,14 +101,16 @@ class MoEMLP(nn.Module):
             return self._route_sigmoid(x)
         logits = F.linear(x, self.router).float()
         probs = torch.softmax(logits, dim=-1)
-        if self.forced_routing is not None:
-            idx = self.forced_routing
+        w, idx = torch.topk(probs, c.num_experts_per_tok, dim=-1)
+        forced = self._forced_rows(x.shape[0])
+        if forced is not None:
+            idx = torch.where((forced >= 0).all(-1, keepdim=True), forced.clamp(min=0), idx)
             w = probs.gather(-1, idx)
-        else:
-            w, idx = torch.topk(probs, c.num_experts_per_tok, dim=-1)
         if c.norm_topk_prob:
             w = w / w.sum(-1, keepdim=True)
         self.last_routing = idx.detach()
+        if self.routing_sink is not None:
+            self.routing_sink(self, self.last_routing)
         return w, idx, probs
 
     def _experts(self, xs: torch.Tensor, counts) -> torch.Tensor:
@@ -172,6 +189,8 @@ class MoEMLP(nn.Module):
             if ws is not None:
                 out, idx = ws.forward(x, residual, self.router, self.gate_up_proj, self.down_proj, bool(c.norm_topk_prob))
                 self.last_routing = idx.clone()   # the workspace's copy is overwritten by the next layer
+                if self.routing_sink is not None:
+                    self.routing_sink(self, self.last_routing)
                 return out
         w, idx, _ = self.route(x)
         flat_e = idx.reshape(-1)

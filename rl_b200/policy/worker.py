@@ -100,6 +100,10 @@ class PolicyWorker:
         cfg = dict(POLICY_DEFAULTS)
         cfg.update(policy_cfg or {})
         self.cfg = cfg
+        # rollout routing replay (``policy.router_replay.enabled``): the experts the engine chose for every position are forced
+        # in the log-prob and training passes, so trainer and engine evaluate the same sub-network
+        # (nemo_rl/models/megatron/train.py set_router_replay_forward)
+        self.router_replay = bool((cfg.get("router_replay") or {}).get("enabled"))
         self.draft = self.draft_opt = None          # policy.draft / policy.quant_cfg: set up at the end of construction
         self.draft_loss_weight = 1.0
         self.quantizers: dict = {}
@@ -550,6 +554,8 @@ class PolicyWorker:
             split_group = st.cp_group   # context-parallel ranks hold the same prompts and the same (full) weights
         self.generation = NativeGeneration(engine_model, merged, self.tokenizer, pool_group=pool_group, pool_stride=pool_stride,
                                            split_group=split_group)
+        if self.router_replay and getattr(self.generation, "engine", None) is not None:
+            self.generation.engine.set_record_routing(True)     # the engine files the experts it chose per position
         self.temperature = float(self.generation.cfg["temperature"] or 1.0)
         self.train_top_k = int(self.generation.cfg["top_k"]) if self.generation.cfg.get("top_k") else None
         self.train_top_p = float(self.generation.cfg.get("top_p") or 1.0)
@@ -731,11 +737,35 @@ class PolicyWorker:
             batch = batch.pad_to_multiple(8 * self.tp.world)
         elif self.cp.world > 1:
             batch = batch.pad_to_multiple(16 * self.cp.world)   # 2 cp chunks of whole 8-row groups
+        if self.router_replay:
+            self._set_router_replay(mb, lens, ids.shape[1], int(batch.input_ids.numel()))
         if "pixel_patches" in mb:   # vision-language batch: image patch rows in sample order (models/vision.py)
             parts = [t for t in mb["pixel_patches"] if t is not None]
             batch.mm = dict(patches=to_device(torch.cat(parts), self.device) if parts else None,
                             sizes=[int(x) for row in mb["image_sizes"] for x in (row or [])])
         return batch, ids.shape[1]
+
+    def _set_router_replay(self, mb: BatchedDataDict, lens: torch.Tensor, S: int, packed_rows: int) -> None:
+        """Hands every MoE layer the engine's expert choices for the rows of the next forward pass (packed order); without a
+        record in the batch the routers decide themselves."""
+        from rl_b200.utils import routing_trace as RT
+
+        if self.pipeline is not None:
+            raise NotImplementedError("rollout routing replay with pipeline parallelism")
+        re = mb.get("routed_experts") if hasattr(mb, "get") else None
+        if re is None:
+            RT.replay(self.model, None)
+            return
+        re = to_device(re[:, :S], self.device)
+        keep = torch.arange(S, device=self.device)[None, :] < lens[:, None].clamp(max=S)
+        rows = re[keep]                                   # [T, MoE layers, k], the order PackedBatch.from_padded uses
+        if rows.shape[0] < packed_rows:                   # rows appended for tensor / context parallel alignment
+            rows = torch.cat([rows, rows.new_full((packed_rows - rows.shape[0],) + tuple(rows.shape[1:]), -1)])
+        RT.replay_rows(self.model, rows)
+        if os.environ.get("RLB_R3_TRACE"):      # the record as this pass sees it; `maybe_dump(model, ...)` after the pass writes the capture
+            os.makedirs(os.environ["RLB_R3_TRACE"], exist_ok=True)
+            self._r3_dumps = getattr(self, "_r3_dumps", 0) + 1
+            torch.save(rows.cpu(), os.path.join(os.environ["RLB_R3_TRACE"], f"record_rank{self.rank}_{self._r3_dumps}.pt"))
 
     # ------------------------------------------------------------------ inference passes
     @torch.no_grad()

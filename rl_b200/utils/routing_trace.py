@@ -11,7 +11,7 @@ import torch
 
 
 def _moe_layers(model):
-    return [(i, l.mlp) for i, l in enumerate(model.layers) if hasattr(l.mlp, "last_routing")]
+    return [(i, l.mlp) for i, l in enumerate(model.layers) if getattr(l, "mlp", None) is not None and hasattr(l.mlp, "last_routing")]
 
 
 def capture(model) -> dict[int, torch.Tensor]:
@@ -24,6 +24,16 @@ def replay(model, trace: Optional[dict[int, torch.Tensor]]) -> None:
     for i, m in _moe_layers(model):
         t = None if trace is None else trace.get(i)
         m.forced_routing = None if t is None else t.to(torch.int64).to(m.router.device)
+
+
+def replay_rows(model, rows: Optional[torch.Tensor]) -> None:
+    """``rows`` [T, MoE layers, k] (the engine's record for the T rows of the next pass, -1 where it has none): MoE layer j of
+    the model is forced to ``rows[:, j]``; rows of -1 leave the choice to the router."""
+    layers = _moe_layers(model)
+    if rows is not None and rows.shape[1] != len(layers):
+        raise ValueError(f"the routing record has {rows.shape[1]} layers, the model {len(layers)} mixture layers")
+    for j, (_, m) in enumerate(layers):
+        m.forced_routing = None if rows is None else rows[:, j].to(torch.int64)
 
 
 def agreement(a: dict[int, torch.Tensor], b: dict[int, torch.Tensor]) -> float:

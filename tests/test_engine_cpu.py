@@ -230,3 +230,59 @@ def test_engine_serves_hybrid_state_space_models():
             assert eng.sched.num_preemptions > 0
         eng.sleep()
         assert eng.mamba_ssm is None
+
+
+def test_rollout_routing_replay_end_to_end():
+    """The engine files the experts every MoE layer chose for every position it ran; the generation output carries them; the
+    trainer forced to them reproduces exactly that routing (and leaves positions without a record to its own router)."""
+    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+    from rl_b200.policy.worker import PolicyWorker
+    from rl_b200.utils import routing_trace as RT
+
+    mc = ModelConfig(model_type="qwen3_moe", vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, qk_norm=True, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=16,
+                     torch_dtype="float32")
+    cfg = dict(precision="float32", train_global_batch_size=4, train_micro_batch_size=2, max_total_sequence_length=64, router_replay=dict(enabled=True),
+               optimizer=dict(name="torch.optim.AdamW", kwargs=dict(lr=1e-3)),
+               generation=dict(max_new_tokens=6, temperature=1.0, stop_token_ids=[], kv_cache_tokens=1024, block_size=4, max_running=8, max_prefill_tokens=5))
+    w = PolicyWorker(cfg, model_cfg=mc, device="cpu", init_reference_model=False, seed=1)
+    gen = w.build_generation()
+    assert gen.engine.record_routing
+    gen.prepare_for_generation()
+    ids = torch.tensor([[1, 2, 3, 4, 5, 6, 7, 8, 9], [9, 8, 7, 0, 0, 0, 0, 0, 0], [1, 2, 3, 4, 5, 6, 7, 8, 9]])
+    lens = torch.tensor([9, 3, 9])
+    out = gen.generate(BatchedDataDict(input_ids=ids, input_lengths=lens))
+    gen.finish_generation()
+    re = out["routed_experts"]
+    tot = out["unpadded_sequence_lengths"]
+    assert re.shape == (3, int(tot.max()), 3, 2) and re.dtype == torch.int16
+    for i in range(3):
+        n = int(tot[i])
+        assert (re[i, : n - 1] >= 0).all() and (re[i, n - 1 :] == -1).all()      # every position but the last sampled token ran
+    # the trainer's own routing on the same tokens agrees almost everywhere (fp32: everywhere but exact ties) ...
+    data = BatchedDataDict(input_ids=out["output_ids"], input_lengths=tot)
+    w.router_replay = False
+    RT.replay(w.model, None)
+    w.get_logprobs(data)
+    # ... and with the record forced, exactly: perturb the record and see the trainer follow it
+    w.router_replay = True
+    bent = re.clone()
+    bent[0, 2, 1] = torch.tensor([7, 6], dtype=torch.int16)
+    data["routed_experts"] = bent
+    lp_forced = w.get_logprobs(data)["logprobs"]
+    last = w.model.layers[1].mlp.last_routing        # packed rows of the last micro-batch
+    assert last.shape[1] == 2
+    data["routed_experts"] = re
+    lp_replay = w.get_logprobs(data)["logprobs"]
+    mask = out["logprobs"] != 0
+    assert float((lp_replay - out["logprobs"]).abs()[mask].max()) < 1e-4
+    assert not torch.allclose(lp_forced[0], lp_replay[0], atol=1e-6) and torch.allclose(lp_forced[1], lp_replay[1], atol=1e-6)
+    # training runs through the forced routing
+    from rl_b200.algorithms.loss.loss_functions import NLLLossFn
+
+    tm = torch.zeros_like(out["output_ids"], dtype=torch.float32)
+    for i in range(3):
+        tm[i, int(lens[i]) : int(tot[i])] = 1
+    train = BatchedDataDict(input_ids=out["output_ids"], input_lengths=tot, token_mask=tm, sample_mask=torch.ones(3), routed_experts=re)
+    res = w.train(train.slice(0, 2), NLLLossFn(), gbs=2, mbs=2)
+    assert torch.isfinite(res["loss"]).all()

@@ -187,3 +187,38 @@ def test_model_diagnostics_sub_commands_on_cpu():
     r = D.prefix_caching("tiny-llama-oracle", "cpu")
     assert r["ok"] and r["cached_prefix_tokens"] > 0
     assert D.routed_experts("cpu")["ok"]
+
+
+def test_small_tools(tmp_path, capsys):
+    import os
+
+    import torch
+
+    from rl_b200.tools import benchmark_tokenizer, check_r3_trace, code_snapshot, find_available_port_ranges
+
+    # routing record against a capture: identical sets in any order agree; -1 rows do not count; a bent row is found
+    rec = torch.tensor([[[0, 1], [2, 3]], [[4, 5], [6, 7]], [[-1, -1], [-1, -1]]], dtype=torch.int16)     # [T=3, layers=2, k=2]
+    cap = torch.tensor([[[1, 0], [2, 3]], [[4, 5], [7, 1]], [[0, 1], [2, 3]]], dtype=torch.int16)
+    r = check_r3_trace.compare(rec, {0: cap[:, 0], 1: cap[:, 1]})
+    assert r["layers"][0]["agreement"] == 1.0 and r["layers"][1]["agreement"] == 0.5 and r["recorded_positions"] == 4
+    assert abs(r["layers"][0]["unrecorded_fraction"] - 1 / 3) < 1e-9
+    torch.save(rec, tmp_path / "a.pt")
+    torch.save(rec, tmp_path / "b.pt")
+    assert check_r3_trace.main(["--record", str(tmp_path / "a.pt"), "--capture", str(tmp_path / "b.pt")]) == 0
+    # free port runs from a fake probe
+    busy = {1030, 1031, 1040}
+    assert find_available_port_ranges.free_ranges(1028, 1042, probe=lambda p, h: p not in busy) == [(1028, 1029), (1032, 1039), (1041, 1042)]
+    # tokenizer throughput numbers
+    from rl_b200.data.tokenizers import ByteTokenizer
+
+    b = benchmark_tokenizer.benchmark(ByteTokenizer(), benchmark_tokenizer.synthetic_docs(20, 30), batch=4)
+    assert b["tokens"] > 0 and b["encode_tokens_per_s"] > 0 and b["chat_templates_per_s"] > 0
+    # a snapshot holds the sources and is re-used by name
+    src = tmp_path / "proj"
+    (src / "pkg").mkdir(parents=True)
+    (src / "pkg" / "a.py").write_text("x = 1\n")
+    (src / "data.bin").write_bytes(b"\0")
+    snap = code_snapshot.snapshot("exp1", str(src))
+    assert (tmp_path / "proj" / "code_snapshots" / "exp1" / "pkg" / "a.py").exists() and not os.path.exists(os.path.join(snap, "data.bin"))
+    (src / "pkg" / "a.py").write_text("x = 2\n")
+    assert code_snapshot.snapshot("exp1", str(src)) == snap and open(os.path.join(snap, "pkg", "a.py")).read() == "x = 1\n"

@@ -451,6 +451,11 @@ class GenerationEngine:
         self._step_counter = 0
         self._n_stop = 0
         self.window_hook = None   # optional callable run at every host visit of the generate loop
+        # continuous admission (the serving frontend's asynchronous loop): ``admit_hook()`` is asked at every host visit for new
+        # requests ``(prompt, max_new_tokens or None, uid, tag)`` that join the running batch; ``finish_hook(request)`` is told
+        # the moment a request is complete, long before the generate call returns
+        self.admit_hook = None
+        self.finish_hook = None
         self.stats = dict(prefill_tokens=0, cached_prefix_tokens=0, decode_steps=0, generated_tokens=0, prefill_s=0.0, decode_s=0.0)
         # optional scheduler timeline: (seconds since the generate call began, sequences decoding, sequences prefilled this
         # iteration, requests not yet finished) per engine iteration, for in-flight batch-size plots
@@ -536,7 +541,7 @@ class GenerationEngine:
 
     def _r3_assemble(self, reqs: dict) -> None:
         buf, self._r3_buf, self._r3_meta = self._r3_buf, [], None
-        if not buf:
+        if not buf or not reqs:
             return
         k = buf[0][3].shape[1]
         start, total = {}, 0
@@ -1128,6 +1133,8 @@ class GenerationEngine:
                 r = reqs[sid]
                 r.finished = True
                 r.truncated = fin[j] == 2 and r.out_tokens[-1] not in stop
+                if self.finish_hook is not None:
+                    self.finish_hook(r)
         self.stats["decode_steps"] += steps
         self.stats["generated_tokens"] += sum(prod)
         self.stats["decode_s"] += time.perf_counter() - t0
@@ -1210,6 +1217,21 @@ class GenerationEngine:
         while True:
             if self.window_hook is not None:   # between two host visits (e.g. an in-flight weight update)
                 self.window_hook()
+            if self.admit_hook is not None and not lock:
+                for p, mx, uid, tag in self.admit_hook():
+                    rid = (max(reqs) + 1) if reqs else 0
+                    p = [int(t) for t in p]
+                    mx = max(1, min(int(mx) if mx is not None else sp.max_new_tokens, self.max_model_len - len(p)))
+                    r = _Request(rid, p, mx, uid=int(uid))
+                    r.tag = tag
+                    if self.sched.add(rid, len(p), mx, -1) != 0:
+                        r.finished, r.truncated, r.error = True, True, "the request can never fit the KV cache"
+                        if self.finish_hook is not None:
+                            self.finish_hook(r)
+                        continue
+                    reqs[rid] = r
+                    if self.prefix_caching and not self.record_routing:
+                        self.sched.set_hashes(rid, self._block_hashes(p))
             idle = self.sched.idle()
             if not lock and idle:
                 break
@@ -1277,6 +1299,8 @@ class GenerationEngine:
                     if fin[j]:
                         r.finished = True
                         r.truncated = fin[j] == 2 and tok_h[j] not in stop
+                        if self.finish_hook is not None:
+                            self.finish_hook(r)
                 self.stats["decode_steps"] += 1
                 self.stats["generated_tokens"] += n
                 self.stats["decode_s"] += time.perf_counter() - t0
@@ -1322,6 +1346,8 @@ class GenerationEngine:
                     if fin[j]:
                         r.finished = True
                         r.truncated = fin[j] == 2 and tok_h[j] not in stop
+                        if self.finish_hook is not None:
+                            self.finish_hook(r)
                 # logits of a prompt are kept while siblings that share it may still be admitted
                 pending_partners = {reqs[s].share_with for s in reqs if not reqs[s].out_tokens and reqs[s].share_with >= 0}
                 for sid in list(last_logits):

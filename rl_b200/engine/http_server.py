@@ -31,10 +31,15 @@ class _Pending:
 
 
 class BatchingFrontend:
-    """Collects requests from many threads and runs them through ``engine.generate`` in groups."""
+    """Collects requests from many threads and runs them through the engine. ``continuous`` (default): ONE engine loop stays
+    open while requests keep arriving; a request with the sampling settings of the running loop joins it at the engine's next
+    host visit and is answered the moment it finishes (asynchronous, sample-level serving: the role of the reference's
+    async vLLM engine, nemo_rl/models/generation/vllm/vllm_worker_async.py). Without it requests run in closed groups."""
 
-    def __init__(self, engine, batch_window_s: float = 0.005, max_batch: int = 512):
+    def __init__(self, engine, batch_window_s: float = 0.005, max_batch: int = 512, continuous: bool = True):
         self.engine, self.window, self.max_batch = engine, batch_window_s, max_batch
+        self.continuous = continuous
+        self.stats = dict(loops=0, joined_running_loop=0, answered=0)
         self._q: list[_Pending] = []
         self._cv = threading.Condition()
         self._stop = False
@@ -75,6 +80,66 @@ class BatchingFrontend:
             raise RuntimeError(p.error)
         return p.record
 
+    def _run_continuous(self) -> None:
+        """One open engine loop for all queued (and still arriving) requests that share the first one's sampling settings."""
+        with self._cv:
+            if not self._q:
+                self._idle.set()
+                return
+            key = self._q[0].key
+        t, tp, tk, mx, stops, greedy = key
+        self._calls += 1
+        self.stats["loops"] += 1
+        sp = SamplingParams(temperature=t, top_p=tp, top_k=tk, max_new_tokens=mx, stop_token_ids=list(stops), greedy=greedy, seed=1013 * self._calls)
+        in_flight: set = set()
+        first = [True]
+
+        def admit():
+            if self._paused.is_set() or self._stop:     # the trainer wants the engine: let the running requests drain
+                return []
+            with self._cv:
+                room = self.max_batch - len(in_flight)
+                take = [p for p in self._q if p.key == key][: max(0, room)]
+                taken = set(map(id, take))
+                self._q = [p for p in self._q if id(p) not in taken]
+            if not first[0]:
+                self.stats["joined_running_loop"] += len(take)
+            first[0] = False
+            out = []
+            for p in take:
+                in_flight.add(id(p))
+                self._uid = getattr(self, "_uid", 0) + 1
+                out.append((p.prompt, mx, self._uid, p))
+            return out
+
+        def finished(r):
+            p = getattr(r, "tag", None)
+            if p is None:
+                return
+            if getattr(r, "error", None):
+                p.error = r.error
+            p.record = r
+            in_flight.discard(id(p))
+            self.stats["answered"] += 1
+            p.done.set()
+
+        eng = self.engine
+        eng.admit_hook, eng.finish_hook = admit, finished
+        try:
+            eng.wake()
+            eng.generate([], sp)
+        except Exception as e:
+            with self._cv:
+                stuck = [p for p in self._q if p.key == key]
+            for p in stuck:      # requests of this loop that never got an answer are told why
+                p.error = f"{type(e).__name__}: {e}"
+                p.done.set()
+            with self._cv:
+                self._q = [p for p in self._q if p.key != key]
+        finally:
+            eng.admit_hook = eng.finish_hook = None
+            self._idle.set()
+
     def _run(self) -> None:
         while True:
             with self._cv:
@@ -87,6 +152,9 @@ class BatchingFrontend:
                     return
                 self._idle.clear()
             time.sleep(self.window)  # let concurrent requests join this batch
+            if self.continuous:
+                self._run_continuous()
+                continue
             with self._cv:
                 key = self._q[0].key
                 batch = [p for p in self._q if p.key == key][: self.max_batch]

@@ -168,3 +168,51 @@ def test_async_sample_level_rollout_through_the_batching_frontend():
         assert fe._calls < 12          # concurrent samples shared engine calls
     finally:
         fe.close()
+
+
+def test_requests_join_the_running_engine_loop_and_leave_when_done():
+    """Continuous admission: a short request that arrives while a long one is decoding joins the same engine loop at the next
+    host visit and is answered first; its tokens are what the model gives for it alone (the shared batch changes nothing)."""
+    import time
+
+    from rl_b200.engine.engine import SamplingParams
+    from rl_b200.engine.http_server import BatchingFrontend
+
+    tok = ByteTokenizer(vocab_size=300)
+    mc = ModelConfig(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=8, torch_dtype="float32")
+    model = CausalLM(mc, dtype=torch.float32, device="cpu", seed=1)
+    eng = GenerationEngine(model, block_size=4, num_blocks=256, max_running=16, max_model_len=256, use_cuda_graphs=False)
+    slow = []
+    eng.window_hook = lambda: (time.sleep(0.01), slow.append(1))       # stretch the loop so that the second request arrives mid-way
+    fe = BatchingFrontend(eng, batch_window_s=0.0)
+    sp = dict(temperature=1.0, max_new_tokens=60, stop_token_ids=[], greedy=True)
+    done_at, recs = {}, {}
+
+    def ask(name, prompt, **over):
+        recs[name] = fe.submit(prompt, dict(sp, **over))
+        done_at[name] = time.perf_counter()
+
+    a = threading.Thread(target=ask, args=("long", [1, 2, 3, 4, 5]))
+    a.start()
+    while len(slow) < 5:       # the long request is decoding
+        time.sleep(0.005)
+    b = threading.Thread(target=ask, args=("short", [9, 8, 7]), kwargs=dict(max_new_tokens=60))
+    b.start()
+    b.join(60)
+    a.join(60)
+    try:
+        assert fe.stats["loops"] == 1 and fe.stats["joined_running_loop"] == 1 and fe.stats["answered"] == 2
+        assert len(recs["long"].out_tokens) == 60 and len(recs["short"].out_tokens) == 60
+        assert done_at["long"] < done_at["short"]       # same length, started earlier: each leaves when ITS tokens are done
+        assert fe.pause(10)          # the frontend's loop has fully ended: the engine may be driven from this thread
+        eng.window_hook = None
+        alone = eng.generate([[9, 8, 7]], SamplingParams(max_new_tokens=60, stop_token_ids=[], greedy=True))[0]
+        fe.resume()
+        assert alone.out_tokens == recs["short"].out_tokens
+        # a different sampling setting waits for a loop of its own; pausing drains the running loop
+        fe.submit([4, 4], dict(sp, temperature=0.5, greedy=False, max_new_tokens=3))
+        assert fe.stats["loops"] == 2 and fe.pause(10)
+        fe.resume()
+    finally:
+        fe.close()

@@ -74,6 +74,10 @@ def prepare_xtoken_batch(texts: Sequence[str], aligner: TokenAligner, proj: torc
                          logprob_batch_size: Optional[int] = None) -> BatchedDataDict:
     """Tokenises ``texts`` for both models, runs the teacher (top-k next-token logits and token log-probabilities) and
     lays out what the loss needs, padded per batch. ``teacher``: a policy worker built on the teacher's tokenizer."""
+    if isinstance(proj, dict):      # a sparse map from rl_b200/tools/x_token_projection.py: every teacher token's heaviest student target
+        from rl_b200.tools.x_token_projection import as_one_to_one
+
+        proj = as_one_to_one(proj)
     s_tok, t_tok = aligner.s_tok, aligner.t_tok
     n = len(texts)
     S_ids, T_ids, CH = [], [], []

@@ -70,6 +70,9 @@ def parallel_sizes(policy_cfg: dict) -> dict:
                 return src[a]
         return None
 
+    vpp = pick("virtual_pipeline_stages", "virtual_pipeline_model_parallel_size", "num_layers_per_virtual_pipeline_stage")
+    if vpp not in (None, 0, 1):
+        raise NotImplementedError("interleaved (virtual) pipeline stages are not available: every pipeline rank owns one contiguous run of layers")
     tp = int(pick("tensor_parallel_size", "tensor_parallel_size", "tensor_model_parallel_size") or 1)
     return dict(tp=tp, pp=int(pick("pipeline_parallel_size", "pipeline_model_parallel_size") or 1),
                 cp=int(pick("context_parallel_size", "context_parallel_size") or 1),

@@ -99,3 +99,43 @@ def test_training_loop_pulls_student_towards_teacher(tmp_path):
     assert len(hist) == 10
     assert hist[-1]["loss"] < 0.5 * hist[0]["loss"] and hist[-1]["chunk_loss"] < hist[0]["chunk_loss"]
     assert all(h["aligned_positions"] > 0 and h["next_token_kl"] >= 0 for h in hist)
+
+
+def test_sparse_vocabulary_projection_between_tokenizers(tmp_path):
+    """Student = byte tokenizer, teacher = byte pairs: a teacher pair token has no twin in the student's vocabulary and is spelled
+    by two byte tokens (first one heavier); single bytes map one to one; specials map to nothing."""
+    from rl_b200.data.tokenizers import ByteTokenizer, PairTokenizer
+    from rl_b200.tools import x_token_projection as X
+
+    s_tok, t_tok = ByteTokenizer(vocab_size=512), PairTokenizer(vocab_size=1024)
+    proj = X.build_sparse_projection(s_tok, t_tok, top_k=3)
+    assert proj["indices"].shape == (1024, 3) and proj["student_vocab"] == 512
+    a = t_tok.encode("a")[0]
+    assert proj["indices"][a].tolist() == [s_tok.encode("a")[0], -1, -1] and proj["values"][a, 0] == 1.0 and bool(proj["exact"][a])
+    th = t_tok.encode("th")
+    assert len(th) == 1
+    row_i, row_v = proj["indices"][th[0]], proj["values"][th[0]]
+    assert row_i[:2].tolist() == [s_tok.encode("t")[0], s_tok.encode("h")[0]] and row_v[:2].tolist() == pytest.approx([2 / 3, 1 / 3])
+    assert not bool(proj["exact"][th[0]])
+    aa = t_tok.encode("aa")[0]                                  # the same student token twice: one target, all the weight
+    assert proj["indices"][aa].tolist() == [s_tok.encode("a")[0], -1, -1] and float(proj["values"][aa, 0]) == pytest.approx(1.0)
+    cov = X.coverage(proj)
+    assert cov["exact"] >= 128 and cov["spelled"] == 676 and cov["mapped"] + cov["unmapped"] == 1024
+    # teacher probabilities land on the student's vocabulary with their mass conserved on mapped tokens
+    p = torch.zeros(2, 1024)
+    p[0, th[0]], p[0, a], p[1, aa] = 0.6, 0.4, 1.0
+    q = X.project_token_likelihoods(p, proj)
+    assert q.shape == (2, 512) and q.sum(-1).tolist() == pytest.approx([1.0, 1.0])
+    assert float(q[0, s_tok.encode("t")[0]]) == pytest.approx(0.4) and float(q[0, s_tok.encode("a")[0]]) == pytest.approx(0.4)
+    # cut to the single heaviest target, the form the distillation batch takes
+    one = X.as_one_to_one(X.sort_and_cut(proj, 1))
+    assert int(one[th[0]]) == s_tok.encode("t")[0] and int(one[a]) == s_tok.encode("a")[0]
+    # an edited map gets its exact rows back
+    bent = dict(proj, values=proj["values"].clone(), indices=proj["indices"].clone())
+    bent["indices"][a, 1], bent["values"][a] = 5, torch.tensor([0.5, 0.5, 0.0])
+    fixed = X.reapply_exact_map(bent)
+    assert fixed["indices"][a].tolist() == proj["indices"][a].tolist() and fixed["values"][a].tolist() == [1.0, 0.0, 0.0]
+    exact_only = X.build_sparse_projection(s_tok, t_tok, top_k=2, exact_only=True)
+    assert float(exact_only["values"][th[0]].sum()) == 0.0
+    assert X.main(["--student", "byte", "--teacher", "pair", "--top-k", "2", "--out", str(tmp_path / "p.pt")]) == 0
+    assert torch.load(tmp_path / "p.pt", weights_only=False)["indices"].shape[1] == 2

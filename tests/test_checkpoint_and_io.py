@@ -70,3 +70,49 @@ def test_model_packed_equals_separate_sequences():
         one, _ = m.next_token_logprobs(PackedBatch.from_padded(ids[i : i + 1, : lens[i]], lens[i : i + 1]))
         assert torch.allclose(out[i, : lens[i]], one, atol=1e-5)
         assert out[i, 0] == 0
+
+
+@pytest.mark.parametrize("stacked,arch", [(False, "llama"), (True, "qwen3"), (False, "moe")])
+def test_megatron_checkpoint_converts_to_hf(tmp_path, stacked, arch):
+    """A Megatron-core style distributed checkpoint (grouped qkv, fused gate / up, norms folded into the linear layers' names,
+    experts by index; per-layer keys or one key per kind with a leading layer axis) becomes the HF checkpoint it came from."""
+    import sys
+
+    import torch.distributed.checkpoint as dcp
+
+    from rl_b200.checkpoint import megatron_names as M
+    from rl_b200.models.config import ModelConfig
+    from rl_b200.models.hf_io import iter_hf_tensors, load_pretrained
+    from rl_b200.models.transformer import build_model
+
+    base = dict(vocab_size=96, hidden_size=32, intermediate_size=48, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                torch_dtype="float32")
+    cfg = {"llama": ModelConfig(model_type="llama", **base),
+           "qwen3": ModelConfig(model_type="qwen3", qk_norm=True, **base),
+           "moe": ModelConfig(model_type="qwen3_moe", qk_norm=True, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16, **base)}[arch]
+    model = build_model(cfg, dtype=torch.float32, seed=4)
+    hf = {k: v.detach().clone() for k, v in iter_hf_tensors(model)}
+    q, k, v = (hf[f"model.layers.1.self_attn.{n}_proj.weight"] for n in "qkv")
+    merged = M.merge_qkv(q, k, v, cfg)
+    assert torch.equal(merged[:16], q[:16]) and torch.equal(merged[16:24], k[:8]) and torch.equal(merged[24:32], v[:8])      # group 0: 2 q heads, k, v
+    assert all(torch.equal(a, b) for a, b in zip(M.split_qkv(merged, cfg), (q, k, v)))
+    meg = M.hf_to_megatron(hf, cfg)
+    if stacked:      # homogeneous stack: one entry per kind with a leading layer axis, under a "model." prefix
+        kinds = {}
+        for key, t in meg.items():
+            m = __import__("re").match(r"decoder\.layers\.(\d+)\.(.*)", key)
+            if m:
+                kinds.setdefault(m.group(2), {})[int(m.group(1))] = t
+        meg = {k_: t for k_, t in meg.items() if not k_.startswith("decoder.layers.")}
+        meg.update({f"decoder.layers.{rest}": torch.stack([ts[i] for i in range(3)]) for rest, ts in kinds.items()})
+        meg = {"model." + k_: t for k_, t in meg.items()}
+    ck = tmp_path / "meg" / "iter_0000005"
+    dcp.save({k_: t.contiguous() for k_, t in meg.items()}, checkpoint_id=str(ck), no_dist=True)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from examples.converters import convert_megatron_to_hf as conv
+
+    cfg.save_pretrained(str(tmp_path / "cfg"))
+    conv.main(["--megatron-ckpt-path", str(tmp_path / "meg"), "--hf-config", str(tmp_path / "cfg"), "--hf-ckpt-path", str(tmp_path / "hf")])
+    back = load_pretrained(str(tmp_path / "hf"), dtype=torch.float32)
+    for (n, a), (_, b) in zip(model.named_parameters(), back.named_parameters()):
+        assert torch.equal(a, b), n

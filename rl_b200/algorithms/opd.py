@@ -146,6 +146,16 @@ class TeacherGroup:
 
 def create_teacher_groups(master_config: dict, tokenizer=None, model_cfg=None) -> tuple[dict[str, TeacherGroup], dict[str, str]]:
     cfg = opd_cfg(master_config)
+    if is_non_colocated_teachers_enabled(master_config) and not (torch.distributed.is_available() and torch.distributed.is_initialized()
+                                                                 and torch.distributed.get_world_size() > 1):
+        # teachers on GPUs of their own, driven from this (single controller) process through worker groups
+        from dataclasses import asdict
+
+        from rl_b200.policy.lm_policy import create_teacher_worker_groups
+
+        return create_teacher_worker_groups(master_config, asdict(model_cfg) if model_cfg is not None else None,
+                                            (master_config.get("policy") or {}).get("tokenizer"),
+                                            (master_config.get("cluster") or {}).get("backend"))
     groups = {t.alias: TeacherGroup(t, master_config["policy"], tokenizer, model_cfg) for t in create_teacher_configs(cfg)}
     return groups, alias_to_group_alias(cfg)
 

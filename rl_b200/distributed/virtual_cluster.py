@@ -135,6 +135,45 @@ class _SubCluster(VirtualCluster):
         return list(self._bundles)
 
 
+@dataclass(frozen=True)
+class NodeInfo:
+    """What the launcher knows about a node: address, free GPUs and the NVLink domain it sits in (GPUs of one domain -- an
+    NVL72 rack, an HGX board -- reach each other without leaving NVLink; None: unknown, a domain of its own)."""
+
+    address: str
+    gpus: int
+    nvlink_domain: Optional[str] = None
+
+
+def place_on_nodes(nodes: Sequence[NodeInfo], num_nodes: int, gpus_per_node: int) -> list[NodeInfo]:
+    """Chooses ``num_nodes`` nodes with at least ``gpus_per_node`` GPUs each so that the job spans as few NVLink domains as
+    possible, and orders them domain by domain (ranks that talk most -- consecutive ranks -- then share a domain). Domains are
+    taken largest first; ties and the order inside a domain follow the node addresses, so the choice is reproducible.
+    Role of the topology-aware sort of nemo_rl/distributed/virtual_cluster.py."""
+    ok = [n for n in nodes if n.gpus >= gpus_per_node]
+    if len(ok) < num_nodes:
+        raise ResourceInsufficientError(f"{num_nodes} nodes with {gpus_per_node} GPUs were asked for, {len(ok)} of {len(nodes)} qualify")
+    by_domain: dict = {}
+    for n in sorted(ok, key=lambda n: n.address):
+        by_domain.setdefault(n.nvlink_domain if n.nvlink_domain is not None else f"\0{n.address}", []).append(n)
+    whole = sorted(by_domain.items(), key=lambda kv: (-len(kv[1]), kv[0]))
+    # a single domain that can hold the whole job wins (the smallest such, to leave large domains for large jobs)
+    fits = [kv for kv in whole if len(kv[1]) >= num_nodes]
+    if fits:
+        return list(min(fits, key=lambda kv: (len(kv[1]), kv[0]))[1][:num_nodes])
+    out: list[NodeInfo] = []
+    for _, members in whole:
+        out += members[: num_nodes - len(out)]
+        if len(out) == num_nodes:
+            break
+    return out
+
+
+def cluster_from_nodes(nodes: Sequence[NodeInfo], num_nodes: int, gpus_per_node: int, **kw) -> VirtualCluster:
+    chosen = place_on_nodes(nodes, num_nodes, gpus_per_node)
+    return VirtualCluster([gpus_per_node] * num_nodes, num_gpus_per_node=gpus_per_node, node_addresses=[n.address for n in chosen], **kw)
+
+
 def cluster_from_config(cluster_cfg: dict, colocated_groups: int = 2, name: str = "cluster") -> VirtualCluster:
     """``cluster: {gpus_per_node, num_nodes}`` of a recipe -> the job's cluster (node addresses from ``RLB_NODE_ADDRESSES``, a
     comma-separated list the launcher exports on multi-node jobs)."""

@@ -246,3 +246,48 @@ class PolicyGeneration:
 
     def shutdown(self) -> bool:
         return True
+
+
+class TeacherWorkerGroup:
+    """A frozen teacher on GPUs of its own (``on_policy_distillation.non_colocated_teachers``): a worker group sized by the
+    teacher's ``num_nodes x gpus_per_node`` with its own tensor / pipeline / context parallel sizes, scoring only -- no
+    optimizer, no reference copy, no engine. Answers like the in-process teacher of ``rl_b200/algorithms/opd.py`` does. Role of
+    nemo_rl/models/policy/teacher_worker_group.py."""
+
+    def __init__(self, tcfg, policy_config: dict, cluster: Optional[VirtualCluster] = None, model_cfg: Optional[dict] = None,
+                 tokenizer_cfg: Optional[dict] = None, backend: Optional[str] = None):
+        from rl_b200.distributed.virtual_cluster import visible_gpu_count
+
+        self.alias, self.model_name, self.cfg = tcfg.alias, tcfg.model_name, tcfg
+        cfg = {k: v for k, v in policy_config.items() if k not in ("optimizer", "scheduler", "generation", "lora_cfg", "draft", "quant_cfg")}
+        cfg.update(model_name=tcfg.model_name, precision=tcfg.precision, logprob_batch_size=tcfg.micro_batch_size)
+        cfg["parallel"] = dict(tensor_parallel_size=tcfg.tensor_model_parallel_size, pipeline_parallel_size=tcfg.pipeline_model_parallel_size,
+                               context_parallel_size=tcfg.context_parallel_size, expert_parallel_size=tcfg.expert_model_parallel_size)
+        cfg.update(tcfg.overrides)
+        self._own_cluster = cluster is None
+        self.cluster = cluster or VirtualCluster([tcfg.gpus_per_node] * tcfg.num_nodes, use_gpus=visible_gpu_count() > 0, name=f"teacher-{tcfg.alias}")
+        self.policy = Policy(self.cluster, cfg, tokenizer_cfg=tokenizer_cfg, name_prefix=f"teacher_{tcfg.alias}", init_optimizer=False,
+                             init_reference_model=False, weights_path=tcfg.model_name if model_cfg is None else None, model_cfg=model_cfg,
+                             backend=backend)
+
+    def get_logprobs(self, data: BatchedDataDict, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        return BatchedDataDict(reference_logprobs=self.policy.get_logprobs(data, micro_batch_size)["logprobs"])
+
+    def get_topk_logits(self, data: BatchedDataDict, k: int, micro_batch_size: Optional[int] = None) -> BatchedDataDict:
+        return self.policy.get_topk_logits(data, k, micro_batch_size)
+
+    def shutdown(self) -> bool:
+        ok = self.policy.shutdown()
+        if self._own_cluster:
+            self.cluster.shutdown()
+        return ok
+
+
+def create_teacher_worker_groups(master_config: dict, model_cfg: Optional[dict] = None, tokenizer_cfg: Optional[dict] = None,
+                                 backend: Optional[str] = None) -> tuple[dict, dict]:
+    """One :class:`TeacherWorkerGroup` per distinct teacher checkpoint of ``on_policy_distillation`` and the alias -> group map."""
+    from rl_b200.algorithms import opd
+
+    cfg = opd.opd_cfg(master_config)
+    groups = {t.alias: TeacherWorkerGroup(t, master_config["policy"], None, model_cfg, tokenizer_cfg, backend) for t in opd.create_teacher_configs(cfg)}
+    return groups, opd.alias_to_group_alias(cfg)

@@ -68,6 +68,21 @@ def test_virtual_cluster_shapes_and_limits():
     assert g.get_master_address_and_port()[0] == "127.0.0.1" and g.get_master_address_and_port()[1] > 0
 
 
+def test_placement_prefers_few_nvlink_domains():
+    from rl_b200.distributed.virtual_cluster import NodeInfo, cluster_from_nodes, place_on_nodes
+
+    nodes = [NodeInfo("n1", 8, "rackA"), NodeInfo("n2", 8, "rackB"), NodeInfo("n3", 8, "rackA"), NodeInfo("n4", 4, "rackA"), NodeInfo("n5", 8, "rackB"),
+             NodeInfo("n6", 8, "rackB"), NodeInfo("n7", 8, None)]
+    assert [n.address for n in place_on_nodes(nodes, 2, 8)] == ["n1", "n3"]                 # the smallest domain that holds the job
+    assert [n.address for n in place_on_nodes(nodes, 3, 8)] == ["n2", "n5", "n6"]           # only rack B holds three
+    assert [n.address for n in place_on_nodes(nodes, 5, 8)] == ["n2", "n5", "n6", "n1", "n3"]     # largest domains first, kept together
+    assert [n.address for n in place_on_nodes(nodes, 3, 4)][:3] == ["n1", "n3", "n4"]       # the 4-GPU node qualifies for 4-GPU bundles
+    with pytest.raises(ResourceInsufficientError):
+        place_on_nodes(nodes, 7, 8)
+    c = cluster_from_nodes(nodes, 2, 8, use_gpus=False, name="t")
+    assert c.node_addresses == ["n1", "n3"] and c.world_size() == 16
+
+
 def test_worker_group_dispatch_forms_and_failures(tmp_path):
     cluster = VirtualCluster([4], use_gpus=False, name="t")
     sa = NamedSharding.from_sizes(4, data_parallel=2, tensor_parallel=2)
@@ -178,3 +193,36 @@ def test_policy_facade_matches_an_in_process_worker(par, tmp_path):
         assert os.path.exists(tmp_path / "w" / "config.json")
     finally:
         assert pol.shutdown()
+
+
+def test_teacher_worker_group_scores_like_the_in_process_teacher():
+    """A non-colocated teacher (its own worker group, tensor parallel 2) answers with the log-probabilities the in-process teacher
+    gives; aliases that share a checkpoint share the group."""
+    from dataclasses import asdict
+
+    from rl_b200.algorithms import opd
+    from rl_b200.models.config import preset
+    from rl_b200.parallel.state import reset_parallel
+
+    mc = preset("tiny-llama-oracle", torch_dtype="float32")
+    master = dict(policy=_policy_cfg(), cluster=dict(backend="gloo"),
+                  grpo=dict(adv_estimator=dict(name="opd")),
+                  on_policy_distillation=dict(teacher_model_by_agent_name={"math": "tiny-llama-oracle", "code": "tiny-llama-oracle"},
+                                              non_colocated_teachers=dict(enabled=True, default_teacher_cfg=dict(
+                                                  num_nodes=1, gpus_per_node=2, tensor_model_parallel_size=2, precision="float32"))))
+    data = _policy_data()
+    reset_parallel()
+    solo = opd.TeacherGroup(opd.create_teacher_configs(opd.opd_cfg(master))[0], master["policy"], model_cfg=mc)
+    want = solo.get_logprobs(data)["reference_logprobs"]
+    groups, alias_map = opd.create_teacher_groups(master, model_cfg=mc)
+    try:
+        assert list(groups) == ["math"] and alias_map == {"math": "math", "code": "math"}
+        g = groups["math"]
+        assert g.cluster.world_size() == 2 and g.policy.dp == 1 and [l["tp"] for l in g.policy.layouts()] == [2, 2]
+        got = g.get_logprobs(data)["reference_logprobs"]
+        assert torch.allclose(got, want, atol=3e-5)
+        top = g.get_topk_logits(data, 4)
+        assert top["topk_logits"].shape[0] == 8 and top["topk_indices"].shape[-1] == 4
+    finally:
+        for g in groups.values():
+            assert g.shutdown()

@@ -65,6 +65,30 @@ class StatelessProcessGroup:
 
     # Rank 0 hosts the store: it must keep this object alive until every member is done with the group.
 
+    def bulk_group(self, device=None, timeout_s: float = 1800.0):
+        """A ``torch.distributed`` backend object (NCCL for CUDA tensors, gloo otherwise) over this group's members, built
+        straight on the group's store: bulk tensors (weights) move through it while the default process group of either side
+        is left alone. Every member must call this once, with the same kind of device."""
+        if getattr(self, "_bulk", None) is None:
+            import torch.distributed as dist
+
+            store = dist.PrefixStore("slpg_bulk", self.store)
+            dev = torch.device(device) if device is not None else torch.device("cpu")
+            if dev.type == "cuda":
+                self._bulk = dist.ProcessGroupNCCL(store, self.rank, self.world_size, timedelta(seconds=timeout_s))
+            else:
+                self._bulk = dist.ProcessGroupGloo(store, self.rank, self.world_size, timedelta(seconds=timeout_s))
+        return self._bulk
+
+    def broadcast_bulk(self, t: torch.Tensor, src: int = 0) -> torch.Tensor:
+        """In-place broadcast of a (large) tensor from ``src`` to every member over :meth:`bulk_group`."""
+        import torch.distributed as dist
+
+        opts = dist.BroadcastOptions()
+        opts.rootRank, opts.rootTensor = src, 0
+        self.bulk_group(t.device).broadcast([t], opts).wait()
+        return t
+
     def unique_id(self) -> bytes:
         """A 128-byte token agreed by all members (what a communicator bootstrap needs)."""
         import os

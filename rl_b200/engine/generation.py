@@ -99,6 +99,58 @@ class NativeGeneration:
         self.engine.sleep(free_kv_cache=bool(self.cfg["free_kv_cache_on_sleep"]))
         return True
 
+    # ------------------------------------------------------------------ weights from a trainer outside this job
+    def init_collective(self, rank_prefix: int, ip: str, port: int, world_size: int, *, train_world_size: int = 1) -> None:
+        """Joins the trainer's weight communicator as rank ``train_world_size + rank_prefix`` (``GenerationInterface.init_collective``)."""
+        from rl_b200.distributed.stateless_group import StatelessProcessGroup
+
+        self._collective = StatelessProcessGroup(ip, port, int(train_world_size) + int(rank_prefix), world_size)
+
+    def prepare_refit_info(self, state_dict_info: Optional[dict] = None) -> None:
+        """Names, shapes and dtypes the trainer is going to send (checked against what arrives)."""
+        self._refit_info = dict(state_dict_info or {})
+
+    def update_weights_from_collective(self) -> bool:
+        """Receives the buckets of ``PolicyWorker.broadcast_weights_for_collective`` and copies every tensor into this engine's
+        (possibly tensor-parallel) parameters; the KV cache and the prefix cache of the old weights are dropped."""
+        from rl_b200.models.hf_io import load_hf_tensors
+        from rl_b200.refit.packed_broadcast import _numel, unpack
+
+        g = self._collective
+        info = getattr(self, "_refit_info", None) or {}
+        dev = self.engine.device
+        while True:
+            meta = g.broadcast_obj(None, 0)
+            if meta is None:
+                break
+            for n, shape, dt in meta:
+                if n in info and (tuple(info[n][0]) != tuple(shape)):
+                    raise ValueError(f"{n}: announced shape {tuple(info[n][0])}, received {tuple(shape)}")
+            size = sum(-(-_numel(s) * torch.empty((), dtype=d).element_size() // 16) * 16 for _, s, d in meta)
+            buf = torch.empty(size, dtype=torch.uint8, device=dev)
+            g.broadcast_bulk(buf, 0)
+            got = dict(unpack(buf, meta))
+            load_hf_tensors(self.engine.model, got.get, strict=False)
+        self.invalidate_kv_cache()
+        if getattr(self.engine, "quantization", None):
+            self.engine.requantize()
+        return True
+
+    def update_weights_via_ipc_zmq(self) -> bool:
+        """Colocated: the engine already addresses the trainer's buffers (or its arena was filled by the re-shard kernel)."""
+        return True
+
+    def get_collective_sender_spec(self) -> dict:
+        return {"sender_rank": 0, "transport": "packed buckets over a stateless process group"}
+
+    @property
+    def requires_kv_scale_sync(self) -> bool:
+        return False      # no FP8 KV cache: no scales to carry
+
+    @property
+    def blocks_training(self) -> bool:
+        return True       # colocated engines share the trainer's GPUs: generation and training alternate
+
     def invalidate_kv_cache(self) -> bool:
         self.engine.sched.reset()
         return True

@@ -40,6 +40,20 @@ class ColocatablePolicyInterface(PolicyInterface, Protocol):
 
     def build_generation(self, gen_cfg: Optional[dict] = None) -> "GenerationInterface": ...
 
+    def prepare_refit_info(self) -> dict:
+        """HF name -> (shape, dtype) of every tensor a refit carries."""
+
+    def offload_before_refit(self) -> None: ...
+
+    def offload_after_refit(self) -> None: ...
+
+    # an engine outside the trainer's job (nemo_rl/models/policy/interfaces.py:166-262)
+    def init_collective(self, ip: str, port: int, world_size: int, *, train_world_size: int = 1) -> None: ...
+
+    def broadcast_weights_for_collective(self, kv_scales: Any = None) -> int: ...
+
+    def stream_weights_via_ipc_zmq(self, *args, **kwargs) -> int: ...
+
 
 @runtime_checkable
 class ValueInterface(Protocol):
@@ -63,3 +77,16 @@ class GenerationInterface(Protocol):
     def invalidate_kv_cache(self) -> bool: ...
 
     def shutdown(self) -> bool: ...
+
+
+@runtime_checkable
+class RefittableGenerationInterface(GenerationInterface, Protocol):
+    """The weight-receiving side (nemo_rl/models/generation/interfaces.py:392-527)."""
+
+    def init_collective(self, rank_prefix: int, ip: str, port: int, world_size: int, *, train_world_size: int = 1) -> None: ...
+
+    def prepare_refit_info(self, state_dict_info: Optional[dict] = None) -> None: ...
+
+    def update_weights_from_collective(self) -> bool: ...
+
+    def update_weights_via_ipc_zmq(self) -> bool: ...

@@ -80,6 +80,16 @@ def parallel_sizes(policy_cfg: dict) -> dict:
                 sequence_parallel=bool(tp > 1 and (pick("sequence_parallel", "sequence_parallel") in (None, True))))
 
 
+def _peak_tflops() -> float:
+    """Dense bf16 peak of one GPU (what model-FLOPs utilisation is quoted against)."""
+    from rl_b200.utils.flops import device_peak_tflops
+
+    try:
+        return float(device_peak_tflops(torch.cuda.get_device_name(0) if torch.cuda.is_available() else "B200"))
+    except Exception:
+        return float(device_peak_tflops("B200"))
+
+
 def ensure_parallel(policy_cfg: dict):
     """Initialises the process-wide parallel layout from the policy config (idempotent; collective on first use)."""
     from rl_b200.parallel.state import get_state, init_parallel
@@ -670,6 +680,48 @@ class PolicyWorker:
                     p.data = fl.flat[o : o + n].view(p.shape)
             self._weights_changed()
 
+    # ------------------------------------------------------------------ weights to an engine outside this job
+    def init_collective(self, ip: str, port: int, world_size: int, *, train_world_size: int = 1) -> None:
+        """Joins a communicator that spans this trainer's rank 0 (as its rank 0) and the ranks of an external generation
+        service (ranks 1..), outside both sides' default process groups (``PolicyInterface.init_collective`` of the reference).
+        Ranks other than 0 of the trainer only take part in gathering their shards."""
+        from rl_b200.distributed.stateless_group import StatelessProcessGroup
+
+        self._collective = StatelessProcessGroup(ip, port, 0, world_size) if self.rank == 0 and self.pstate.rank == 0 else None
+
+    def broadcast_weights_for_collective(self, kv_scales=None, bucket_bytes: int = 1 << 28) -> int:
+        """Sends the current weights (HF names, gathered over tensor parallelism) to the generation ranks of
+        :meth:`init_collective` in packed buckets: a small header through the group's store, the bytes through its bulk
+        backend. Returns the payload bytes. The receiving side runs ``NativeGeneration.update_weights_from_collective``."""
+        from rl_b200.models.hf_io import iter_hf_tensors
+        from rl_b200.refit.packed_broadcast import _buckets, pack
+
+        g = getattr(self, "_collective", None)
+        total = 0
+        for bucket in _buckets(((n, t.detach()) for n, t in iter_hf_tensors(self.model)), bucket_bytes):   # (collective over tp)
+            if g is None:
+                continue
+            g.broadcast_obj([(n, tuple(t.shape), t.dtype) for n, t in bucket], 0)
+            buf = pack([t for _, t in bucket], self.device)
+            g.broadcast_bulk(buf, 0)
+            total += buf.numel()
+        if g is not None:
+            g.broadcast_obj(None, 0)
+        return total
+
+    def stream_weights_via_ipc_zmq(self, *args, **kwargs) -> int:
+        """Colocated engines read the trainer's own buffers (matching layouts) or are filled by the peer-memory re-shard kernel
+        (``rl_b200/refit``): there is nothing to stream through host sockets. Kept so that callers written against the
+        reference's colocated interface run; returns the bytes the synchronizer moved (0 for shared buffers)."""
+        sync = getattr(self, "weight_synchronizer", None)
+        if sync is not None:
+            sync.sync_weights(None)
+            return int(getattr(sync, "last_bytes", 0))
+        return 0
+
+    def offload_to_cpu(self) -> None:
+        self.offload_before_refit()
+
     def _weights_changed(self) -> None:
         """Derived copies of the weights (quantised forms) are stale."""
         if getattr(self, "quantizers", None):
@@ -962,6 +1014,7 @@ class PolicyWorker:
             "all_mb_metrics": mb_metrics,
             "total_flops": flops,
             "num_ranks": self.world,
+            "theoretical_tflops": _peak_tflops(),
             "train_time_s": elapsed,
             "train_tokens": total_tokens,
         }

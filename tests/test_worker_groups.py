@@ -226,3 +226,62 @@ def test_teacher_worker_group_scores_like_the_in_process_teacher():
     finally:
         for g in groups.values():
             assert g.shutdown()
+
+
+class _RefitPeer:
+    """Rank 0 hosts a trainer, rank 1 a generation service with different weights; neither joins a default process group."""
+
+    def __init__(self, port):
+        from rl_b200.models.config import preset
+        from rl_b200.parallel.state import reset_parallel
+        from rl_b200.policy.worker import PolicyWorker
+
+        self.rank, self.port = int(os.environ["RANK"]), port
+        reset_parallel()
+        mc = preset("tiny-llama-oracle", torch_dtype="float32")
+        self.worker = PolicyWorker(_policy_cfg(), model_cfg=mc, device="cpu", init_reference_model=False, init_optimizer=False, seed=11 + self.rank)
+        self.gen = self.worker.build_generation() if self.rank == 1 else None
+
+    def logprobs(self, data):
+        return self.worker.get_logprobs(data)["logprobs"]
+
+    def connect(self):
+        if self.rank == 0:
+            self.worker.init_collective("127.0.0.1", self.port, 2, train_world_size=1)
+            return self.worker.prepare_refit_info()
+        self.gen.init_collective(0, "127.0.0.1", self.port, 2, train_world_size=1)
+        return None
+
+    def refit(self, info=None):
+        if self.rank == 0:
+            return self.worker.broadcast_weights_for_collective(bucket_bytes=1 << 18)      # several buckets
+        self.gen.prepare_refit_info(info)
+        return self.gen.update_weights_from_collective()
+
+    def generate(self, data):
+        self.gen.prepare_for_generation()
+        out = self.gen.generate(data, greedy=True)
+        self.gen.finish_generation()
+        return out["output_ids"]
+
+
+def test_weights_reach_an_engine_outside_the_trainers_job():
+    """The reference's collective refit interface: a trainer process and a generation process that share no process group meet
+    on a communicator of their own, the trainer broadcasts packed buckets, the engine's weights become the trainer's."""
+    from rl_b200.distributed.virtual_cluster import free_port
+
+    data = _policy_data()
+    g = WorkerGroup(VirtualCluster([2], use_gpus=False), WorkerBuilder(_RefitPeer, free_port()), name="refit")
+    try:
+        before = g.get_all_worker_results(g.run_all_workers_single_data("logprobs", data))
+        assert not torch.allclose(before[0], before[1], atol=1e-3)                     # different seeds, different policies
+        info = g.get_all_worker_results(g.run_all_workers_single_data("connect"))[0]
+        assert "model.embed_tokens.weight" in info or len(info) > 0
+        sent, ok = g.get_all_worker_results(g.run_all_workers_multiple_data("refit", [None, info]))
+        assert sent > 1_000_000 and ok is True
+        after = g.get_all_worker_results(g.run_all_workers_single_data("logprobs", data))
+        assert torch.allclose(after[0], after[1], atol=1e-6) and torch.allclose(after[0], before[0], atol=1e-6)
+        out = g.run_single_worker_single_data("generate", 1, data).result()
+        assert out.shape[0] == 8
+    finally:
+        g.shutdown()

@@ -71,6 +71,36 @@ def calculate_rewards(batch: BatchedDataDict, task_to_env: dict[str, Environment
     return EnvironmentReturn(obs, meta, stops, rewards if rewards is not None else torch.zeros(0), term, answers)
 
 
+def environment_metrics(batch: BatchedDataDict, task_to_env: dict[str, EnvironmentInterface]) -> dict[str, float]:
+    """Every environment's own view of the finished batch (``global_post_process_and_metrics``: accuracy, properly-ended
+    fraction, pass@samples...), per task: ``<task>/<metric>``, and without the prefix when the batch has one task only
+    (nemo_rl/experience/rollouts.py runs the same hook after its rollouts)."""
+    tasks = batch.get("task_name")
+    if tasks is None or "total_reward" not in batch:
+        return {}
+    by_task: dict[str, list[int]] = {}
+    for i, t in enumerate(tasks):
+        by_task.setdefault(t, []).append(i)
+    out: dict[str, float] = {}
+    for task, idx in by_task.items():
+        env = task_to_env.get(task)
+        hook = getattr(env, "global_post_process_and_metrics", None)
+        if hook is None:
+            continue
+        sub = batch.select_indices(idx)
+        try:
+            res = hook(sub)
+        except Exception:      # a metrics hook must never cost the step its samples
+            continue
+        m = res[1] if isinstance(res, tuple) and len(res) == 2 else {}
+        for k, v in (m or {}).items():
+            if isinstance(v, (int, float)):
+                out[f"{task}/{k}"] = float(v)
+                if len(by_task) == 1:
+                    out[k] = float(v)
+    return out
+
+
 def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, task_to_env: dict[str, EnvironmentInterface],
                            max_seq_len: int, max_rollout_turns: int = 1, greedy: bool = False,
                            pad_token_id: int = 0) -> tuple[BatchedDataDict, dict[str, Any]]:
@@ -142,7 +172,9 @@ def run_multi_turn_rollout(generation, input_batch: BatchedDataDict, tokenizer, 
     if routed is not None:
         batch["routed_experts"] = routed
     batch["length"] = torch.tensor([sum(int(m["token_ids"].numel()) for m in log) for log in batch["message_log"]], dtype=torch.long)
+    env_metrics = environment_metrics(batch, task_to_env)
     metrics = {
+        **env_metrics,
         "total_turns": int(turns.sum()),
         "avg_turns_per_sample": float(turns.float().mean()) if n else 0.0,
         "max_turns_per_sample": int(turns.max()) if n else 0,

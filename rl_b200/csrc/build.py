@@ -96,6 +96,12 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_v: bool = False)
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    try:      # what the library was built from, so that a stale library can be told from its sources at load time
+        from rl_b200.tools.fingerprint import source_hash
+
+        Path(str(LIB) + ".sources").write_text(source_hash())
+    except Exception:
+        pass
     return LIB
 
 

@@ -73,6 +73,31 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+def _warn_if_stale() -> None:
+    """The build records a hash of the native sources beside the library; when the sources have changed since, say so once
+    (``RLB_STRICT_NATIVE=1``: refuse to run). The analogue of the reference's container fingerprint check at import
+    (nemo_rl/__init__.py:98-229): the failure it guards against here is a library older than the code that calls it."""
+    try:
+        stamp = _LIB_PATH.with_name(_LIB_PATH.name + ".sources")
+        if not stamp.exists():
+            return
+        from rl_b200.tools.fingerprint import source_hash
+
+        built, now = stamp.read_text().strip(), source_hash()
+        if built and built != now:
+            msg = (f"{_LIB_PATH.name} was built from other sources (built {built}, sources now {now}): "
+                   "rebuild with `python -m rl_b200.csrc.build`")
+            if os.environ.get("RLB_STRICT_NATIVE", "0") == "1":
+                raise NativeLibraryError(msg)
+            import warnings
+
+            warnings.warn(msg, RuntimeWarning, stacklevel=3)
+    except NativeLibraryError:
+        raise
+    except Exception:
+        pass
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
@@ -82,6 +107,7 @@ def lib() -> C.CDLL:
                 "(the CUDA path never falls back to eager PyTorch)"
             )
         _lib = C.CDLL(str(_LIB_PATH))
+        _warn_if_stale()
         for name, sig in list(_SIGS.items()):
             try:
                 fn = getattr(_lib, name)

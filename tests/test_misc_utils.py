@@ -222,3 +222,25 @@ def test_small_tools(tmp_path, capsys):
     assert (tmp_path / "proj" / "code_snapshots" / "exp1" / "pkg" / "a.py").exists() and not os.path.exists(os.path.join(snap, "data.bin"))
     (src / "pkg" / "a.py").write_text("x = 2\n")
     assert code_snapshot.snapshot("exp1", str(src)) == snap and open(os.path.join(snap, "pkg", "a.py")).read() == "x = 1\n"
+
+
+def test_stale_native_library_is_reported(tmp_path, monkeypatch):
+    from rl_b200.ops import lib as L
+    from rl_b200.tools.fingerprint import source_hash
+
+    fake = tmp_path / "_C.so"
+    fake.write_bytes(b"")
+    monkeypatch.setattr(L, "_LIB_PATH", fake)
+    L._warn_if_stale()                                           # no record beside the library: nothing to compare
+    (tmp_path / "_C.so.sources").write_text(source_hash())
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        L._warn_if_stale()                                       # built from the current sources: silent
+    (tmp_path / "_C.so.sources").write_text("0123456789abcdef")
+    with pytest.warns(RuntimeWarning, match="rebuild"):
+        L._warn_if_stale()
+    monkeypatch.setenv("RLB_STRICT_NATIVE", "1")
+    with pytest.raises(L.NativeLibraryError):
+        L._warn_if_stale()

@@ -59,7 +59,6 @@ def megatron_to_hf(state: dict[str, torch.Tensor], cfg: ModelConfig) -> Iterator
         yield "model.norm.weight", state["decoder.final_layernorm.weight"]
     if get("output_layer.weight") is not None and not cfg.tie_word_embeddings:
         yield "lm_head.weight", state["output_layer.weight"][: cfg.vocab_size]
-    f = cfg.intermediate_size
     for n in range(cfg.num_hidden_layers):
         mp, hp = f"decoder.layers.{n}", f"model.layers.{n}"
         qkv = get(f"{mp}.self_attention.linear_qkv.weight")
@@ -93,7 +92,6 @@ def megatron_to_hf(state: dict[str, torch.Tensor], cfg: ModelConfig) -> Iterator
                 yield f"{hp}.mlp.experts.{e}.gate_proj.weight", w1[: w1.shape[0] // 2]
                 yield f"{hp}.mlp.experts.{e}.up_proj.weight", w1[w1.shape[0] // 2 :]
                 yield f"{hp}.mlp.experts.{e}.down_proj.weight", w2
-    _ = f
 
 
 def hf_to_megatron(hf: dict[str, torch.Tensor], cfg: ModelConfig) -> dict[str, torch.Tensor]:

@@ -27,7 +27,7 @@ def list_files(root: str) -> list[str]:
         pass
     files = []
     for d, dirs, fs in os.walk(root):
-        dirs[:] = [x for x in dirs if not x.startswith(".") and x not in ("code_snapshots", "__pycache__", "results", "logs", "gpurun_out", "_work")]
+        dirs[:] = [x for x in dirs if not x.startswith(".") and x not in ("code_snapshots", "__pycache__", "results", "logs", "build")]
         files += [os.path.relpath(os.path.join(d, f), root) for f in fs if f.endswith(SOURCE_SUFFIXES)]
     return files
 

@@ -30,7 +30,7 @@ from rl_b200.distributed.health import HealthPolicy, HealthTracker, ShardState, 
 from rl_b200.utils.timer import Timer
 
 SC_DEFAULTS = dict(max_trajectory_age_steps=1, rollout_ahead_batches=2, pump_mode="interleaved", stall_timeout_s=600.0,
-                   max_generation_failures=3, poll_s=0.01)
+                   max_generation_failures=3, poll_s=0.01, probe_interval_s=30.0, probe_prompt_tokens=4, restart_dead_engine=True)
 
 
 class ControllerStalled(RuntimeError):
@@ -62,7 +62,10 @@ class SingleController:
         self._error: Optional[BaseException] = None
         self.health = HealthTracker(1, HealthPolicy(dead_after_failures=int(sc["max_generation_failures"])))
         self.watchdog = StallWatchdog(float(sc["stall_timeout_s"]), on_stall=self._on_stall)
-        self.stats = dict(rollout_batches=0, samples_stored=0, samples_trained=0, dropped_stale=0, generation_failures=0)
+        self.stats = dict(rollout_batches=0, samples_stored=0, samples_trained=0, dropped_stale=0, generation_failures=0,
+                          weight_syncs=0, weight_sync_s=0.0, probes=0, probe_failures=0, engine_restarts=0)
+        self.engine_version = -1           # the weight version the engine serves (set by the weight-sync pump)
+        self._last_probe = time.monotonic()
         self.use_ref = loss_fn.cfg["reference_policy_kl_penalty"] != 0 and policy.ref_flat is not None
         assert loss_fn.cfg["use_importance_sampling_correction"] or int(sc["max_trajectory_age_steps"]) == 0, \
             "off-policy trajectories need loss_fn.use_importance_sampling_correction=true"
@@ -82,10 +85,8 @@ class SingleController:
             return 0
         with self.engine_lock:
             try:
-                if self._refit_needed:
-                    refit_policy_generation(self.policy, self.generation, self.timer)
-                    self._refit_needed = False
-                version = self.version
+                self._sync_weights_locked()      # (no-op when the weight-sync pump already brought the engine up to date)
+                version = self.engine_version
                 traj, _ = _collect(self.policy, self.generation, batch, self.tokenizer, self.envs, self.cfg, self.pad, self.timer)
                 self.generation.finish_generation()
                 self.health.report_success(0)
@@ -111,6 +112,92 @@ class SingleController:
         self.stats["samples_stored"] += len(recs)
         self.watchdog.progress()
         return len(recs)
+
+    # ------------------------------------------------------------------ weight-sync pump
+    def _sync_weights_locked(self) -> bool:
+        if not self._refit_needed and self.engine_version == self.version:
+            return False
+        t0 = time.perf_counter()
+        refit_policy_generation(self.policy, self.generation, self.timer)
+        self._refit_needed = False
+        self.engine_version = self.version
+        self.stats["weight_syncs"] += 1
+        self.stats["weight_sync_s"] += time.perf_counter() - t0
+        return True
+
+    def sync_weights_once(self, blocking: bool = False) -> bool:
+        """Brings the engine to the trainer's current weight version as soon as the engine is free, instead of at the start of
+        the next rollout: the rollout pump then finds a current engine and generation starts without the refit in front of it
+        (role of the controller's weight-sync pump, nemo_rl/algorithms/single_controller.py:1607). Returns whether it synced."""
+        if not self._refit_needed and self.engine_version == self.version:
+            return False
+        if not self.engine_lock.acquire(blocking=blocking):
+            return False
+        try:
+            return self._sync_weights_locked()
+        except Exception as e:
+            self.stats["generation_failures"] += 1
+            self.health.report_failure(0, f"weight sync: {type(e).__name__}: {e}")
+            return False
+        finally:
+            self.engine_lock.release()
+
+    # ------------------------------------------------------------------ fleet probe pump
+    def probe_once(self, force: bool = False) -> Optional[bool]:
+        """A cheap liveness check of the generation side between rollouts (a few tokens through the engine, or the engine's own
+        ``health_check`` when it has one): failures feed the same health tracker the rollouts report to, so a dead engine is
+        found before a whole prompt batch is spent on it, and is restarted (``generation.restart()`` when available, else
+        sleep / wake) when ``restart_dead_engine`` (nemo_rl/algorithms/single_controller.py:1311). None: not due, or busy."""
+        now = time.monotonic()
+        if not force and now - self._last_probe < float(self.sc["probe_interval_s"]):
+            return None
+        if not self.engine_lock.acquire(blocking=False):
+            return None
+        try:
+            self._last_probe = now
+            self.stats["probes"] += 1
+            try:
+                hc = getattr(self.generation, "health_check", None)
+                if hc is not None:
+                    ok = bool(hc())
+                else:
+                    from rl_b200.distributed.batched_data_dict import BatchedDataDict
+
+                    n = int(self.sc["probe_prompt_tokens"])
+                    self._sync_weights_locked()
+                    out = self.generation.generate(BatchedDataDict(input_ids=torch.full((1, n), max(self.pad - 1, 0), dtype=torch.long),
+                                                                   input_lengths=torch.tensor([n])), greedy=True)
+                    self.generation.finish_generation()
+                    ok = int(out["generation_lengths"][0]) > 0
+                if not ok:
+                    raise RuntimeError("the engine answered the probe with nothing")
+                self.health.report_success(0)
+                return True
+            except Exception as e:
+                self.stats["probe_failures"] += 1
+                state = self.health.report_failure(0, f"probe: {type(e).__name__}: {e}")
+                if state == ShardState.DEAD and self.sc["restart_dead_engine"]:
+                    self._restart_engine()
+                return False
+        finally:
+            self.engine_lock.release()
+
+    def _restart_engine(self) -> None:
+        if self.health.begin_restart(0) != ShardState.RESTARTING:      # restart budget spent: the shard is retired
+            return
+        ok = True
+        try:
+            if hasattr(self.generation, "restart"):
+                self.generation.restart()
+            else:
+                self.generation.shutdown()
+                self.generation.prepare_for_generation()
+            self._refit_needed = True
+            self.engine_version = -1
+            self.stats["engine_restarts"] += 1
+        except Exception:
+            ok = False
+        self.health.finish_restart(0, ok, weight_version=self.health.current_weight_version)
 
     # ------------------------------------------------------------------ train pump
     def _select(self) -> Optional[list[SampleMeta]]:
@@ -161,6 +248,7 @@ class SingleController:
         self.stats["samples_trained"] += len(keys)
         metrics = _aggregate_train_metrics(res)
         metrics.update(reward=float(rewards.mean()), trajectory_age=float(age), weight_version=float(self.version),
+                       engine_version=float(self.engine_version), weight_syncs=float(self.stats["weight_syncs"]),
                        stored_samples=float(self.plane.stats().get("resident_samples", 0)))
         self.save_state.update(total_steps=self.steps, current_step=self.steps, weight_version=self.version)
         if self.logger is not None:
@@ -209,8 +297,19 @@ class SingleController:
                         self._error = e
                         self._stop.set()
 
+                def side_pumps():     # weight sync as soon as the engine is free; a health probe every probe_interval_s
+                    while not self._stop.is_set():
+                        try:
+                            self.sync_weights_once()
+                            self.probe_once()
+                        except BaseException as e:
+                            self._error = e
+                            self._stop.set()
+                        time.sleep(float(self.sc["poll_s"]))
+
                 t = threading.Thread(target=pump, daemon=True, name="rlb-rollout-pump")
                 t.start()
+                threading.Thread(target=side_pumps, daemon=True, name="rlb-sync-probe-pumps").start()
                 while self.steps < max_steps and not self._stop.is_set():
                     out = self.train_once()
                     if out is None:
@@ -226,6 +325,8 @@ class SingleController:
                     while self._pending_batches() < ahead and self.rollout_once() > 0:
                         pass
                     out = self.train_once()
+                    self.sync_weights_once(blocking=True)
+                    self.probe_once()
                     if out is None:
                         if self._exhausted:
                             break

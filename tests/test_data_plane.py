@@ -148,6 +148,34 @@ def test_single_controller_drops_stale_and_reports_stall(tmp_path):
         sc2.run()
 
 
+def test_single_controller_weight_sync_and_fleet_probe_pumps(tmp_path):
+    """The weight-sync pump brings the engine to the trainer's version as soon as the engine is free; the probe pump checks the
+    engine between rollouts, counts failures in the same health tracker, and restarts an engine that died."""
+    from rl_b200.distributed.health import ShardState
+
+    sc, hist = _controller(tmp_path, "interleaved", steps=2)
+    assert sc.engine_version == -1 and sc.sync_weights_once(blocking=True) and sc.engine_version == 0 and not sc.sync_weights_once()
+    assert sc.rollout_once() > 0 and sc.train_once() is not None
+    assert sc.version == 1 and sc.engine_version == 0                  # the trainer moved on, the engine has not yet
+    assert sc.sync_weights_once(blocking=True) and sc.engine_version == 1 and sc.stats["weight_syncs"] == 2
+    assert sc.probe_once() is None                                     # not due yet
+    assert sc.probe_once(force=True) is True and sc.stats["probes"] == 1 and sc.health.state(0) == ShardState.HEALTHY
+    with sc.engine_lock:
+        assert sc.probe_once(force=True) is None                       # the engine is busy: the probe does not queue behind it
+    # an engine that stops answering: failures add up to DEAD, the pump restarts it and rollouts go on
+    calls = dict(restart=0)
+    sc.generation.health_check = lambda: (_ for _ in ()).throw(RuntimeError("no answer"))
+    sc.generation.restart = lambda: calls.__setitem__("restart", calls["restart"] + 1)
+    for _ in range(int(sc.sc["max_generation_failures"])):
+        assert sc.probe_once(force=True) is False
+    assert calls["restart"] == 1 and sc.stats["engine_restarts"] == 1 and sc.stats["probe_failures"] == 3
+    assert sc.health.state(0) == ShardState.HEALTHY and sc.engine_version == -1
+    del sc.generation.health_check
+    assert sc.probe_once(force=True) is True and sc.engine_version == 1   # the probe re-synced the restarted engine
+    sc.run()
+    assert sc.steps == 2 and hist[-1]["engine_version"] >= 1 and hist[-1]["weight_syncs"] >= 3
+
+
 def test_observed_data_plane_counts_events():
     dp = create_data_plane({"backend": "local", "observe": True})
     dp.put("a", {"x": torch.arange(3)})

@@ -12,7 +12,7 @@ from typing import Callable, Optional
 import torch
 
 from rl_b200.algorithms.advantage_estimator import GAEAdvantageEstimator
-from rl_b200.algorithms.grpo import (GRPO_DEFAULTS, _aggregate_train_metrics, _all_reduce_scalars, _is_main, _ShardedPromptLoader, _world,
+from rl_b200.algorithms.grpo import (GRPO_DEFAULTS, _aggregate_train_metrics, compute_and_apply_seq_logprob_error_masking, _all_reduce_scalars, _is_main, _ShardedPromptLoader, _world,
                                      build_train_data, refit_policy_generation, save_checkpoint)
 from rl_b200.algorithms.loss.loss_functions import ClippedPGLossFn, MseValueLossFn
 from rl_b200.algorithms.reward_functions import apply_reward_shaping, scale_rewards
@@ -28,6 +28,12 @@ PPO_DEFAULTS = dict(
     val_period=0, seed=42, gamma=1.0, gae_lambda=0.95, lambda_critic=None, length_adaptive_alpha=None,
     normalize_advantages=True, value_clip=0.2, num_value_warmup_steps=0, policy_epochs=1, value_epochs=1,
     reward_shaping=None, reward_scaling=None,
+    # names of the reference's PPOConfig (nemo_rl/algorithms/ppo.py:168-216) that map onto the ones above or add behaviour
+    ppo_epochs=None,                    # passes over the batch for the policy AND the critic (overrides policy_epochs / value_epochs)
+    policy_training_start_step=None,    # the critic trains alone before this step (overrides num_value_warmup_steps)
+    overlong_filtering=False,           # truncated samples do not contribute to either loss
+    seq_logprob_error_threshold=None,   # sequences whose trainer / engine log-probabilities disagree by more are masked
+    val_at_start=False, val_at_end=False, val_batch_size=256,
 )
 
 
@@ -44,6 +50,10 @@ def setup(cfg: dict, tokenizer, dataset, val_dataset, task_to_env, model_cfg=Non
     rank, world = _world()
     p = dict(PPO_DEFAULTS)
     p.update(cfg.get("ppo") or {})
+    if p.get("ppo_epochs"):
+        p["policy_epochs"] = p["value_epochs"] = int(p["ppo_epochs"])
+    if p.get("policy_training_start_step") is not None:
+        p["num_value_warmup_steps"] = int(p["policy_training_start_step"])
     cfg["ppo"] = p
     set_seed(p["seed"] + rank)
     logger = Logger(cfg.get("logger"), is_main=_is_main())
@@ -95,12 +105,15 @@ def ppo_train(policy, value, generation, loader, tokenizer, policy_loss, value_l
                 repeated = scale_rewards(repeated, p.get("reward_scaling"))
                 repeated = apply_reward_shaping(repeated, p.get("reward_shaping"))
                 rewards = repeated["total_reward"].float()
+                if p.get("overlong_filtering"):
+                    repeated["loss_multiplier"] = repeated["loss_multiplier"] * (~repeated["truncated"].bool()).float()
                 train_data = build_train_data(repeated, pad)
                 with timer.time("policy_and_reference_logprobs"):
                     policy.prepare_for_lp_inference()
                     train_data["prev_logprobs"] = policy.get_logprobs(train_data)["logprobs"]
                     train_data["reference_policy_logprobs"] = (policy.get_reference_policy_logprobs(train_data)["reference_logprobs"]
                                                                if use_ref else torch.zeros_like(train_data["prev_logprobs"]))
+                mask_metrics = compute_and_apply_seq_logprob_error_masking(train_data, p.get("seq_logprob_error_threshold"))
                 with timer.time("value_inference"):
                     old_values = value.score(train_data)["values"]
                 with timer.time("advantage_calculation"):
@@ -118,6 +131,7 @@ def ppo_train(policy, value, generation, loader, tokenizer, policy_loss, value_l
                         vres = value.train(train_data, value_loss, gbs=pcfg["train_global_batch_size"], mbs=pcfg["train_micro_batch_size"])
             total_steps += 1
             metrics = _aggregate_train_metrics(res) if res is not None else {}
+            metrics.update(mask_metrics)
             vmetrics = _aggregate_train_metrics(vres)
             metrics.update({f"value_{k}": v for k, v in vmetrics.items() if k in ("loss", "grad_norm", "value_mean", "value_clip_frac")})
             counts = _all_reduce_scalars({"r": float(rewards.sum()), "n": float(rewards.numel()), "tok": float(train_data["input_lengths"].sum()),

@@ -269,7 +269,8 @@ DPO = dict(SFT, reference_policy_kl_penalty=F(float, int), preference_average_lo
 
 PPO = dict(GRPO, critic=F(dict), gamma=F(float, int), value_clip=F(float, int), critic_warmup_steps=F(int), vapo=F(dict),
            gae_lambda=F(float, int), lambda_critic=F(float, int), length_adaptive_alpha=F(float, int), normalize_advantages=F(bool),
-           num_value_warmup_steps=F(int), policy_epochs=F(int), value_epochs=F(int))
+           num_value_warmup_steps=F(int), policy_epochs=F(int), value_epochs=F(int), ppo_epochs=F(int), policy_training_start_step=F(int),
+           async_ppo=F(dict))
 PPO["lambda"] = F(float, int)
 
 DISTILLATION = dict(num_prompts_per_step=F(int), num_generations_per_prompt=F(int), max_rollout_turns=F(int), max_num_steps=F(int),

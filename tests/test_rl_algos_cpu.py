@@ -32,6 +32,36 @@ def test_ppo_runs_and_value_loss_falls(tmp_path):
     assert hist[-1]["value_loss"] <= hist[0]["value_loss"] + 1e-3
 
 
+def test_ppo_reference_config_names(tmp_path):
+    """``ppo_epochs`` / ``policy_training_start_step`` / ``overlong_filtering`` / ``seq_logprob_error_threshold`` of the reference's
+    PPO config: the critic trains alone before the start step, truncated samples leave the losses, the masking metric is logged."""
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+    cfg = {"ppo": dict(num_prompts_per_step=8, num_generations_per_prompt=1, max_num_steps=3, seed=0, ppo_epochs=2, policy_training_start_step=2,
+                       seq_logprob_error_threshold=10.0), "loss_fn": {},
+           "policy": _policy_cfg(), "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    policy, value, gen, loader, pl, vl, logger, ck, ss, cfg = ppo.setup(cfg, None, ds, None, env, model_cfg=_mc())
+    assert cfg["ppo"]["policy_epochs"] == cfg["ppo"]["value_epochs"] == 2 and cfg["ppo"]["num_value_warmup_steps"] == 2
+    w0 = policy.flat.flat.clone()
+    hist = []
+
+    def cb(step, m):
+        hist.append(m["train"])
+        if step == 2:      # two critic-only steps: the policy has not moved
+            assert torch.equal(policy.flat.flat, w0)
+
+    ppo.ppo_train(policy, value, gen, loader, None, pl, vl, env, logger, ck, ss, cfg, step_callback=cb)
+    assert len(hist) == 3 and "loss" not in hist[0] and "loss" in hist[2] and not torch.equal(policy.flat.flat, w0)
+    assert all("seq_logprob_error_masked_fraction" in h and h["seq_logprob_error_masked_fraction"] == 0.0 for h in hist)
+    assert any(h["value_loss"] > 0.0 for h in hist)
+    # every sample is cut by the 8-token limit (no stop token): with overlong filtering nothing is left to train on
+    cfg2 = {"ppo": dict(num_prompts_per_step=8, num_generations_per_prompt=1, max_num_steps=1, seed=0, overlong_filtering=True), "loss_fn": {},
+            "policy": _policy_cfg(), "logger": dict(log_dir=str(tmp_path)), "checkpointing": dict(enabled=False)}
+    policy, value, gen, loader, pl, vl, logger, ck, ss, cfg2 = ppo.setup(cfg2, None, ds, None, env, model_cfg=_mc())
+    out = ppo.ppo_train(policy, value, gen, loader, None, pl, vl, env, logger, ck, ss, cfg2)
+    assert out["train"]["value_loss"] == 0.0 and out["train"]["loss"] == 0.0
+
+
 def test_distillation_pulls_student_to_teacher(tmp_path):
     ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
     env = {"synthetic": TokenFractionEnv({})}

@@ -12,7 +12,7 @@ from typing import Callable, Optional
 import torch
 
 from rl_b200.algorithms.grpo import (_aggregate_train_metrics, _all_reduce_scalars, _ShardedPromptLoader, _is_main, _world, build_train_data,
-                                     refit_policy_generation, save_checkpoint)
+                                     refit_policy_generation, save_checkpoint, validate)
 from rl_b200.algorithms.loss.loss_functions import DistillationLossFn
 from rl_b200.algorithms.utils import set_seed
 from rl_b200.experience.rollouts import run_multi_turn_rollout
@@ -21,7 +21,8 @@ from rl_b200.utils.logger import Logger
 from rl_b200.utils.timer import Timer
 
 DISTILLATION_DEFAULTS = dict(num_prompts_per_step=32, num_generations_per_prompt=1, max_num_epochs=1, max_num_steps=1_000_000,
-                             max_rollout_turns=1, topk_logits_k=64, seed=42, val_period=0)
+                             max_rollout_turns=1, topk_logits_k=64, seed=42, val_period=0, val_batch_size=64, val_at_start=False,
+                             val_at_end=False, max_val_samples=512, val_num_generations_per_prompt=1)
 
 
 def setup(cfg: dict, tokenizer, dataset, val_dataset, task_to_env, student_cfg=None, teacher_cfg=None, teacher=None):
@@ -38,10 +39,22 @@ def setup(cfg: dict, tokenizer, dataset, val_dataset, task_to_env, student_cfg=N
     set_seed(d["seed"] + rank)
     logger = Logger(cfg.get("logger"), is_main=_is_main())
     checkpointer = CheckpointManager(cfg.get("checkpointing"))
-    save_state = {"current_step": 0, "total_steps": 0, "current_epoch": 0}
+    save_state = {"current_step": 0, "total_steps": 0, "current_epoch": 0, "val_reward": -1e9, "consumed_samples": 0, "total_valid_tokens": 0}
+    resume = checkpointer.get_resume_paths() if checkpointer.enabled else None
+    if resume:
+        save_state.update(checkpointer.load_training_info(resume["root"]) or {})
     loader = _ShardedPromptLoader(dataset, d["num_prompts_per_step"], rl_collate_fn, bool((cfg.get("data") or {}).get("shuffle", True)),
                                   d["seed"], rank, world)
+    if resume and resume.get("dataloader"):
+        loader.load_state_dict(torch.load(resume["dataloader"], weights_only=False))
     student = PolicyWorker(cfg["policy"], model_cfg=student_cfg, tokenizer=tokenizer, init_reference_model=False, seed=d["seed"])
+    if resume and resume.get("weights"):
+        student.load_checkpoint(resume["weights"], resume.get("optimizer"))
+    # validation prompts (the student's accuracy on held-out tasks is the number distillation is judged by)
+    loader.val_loader = None      # (rides on the training loader: the tuple this function returns is part of the entrypoints' contract)
+    if val_dataset is not None and len(val_dataset):
+        vb = max(world, (min(d["val_batch_size"], len(val_dataset)) // world) * world)
+        loader.val_loader = _ShardedPromptLoader(val_dataset, vb, rl_collate_fn, False, 0, rank, world)
     if teacher is None:
         teacher = PolicyWorker(cfg.get("teacher") or cfg["policy"], model_cfg=teacher_cfg, tokenizer=tokenizer, init_optimizer=False,
                                init_reference_model=False, seed=d["seed"] + 17)
@@ -59,6 +72,13 @@ def distillation_train(student, teacher, generation, loader, tokenizer, loss_fn,
     n_gen = d["num_generations_per_prompt"]
     total_steps, epoch = save_state["total_steps"], save_state["current_epoch"]
     last: dict = {}
+    val_loader = getattr(loader, "val_loader", None)
+    # the validation routine is GRPO's (rollouts on held-out prompts, mean reward): give it the keys it reads
+    vcfg = dict(cfg, grpo=dict(val_num_generations_per_prompt=d["val_num_generations_per_prompt"], max_rollout_turns=d["max_rollout_turns"],
+                               max_val_samples=d["max_val_samples"] or 1 << 30))
+    if val_loader is not None and d["val_at_start"] and total_steps == 0:
+        val, _ = validate(student, generation, val_loader, tokenizer, task_to_env, 0, vcfg, logger)
+        save_state["val_reward"] = val.get("accuracy", -1e9)
     while epoch < d["max_num_epochs"] and total_steps < d["max_num_steps"]:
         for batch in loader:
             if total_steps >= d["max_num_steps"]:
@@ -84,7 +104,14 @@ def distillation_train(student, teacher, generation, loader, tokenizer, loss_fn,
             total_steps += 1
             metrics = _aggregate_train_metrics(res)
             metrics.update({k: v for k, v in rollout_metrics.items() if isinstance(v, (int, float))})
-            save_state.update(current_step=total_steps, total_steps=total_steps, current_epoch=epoch)
+            is_last = total_steps >= d["max_num_steps"]
+            if val_loader is not None and ((d["val_period"] > 0 and total_steps % d["val_period"] == 0) or (is_last and d["val_at_end"])):
+                val, _ = validate(student, generation, val_loader, tokenizer, task_to_env, total_steps, vcfg, logger)
+                save_state["val_reward"] = val.get("accuracy", save_state["val_reward"])
+                metrics["val_accuracy"] = save_state["val_reward"]
+            save_state.update(current_step=total_steps, total_steps=total_steps, current_epoch=epoch,
+                              consumed_samples=save_state["consumed_samples"] + repeated.size * world,
+                              total_valid_tokens=save_state["total_valid_tokens"] + int(train_data["token_mask"].sum()) * world)
             timing = timer.get_timing_metrics("sum")
             ck = cfg.get("checkpointing") or {}
             if checkpointer.enabled and ck.get("save_period") and total_steps % ck["save_period"] == 0:

@@ -32,6 +32,36 @@ def test_ppo_runs_and_value_loss_falls(tmp_path):
     assert hist[-1]["value_loss"] <= hist[0]["value_loss"] + 1e-3
 
 
+def test_distillation_validates_counts_and_resumes(tmp_path):
+    """Validation on held-out prompts at start / every period / at the end, consumed-sample and token counters, and a resume
+    from the last checkpoint that continues the step count with the student's weights."""
+    ds = RandomTokenPromptDataset(256, 4, 8, 32, seed=0)
+    val = RandomTokenPromptDataset(16, 4, 8, 32, seed=1)
+    env = {"synthetic": TokenFractionEnv({"target_token_id": 7})}
+
+    def cfg_(steps):
+        return {"distillation": dict(num_prompts_per_step=8, max_num_steps=steps, topk_logits_k=8, seed=0, val_period=2, val_at_start=True,
+                                     val_at_end=True, val_batch_size=8, max_val_samples=16),
+                "loss_fn": dict(kl_type="forward"), "policy": _policy_cfg(1e-2), "logger": dict(log_dir=str(tmp_path / "logs")),
+                "checkpointing": dict(enabled=True, checkpoint_dir=str(tmp_path / "ckpt"), save_period=2, keep_top_k=None)}
+
+    student, teacher, gen, loader, loss_fn, logger, ck, ss, cfg = distillation.setup(cfg_(3), None, ds, val, env, student_cfg=_mc(), teacher_cfg=_mc())
+    hist = []
+    distillation.distillation_train(student, teacher, gen, loader, None, loss_fn, env, logger, ck, ss, cfg,
+                                    step_callback=lambda s, m: hist.append(m["train"]))
+    assert len(hist) == 3 and "val_accuracy" in hist[1] and "val_accuracy" in hist[2] and "val_accuracy" not in hist[0]
+    assert ss["consumed_samples"] == 24 and ss["total_valid_tokens"] > 0 and ss["val_reward"] >= 0.0
+    w = student.flat.flat.clone()
+    # a new run finds step_2 and goes on from there
+    student2, teacher2, gen2, loader2, loss_fn2, logger2, ck2, ss2, cfg2 = distillation.setup(cfg_(4), None, ds, val, env, student_cfg=_mc(),
+                                                                                            teacher_cfg=_mc())
+    assert ss2["total_steps"] == 2 and ss2["consumed_samples"] == 16 and not torch.equal(student2.flat.flat, w)
+    steps = []
+    distillation.distillation_train(student2, teacher2, gen2, loader2, None, loss_fn2, env, logger2, ck2, ss2, cfg2,
+                                    step_callback=lambda s, m: steps.append(s))
+    assert steps == [3, 4]
+
+
 def test_ppo_reference_config_names(tmp_path):
     """``ppo_epochs`` / ``policy_training_start_step`` / ``overlong_filtering`` / ``seq_logprob_error_threshold`` of the reference's
     PPO config: the critic trains alone before the start step, truncated samples leave the losses, the masking metric is logged."""

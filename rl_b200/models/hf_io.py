@@ -21,13 +21,16 @@ from .transformer import CausalLM
 
 
 def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offset: int = 0, num_local_layers: Optional[int] = None,
-                first_stage: bool = True, last_stage: bool = True):
+                first_stage: bool = True, last_stage: bool = True, layer_ids=None):
     """Rows of (hf_name, local_name, local_rows or None, expert index or None, hf_slice or None).
 
     The HF tensor, restricted to ``hf_slice = (dim, start, length)`` when this rank holds a tensor-parallel shard of it,
     is rows ``local_rows`` of the local parameter (of global expert ``e`` when the local parameter is expert-stacked).
-    Local layer ``j`` is HF layer ``layer_offset + j`` (pipeline stages own contiguous layer ranges)."""
+    Local layer ``j`` is HF layer ``layer_offset + j`` (pipeline stages own contiguous layer ranges), or ``layer_ids[j]`` when
+    the stage interleaves several runs of layers."""
     n_layers = cfg.num_hidden_layers - layer_offset if num_local_layers is None else num_local_layers
+    ids = list(layer_ids) if layer_ids is not None else [layer_offset + j for j in range(n_layers)]
+    n_layers = len(ids)
     tied = cfg.tie_word_embeddings and not cfg.value_head
     rows = []
     hybrid = cfg.is_hybrid     # Nemotron-H names: model.embeddings, model.norm_f, layers.N.norm + layers.N.mixer.*
@@ -54,8 +57,8 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         return (dim, tp_rank * n, n) if tp_size > 1 else None
 
     for j in range(n_layers if hybrid else 0):
-        hp, lp = f"model.layers.{layer_offset + j}", f"layers.{j}"
-        mx, kind = f"{hp}.mixer", cfg.block_type(layer_offset + j)
+        hp, lp = f"model.layers.{ids[j]}", f"layers.{j}"
+        mx, kind = f"{hp}.mixer", cfg.block_type(ids[j])
         rows.append((f"{hp}.norm.weight", f"{lp}.norm", None, None, None))
         if kind == "mamba":
             rows += [(f"{mx}.in_proj.weight", f"{lp}.mamba.in_proj", None, None, None),
@@ -93,7 +96,7 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
                 rows += [(f"{mx}.experts.{e}.up_proj.weight", f"{lp}.mlp.up_proj", None, e, None),
                          (f"{mx}.experts.{e}.down_proj.weight", f"{lp}.mlp.down_proj", None, e, None)]
     for j in range(0 if hybrid else n_layers):
-        hp, lp = f"model.layers.{layer_offset + j}", f"layers.{j}"
+        hp, lp = f"model.layers.{ids[j]}", f"layers.{j}"
         rows += [
             (f"{hp}.input_layernorm.weight", f"{lp}.input_layernorm", None, None, None),
             (f"{hp}.post_attention_layernorm.weight", f"{lp}.post_attention_layernorm", None, None, None),
@@ -129,7 +132,7 @@ def hf_name_map(cfg: ModelConfig, tp_rank: int = 0, tp_size: int = 1, layer_offs
         if cfg.sandwich_norm:
             rows += [(f"{hp}.pre_feedforward_layernorm.weight", f"{lp}.pre_feedforward_layernorm", None, None, None),
                      (f"{hp}.post_feedforward_layernorm.weight", f"{lp}.post_feedforward_layernorm", None, None, None)]
-        if cfg.layer_is_moe(layer_offset + j):
+        if cfg.layer_is_moe(ids[j]):
             f = cfg.moe_intermediate_size
             rows.append((f"{hp}.mlp.gate.weight", f"{lp}.mlp.router", None, None, None))
             if cfg.scoring_func == "sigmoid":
@@ -163,7 +166,8 @@ def _local(model: CausalLM) -> dict[str, torch.Tensor]:
 
 
 def _model_map(model: CausalLM):
-    return hf_name_map(model.cfg, model.tp.rank, model.tp.world, model.layer_offset, len(model.layers), model.first_stage, model.last_stage)
+    return hf_name_map(model.cfg, model.tp.rank, model.tp.world, model.layer_offset, len(model.layers), model.first_stage, model.last_stage,
+                       layer_ids=getattr(model, "layer_ids", None))
 
 
 def iter_hf_shards(model: CausalLM) -> Iterator[tuple[str, torch.Tensor, Optional[tuple[int, int, int]]]]:
@@ -328,12 +332,12 @@ class _SafetensorsDir:
 
 
 def load_pretrained(path: str, device="cpu", dtype: Optional[torch.dtype] = None, strict: bool = True, tp=None, ep=None,
-                    pp_rank: int = 0, pp_size: int = 1, lora: Optional[dict] = None, **cfg_overrides) -> CausalLM:
+                    pp_rank: int = 0, pp_size: int = 1, lora: Optional[dict] = None, vpp: int = 1, **cfg_overrides) -> CausalLM:
     """Builds a model (or this rank's tensor / expert / pipeline shard of it) from an HF checkpoint directory."""
     cfg = ModelConfig.from_pretrained(path, **cfg_overrides)
     from .transformer import build_model
 
-    model = build_model(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, lora=lora)
+    model = build_model(cfg, dtype=dtype, device=device, init=False, tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, lora=lora, vpp=vpp)
     if lora:
         from .transformer import LoRA
 
@@ -367,7 +371,7 @@ def iter_lora_tensors(model: CausalLM) -> Iterator[tuple[str, torch.Tensor]]:
     for mod_name, mod in model.named_modules():
         if not isinstance(mod, LoRA):
             continue
-        li = int(mod_name.split(".")[1]) + model.layer_offset
+        li = model.layer_ids[int(mod_name.split(".")[1])]
         parent = "self_attn" if ".self_attn." in mod_name else "mlp"
         row = 0
         for s, (seg, n) in enumerate(mod.segments):

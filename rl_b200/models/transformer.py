@@ -480,11 +480,13 @@ class CausalLM(nn.Module):
     Model parallelism: ``tp`` shards attention heads, MLP columns and the output vocabulary over a tensor-parallel group
     (activations between blocks are sequence parallel when ``tp.sequence_parallel``); ``ep`` shards MoE experts;
     ``pp_rank`` / ``pp_size`` keep a contiguous slice of the layers on this rank (embedding on the first stage, final
-    norm and output head on the last)."""
+    norm and output head on the last). ``vpp`` > 1 interleaves: the layers are cut into ``pp_size * vpp`` runs, run
+    ``c * pp_size + pp_rank`` is this rank's chunk ``c`` (``self.layers`` holds the chunks one after another,
+    ``self.layer_ids`` their global indices) and ``active_chunk`` selects the chunk a forward call runs."""
 
     def __init__(self, cfg: ModelConfig, dtype: Optional[torch.dtype] = None, device="cpu", init: bool = True,
                  seed: int = 0, activation_checkpointing: bool = False, tp: Optional[TP] = None, ep=None,
-                 pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None):
+                 pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None, vpp: int = 1):
         super().__init__()
         self.cfg = cfg
         self.lora_cfg = dict(lora) if (lora and lora.get("enabled", True)) else None
@@ -495,9 +497,17 @@ class CausalLM(nn.Module):
         self.cp = cp if (cp is not None and cp.world > 1) else None
         self.pp_rank, self.pp_size = pp_rank, pp_size
         L = cfg.num_hidden_layers
-        per = -(-L // pp_size)
-        self.layer_offset = pp_rank * per
-        n_local = max(0, min(L, (pp_rank + 1) * per) - self.layer_offset)
+        self.vpp = max(1, int(vpp)) if pp_size > 1 else 1
+        per = -(-L // (pp_size * self.vpp))
+        self.layer_ids, self.chunk_bounds = [], []      # global index of local layer j; [lo, hi) local range of chunk c
+        for c in range(self.vpp):
+            lo = (c * pp_size + pp_rank) * per
+            ids = list(range(lo, max(lo, min(L, lo + per))))
+            self.chunk_bounds.append((len(self.layer_ids), len(self.layer_ids) + len(ids)))
+            self.layer_ids += ids
+        self.layer_offset = self.layer_ids[0] if self.layer_ids else min(L, pp_rank * per)   # (meaningful when vpp == 1)
+        self.active_chunk: Optional[int] = None
+        n_local = len(self.layer_ids)
         self.first_stage, self.last_stage = pp_rank == 0, pp_rank == pp_size - 1
         d = cfg.hidden_size
         tpw = self.tp.world
@@ -512,7 +522,7 @@ class CausalLM(nn.Module):
         block = HybridBlock if cfg.is_hybrid else DecoderLayer
         if cfg.is_hybrid and self.tp.sequence_parallel:
             raise NotImplementedError("sequence parallelism is not available for hybrid state-space models")
-        self.layers = nn.ModuleList([block(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg, layer_idx=self.layer_offset + i)
+        self.layers = nn.ModuleList([block(cfg, dtype, device, self.tp, ep, self.cp, self.lora_cfg, layer_idx=self.layer_ids[i])
                                      for i in range(n_local)])
         self.lm_head = None
         if self.last_stage:
@@ -558,7 +568,7 @@ class CausalLM(nn.Module):
                 return True
             if leaf not in ("up_proj", "down_proj") or ".mlp." not in name or "shared_experts" in name:
                 return False
-            li = int(name.split(".")[1]) + self.layer_offset
+            li = self.layer_ids[int(name.split(".")[1])]
             return self.cfg.block_type(li) == "mlp"
         return leaf in self._TP_SHARDED and ".mlp.router" not in name and not (self.cfg.is_moe and ".mlp." in name)
 
@@ -659,6 +669,16 @@ class CausalLM(nn.Module):
         return out
 
     @property
+    def at_input(self) -> bool:
+        """The chunk about to run starts the model (it embeds the tokens)."""
+        return self.first_stage and self.active_chunk in (None, 0)
+
+    @property
+    def at_output(self) -> bool:
+        """The chunk about to run ends the model (final norm, output head, loss)."""
+        return self.last_stage and self.active_chunk in (None, self.vpp - 1)
+
+    @property
     def output_weight(self) -> torch.Tensor:
         """This rank's rows of the output projection ([V/tp, d])."""
         if self.lm_head is not None:
@@ -699,24 +719,26 @@ class CausalLM(nn.Module):
         cap = self.capture_layers
         if cap is not None:
             self.captured = {"embeds": h}
-        for i, layer in enumerate(self.layers):
+        lo, hi = (0, len(self.layers)) if self.active_chunk is None else self.chunk_bounds[self.active_chunk]
+        for i in range(lo, hi):
+            layer = self.layers[i]
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = ckpt.checkpoint(layer, h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen, use_reentrant=False)
             else:
                 h = layer(h, batch.positions, inv_freq, batch.cu_seqlens, batch.max_seqlen)
-            if cap is not None and (self.layer_offset + i) in cap:
-                self.captured[self.layer_offset + i] = h
+            if cap is not None and self.layer_ids[i] in cap:
+                self.captured[self.layer_ids[i]] = h
         return h
 
     def hidden_states(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Output of this stage: the normed final hidden states on the last stage, else the residual stream handed to
         the next stage. Rows are this rank's sequence-parallel shard when ``tp.sequence_parallel``."""
-        h = self.embed(batch) if self.first_stage else h_in
+        h = self.embed(batch) if self.at_input else h_in
         h = self.run_layers(h, batch)
         if self.sharder is not None:
             return self.sharder.run("head", lambda x: F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps), h)
-        out = F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.last_stage else h
-        if self.capture_layers is not None and self.last_stage:
+        out = F.rmsnorm(h, self.norm, self.cfg.rms_norm_eps) if self.at_output else h
+        if self.capture_layers is not None and self.at_output:
             self.captured["final"] = out
         return out
 
@@ -838,9 +860,9 @@ class CausalLM(nn.Module):
 
 def build_model(cfg: ModelConfig, device="cpu", dtype: Optional[torch.dtype] = None, seed: int = 0,
                 activation_checkpointing: bool = False, init: bool = True, tp: Optional[TP] = None, ep=None,
-                pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None) -> CausalLM:
+                pp_rank: int = 0, pp_size: int = 1, cp=None, lora: Optional[dict] = None, vpp: int = 1) -> CausalLM:
     cls = CausalLM
     if cfg.vision is not None:
         from .vision import VLMCausalLM as cls
     return cls(cfg, dtype=dtype, device=device, init=init, seed=seed, activation_checkpointing=activation_checkpointing,
-               tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp, lora=lora)
+               tp=tp, ep=ep, pp_rank=pp_rank, pp_size=pp_size, cp=cp, lora=lora, vpp=vpp)

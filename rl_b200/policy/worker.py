@@ -55,7 +55,7 @@ def _dp_info(group=None):
     return 0, 1
 
 
-def parallel_sizes(policy_cfg: dict) -> dict:
+def parallel_sizes(policy_cfg: dict, num_layers: Optional[int] = None) -> dict:
     """tp / pp / cp / ep sizes and the sequence-parallel flag from ``policy.parallel`` (or, for configs written for the
     reference, ``dtensor_cfg`` / ``megatron_cfg`` keys)."""
     par = dict(policy_cfg.get("parallel") or {})
@@ -70,11 +70,16 @@ def parallel_sizes(policy_cfg: dict) -> dict:
                 return src[a]
         return None
 
-    vpp = pick("virtual_pipeline_stages", "virtual_pipeline_model_parallel_size", "num_layers_per_virtual_pipeline_stage")
-    if vpp not in (None, 0, 1):
-        raise NotImplementedError("interleaved (virtual) pipeline stages are not available: every pipeline rank owns one contiguous run of layers")
     tp = int(pick("tensor_parallel_size", "tensor_parallel_size", "tensor_model_parallel_size") or 1)
-    return dict(tp=tp, pp=int(pick("pipeline_parallel_size", "pipeline_model_parallel_size") or 1),
+    pp = int(pick("pipeline_parallel_size", "pipeline_model_parallel_size") or 1)
+    # interleaved schedule: chunks of layers per pipeline rank, given directly or as layers per chunk (Megatron's two spellings)
+    vpp = int(pick("virtual_pipeline_stages", "virtual_pipeline_model_parallel_size") or 1)
+    per_chunk = src.get("num_layers_per_virtual_pipeline_stage")
+    if vpp <= 1 and per_chunk and num_layers:
+        vpp = max(1, int(num_layers) // (pp * int(per_chunk)))
+    if vpp > 1 and pp == 1:
+        raise ValueError("virtual pipeline stages need pipeline_parallel_size > 1")
+    return dict(tp=tp, pp=pp, vpp=max(1, vpp),
                 cp=int(pick("context_parallel_size", "context_parallel_size") or 1),
                 ep=int(pick("expert_parallel_size", "expert_model_parallel_size") or 1),
                 sequence_parallel=bool(tp > 1 and (pick("sequence_parallel", "sequence_parallel") in (None, True))))
@@ -172,7 +177,14 @@ class PolicyWorker:
         self.cp = CP.from_state(st)
         lora = cfg.get("lora_cfg") or (cfg.get("dtensor_cfg") or {}).get("lora_cfg") or ((cfg.get("megatron_cfg") or {}).get("peft"))
         self.lora_cfg = dict(lora) if (lora and lora.get("enabled")) else None
-        mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp, cp=self.cp)
+        n_layers = model_cfg.num_hidden_layers if model_cfg is not None else None
+        if n_layers is None and weights_path and os.path.exists(os.path.join(weights_path, "config.json")):
+            import json
+
+            with open(os.path.join(weights_path, "config.json")) as f:
+                n_layers = json.load(f).get("num_hidden_layers")
+        self.vpp = parallel_sizes(cfg, n_layers)["vpp"] if st.pp > 1 else 1
+        mp = dict(tp=self.tp, ep=self.ep if self.ep.world > 1 else None, pp_rank=st.pp_rank, pp_size=st.pp, cp=self.cp, vpp=self.vpp)
         if weights_path:
             from rl_b200.models.hf_io import load_pretrained
 
@@ -298,7 +310,7 @@ class PolicyWorker:
 
             div = self.tp.world if (self.tp.world > 1 and self.tp.sequence_parallel) else 1
             self.pipeline = PipelineRunner(self.model, st.pp_group, st.pp_rank, st.pp, model_cfg.hidden_size, dtype, self.device,
-                                           rows_of=lambda item: int(item[0].input_ids.numel()) // div)
+                                           rows_of=lambda item: int(item[0].input_ids.numel()) // div, vpp=self.vpp)
         self.generation = None
         self.temperature = 1.0
         self.train_top_k, self.train_top_p = None, 1.0   # the sampler's filters, mirrored in the training log-probabilities
@@ -833,7 +845,7 @@ class PolicyWorker:
             items = [(*self._pack(mb), idx) for mb, idx in self._microbatches(data, mbs, self._token_budget("logprob"))]
 
             def stage(item, h_in):
-                if self.model.last_stage:
+                if self.model.at_output:
                     return self._policy_logprobs(item[0], h_in=h_in)
                 return self.model.hidden_states(item[0], h_in)
 
@@ -1034,7 +1046,7 @@ class PolicyWorker:
 
         def stage(item, h_in):
             batch, S, mb_dev = item
-            if not self.model.last_stage:
+            if not self.model.at_output:
                 return self.model.hidden_states(batch, h_in)
             inputs = self._loss_inputs(loss_fn, batch, S, mb_dev, h_in)
             loss, metrics = loss_fn(data=mb_dev, global_valid_seqs=global_valid_seqs, global_valid_toks=global_valid_toks, **inputs)

@@ -104,7 +104,7 @@ class _GradView:
     """Presents a model's gradients under its parameter names so that the HF mapping can gather them."""
 
     def __init__(self, model):
-        self.__dict__.update(cfg=model.cfg, tp=model.tp, ep=model.ep, layer_offset=model.layer_offset, layers=model.layers,
+        self.__dict__.update(cfg=model.cfg, tp=model.tp, ep=model.ep, layer_offset=model.layer_offset, layer_ids=model.layer_ids, layers=model.layers,
                              first_stage=model.first_stage, last_stage=model.last_stage)
         self._m = model
 
@@ -180,13 +180,16 @@ def _train_data():
                            token_mask=torch.ones(4, 24), sample_mask=torch.ones(4))
 
 
-def _pp_worker(rank, world, tied, tp):
+def _pp_worker(rank, world, tied, tp, vpp=1, layers=None):
     from rl_b200.algorithms.loss.loss_functions import NLLLossFn
     from rl_b200.models.config import preset
     from rl_b200.policy.worker import PolicyWorker
 
-    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied)
-    w = PolicyWorker(_worker_cfg(pipeline_parallel_size=world // tp, tensor_parallel_size=tp), model_cfg=mc, init_reference_model=False, seed=4)
+    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied, **({"num_hidden_layers": layers} if layers else {}))
+    w = PolicyWorker(_worker_cfg(pipeline_parallel_size=world // tp, tensor_parallel_size=tp, virtual_pipeline_stages=vpp), model_cfg=mc,
+                     init_reference_model=False, seed=4)
+    if vpp > 1:
+        assert w.model.vpp == vpp and len(w.model.chunk_bounds) == vpp and w.pipeline.vpp == vpp
     data = _train_data()
     lp = w.get_logprobs(data)["logprobs"]
     outs = [w.train(data, NLLLossFn(), gbs=4, mbs=1) for _ in range(2)]
@@ -194,14 +197,14 @@ def _pp_worker(rank, world, tied, tp):
     return dict(lp=lp.sum().item(), lp2=lp2.sum().item(), loss=[float(o["loss"][0]) for o in outs], gn=[float(o["grad_norm"][0]) for o in outs])
 
 
-def _single_reference(tied):
+def _single_reference(tied, layers=None):
     from rl_b200.algorithms.loss.loss_functions import NLLLossFn
     from rl_b200.models.config import preset
     from rl_b200.parallel.state import reset_parallel
     from rl_b200.policy.worker import PolicyWorker
 
     reset_parallel()
-    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied)
+    mc = preset("tiny-llama-oracle", torch_dtype="float32", tie_word_embeddings=tied, **({"num_hidden_layers": layers} if layers else {}))
     w = PolicyWorker(_worker_cfg(), model_cfg=mc, init_reference_model=False, seed=4)
     data = _train_data()
     lp = w.get_logprobs(data)["logprobs"]
@@ -556,3 +559,78 @@ def test_single_controller_on_two_ranks_stays_in_lock_step():
     assert a["steps"] == b["steps"] == 3 and a["trained"] == b["trained"] == 3 * 4
     assert a["loss"] == pytest.approx(b["loss"]) and a["gn"] == pytest.approx(b["gn"])     # global-batch metrics agree
     assert a["w"] == pytest.approx(b["w"], rel=1e-12) and max(a["ages"]) <= 1             # replicas hold the same weights
+
+
+@pytest.mark.parametrize("world,tp,tied,vpp,layers", [(2, 1, False, 2, 4), (2, 1, True, 2, 5), (4, 2, False, 3, 6)])
+def test_interleaved_pipeline_worker_matches_single_rank(world, tp, tied, vpp, layers):
+    """Virtual pipeline stages: every rank owns ``vpp`` runs of layers (the last run may be short or empty) and the interleaved
+    schedule gives the single-rank losses, gradient norms and updated log-probabilities."""
+    ref = _single_reference(tied, layers)
+    out = _spawn(_pp_worker, world, tied, tp, vpp, layers)
+    for r, m in out.items():
+        assert m["lp"] == pytest.approx(ref["lp"], rel=1e-5), (r, m, ref)
+        assert m["loss"] == pytest.approx(ref["loss"], rel=1e-4), (r, m, ref)
+        assert m["gn"] == pytest.approx(ref["gn"], rel=2e-3), (r, m, ref)
+        assert m["lp2"] == pytest.approx(ref["lp2"], rel=1e-4), (r, m, ref)
+
+
+@pytest.mark.parametrize("P,V,n", [(2, 2, 4), (3, 2, 6), (4, 2, 8), (4, 4, 16), (8, 3, 16), (4, 2, 5), (3, 4, 1)])
+def test_interleaved_schedule_is_complete_ordered_and_tight(P, V, n):
+    from rl_b200.parallel.pipeline import interleaved_schedule
+
+    for train in (True, False):
+        ticks = interleaved_schedule(P, V, n, train)
+        arrived, done = set(), set()
+        for ops, msgs in ticks:
+            for r, o in enumerate(ops):
+                if o is None:
+                    continue
+                kind, m, c = o
+                s = c * P + r
+                assert (r, kind, m, c) not in done
+                if kind == "F":
+                    assert s == 0 or (r, "F", m, c) in arrived           # the activation got here in an earlier tick
+                else:
+                    assert (r, "F", m, c) in done and (s == P * V - 1 or (r, "B", m, c) in arrived)
+                done.add((r, kind, m, c))
+            for (src, dst, kind, m, c) in msgs:
+                assert ops[src] is not None and dst == (src + (1 if kind == "F" else -1)) % P
+                arrived.add((dst, kind, m, c))
+        assert len(done) == (2 if train else 1) * n * V * P              # every chunk of every micro-batch ran on every rank
+        if n % P == 0 and train:   # the bubble is 2 (P - 1) chunk-sized slots, i.e. 1 / V of the plain schedule's
+            assert len(ticks) == 2 * n * V + 2 * (P - 1)
+        if not train:
+            assert len(ticks) >= n * V + P - 1
+
+
+def test_parallel_sizes_reads_both_spellings_of_virtual_stages():
+    from rl_b200.policy.worker import parallel_sizes
+
+    assert parallel_sizes(dict(parallel=dict(pipeline_parallel_size=2, virtual_pipeline_stages=3)))["vpp"] == 3
+    mg = dict(megatron_cfg=dict(enabled=True, pipeline_model_parallel_size=4, virtual_pipeline_model_parallel_size=2))
+    assert parallel_sizes(mg)["vpp"] == 2 and parallel_sizes(mg)["pp"] == 4
+    mg = dict(megatron_cfg=dict(enabled=True, pipeline_model_parallel_size=2, num_layers_per_virtual_pipeline_stage=4))
+    assert parallel_sizes(mg, num_layers=32)["vpp"] == 4 and parallel_sizes(mg)["vpp"] == 1
+    with pytest.raises(ValueError):
+        parallel_sizes(dict(parallel=dict(virtual_pipeline_stages=2)))
+
+
+def test_interleaved_stages_cover_the_checkpoint_names_once():
+    """The chunks of all pipeline ranks together hold every HF tensor exactly once (the embedding twice when it is tied and the
+    last rank needs it for the output head), under the same names and values as the whole model."""
+    from rl_b200.models.config import preset
+    from rl_b200.models.hf_io import iter_hf_tensors, load_hf_tensors
+    from rl_b200.models.transformer import build_model
+
+    cfg = preset("tiny-llama-oracle", torch_dtype="float32", num_hidden_layers=7)
+    full = build_model(cfg, dtype=torch.float32, seed=3)
+    sd = dict(iter_hf_tensors(full))
+    seen: dict = {}
+    for r in range(2):
+        part = build_model(cfg, dtype=torch.float32, seed=50 + r, pp_rank=r, pp_size=2, vpp=3)
+        assert part.layer_ids == [i for c in range(3) for i in range((c * 2 + r) * 2, min(7, (c * 2 + r) * 2 + 2))]
+        load_hf_tensors(part, sd.get)
+        for n, t in iter_hf_tensors(part):
+            assert n not in seen and torch.equal(t, sd[n]), n
+            seen[n] = r
+    assert set(seen) == set(sd)
